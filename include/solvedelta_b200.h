@@ -1,0 +1,128 @@
+/*
+ * solvedelta_b200 -- C ABI of the B200 (sm_100a) SolveDelta chunked recurrence.
+ *
+ * Plain pointers and sizes only.  Every device pointer is memory of the GPU
+ * that is current when the call is made; the library allocates nothing
+ * (callers pass the `saved` and `scratch` buffers, sized by the query
+ * functions), launches only asynchronous work on the stream it is given and
+ * never synchronises.  Functions return 0 on success and a negative
+ * sd_status otherwise; nothing throws, nothing exits.
+ *
+ * Upstream interfaces these entry points stand in for (paths inside the
+ * SolveDelta project):
+ *   sd_forward      causallsso/ops/operator.py:13-55 (solvedelta_native) ->
+ *                   causallsso/ops/residual_frame/operator.py:154-304
+ *                   (solvedelta_residual_frame_native, dense branch)
+ *   sd_backward     the autograd reverse of the same call:
+ *                   causallsso/ops/residual_frame/operator.py:74-138
+ *                   (_RelativeExterior.backward),
+ *                   causallsso/ops/residual_frame/predictor.py:129-282
+ *                   (_OjaResidual.backward),
+ *                   causallsso/ops/residual_frame/l2norm.py:129-146
+ *   sd_decode_step  causallsso/ops/residual_frame/recurrent.py:188-327
+ *                   (solvedelta_recurrent_inference, T = 1, no grad)
+ *
+ * Tensor contract (same as upstream): u, h, q, keys, values, erase_raw,
+ * write_raw are BF16 with unit innermost stride and arbitrary outer strides
+ * (views into a fused projection row are legal); log_decay and gamma are FP32;
+ * the continuation states are FP32, contiguous, C [B,H,r,r] with
+ * prediction = C u and S [B,H,r,V].  r and V may be any value in 1..128.
+ */
+#ifndef SOLVEDELTA_B200_H
+#define SOLVEDELTA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    SD_OK = 0,
+    SD_ERR_INVALID_ARGUMENT = -1, /* null pointer, non-positive size, bad stride */
+    SD_ERR_UNSUPPORTED_SHAPE = -2, /* r or V outside 1..128 */
+    SD_ERR_BUFFER_TOO_SMALL = -3,  /* saved / scratch smaller than the query says */
+    SD_ERR_LAUNCH_FAILED = -4,     /* the CUDA runtime refused a launch */
+    SD_ERR_NO_DEVICE = -5          /* no CUDA device / wrong architecture */
+} sd_status;
+
+/* A strided [B,T,H,width] operand: element strides of batch, token, head. */
+typedef struct {
+    const void *ptr;
+    int64_t stride_b, stride_t, stride_h;
+} sd_operand;
+
+typedef struct {
+    int32_t B, T, H, r, V;
+} sd_shape;
+
+typedef struct {
+    sd_shape shape;
+    sd_operand u, h, q, keys, values;  /* BF16, widths r,r,r,r,V */
+    sd_operand erase_raw, write_raw;    /* BF16 raw gate logits, widths r,V */
+    sd_operand log_decay;               /* FP32, width r, values <= 0 */
+    sd_operand gamma;                   /* FP32, width 1 (per token; strides may be 0) */
+    const float *C0, *S0;               /* initial states or NULL (= zero) */
+    void *y;                            /* out: BF16 contiguous [B,T,H,V] */
+    float *C_T, *S_T;                   /* out: final states or NULL */
+    void *saved;                        /* out: kept for sd_backward (sd_saved_bytes) */
+    size_t saved_bytes;
+    void *scratch;                      /* temporary (sd_forward_scratch_bytes) */
+    size_t scratch_bytes;
+} sd_forward_args;
+
+typedef struct {
+    sd_shape shape;
+    sd_operand u, h, q, keys, values, erase_raw, write_raw, log_decay, gamma;
+    sd_operand dy;                      /* BF16 upstream gradient of y, width V */
+    const float *dC_T, *dS_T;           /* gradients of the final states or NULL */
+    const void *saved;                  /* what sd_forward wrote */
+    size_t saved_bytes;
+    void *scratch;                      /* temporary (sd_backward_scratch_bytes) */
+    size_t scratch_bytes;
+    /* outputs, all contiguous: BF16 [B,T,H,width] ... */
+    void *du, *dh, *dq, *dkeys, *dvalues, *derase_raw, *dwrite_raw;
+    float *dlog_decay;                  /* FP32 [B,T,H,r] */
+    float *dgamma;                      /* FP32 [B,T,H] */
+    float *dC0, *dS0;                   /* FP32 or NULL */
+} sd_backward_args;
+
+typedef struct {
+    sd_shape shape;                     /* T must be 1 */
+    sd_operand u, h, q, keys, values, erase_raw, write_raw, log_decay, gamma;
+    float *C, *S;                       /* in/out recurrent cache, updated in place */
+    void *y;                            /* out: BF16 [B,1,H,V] */
+} sd_decode_args;
+
+/* Bytes of the buffer sd_forward fills for sd_backward. */
+size_t sd_saved_bytes(const sd_shape *shape);
+size_t sd_forward_scratch_bytes(const sd_shape *shape);
+size_t sd_backward_scratch_bytes(const sd_shape *shape);
+
+/* `stream` is a cudaStream_t passed as void* (NULL = legacy default stream). */
+int sd_forward(const sd_forward_args *args, void *stream);
+int sd_backward(const sd_backward_args *args, void *stream);
+int sd_decode_step(const sd_decode_args *args, void *stream);
+
+/* Number of kernels one call launches for this shape (for accounting). */
+int sd_forward_launches(const sd_shape *shape);
+int sd_backward_launches(const sd_shape *shape);
+
+/*
+ * Introspection for tests: offset and size of a named intermediate panel
+ * inside the saved (which = 0), forward-scratch (1) or backward-scratch (2)
+ * buffer.  Returns SD_ERR_INVALID_ARGUMENT for an unknown name.
+ */
+int sd_panel_info(const sd_shape *shape, int which, const char *name,
+                  size_t *offset, size_t *bytes);
+
+const char *sd_status_string(int status);
+int sd_version(void);
+/* Tokens per chunk of the chunked scan (a private tuning constant upstream). */
+int sd_chunk_tokens(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SOLVEDELTA_B200_H */

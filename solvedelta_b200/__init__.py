@@ -1,0 +1,24 @@
+"""B200-native SolveDelta chunked recurrence (forward + full VJP).
+
+Drop-in for the upstream operator entry points
+(causallsso/ops/__init__.py:3, causallsso/ops/operator.py:13-26):
+``solvedelta_native`` keeps its name, signature, dtype/stride contract,
+error types and autograd behaviour; the arithmetic runs in hand-written
+sm_100a CUDA kernels behind a C ABI (include/solvedelta_b200.h).
+"""
+from ._lib import build, load
+from .ops import (
+    SolveDeltaState,
+    solvedelta_native,
+    solvedelta_residual_frame_native,
+    solvedelta_zero_state,
+)
+
+__all__ = [
+    "SolveDeltaState",
+    "build",
+    "load",
+    "solvedelta_native",
+    "solvedelta_residual_frame_native",
+    "solvedelta_zero_state",
+]

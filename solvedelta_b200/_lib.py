@@ -1,0 +1,153 @@
+"""Loader and builder of the CUDA library behind the C ABI.
+
+The shared object is built in-tree (``solvedelta_b200/_build``) with nvcc for
+sm_100a and loaded through ctypes; the structures below mirror
+``include/solvedelta_b200.h`` field by field.  There is no fallback: if the
+library is missing, every entry point raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import shutil
+import subprocess
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+_ROOT = os.path.dirname(_PKG)
+_SRC = os.path.join(_PKG, "csrc")
+_BUILD = os.path.join(_PKG, "_build")
+LIB_PATH = os.path.join(_BUILD, "libsolvedelta_b200.so")
+HEADER_PATH = os.path.join(_ROOT, "include", "solvedelta_b200.h")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--expt-extended-lambda", "-shared", "-Xcompiler", "-fPIC",
+]
+
+
+def _sources():
+    out = [HEADER_PATH]
+    for name in sorted(os.listdir(_SRC)):
+        if name.endswith((".cu", ".cuh", ".h")):
+            out.append(os.path.join(_SRC, name))
+    return out
+
+
+def _nvcc():
+    for cand in (shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    return None
+
+
+def is_stale() -> bool:
+    if not os.path.exists(LIB_PATH):
+        return True
+    built = os.path.getmtime(LIB_PATH)
+    return any(os.path.getmtime(s) > built for s in _sources())
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile csrc/*.cu into the in-tree shared library (sm_100a only)."""
+    if not force and not is_stale():
+        return LIB_PATH
+    nvcc = _nvcc()
+    if nvcc is None:
+        raise RuntimeError("nvcc not found: cannot build libsolvedelta_b200.so")
+    os.makedirs(_BUILD, exist_ok=True)
+    units = [os.path.join(_SRC, n) for n in sorted(os.listdir(_SRC)) if n.endswith(".cu")]
+    cmd = [nvcc, *NVCC_FLAGS, "-o", LIB_PATH, *units]
+    if verbose:
+        cmd.insert(1, "-Xptxas")
+        cmd.insert(2, "-v")
+    subprocess.check_call(cmd)
+    return LIB_PATH
+
+
+class Shape(ctypes.Structure):
+    _fields_ = [("B", ctypes.c_int32), ("T", ctypes.c_int32), ("H", ctypes.c_int32),
+                ("r", ctypes.c_int32), ("V", ctypes.c_int32)]
+
+
+class Operand(ctypes.Structure):
+    _fields_ = [("ptr", ctypes.c_void_p), ("stride_b", ctypes.c_int64),
+                ("stride_t", ctypes.c_int64), ("stride_h", ctypes.c_int64)]
+
+
+_OPERANDS = ("u", "h", "q", "keys", "values", "erase_raw", "write_raw", "log_decay", "gamma")
+
+
+class ForwardArgs(ctypes.Structure):
+    _fields_ = ([("shape", Shape)] + [(n, Operand) for n in _OPERANDS] + [
+        ("C0", ctypes.c_void_p), ("S0", ctypes.c_void_p), ("y", ctypes.c_void_p),
+        ("C_T", ctypes.c_void_p), ("S_T", ctypes.c_void_p),
+        ("saved", ctypes.c_void_p), ("saved_bytes", ctypes.c_size_t),
+        ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t)])
+
+
+class BackwardArgs(ctypes.Structure):
+    _fields_ = ([("shape", Shape)] + [(n, Operand) for n in _OPERANDS] + [
+        ("dy", Operand), ("dC_T", ctypes.c_void_p), ("dS_T", ctypes.c_void_p),
+        ("saved", ctypes.c_void_p), ("saved_bytes", ctypes.c_size_t),
+        ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t),
+        ("du", ctypes.c_void_p), ("dh", ctypes.c_void_p), ("dq", ctypes.c_void_p),
+        ("dkeys", ctypes.c_void_p), ("dvalues", ctypes.c_void_p),
+        ("derase_raw", ctypes.c_void_p), ("dwrite_raw", ctypes.c_void_p),
+        ("dlog_decay", ctypes.c_void_p), ("dgamma", ctypes.c_void_p),
+        ("dC0", ctypes.c_void_p), ("dS0", ctypes.c_void_p)])
+
+
+class DecodeArgs(ctypes.Structure):
+    _fields_ = ([("shape", Shape)] + [(n, Operand) for n in _OPERANDS] + [
+        ("C", ctypes.c_void_p), ("S", ctypes.c_void_p), ("y", ctypes.c_void_p)])
+
+
+EXPORTS = (
+    "sd_saved_bytes", "sd_forward_scratch_bytes", "sd_backward_scratch_bytes",
+    "sd_forward", "sd_backward", "sd_decode_step", "sd_forward_launches",
+    "sd_backward_launches", "sd_panel_info", "sd_status_string", "sd_version",
+    "sd_chunk_tokens",
+)
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Return the loaded library; raise if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -c 'import solvedelta_b200; "
+            "solvedelta_b200.build()'` (needs nvcc); there is no fallback path")
+    lib = ctypes.CDLL(LIB_PATH)
+    sp = ctypes.POINTER(Shape)
+    for name in ("sd_saved_bytes", "sd_forward_scratch_bytes", "sd_backward_scratch_bytes"):
+        getattr(lib, name).restype = ctypes.c_size_t
+        getattr(lib, name).argtypes = [sp]
+    lib.sd_forward.restype = ctypes.c_int
+    lib.sd_forward.argtypes = [ctypes.POINTER(ForwardArgs), ctypes.c_void_p]
+    lib.sd_backward.restype = ctypes.c_int
+    lib.sd_backward.argtypes = [ctypes.POINTER(BackwardArgs), ctypes.c_void_p]
+    lib.sd_decode_step.restype = ctypes.c_int
+    lib.sd_decode_step.argtypes = [ctypes.POINTER(DecodeArgs), ctypes.c_void_p]
+    lib.sd_forward_launches.restype = ctypes.c_int
+    lib.sd_forward_launches.argtypes = [sp]
+    lib.sd_backward_launches.restype = ctypes.c_int
+    lib.sd_backward_launches.argtypes = [sp]
+    lib.sd_panel_info.restype = ctypes.c_int
+    lib.sd_panel_info.argtypes = [sp, ctypes.c_int, ctypes.c_char_p,
+                                  ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)]
+    lib.sd_status_string.restype = ctypes.c_char_p
+    lib.sd_status_string.argtypes = [ctypes.c_int]
+    lib.sd_version.restype = ctypes.c_int
+    lib.sd_chunk_tokens.restype = ctypes.c_int
+    _lib = lib
+    return lib
+
+
+def check(status: int) -> None:
+    if status != 0:
+        msg = load().sd_status_string(status).decode()
+        raise RuntimeError(f"solvedelta_b200: {msg} (status {status})")

@@ -1,0 +1,351 @@
+// C ABI of the SolveDelta chunked recurrence for B200 (sm_100a).
+// Declarations and the upstream interfaces they replace: include/solvedelta_b200.h
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/solvedelta_b200.h"
+#include "sd_backward.cuh"
+#include "sd_common.cuh"
+#include "sd_decode.cuh"
+#include "sd_forward.cuh"
+#include "sd_scan.cuh"
+
+namespace {
+
+using namespace sd;
+
+struct PanelDesc {
+    const char* name;
+    int kind;  // 0 = panel [CL][DP], 1 = matrix [CL][CL], 2 = state [DP][DP], 3 = vector [DP]
+};
+
+const PanelDesc kSaved[] = {{"Lam", 3}, {"Delta", 0}, {"Dprim", 0}, {"Zt", 0}, {"CtCk", 2}, {"SCk", 2}};
+const PanelDesc kFwd[] = {{"Upd", 0}, {"Qc", 0}, {"Ubar", 0}, {"Wd", 0}, {"Ud", 0}, {"Dt", 0}, {"Xg", 0}, {"Aqd", 1}};
+const PanelDesc kBwd[] = {{"Pp", 0},     {"Qp", 0},     {"Ag", 0},     {"Xg", 0},    {"Dyf", 0},   {"Dneg", 0},
+                          {"dR", 0},     {"dSeCk", 2},  {"A1", 0},     {"A2", 0},    {"PY", 0},    {"dDt", 0},
+                          {"SdS", 3},    {"duPart", 0}, {"dkPart", 0}, {"dGPart", 0}, {"dDelta", 0}, {"DG", 0},
+                          {"Xext", 0},   {"Tpre", 0},   {"Khat", 0},   {"Ppp", 0},   {"Qpp", 0},   {"Rneg", 0},
+                          {"dRr", 0},    {"dCeCk", 2},  {"dUbar", 0},  {"dUt", 0},   {"Ti", 0},    {"Tj", 0},
+                          {"CdC", 3}};
+
+size_t kind_floats(int kind) {
+    switch (kind) {
+        case 0: return size_t(CL) * DP;
+        case 1: return size_t(CL) * CL;
+        case 2: return size_t(DP) * DP;
+        default: return DP;
+    }
+}
+
+bool shape_ok(const sd_shape* s) {
+    return s && s->B > 0 && s->T > 0 && s->H > 0 && s->r > 0 && s->V > 0;
+}
+bool shape_supported(const sd_shape* s) { return s->r <= DP && s->V <= DP; }
+
+long long total_chunks(const sd_shape* s) {
+    long long nc = (s->T + CL - 1) / CL;
+    return nc * s->B * s->H;
+}
+
+template <size_t N>
+size_t layout_bytes(const PanelDesc (&tab)[N], const sd_shape* s) {
+    size_t chunks = (size_t)total_chunks(s), total = 0;
+    for (size_t i = 0; i < N; ++i) {
+        size_t bytes = kind_floats(tab[i].kind) * chunks * sizeof(float);
+        total += (bytes + 255) & ~size_t(255);
+    }
+    return total;
+}
+
+template <size_t N>
+bool layout_find(const PanelDesc (&tab)[N], const sd_shape* s, const char* name, size_t* off, size_t* bytes) {
+    size_t chunks = (size_t)total_chunks(s), total = 0;
+    for (size_t i = 0; i < N; ++i) {
+        size_t b = kind_floats(tab[i].kind) * chunks * sizeof(float);
+        if (std::strcmp(tab[i].name, name) == 0) {
+            *off = total;
+            *bytes = b;
+            return true;
+        }
+        total += (b + 255) & ~size_t(255);
+    }
+    return false;
+}
+
+template <size_t N>
+float* panel_at(const PanelDesc (&tab)[N], const sd_shape* s, void* base, const char* name) {
+    size_t off = 0, bytes = 0;
+    if (!layout_find(tab, s, name, &off, &bytes)) return nullptr;
+    return reinterpret_cast<float*>(reinterpret_cast<char*>(base) + off);
+}
+
+Operand make_operand(const sd_operand& o, int elem_bytes) {
+    Operand r;
+    r.ptr = o.ptr;
+    r.sb = o.stride_b;
+    r.st = o.stride_t;
+    r.sh = o.stride_h;
+    const long long per16 = 16 / elem_bytes;
+    r.vec = ((reinterpret_cast<uintptr_t>(o.ptr) & 15) == 0 && o.stride_b % per16 == 0 && o.stride_t % per16 == 0 &&
+             o.stride_h % per16 == 0)
+                ? 1
+                : 0;
+    return r;
+}
+
+Geometry make_geometry(const sd_shape& s) {
+    Geometry g;
+    g.B = s.B; g.T = s.T; g.H = s.H; g.r = s.r; g.V = s.V;
+    g.NC = (s.T + CL - 1) / CL;
+    return g;
+}
+
+template <class K>
+cudaError_t allow_smem(K kernel, size_t bytes) {
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
+// Opt-in to large dynamic shared memory, once per device.  The flag array only
+// caches that the (idempotent) attribute calls were made.
+cudaError_t configure_kernels() {
+    static bool done[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64 && done[dev]) return cudaSuccess;
+    if ((e = allow_smem(k_prep_fwd, PREP_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_primal_fwd, PRIMAL_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_prep_fwd, EXT_PREP_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_output_fwd, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_state_scan, SCAN_SMEM_BYTES)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_prep_bwd, EXT_PREP_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_pair_bwd, EXT_PAIR_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_sources_bwd, SOURCES_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_primal_bwd, PRIMAL_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_predictor_prep_bwd, PRED_PREP_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_predictor_pair_bwd, PRED_PAIR_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_gate_closure_bwd, GATE_CLOSURE_SMEM)) != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) done[dev] = true;
+    return cudaSuccess;
+}
+
+int launch_status() { return cudaGetLastError() == cudaSuccess ? SD_OK : SD_ERR_LAUNCH_FAILED; }
+
+bool operands_ok(const sd_operand* ops, int n) {
+    for (int i = 0; i < n; ++i)
+        if (ops[i].ptr == nullptr) return false;
+    return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t sd_saved_bytes(const sd_shape* shape) {
+    if (!shape_ok(shape) || !shape_supported(shape)) return 0;
+    return layout_bytes(kSaved, shape);
+}
+size_t sd_forward_scratch_bytes(const sd_shape* shape) {
+    if (!shape_ok(shape) || !shape_supported(shape)) return 0;
+    return layout_bytes(kFwd, shape);
+}
+size_t sd_backward_scratch_bytes(const sd_shape* shape) {
+    if (!shape_ok(shape) || !shape_supported(shape)) return 0;
+    return layout_bytes(kBwd, shape);
+}
+
+int sd_panel_info(const sd_shape* shape, int which, const char* name, size_t* offset, size_t* bytes) {
+    if (!shape_ok(shape) || !name || !offset || !bytes) return SD_ERR_INVALID_ARGUMENT;
+    if (!shape_supported(shape)) return SD_ERR_UNSUPPORTED_SHAPE;
+    bool found = false;
+    if (which == 0) found = layout_find(kSaved, shape, name, offset, bytes);
+    if (which == 1) found = layout_find(kFwd, shape, name, offset, bytes);
+    if (which == 2) found = layout_find(kBwd, shape, name, offset, bytes);
+    return found ? SD_OK : SD_ERR_INVALID_ARGUMENT;
+}
+
+int sd_forward_launches(const sd_shape* shape) { return shape_ok(shape) ? 6 : 0; }
+int sd_backward_launches(const sd_shape* shape) { return shape_ok(shape) ? 9 : 0; }
+int sd_chunk_tokens(void) { return CL; }
+int sd_version(void) { return 1; }
+
+const char* sd_status_string(int status) {
+    switch (status) {
+        case SD_OK: return "ok";
+        case SD_ERR_INVALID_ARGUMENT: return "invalid argument";
+        case SD_ERR_UNSUPPORTED_SHAPE: return "unsupported shape (r and V must be in 1..128)";
+        case SD_ERR_BUFFER_TOO_SMALL: return "saved or scratch buffer too small";
+        case SD_ERR_LAUNCH_FAILED: return "CUDA launch failed";
+        case SD_ERR_NO_DEVICE: return "no usable CUDA device";
+        default: return "unknown status";
+    }
+}
+
+int sd_forward(const sd_forward_args* a, void* stream_) {
+    if (!a || !shape_ok(&a->shape)) return SD_ERR_INVALID_ARGUMENT;
+    if (!shape_supported(&a->shape)) return SD_ERR_UNSUPPORTED_SHAPE;
+    const sd_operand ops[] = {a->u, a->h, a->q, a->keys, a->values, a->erase_raw, a->write_raw, a->log_decay, a->gamma};
+    if (!operands_ok(ops, 9) || !a->y || !a->saved || !a->scratch) return SD_ERR_INVALID_ARGUMENT;
+    if (a->saved_bytes < sd_saved_bytes(&a->shape) || a->scratch_bytes < sd_forward_scratch_bytes(&a->shape))
+        return SD_ERR_BUFFER_TOO_SMALL;
+    if ((reinterpret_cast<uintptr_t>(a->saved) & 15) || (reinterpret_cast<uintptr_t>(a->scratch) & 15))
+        return SD_ERR_INVALID_ARGUMENT;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (configure_kernels() != cudaSuccess) return SD_ERR_NO_DEVICE;
+
+    const sd_shape* s = &a->shape;
+    FwdParams p;
+    p.g = make_geometry(*s);
+    p.u = make_operand(a->u, 2);
+    p.h = make_operand(a->h, 2);
+    p.q = make_operand(a->q, 2);
+    p.k = make_operand(a->keys, 2);
+    p.v = make_operand(a->values, 2);
+    p.er = make_operand(a->erase_raw, 2);
+    p.wr = make_operand(a->write_raw, 2);
+    p.ld = make_operand(a->log_decay, 4);
+    p.gam = make_operand(a->gamma, 4);
+    p.Upd = panel_at(kFwd, s, a->scratch, "Upd");
+    p.Qc = panel_at(kFwd, s, a->scratch, "Qc");
+    p.Ubar = panel_at(kFwd, s, a->scratch, "Ubar");
+    p.Wd = panel_at(kFwd, s, a->scratch, "Wd");
+    p.Ud = panel_at(kFwd, s, a->scratch, "Ud");
+    p.Dt = panel_at(kFwd, s, a->scratch, "Dt");
+    p.Xg = panel_at(kFwd, s, a->scratch, "Xg");
+    p.Aqd = panel_at(kFwd, s, a->scratch, "Aqd");
+    p.Lam = panel_at(kSaved, s, a->saved, "Lam");
+    p.Delta = panel_at(kSaved, s, a->saved, "Delta");
+    p.Dprim = panel_at(kSaved, s, a->saved, "Dprim");
+    p.Zt = panel_at(kSaved, s, a->saved, "Zt");
+    p.CtCk = panel_at(kSaved, s, a->saved, "CtCk");
+    p.SCk = panel_at(kSaved, s, a->saved, "SCk");
+    p.y = a->y;
+
+    const int chunks = (int)total_chunks(s);
+    const int streams = s->B * s->H;
+    const dim3 scan_grid(DP / SCAN_NS, streams);
+
+    k_prep_fwd<<<chunks, NTHREADS, PREP_FWD_SMEM, stream>>>(p);
+    {
+        ScanParams sp{};
+        sp.P = p.Upd; sp.Q = p.Qc; sp.R = p.Ubar; sp.R2 = nullptr; sp.X2 = nullptr;
+        sp.lam = p.Lam; sp.X = p.Delta; sp.ck = p.CtCk;
+        sp.init = a->C0; sp.fin = a->C_T;
+        sp.NC = p.g.NC; sp.reverse = 0; sp.transposed_io = 1; sp.nrows = s->r; sp.ncols = s->r;
+        k_state_scan<<<scan_grid, NTHREADS, SCAN_SMEM_BYTES, stream>>>(sp);
+    }
+    k_primal_fwd<<<chunks, NTHREADS, PRIMAL_FWD_SMEM, stream>>>(p);
+    k_exterior_prep_fwd<<<chunks, NTHREADS, EXT_PREP_FWD_SMEM, stream>>>(p);
+    {
+        ScanParams sp{};
+        sp.P = p.Ud; sp.Q = p.Wd; sp.R = p.Dt; sp.R2 = nullptr; sp.X2 = nullptr;
+        sp.lam = p.Lam; sp.X = p.Zt; sp.ck = p.SCk;
+        sp.init = a->S0; sp.fin = a->S_T;
+        sp.NC = p.g.NC; sp.reverse = 0; sp.transposed_io = 0; sp.nrows = s->r; sp.ncols = s->V;
+        k_state_scan<<<scan_grid, NTHREADS, SCAN_SMEM_BYTES, stream>>>(sp);
+    }
+    k_output_fwd<<<chunks, NTHREADS, OUTPUT_FWD_SMEM, stream>>>(p);
+    return launch_status();
+}
+
+int sd_backward(const sd_backward_args* a, void* stream_) {
+    if (!a || !shape_ok(&a->shape)) return SD_ERR_INVALID_ARGUMENT;
+    if (!shape_supported(&a->shape)) return SD_ERR_UNSUPPORTED_SHAPE;
+    const sd_operand ops[] = {a->u,         a->h,         a->q,         a->keys,  a->values,
+                              a->erase_raw, a->write_raw, a->log_decay, a->gamma, a->dy};
+    if (!operands_ok(ops, 10) || !a->saved || !a->scratch) return SD_ERR_INVALID_ARGUMENT;
+    if (!a->du || !a->dh || !a->dq || !a->dkeys || !a->dvalues || !a->derase_raw || !a->dwrite_raw ||
+        !a->dlog_decay || !a->dgamma)
+        return SD_ERR_INVALID_ARGUMENT;
+    if (a->saved_bytes < sd_saved_bytes(&a->shape) || a->scratch_bytes < sd_backward_scratch_bytes(&a->shape))
+        return SD_ERR_BUFFER_TOO_SMALL;
+    if ((reinterpret_cast<uintptr_t>(a->saved) & 15) || (reinterpret_cast<uintptr_t>(a->scratch) & 15))
+        return SD_ERR_INVALID_ARGUMENT;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (configure_kernels() != cudaSuccess) return SD_ERR_NO_DEVICE;
+
+    const sd_shape* s = &a->shape;
+    BwdParams p;
+    p.g = make_geometry(*s);
+    p.u = make_operand(a->u, 2);
+    p.h = make_operand(a->h, 2);
+    p.q = make_operand(a->q, 2);
+    p.k = make_operand(a->keys, 2);
+    p.v = make_operand(a->values, 2);
+    p.er = make_operand(a->erase_raw, 2);
+    p.wr = make_operand(a->write_raw, 2);
+    p.ld = make_operand(a->log_decay, 4);
+    p.gam = make_operand(a->gamma, 4);
+    p.dy = make_operand(a->dy, 2);
+    void* sv = const_cast<void*>(a->saved);
+    p.Lam = panel_at(kSaved, s, sv, "Lam");
+    p.Delta = panel_at(kSaved, s, sv, "Delta");
+    p.Dprim = panel_at(kSaved, s, sv, "Dprim");
+    p.Zt = panel_at(kSaved, s, sv, "Zt");
+    p.CtCk = panel_at(kSaved, s, sv, "CtCk");
+    p.SCk = panel_at(kSaved, s, sv, "SCk");
+#define SD_BP(field) p.field = panel_at(kBwd, s, a->scratch, #field)
+    SD_BP(Pp); SD_BP(Qp); SD_BP(Ag); SD_BP(Xg); SD_BP(Dyf); SD_BP(Dneg); SD_BP(dR); SD_BP(dSeCk);
+    SD_BP(A1); SD_BP(A2); SD_BP(PY); SD_BP(dDt); SD_BP(SdS);
+    SD_BP(duPart); SD_BP(dkPart); SD_BP(dGPart); SD_BP(dDelta); SD_BP(DG); SD_BP(Xext); SD_BP(Tpre); SD_BP(Khat);
+    SD_BP(Ppp); SD_BP(Qpp); SD_BP(Rneg); SD_BP(dRr); SD_BP(dCeCk);
+    SD_BP(dUbar); SD_BP(dUt); SD_BP(Ti); SD_BP(Tj); SD_BP(CdC);
+#undef SD_BP
+    p.du = a->du; p.dh = a->dh; p.dq = a->dq; p.dk = a->dkeys; p.dv = a->dvalues;
+    p.der = a->derase_raw; p.dwr = a->dwrite_raw; p.dld = a->dlog_decay; p.dgam = a->dgamma;
+
+    const int chunks = (int)total_chunks(s);
+    const int streams = s->B * s->H;
+    const dim3 scan_grid(DP / SCAN_NS, streams);
+
+    k_exterior_prep_bwd<<<chunks, NTHREADS, EXT_PREP_BWD_SMEM, stream>>>(p);
+    {
+        ScanParams sp{};
+        sp.P = p.Pp; sp.Q = p.Qp; sp.R = p.Ag; sp.R2 = p.Xg; sp.X2 = p.Dyf;
+        sp.lam = p.Lam; sp.X = p.dR; sp.ck = p.dSeCk;
+        sp.init = a->dS_T; sp.fin = a->dS0;
+        sp.NC = p.g.NC; sp.reverse = 1; sp.transposed_io = 0; sp.nrows = s->r; sp.ncols = s->V;
+        k_state_scan<<<scan_grid, NTHREADS, SCAN_SMEM_BYTES, stream>>>(sp);
+    }
+    k_exterior_pair_bwd<<<chunks, NTHREADS, EXT_PAIR_BWD_SMEM, stream>>>(p);
+    k_sources_bwd<<<chunks, NTHREADS, SOURCES_BWD_SMEM, stream>>>(p);
+    k_primal_bwd<<<chunks, NTHREADS, PRIMAL_BWD_SMEM, stream>>>(p);
+    k_predictor_prep_bwd<<<chunks, NTHREADS, PRED_PREP_BWD_SMEM, stream>>>(p);
+    {
+        ScanParams sp{};
+        sp.P = p.Ppp; sp.Q = p.Qpp; sp.R = p.Rneg; sp.R2 = p.DG; sp.X2 = p.Khat;
+        sp.lam = p.Lam; sp.X = p.dRr; sp.ck = p.dCeCk;
+        sp.init = a->dC_T; sp.fin = a->dC0;
+        sp.NC = p.g.NC; sp.reverse = 1; sp.transposed_io = 1; sp.nrows = s->r; sp.ncols = s->r;
+        k_state_scan<<<scan_grid, NTHREADS, SCAN_SMEM_BYTES, stream>>>(sp);
+    }
+    k_predictor_pair_bwd<<<chunks, NTHREADS, PRED_PAIR_BWD_SMEM, stream>>>(p);
+    k_gate_closure_bwd<<<chunks, NTHREADS, GATE_CLOSURE_SMEM, stream>>>(p);
+    return launch_status();
+}
+
+int sd_decode_step(const sd_decode_args* a, void* stream_) {
+    if (!a || !shape_ok(&a->shape) || a->shape.T != 1) return SD_ERR_INVALID_ARGUMENT;
+    if (!shape_supported(&a->shape)) return SD_ERR_UNSUPPORTED_SHAPE;
+    const sd_operand ops[] = {a->u, a->h, a->q, a->keys, a->values, a->erase_raw, a->write_raw, a->log_decay, a->gamma};
+    if (!operands_ok(ops, 9) || !a->C || !a->S || !a->y) return SD_ERR_INVALID_ARGUMENT;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    DecodeParams p;
+    p.g = make_geometry(a->shape);
+    p.u = make_operand(a->u, 2);
+    p.h = make_operand(a->h, 2);
+    p.q = make_operand(a->q, 2);
+    p.k = make_operand(a->keys, 2);
+    p.v = make_operand(a->values, 2);
+    p.er = make_operand(a->erase_raw, 2);
+    p.wr = make_operand(a->write_raw, 2);
+    p.ld = make_operand(a->log_decay, 4);
+    p.gam = make_operand(a->gamma, 4);
+    p.C = a->C;
+    p.S = a->S;
+    p.y = a->y;
+    k_decode_step<<<a->shape.B * a->shape.H, DEC_THREADS, 0, stream>>>(p);
+    return launch_status();
+}
+
+}  // extern "C"

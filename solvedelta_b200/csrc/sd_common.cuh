@@ -1,0 +1,375 @@
+// Shared device helpers of the SolveDelta chunk kernels (sm_100a).
+//
+// A "panel" is the FP32 image of one chunk of one (batch, head) stream:
+// CL token rows by DP channels.  In global memory panels are dense
+// [CL][DP]; in shared memory rows are padded to LDP floats.  r and V may be
+// smaller than DP: the extra channels are zero on load and skipped on store,
+// so one instantiation serves every width up to 128.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace sd {
+
+constexpr int CL = 64;        // tokens per chunk
+constexpr int DP = 128;       // padded channel width
+constexpr int LDP = DP + 4;   // shared-memory row pitch of a panel
+constexpr int LDA = CL + 4;   // row pitch of a CL x CL matrix
+constexpr int LDH = CL + 4;   // row pitch of a [DP][CL] half state (transposed read)
+constexpr int NTHREADS = 256;
+constexpr float RHO = 0.625f; // radius of the residual-local frame
+constexpr float EXP_CLAMP = 80.0f;
+
+constexpr int SLOT_FLOATS = (CL * LDP > DP * LDH) ? CL * LDP : DP * LDH;
+constexpr int MAT_FLOATS = CL * LDA;
+constexpr size_t SLOT_BYTES = size_t(SLOT_FLOATS) * 4;
+constexpr size_t MAT_BYTES = size_t(MAT_FLOATS) * 4;
+
+struct Operand {
+    const void* ptr;
+    long long sb, st, sh;  // element strides
+    int vec;               // 1 when 16-byte vector access is legal
+};
+
+struct Geometry {
+    int B, T, H, r, V, NC;  // NC = chunks per stream
+};
+
+struct Chunk {
+    int s, c, b, hh, t0, nvalid;
+    long long gi;  // global chunk index s * NC + c
+};
+
+__device__ __forceinline__ Chunk chunk_of(const Geometry& g, int idx) {
+    Chunk ch;
+    ch.gi = idx;
+    ch.s = idx / g.NC;
+    ch.c = idx - ch.s * g.NC;
+    ch.b = ch.s / g.H;
+    ch.hh = ch.s - ch.b * g.H;
+    ch.t0 = ch.c * CL;
+    int left = g.T - ch.t0;
+    ch.nvalid = left < CL ? left : CL;
+    return ch;
+}
+
+__device__ __forceinline__ float* panel_ptr(float* base, long long gi) {
+    return base + gi * (long long)(CL * DP);
+}
+__device__ __forceinline__ const float* panel_ptr(const float* base, long long gi) {
+    return base + gi * (long long)(CL * DP);
+}
+__device__ __forceinline__ float* mat_ptr(float* base, long long gi) {
+    return base + gi * (long long)(CL * CL);
+}
+__device__ __forceinline__ const float* mat_ptr(const float* base, long long gi) {
+    return base + gi * (long long)(CL * CL);
+}
+__device__ __forceinline__ float* state_ptr(float* base, long long gi) {
+    return base + gi * (long long)(DP * DP);
+}
+__device__ __forceinline__ const float* state_ptr(const float* base, long long gi) {
+    return base + gi * (long long)(DP * DP);
+}
+
+__device__ __forceinline__ float clamp_exp_neg(float G) {
+    // exp(-G) with the exponent clamped so that strong forgetting stays finite
+    return __expf(fminf(-G, EXP_CLAMP));
+}
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
+
+// ---- half-warp (16 lanes = one token row) reductions ---------------------
+__device__ __forceinline__ float row_sum16(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 8);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    return v;
+}
+
+// ---- strided BF16 / FP32 row access --------------------------------------
+__device__ __forceinline__ const __nv_bfloat16* row_bf16(const Operand& op, const Chunk& ch, int i) {
+    return reinterpret_cast<const __nv_bfloat16*>(op.ptr) + ch.b * op.sb + (long long)(ch.t0 + i) * op.st +
+           ch.hh * op.sh;
+}
+__device__ __forceinline__ const float* row_f32(const Operand& op, const Chunk& ch, int i) {
+    return reinterpret_cast<const float*>(op.ptr) + ch.b * op.sb + (long long)(ch.t0 + i) * op.st + ch.hh * op.sh;
+}
+
+// Eight consecutive channels of a BF16 row; channels >= width read as zero.
+__device__ __forceinline__ void load8_bf16(const __nv_bfloat16* row, int c0, int width, int vec, bool valid,
+                                           float (&x)[8]) {
+    if (!valid || c0 >= width) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = 0.f;
+        return;
+    }
+    if (vec && c0 + 8 <= width) {
+        uint4 raw = *reinterpret_cast<const uint4*>(row + c0);
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float2 f = __bfloat1622float2(p[e]);
+            x[2 * e] = f.x;
+            x[2 * e + 1] = f.y;
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = (c0 + e < width) ? __bfloat162float(row[c0 + e]) : 0.f;
+    }
+}
+
+__device__ __forceinline__ void load8_f32(const float* row, int c0, int width, int vec, bool valid, float (&x)[8]) {
+    if (!valid || c0 >= width) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = 0.f;
+        return;
+    }
+    if (vec && c0 + 8 <= width) {
+        float4 a = *reinterpret_cast<const float4*>(row + c0);
+        float4 b = *reinterpret_cast<const float4*>(row + c0 + 4);
+        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+        x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = (c0 + e < width) ? row[c0 + e] : 0.f;
+    }
+}
+
+// Contiguous outputs [B,T,H,width]: eight channels of one row.
+__device__ __forceinline__ void store8_bf16(void* base, const Geometry& g, const Chunk& ch, int i, int c0,
+                                            int width, const float (&x)[8]) {
+    if (i >= ch.nvalid || c0 >= width) return;
+    __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(base) +
+                         (((long long)ch.b * g.T + ch.t0 + i) * g.H + ch.hh) * (long long)width;
+    if ((width & 7) == 0) {
+        uint4 raw;
+        __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) p[e] = __floats2bfloat162_rn(x[2 * e], x[2 * e + 1]);
+        *reinterpret_cast<uint4*>(row + c0) = raw;
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            if (c0 + e < width) row[c0 + e] = __float2bfloat16_rn(x[e]);
+    }
+}
+
+// ---- dense panel movement -------------------------------------------------
+__device__ __forceinline__ void g2s_panel(float* sm, const float* g) {
+    for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += NTHREADS) {
+        int i = idx >> 5, c4 = (idx & 31) << 2;
+        *reinterpret_cast<float4*>(sm + i * LDP + c4) = *reinterpret_cast<const float4*>(g + i * DP + c4);
+    }
+}
+__device__ __forceinline__ void s2g_panel(float* g, const float* sm) {
+    for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += NTHREADS) {
+        int i = idx >> 5, c4 = (idx & 31) << 2;
+        *reinterpret_cast<float4*>(g + i * DP + c4) = *reinterpret_cast<const float4*>(sm + i * LDP + c4);
+    }
+}
+__device__ __forceinline__ void g2s_mat(float* sm, const float* g) {
+    for (int idx = threadIdx.x; idx < CL * (CL / 4); idx += NTHREADS) {
+        int i = idx >> 4, c4 = (idx & 15) << 2;
+        *reinterpret_cast<float4*>(sm + i * LDA + c4) = *reinterpret_cast<const float4*>(g + i * CL + c4);
+    }
+}
+__device__ __forceinline__ void s2g_mat(float* g, const float* sm) {
+    for (int idx = threadIdx.x; idx < CL * (CL / 4); idx += NTHREADS) {
+        int i = idx >> 4, c4 = (idx & 15) << 2;
+        *reinterpret_cast<float4*>(g + i * CL + c4) = *reinterpret_cast<const float4*>(sm + i * LDA + c4);
+    }
+}
+// Rows [half*64, half*64+64) of a [DP][DP] state -> panel-shaped slot [CL][LDP].
+__device__ __forceinline__ void g2s_state_rows(float* sm, const float* st, int half) {
+    g2s_panel(sm, st + half * CL * DP);
+}
+// Columns [half*64, half*64+64) of a [DP][DP] state -> slot [DP][LDH].
+__device__ __forceinline__ void g2s_state_cols(float* sm, const float* st, int half) {
+    for (int idx = threadIdx.x; idx < DP * (CL / 4); idx += NTHREADS) {
+        int rrow = idx >> 4, c4 = (idx & 15) << 2;
+        *reinterpret_cast<float4*>(sm + rrow * LDH + c4) =
+            *reinterpret_cast<const float4*>(st + rrow * DP + half * CL + c4);
+    }
+}
+
+// ---- TF32 tensor-core contraction on shared-memory operands --------------
+__device__ __forceinline__ uint32_t f2tf32(float x) {
+    uint32_t y;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NTW>
+__device__ __forceinline__ void acc_zero(float (&acc)[NTW][4]) {
+#pragma unroll
+    for (int n = 0; n < NTW; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[n][e] = 0.f;
+}
+
+// acc[16 x 8*NTW] += A[r0.., kbeg..kend) * B[kbeg..kend), n0..), one warp.
+// fa(i, k) and fb(k, n) return floats (any shared-memory indexing).
+template <int NTW, class FA, class FB>
+__device__ __forceinline__ void warp_mma(float (&acc)[NTW][4], int r0, int n0, int kbeg, int kend, FA fa, FB fb) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+#pragma unroll 2
+    for (int kk = kbeg; kk < kend; kk += 8) {
+        uint32_t a0 = f2tf32(fa(r0 + g, kk + t));
+        uint32_t a1 = f2tf32(fa(r0 + g + 8, kk + t));
+        uint32_t a2 = f2tf32(fa(r0 + g, kk + t + 4));
+        uint32_t a3 = f2tf32(fa(r0 + g + 8, kk + t + 4));
+#pragma unroll
+        for (int nt = 0; nt < NTW; ++nt) {
+            uint32_t b0 = f2tf32(fb(kk + t, n0 + nt * 8 + g));
+            uint32_t b1 = f2tf32(fb(kk + t + 4, n0 + nt * 8 + g));
+            mma_tf32(acc[nt], a0, a1, a2, a3, b0, b1);
+        }
+    }
+}
+
+// fe(i, j, v0, v1): element (i, j) = v0 and (i, j + 1) = v1, j even.
+template <int NTW, class FE>
+__device__ __forceinline__ void warp_epi(float (&acc)[NTW][4], int r0, int n0, FE fe) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int nt = 0; nt < NTW; ++nt) {
+        int j = n0 + nt * 8 + 2 * t;
+        fe(r0 + g, j, acc[nt][0], acc[nt][1]);
+        fe(r0 + g + 8, j, acc[nt][2], acc[nt][3]);
+    }
+}
+
+// Warp tiling of a CL x N output over the 8 warps of a chunk CTA.
+template <int N>
+struct Tile64 {
+    static constexpr int NTW = N / 16;
+    __device__ static __forceinline__ int r0() { return ((threadIdx.x >> 5) & 3) * 16; }
+    __device__ static __forceinline__ int n0() { return (threadIdx.x >> 7) * (N / 2); }
+};
+
+// ---- unit-triangular solves ------------------------------------------------
+// Solves (I + sgn * M) X = RHS in place for the 2*DP columns of two panels.
+// Mr is stored by rows of the system actually solved:
+//   UPPER == false: Mr[i][k] = M[i][k], non-zero only for k < i.
+//   UPPER == true : Mr[i][k] = M[k][i], non-zero only for k > i
+//                   (the transposed system), solved from the last row up.
+// Entries outside the stated triangle must be exactly zero.
+template <bool UPPER>
+__device__ __forceinline__ void trisolve(const float* Mr, float sgn, float* P0, float* P1) {
+    float* P = (threadIdx.x < DP) ? P0 : P1;
+    const int col = threadIdx.x & (DP - 1);
+    float x[CL];
+#pragma unroll
+    for (int i = 0; i < CL; ++i) x[i] = P[i * LDP + col];
+    if (!UPPER) {
+#pragma unroll
+        for (int i = 1; i < CL; ++i) {
+            float acc = 0.f;
+#pragma unroll
+            for (int k4 = 0; k4 < i; k4 += 4) {
+                float4 m = *reinterpret_cast<const float4*>(Mr + i * LDA + k4);
+                acc = fmaf(m.x, x[k4], acc);
+                acc = fmaf(m.y, x[k4 + 1], acc);
+                acc = fmaf(m.z, x[k4 + 2], acc);
+                acc = fmaf(m.w, x[k4 + 3], acc);
+            }
+            x[i] = fmaf(-sgn, acc, x[i]);
+        }
+    } else {
+#pragma unroll
+        for (int i = CL - 2; i >= 0; --i) {
+            float acc = 0.f;
+#pragma unroll
+            for (int k4 = ((i + 1) & ~3); k4 < CL; k4 += 4) {
+                float4 m = *reinterpret_cast<const float4*>(Mr + i * LDA + k4);
+                acc = fmaf(m.x, x[k4], acc);
+                acc = fmaf(m.y, x[k4 + 1], acc);
+                acc = fmaf(m.z, x[k4 + 2], acc);
+                acc = fmaf(m.w, x[k4 + 3], acc);
+            }
+            x[i] = fmaf(-sgn, acc, x[i]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < CL; ++i) P[i * LDP + col] = x[i];
+}
+
+// ---- chunk-local gate algebra ----------------------------------------------
+// In place: sG[i][c] <- sum_{j<=i} g[j][c].  Call with all threads; needs a
+// __syncthreads() before and after.
+__device__ __forceinline__ void chunk_cumsum(float* sG) {
+    if (threadIdx.x < DP) {
+        float run = 0.f;
+        float* p = sG + threadIdx.x;
+#pragma unroll 8
+        for (int i = 0; i < CL; ++i) {
+            run += p[i * LDP];
+            p[i * LDP] = run;
+        }
+    }
+}
+
+// Loads a BF16 operand chunk, L2-normalises every row and stores it as FP32.
+// rstd (may be null) receives 1/|x| per row.
+__device__ __forceinline__ void load_norm_panel(const Operand& op, const Chunk& ch, int width, float* sm,
+                                                float* rstd) {
+    const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
+#pragma unroll
+    for (int p = 0; p < CL / 16; ++p) {
+        int i = lr + 16 * p;
+        float x[8];
+        load8_bf16(row_bf16(op, ch, i), c0, width, op.vec, i < ch.nvalid, x);
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
+        ss = row_sum16(ss);
+        float rs = rsqrtf(ss + 1e-24f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sm[i * LDP + c0 + e] = x[e] * rs;
+        if (rstd != nullptr && (threadIdx.x & 15) == 0) rstd[i] = rs;
+    }
+}
+
+__device__ __forceinline__ void load_raw_panel(const Operand& op, const Chunk& ch, int width, float* sm) {
+    const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
+#pragma unroll
+    for (int p = 0; p < CL / 16; ++p) {
+        int i = lr + 16 * p;
+        float x[8];
+        load8_bf16(row_bf16(op, ch, i), c0, width, op.vec, i < ch.nvalid, x);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sm[i * LDP + c0 + e] = x[e];
+    }
+}
+
+__device__ __forceinline__ void load_f32_panel(const Operand& op, const Chunk& ch, int width, float* sm) {
+    const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
+#pragma unroll
+    for (int p = 0; p < CL / 16; ++p) {
+        int i = lr + 16 * p;
+        float x[8];
+        load8_f32(row_f32(op, ch, i), c0, width, op.vec, i < ch.nvalid, x);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sm[i * LDP + c0 + e] = x[e];
+    }
+}
+
+__device__ __forceinline__ void load_gamma(const Operand& op, const Chunk& ch, float* sg) {
+    if (threadIdx.x < CL) {
+        int i = threadIdx.x;
+        sg[i] = (i < ch.nvalid) ? *row_f32(op, ch, i) : 0.f;
+    }
+}
+
+}  // namespace sd

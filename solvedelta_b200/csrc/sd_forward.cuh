@@ -1,0 +1,359 @@
+// Chunk-parallel forward kernels: one CTA per (stream, chunk).
+//
+// Pipeline: k_prep_fwd -> scan(C) -> k_primal_fwd -> k_exterior_prep_fwd
+//           -> scan(S) -> k_output_fwd.
+#pragma once
+#include "sd_common.cuh"
+
+namespace sd {
+
+struct FwdParams {
+    Geometry g;
+    Operand u, h, q, k, v, er, wr, ld, gam;
+    // forward scratch
+    float *Upd, *Qc, *Ubar, *Wd, *Ud, *Dt, *Xg, *Aqd;
+    // kept for backward
+    float *Lam, *Delta, *Dprim, *Zt, *CtCk, *SCk;
+    void* y;
+};
+
+// Per-token frame covector phi, dual address e and query chi for the eight
+// channels a lane owns.  All 16 lanes of a row must call together.
+struct Sources {
+    float phi[8], b[8], e[8], chi[8];
+    float s, n2, den, sb, sq;
+};
+
+__device__ __forceinline__ void sources_fwd(const float (&uh)[8], const float (&kh)[8], const float (&qh)[8],
+                                            const float (&dl)[8], const float (&se)[8], Sources& o) {
+    float n2 = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) n2 = fmaf(dl[e], dl[e], n2);
+    n2 = row_sum16(n2);
+    const float s = RHO * rsqrtf(RHO * RHO + n2);
+    float pu = 0.f, ub = 0.f, uq = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        o.phi[e] = s * dl[e];
+        o.b[e] = se[e] * kh[e];
+        pu = fmaf(o.phi[e], uh[e], pu);
+        ub = fmaf(uh[e], o.b[e], ub);
+        uq = fmaf(uh[e], qh[e], uq);
+    }
+    const float den = 1.f + row_sum16(pu);
+    const float sb = row_sum16(ub) / den, sq = row_sum16(uq) / den;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        o.e[e] = o.b[e] - o.phi[e] * sb;
+        o.chi[e] = qh[e] - o.phi[e] * sq;
+    }
+    o.s = s;
+    o.n2 = n2;
+    o.den = den;
+    o.sb = sb;
+    o.sq = sq;
+}
+
+// Eight channels of one normalised BF16 row, in registers.
+__device__ __forceinline__ float load8_norm(const Operand& op, const Chunk& ch, int i, int c0, int width,
+                                            float (&x)[8]) {
+    load8_bf16(row_bf16(op, ch, i), c0, width, op.vec, i < ch.nvalid, x);
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
+    ss = row_sum16(ss);
+    const float rs = rsqrtf(ss + 1e-24f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] *= rs;
+    return rs;
+}
+
+__device__ __forceinline__ void load8_panel(const float* panel, int i, int c0, float (&x)[8]) {
+    float4 a = *reinterpret_cast<const float4*>(panel + i * DP + c0);
+    float4 b = *reinterpret_cast<const float4*>(panel + i * DP + c0 + 4);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+    x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+__device__ __forceinline__ void store8_panel(float* panel, int i, int c0, const float (&x)[8]) {
+    *reinterpret_cast<float4*>(panel + i * DP + c0) = make_float4(x[0], x[1], x[2], x[3]);
+    *reinterpret_cast<float4*>(panel + i * DP + c0 + 4) = make_float4(x[4], x[5], x[6], x[7]);
+}
+__device__ __forceinline__ void load8_smem(const float* sm, int i, int c0, float (&x)[8]) {
+    float4 a = *reinterpret_cast<const float4*>(sm + i * LDP + c0);
+    float4 b = *reinterpret_cast<const float4*>(sm + i * LDP + c0 + 4);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+    x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+__device__ __forceinline__ void store8_smem(float* sm, int i, int c0, const float (&x)[8]) {
+    *reinterpret_cast<float4*>(sm + i * LDP + c0) = make_float4(x[0], x[1], x[2], x[3]);
+    *reinterpret_cast<float4*>(sm + i * LDP + c0 + 4) = make_float4(x[4], x[5], x[6], x[7]);
+}
+
+// ---------------------------------------------------------------------------
+// Predictor preparation: pair matrix Lm, and the two solved panels
+//   Upd = (I+Lm)^-1 (gamma h),  W = (I+Lm)^-1 (gamma U~)   (stored negated as Qc)
+// so that the C scan is  Delta = Upd + Qc Ct.
+constexpr size_t PREP_FWD_SMEM = 5 * SLOT_BYTES + MAT_BYTES + CL * sizeof(float);
+
+__global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
+    extern __shared__ __align__(16) float smem[];
+    float* s_uh = smem;
+    float* s_G = s_uh + SLOT_FLOATS;
+    float* s_ut = s_G + SLOT_FLOATS;
+    float* s_un = s_ut + SLOT_FLOATS;
+    float* s_h = s_un + SLOT_FLOATS;
+    float* s_lm = s_h + SLOT_FLOATS;
+    float* s_gam = s_lm + MAT_FLOATS;
+    const Chunk ch = chunk_of(p.g, blockIdx.x);
+    const int r = p.g.r;
+
+    load_norm_panel(p.u, ch, r, s_uh, nullptr);
+    load_f32_panel(p.ld, ch, r, s_G);
+    load_raw_panel(p.h, ch, r, s_h);
+    load_gamma(p.gam, ch, s_gam);
+    __syncthreads();
+    chunk_cumsum(s_G);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < CL * DP; idx += NTHREADS) {
+        int i = idx >> 7, c = idx & (DP - 1);
+        float G = s_G[i * LDP + c];
+        float E = i ? s_G[(i - 1) * LDP + c] : 0.f;
+        float uh = s_uh[i * LDP + c];
+        s_ut[i * LDP + c] = uh * __expf(E);
+        s_un[i * LDP + c] = uh * clamp_exp_neg(G);
+    }
+    __syncthreads();
+    {
+        float acc[4][4];
+        acc_zero<4>(acc);
+        const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
+        warp_mma<4>(acc, r0, n0, 0, DP, [&](int i, int k) { return s_ut[i * LDP + k]; },
+                    [&](int k, int n) { return s_un[n * LDP + k]; });
+        warp_epi<4>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
+            float gm = s_gam[i];
+            s_lm[i * LDA + j] = (j < i) ? gm * v0 : 0.f;
+            s_lm[i * LDA + j + 1] = (j + 1 < i) ? gm * v1 : 0.f;
+        });
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < CL * DP; idx += NTHREADS) {
+        int i = idx >> 7, c = idx & (DP - 1);
+        float gm = s_gam[i];
+        s_h[i * LDP + c] *= gm;
+        s_ut[i * LDP + c] *= gm;
+    }
+    __syncthreads();
+    trisolve<false>(s_lm, 1.f, s_h, s_ut);
+    __syncthreads();
+    float* gUpd = panel_ptr(p.Upd, ch.gi);
+    float* gQc = panel_ptr(p.Qc, ch.gi);
+    float* gUbar = panel_ptr(p.Ubar, ch.gi);
+    for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += NTHREADS) {
+        int i = idx >> 5, c4 = (idx & 31) << 2;
+        float4 up = *reinterpret_cast<const float4*>(s_h + i * LDP + c4);
+        float4 w = *reinterpret_cast<const float4*>(s_ut + i * LDP + c4);
+        float4 uh = *reinterpret_cast<const float4*>(s_uh + i * LDP + c4);
+        float4 G = *reinterpret_cast<const float4*>(s_G + i * LDP + c4);
+        float4 GL = *reinterpret_cast<const float4*>(s_G + (CL - 1) * LDP + c4);
+        *reinterpret_cast<float4*>(gUpd + i * DP + c4) = up;
+        *reinterpret_cast<float4*>(gQc + i * DP + c4) = make_float4(-w.x, -w.y, -w.z, -w.w);
+        *reinterpret_cast<float4*>(gUbar + i * DP + c4) =
+            make_float4(uh.x * __expf(GL.x - G.x), uh.y * __expf(GL.y - G.y), uh.z * __expf(GL.z - G.z),
+                        uh.w * __expf(GL.w - G.w));
+    }
+    if (threadIdx.x < DP) p.Lam[ch.gi * DP + threadIdx.x] = __expf(s_G[(CL - 1) * LDP + threadIdx.x]);
+}
+
+// ---------------------------------------------------------------------------
+// Primal address d = k^ + C_t^T k^ for every token of the chunk:
+//   d = k^ + exp(G) * ( K^ Ct^T + tril(K^ Delta^T) (U^ exp(-G)) ).
+constexpr size_t PRIMAL_FWD_SMEM = 5 * SLOT_BYTES + MAT_BYTES;
+
+__global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
+    extern __shared__ __align__(16) float smem[];
+    float* s_kh = smem;
+    float* s_un = s_kh + SLOT_FLOATS;
+    float* s_G = s_un + SLOT_FLOATS;
+    float* s_dl = s_G + SLOT_FLOATS;
+    float* s_st = s_dl + SLOT_FLOATS;
+    float* s_aqk = s_st + SLOT_FLOATS;
+    const Chunk ch = chunk_of(p.g, blockIdx.x);
+    const int r = p.g.r;
+
+    load_norm_panel(p.k, ch, r, s_kh, nullptr);
+    load_norm_panel(p.u, ch, r, s_un, nullptr);
+    load_f32_panel(p.ld, ch, r, s_G);
+    g2s_panel(s_dl, panel_ptr(p.Delta, ch.gi));
+    __syncthreads();
+    chunk_cumsum(s_G);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < CL * DP; idx += NTHREADS) {
+        int i = idx >> 7, c = idx & (DP - 1);
+        s_un[i * LDP + c] *= clamp_exp_neg(s_G[i * LDP + c]);
+    }
+    {
+        float acc[4][4];
+        acc_zero<4>(acc);
+        const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
+        warp_mma<4>(acc, r0, n0, 0, DP, [&](int i, int k) { return s_kh[i * LDP + k]; },
+                    [&](int k, int n) { return s_dl[n * LDP + k]; });
+        warp_epi<4>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
+            s_aqk[i * LDA + j] = (j <= i) ? v0 : 0.f;
+            s_aqk[i * LDA + j + 1] = (j + 1 <= i) ? v1 : 0.f;
+        });
+    }
+    __syncthreads();
+    float acc[8][4];
+    acc_zero<8>(acc);
+    const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
+    const float* ct = state_ptr(p.CtCk, ch.gi);
+    for (int half = 0; half < 2; ++half) {
+        g2s_state_cols(s_st, ct, half);
+        __syncthreads();
+        warp_mma<8>(acc, r0, n0, 0, CL, [&](int i, int k) { return s_kh[i * LDP + half * CL + k]; },
+                    [&](int k, int n) { return s_st[n * LDH + k]; });
+        __syncthreads();
+    }
+    warp_mma<8>(acc, r0, n0, 0, r0 + 16, [&](int i, int k) { return s_aqk[i * LDA + k]; },
+                [&](int k, int n) { return s_un[k * LDP + n]; });
+    float* gd = panel_ptr(p.Dprim, ch.gi);
+    warp_epi<8>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
+        float2 kh = *reinterpret_cast<const float2*>(s_kh + i * LDP + j);
+        float2 G = *reinterpret_cast<const float2*>(s_G + i * LDP + j);
+        *reinterpret_cast<float2*>(gd + i * DP + j) =
+            make_float2(kh.x + __expf(G.x) * v0, kh.y + __expf(G.y) * v1);
+    });
+}
+
+// ---------------------------------------------------------------------------
+// Exterior preparation: sources (e, chi, z), the pair matrices Aqd / Aed and
+// the solved panels Wd = (I-Aed)^-1 ag, Ud = (I-Aed)^-1 Z for the S scan.
+constexpr size_t EXT_PREP_FWD_SMEM = 5 * SLOT_BYTES + MAT_BYTES;
+
+__global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) {
+    extern __shared__ __align__(16) float smem[];
+    float* s_xg = smem;
+    float* s_ag = s_xg + SLOT_FLOATS;
+    float* s_dn = s_ag + SLOT_FLOATS;
+    float* s_z = s_dn + SLOT_FLOATS;
+    float* s_G = s_z + SLOT_FLOATS;
+    float* s_aed = s_G + SLOT_FLOATS;
+    const Chunk ch = chunk_of(p.g, blockIdx.x);
+    const int r = p.g.r, V = p.g.V;
+
+    load_f32_panel(p.ld, ch, r, s_G);
+    __syncthreads();
+    chunk_cumsum(s_G);
+    __syncthreads();
+    {
+        const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
+        const float* gDelta = panel_ptr(p.Delta, ch.gi);
+        const float* gd = panel_ptr(p.Dprim, ch.gi);
+        float* gDt = panel_ptr(p.Dt, ch.gi);
+        float* gXg = panel_ptr(p.Xg, ch.gi);
+        float GL[8];
+        load8_smem(s_G, CL - 1, c0, GL);
+#pragma unroll 1
+        for (int pp = 0; pp < CL / 16; ++pp) {
+            const int i = lr + 16 * pp;
+            float uh[8], kh[8], qh[8], dl[8], d[8], er[8], wr[8], v[8], G[8], se[8];
+            load8_norm(p.u, ch, i, c0, r, uh);
+            load8_norm(p.k, ch, i, c0, r, kh);
+            load8_norm(p.q, ch, i, c0, r, qh);
+            load8_panel(gDelta, i, c0, dl);
+            load8_panel(gd, i, c0, d);
+            load8_bf16(row_bf16(p.er, ch, i), c0, r, p.er.vec, i < ch.nvalid, er);
+            load8_bf16(row_bf16(p.wr, ch, i), c0, V, p.wr.vec, i < ch.nvalid, wr);
+            load8_bf16(row_bf16(p.v, ch, i), c0, V, p.v.vec, i < ch.nvalid, v);
+            load8_smem(s_G, i, c0, G);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) se[e] = sigmoidf_(er[e]);
+            Sources src;
+            sources_fwd(uh, kh, qh, dl, se, src);
+            float xg[8], ag[8], dn[8], z[8], dt[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float ep = __expf(G[e]);
+                xg[e] = src.chi[e] * ep;
+                ag[e] = -src.e[e] * ep;
+                dn[e] = d[e] * clamp_exp_neg(G[e]);
+                dt[e] = d[e] * __expf(GL[e] - G[e]);
+                z[e] = sigmoidf_(wr[e]) * v[e];
+            }
+            store8_smem(s_xg, i, c0, xg);
+            store8_smem(s_ag, i, c0, ag);
+            store8_smem(s_dn, i, c0, dn);
+            store8_smem(s_z, i, c0, z);
+            store8_panel(gDt, i, c0, dt);
+            store8_panel(gXg, i, c0, xg);
+        }
+    }
+    __syncthreads();
+    {
+        float a1[4][4], a2[4][4];
+        acc_zero<4>(a1);
+        acc_zero<4>(a2);
+        const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
+        auto fb = [&](int k, int n) { return s_dn[n * LDP + k]; };
+        warp_mma<4>(a1, r0, n0, 0, DP, [&](int i, int k) { return s_xg[i * LDP + k]; }, fb);
+        warp_mma<4>(a2, r0, n0, 0, DP, [&](int i, int k) { return s_ag[i * LDP + k]; }, fb);
+        float* gAqd = mat_ptr(p.Aqd, ch.gi);
+        warp_epi<4>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
+            *reinterpret_cast<float2*>(gAqd + i * CL + j) =
+                make_float2((j <= i) ? v0 : 0.f, (j + 1 <= i) ? v1 : 0.f);
+        });
+        warp_epi<4>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
+            s_aed[i * LDA + j] = (j < i) ? v0 : 0.f;
+            s_aed[i * LDA + j + 1] = (j + 1 < i) ? v1 : 0.f;
+        });
+    }
+    __syncthreads();
+    trisolve<false>(s_aed, -1.f, s_ag, s_z);
+    __syncthreads();
+    s2g_panel(panel_ptr(p.Wd, ch.gi), s_ag);
+    s2g_panel(panel_ptr(p.Ud, ch.gi), s_z);
+}
+
+// ---------------------------------------------------------------------------
+// Output rows: y = Xg S_c + tril(Aqd) Z~.
+constexpr size_t OUTPUT_FWD_SMEM = 3 * SLOT_BYTES + MAT_BYTES;
+
+__global__ void __launch_bounds__(NTHREADS, 1) k_output_fwd(FwdParams p) {
+    extern __shared__ __align__(16) float smem[];
+    float* s_xg = smem;
+    float* s_st = s_xg + SLOT_FLOATS;
+    float* s_zt = s_st + SLOT_FLOATS;
+    float* s_aqd = s_zt + SLOT_FLOATS;
+    const Chunk ch = chunk_of(p.g, blockIdx.x);
+    const int V = p.g.V;
+
+    g2s_panel(s_xg, panel_ptr(p.Xg, ch.gi));
+    g2s_panel(s_zt, panel_ptr(p.Zt, ch.gi));
+    g2s_mat(s_aqd, mat_ptr(p.Aqd, ch.gi));
+    float acc[8][4];
+    acc_zero<8>(acc);
+    const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
+    const float* sc = state_ptr(p.SCk, ch.gi);
+    for (int half = 0; half < 2; ++half) {
+        g2s_state_rows(s_st, sc, half);
+        __syncthreads();
+        warp_mma<8>(acc, r0, n0, 0, CL, [&](int i, int k) { return s_xg[i * LDP + half * CL + k]; },
+                    [&](int k, int n) { return s_st[k * LDP + n]; });
+        __syncthreads();
+    }
+    warp_mma<8>(acc, r0, n0, 0, r0 + 16, [&](int i, int k) { return s_aqd[i * LDA + k]; },
+                [&](int k, int n) { return s_zt[k * LDP + n]; });
+    __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y);
+    warp_epi<8>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
+        if (i >= ch.nvalid || j >= V) return;
+        __nv_bfloat16* row = y + (((long long)ch.b * p.g.T + ch.t0 + i) * p.g.H + ch.hh) * (long long)V;
+        if (j + 1 < V && (V & 1) == 0) {
+            *reinterpret_cast<__nv_bfloat162*>(row + j) = __floats2bfloat162_rn(v0, v1);
+        } else {
+            row[j] = __float2bfloat16_rn(v0);
+            if (j + 1 < V) row[j + 1] = __float2bfloat16_rn(v1);
+        }
+    });
+}
+
+}  // namespace sd

@@ -1,0 +1,196 @@
+// The serial chunk-state scan shared by all four state carries.
+//
+// For every chunk, in forward or reverse chunk order:
+//     X  = P + Q * St              (CL x NS, contraction over the DP state rows)
+//     checkpoint St
+//     St = diag(lam) St + R^T X  (+ R2^T X2)
+// St is a [DP][NS] column slice of the carried state (the predictor state is
+// carried transposed, St[c][a] = C[a][c], so that both C and S decay by rows).
+// Column slices never exchange data, so a stream is split over DP/NS CTAs.
+// The slice lives in tensor-core accumulator registers for the whole
+// sequence; panels of the next chunk stream in through cp.async while the
+// current contraction runs.
+#pragma once
+#include "sd_common.cuh"
+
+namespace sd {
+
+constexpr int SCAN_NS = 64;            // state columns per CTA
+constexpr int LDT = SCAN_NS + 8;       // pitch of [*][NS] shared buffers
+
+struct ScanParams {
+    const float* P;    // [chunks][CL][DP]
+    const float* Q;
+    const float* R;
+    const float* R2;   // nullable
+    const float* X2;   // nullable (same column slicing as P)
+    const float* lam;  // [chunks][DP]
+    float* X;          // out [chunks][CL][DP]
+    float* ck;         // out [chunks][DP][DP] state before the chunk's update
+    const float* init; // nullable: true-dimension state [S][rows][cols] (or transposed)
+    float* fin;        // nullable
+    int NC;            // chunks per stream
+    int reverse;       // walk chunks last to first
+    int transposed_io; // init/fin hold the transpose (predictor state C[a][c])
+    int nrows, ncols;  // true dims of the carried St: rows (<= DP), cols (<= DP)
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N));
+}
+
+__device__ __forceinline__ void async_panel(float* sm, const float* g) {
+    for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += NTHREADS) {
+        int i = idx >> 5, c4 = (idx & 31) << 2;
+        cp_async16(sm + i * LDP + c4, g + i * DP + c4);
+    }
+}
+__device__ __forceinline__ void async_slice(float* sm, const float* g, int col0) {
+    for (int idx = threadIdx.x; idx < CL * (SCAN_NS / 4); idx += NTHREADS) {
+        int i = idx / (SCAN_NS / 4), c4 = (idx % (SCAN_NS / 4)) << 2;
+        cp_async16(sm + i * LDT + c4, g + i * DP + col0 + c4);
+    }
+}
+
+constexpr size_t SCAN_SMEM_BYTES =
+    (size_t(3) * CL * LDP + size_t(3) * CL * LDT + size_t(DP) * LDT) * sizeof(float);
+
+__global__ void __launch_bounds__(NTHREADS, 1) k_state_scan(ScanParams p) {
+    extern __shared__ __align__(16) float smem[];
+    float* sQ = smem;
+    float* sR = sQ + CL * LDP;
+    float* sR2 = sR + CL * LDP;
+    float* sP = sR2 + CL * LDP;   // [CL][LDT]
+    float* sX = sP + CL * LDT;    // [CL][LDT]
+    float* sX2 = sX + CL * LDT;   // [CL][LDT]
+    float* sSt = sX2 + CL * LDT;  // [DP][LDT]
+
+    const int col0 = blockIdx.x * SCAN_NS;
+    const int s = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const bool has2 = p.R2 != nullptr;
+    const long long base = (long long)s * p.NC;
+
+    // state slice: warp owns rows [16*warp, 16*warp+16), all NS columns
+    float st[SCAN_NS / 8][4];
+    const int row_a = warp * 16 + g, row_b = row_a + 8;
+#pragma unroll
+    for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            int rr = (e < 2) ? row_a : row_b;
+            int cc = col0 + nt * 8 + 2 * t + (e & 1);
+            float v = 0.f;
+            if (p.init != nullptr && rr < p.nrows && cc < p.ncols) {
+                const float* src = p.init + (long long)s * p.nrows * p.ncols;
+                v = p.transposed_io ? src[(long long)cc * p.nrows + rr] : src[(long long)rr * p.ncols + cc];
+            }
+            st[nt][e] = v;
+        }
+    }
+
+    auto chunk_at = [&](int step) { return base + (p.reverse ? (p.NC - 1 - step) : step); };
+    auto issue_a = [&](int step) {  // what the first contraction needs
+        long long gi = chunk_at(step);
+        async_panel(sQ, panel_ptr(p.Q, gi));
+        async_slice(sP, panel_ptr(p.P, gi), col0);
+    };
+    auto issue_b = [&](int step) {  // what the state update needs
+        long long gi = chunk_at(step);
+        async_panel(sR, panel_ptr(p.R, gi));
+        if (has2) {
+            async_panel(sR2, panel_ptr(p.R2, gi));
+            async_slice(sX2, panel_ptr(p.X2, gi), col0);
+        }
+    };
+
+    issue_a(0);
+    cp_async_commit();
+    issue_b(0);
+    cp_async_commit();
+
+    for (int step = 0; step < p.NC; ++step) {
+        const long long gi = chunk_at(step);
+        // publish the state slice: shared copy for the contraction, global checkpoint
+        {
+            float* ck = state_ptr(p.ck, gi);
+#pragma unroll
+            for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
+                int cc = nt * 8 + 2 * t;
+                *reinterpret_cast<float2*>(sSt + row_a * LDT + cc) = make_float2(st[nt][0], st[nt][1]);
+                *reinterpret_cast<float2*>(sSt + row_b * LDT + cc) = make_float2(st[nt][2], st[nt][3]);
+                *reinterpret_cast<float2*>(ck + row_a * DP + col0 + cc) = make_float2(st[nt][0], st[nt][1]);
+                *reinterpret_cast<float2*>(ck + row_b * DP + col0 + cc) = make_float2(st[nt][2], st[nt][3]);
+            }
+        }
+        cp_async_wait<1>();
+        __syncthreads();
+        // X = P + Q St : warp tile 16 rows x 32 columns
+        {
+            float acc[4][4];
+            acc_zero<4>(acc);
+            const int r0 = (warp & 3) * 16, n0 = (warp >> 2) * 32;
+            warp_mma<4>(acc, r0, n0, 0, DP, [&](int i, int k) { return sQ[i * LDP + k]; },
+                        [&](int k, int n) { return sSt[k * LDT + n]; });
+            float* xg = panel_ptr(p.X, gi);
+            warp_epi<4>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
+                float2 pv = *reinterpret_cast<const float2*>(sP + i * LDT + j);
+                float2 xv = make_float2(pv.x + v0, pv.y + v1);
+                *reinterpret_cast<float2*>(sX + i * LDT + j) = xv;
+                *reinterpret_cast<float2*>(xg + i * DP + col0 + j) = xv;
+            });
+        }
+        __syncthreads();
+        if (step + 1 < p.NC) issue_a(step + 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        // St = lam St + R^T X (+ R2^T X2) : warp tile 16 state rows x NS columns
+        {
+            const float* lam = p.lam + gi * DP;
+            const float la = lam[row_a], lb = lam[row_b];
+#pragma unroll
+            for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
+                st[nt][0] *= la;
+                st[nt][1] *= la;
+                st[nt][2] *= lb;
+                st[nt][3] *= lb;
+            }
+            warp_mma<SCAN_NS / 8>(st, warp * 16, 0, 0, CL, [&](int c, int j) { return sR[j * LDP + c]; },
+                                  [&](int j, int n) { return sX[j * LDT + n]; });
+            if (has2)
+                warp_mma<SCAN_NS / 8>(st, warp * 16, 0, 0, CL, [&](int c, int j) { return sR2[j * LDP + c]; },
+                                      [&](int j, int n) { return sX2[j * LDT + n]; });
+        }
+        __syncthreads();
+        if (step + 1 < p.NC) issue_b(step + 1);
+        cp_async_commit();
+    }
+    cp_async_wait<0>();
+
+    if (p.fin != nullptr) {
+        float* dst = p.fin + (long long)s * p.nrows * p.ncols;
+#pragma unroll
+        for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                int rr = (e < 2) ? row_a : row_b;
+                int cc = col0 + nt * 8 + 2 * t + (e & 1);
+                if (rr < p.nrows && cc < p.ncols) {
+                    if (p.transposed_io)
+                        dst[(long long)cc * p.nrows + rr] = st[nt][e];
+                    else
+                        dst[(long long)rr * p.ncols + cc] = st[nt][e];
+                }
+            }
+        }
+    }
+}
+
+}  // namespace sd

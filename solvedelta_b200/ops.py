@@ -1,0 +1,303 @@
+"""Operator entry points with the upstream names, signatures and errors.
+
+Mirrors causallsso/ops/operator.py:13-55 (``solvedelta_native``) and
+causallsso/ops/residual_frame/operator.py:154-304
+(``solvedelta_residual_frame_native``): BF16 CUDA activations with unit
+innermost stride and arbitrary outer strides, FP32 ``associative_log_decay``
+and ``geometry_write`` ([H], [1,H] or [B,T,H]), FP32 continuation states
+``SolveDeltaState(predictor=C [B,H,r,r], S [B,H,r,V])``.  One
+``torch.autograd.Function`` covers the whole operator; ``None`` incoming
+gradients are legal (``set_materialize_grads(False)``), gradients are returned
+for the nine tensor operands and for both initial states.
+
+PyTorch is used for device memory and the current stream only; all arithmetic
+is in the CUDA library behind ``include/solvedelta_b200.h``.  There is no CPU
+or eager fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import NamedTuple, Optional, Tuple
+
+import torch
+
+from . import _lib
+
+
+class SolveDeltaState(NamedTuple):
+    """Continuation state; same field names as causallsso/reference.py:14-16."""
+
+    predictor: torch.Tensor
+    S: torch.Tensor
+
+
+def solvedelta_zero_state(batch: int, heads: int, rank: int, value_dim: int, *,
+                          dtype: torch.dtype, device: torch.device) -> SolveDeltaState:
+    return SolveDeltaState(
+        predictor=torch.zeros(batch, heads, rank, rank, dtype=dtype, device=device),
+        S=torch.zeros(batch, heads, rank, value_dim, dtype=dtype, device=device),
+    )
+
+
+def _operand(t: torch.Tensor) -> _lib.Operand:
+    """[B,T,H,w] tensor (any outer strides, unit inner stride) -> C operand."""
+    sb, st, sh = t.stride(0), t.stride(1), t.stride(2)
+    return _lib.Operand(t.data_ptr(), sb, st, sh)
+
+
+def _gamma_operand(t: torch.Tensor) -> _lib.Operand:
+    return _lib.Operand(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
+
+
+def _shape(u: torch.Tensor, value_dim: int) -> _lib.Shape:
+    B, T, H, r = u.shape
+    return _lib.Shape(B, T, H, r, value_dim)
+
+
+def _stream_ptr(device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _buffer(nbytes: int, device) -> torch.Tensor:
+    return torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=device)
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _fill_operands(args, tensors):
+    names = ("u", "h", "q", "keys", "values", "erase_raw", "write_raw", "log_decay")
+    u, h, q, k, v, ld, er, wr, gam = tensors
+    for name, t in zip(names, (u, h, q, k, v, er, wr, ld)):
+        setattr(args, name, _operand(t))
+    args.gamma = _gamma_operand(gam)
+
+
+class _SolveDeltaFunction(torch.autograd.Function):
+    """forward(u,h,q,k,v,log_decay,erase_raw,write_raw,gamma[B,T,H],C0|None,S0|None)
+    -> (y, C_T, S_T); k,v,erase_raw,write_raw are the 4-D views without the edit axis."""
+
+    @staticmethod
+    def forward(ctx, u, h, q, k, v, log_decay, erase_raw, write_raw, gamma, C0, S0):
+        lib = _lib.load()
+        device = u.device
+        B, T, H, r = u.shape
+        V = v.shape[-1]
+        shape = _shape(u, V)
+        with torch.cuda.device(device):
+            y = torch.empty(B, T, H, V, dtype=torch.bfloat16, device=device)
+            C_T = torch.empty(B, H, r, r, dtype=torch.float32, device=device)
+            S_T = torch.empty(B, H, r, V, dtype=torch.float32, device=device)
+            saved = _buffer(lib.sd_saved_bytes(ctypes.byref(shape)), device)
+            scratch = _buffer(lib.sd_forward_scratch_bytes(ctypes.byref(shape)), device)
+            C0c = None if C0 is None else C0.contiguous()
+            S0c = None if S0 is None else S0.contiguous()
+            args = _lib.ForwardArgs()
+            args.shape = shape
+            _fill_operands(args, (u, h, q, k, v, log_decay, erase_raw, write_raw, gamma))
+            args.C0, args.S0 = _ptr(C0c), _ptr(S0c)
+            args.y, args.C_T, args.S_T = y.data_ptr(), C_T.data_ptr(), S_T.data_ptr()
+            args.saved, args.saved_bytes = saved.data_ptr(), saved.numel()
+            args.scratch, args.scratch_bytes = scratch.data_ptr(), scratch.numel()
+            _lib.check(lib.sd_forward(ctypes.byref(args), _stream_ptr(device)))
+        ctx.set_materialize_grads(False)
+        ctx.has_state = (C0 is not None, S0 is not None)
+        ctx.save_for_backward(u, h, q, k, v, log_decay, erase_raw, write_raw, gamma, saved)
+        return y, C_T, S_T
+
+    @staticmethod
+    def backward(ctx, dy, dC_T, dS_T):
+        lib = _lib.load()
+        u, h, q, k, v, log_decay, erase_raw, write_raw, gamma, saved = ctx.saved_tensors
+        device = u.device
+        B, T, H, r = u.shape
+        V = v.shape[-1]
+        shape = _shape(u, V)
+        with torch.cuda.device(device):
+            if dy is None:
+                dy = torch.zeros(B, T, H, V, dtype=torch.bfloat16, device=device)
+            elif dy.dtype != torch.bfloat16 or dy.stride(-1) != 1:
+                dy = dy.to(torch.bfloat16).contiguous()
+            dC_T = None if dC_T is None else dC_T.float().contiguous()
+            dS_T = None if dS_T is None else dS_T.float().contiguous()
+            bf = dict(dtype=torch.bfloat16, device=device)
+            du = torch.empty(B, T, H, r, **bf)
+            dh = torch.empty(B, T, H, r, **bf)
+            dq = torch.empty(B, T, H, r, **bf)
+            dk = torch.empty(B, T, H, r, **bf)
+            dv = torch.empty(B, T, H, V, **bf)
+            der = torch.empty(B, T, H, r, **bf)
+            dwr = torch.empty(B, T, H, V, **bf)
+            dld = torch.empty(B, T, H, r, dtype=torch.float32, device=device)
+            dgam = torch.empty(B, T, H, dtype=torch.float32, device=device)
+            dC0 = torch.empty(B, H, r, r, dtype=torch.float32, device=device)
+            dS0 = torch.empty(B, H, r, V, dtype=torch.float32, device=device)
+            scratch = _buffer(lib.sd_backward_scratch_bytes(ctypes.byref(shape)), device)
+            args = _lib.BackwardArgs()
+            args.shape = shape
+            _fill_operands(args, (u, h, q, k, v, log_decay, erase_raw, write_raw, gamma))
+            args.dy = _operand(dy)
+            args.dC_T, args.dS_T = _ptr(dC_T), _ptr(dS_T)
+            args.saved, args.saved_bytes = saved.data_ptr(), saved.numel()
+            args.scratch, args.scratch_bytes = scratch.data_ptr(), scratch.numel()
+            args.du, args.dh, args.dq = du.data_ptr(), dh.data_ptr(), dq.data_ptr()
+            args.dkeys, args.dvalues = dk.data_ptr(), dv.data_ptr()
+            args.derase_raw, args.dwrite_raw = der.data_ptr(), dwr.data_ptr()
+            args.dlog_decay, args.dgamma = dld.data_ptr(), dgam.data_ptr()
+            args.dC0, args.dS0 = dC0.data_ptr(), dS0.data_ptr()
+            _lib.check(lib.sd_backward(ctypes.byref(args), _stream_ptr(device)))
+        has_C0, has_S0 = ctx.has_state
+        return (du, dh, dq, dk, dv, dld, der, dwr, dgam,
+                dC0 if has_C0 else None, dS0 if has_S0 else None)
+
+
+def _decode_step(u, h, q, k, v, log_decay, erase_raw, write_raw, gamma, C0, S0):
+    lib = _lib.load()
+    device = u.device
+    B, T, H, r = u.shape
+    V = v.shape[-1]
+    with torch.cuda.device(device):
+        C = (torch.zeros(B, H, r, r, dtype=torch.float32, device=device) if C0 is None
+             else C0.detach().clone(memory_format=torch.contiguous_format))
+        S = (torch.zeros(B, H, r, V, dtype=torch.float32, device=device) if S0 is None
+             else S0.detach().clone(memory_format=torch.contiguous_format))
+        y = torch.empty(B, 1, H, V, dtype=torch.bfloat16, device=device)
+        args = _lib.DecodeArgs()
+        args.shape = _shape(u, V)
+        _fill_operands(args, (u, h, q, k, v, log_decay, erase_raw, write_raw, gamma))
+        args.C, args.S, args.y = C.data_ptr(), S.data_ptr(), y.data_ptr()
+        _lib.check(lib.sd_decode_step(ctypes.byref(args), _stream_ptr(device)))
+    return y, C, S
+
+
+def solvedelta_residual_frame_native(
+    u: torch.Tensor,
+    h: torch.Tensor,
+    q: torch.Tensor,
+    keys: torch.Tensor,
+    values: torch.Tensor,
+    associative_log_decay: torch.Tensor,
+    erase_raw: torch.Tensor,
+    write_raw: torch.Tensor,
+    geometry_write: torch.Tensor,
+    *,
+    initial_state: Optional[SolveDeltaState] = None,
+    return_final_state: bool = True,
+) -> Tuple[torch.Tensor, Optional[SolveDeltaState]]:
+    """Dense BF16 path from raw gate logits.
+
+    Same checks, in the same order and with the same exception types, as
+    causallsso/ops/residual_frame/operator.py:169-196 and :247-262.  Any
+    sequence length is accepted: a ragged last chunk is completed inside the
+    kernels with neutral tokens (the upstream path pads with zero tokens,
+    residual_frame/operator.py:218-245, which is the same arithmetic).
+    """
+    if u.ndim != 4:
+        raise ValueError("u must have shape [B,T,H,r]")
+    batch, length, heads, rank = u.shape
+    if h.shape != u.shape or q.shape != u.shape:
+        raise ValueError("h and q must match u")
+    if keys.shape != (batch, length, heads, 1, rank):
+        raise ValueError("Residual-Frame SolveDelta requires keys [B,T,H,1,r]")
+    if values.ndim != 5 or values.shape[:4] != (batch, length, heads, 1):
+        raise ValueError("values must have shape [B,T,H,1,d_v]")
+    value_dim = values.shape[-1]
+    if associative_log_decay.shape != (batch, length, heads, rank):
+        raise ValueError("associative_log_decay must have shape [B,T,H,r]")
+    if erase_raw.shape != keys.shape or write_raw.shape != values.shape:
+        raise ValueError("erase_raw/write_raw shapes must match keys/values")
+    if geometry_write.shape not in ((heads,), (1, heads), (batch, length, heads)):
+        raise ValueError("geometry_write must have shape [H], [1,H], or [B,T,H]")
+    if u.device.type != "cuda" or u.dtype != torch.bfloat16:
+        raise TypeError("the production Residual-Frame path requires BF16 CUDA operands")
+    if any(x.dtype != u.dtype for x in (h, q, keys, values, erase_raw, write_raw)):
+        raise TypeError("all public vector operands must be BF16")
+    if associative_log_decay.dtype != torch.float32:
+        raise TypeError("associative_log_decay must be FP32")
+    if geometry_write.dtype != torch.float32:
+        raise TypeError("geometry_write must be FP32")
+    if rank > 128 or value_dim > 128:
+        raise ValueError("the B200 kernels support head widths up to 128")
+    if any(x.stride(-1) != 1 for x in (u, h, q, keys, values, erase_raw, write_raw)):
+        raise ValueError("native vector operands require unit innermost stride")
+    if associative_log_decay.stride(-1) != 1:
+        associative_log_decay = associative_log_decay.contiguous()
+
+    predictor_initial = memory_initial = None
+    if initial_state is not None:
+        expected = ((batch, heads, rank, rank), (batch, heads, rank, value_dim))
+        if any(value.shape != exp for value, exp in zip(initial_state, expected)):
+            raise ValueError("initial_state shapes do not match the input geometry")
+        if any(value.dtype != torch.float32 for value in initial_state):
+            raise TypeError("all continuation states must be FP32")
+        predictor_initial, memory_initial = initial_state
+
+    if geometry_write.shape != (batch, length, heads):
+        geometry_write = geometry_write.reshape(1, 1, heads).expand(batch, length, heads)
+
+    k4, v4 = keys.squeeze(-2), values.squeeze(-2)
+    er4, wr4 = erase_raw.squeeze(-2), write_raw.squeeze(-2)
+
+    if length == 0:
+        output = values.new_zeros(batch, 0, heads, value_dim)
+        if not return_final_state:
+            return output, None
+        if initial_state is not None:
+            return output, initial_state
+        return output, solvedelta_zero_state(batch, heads, rank, value_dim, dtype=torch.float32,
+                                             device=u.device)
+
+    if length == 1 and not torch.is_grad_enabled():
+        # single-token recurrent inference (causallsso/ops/residual_frame/operator.py:198-216)
+        y, C, S = _decode_step(u, h, q, k4, v4, associative_log_decay, er4, wr4, geometry_write,
+                               predictor_initial, memory_initial)
+        return y, (SolveDeltaState(C, S) if return_final_state else None)
+
+    y, C_T, S_T = _SolveDeltaFunction.apply(
+        u, h, q, k4, v4, associative_log_decay, er4, wr4, geometry_write,
+        predictor_initial, memory_initial)
+    if not return_final_state:
+        return y, None
+    return y, SolveDeltaState(predictor=C_T, S=S_T)
+
+
+def solvedelta_native(
+    u: torch.Tensor,
+    h: torch.Tensor,
+    q: torch.Tensor,
+    keys: torch.Tensor,
+    values: torch.Tensor,
+    associative_log_decay: torch.Tensor,
+    erase_raw: torch.Tensor,
+    write_raw: torch.Tensor,
+    geometry_write: torch.Tensor,
+    *,
+    initial_state: Optional[SolveDeltaState] = None,
+    return_final_state: bool = False,
+) -> Tuple[torch.Tensor, Optional[SolveDeltaState]]:
+    """Execute dense K=1 SolveDelta from raw fused-projection views.
+
+    Same contract as causallsso/ops/operator.py:13-55.
+    """
+    if u.device.type != "cuda" or u.dtype != torch.bfloat16:
+        raise TypeError("solvedelta_native requires BF16 CUDA activations")
+    if keys.ndim != 5 or keys.shape[-2] != 1:
+        raise ValueError("the current production path requires num_edits=1")
+    if erase_raw.shape != keys.shape or erase_raw.dtype != torch.bfloat16:
+        raise ValueError("erase_raw must be BF16 with the same shape as keys")
+    if write_raw.shape != values.shape or write_raw.dtype != torch.bfloat16:
+        raise ValueError("write_raw must be BF16 with the same shape as values")
+    if any(operand.stride(-1) != 1 for operand in (u, h, q, keys, values, erase_raw, write_raw)):
+        raise ValueError("native vector operands require unit innermost stride")
+    return solvedelta_residual_frame_native(
+        u, h, q, keys, values, associative_log_decay, erase_raw, write_raw, geometry_write,
+        initial_state=initial_state, return_final_state=return_final_state)
+
+
+__all__ = [
+    "SolveDeltaState",
+    "solvedelta_native",
+    "solvedelta_residual_frame_native",
+    "solvedelta_zero_state",
+]

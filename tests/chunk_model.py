@@ -189,6 +189,10 @@ class Model:
         y = self.mm(ext["Xg"], S_ck) + self.mm(ext["Aqd"], Zt)
         saved = dict(loc=loc, Upd=Upd, W=W, Delta=Delta, Ct_ck=Ct_ck, d=d, Wd=Wd, Ud=Ud,
                      Zt=Zt, S_ck=S_ck, Xg=ext["Xg"], Aqd=ext["Aqd"], Dt=ext["Dt"])
+        # the same quantities under the names the CUDA library gives its panels
+        saved["panels"] = dict(Lam=loc["lam"], Delta=Delta, Dprim=d, Zt=Zt, CtCk=Ct_ck, SCk=S_ck,
+                               Upd=Upd, Qc=-W, Ubar=loc["Ubar"], Wd=Wd, Ud=Ud, Dt=ext["Dt"],
+                               Xg=ext["Xg"], Aqd=ext["Aqd"])
         yo = self._unchunks(y, B, T, H)
         C_T = Ct_fin.transpose(-1, -2).reshape(B, H, r, r)
         S_T = S_fin.reshape(B, H, r, V)
@@ -227,7 +231,7 @@ class Model:
         de = -loc["epos"] * (PX2 + dag)
         PY = self.mm(dAqd.transpose(-1, -2), ext["Xg"]) + self.mm(dAed.transpose(-1, -2), ext["ag"])
         dd = loc["eneg"] * PY + dDt * loc["etail"]
-        dG = src["chi"] * dchi + src["e"] * de - ext["Dneg"] * PY - dDt * ext["Dt"]
+        dG = src["chi"] * dchi + src["e"] * de - ext["Dneg"] * PY
         dGL = loc["lam"] * (S_ck * dSe).sum(-1) + (dDt * ext["Dt"]).sum(2)  # [S,NC,r]
         # sources backward
         phi, den, sb, sq, b = src["phi"], src["den"], src["sb"], src["sq"], src["b"]
@@ -245,6 +249,10 @@ class Model:
         dDelta = s * dphi - (dphi * Delta).sum(-1, keepdim=True) * s / (RHO * RHO + src["n2"]) * Delta
         se, sw = loc["se"], loc["sw"]
         dkh = se * db
+        duPart, dkPart = duh.clone(), dkh + dd
+        dGPart = dG + dd * (d - kh)
+        Xext = dDt * ext["Dt"]
+        dG = dG - Xext
         d_erase_raw = db * kh * se * (1 - se)
         dv = sw * dR
         d_write_raw = dR * loc["v"] * sw * (1 - sw)
@@ -255,7 +263,8 @@ class Model:
         dkh = dkh + self.mm(DG, Ct_ck)
         dAqk = self.mm(DG, loc["Uneg"].transpose(-1, -2)) * loc["tril"]
         Aqk = self.mm(kh, Delta.transpose(-1, -2)) * loc["tril"]
-        t_u = loc["eneg"] * self.mm(Aqk.transpose(-1, -2), DG)
+        Tpre = self.mm(Aqk.transpose(-1, -2), DG)
+        t_u = loc["eneg"] * Tpre
         duh = duh + t_u
         dG = dG + dact * (d - kh) - uh * t_u
         dkh = dkh + self.mm(dAqk, Delta)
@@ -280,8 +289,10 @@ class Model:
         duh = duh + dUt * loc["eE"]
         dE = dUt * loc["Ut"]
         dN = gam * dLm
-        t_i = loc["eE"] * self.mm(dN, loc["Uneg"])
-        t_j = loc["eneg"] * self.mm(dN.transpose(-1, -2), loc["Ut"])
+        Ti = self.mm(dN, loc["Uneg"])
+        Tj = self.mm(dN.transpose(-1, -2), loc["Ut"])
+        t_i = loc["eE"] * Ti
+        t_j = loc["eneg"] * Tj
         duh = duh + t_i + t_j
         dE = dE + uh * t_i
         dG = dG - uh * t_j
@@ -307,6 +318,10 @@ class Model:
             C0=dCt0.transpose(-1, -2).reshape(B, H, r, r),
             S0=dS0.reshape(B, H, r, V),
         )
-        panels = dict(Pp=Pp, Qp=Qp, dR=dR, dSe=dSe, Ppp=Ppp, Qpp=Qpp, dRr=dRr, dCe=dCe,
-                      DG=DG, dd=dd)
+        panels = dict(Pp=Pp, Qp=Qp, Ag=ext["ag"], Xg=ext["Xg"], Dyf=dyc, Dneg=ext["Dneg"], dR=dR,
+                      dSeCk=dSe, A1=PX1 + dXg, A2=PX2 + dag, PY=PY, dDt=dDt,
+                      SdS=(S_ck * dSe).sum(-1), duPart=duPart, dkPart=dkPart, dGPart=dGPart,
+                      dDelta=dDelta, DG=DG, Xext=Xext, Tpre=Tpre, Khat=kh, Ppp=Ppp, Qpp=Qpp,
+                      Rneg=-gam * loc["Ut"], dRr=dRr, dCeCk=dCe, dUbar=dUbar, dUt=dUt, Ti=Ti,
+                      Tj=Tj, CdC=(Ct_ck * dCe).sum(-1))
         return grads, panels

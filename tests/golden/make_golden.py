@@ -50,21 +50,30 @@ def seed7_inputs(length=6, rank=8, value_dim=5):
     return [u, h, q, keys, values, decay, erase, write, gamma]
 
 
+RAW_GATES = {}
+
+
 def bench_like_inputs(batch, length, heads, rank, value_dim, seed):
-    """Same distributions as the benchmark workload, in FP64."""
+    """Same distributions as the benchmark workload.  Every value is exactly
+    representable in the dtype the CUDA path takes (BF16 vectors and raw gate
+    logits, FP32 decay / geometry rate), so the GPU consumes these vectors
+    without a rounding step of its own; the FP64 oracle sees the same numbers."""
     gen = torch.Generator().manual_seed(seed)
     rn = lambda *s: torch.randn(*s, generator=gen, dtype=torch.float64)
-    u, h, q = rn(batch, length, heads, rank), rn(batch, length, heads, rank), rn(batch, length, heads, rank)
-    keys = rn(batch, length, heads, 1, rank)
-    values = rn(batch, length, heads, 1, value_dim)
-    decay = torch.nn.functional.logsigmoid(rn(batch, length, heads, rank) + 4.0)
-    erase = torch.sigmoid(rn(batch, length, heads, 1, rank))
-    write = torch.sigmoid(rn(batch, length, heads, 1, value_dim))
-    gamma = 0.1 * torch.rand(batch, length, heads, generator=gen, dtype=torch.float64)
-    return [u, h, q, keys, values, decay, erase, write, gamma]
+    bf = lambda x: x.to(torch.bfloat16).to(torch.float64)
+    f32 = lambda x: x.to(torch.float32).to(torch.float64)
+    u, h, q = bf(rn(batch, length, heads, rank)), bf(rn(batch, length, heads, rank)), bf(rn(batch, length, heads, rank))
+    keys = bf(rn(batch, length, heads, 1, rank))
+    values = bf(rn(batch, length, heads, 1, value_dim))
+    decay = f32(torch.nn.functional.logsigmoid(rn(batch, length, heads, rank) + 4.0))
+    erase_raw = bf(rn(batch, length, heads, 1, rank))
+    write_raw = bf(rn(batch, length, heads, 1, value_dim))
+    gamma = f32(0.1 * torch.rand(batch, length, heads, generator=gen, dtype=torch.float64))
+    RAW_GATES["erase_raw"], RAW_GATES["write_raw"] = erase_raw, write_raw
+    return [u, h, q, keys, values, decay, torch.sigmoid(erase_raw), torch.sigmoid(write_raw), gamma]
 
 
-def run_case(ref, name, args, *, state=None, valid=None, reset=None, seed=29):
+def run_case(ref, name, args, *, state=None, valid=None, reset=None, seed=29, raw_gates=None):
     leaves = [a.clone().requires_grad_() for a in args]
     st = None
     if state is not None:
@@ -73,6 +82,8 @@ def run_case(ref, name, args, *, state=None, valid=None, reset=None, seed=29):
         *leaves, initial_state=st, valid_mask=valid, reset_mask=reset)
     gen = torch.Generator().manual_seed(seed)
     dy = torch.randn(out.shape, generator=gen, dtype=torch.float64)
+    if raw_gates is not None:
+        dy = dy.to(torch.bfloat16).to(torch.float64)
     dC = torch.randn(fin.predictor.shape, generator=gen, dtype=torch.float64)
     dS = torch.randn(fin.S.shape, generator=gen, dtype=torch.float64)
     loss = (out * dy).sum() + (fin.predictor * dC).sum() + (fin.S * dS).sum()
@@ -87,6 +98,9 @@ def run_case(ref, name, args, *, state=None, valid=None, reset=None, seed=29):
     if st is not None:
         blob["in_C0"], blob["in_S0"] = state[0].numpy(), state[1].numpy()
         blob["grad_C0"], blob["grad_S0"] = grads[9].numpy(), grads[10].numpy()
+    if raw_gates is not None:
+        blob["in_erase_raw"] = raw_gates["erase_raw"].numpy()
+        blob["in_write_raw"] = raw_gates["write_raw"].numpy()
     if valid is not None:
         blob["valid"] = valid.numpy()
     if reset is not None:
@@ -121,17 +135,15 @@ def main():
 
     args = bench_like_inputs(1, 40, 2, 16, 12, seed=0)
     torch.manual_seed(131)
-    state = (0.02 * torch.randn(1, 2, 16, 16, dtype=torch.float64),
-             0.02 * torch.randn(1, 2, 16, 12, dtype=torch.float64))
-    run_case(ref, "benchlike_r16_state", args, state=state)
+    state = ((0.02 * torch.randn(1, 2, 16, 16)).double(), (0.02 * torch.randn(1, 2, 16, 12)).double())
+    run_case(ref, "benchlike_r16_state", args, state=state, raw_gates=dict(RAW_GATES))
 
     # chunk-spanning case for the chunked CUDA path: T=150 crosses two 64-token
     # chunk boundaries and ends on a ragged tail
     args = bench_like_inputs(1, 150, 1, 32, 32, seed=1)
     torch.manual_seed(137)
-    state = (0.02 * torch.randn(1, 1, 32, 32, dtype=torch.float64),
-             0.02 * torch.randn(1, 1, 32, 32, dtype=torch.float64))
-    run_case(ref, "benchlike_r32_t150_state", args, state=state)
+    state = ((0.02 * torch.randn(1, 1, 32, 32)).double(), (0.02 * torch.randn(1, 1, 32, 32)).double())
+    run_case(ref, "benchlike_r32_t150_state", args, state=state, raw_gates=dict(RAW_GATES))
 
 
 if __name__ == "__main__":

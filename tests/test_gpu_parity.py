@@ -1,0 +1,258 @@
+"""CUDA path vs the FP64 CPU checker, through the public entry points.
+
+Cases follow upstream tests/core/test_rebuild_semantics.py: forward + full VJP
+with continuation states (:540-597), r=128 multi-tile (:600-696), extreme
+forgetting stays finite (:699-747), aligned recurrent split (:850-867),
+ragged tails T=1/19 (:870-897), single-token recurrent inference (:900-929),
+strided views bit-equal to packed operands (:487-537), zero geometry write
+reduces to the GDN2 edit (:296-316).
+
+Tolerances: outputs and gradients max relative error (max|a-b| / max|b|)
+<= 2e-2 and relative L2 <= 3e-2 (upstream :560-597); FP32 states max relative
+error <= 1e-3.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import solvedelta_oracle as orc
+from solvedelta_b200 import SolveDeltaState, solvedelta_native
+from tests.gpu_harness import make_inputs, oracle_args, oracle_state, raw_gate_grads
+from tests.helpers import golden_inputs, golden_state, load_golden, max_rel, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+OUT_TOL = 2e-2
+STATE_TOL = 1e-3
+GRAD_L2_TOL = 3e-2
+
+
+def _native(dev, *, grad=False, return_final_state=True):
+    names = ("u", "h", "q", "keys", "values", "log_decay", "erase_raw", "write_raw", "geometry_write")
+    leaves = [dev[n].detach().clone().requires_grad_(grad) for n in names]
+    state = None
+    if dev["C0"] is not None:
+        state = SolveDeltaState(dev["C0"].detach().clone().requires_grad_(grad),
+                                dev["S0"].detach().clone().requires_grad_(grad))
+    y, fin = solvedelta_native(*leaves, initial_state=state, return_final_state=return_final_state)
+    return leaves, state, y, fin
+
+
+def _check_forward(cpu, y, fin):
+    yo, so = orc.forward(*oracle_args(cpu), initial_state=oracle_state(cpu))
+    assert torch.isfinite(y).all()
+    assert max_rel(y.float().cpu().numpy(), yo) <= OUT_TOL
+    assert rel_l2(y.float().cpu().numpy(), yo) <= OUT_TOL
+    assert max_rel(fin.predictor.cpu().numpy(), so.predictor) <= STATE_TOL or np.abs(so.predictor).max() < 1e-12
+    assert max_rel(fin.S.cpu().numpy(), so.S) <= STATE_TOL
+    return yo, so
+
+
+def _check_vjp(cpu, leaves, state, y, fin, seed=29):
+    gen = torch.Generator().manual_seed(seed)
+    dy = torch.randn(y.shape, generator=gen).to(torch.bfloat16)
+    dC = torch.randn(fin.predictor.shape, generator=gen)
+    dS = torch.randn(fin.S.shape, generator=gen)
+    loss = (y.float() * dy.cuda().float()).sum() + (fin.predictor * dC.cuda()).sum() + (fin.S * dS.cuda()).sum()
+    wrt = list(leaves) + (list(state) if state is not None else [])
+    got = torch.autograd.grad(loss, wrt)
+    ref = orc.backward(*oracle_args(cpu), dy.double().numpy(), dC_T=dC.double().numpy(),
+                       dS_T=dS.double().numpy(), initial_state=oracle_state(cpu))
+    d_er, d_wr = raw_gate_grads(cpu, ref)
+    gam = ref["geometry_write"]
+    if cpu["geometry_write"].ndim == 1:
+        gam = gam.sum(axis=(0, 1))
+    want = [ref["u"], ref["h"], ref["q"], ref["keys"][:, :, :, None], ref["values"][:, :, :, None],
+            ref["log_decay"], d_er[:, :, :, None], d_wr[:, :, :, None], gam]
+    names = ["u", "h", "q", "keys", "values", "log_decay", "erase_raw", "write_raw", "geometry_write"]
+    if state is not None:
+        want += [ref["C0"], ref["S0"]]
+        names += ["C0", "S0"]
+    for name, g, w in zip(names, got, want):
+        g = g.float().cpu().numpy()
+        assert np.isfinite(g).all(), name
+        assert g.shape == w.shape, (name, g.shape, w.shape)
+        assert rel_l2(g, w) <= GRAD_L2_TOL, (name, rel_l2(g, w))
+        assert max_rel(g, w) <= OUT_TOL, (name, max_rel(g, w))
+
+
+@pytest.mark.parametrize("B,T,H,r,V,gamma_mode", [
+    (1, 16, 2, 16, 16, "token"),      # upstream _native_inputs geometry
+    (2, 150, 2, 32, 48, "head"),      # crosses chunk boundaries, ragged tail, r != V
+    (1, 32, 1, 128, 128, "token"),    # multi-tile widths
+    (1, 256, 2, 128, 128, "token"),   # benchmark head geometry, four chunks
+    (1, 19, 2, 16, 16, "token"),      # ragged tail
+    (1, 1, 2, 16, 16, "token"),       # single token through the autograd path
+])
+def test_forward_and_full_vjp_match_checker(B, T, H, r, V, gamma_mode):
+    cpu, dev = make_inputs(B, T, H, r, V, seed=23, gamma_mode=gamma_mode)
+    leaves, state, y, fin = _native(dev, grad=True)
+    assert y.dtype == torch.bfloat16 and fin.predictor.dtype == torch.float32
+    _check_forward(cpu, y, fin)
+    _check_vjp(cpu, leaves, state, y, fin)
+
+
+def test_upstream_test_distribution_small_decay():
+    # decay -0.02*rand, gate logits 0.5*randn, gamma 0.2 (upstream :375-398)
+    cpu, dev = make_inputs(1, 16, 2, 16, 16, seed=7, decay_scale=0.02)
+    cpu["geometry_write"] = torch.full((1, 16, 2), 0.2)
+    dev["geometry_write"] = cpu["geometry_write"].cuda()
+    leaves, state, y, fin = _native(dev, grad=True)
+    _check_forward(cpu, y, fin)
+    _check_vjp(cpu, leaves, state, y, fin)
+
+
+@pytest.mark.parametrize("name", ["benchlike_r16_state", "benchlike_r32_t150_state"])
+def test_committed_golden_vectors(name):
+    """Upstream-generated vectors whose inputs are exactly BF16/FP32 representable."""
+    g = load_golden(name)
+    bf = lambda x: torch.from_numpy(x).to(torch.bfloat16).cuda()
+    f32 = lambda x: torch.from_numpy(x).float().cuda()
+    u, h, q, keys, values, decay, _, _, gamma = golden_inputs(g)
+    C0, S0 = golden_state(g)
+    leaves = [bf(u), bf(h), bf(q), bf(keys), bf(values), f32(decay), bf(g["in_erase_raw"]),
+              bf(g["in_write_raw"]), f32(gamma)]
+    for leaf, src in zip(leaves, (u, h, q, keys, values, decay, g["in_erase_raw"], g["in_write_raw"], gamma)):
+        assert np.array_equal(leaf.double().cpu().numpy(), src)  # nothing was rounded
+        leaf.requires_grad_()
+    state = SolveDeltaState(f32(C0).requires_grad_(), f32(S0).requires_grad_())
+    y, fin = solvedelta_native(*leaves, initial_state=state, return_final_state=True)
+    assert max_rel(y.float().cpu().numpy(), g["out"]) <= OUT_TOL
+    assert max_rel(fin.predictor.cpu().numpy(), g["C_T"]) <= STATE_TOL
+    assert max_rel(fin.S.cpu().numpy(), g["S_T"]) <= STATE_TOL
+    loss = ((y.float() * f32(g["dy"])).sum() + (fin.predictor * f32(g["dC_T"])).sum()
+            + (fin.S * f32(g["dS_T"])).sum())
+    got = torch.autograd.grad(loss, leaves + list(state))
+    er, wr = g["in_erase"], g["in_write"]
+    want = [g["grad_u"], g["grad_h"], g["grad_q"], g["grad_keys"], g["grad_values"], g["grad_log_decay"],
+            g["grad_erase"] * er * (1 - er), g["grad_write"] * wr * (1 - wr), g["grad_geometry_write"],
+            g["grad_C0"], g["grad_S0"]]
+    for i, (a, b) in enumerate(zip(got, want)):
+        assert rel_l2(a.float().cpu().numpy(), b) <= GRAD_L2_TOL, i
+
+
+def test_zero_geometry_write_reduces_to_gdn2_edit():
+    cpu, dev = make_inputs(1, 100, 2, 32, 32, seed=5, gamma_mode="zero", with_state=False)
+    _, _, y, fin = _native(dev)
+    # explicit GDN2 loop in FP64 on the same quantised inputs
+    q = torch.nn.functional.normalize(cpu["q"].double(), dim=-1)
+    k = torch.nn.functional.normalize(cpu["keys"].double()[:, :, :, 0], dim=-1)
+    er = torch.sigmoid(cpu["erase_raw"].double()[:, :, :, 0])
+    wr = torch.sigmoid(cpu["write_raw"].double()[:, :, :, 0])
+    v = cpu["values"].double()[:, :, :, 0]
+    mem = torch.zeros(1, 2, 32, 32, dtype=torch.float64)
+    rows = []
+    for t in range(100):
+        mem = cpu["log_decay"][:, t].double().exp()[..., None] * mem
+        pred = torch.einsum("bhrv,bhr->bhv", mem, er[:, t] * k[:, t])
+        mem = mem + k[:, t][..., :, None] * (wr[:, t] * v[:, t] - pred)[..., None, :]
+        rows.append(torch.einsum("bhrv,bhr->bhv", mem, q[:, t]))
+    want = torch.stack(rows, dim=1)
+    assert max_rel(y.float().cpu().numpy(), want.numpy()) <= OUT_TOL
+    assert max_rel(fin.S.cpu().numpy(), mem.numpy()) <= STATE_TOL
+    assert float(fin.predictor.abs().max()) == 0.0
+
+
+def test_aligned_and_ragged_split_continuation():
+    cpu, dev = make_inputs(1, 160, 2, 32, 32, seed=9)
+    _, _, y, fin = _native(dev)
+    for split in (64, 100):
+        def part(lo, hi, state):
+            sub = {n: (t[:, lo:hi] if n not in ("C0", "S0") and t.ndim >= 3 else t) for n, t in dev.items()}
+            sub["C0"], sub["S0"] = state
+            return _native(sub)
+        _, _, y1, s1 = part(0, split, (dev["C0"], dev["S0"]))
+        _, _, y2, s2 = part(split, 160, (s1.predictor, s1.S))
+        both = torch.cat([y1, y2], dim=1)
+        if split % 64 == 0:  # chunk-aligned: identical arithmetic, identical bits
+            assert torch.equal(both, y) and torch.equal(s2.predictor, fin.predictor) and torch.equal(s2.S, fin.S)
+        else:
+            assert max_rel(both.float().cpu().numpy(), y.float().cpu().numpy()) <= OUT_TOL
+            assert max_rel(s2.S.cpu().numpy(), fin.S.cpu().numpy()) <= STATE_TOL
+            assert max_rel(s2.predictor.cpu().numpy(), fin.predictor.cpu().numpy()) <= STATE_TOL
+
+
+def test_single_token_recurrent_inference_matches_checker():
+    cpu, dev = make_inputs(2, 1, 2, 64, 64, seed=13)
+    with torch.no_grad():
+        _, _, y, fin = _native(dev)
+    assert y.shape == (2, 1, 2, 64)
+    _check_forward(cpu, y, fin)
+    # sixteen decode steps equal one dense pass (upstream tests/model:264-301)
+    cpu, dev = make_inputs(1, 16, 2, 32, 32, seed=17)
+    _, _, y_dense, fin_dense = _native(dev)
+    state = (dev["C0"], dev["S0"])
+    outs = []
+    with torch.no_grad():
+        for t in range(16):
+            sub = {n: (x[:, t:t + 1] if n not in ("C0", "S0") and x.ndim >= 3 else x) for n, x in dev.items()}
+            sub["C0"], sub["S0"] = state
+            _, _, yt, st = _native(sub)
+            outs.append(yt)
+            state = (st.predictor, st.S)
+    assert max_rel(torch.cat(outs, 1).float().cpu().numpy(), y_dense.float().cpu().numpy()) <= OUT_TOL
+    assert max_rel(state[1].cpu().numpy(), fin_dense.S.cpu().numpy()) <= STATE_TOL
+
+
+def test_strided_projection_views_are_bit_equal_to_packed():
+    cpu, dev = make_inputs(1, 40, 2, 16, 16, seed=19)
+    _, _, y_ref, fin_ref = _native(dev)
+    # place every BF16 operand inside a wider row with an odd (non 16-byte) pitch
+    def strided(t):
+        wide = torch.zeros(*t.shape[:-1], 23, dtype=t.dtype, device=t.device)
+        wide[..., 3:3 + t.shape[-1]] = t
+        return wide[..., 3:3 + t.shape[-1]]
+    sub = dict(dev)
+    for n in ("u", "h", "q", "keys", "values", "erase_raw", "write_raw"):
+        sub[n] = strided(dev[n])
+        assert not sub[n].is_contiguous()
+    leaves, state, y, fin = _native(sub, grad=False)
+    # _native clones leaves (making them packed); call the entry point on the views directly
+    y, fin = solvedelta_native(sub["u"], sub["h"], sub["q"], sub["keys"], sub["values"], sub["log_decay"],
+                               sub["erase_raw"], sub["write_raw"], sub["geometry_write"],
+                               initial_state=SolveDeltaState(sub["C0"], sub["S0"]), return_final_state=True)
+    assert torch.equal(y, y_ref) and torch.equal(fin.S, fin_ref.S) and torch.equal(fin.predictor, fin_ref.predictor)
+
+
+def test_extreme_forgetting_remains_finite():
+    cpu, dev = make_inputs(1, 70, 2, 32, 32, seed=21)
+    dev["log_decay"] = torch.full_like(dev["log_decay"], -100.0)
+    leaves, state, y, fin = _native(dev, grad=True)
+    loss = y.float().sum() + fin.predictor.sum() + fin.S.sum()
+    grads = torch.autograd.grad(loss, list(leaves) + list(state))
+    assert torch.isfinite(y).all() and torch.isfinite(fin.S).all() and torch.isfinite(fin.predictor).all()
+    for g in grads:
+        assert torch.isfinite(g).all()
+
+
+def test_return_final_state_false_and_none_cotangents():
+    cpu, dev = make_inputs(1, 70, 1, 16, 16, seed=25)
+    leaves, state, y, fin = _native(dev, grad=True, return_final_state=False)
+    assert fin is None
+    (y.float().sum()).backward()
+    assert all(leaf.grad is not None and torch.isfinite(leaf.grad).all() for leaf in leaves)
+    # only a state cotangent, no output cotangent
+    leaves, state, y, fin = _native(dev, grad=True)
+    grads = torch.autograd.grad(fin.S.sum(), leaves[:5])
+    assert all(torch.isfinite(g).all() for g in grads)
+
+
+def test_contract_errors_match_upstream_types():
+    cpu, dev = make_inputs(1, 8, 1, 16, 16, seed=1)
+    a = [dev[n] for n in ("u", "h", "q", "keys", "values", "log_decay", "erase_raw", "write_raw", "geometry_write")]
+    with pytest.raises(ValueError, match="num_edits=1"):
+        bad = list(a)
+        bad[3] = a[3].expand(-1, -1, -1, 2, -1)
+        solvedelta_native(*bad)
+    with pytest.raises(TypeError):
+        bad = list(a)
+        bad[5] = a[5].double()
+        solvedelta_native(*bad)
+    with pytest.raises(ValueError, match="unit innermost stride"):
+        bad = list(a)
+        bad[0] = a[0].repeat_interleave(2, dim=-1)[..., ::2]
+        solvedelta_native(*bad)
+    with pytest.raises(ValueError, match="initial_state"):
+        solvedelta_native(*a, initial_state=SolveDeltaState(dev["C0"][:, :, :8], dev["S0"]))
+    with pytest.raises(TypeError, match="FP32"):
+        solvedelta_native(*a, initial_state=SolveDeltaState(dev["C0"].double(), dev["S0"].double()))
