@@ -110,6 +110,17 @@ int sd_forward_launches(const sd_shape *shape);
 int sd_backward_launches(const sd_shape *shape);
 
 /*
+ * Diagnostic (no upstream counterpart): runs sd_forward and, when `bwd` is not
+ * NULL, sd_backward, with a CUDA event between launches, waits for the stream
+ * and returns the device time of every launch in milliseconds (`count`
+ * entries, in launch order; sd_launch_name gives their names).  Not thread
+ * safe; not for use inside stream capture.
+ */
+int sd_profile_step(const sd_forward_args *fwd, const sd_backward_args *bwd, void *stream,
+                    float *ms, int capacity, int *count);
+const char *sd_launch_name(int index);
+
+/*
  * Introspection for tests: offset and size of a named intermediate panel
  * inside the saved (which = 0), forward-scratch (1) or backward-scratch (2)
  * buffer.  Returns SD_ERR_INVALID_ARGUMENT for an unknown name.

@@ -129,6 +129,21 @@ cudaError_t configure_kernels() {
     return cudaSuccess;
 }
 
+// Diagnostic launch recorder used by sd_profile_step only (not thread safe).
+struct LaunchRecorder {
+    cudaEvent_t ev[40];
+    int n;
+};
+LaunchRecorder* g_rec = nullptr;
+inline void mark(cudaStream_t stream) {
+    if (g_rec != nullptr && g_rec->n < 40) cudaEventRecord(g_rec->ev[g_rec->n++], stream);
+}
+
+const char* const kLaunchNames[] = {
+    "k_prep_fwd",          "k_state_scan[C]",     "k_primal_fwd",         "k_exterior_prep_fwd", "k_state_scan[S]",
+    "k_output_fwd",        "k_exterior_prep_bwd", "k_state_scan[dS]",     "k_exterior_pair_bwd", "k_sources_bwd",
+    "k_primal_bwd",        "k_predictor_prep_bwd", "k_state_scan[dC]",    "k_predictor_pair_bwd", "k_gate_closure_bwd"};
+
 int launch_status() { return cudaGetLastError() == cudaSuccess ? SD_OK : SD_ERR_LAUNCH_FAILED; }
 
 bool operands_ok(const sd_operand* ops, int n) {
@@ -226,6 +241,7 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
     const dim3 scan_grid(DP / SCAN_NS, streams);
 
     k_prep_fwd<<<chunks, NTHREADS, PREP_FWD_SMEM, stream>>>(p);
+    mark(stream);
     {
         ScanParams sp{};
         sp.P = p.Upd; sp.Q = p.Qc; sp.R = p.Ubar; sp.R2 = nullptr; sp.X2 = nullptr;
@@ -233,9 +249,12 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
         sp.init = a->C0; sp.fin = a->C_T;
         sp.NC = p.g.NC; sp.reverse = 0; sp.transposed_io = 1; sp.nrows = s->r; sp.ncols = s->r;
         k_state_scan<<<scan_grid, NTHREADS, SCAN_SMEM_BYTES, stream>>>(sp);
+    mark(stream);
     }
     k_primal_fwd<<<chunks, NTHREADS, PRIMAL_FWD_SMEM, stream>>>(p);
+    mark(stream);
     k_exterior_prep_fwd<<<chunks, NTHREADS, EXT_PREP_FWD_SMEM, stream>>>(p);
+    mark(stream);
     {
         ScanParams sp{};
         sp.P = p.Ud; sp.Q = p.Wd; sp.R = p.Dt; sp.R2 = nullptr; sp.X2 = nullptr;
@@ -243,8 +262,10 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
         sp.init = a->S0; sp.fin = a->S_T;
         sp.NC = p.g.NC; sp.reverse = 0; sp.transposed_io = 0; sp.nrows = s->r; sp.ncols = s->V;
         k_state_scan<<<scan_grid, NTHREADS, SCAN_SMEM_BYTES, stream>>>(sp);
+    mark(stream);
     }
     k_output_fwd<<<chunks, NTHREADS, OUTPUT_FWD_SMEM, stream>>>(p);
+    mark(stream);
     return launch_status();
 }
 
@@ -299,6 +320,7 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
     const dim3 scan_grid(DP / SCAN_NS, streams);
 
     k_exterior_prep_bwd<<<chunks, NTHREADS, EXT_PREP_BWD_SMEM, stream>>>(p);
+    mark(stream);
     {
         ScanParams sp{};
         sp.P = p.Pp; sp.Q = p.Qp; sp.R = p.Ag; sp.R2 = p.Xg; sp.X2 = p.Dyf;
@@ -306,11 +328,16 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
         sp.init = a->dS_T; sp.fin = a->dS0;
         sp.NC = p.g.NC; sp.reverse = 1; sp.transposed_io = 0; sp.nrows = s->r; sp.ncols = s->V;
         k_state_scan<<<scan_grid, NTHREADS, SCAN_SMEM_BYTES, stream>>>(sp);
+    mark(stream);
     }
     k_exterior_pair_bwd<<<chunks, NTHREADS, EXT_PAIR_BWD_SMEM, stream>>>(p);
+    mark(stream);
     k_sources_bwd<<<chunks, NTHREADS, SOURCES_BWD_SMEM, stream>>>(p);
+    mark(stream);
     k_primal_bwd<<<chunks, NTHREADS, PRIMAL_BWD_SMEM, stream>>>(p);
+    mark(stream);
     k_predictor_prep_bwd<<<chunks, NTHREADS, PRED_PREP_BWD_SMEM, stream>>>(p);
+    mark(stream);
     {
         ScanParams sp{};
         sp.P = p.Ppp; sp.Q = p.Qpp; sp.R = p.Rneg; sp.R2 = p.DG; sp.X2 = p.Khat;
@@ -318,10 +345,44 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
         sp.init = a->dC_T; sp.fin = a->dC0;
         sp.NC = p.g.NC; sp.reverse = 1; sp.transposed_io = 1; sp.nrows = s->r; sp.ncols = s->r;
         k_state_scan<<<scan_grid, NTHREADS, SCAN_SMEM_BYTES, stream>>>(sp);
+    mark(stream);
     }
     k_predictor_pair_bwd<<<chunks, NTHREADS, PRED_PAIR_BWD_SMEM, stream>>>(p);
+    mark(stream);
     k_gate_closure_bwd<<<chunks, NTHREADS, GATE_CLOSURE_SMEM, stream>>>(p);
+    mark(stream);
     return launch_status();
+}
+
+const char* sd_launch_name(int index) {
+    const int n = (int)(sizeof(kLaunchNames) / sizeof(kLaunchNames[0]));
+    return (index >= 0 && index < n) ? kLaunchNames[index] : "";
+}
+
+int sd_profile_step(const sd_forward_args* fwd, const sd_backward_args* bwd, void* stream_, float* ms,
+                    int capacity, int* count) {
+    if (!fwd || !ms || !count || capacity < 15) return SD_ERR_INVALID_ARGUMENT;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    LaunchRecorder rec;
+    rec.n = 0;
+    for (int i = 0; i < 40; ++i)
+        if (cudaEventCreate(&rec.ev[i]) != cudaSuccess) return SD_ERR_NO_DEVICE;
+    cudaEventRecord(rec.ev[rec.n++], stream);
+    g_rec = &rec;
+    int status = sd_forward(fwd, stream_);
+    if (status == SD_OK && bwd != nullptr) status = sd_backward(bwd, stream_);
+    g_rec = nullptr;
+    cudaError_t e = cudaStreamSynchronize(stream);
+    *count = 0;
+    if (status == SD_OK && e == cudaSuccess) {
+        for (int i = 1; i < rec.n && i - 1 < capacity; ++i) {
+            cudaEventElapsedTime(&ms[i - 1], rec.ev[i - 1], rec.ev[i]);
+            *count = i;
+        }
+    }
+    for (int i = 0; i < 40; ++i) cudaEventDestroy(rec.ev[i]);
+    if (e != cudaSuccess) return SD_ERR_LAUNCH_FAILED;
+    return status;
 }
 
 int sd_decode_step(const sd_decode_args* a, void* stream_) {
@@ -345,6 +406,7 @@ int sd_decode_step(const sd_decode_args* a, void* stream_) {
     p.S = a->S;
     p.y = a->y;
     k_decode_step<<<a->shape.B * a->shape.H, DEC_THREADS, 0, stream>>>(p);
+    mark(stream);
     return launch_status();
 }
 

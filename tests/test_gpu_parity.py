@@ -38,13 +38,17 @@ def _native(dev, *, grad=False, return_final_state=True):
     return leaves, state, y, fin
 
 
+def _np(t):
+    return t.detach().float().cpu().numpy()
+
+
 def _check_forward(cpu, y, fin):
     yo, so = orc.forward(*oracle_args(cpu), initial_state=oracle_state(cpu))
     assert torch.isfinite(y).all()
-    assert max_rel(y.float().cpu().numpy(), yo) <= OUT_TOL
-    assert rel_l2(y.float().cpu().numpy(), yo) <= OUT_TOL
-    assert max_rel(fin.predictor.cpu().numpy(), so.predictor) <= STATE_TOL or np.abs(so.predictor).max() < 1e-12
-    assert max_rel(fin.S.cpu().numpy(), so.S) <= STATE_TOL
+    assert max_rel(_np(y), yo) <= OUT_TOL
+    assert rel_l2(_np(y), yo) <= OUT_TOL
+    assert max_rel(_np(fin.predictor), so.predictor) <= STATE_TOL or np.abs(so.predictor).max() < 1e-12
+    assert max_rel(_np(fin.S), so.S) <= STATE_TOL
     return yo, so
 
 
@@ -117,9 +121,9 @@ def test_committed_golden_vectors(name):
         leaf.requires_grad_()
     state = SolveDeltaState(f32(C0).requires_grad_(), f32(S0).requires_grad_())
     y, fin = solvedelta_native(*leaves, initial_state=state, return_final_state=True)
-    assert max_rel(y.float().cpu().numpy(), g["out"]) <= OUT_TOL
-    assert max_rel(fin.predictor.cpu().numpy(), g["C_T"]) <= STATE_TOL
-    assert max_rel(fin.S.cpu().numpy(), g["S_T"]) <= STATE_TOL
+    assert max_rel(_np(y), g["out"]) <= OUT_TOL
+    assert max_rel(_np(fin.predictor), g["C_T"]) <= STATE_TOL
+    assert max_rel(_np(fin.S), g["S_T"]) <= STATE_TOL
     loss = ((y.float() * f32(g["dy"])).sum() + (fin.predictor * f32(g["dC_T"])).sum()
             + (fin.S * f32(g["dS_T"])).sum())
     got = torch.autograd.grad(loss, leaves + list(state))
@@ -128,7 +132,7 @@ def test_committed_golden_vectors(name):
             g["grad_erase"] * er * (1 - er), g["grad_write"] * wr * (1 - wr), g["grad_geometry_write"],
             g["grad_C0"], g["grad_S0"]]
     for i, (a, b) in enumerate(zip(got, want)):
-        assert rel_l2(a.float().cpu().numpy(), b) <= GRAD_L2_TOL, i
+        assert rel_l2(_np(a), b) <= GRAD_L2_TOL, i
 
 
 def test_zero_geometry_write_reduces_to_gdn2_edit():
@@ -148,8 +152,8 @@ def test_zero_geometry_write_reduces_to_gdn2_edit():
         mem = mem + k[:, t][..., :, None] * (wr[:, t] * v[:, t] - pred)[..., None, :]
         rows.append(torch.einsum("bhrv,bhr->bhv", mem, q[:, t]))
     want = torch.stack(rows, dim=1)
-    assert max_rel(y.float().cpu().numpy(), want.numpy()) <= OUT_TOL
-    assert max_rel(fin.S.cpu().numpy(), mem.numpy()) <= STATE_TOL
+    assert max_rel(_np(y), want.numpy()) <= OUT_TOL
+    assert max_rel(_np(fin.S), mem.numpy()) <= STATE_TOL
     assert float(fin.predictor.abs().max()) == 0.0
 
 
@@ -167,9 +171,9 @@ def test_aligned_and_ragged_split_continuation():
         if split % 64 == 0:  # chunk-aligned: identical arithmetic, identical bits
             assert torch.equal(both, y) and torch.equal(s2.predictor, fin.predictor) and torch.equal(s2.S, fin.S)
         else:
-            assert max_rel(both.float().cpu().numpy(), y.float().cpu().numpy()) <= OUT_TOL
-            assert max_rel(s2.S.cpu().numpy(), fin.S.cpu().numpy()) <= STATE_TOL
-            assert max_rel(s2.predictor.cpu().numpy(), fin.predictor.cpu().numpy()) <= STATE_TOL
+            assert max_rel(_np(both), _np(y)) <= OUT_TOL
+            assert max_rel(_np(s2.S), _np(fin.S)) <= STATE_TOL
+            assert max_rel(_np(s2.predictor), _np(fin.predictor)) <= STATE_TOL
 
 
 def test_single_token_recurrent_inference_matches_checker():
@@ -190,8 +194,8 @@ def test_single_token_recurrent_inference_matches_checker():
             _, _, yt, st = _native(sub)
             outs.append(yt)
             state = (st.predictor, st.S)
-    assert max_rel(torch.cat(outs, 1).float().cpu().numpy(), y_dense.float().cpu().numpy()) <= OUT_TOL
-    assert max_rel(state[1].cpu().numpy(), fin_dense.S.cpu().numpy()) <= STATE_TOL
+    assert max_rel(_np(torch.cat(outs, 1)), _np(y_dense)) <= OUT_TOL
+    assert max_rel(_np(state[1]), _np(fin_dense.S)) <= STATE_TOL
 
 
 def test_strided_projection_views_are_bit_equal_to_packed():
