@@ -304,7 +304,9 @@ def run_ours(opts, rank, world, local_rank):
     device = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    w = WORKLOAD
+    w = dict(WORKLOAD)
+    if opts.case == "small":
+        w.update(B=2, T=1024)
     B, T, H, r, V = w["B"], w["T"], w["H"], w["r"], w["V"]
     cpu = make_cpu_inputs(B, T, H, r, V, seed=rank)
     runner = DeviceStep(cpu, device)
@@ -380,26 +382,28 @@ def run_ours(opts, rank, world, local_rank):
             dst.copy_(src, non_blocking=True)
         return sum(x.numel() * x.element_size() for x in results)
 
-    e2e_steps = max(2, min(opts.steps, 5))
-    d2h = 0
-    for _ in range(2):
-        d2h = e2e_step()
-    barrier()
-    e0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e1.record()
-    barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item()) / e2e_steps
-    e2e = {"value": world * runner.tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
-           "steps": e2e_steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+    e2e = None
+    if not opts.skip_e2e:
+        e2e_steps = max(2, min(opts.steps, 5))
+        d2h = 0
+        for _ in range(2):
+            d2h = e2e_step()
+        barrier()
+        e0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item()) / e2e_steps
+        e2e = {"value": world * runner.tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+               "steps": e2e_steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
 
     if rank == 0:
         cpu_baseline = None
-        if world == 1:
+        if world == 1 and not opts.skip_cpu:
             threads = os.cpu_count() or 1
             rows = min(B, max(1, -(-threads // H)))
             calib = make_cpu_inputs(rows, 64, H, r, V, seed=0)
@@ -430,6 +434,10 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--case", default="full", choices=["full", "small"],
+                    help="small = B=2, T=1024 (for profiler captures); the reported metric is defined on full")
+    ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
+    ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg (profiler captures)")
     opts = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
