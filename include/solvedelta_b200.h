@@ -44,7 +44,8 @@ typedef enum {
     SD_ERR_UNSUPPORTED_SHAPE = -2, /* r or V outside 1..128 */
     SD_ERR_BUFFER_TOO_SMALL = -3,  /* saved / scratch smaller than the query says */
     SD_ERR_LAUNCH_FAILED = -4,     /* the CUDA runtime refused a launch */
-    SD_ERR_NO_DEVICE = -5          /* no CUDA device / wrong architecture */
+    SD_ERR_NO_DEVICE = -5,         /* no CUDA device / wrong architecture */
+    SD_ERR_STATIC_WORKSPACE_EXCEEDED = -6 /* sd_forward_static: shape too large, see below */
 } sd_status;
 
 /* A strided [B,T,H,width] operand: element strides of batch, token, head. */
@@ -104,6 +105,36 @@ size_t sd_backward_scratch_bytes(const sd_shape *shape);
 int sd_forward(const sd_forward_args *args, void *stream);
 int sd_backward(const sd_backward_args *args, void *stream);
 int sd_decode_step(const sd_decode_args *args, void *stream);
+
+/*
+ * sd_forward_static -- forward pass for callers that are not allowed to
+ * allocate device memory.  It has no counterpart in the upstream project.
+ *
+ * Who needs it: a serving loop that has handed all device memory to its own
+ * arena, code that runs while a stream is being captured, or a plugin host
+ * whose rules forbid cudaMalloc inside an operator -- such callers cannot
+ * produce the `saved` and `scratch` buffers sd_forward asks for.  Here the
+ * library brings its own: one fixed device array of SD_STATIC_WORKSPACE_BYTES
+ * that every GPU loading the library holds until the process exits.  The
+ * caller passes inputs, outputs and states exactly as for sd_forward; the
+ * fields `saved`, `saved_bytes`, `scratch`, `scratch_bytes` are ignored.
+ *
+ * Limit: sd_saved_bytes(shape) + sd_forward_scratch_bytes(shape) must not
+ * exceed SD_STATIC_WORKSPACE_BYTES, i.e. about B*H*ceil(T/64) <= 70 chunk
+ * tasks (for example B=1, H=8, T<=512).  Larger shapes are refused with
+ * SD_ERR_STATIC_WORKSPACE_EXCEEDED before anything is launched.
+ *
+ * The call itself never calls cudaMalloc, cudaFree or any allocating routine.
+ * The first call on each device looks up the array's device address (with
+ * that device current); make that first call before starting a stream
+ * capture.  All calls on a device share the one array: two calls whose
+ * kernels may overlap on the GPU (different streams) race on it -- keep them
+ * on one stream or order them yourself.  Nothing in the array needs zeroing
+ * between calls, and what it holds afterwards is not a usable `saved` buffer
+ * for sd_backward once another call has run.
+ */
+#define SD_STATIC_WORKSPACE_BYTES (32u * 1024u * 1024u)
+int sd_forward_static(const sd_forward_args *args, void *stream);
 
 /* Number of kernels one call launches for this shape (for accounting). */
 int sd_forward_launches(const sd_shape *shape);

@@ -106,7 +106,7 @@ EXPORTS = (
     "sd_saved_bytes", "sd_forward_scratch_bytes", "sd_backward_scratch_bytes",
     "sd_forward", "sd_backward", "sd_decode_step", "sd_forward_launches",
     "sd_backward_launches", "sd_panel_info", "sd_status_string", "sd_version",
-    "sd_chunk_tokens", "sd_profile_step", "sd_launch_name",
+    "sd_chunk_tokens", "sd_profile_step", "sd_launch_name", "sd_forward_static",
 )
 
 _lib = None
@@ -128,6 +128,8 @@ def load() -> ctypes.CDLL:
         getattr(lib, name).argtypes = [sp]
     lib.sd_forward.restype = ctypes.c_int
     lib.sd_forward.argtypes = [ctypes.POINTER(ForwardArgs), ctypes.c_void_p]
+    lib.sd_forward_static.restype = ctypes.c_int
+    lib.sd_forward_static.argtypes = [ctypes.POINTER(ForwardArgs), ctypes.c_void_p]
     lib.sd_backward.restype = ctypes.c_int
     lib.sd_backward.argtypes = [ctypes.POINTER(BackwardArgs), ctypes.c_void_p]
     lib.sd_decode_step.restype = ctypes.c_int

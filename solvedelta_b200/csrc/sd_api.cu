@@ -192,6 +192,9 @@ const char* sd_status_string(int status) {
         case SD_ERR_BUFFER_TOO_SMALL: return "saved or scratch buffer too small";
         case SD_ERR_LAUNCH_FAILED: return "CUDA launch failed";
         case SD_ERR_NO_DEVICE: return "no usable CUDA device";
+        case SD_ERR_STATIC_WORKSPACE_EXCEEDED:
+            return "shape needs more than SD_STATIC_WORKSPACE_BYTES of workspace: B*H*ceil(T/64) is too large for "
+                   "sd_forward_static, use sd_forward with caller-provided buffers";
         default: return "unknown status";
     }
 }
@@ -383,6 +386,41 @@ int sd_profile_step(const sd_forward_args* fwd, const sd_backward_args* bwd, voi
     for (int i = 0; i < 40; ++i) cudaEventDestroy(rec.ev[i]);
     if (e != cudaSuccess) return SD_ERR_LAUNCH_FAILED;
     return status;
+}
+
+// ---------------------------------------------------------------------------
+// Forward pass on library-owned scratch, for hosts that must not allocate.
+// The workspace of sd_forward (the `saved` and `scratch` regions) lives in one
+// file-scope device array; its device address is looked up once per device.
+static __device__ __align__(256) unsigned char g_static_workspace[SD_STATIC_WORKSPACE_BYTES];
+
+int sd_forward_static(const sd_forward_args* a, void* stream_) {
+    if (!a || !shape_ok(&a->shape)) return SD_ERR_INVALID_ARGUMENT;
+    if (!shape_supported(&a->shape)) return SD_ERR_UNSUPPORTED_SHAPE;
+    const size_t saved_bytes = sd_saved_bytes(&a->shape);
+    const size_t scratch_bytes = sd_forward_scratch_bytes(&a->shape);
+    if (saved_bytes + scratch_bytes > (size_t)SD_STATIC_WORKSPACE_BYTES) return SD_ERR_STATIC_WORKSPACE_EXCEEDED;
+    // In host code the array's name is only a handle; kernels need the device
+    // address, which differs per GPU.  Resolve it with that GPU current.
+    static void* base_of_device[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return SD_ERR_NO_DEVICE;
+    if (base_of_device[dev] == nullptr) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_static_workspace) != cudaSuccess || ptr == nullptr) {
+            cudaGetLastError();
+            return SD_ERR_NO_DEVICE;
+        }
+        base_of_device[dev] = ptr;
+    }
+    sd_forward_args local = *a;
+    local.saved = base_of_device[dev];
+    local.saved_bytes = saved_bytes;
+    local.scratch = static_cast<unsigned char*>(base_of_device[dev]) + saved_bytes;
+    local.scratch_bytes = scratch_bytes;
+    // Every panel of the workspace is written in full before any kernel reads
+    // it, so nothing left by an earlier call has to be cleared.
+    return sd_forward(&local, stream_);
 }
 
 int sd_decode_step(const sd_decode_args* a, void* stream_) {
