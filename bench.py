@@ -271,22 +271,24 @@ class DeviceStep:
 # = 16 KiB, state = 64 KiB, pair matrix = 16 KiB): every input and output of
 # the kernel counted once.
 KIB = 1024
+# f = FP32 panel 32 KiB, b = BF16 panel or BF16 operand chunk 16 KiB, s = FP32 state 64 KiB,
+# t = BF16 state 32 KiB, m = BF16 pair matrix 8 KiB
+_F, _B, _S, _T, _M = 32 * KIB, 16 * KIB, 64 * KIB, 32 * KIB, 8 * KIB
 KERNEL_BYTES_PER_CHUNK = {
-    "k_prep_fwd": (2 * 16 + 32 + 3 * 32) * KIB,
-    "k_state_scan[C]": (4 * 32 + 64) * KIB,
-    "k_primal_fwd": (2 * 16 + 32 + 32 + 64 + 32) * KIB,
-    "k_exterior_prep_fwd": (6 * 16 + 32 + 2 * 32 + 4 * 32 + 16) * KIB,
-    "k_state_scan[S]": (4 * 32 + 64) * KIB,
-    "k_output_fwd": (2 * 32 + 16 + 64 + 16) * KIB,
-    "k_exterior_prep_bwd": (5 * 16 + 32 + 2 * 32 + 6 * 32) * KIB,
-    "k_state_scan[dS]": (6 * 32 + 64) * KIB,
-    "k_exterior_pair_bwd": (6 * 32 + 2 * 64 + 4 * 32) * KIB,
-    "k_sources_bwd": (6 * 16 + 32 + 7 * 32 + 6 * 32 + 4 * 16) * KIB,
-    "k_primal_bwd": (2 * 16 + 32 + 3 * 32 + 64 + 3 * 32 + 16) * KIB,
-    "k_predictor_prep_bwd": (16 + 32 + 32 + 3 * 32) * KIB,
-    "k_state_scan[dC]": (6 * 32 + 64) * KIB,
-    "k_predictor_pair_bwd": (2 * 16 + 32 + 2 * 32 + 2 * 64 + 4 * 32) * KIB,
-    "k_gate_closure_bwd": (16 + 32 + 9 * 32 + 2 * 16 + 32) * KIB,
+    "k_prep_fwd": 2 * _B + _F + 4 * _F,                         # u,h,g -> Upd,Qc,Ubar,G
+    "k_state_scan[C]": 4 * _F + _S,                             # P,Q,R -> X, ckpt
+    "k_primal_fwd": 2 * _B + 2 * _F + _S + _F,                  # u,k,G,Delta,Ct -> d
+    "k_exterior_prep_fwd": 6 * _B + 3 * _F + 3 * _F + _B + _M,  # 6 operands,G,Delta,d -> Wd,Ud,Dt,Xg,Aqd
+    "k_state_scan[S]": 4 * _F + _S,
+    "k_output_fwd": _B + _M + _F + _S + _B,                     # Xg,Aqd,Zt,S -> y
+    "k_exterior_prep_bwd": 5 * _B + 3 * _F + 6 * _B,            # u,k,q,er,dy,G,Delta,d -> Ag,Xg,Dyf,Dneg,Pp,Qp
+    "k_state_scan_b[dS]": 6 * _B + _T,
+    "k_exterior_pair_bwd": 5 * _B + _F + _S + _T + 4 * _B,      # Dyf,dR,Dneg,Xg,Ag,Zt,S,dSe -> A1,A2,PY,dDt
+    "k_sources_bwd": 6 * _B + 3 * _F + 5 * _B + 5 * _F + _B + 4 * _B,
+    "k_primal_bwd": 2 * _B + 2 * _F + _B + _S + 2 * _F + 5 * _B + _B,
+    "k_state_scan_b[dC]": 6 * _B + _T,
+    "k_predictor_pair_bwd": 2 * _B + 2 * _F + _B + _S + _T + 4 * _B,
+    "k_gate_closure_bwd": _B + _F + 3 * _F + 6 * _B + 2 * _B + _F,
 }
 
 

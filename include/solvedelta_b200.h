@@ -158,6 +158,10 @@ const char *sd_launch_name(int index);
  */
 int sd_panel_info(const sd_shape *shape, int which, const char *name,
                   size_t *offset, size_t *bytes);
+/* Element layout of that panel: FP32 0 = [64][128] panel, 1 = [64][64] matrix,
+ * 2 = [128][128] state, 3 = [128] vector; BF16 4 = panel, 5 = matrix, 6 = state.
+ * Negative = unknown name. */
+int sd_panel_kind(const sd_shape *shape, int which, const char *name);
 
 const char *sd_status_string(int status);
 int sd_version(void);

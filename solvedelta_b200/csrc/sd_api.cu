@@ -16,24 +16,29 @@ using namespace sd;
 
 struct PanelDesc {
     const char* name;
-    int kind;  // 0 = panel [CL][DP], 1 = matrix [CL][CL], 2 = state [DP][DP], 3 = vector [DP]
+    // FP32: 0 = panel [CL][DP], 1 = matrix [CL][CL], 2 = state [DP][DP], 3 = vector [DP]
+    // BF16: 4 = panel, 5 = matrix, 6 = state
+    int kind;
 };
 
-const PanelDesc kSaved[] = {{"Lam", 3}, {"Delta", 0}, {"Dprim", 0}, {"Zt", 0}, {"CtCk", 2}, {"SCk", 2}};
-const PanelDesc kFwd[] = {{"Upd", 0}, {"Qc", 0}, {"Ubar", 0}, {"Wd", 0}, {"Ud", 0}, {"Dt", 0}, {"Xg", 0}, {"Aqd", 1}};
-const PanelDesc kBwd[] = {{"Pp", 0},     {"Qp", 0},     {"Ag", 0},     {"Xg", 0},    {"Dyf", 0},   {"Dneg", 0},
-                          {"dR", 0},     {"dSeCk", 2},  {"A1", 0},     {"A2", 0},    {"PY", 0},    {"dDt", 0},
-                          {"SdS", 3},    {"duPart", 0}, {"dkPart", 0}, {"dGPart", 0}, {"dDelta", 0}, {"DG", 0},
-                          {"Xext", 0},   {"Tpre", 0},   {"Khat", 0},   {"Ppp", 0},   {"Qpp", 0},   {"Rneg", 0},
-                          {"dRr", 0},    {"dCeCk", 2},  {"dUbar", 0},  {"dUt", 0},   {"Ti", 0},    {"Tj", 0},
+const PanelDesc kSaved[] = {{"Lam", 3}, {"G", 0}, {"Delta", 0}, {"Dprim", 0}, {"Zt", 0}, {"CtCk", 2}, {"SCk", 2}};
+const PanelDesc kFwd[] = {{"Upd", 0}, {"Qc", 0}, {"Ubar", 0}, {"Wd", 0}, {"Ud", 0}, {"Dt", 0}, {"Xg", 4}, {"Aqd", 5}};
+const PanelDesc kBwd[] = {{"Pp", 4},     {"Qp", 4},     {"Ag", 4},     {"Xg", 4},     {"Dyf", 4},    {"Dneg", 4},
+                          {"dR", 4},     {"dSeCk", 6},  {"A1", 4},     {"A2", 4},     {"PY", 4},     {"dDt", 4},
+                          {"SdS", 3},    {"duPart", 0}, {"dkPart", 0}, {"dGPart", 0}, {"dDelta", 0}, {"DG", 4},
+                          {"Xext", 0},   {"Tpre", 4},   {"Khat", 4},   {"Ppp", 4},    {"Qpp", 4},    {"Rneg", 4},
+                          {"dRr", 4},    {"dCeCk", 6},  {"dUbar", 4},  {"dUt", 4},    {"Ti", 4},     {"Tj", 4},
                           {"CdC", 3}};
 
-size_t kind_floats(int kind) {
+size_t kind_bytes(int kind) {
     switch (kind) {
-        case 0: return size_t(CL) * DP;
-        case 1: return size_t(CL) * CL;
-        case 2: return size_t(DP) * DP;
-        default: return DP;
+        case 0: return size_t(CL) * DP * 4;
+        case 1: return size_t(CL) * CL * 4;
+        case 2: return size_t(DP) * DP * 4;
+        case 3: return size_t(DP) * 4;
+        case 4: return size_t(CL) * DP * 2;
+        case 5: return size_t(CL) * CL * 2;
+        default: return size_t(DP) * DP * 2;
     }
 }
 
@@ -51,20 +56,22 @@ template <size_t N>
 size_t layout_bytes(const PanelDesc (&tab)[N], const sd_shape* s) {
     size_t chunks = (size_t)total_chunks(s), total = 0;
     for (size_t i = 0; i < N; ++i) {
-        size_t bytes = kind_floats(tab[i].kind) * chunks * sizeof(float);
+        size_t bytes = kind_bytes(tab[i].kind) * chunks;
         total += (bytes + 255) & ~size_t(255);
     }
     return total;
 }
 
 template <size_t N>
-bool layout_find(const PanelDesc (&tab)[N], const sd_shape* s, const char* name, size_t* off, size_t* bytes) {
+bool layout_find(const PanelDesc (&tab)[N], const sd_shape* s, const char* name, size_t* off, size_t* bytes,
+                 int* kind = nullptr) {
     size_t chunks = (size_t)total_chunks(s), total = 0;
     for (size_t i = 0; i < N; ++i) {
-        size_t b = kind_floats(tab[i].kind) * chunks * sizeof(float);
+        size_t b = kind_bytes(tab[i].kind) * chunks;
         if (std::strcmp(tab[i].name, name) == 0) {
             *off = total;
             *bytes = b;
+            if (kind) *kind = tab[i].kind;
             return true;
         }
         total += (b + 255) & ~size_t(255);
@@ -77,6 +84,10 @@ float* panel_at(const PanelDesc (&tab)[N], const sd_shape* s, void* base, const 
     size_t off = 0, bytes = 0;
     if (!layout_find(tab, s, name, &off, &bytes)) return nullptr;
     return reinterpret_cast<float*>(reinterpret_cast<char*>(base) + off);
+}
+template <size_t N>
+bf16* bpanel_at(const PanelDesc (&tab)[N], const sd_shape* s, void* base, const char* name) {
+    return reinterpret_cast<bf16*>(panel_at(tab, s, base, name));
 }
 
 Operand make_operand(const sd_operand& o, int elem_bytes) {
@@ -118,11 +129,10 @@ cudaError_t configure_kernels() {
     if ((e = allow_smem(k_exterior_prep_fwd, EXT_PREP_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_output_fwd, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_state_scan, SCAN_SMEM_BYTES)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_state_scan_b, SCAN_B_SMEM_BYTES)) != cudaSuccess) return e;
     if ((e = allow_smem(k_exterior_prep_bwd, EXT_PREP_BWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_exterior_pair_bwd, EXT_PAIR_BWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_sources_bwd, SOURCES_BWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_primal_bwd, PRIMAL_BWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_predictor_prep_bwd, PRED_PREP_BWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_predictor_pair_bwd, PRED_PAIR_BWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_gate_closure_bwd, GATE_CLOSURE_SMEM)) != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) done[dev] = true;
@@ -141,8 +151,8 @@ inline void mark(cudaStream_t stream) {
 
 const char* const kLaunchNames[] = {
     "k_prep_fwd",          "k_state_scan[C]",     "k_primal_fwd",         "k_exterior_prep_fwd", "k_state_scan[S]",
-    "k_output_fwd",        "k_exterior_prep_bwd", "k_state_scan[dS]",     "k_exterior_pair_bwd", "k_sources_bwd",
-    "k_primal_bwd",        "k_predictor_prep_bwd", "k_state_scan[dC]",    "k_predictor_pair_bwd", "k_gate_closure_bwd"};
+    "k_output_fwd",        "k_exterior_prep_bwd", "k_state_scan_b[dS]",   "k_exterior_pair_bwd", "k_sources_bwd",
+    "k_primal_bwd",        "k_state_scan_b[dC]",  "k_predictor_pair_bwd", "k_gate_closure_bwd"};
 
 int launch_status() { return cudaGetLastError() == cudaSuccess ? SD_OK : SD_ERR_LAUNCH_FAILED; }
 
@@ -179,8 +189,19 @@ int sd_panel_info(const sd_shape* shape, int which, const char* name, size_t* of
     return found ? SD_OK : SD_ERR_INVALID_ARGUMENT;
 }
 
+int sd_panel_kind(const sd_shape* shape, int which, const char* name) {
+    if (!shape_ok(shape) || !name || !shape_supported(shape)) return SD_ERR_INVALID_ARGUMENT;
+    size_t off = 0, bytes = 0;
+    int kind = -1;
+    bool found = false;
+    if (which == 0) found = layout_find(kSaved, shape, name, &off, &bytes, &kind);
+    if (which == 1) found = layout_find(kFwd, shape, name, &off, &bytes, &kind);
+    if (which == 2) found = layout_find(kBwd, shape, name, &off, &bytes, &kind);
+    return found ? kind : SD_ERR_INVALID_ARGUMENT;
+}
+
 int sd_forward_launches(const sd_shape* shape) { return shape_ok(shape) ? 6 : 0; }
-int sd_backward_launches(const sd_shape* shape) { return shape_ok(shape) ? 9 : 0; }
+int sd_backward_launches(const sd_shape* shape) { return shape_ok(shape) ? 8 : 0; }
 int sd_chunk_tokens(void) { return CL; }
 int sd_version(void) { return 1; }
 
@@ -229,9 +250,10 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
     p.Wd = panel_at(kFwd, s, a->scratch, "Wd");
     p.Ud = panel_at(kFwd, s, a->scratch, "Ud");
     p.Dt = panel_at(kFwd, s, a->scratch, "Dt");
-    p.Xg = panel_at(kFwd, s, a->scratch, "Xg");
-    p.Aqd = panel_at(kFwd, s, a->scratch, "Aqd");
+    p.Xg = bpanel_at(kFwd, s, a->scratch, "Xg");
+    p.Aqd = bpanel_at(kFwd, s, a->scratch, "Aqd");
     p.Lam = panel_at(kSaved, s, a->saved, "Lam");
+    p.Gp = panel_at(kSaved, s, a->saved, "G");
     p.Delta = panel_at(kSaved, s, a->saved, "Delta");
     p.Dprim = panel_at(kSaved, s, a->saved, "Dprim");
     p.Zt = panel_at(kSaved, s, a->saved, "Zt");
@@ -303,17 +325,20 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
     p.dy = make_operand(a->dy, 2);
     void* sv = const_cast<void*>(a->saved);
     p.Lam = panel_at(kSaved, s, sv, "Lam");
+    p.Gp = panel_at(kSaved, s, sv, "G");
     p.Delta = panel_at(kSaved, s, sv, "Delta");
     p.Dprim = panel_at(kSaved, s, sv, "Dprim");
     p.Zt = panel_at(kSaved, s, sv, "Zt");
     p.CtCk = panel_at(kSaved, s, sv, "CtCk");
     p.SCk = panel_at(kSaved, s, sv, "SCk");
 #define SD_BP(field) p.field = panel_at(kBwd, s, a->scratch, #field)
-    SD_BP(Pp); SD_BP(Qp); SD_BP(Ag); SD_BP(Xg); SD_BP(Dyf); SD_BP(Dneg); SD_BP(dR); SD_BP(dSeCk);
-    SD_BP(A1); SD_BP(A2); SD_BP(PY); SD_BP(dDt); SD_BP(SdS);
-    SD_BP(duPart); SD_BP(dkPart); SD_BP(dGPart); SD_BP(dDelta); SD_BP(DG); SD_BP(Xext); SD_BP(Tpre); SD_BP(Khat);
-    SD_BP(Ppp); SD_BP(Qpp); SD_BP(Rneg); SD_BP(dRr); SD_BP(dCeCk);
-    SD_BP(dUbar); SD_BP(dUt); SD_BP(Ti); SD_BP(Tj); SD_BP(CdC);
+#define SD_BB(field) p.field = bpanel_at(kBwd, s, a->scratch, #field)
+    SD_BB(Pp); SD_BB(Qp); SD_BB(Ag); SD_BB(Xg); SD_BB(Dyf); SD_BB(Dneg); SD_BB(dR); SD_BB(dSeCk);
+    SD_BB(A1); SD_BB(A2); SD_BB(PY); SD_BB(dDt); SD_BB(DG); SD_BB(Tpre); SD_BB(Khat);
+    SD_BB(Ppp); SD_BB(Qpp); SD_BB(Rneg); SD_BB(dRr); SD_BB(dCeCk);
+    SD_BB(dUbar); SD_BB(dUt); SD_BB(Ti); SD_BB(Tj);
+    SD_BP(duPart); SD_BP(dkPart); SD_BP(dGPart); SD_BP(dDelta); SD_BP(Xext); SD_BP(SdS); SD_BP(CdC);
+#undef SD_BB
 #undef SD_BP
     p.du = a->du; p.dh = a->dh; p.dq = a->dq; p.dk = a->dkeys; p.dv = a->dvalues;
     p.der = a->derase_raw; p.dwr = a->dwrite_raw; p.dld = a->dlog_decay; p.dgam = a->dgamma;
@@ -325,29 +350,27 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
     k_exterior_prep_bwd<<<chunks, NTHREADS, EXT_PREP_BWD_SMEM, stream>>>(p);
     mark(stream);
     {
-        ScanParams sp{};
+        ScanParamsB sp{};
         sp.P = p.Pp; sp.Q = p.Qp; sp.R = p.Ag; sp.R2 = p.Xg; sp.X2 = p.Dyf;
         sp.lam = p.Lam; sp.X = p.dR; sp.ck = p.dSeCk;
         sp.init = a->dS_T; sp.fin = a->dS0;
         sp.NC = p.g.NC; sp.reverse = 1; sp.transposed_io = 0; sp.nrows = s->r; sp.ncols = s->V;
-        k_state_scan<<<scan_grid, NTHREADS, SCAN_SMEM_BYTES, stream>>>(sp);
+        k_state_scan_b<<<scan_grid, NTHREADS, SCAN_B_SMEM_BYTES, stream>>>(sp);
     mark(stream);
     }
     k_exterior_pair_bwd<<<chunks, NTHREADS, EXT_PAIR_BWD_SMEM, stream>>>(p);
     mark(stream);
-    k_sources_bwd<<<chunks, NTHREADS, SOURCES_BWD_SMEM, stream>>>(p);
+    k_sources_bwd<<<chunks, NTHREADS, 0, stream>>>(p);
     mark(stream);
     k_primal_bwd<<<chunks, NTHREADS, PRIMAL_BWD_SMEM, stream>>>(p);
     mark(stream);
-    k_predictor_prep_bwd<<<chunks, NTHREADS, PRED_PREP_BWD_SMEM, stream>>>(p);
-    mark(stream);
     {
-        ScanParams sp{};
+        ScanParamsB sp{};
         sp.P = p.Ppp; sp.Q = p.Qpp; sp.R = p.Rneg; sp.R2 = p.DG; sp.X2 = p.Khat;
         sp.lam = p.Lam; sp.X = p.dRr; sp.ck = p.dCeCk;
         sp.init = a->dC_T; sp.fin = a->dC0;
         sp.NC = p.g.NC; sp.reverse = 1; sp.transposed_io = 1; sp.nrows = s->r; sp.ncols = s->r;
-        k_state_scan<<<scan_grid, NTHREADS, SCAN_SMEM_BYTES, stream>>>(sp);
+        k_state_scan_b<<<scan_grid, NTHREADS, SCAN_B_SMEM_BYTES, stream>>>(sp);
     mark(stream);
     }
     k_predictor_pair_bwd<<<chunks, NTHREADS, PRED_PAIR_BWD_SMEM, stream>>>(p);
@@ -364,7 +387,7 @@ const char* sd_launch_name(int index) {
 
 int sd_profile_step(const sd_forward_args* fwd, const sd_backward_args* bwd, void* stream_, float* ms,
                     int capacity, int* count) {
-    if (!fwd || !ms || !count || capacity < 15) return SD_ERR_INVALID_ARGUMENT;
+    if (!fwd || !ms || !count || capacity < 14) return SD_ERR_INVALID_ARGUMENT;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     LaunchRecorder rec;
     rec.n = 0;

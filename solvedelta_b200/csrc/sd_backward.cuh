@@ -1,11 +1,14 @@
 // Chunk-parallel backward kernels: one CTA per (stream, chunk).
 //
 // Pipeline: k_exterior_prep_bwd -> scan(dS, reverse) -> k_exterior_pair_bwd
-//           -> k_sources_bwd -> k_primal_bwd -> k_predictor_prep_bwd
+//           -> k_sources_bwd -> k_primal_bwd (also prepares the dC scan)
 //           -> scan(dC, reverse) -> k_predictor_pair_bwd -> k_gate_closure_bwd.
 // Forward locals are recomputed from the raw inputs and the panels the forward
-// pass kept (Delta, d, Z~, the chunk-entry states and lam).
+// pass kept (G, Delta, d, Z~, the chunk-entry states and lam).  Gradients
+// tolerate BF16 operands, so every contraction here is BF16 x BF16 -> FP32 and
+// every panel that only feeds a contraction or a gradient row is BF16 in HBM.
 #pragma once
+#include "sd_bf16.cuh"
 #include "sd_common.cuh"
 #include "sd_forward.cuh"
 
@@ -14,14 +17,15 @@ namespace sd {
 struct BwdParams {
     Geometry g;
     Operand u, h, q, k, v, er, wr, ld, gam, dy;
-    // kept by forward
-    const float *Lam, *Delta, *Dprim, *Zt, *CtCk, *SCk;
-    // backward scratch panels
-    float *Pp, *Qp, *Ag, *Xg, *Dyf, *Dneg, *dR, *dSeCk;
-    float *A1, *A2, *PY, *dDt, *SdS;
-    float *duPart, *dkPart, *dGPart, *dDelta, *DG, *Xext, *Tpre, *Khat;
-    float *Ppp, *Qpp, *Rneg, *dRr, *dCeCk;
-    float *dUbar, *dUt, *Ti, *Tj, *CdC;
+    // kept by forward (FP32)
+    const float *Lam, *Gp, *Delta, *Dprim, *Zt, *CtCk, *SCk;
+    // backward scratch: BF16 contraction operands / scanned panels
+    bf16 *Pp, *Qp, *Ag, *Xg, *Dyf, *Dneg, *dR, *dSeCk;
+    bf16 *A1, *A2, *PY, *dDt, *DG, *Tpre, *Khat;
+    bf16 *Ppp, *Qpp, *Rneg, *dRr, *dCeCk;
+    bf16 *dUbar, *dUt, *Ti, *Tj;
+    // FP32 partial cotangents and reductions
+    float *duPart, *dkPart, *dGPart, *dDelta, *Xext, *SdS, *CdC;
     // outputs
     void *du, *dh, *dq, *dk, *dv, *der, *dwr;
     float *dld, *dgam;
@@ -37,39 +41,86 @@ __device__ __forceinline__ void norm_vjp8(const float (&dxh)[8], const float (&x
     for (int e = 0; e < 8; ++e) dx[e] = (dxh[e] - dot * xh[e]) * rstd;
 }
 
+// Transposed unit-triangular solve on BF16 panels: (I + sgn*M)^T X = RHS, two
+// panels of DP columns, FP32 arithmetic in registers.  Mr[i][k] = M[k][i] for
+// k > i, zero elsewhere (same convention as trisolve<true>).
+__device__ __forceinline__ void trisolve_upper_b(const float* Mr, float sgn, bf16* P0, bf16* P1) {
+    bf16* P = (threadIdx.x < DP) ? P0 : P1;
+    const int col = threadIdx.x & (DP - 1);
+    float x[CL];
+#pragma unroll
+    for (int i = 0; i < CL; ++i) x[i] = __bfloat162float(P[i * LDB + col]);
+#pragma unroll
+    for (int i = CL - 2; i >= 0; --i) {
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;  // independent chains
+#pragma unroll
+        for (int k4 = ((i + 1) & ~3); k4 < CL; k4 += 4) {
+            float4 m = *reinterpret_cast<const float4*>(Mr + i * LDA + k4);
+            a0 = fmaf(m.x, x[k4], a0);
+            a1 = fmaf(m.y, x[k4 + 1], a1);
+            a2 = fmaf(m.z, x[k4 + 2], a2);
+            a3 = fmaf(m.w, x[k4 + 3], a3);
+        }
+        x[i] = fmaf(-sgn, (a0 + a1) + (a2 + a3), x[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < CL; ++i) P[i * LDB + col] = __float2bfloat16_rn(x[i]);
+}
+
+// shared BF16 panel -> dense BF16 global panel
+__device__ __forceinline__ void s2g_bpanel(bf16* g, const bf16* sm) {
+    for (int idx = threadIdx.x; idx < CL * (DP / 8); idx += NTHREADS) {
+        int i = idx >> 4, c8 = (idx & 15) << 3;
+        *reinterpret_cast<uint4*>(g + i * DP + c8) = *reinterpret_cast<const uint4*>(sm + i * LDB + c8);
+    }
+}
+// whole BF16 global state [DP][DP] -> shared [DP][LDB], asynchronously
+__device__ __forceinline__ void async_bstate(bf16* sm, const bf16* g) {
+    for (int idx = threadIdx.x; idx < DP * (DP / 8); idx += NTHREADS) {
+        int i = idx >> 4, c8 = (idx & 15) << 3;
+        cp16(sm + i * LDB + c8, g + i * DP + c8);
+    }
+}
+__device__ __forceinline__ bf16* bstate_ptr(bf16* base, long long gi) { return base + gi * (long long)(DP * DP); }
+__device__ __forceinline__ const bf16* bstate_ptr(const bf16* base, long long gi) {
+    return base + gi * (long long)(DP * DP);
+}
+
+template <int NTW>
+__device__ __forceinline__ void epi_store_bpanel(float (&acc)[NTW][4], int r0, int n0, bf16* gpanel) {
+    warp_epi<NTW>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
+        *reinterpret_cast<__nv_bfloat162*>(gpanel + i * DP + j) = __floats2bfloat162_rn(v0, v1);
+    });
+}
+
 // ---------------------------------------------------------------------------
 // Recompute Xg, ag, Dneg, Dt, Aqd, Aed; solve the transposed system for
 //   P' = (I-Aed)^-T (Aqd^T dy),  Q' = (I-Aed)^-T Dt
 // so that the reverse S scan is dR = P' + Q' dS.
-constexpr size_t EXT_PREP_BWD_SMEM = 5 * SLOT_BYTES + 2 * MAT_BYTES + DP * sizeof(float);
+constexpr size_t EXT_PREP_BWD_SMEM = 5 * BSLOT_BYTES + BMAT_BYTES + MAT_BYTES;
 
-__global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) {
-    extern __shared__ __align__(16) float smem[];
-    float* s_xg = smem;
-    float* s_ag = s_xg + SLOT_FLOATS;
-    float* s_dn = s_ag + SLOT_FLOATS;
-    float* s_dy = s_dn + SLOT_FLOATS;
-    float* s_dt = s_dy + SLOT_FLOATS;  // holds G first, Dt afterwards
-    float* s_aqd = s_dt + SLOT_FLOATS;
-    float* s_aedT = s_aqd + MAT_FLOATS;
-    float* s_GL = s_aedT + MAT_FLOATS;
+__global__ void __launch_bounds__(NTHREADS, 2) k_exterior_prep_bwd(BwdParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* b_xg = reinterpret_cast<bf16*>(smem_raw);
+    bf16* b_ag = b_xg + BSLOT_ELEMS;
+    bf16* b_dn = b_ag + BSLOT_ELEMS;
+    bf16* b_dy = b_dn + BSLOT_ELEMS;
+    bf16* b_dt = b_dy + BSLOT_ELEMS;
+    bf16* b_aqd = b_dt + BSLOT_ELEMS;
+    float* f_aedT = reinterpret_cast<float*>(b_aqd + BMAT_ELEMS);
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r, V = p.g.V;
-
-    load_f32_panel(p.ld, ch, r, s_dt);
-    __syncthreads();
-    chunk_cumsum(s_dt);
-    __syncthreads();
-    if (threadIdx.x < DP) s_GL[threadIdx.x] = s_dt[(CL - 1) * LDP + threadIdx.x];
-    __syncthreads();
     {
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
         const float* gDelta = panel_ptr(p.Delta, ch.gi);
         const float* gd = panel_ptr(p.Dprim, ch.gi);
-        float* gAg = panel_ptr(p.Ag, ch.gi);
-        float* gXg = panel_ptr(p.Xg, ch.gi);
-        float* gDyf = panel_ptr(p.Dyf, ch.gi);
-        float* gDneg = panel_ptr(p.Dneg, ch.gi);
+        const float* gG = panel_ptr(p.Gp, ch.gi);
+        bf16* gAg = bpanel_ptr(p.Ag, ch.gi);
+        bf16* gXg = bpanel_ptr(p.Xg, ch.gi);
+        bf16* gDyf = bpanel_ptr(p.Dyf, ch.gi);
+        bf16* gDneg = bpanel_ptr(p.Dneg, ch.gi);
+        float GL[8];
+        load8_panel(gG, CL - 1, c0, GL);
 #pragma unroll 1
         for (int pp = 0; pp < CL / 16; ++pp) {
             const int i = lr + 16 * pp;
@@ -79,9 +130,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) 
             load8_norm(p.q, ch, i, c0, r, qh);
             load8_panel(gDelta, i, c0, dl);
             load8_panel(gd, i, c0, d);
+            load8_panel(gG, i, c0, G);
             load8_bf16(row_bf16(p.er, ch, i), c0, r, p.er.vec, i < ch.nvalid, er);
             load8_bf16(row_bf16(p.dy, ch, i), c0, V, p.dy.vec, i < ch.nvalid, dy);
-            load8_smem(s_dt, i, c0, G);
 #pragma unroll
             for (int e = 0; e < 8; ++e) se[e] = sigmoidf_(er[e]);
             Sources src;
@@ -93,17 +144,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) 
                 xg[e] = src.chi[e] * ep;
                 ag[e] = -src.e[e] * ep;
                 dn[e] = d[e] * clamp_exp_neg(G[e]);
-                dt[e] = d[e] * __expf(s_GL[c0 + e] - G[e]);
+                dt[e] = d[e] * __expf(GL[e] - G[e]);
             }
-            store8_smem(s_xg, i, c0, xg);
-            store8_smem(s_ag, i, c0, ag);
-            store8_smem(s_dn, i, c0, dn);
-            store8_smem(s_dy, i, c0, dy);
-            store8_smem(s_dt, i, c0, dt);
-            store8_panel(gAg, i, c0, ag);
-            store8_panel(gXg, i, c0, xg);
-            store8_panel(gDyf, i, c0, dy);
-            store8_panel(gDneg, i, c0, dn);
+            store8_bsm(b_xg, i, c0, xg);
+            store8_bsm(b_ag, i, c0, ag);
+            store8_bsm(b_dn, i, c0, dn);
+            store8_bsm(b_dy, i, c0, dy);
+            store8_bsm(b_dt, i, c0, dt);
+            store8_bpanel(gAg, i, c0, ag);
+            store8_bpanel(gXg, i, c0, xg);
+            store8_bpanel(gDyf, i, c0, dy);
+            store8_bpanel(gDneg, i, c0, dn);
         }
     }
     __syncthreads();
@@ -112,16 +163,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) 
         acc_zero<4>(a1);
         acc_zero<4>(a2);
         const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
-        auto fb = [&](int k, int n) { return s_dn[n * LDP + k]; };
-        warp_mma<4>(a1, r0, n0, 0, DP, [&](int i, int k) { return s_xg[i * LDP + k]; }, fb);
-        warp_mma<4>(a2, r0, n0, 0, DP, [&](int i, int k) { return s_ag[i * LDP + k]; }, fb);
+        warp_mma_bf16<4, false, true>(a1, b_xg, LDB, b_dn, LDB, r0, n0, 0, DP);
+        warp_mma_bf16<4, false, true>(a2, b_ag, LDB, b_dn, LDB, r0, n0, 0, DP);
         warp_epi<4>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
-            s_aqd[i * LDA + j] = (j <= i) ? v0 : 0.f;
-            s_aqd[i * LDA + j + 1] = (j + 1 <= i) ? v1 : 0.f;
+            *reinterpret_cast<__nv_bfloat162*>(b_aqd + i * LDM + j) =
+                __floats2bfloat162_rn((j <= i) ? v0 : 0.f, (j + 1 <= i) ? v1 : 0.f);
         });
         warp_epi<4>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
-            s_aedT[j * LDA + i] = (j < i) ? v0 : 0.f;
-            s_aedT[(j + 1) * LDA + i] = (j + 1 < i) ? v1 : 0.f;
+            f_aedT[j * LDA + i] = (j < i) ? v0 : 0.f;
+            f_aedT[(j + 1) * LDA + i] = (j + 1 < i) ? v1 : 0.f;
         });
     }
     __syncthreads();
@@ -129,18 +179,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) 
         float acc[8][4];
         acc_zero<8>(acc);
         const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
-        warp_mma<8>(acc, r0, n0, r0, CL, [&](int j, int k) { return s_aqd[k * LDA + j]; },
-                    [&](int k, int n) { return s_dy[k * LDP + n]; });
+        warp_mma_bf16<8, true, false>(acc, b_aqd, LDM, b_dy, LDB, r0, n0, r0, CL);
         __syncthreads();
         warp_epi<8>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
-            *reinterpret_cast<float2*>(s_dy + i * LDP + j) = make_float2(v0, v1);
+            *reinterpret_cast<__nv_bfloat162*>(b_dy + i * LDB + j) = __floats2bfloat162_rn(v0, v1);
         });
     }
     __syncthreads();
-    trisolve<true>(s_aedT, -1.f, s_dy, s_dt);
+    trisolve_upper_b(f_aedT, -1.f, b_dy, b_dt);
     __syncthreads();
-    s2g_panel(panel_ptr(p.Pp, ch.gi), s_dy);
-    s2g_panel(panel_ptr(p.Qp, ch.gi), s_dt);
+    s2g_bpanel(bpanel_ptr(p.Pp, ch.gi), b_dy);
+    s2g_bpanel(bpanel_ptr(p.Qp, ch.gi), b_dt);
 }
 
 // ---------------------------------------------------------------------------
@@ -149,109 +198,95 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) 
 //   A2 = dR S^T + stril(dR Z~^T) Dneg       (-> d e)
 //   PY = tril(dy Z~^T)^T Xg + stril(dR Z~^T)^T ag
 //   dDt = Z~ dS_end^T ,  SdS[c] = sum_v S[c][v] dS_end[c][v]
-constexpr size_t EXT_PAIR_BWD_SMEM = 4 * SLOT_BYTES + 2 * MAT_BYTES;
+// Every operand is resident; the BF16 ones stream in with cp.async while the
+// FP32 panels kept by forward are converted.
+constexpr size_t EXT_PAIR_BWD_SMEM = 6 * BSLOT_BYTES + 2 * BSTATE_BYTES + 2 * BMAT_BYTES;
 
 __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) {
-    extern __shared__ __align__(16) float smem[];
-    float* s0 = smem;
-    float* s1 = s0 + SLOT_FLOATS;
-    float* s2 = s1 + SLOT_FLOATS;
-    float* s3 = s2 + SLOT_FLOATS;
-    float* s_daqd = s3 + SLOT_FLOATS;
-    float* s_daed = s_daqd + MAT_FLOATS;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* b_dy = reinterpret_cast<bf16*>(smem_raw);
+    bf16* b_zt = b_dy + BSLOT_ELEMS;
+    bf16* b_dr = b_zt + BSLOT_ELEMS;
+    bf16* b_dn = b_dr + BSLOT_ELEMS;
+    bf16* b_xg = b_dn + BSLOT_ELEMS;
+    bf16* b_ag = b_xg + BSLOT_ELEMS;
+    bf16* b_S = b_ag + BSLOT_ELEMS;
+    bf16* b_dS = b_S + DP * LDB;
+    bf16* b_daqd = b_dS + DP * LDB;
+    bf16* b_daed = b_daqd + BMAT_ELEMS;
     const Chunk ch = chunk_of(p.g, blockIdx.x);
 
-    g2s_panel(s0, panel_ptr(p.Dyf, ch.gi));
-    g2s_panel(s1, panel_ptr(p.Zt, ch.gi));
-    g2s_panel(s2, panel_ptr(p.dR, ch.gi));
+    async_bpanel(b_dy, bpanel_ptr(p.Dyf, ch.gi));
+    async_bpanel(b_dr, bpanel_ptr(p.dR, ch.gi));
+    cp_commit();
+    async_bpanel(b_dn, bpanel_ptr(p.Dneg, ch.gi));
+    cp_commit();
+    async_bpanel(b_xg, bpanel_ptr(p.Xg, ch.gi));
+    async_bpanel(b_ag, bpanel_ptr(p.Ag, ch.gi));
+    cp_commit();
+    async_bstate(b_dS, bstate_ptr(p.dSeCk, ch.gi));
+    cp_commit();
+    g2s_panel_f32_to_bf16(b_zt, panel_ptr(p.Zt, ch.gi));
+    g2s_state_f32_to_bf16(b_S, state_ptr(p.SCk, ch.gi));
+    cp_wait<3>();
     __syncthreads();
     {
         float a1[4][4], a2[4][4];
         acc_zero<4>(a1);
         acc_zero<4>(a2);
         const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
-        auto fb = [&](int k, int n) { return s1[n * LDP + k]; };
-        warp_mma<4>(a1, r0, n0, 0, DP, [&](int i, int k) { return s0[i * LDP + k]; }, fb);
-        warp_mma<4>(a2, r0, n0, 0, DP, [&](int i, int k) { return s2[i * LDP + k]; }, fb);
+        warp_mma_bf16<4, false, true>(a1, b_dy, LDB, b_zt, LDB, r0, n0, 0, DP);
+        warp_mma_bf16<4, false, true>(a2, b_dr, LDB, b_zt, LDB, r0, n0, 0, DP);
         warp_epi<4>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
-            s_daqd[i * LDA + j] = (j <= i) ? v0 : 0.f;
-            s_daqd[i * LDA + j + 1] = (j + 1 <= i) ? v1 : 0.f;
+            *reinterpret_cast<__nv_bfloat162*>(b_daqd + i * LDM + j) =
+                __floats2bfloat162_rn((j <= i) ? v0 : 0.f, (j + 1 <= i) ? v1 : 0.f);
         });
         warp_epi<4>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
-            s_daed[i * LDA + j] = (j < i) ? v0 : 0.f;
-            s_daed[i * LDA + j + 1] = (j + 1 < i) ? v1 : 0.f;
+            *reinterpret_cast<__nv_bfloat162*>(b_daed + i * LDM + j) =
+                __floats2bfloat162_rn((j < i) ? v0 : 0.f, (j + 1 < i) ? v1 : 0.f);
         });
     }
+    cp_wait<2>();
     __syncthreads();
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
-    g2s_panel(s1, panel_ptr(p.Dneg, ch.gi));
     {
         float a1[8][4], a2[8][4];
         acc_zero<8>(a1);
         acc_zero<8>(a2);
-        const float* sc = state_ptr(p.SCk, ch.gi);
-        for (int half = 0; half < 2; ++half) {
-            g2s_state_cols(s3, sc, half);
-            __syncthreads();
-            auto fb = [&](int k, int n) { return s3[n * LDH + k]; };
-            warp_mma<8>(a1, r0, n0, 0, CL, [&](int i, int k) { return s0[i * LDP + half * CL + k]; }, fb);
-            warp_mma<8>(a2, r0, n0, 0, CL, [&](int i, int k) { return s2[i * LDP + half * CL + k]; }, fb);
-            __syncthreads();
-        }
-        auto fbd = [&](int k, int n) { return s1[k * LDP + n]; };
-        warp_mma<8>(a1, r0, n0, 0, r0 + 16, [&](int i, int k) { return s_daqd[i * LDA + k]; }, fbd);
-        warp_mma<8>(a2, r0, n0, 0, r0 + 16, [&](int i, int k) { return s_daed[i * LDA + k]; }, fbd);
-        float* gA1 = panel_ptr(p.A1, ch.gi);
-        float* gA2 = panel_ptr(p.A2, ch.gi);
-        warp_epi<8>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
-            *reinterpret_cast<float2*>(gA1 + i * DP + j) = make_float2(v0, v1);
-        });
-        warp_epi<8>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
-            *reinterpret_cast<float2*>(gA2 + i * DP + j) = make_float2(v0, v1);
-        });
+        warp_mma_bf16<8, false, true>(a1, b_dy, LDB, b_S, LDB, r0, n0, 0, DP);
+        warp_mma_bf16<8, false, true>(a2, b_dr, LDB, b_S, LDB, r0, n0, 0, DP);
+        warp_mma_bf16<8, false, false>(a1, b_daqd, LDM, b_dn, LDB, r0, n0, 0, r0 + 16);
+        warp_mma_bf16<8, false, false>(a2, b_daed, LDM, b_dn, LDB, r0, n0, 0, r0 + 16);
+        epi_store_bpanel<8>(a1, r0, n0, bpanel_ptr(p.A1, ch.gi));
+        epi_store_bpanel<8>(a2, r0, n0, bpanel_ptr(p.A2, ch.gi));
     }
-    __syncthreads();
-    g2s_panel(s0, panel_ptr(p.Xg, ch.gi));
-    g2s_panel(s2, panel_ptr(p.Ag, ch.gi));
-    g2s_panel(s1, panel_ptr(p.Zt, ch.gi));
+    cp_wait<1>();
     __syncthreads();
     {
         float acc[8][4];
         acc_zero<8>(acc);
-        warp_mma<8>(acc, r0, n0, r0, CL, [&](int j, int k) { return s_daqd[k * LDA + j]; },
-                    [&](int k, int n) { return s0[k * LDP + n]; });
-        warp_mma<8>(acc, r0, n0, r0, CL, [&](int j, int k) { return s_daed[k * LDA + j]; },
-                    [&](int k, int n) { return s2[k * LDP + n]; });
-        float* gPY = panel_ptr(p.PY, ch.gi);
-        warp_epi<8>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
-            *reinterpret_cast<float2*>(gPY + i * DP + j) = make_float2(v0, v1);
-        });
+        warp_mma_bf16<8, true, false>(acc, b_daqd, LDM, b_xg, LDB, r0, n0, r0, CL);
+        warp_mma_bf16<8, true, false>(acc, b_daed, LDM, b_ag, LDB, r0, n0, r0, CL);
+        epi_store_bpanel<8>(acc, r0, n0, bpanel_ptr(p.PY, ch.gi));
     }
+    cp_wait<0>();
+    __syncthreads();
     {
         float acc[8][4];
         acc_zero<8>(acc);
-        const float* ds = state_ptr(p.dSeCk, ch.gi);
-        for (int half = 0; half < 2; ++half) {
-            g2s_state_cols(s3, ds, half);
-            __syncthreads();
-            warp_mma<8>(acc, r0, n0, 0, CL, [&](int i, int k) { return s1[i * LDP + half * CL + k]; },
-                        [&](int k, int n) { return s3[n * LDH + k]; });
-            __syncthreads();
-        }
-        float* gdDt = panel_ptr(p.dDt, ch.gi);
-        warp_epi<8>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
-            *reinterpret_cast<float2*>(gdDt + i * DP + j) = make_float2(v0, v1);
-        });
+        warp_mma_bf16<8, false, true>(acc, b_zt, LDB, b_dS, LDB, r0, n0, 0, DP);
+        epi_store_bpanel<8>(acc, r0, n0, bpanel_ptr(p.dDt, ch.gi));
     }
     {
-        const float* sc = state_ptr(p.SCk, ch.gi);
-        const float* ds = state_ptr(p.dSeCk, ch.gi);
         const int c = threadIdx.x >> 1, hf = threadIdx.x & 1;
         float acc = 0.f;
-        for (int v4 = 0; v4 < CL; v4 += 4) {
-            float4 a = *reinterpret_cast<const float4*>(sc + c * DP + hf * CL + v4);
-            float4 b = *reinterpret_cast<const float4*>(ds + c * DP + hf * CL + v4);
-            acc += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+#pragma unroll
+        for (int v8 = 0; v8 < CL; v8 += 8) {
+            float a[8], b[8];
+            load8_bsm(b_S, c, hf * CL + v8, a);
+            load8_bsm(b_dS, c, hf * CL + v8, b);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc = fmaf(a[e], b[e], acc);
         }
         acc += __shfl_xor_sync(0xffffffffu, acc, 1);
         if (hf == 0) p.SdS[ch.gi * DP + c] = acc;
@@ -262,27 +297,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
 // Per-token reverse of the sources and of the gate factors of the exterior.
 // Writes the final gradients of q, values, erase_raw, write_raw and the
 // partial cotangents the predictor reverse still has to complete.
-constexpr size_t SOURCES_BWD_SMEM = 1 * SLOT_BYTES;
-
-__global__ void __launch_bounds__(NTHREADS, 1) k_sources_bwd(BwdParams p) {
-    extern __shared__ __align__(16) float smem[];
-    float* s_G = smem;
+__global__ void __launch_bounds__(NTHREADS, 2) k_sources_bwd(BwdParams p) {
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r, V = p.g.V;
-    load_f32_panel(p.ld, ch, r, s_G);
-    __syncthreads();
-    chunk_cumsum(s_G);
-    __syncthreads();
     const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
     const float* gDelta = panel_ptr(p.Delta, ch.gi);
     const float* gd = panel_ptr(p.Dprim, ch.gi);
-    const float* gA1 = panel_ptr(p.A1, ch.gi);
-    const float* gA2 = panel_ptr(p.A2, ch.gi);
-    const float* gPY = panel_ptr(p.PY, ch.gi);
-    const float* gdDt = panel_ptr(p.dDt, ch.gi);
-    const float* gdR = panel_ptr(p.dR, ch.gi);
+    const float* gG = panel_ptr(p.Gp, ch.gi);
+    const bf16* gA1 = bpanel_ptr(p.A1, ch.gi);
+    const bf16* gA2 = bpanel_ptr(p.A2, ch.gi);
+    const bf16* gPY = bpanel_ptr(p.PY, ch.gi);
+    const bf16* gdDt = bpanel_ptr(p.dDt, ch.gi);
+    const bf16* gdR = bpanel_ptr(p.dR, ch.gi);
     float GL[8];
-    load8_smem(s_G, CL - 1, c0, GL);
+    load8_panel(gG, CL - 1, c0, GL);
 #pragma unroll 1
     for (int pp = 0; pp < CL / 16; ++pp) {
         const int i = lr + 16 * pp;
@@ -292,17 +320,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_sources_bwd(BwdParams p) {
         const float rstd_q = load8_norm(p.q, ch, i, c0, r, qh);
         load8_panel(gDelta, i, c0, dl);
         load8_panel(gd, i, c0, d);
+        load8_panel(gG, i, c0, G);
         load8_bf16(row_bf16(p.er, ch, i), c0, r, p.er.vec, i < ch.nvalid, er);
-        load8_smem(s_G, i, c0, G);
 #pragma unroll
         for (int e = 0; e < 8; ++e) se[e] = sigmoidf_(er[e]);
         Sources src;
         sources_fwd(uh, kh, qh, dl, se, src);
         float a1[8], a2[8], py[8], ddt[8];
-        load8_panel(gA1, i, c0, a1);
-        load8_panel(gA2, i, c0, a2);
-        load8_panel(gPY, i, c0, py);
-        load8_panel(gdDt, i, c0, ddt);
+        load8_bpanel(gA1, i, c0, a1);
+        load8_bpanel(gA2, i, c0, a2);
+        load8_bpanel(gPY, i, c0, py);
+        load8_bpanel(gdDt, i, c0, ddt);
         float dchi[8], de[8], dd[8], dG[8], xext[8], dg_[8];
         float dsb = 0.f, dsq = 0.f;
 #pragma unroll
@@ -349,13 +377,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_sources_bwd(BwdParams p) {
         store8_panel(panel_ptr(p.dkPart, ch.gi), i, c0, dkp);
         store8_panel(panel_ptr(p.dGPart, ch.gi), i, c0, dG);
         store8_panel(panel_ptr(p.dDelta, ch.gi), i, c0, ddl);
-        store8_panel(panel_ptr(p.DG, ch.gi), i, c0, dg_);
+        store8_bpanel(bpanel_ptr(p.DG, ch.gi), i, c0, dg_);
         store8_panel(panel_ptr(p.Xext, ch.gi), i, c0, xext);
         // value side: dv = sigmoid(write) dR, d write_raw = dR v sigmoid'(write)
         float wr[8], v[8], dr[8], dv[8], dwr[8];
         load8_bf16(row_bf16(p.wr, ch, i), c0, V, p.wr.vec, i < ch.nvalid, wr);
         load8_bf16(row_bf16(p.v, ch, i), c0, V, p.v.vec, i < ch.nvalid, v);
-        load8_panel(gdR, i, c0, dr);
+        load8_bpanel(gdR, i, c0, dr);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             float sw = sigmoidf_(wr[e]);
@@ -368,170 +396,186 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_sources_bwd(BwdParams p) {
 }
 
 // ---------------------------------------------------------------------------
-// Reverse of the primal address d = k^ + C_t^T k^:
+// Reverse of the primal address d = k^ + C_t^T k^, and preparation of the dC
+// scan:
 //   dk^ = dkPart + DG Ct + tril(DG Uneg^T) Delta        -> final dkeys
-//   dDelta += tril(DG Uneg^T)^T K^
+//   dDelta_loc = dDelta_src + tril(DG Uneg^T)^T K^
 //   Tpre = tril(K^ Delta^T)^T DG                         (-> d u^ after exp(-G))
-constexpr size_t PRIMAL_BWD_SMEM = 5 * SLOT_BYTES + 2 * MAT_BYTES + CL * sizeof(float);
+//   P'' = (I+Lm)^-T dDelta_loc,  Q'' = (I+Lm)^-T Ubar,  Rneg = -gamma U~.
+constexpr size_t PRIMAL_BWD_SMEM =
+    6 * BSLOT_BYTES + BSTATE_BYTES + 2 * BMAT_BYTES + MAT_BYTES + (2 * CL + 2 * CL) * sizeof(float);
 
 __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
-    extern __shared__ __align__(16) float smem[];
-    float* s_un = smem;
-    float* s_kh = s_un + SLOT_FLOATS;
-    float* s_dl = s_kh + SLOT_FLOATS;
-    float* s_dg = s_dl + SLOT_FLOATS;
-    float* s_st = s_dg + SLOT_FLOATS;
-    float* s_aqk = s_st + SLOT_FLOATS;
-    float* s_daqk = s_aqk + MAT_FLOATS;
-    float* s_rk = s_daqk + MAT_FLOATS;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* b_un = reinterpret_cast<bf16*>(smem_raw);
+    bf16* b_ut = b_un + BSLOT_ELEMS;
+    bf16* b_ub = b_ut + BSLOT_ELEMS;   // Ubar, then Q''
+    bf16* b_kh = b_ub + BSLOT_ELEMS;
+    bf16* b_dl = b_kh + BSLOT_ELEMS;   // Delta, then dDelta_loc / P''
+    bf16* b_dg = b_dl + BSLOT_ELEMS;
+    bf16* b_Ct = b_dg + BSLOT_ELEMS;
+    bf16* b_aqk = b_Ct + DP * LDB;
+    bf16* b_daqk = b_aqk + BMAT_ELEMS;
+    float* f_lmT = reinterpret_cast<float*>(b_daqk + BMAT_ELEMS);
+    float* s_rk = f_lmT + MAT_FLOATS;   // 1/|k| per row
+    float* s_gam = s_rk + CL;
+    float* s_dot = s_gam + CL;          // [CL][2] partial dots of the norm VJP
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r;
 
-    load_norm_panel(p.u, ch, r, s_un, nullptr);
-    load_f32_panel(p.ld, ch, r, s_kh);  // G, temporarily
-    __syncthreads();
-    chunk_cumsum(s_kh);
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < CL * DP; idx += NTHREADS) {
-        int i = idx >> 7, c = idx & (DP - 1);
-        s_un[i * LDP + c] *= clamp_exp_neg(s_kh[i * LDP + c]);
+    async_bpanel(b_dg, bpanel_ptr(p.DG, ch.gi));
+    cp_commit();
+    load_gamma(p.gam, ch, s_gam);
+    {
+        const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
+        const float* gG = panel_ptr(p.Gp, ch.gi);
+        const float* gDelta = panel_ptr(p.Delta, ch.gi);
+        bf16* gKhat = bpanel_ptr(p.Khat, ch.gi);
+        bf16* gR = bpanel_ptr(p.Rneg, ch.gi);
+        float GL[8];
+        load8_panel(gG, CL - 1, c0, GL);
+#pragma unroll 1
+        for (int pp = 0; pp < CL / 16; ++pp) {
+            const int i = lr + 16 * pp;
+            float uh[8], kh[8], G[8], E[8], dl[8];
+            load8_norm(p.u, ch, i, c0, r, uh);
+            const float rk = load8_norm(p.k, ch, i, c0, r, kh);
+            load8_panel(gG, i, c0, G);
+            if (i > 0) {
+                load8_panel(gG, i - 1, c0, E);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) E[e] = 0.f;
+            }
+            load8_panel(gDelta, i, c0, dl);
+            const float gm = (i < ch.nvalid) ? *row_f32(p.gam, ch, i) : 0.f;
+            float un[8], ut[8], ub[8], rn[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                un[e] = uh[e] * clamp_exp_neg(G[e]);
+                ut[e] = uh[e] * __expf(E[e]);
+                ub[e] = uh[e] * __expf(GL[e] - G[e]);
+                rn[e] = -gm * ut[e];
+            }
+            store8_bsm(b_un, i, c0, un);
+            store8_bsm(b_ut, i, c0, ut);
+            store8_bsm(b_ub, i, c0, ub);
+            store8_bsm(b_kh, i, c0, kh);
+            store8_bsm(b_dl, i, c0, dl);
+            store8_bpanel(gKhat, i, c0, kh);
+            store8_bpanel(gR, i, c0, rn);
+            if ((threadIdx.x & 15) == 0) s_rk[i] = rk;
+        }
     }
-    __syncthreads();
-    load_norm_panel(p.k, ch, r, s_kh, s_rk);
-    g2s_panel(s_dl, panel_ptr(p.Delta, ch.gi));
-    g2s_panel(s_dg, panel_ptr(p.DG, ch.gi));
+    g2s_state_f32_to_bf16(b_Ct, state_ptr(p.CtCk, ch.gi));
+    cp_wait<0>();
     __syncthreads();
     {
-        float a1[4][4], a2[4][4];
+        float a1[4][4], a2[4][4], a3[4][4];
         acc_zero<4>(a1);
         acc_zero<4>(a2);
+        acc_zero<4>(a3);
         const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
-        warp_mma<4>(a1, r0, n0, 0, DP, [&](int i, int k) { return s_kh[i * LDP + k]; },
-                    [&](int k, int n) { return s_dl[n * LDP + k]; });
-        warp_mma<4>(a2, r0, n0, 0, DP, [&](int i, int k) { return s_dg[i * LDP + k]; },
-                    [&](int k, int n) { return s_un[n * LDP + k]; });
+        warp_mma_bf16<4, false, true>(a1, b_kh, LDB, b_dl, LDB, r0, n0, 0, DP);
+        warp_mma_bf16<4, false, true>(a2, b_dg, LDB, b_un, LDB, r0, n0, 0, DP);
+        warp_mma_bf16<4, false, true>(a3, b_ut, LDB, b_un, LDB, r0, n0, 0, DP);
         warp_epi<4>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
-            s_aqk[i * LDA + j] = (j <= i) ? v0 : 0.f;
-            s_aqk[i * LDA + j + 1] = (j + 1 <= i) ? v1 : 0.f;
+            *reinterpret_cast<__nv_bfloat162*>(b_aqk + i * LDM + j) =
+                __floats2bfloat162_rn((j <= i) ? v0 : 0.f, (j + 1 <= i) ? v1 : 0.f);
         });
         warp_epi<4>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
-            s_daqk[i * LDA + j] = (j <= i) ? v0 : 0.f;
-            s_daqk[i * LDA + j + 1] = (j + 1 <= i) ? v1 : 0.f;
+            *reinterpret_cast<__nv_bfloat162*>(b_daqk + i * LDM + j) =
+                __floats2bfloat162_rn((j <= i) ? v0 : 0.f, (j + 1 <= i) ? v1 : 0.f);
+        });
+        warp_epi<4>(a3, r0, n0, [&](int i, int j, float v0, float v1) {
+            float gm = s_gam[i];
+            f_lmT[j * LDA + i] = (j < i) ? gm * v0 : 0.f;
+            f_lmT[(j + 1) * LDA + i] = (j + 1 < i) ? gm * v1 : 0.f;
         });
     }
     __syncthreads();
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
+    float accd[8][4];  // dAqk^T K^  (added to dDelta_src below)
+    acc_zero<8>(accd);
+    warp_mma_bf16<8, true, false>(accd, b_daqk, LDM, b_kh, LDB, r0, n0, r0, CL);
     {
         float acc[8][4];
         acc_zero<8>(acc);
-        warp_mma<8>(acc, r0, n0, r0, CL, [&](int j, int k) { return s_daqk[k * LDA + j]; },
-                    [&](int k, int n) { return s_kh[k * LDP + n]; });
-        float* gdd = panel_ptr(p.dDelta, ch.gi);
-        warp_epi<8>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
-            float2 old = *reinterpret_cast<const float2*>(gdd + i * DP + j);
-            *reinterpret_cast<float2*>(gdd + i * DP + j) = make_float2(old.x + v0, old.y + v1);
-        });
+        warp_mma_bf16<8, true, false>(acc, b_aqk, LDM, b_dg, LDB, r0, n0, r0, CL);
+        epi_store_bpanel<8>(acc, r0, n0, bpanel_ptr(p.Tpre, ch.gi));
     }
     {
+        // dk^ and its norm VJP, in accumulator layout
         float acc[8][4];
         acc_zero<8>(acc);
-        warp_mma<8>(acc, r0, n0, r0, CL, [&](int j, int k) { return s_aqk[k * LDA + j]; },
-                    [&](int k, int n) { return s_dg[k * LDP + n]; });
-        float* gt = panel_ptr(p.Tpre, ch.gi);
-        warp_epi<8>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
-            *reinterpret_cast<float2*>(gt + i * DP + j) = make_float2(v0, v1);
-        });
-    }
-    {
-        float acc[8][4];
-        acc_zero<8>(acc);
-        const float* ct = state_ptr(p.CtCk, ch.gi);
-        for (int half = 0; half < 2; ++half) {
-            g2s_state_rows(s_st, ct, half);
-            __syncthreads();
-            warp_mma<8>(acc, r0, n0, 0, CL, [&](int i, int k) { return s_dg[i * LDP + half * CL + k]; },
-                        [&](int k, int n) { return s_st[k * LDP + n]; });
-            __syncthreads();
-        }
-        warp_mma<8>(acc, r0, n0, 0, r0 + 16, [&](int i, int k) { return s_daqk[i * LDA + k]; },
-                    [&](int k, int n) { return s_dl[k * LDP + n]; });
+        warp_mma_bf16<8, false, false>(acc, b_dg, LDB, b_Ct, LDB, r0, n0, 0, DP);
+        warp_mma_bf16<8, false, false>(acc, b_daqk, LDM, b_dl, LDB, r0, n0, 0, r0 + 16);
+        const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+        const int ia = r0 + g, ib = ia + 8;
         const float* gkp = panel_ptr(p.dkPart, ch.gi);
-        warp_epi<8>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
-            float2 part = *reinterpret_cast<const float2*>(gkp + i * DP + j);
-            *reinterpret_cast<float2*>(s_st + i * LDP + j) = make_float2(part.x + v0, part.y + v1);
-        });
-    }
-    __syncthreads();
-    {
-        const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
-#pragma unroll 1
-        for (int pp = 0; pp < CL / 16; ++pp) {
-            const int i = lr + 16 * pp;
-            float dkh[8], kh[8], dk[8];
-            load8_smem(s_st, i, c0, dkh);
-            load8_smem(s_kh, i, c0, kh);
-            norm_vjp8(dkh, kh, s_rk[i], dk);
-            store8_bf16(p.dk, p.g, ch, i, c0, r, dk);
+        const __nv_bfloat16* ka = row_bf16(p.k, ch, ia);
+        const __nv_bfloat16* kb = row_bf16(p.k, ch, ib);
+        const float rka = s_rk[ia], rkb = s_rk[ib];
+        float kha[8][2], khb[8][2];
+        float dota = 0.f, dotb = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            const int j = n0 + nt * 8 + 2 * t;
+            float2 pa = *reinterpret_cast<const float2*>(gkp + ia * DP + j);
+            float2 pb = *reinterpret_cast<const float2*>(gkp + ib * DP + j);
+            acc[nt][0] += pa.x; acc[nt][1] += pa.y;
+            acc[nt][2] += pb.x; acc[nt][3] += pb.y;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                kha[nt][e] = (ia < ch.nvalid && j + e < r) ? __bfloat162float(ka[j + e]) * rka : 0.f;
+                khb[nt][e] = (ib < ch.nvalid && j + e < r) ? __bfloat162float(kb[j + e]) * rkb : 0.f;
+            }
+            dota = fmaf(acc[nt][0], kha[nt][0], fmaf(acc[nt][1], kha[nt][1], dota));
+            dotb = fmaf(acc[nt][2], khb[nt][0], fmaf(acc[nt][3], khb[nt][1], dotb));
+        }
+        dota += __shfl_xor_sync(0xffffffffu, dota, 1);
+        dota += __shfl_xor_sync(0xffffffffu, dota, 2);
+        dotb += __shfl_xor_sync(0xffffffffu, dotb, 1);
+        dotb += __shfl_xor_sync(0xffffffffu, dotb, 2);
+        const int nh = threadIdx.x >> 7;
+        if (t == 0) {
+            s_dot[ia * 2 + nh] = dota;
+            s_dot[ib * 2 + nh] = dotb;
+        }
+        __syncthreads();
+        dota = s_dot[ia * 2] + s_dot[ia * 2 + 1];
+        dotb = s_dot[ib * 2] + s_dot[ib * 2 + 1];
+        __nv_bfloat16* dk = reinterpret_cast<__nv_bfloat16*>(p.dk);
+        __nv_bfloat16* rowa = dk + (((long long)ch.b * p.g.T + ch.t0 + ia) * p.g.H + ch.hh) * (long long)r;
+        __nv_bfloat16* rowb = dk + (((long long)ch.b * p.g.T + ch.t0 + ib) * p.g.H + ch.hh) * (long long)r;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            const int j = n0 + nt * 8 + 2 * t;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                if (j + e < r) {
+                    if (ia < ch.nvalid)
+                        rowa[j + e] = __float2bfloat16_rn((acc[nt][e] - dota * kha[nt][e]) * rka);
+                    if (ib < ch.nvalid)
+                        rowb[j + e] = __float2bfloat16_rn((acc[nt][2 + e] - dotb * khb[nt][e]) * rkb);
+                }
+            }
         }
     }
-    s2g_panel(panel_ptr(p.Khat, ch.gi), s_kh);
-}
-
-// ---------------------------------------------------------------------------
-// Predictor reverse, preparation of the dC scan:
-//   P'' = (I+Lm)^-T dDelta,  Q'' = (I+Lm)^-T Ubar,  Rneg = -gamma U~.
-constexpr size_t PRED_PREP_BWD_SMEM = 4 * SLOT_BYTES + MAT_BYTES + CL * sizeof(float);
-
-__global__ void __launch_bounds__(NTHREADS, 1) k_predictor_prep_bwd(BwdParams p) {
-    extern __shared__ __align__(16) float smem[];
-    float* s_uh = smem;  // becomes Ubar
-    float* s_G = s_uh + SLOT_FLOATS;  // becomes dDelta
-    float* s_ut = s_G + SLOT_FLOATS;
-    float* s_un = s_ut + SLOT_FLOATS;
-    float* s_lmT = s_un + SLOT_FLOATS;
-    float* s_gam = s_lmT + MAT_FLOATS;
-    const Chunk ch = chunk_of(p.g, blockIdx.x);
-    const int r = p.g.r;
-
-    load_norm_panel(p.u, ch, r, s_uh, nullptr);
-    load_f32_panel(p.ld, ch, r, s_G);
-    load_gamma(p.gam, ch, s_gam);
-    __syncthreads();
-    chunk_cumsum(s_G);
-    __syncthreads();
-    float* gR = panel_ptr(p.Rneg, ch.gi);
-    for (int idx = threadIdx.x; idx < CL * DP; idx += NTHREADS) {
-        int i = idx >> 7, c = idx & (DP - 1);
-        float G = s_G[i * LDP + c];
-        float E = i ? s_G[(i - 1) * LDP + c] : 0.f;
-        float GL = s_G[(CL - 1) * LDP + c];
-        float uh = s_uh[i * LDP + c];
-        float ut = uh * __expf(E);
-        s_ut[i * LDP + c] = ut;
-        s_un[i * LDP + c] = uh * clamp_exp_neg(G);
-        s_uh[i * LDP + c] = uh * __expf(GL - G);
-        gR[i * DP + c] = -s_gam[i] * ut;
-    }
+    // every contraction that reads b_dl (Delta) is done: reuse it for dDelta_loc
     __syncthreads();
     {
-        float acc[4][4];
-        acc_zero<4>(acc);
-        const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
-        warp_mma<4>(acc, r0, n0, 0, DP, [&](int i, int k) { return s_ut[i * LDP + k]; },
-                    [&](int k, int n) { return s_un[n * LDP + k]; });
-        warp_epi<4>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
-            float gm = s_gam[i];
-            s_lmT[j * LDA + i] = (j < i) ? gm * v0 : 0.f;
-            s_lmT[(j + 1) * LDA + i] = (j + 1 < i) ? gm * v1 : 0.f;
+        const float* gdd = panel_ptr(p.dDelta, ch.gi);
+        warp_epi<8>(accd, r0, n0, [&](int i, int j, float v0, float v1) {
+            float2 src = *reinterpret_cast<const float2*>(gdd + i * DP + j);
+            *reinterpret_cast<__nv_bfloat162*>(b_dl + i * LDB + j) = __floats2bfloat162_rn(src.x + v0, src.y + v1);
         });
     }
-    // the cumsum panel is no longer needed: bring in dDelta
-    g2s_panel(s_G, panel_ptr(p.dDelta, ch.gi));
     __syncthreads();
-    trisolve<true>(s_lmT, 1.f, s_G, s_uh);
+    trisolve_upper_b(f_lmT, 1.f, b_dl, b_ub);
     __syncthreads();
-    s2g_panel(panel_ptr(p.Ppp, ch.gi), s_G);
-    s2g_panel(panel_ptr(p.Qpp, ch.gi), s_uh);
+    s2g_bpanel(bpanel_ptr(p.Ppp, ch.gi), b_dl);
+    s2g_bpanel(bpanel_ptr(p.Qpp, ch.gi), b_ub);
 }
 
 // ---------------------------------------------------------------------------
@@ -540,156 +584,152 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_prep_bwd(BwdParams p)
 //   dgamma = rowsum(dRr * (h - U~ Ct - stril(N) Delta)) ,
 //   Ti = dN Uneg ,  Tj = dN^T U~   with dN = -gamma stril(dRr Delta^T),
 //   CdC[c] = sum_a Ct[c][a] dCt_end[c][a].
-constexpr size_t PRED_PAIR_BWD_SMEM = 5 * SLOT_BYTES + 2 * MAT_BYTES + CL * sizeof(float);
+constexpr size_t PRED_PAIR_BWD_SMEM =
+    4 * BSLOT_BYTES + 2 * BSTATE_BYTES + 2 * BMAT_BYTES + (CL + 2 * CL) * sizeof(float);
 
 __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p) {
-    extern __shared__ __align__(16) float smem[];
-    float* s_ut = smem;
-    float* s_un = s_ut + SLOT_FLOATS;
-    float* s_dl = s_un + SLOT_FLOATS;
-    float* s_dr = s_dl + SLOT_FLOATS;
-    float* s_st = s_dr + SLOT_FLOATS;
-    float* s_N = s_st + SLOT_FLOATS;
-    float* s_dN = s_N + MAT_FLOATS;
-    float* s_gam = s_dN + MAT_FLOATS;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* b_ut = reinterpret_cast<bf16*>(smem_raw);
+    bf16* b_un = b_ut + BSLOT_ELEMS;
+    bf16* b_dl = b_un + BSLOT_ELEMS;
+    bf16* b_dr = b_dl + BSLOT_ELEMS;
+    bf16* b_Ct = b_dr + BSLOT_ELEMS;
+    bf16* b_dC = b_Ct + DP * LDB;
+    bf16* b_N = b_dC + DP * LDB;
+    bf16* b_dN = b_N + BMAT_ELEMS;
+    float* s_gam = reinterpret_cast<float*>(b_dN + BMAT_ELEMS);
+    float* s_dot = s_gam + CL;  // [CL][2]
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r;
 
-    load_norm_panel(p.u, ch, r, s_dl, nullptr);  // u^, temporarily
-    load_f32_panel(p.ld, ch, r, s_dr);           // G, temporarily
+    async_bpanel(b_dr, bpanel_ptr(p.dRr, ch.gi));
+    async_bstate(b_dC, bstate_ptr(p.dCeCk, ch.gi));
+    cp_commit();
     load_gamma(p.gam, ch, s_gam);
-    __syncthreads();
-    chunk_cumsum(s_dr);
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < CL * DP; idx += NTHREADS) {
-        int i = idx >> 7, c = idx & (DP - 1);
-        float G = s_dr[i * LDP + c];
-        float E = i ? s_dr[(i - 1) * LDP + c] : 0.f;
-        float uh = s_dl[i * LDP + c];
-        s_ut[i * LDP + c] = uh * __expf(E);
-        s_un[i * LDP + c] = uh * clamp_exp_neg(G);
+    {
+        const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
+        const float* gG = panel_ptr(p.Gp, ch.gi);
+        const float* gDelta = panel_ptr(p.Delta, ch.gi);
+#pragma unroll 1
+        for (int pp = 0; pp < CL / 16; ++pp) {
+            const int i = lr + 16 * pp;
+            float uh[8], G[8], E[8], dl[8];
+            load8_norm(p.u, ch, i, c0, r, uh);
+            load8_panel(gG, i, c0, G);
+            if (i > 0) {
+                load8_panel(gG, i - 1, c0, E);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) E[e] = 0.f;
+            }
+            load8_panel(gDelta, i, c0, dl);
+            float un[8], ut[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                un[e] = uh[e] * clamp_exp_neg(G[e]);
+                ut[e] = uh[e] * __expf(E[e]);
+            }
+            store8_bsm(b_un, i, c0, un);
+            store8_bsm(b_ut, i, c0, ut);
+            store8_bsm(b_dl, i, c0, dl);
+        }
     }
-    __syncthreads();
-    g2s_panel(s_dl, panel_ptr(p.Delta, ch.gi));
-    g2s_panel(s_dr, panel_ptr(p.dRr, ch.gi));
+    g2s_state_f32_to_bf16(b_Ct, state_ptr(p.CtCk, ch.gi));
+    cp_wait<0>();
     __syncthreads();
     {
         float a1[4][4], a2[4][4];
         acc_zero<4>(a1);
         acc_zero<4>(a2);
         const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
-        warp_mma<4>(a1, r0, n0, 0, DP, [&](int i, int k) { return s_ut[i * LDP + k]; },
-                    [&](int k, int n) { return s_un[n * LDP + k]; });
-        warp_mma<4>(a2, r0, n0, 0, DP, [&](int i, int k) { return s_dr[i * LDP + k]; },
-                    [&](int k, int n) { return s_dl[n * LDP + k]; });
+        warp_mma_bf16<4, false, true>(a1, b_ut, LDB, b_un, LDB, r0, n0, 0, DP);
+        warp_mma_bf16<4, false, true>(a2, b_dr, LDB, b_dl, LDB, r0, n0, 0, DP);
         warp_epi<4>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
-            s_N[i * LDA + j] = (j < i) ? v0 : 0.f;
-            s_N[i * LDA + j + 1] = (j + 1 < i) ? v1 : 0.f;
+            *reinterpret_cast<__nv_bfloat162*>(b_N + i * LDM + j) =
+                __floats2bfloat162_rn((j < i) ? v0 : 0.f, (j + 1 < i) ? v1 : 0.f);
         });
         warp_epi<4>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
             float gm = -s_gam[i];
-            s_dN[i * LDA + j] = (j < i) ? gm * v0 : 0.f;
-            s_dN[i * LDA + j + 1] = (j + 1 < i) ? gm * v1 : 0.f;
+            *reinterpret_cast<__nv_bfloat162*>(b_dN + i * LDM + j) =
+                __floats2bfloat162_rn((j < i) ? gm * v0 : 0.f, (j + 1 < i) ? gm * v1 : 0.f);
         });
     }
     __syncthreads();
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
-    const float* ct = state_ptr(p.CtCk, ch.gi);
-    const float* dce = state_ptr(p.dCeCk, ch.gi);
-    {   // dUbar = Delta dCt_end^T (contraction over the target index a)
+    {   // dUbar[j][c] = sum_a Delta[j][a] dCt[c][a]
         float acc[8][4];
         acc_zero<8>(acc);
-        for (int half = 0; half < 2; ++half) {
-            g2s_state_cols(s_st, dce, half);
-            __syncthreads();
-            warp_mma<8>(acc, r0, n0, 0, CL, [&](int i, int k) { return s_dl[i * LDP + half * CL + k]; },
-                        [&](int k, int n) { return s_st[n * LDH + k]; });
-            __syncthreads();
-        }
-        float* gout = panel_ptr(p.dUbar, ch.gi);
-        warp_epi<8>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
-            *reinterpret_cast<float2*>(gout + i * DP + j) = make_float2(v0, v1);
-        });
+        warp_mma_bf16<8, false, true>(acc, b_dl, LDB, b_dC, LDB, r0, n0, 0, DP);
+        epi_store_bpanel<8>(acc, r0, n0, bpanel_ptr(p.dUbar, ch.gi));
     }
-    {   // dUt = -gamma (dRr Ct^T)
+    {   // dUt[i][c] = -gamma_i sum_a dRr[i][a] Ct[c][a]
         float acc[8][4];
         acc_zero<8>(acc);
-        for (int half = 0; half < 2; ++half) {
-            g2s_state_cols(s_st, ct, half);
-            __syncthreads();
-            warp_mma<8>(acc, r0, n0, 0, CL, [&](int i, int k) { return s_dr[i * LDP + half * CL + k]; },
-                        [&](int k, int n) { return s_st[n * LDH + k]; });
-            __syncthreads();
-        }
-        float* gout = panel_ptr(p.dUt, ch.gi);
+        warp_mma_bf16<8, false, true>(acc, b_dr, LDB, b_Ct, LDB, r0, n0, 0, DP);
+        bf16* gout = bpanel_ptr(p.dUt, ch.gi);
         warp_epi<8>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
             float gm = -s_gam[i];
-            *reinterpret_cast<float2*>(gout + i * DP + j) = make_float2(gm * v0, gm * v1);
+            *reinterpret_cast<__nv_bfloat162*>(gout + i * DP + j) = __floats2bfloat162_rn(gm * v0, gm * v1);
         });
     }
     {   // Ti, Tj
         float acc[8][4];
         acc_zero<8>(acc);
-        warp_mma<8>(acc, r0, n0, 0, r0 + 16, [&](int i, int k) { return s_dN[i * LDA + k]; },
-                    [&](int k, int n) { return s_un[k * LDP + n]; });
-        float* gti = panel_ptr(p.Ti, ch.gi);
-        warp_epi<8>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
-            *reinterpret_cast<float2*>(gti + i * DP + j) = make_float2(v0, v1);
-        });
+        warp_mma_bf16<8, false, false>(acc, b_dN, LDM, b_un, LDB, r0, n0, 0, r0 + 16);
+        epi_store_bpanel<8>(acc, r0, n0, bpanel_ptr(p.Ti, ch.gi));
         acc_zero<8>(acc);
-        warp_mma<8>(acc, r0, n0, r0, CL, [&](int j, int k) { return s_dN[k * LDA + j]; },
-                    [&](int k, int n) { return s_ut[k * LDP + n]; });
-        float* gtj = panel_ptr(p.Tj, ch.gi);
-        warp_epi<8>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
-            *reinterpret_cast<float2*>(gtj + i * DP + j) = make_float2(v0, v1);
-        });
+        warp_mma_bf16<8, true, false>(acc, b_dN, LDM, b_ut, LDB, r0, n0, r0, CL);
+        epi_store_bpanel<8>(acc, r0, n0, bpanel_ptr(p.Tj, ch.gi));
     }
-    {   // residual and dgamma
+    {   // residual rows and dgamma_i = sum_a dRr[i][a] (h[i][a] - (U~ Ct)[i][a] - (N Delta)[i][a])
         float acc[8][4];
         acc_zero<8>(acc);
-        for (int half = 0; half < 2; ++half) {
-            g2s_state_rows(s_st, ct, half);
-            __syncthreads();
-            warp_mma<8>(acc, r0, n0, 0, CL, [&](int i, int k) { return s_ut[i * LDP + half * CL + k]; },
-                        [&](int k, int n) { return s_st[k * LDP + n]; });
-            __syncthreads();
-        }
-        warp_mma<8>(acc, r0, n0, 0, r0 + 16, [&](int i, int k) { return s_N[i * LDA + k]; },
-                    [&](int k, int n) { return s_dl[k * LDP + n]; });
-        warp_epi<8>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
-            float h0 = 0.f, h1 = 0.f;
-            if (i < ch.nvalid) {
-                const __nv_bfloat16* hrow = row_bf16(p.h, ch, i);
-                if (j < r) h0 = __bfloat162float(hrow[j]);
-                if (j + 1 < r) h1 = __bfloat162float(hrow[j + 1]);
+        warp_mma_bf16<8, false, false>(acc, b_ut, LDB, b_Ct, LDB, r0, n0, 0, DP);
+        warp_mma_bf16<8, false, false>(acc, b_N, LDM, b_dl, LDB, r0, n0, 0, r0 + 16);
+        const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+        const int ia = r0 + g, ib = ia + 8;
+        const __nv_bfloat16* ha = row_bf16(p.h, ch, ia);
+        const __nv_bfloat16* hb = row_bf16(p.h, ch, ib);
+        float suma = 0.f, sumb = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            const int j = n0 + nt * 8 + 2 * t;
+            __nv_bfloat162 da = *reinterpret_cast<const __nv_bfloat162*>(b_dr + ia * LDB + j);
+            __nv_bfloat162 db = *reinterpret_cast<const __nv_bfloat162*>(b_dr + ib * LDB + j);
+            float2 fa = __bfloat1622float2(da), fb = __bfloat1622float2(db);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                float h_a = (ia < ch.nvalid && j + e < r) ? __bfloat162float(ha[j + e]) : 0.f;
+                float h_b = (ib < ch.nvalid && j + e < r) ? __bfloat162float(hb[j + e]) : 0.f;
+                suma = fmaf(e ? fa.y : fa.x, h_a - acc[nt][e], suma);
+                sumb = fmaf(e ? fb.y : fb.x, h_b - acc[nt][2 + e], sumb);
             }
-            float2 dr = *reinterpret_cast<const float2*>(s_dr + i * LDP + j);
-            *reinterpret_cast<float2*>(s_st + i * LDP + j) = make_float2(dr.x * (h0 - v0), dr.y * (h1 - v1));
-        });
+        }
+        suma += __shfl_xor_sync(0xffffffffu, suma, 1);
+        suma += __shfl_xor_sync(0xffffffffu, suma, 2);
+        sumb += __shfl_xor_sync(0xffffffffu, sumb, 1);
+        sumb += __shfl_xor_sync(0xffffffffu, sumb, 2);
+        const int nh = threadIdx.x >> 7;
+        if (t == 0) {
+            s_dot[ia * 2 + nh] = suma;
+            s_dot[ib * 2 + nh] = sumb;
+        }
     }
     __syncthreads();
-    {
-        const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
-#pragma unroll
-        for (int pp = 0; pp < CL / 16; ++pp) {
-            const int i = lr + 16 * pp;
-            float x[8];
-            load8_smem(s_st, i, c0, x);
-            float sum = 0.f;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) sum += x[e];
-            sum = row_sum16(sum);
-            if ((threadIdx.x & 15) == 0 && i < ch.nvalid)
-                p.dgam[((long long)ch.b * p.g.T + ch.t0 + i) * p.g.H + ch.hh] = sum;
-        }
+    if (threadIdx.x < CL && threadIdx.x < ch.nvalid) {
+        const int i = threadIdx.x;
+        p.dgam[((long long)ch.b * p.g.T + ch.t0 + i) * p.g.H + ch.hh] = s_dot[i * 2] + s_dot[i * 2 + 1];
     }
     {
         const int c = threadIdx.x >> 1, hf = threadIdx.x & 1;
         float acc = 0.f;
-        for (int v4 = 0; v4 < CL; v4 += 4) {
-            float4 a = *reinterpret_cast<const float4*>(ct + c * DP + hf * CL + v4);
-            float4 b = *reinterpret_cast<const float4*>(dce + c * DP + hf * CL + v4);
-            acc += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+#pragma unroll
+        for (int v8 = 0; v8 < CL; v8 += 8) {
+            float a[8], b[8];
+            load8_bsm(b_Ct, c, hf * CL + v8, a);
+            load8_bsm(b_dC, c, hf * CL + v8, b);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc = fmaf(a[e], b[e], acc);
         }
         acc += __shfl_xor_sync(0xffffffffu, acc, 1);
         if (hf == 0) p.CdC[ch.gi * DP + c] = acc;
@@ -700,46 +740,42 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p)
 // Gate closure: assemble d u^, d G, d E, then
 //   d log_decay = -dE + reverse_cumsum(dG), with dG[last] += dGL.
 // Writes the final gradients of u, h and log_decay.
-constexpr size_t GATE_CLOSURE_SMEM = 4 * SLOT_BYTES;
+constexpr size_t GATE_CLOSURE_SMEM = 3 * SLOT_BYTES;
 
-__global__ void __launch_bounds__(NTHREADS, 1) k_gate_closure_bwd(BwdParams p) {
+__global__ void __launch_bounds__(NTHREADS, 2) k_gate_closure_bwd(BwdParams p) {
     extern __shared__ __align__(16) float smem[];
-    float* s_G = smem;
-    float* s_dG = s_G + SLOT_FLOATS;
+    float* s_dG = smem;
     float* s_dE = s_dG + SLOT_FLOATS;
     float* s_X = s_dE + SLOT_FLOATS;
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r;
-    load_f32_panel(p.ld, ch, r, s_G);
-    __syncthreads();
-    chunk_cumsum(s_G);
-    __syncthreads();
+    const float* gG = panel_ptr(p.Gp, ch.gi);
     {
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
         float GL[8];
-        load8_smem(s_G, CL - 1, c0, GL);
+        load8_panel(gG, CL - 1, c0, GL);
 #pragma unroll 1
         for (int pp = 0; pp < CL / 16; ++pp) {
             const int i = lr + 16 * pp;
             float uh[8], G[8], E[8];
             const float rstd_u = load8_norm(p.u, ch, i, c0, r, uh);
-            load8_smem(s_G, i, c0, G);
+            load8_panel(gG, i, c0, G);
             if (i > 0) {
-                load8_smem(s_G, i - 1, c0, E);
+                load8_panel(gG, i - 1, c0, E);
             } else {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) E[e] = 0.f;
             }
             float dup[8], tpre[8], dub[8], dut[8], ti[8], tj[8], dgp[8], xext[8], drr[8];
             load8_panel(panel_ptr(p.duPart, ch.gi), i, c0, dup);
-            load8_panel(panel_ptr(p.Tpre, ch.gi), i, c0, tpre);
-            load8_panel(panel_ptr(p.dUbar, ch.gi), i, c0, dub);
-            load8_panel(panel_ptr(p.dUt, ch.gi), i, c0, dut);
-            load8_panel(panel_ptr(p.Ti, ch.gi), i, c0, ti);
-            load8_panel(panel_ptr(p.Tj, ch.gi), i, c0, tj);
+            load8_bpanel(bpanel_ptr(p.Tpre, ch.gi), i, c0, tpre);
+            load8_bpanel(bpanel_ptr(p.dUbar, ch.gi), i, c0, dub);
+            load8_bpanel(bpanel_ptr(p.dUt, ch.gi), i, c0, dut);
+            load8_bpanel(bpanel_ptr(p.Ti, ch.gi), i, c0, ti);
+            load8_bpanel(bpanel_ptr(p.Tj, ch.gi), i, c0, tj);
             load8_panel(panel_ptr(p.dGPart, ch.gi), i, c0, dgp);
             load8_panel(panel_ptr(p.Xext, ch.gi), i, c0, xext);
-            load8_panel(panel_ptr(p.dRr, ch.gi), i, c0, drr);
+            load8_bpanel(bpanel_ptr(p.dRr, ch.gi), i, c0, drr);
             float duh[8], dE[8], dG[8], X[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
@@ -767,7 +803,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_gate_closure_bwd(BwdParams p) {
         const int c = threadIdx.x;
         float xs = 0.f;
         for (int i = 0; i < CL; ++i) xs += s_X[i * LDP + c];
-        float run = __expf(s_G[(CL - 1) * LDP + c]) * (p.SdS[ch.gi * DP + c] + p.CdC[ch.gi * DP + c]) + xs;
+        float run = __expf(gG[(CL - 1) * DP + c]) * (p.SdS[ch.gi * DP + c] + p.CdC[ch.gi * DP + c]) + xs;
         for (int i = CL - 1; i >= 0; --i) {
             run += s_dG[i * LDP + c];
             if (i < ch.nvalid)

@@ -275,30 +275,30 @@ __device__ __forceinline__ void trisolve(const float* Mr, float sgn, float* P0, 
     if (!UPPER) {
 #pragma unroll
         for (int i = 1; i < CL; ++i) {
-            float acc = 0.f;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;  // independent chains
 #pragma unroll
             for (int k4 = 0; k4 < i; k4 += 4) {
                 float4 m = *reinterpret_cast<const float4*>(Mr + i * LDA + k4);
-                acc = fmaf(m.x, x[k4], acc);
-                acc = fmaf(m.y, x[k4 + 1], acc);
-                acc = fmaf(m.z, x[k4 + 2], acc);
-                acc = fmaf(m.w, x[k4 + 3], acc);
+                a0 = fmaf(m.x, x[k4], a0);
+                a1 = fmaf(m.y, x[k4 + 1], a1);
+                a2 = fmaf(m.z, x[k4 + 2], a2);
+                a3 = fmaf(m.w, x[k4 + 3], a3);
             }
-            x[i] = fmaf(-sgn, acc, x[i]);
+            x[i] = fmaf(-sgn, (a0 + a1) + (a2 + a3), x[i]);
         }
     } else {
 #pragma unroll
         for (int i = CL - 2; i >= 0; --i) {
-            float acc = 0.f;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;  // independent chains
 #pragma unroll
             for (int k4 = ((i + 1) & ~3); k4 < CL; k4 += 4) {
                 float4 m = *reinterpret_cast<const float4*>(Mr + i * LDA + k4);
-                acc = fmaf(m.x, x[k4], acc);
-                acc = fmaf(m.y, x[k4 + 1], acc);
-                acc = fmaf(m.z, x[k4 + 2], acc);
-                acc = fmaf(m.w, x[k4 + 3], acc);
+                a0 = fmaf(m.x, x[k4], a0);
+                a1 = fmaf(m.y, x[k4 + 1], a1);
+                a2 = fmaf(m.z, x[k4 + 2], a2);
+                a3 = fmaf(m.w, x[k4 + 3], a3);
             }
-            x[i] = fmaf(-sgn, acc, x[i]);
+            x[i] = fmaf(-sgn, (a0 + a1) + (a2 + a3), x[i]);
         }
     }
 #pragma unroll

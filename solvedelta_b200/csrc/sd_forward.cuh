@@ -3,6 +3,7 @@
 // Pipeline: k_prep_fwd -> scan(C) -> k_primal_fwd -> k_exterior_prep_fwd
 //           -> scan(S) -> k_output_fwd.
 #pragma once
+#include "sd_bf16.cuh"
 #include "sd_common.cuh"
 
 namespace sd {
@@ -11,9 +12,10 @@ struct FwdParams {
     Geometry g;
     Operand u, h, q, k, v, er, wr, ld, gam;
     // forward scratch
-    float *Upd, *Qc, *Ubar, *Wd, *Ud, *Dt, *Xg, *Aqd;
+    float *Upd, *Qc, *Ubar, *Wd, *Ud, *Dt;
+    bf16 *Xg, *Aqd;  // operands of the output contraction only
     // kept for backward
-    float *Lam, *Delta, *Dprim, *Zt, *CtCk, *SCk;
+    float *Lam, *Gp, *Delta, *Dprim, *Zt, *CtCk, *SCk;
     void* y;
 };
 
@@ -148,6 +150,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
     float* gUpd = panel_ptr(p.Upd, ch.gi);
     float* gQc = panel_ptr(p.Qc, ch.gi);
     float* gUbar = panel_ptr(p.Ubar, ch.gi);
+    float* gG = panel_ptr(p.Gp, ch.gi);
     for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += NTHREADS) {
         int i = idx >> 5, c4 = (idx & 31) << 2;
         float4 up = *reinterpret_cast<const float4*>(s_h + i * LDP + c4);
@@ -156,6 +159,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
         float4 G = *reinterpret_cast<const float4*>(s_G + i * LDP + c4);
         float4 GL = *reinterpret_cast<const float4*>(s_G + (CL - 1) * LDP + c4);
         *reinterpret_cast<float4*>(gUpd + i * DP + c4) = up;
+        *reinterpret_cast<float4*>(gG + i * DP + c4) = G;
         *reinterpret_cast<float4*>(gQc + i * DP + c4) = make_float4(-w.x, -w.y, -w.z, -w.w);
         *reinterpret_cast<float4*>(gUbar + i * DP + c4) =
             make_float4(uh.x * __expf(GL.x - G.x), uh.y * __expf(GL.y - G.y), uh.z * __expf(GL.z - G.z),
@@ -167,7 +171,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
 // ---------------------------------------------------------------------------
 // Primal address d = k^ + C_t^T k^ for every token of the chunk:
 //   d = k^ + exp(G) * ( K^ Ct^T + tril(K^ Delta^T) (U^ exp(-G)) ).
-constexpr size_t PRIMAL_FWD_SMEM = 5 * SLOT_BYTES + MAT_BYTES;
+constexpr size_t PRIMAL_FWD_SMEM = 6 * SLOT_BYTES + MAT_BYTES;
+
+__device__ __forceinline__ void async_panel_f32(float* sm, const float* g) {
+    for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += NTHREADS) {
+        int i = idx >> 5, c4 = (idx & 31) << 2;
+        cp16(sm + i * LDP + c4, g + i * DP + c4);
+    }
+}
+__device__ __forceinline__ void async_state_cols_f32(float* sm, const float* st, int half) {
+    for (int idx = threadIdx.x; idx < DP * (CL / 4); idx += NTHREADS) {
+        int rrow = idx >> 4, c4 = (idx & 15) << 2;
+        cp16(sm + rrow * LDH + c4, st + rrow * DP + half * CL + c4);
+    }
+}
 
 __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
     extern __shared__ __align__(16) float smem[];
@@ -175,17 +192,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
     float* s_un = s_kh + SLOT_FLOATS;
     float* s_G = s_un + SLOT_FLOATS;
     float* s_dl = s_G + SLOT_FLOATS;
-    float* s_st = s_dl + SLOT_FLOATS;
-    float* s_aqk = s_st + SLOT_FLOATS;
+    float* s_st0 = s_dl + SLOT_FLOATS;
+    float* s_st1 = s_st0 + SLOT_FLOATS;
+    float* s_aqk = s_st1 + SLOT_FLOATS;
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r;
+    const float* ct = state_ptr(p.CtCk, ch.gi);
 
+    // everything that is already FP32 in HBM streams in while the BF16 operands are normalised
+    async_panel_f32(s_G, panel_ptr(p.Gp, ch.gi));
+    async_panel_f32(s_dl, panel_ptr(p.Delta, ch.gi));
+    cp_commit();
+    async_state_cols_f32(s_st0, ct, 0);
+    cp_commit();
+    async_state_cols_f32(s_st1, ct, 1);
+    cp_commit();
     load_norm_panel(p.k, ch, r, s_kh, nullptr);
     load_norm_panel(p.u, ch, r, s_un, nullptr);
-    load_f32_panel(p.ld, ch, r, s_G);
-    g2s_panel(s_dl, panel_ptr(p.Delta, ch.gi));
-    __syncthreads();
-    chunk_cumsum(s_G);
+    cp_wait<2>();
     __syncthreads();
     for (int idx = threadIdx.x; idx < CL * DP; idx += NTHREADS) {
         int i = idx >> 7, c = idx & (DP - 1);
@@ -202,20 +226,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
             s_aqk[i * LDA + j + 1] = (j + 1 <= i) ? v1 : 0.f;
         });
     }
+    cp_wait<1>();
     __syncthreads();
     float acc[8][4];
     acc_zero<8>(acc);
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
-    const float* ct = state_ptr(p.CtCk, ch.gi);
-    for (int half = 0; half < 2; ++half) {
-        g2s_state_cols(s_st, ct, half);
-        __syncthreads();
-        warp_mma<8>(acc, r0, n0, 0, CL, [&](int i, int k) { return s_kh[i * LDP + half * CL + k]; },
-                    [&](int k, int n) { return s_st[n * LDH + k]; });
-        __syncthreads();
-    }
+    warp_mma<8>(acc, r0, n0, 0, CL, [&](int i, int k) { return s_kh[i * LDP + k]; },
+                [&](int k, int n) { return s_st0[n * LDH + k]; });
     warp_mma<8>(acc, r0, n0, 0, r0 + 16, [&](int i, int k) { return s_aqk[i * LDA + k]; },
                 [&](int k, int n) { return s_un[k * LDP + n]; });
+    cp_wait<0>();
+    __syncthreads();
+    warp_mma<8>(acc, r0, n0, 0, CL, [&](int i, int k) { return s_kh[i * LDP + CL + k]; },
+                [&](int k, int n) { return s_st1[n * LDH + k]; });
     float* gd = panel_ptr(p.Dprim, ch.gi);
     warp_epi<8>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
         float2 kh = *reinterpret_cast<const float2*>(s_kh + i * LDP + j);
@@ -228,7 +251,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
 // ---------------------------------------------------------------------------
 // Exterior preparation: sources (e, chi, z), the pair matrices Aqd / Aed and
 // the solved panels Wd = (I-Aed)^-1 ag, Ud = (I-Aed)^-1 Z for the S scan.
-constexpr size_t EXT_PREP_FWD_SMEM = 5 * SLOT_BYTES + MAT_BYTES;
+constexpr size_t EXT_PREP_FWD_SMEM = 4 * SLOT_BYTES + MAT_BYTES;
 
 __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) {
     extern __shared__ __align__(16) float smem[];
@@ -236,23 +259,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
     float* s_ag = s_xg + SLOT_FLOATS;
     float* s_dn = s_ag + SLOT_FLOATS;
     float* s_z = s_dn + SLOT_FLOATS;
-    float* s_G = s_z + SLOT_FLOATS;
-    float* s_aed = s_G + SLOT_FLOATS;
+    float* s_aed = s_z + SLOT_FLOATS;
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r, V = p.g.V;
-
-    load_f32_panel(p.ld, ch, r, s_G);
-    __syncthreads();
-    chunk_cumsum(s_G);
-    __syncthreads();
     {
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
         const float* gDelta = panel_ptr(p.Delta, ch.gi);
         const float* gd = panel_ptr(p.Dprim, ch.gi);
         float* gDt = panel_ptr(p.Dt, ch.gi);
-        float* gXg = panel_ptr(p.Xg, ch.gi);
+        bf16* gXg = bpanel_ptr(p.Xg, ch.gi);
+        const float* gG = panel_ptr(p.Gp, ch.gi);
         float GL[8];
-        load8_smem(s_G, CL - 1, c0, GL);
+        load8_panel(gG, CL - 1, c0, GL);
 #pragma unroll 1
         for (int pp = 0; pp < CL / 16; ++pp) {
             const int i = lr + 16 * pp;
@@ -265,7 +283,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
             load8_bf16(row_bf16(p.er, ch, i), c0, r, p.er.vec, i < ch.nvalid, er);
             load8_bf16(row_bf16(p.wr, ch, i), c0, V, p.wr.vec, i < ch.nvalid, wr);
             load8_bf16(row_bf16(p.v, ch, i), c0, V, p.v.vec, i < ch.nvalid, v);
-            load8_smem(s_G, i, c0, G);
+            load8_panel(gG, i, c0, G);
 #pragma unroll
             for (int e = 0; e < 8; ++e) se[e] = sigmoidf_(er[e]);
             Sources src;
@@ -285,7 +303,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
             store8_smem(s_dn, i, c0, dn);
             store8_smem(s_z, i, c0, z);
             store8_panel(gDt, i, c0, dt);
-            store8_panel(gXg, i, c0, xg);
+            store8_bpanel(gXg, i, c0, xg);
         }
     }
     __syncthreads();
@@ -297,10 +315,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
         auto fb = [&](int k, int n) { return s_dn[n * LDP + k]; };
         warp_mma<4>(a1, r0, n0, 0, DP, [&](int i, int k) { return s_xg[i * LDP + k]; }, fb);
         warp_mma<4>(a2, r0, n0, 0, DP, [&](int i, int k) { return s_ag[i * LDP + k]; }, fb);
-        float* gAqd = mat_ptr(p.Aqd, ch.gi);
+        bf16* gAqd = bmat_ptr(p.Aqd, ch.gi);
         warp_epi<4>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
-            *reinterpret_cast<float2*>(gAqd + i * CL + j) =
-                make_float2((j <= i) ? v0 : 0.f, (j + 1 <= i) ? v1 : 0.f);
+            *reinterpret_cast<__nv_bfloat162*>(gAqd + i * CL + j) =
+                __floats2bfloat162_rn((j <= i) ? v0 : 0.f, (j + 1 <= i) ? v1 : 0.f);
         });
         warp_epi<4>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
             s_aed[i * LDA + j] = (j < i) ? v0 : 0.f;
@@ -315,34 +333,30 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
 }
 
 // ---------------------------------------------------------------------------
-// Output rows: y = Xg S_c + tril(Aqd) Z~.
-constexpr size_t OUTPUT_FWD_SMEM = 3 * SLOT_BYTES + MAT_BYTES;
+// Output rows: y = Xg S_c + tril(Aqd) Z~, BF16 operands (the result is BF16).
+constexpr size_t OUTPUT_FWD_SMEM = 2 * BSLOT_BYTES + BSTATE_BYTES + BMAT_BYTES;
 
-__global__ void __launch_bounds__(NTHREADS, 1) k_output_fwd(FwdParams p) {
-    extern __shared__ __align__(16) float smem[];
-    float* s_xg = smem;
-    float* s_st = s_xg + SLOT_FLOATS;
-    float* s_zt = s_st + SLOT_FLOATS;
-    float* s_aqd = s_zt + SLOT_FLOATS;
+__global__ void __launch_bounds__(NTHREADS, 2) k_output_fwd(FwdParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* b_xg = reinterpret_cast<bf16*>(smem_raw);
+    bf16* b_zt = b_xg + BSLOT_ELEMS;
+    bf16* b_S = b_zt + BSLOT_ELEMS;
+    bf16* b_aqd = b_S + DP * LDB;
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int V = p.g.V;
 
-    g2s_panel(s_xg, panel_ptr(p.Xg, ch.gi));
-    g2s_panel(s_zt, panel_ptr(p.Zt, ch.gi));
-    g2s_mat(s_aqd, mat_ptr(p.Aqd, ch.gi));
+    async_bpanel(b_xg, bpanel_ptr(p.Xg, ch.gi));
+    async_bmat(b_aqd, bmat_ptr(p.Aqd, ch.gi));
+    cp_commit();
+    g2s_state_f32_to_bf16(b_S, state_ptr(p.SCk, ch.gi));
+    g2s_panel_f32_to_bf16(b_zt, panel_ptr(p.Zt, ch.gi));
+    cp_wait<0>();
+    __syncthreads();
     float acc[8][4];
     acc_zero<8>(acc);
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
-    const float* sc = state_ptr(p.SCk, ch.gi);
-    for (int half = 0; half < 2; ++half) {
-        g2s_state_rows(s_st, sc, half);
-        __syncthreads();
-        warp_mma<8>(acc, r0, n0, 0, CL, [&](int i, int k) { return s_xg[i * LDP + half * CL + k]; },
-                    [&](int k, int n) { return s_st[k * LDP + n]; });
-        __syncthreads();
-    }
-    warp_mma<8>(acc, r0, n0, 0, r0 + 16, [&](int i, int k) { return s_aqd[i * LDA + k]; },
-                [&](int k, int n) { return s_zt[k * LDP + n]; });
+    warp_mma_bf16<8, false, false>(acc, b_xg, LDB, b_S, LDB, r0, n0, 0, DP);
+    warp_mma_bf16<8, false, false>(acc, b_aqd, LDM, b_zt, LDB, r0, n0, 0, r0 + 16);
     __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y);
     warp_epi<8>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
         if (i >= ch.nvalid || j >= V) return;

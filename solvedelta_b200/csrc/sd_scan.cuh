@@ -117,6 +117,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_state_scan(ScanParams p) {
 
     for (int step = 0; step < p.NC; ++step) {
         const long long gi = chunk_at(step);
+        const float la = p.lam[gi * DP + row_a], lb = p.lam[gi * DP + row_b];
         // publish the state slice: shared copy for the contraction, global checkpoint
         {
             float* ck = state_ptr(p.ck, gi);
@@ -153,8 +154,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_state_scan(ScanParams p) {
         __syncthreads();
         // St = lam St + R^T X (+ R2^T X2) : warp tile 16 state rows x NS columns
         {
-            const float* lam = p.lam + gi * DP;
-            const float la = lam[row_a], lb = lam[row_b];
 #pragma unroll
             for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
                 st[nt][0] *= la;
@@ -173,6 +172,168 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_state_scan(ScanParams p) {
         cp_async_commit();
     }
     cp_async_wait<0>();
+
+    if (p.fin != nullptr) {
+        float* dst = p.fin + (long long)s * p.nrows * p.ncols;
+#pragma unroll
+        for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                int rr = (e < 2) ? row_a : row_b;
+                int cc = col0 + nt * 8 + 2 * t + (e & 1);
+                if (rr < p.nrows && cc < p.ncols) {
+                    if (p.transposed_io)
+                        dst[(long long)cc * p.nrows + rr] = st[nt][e];
+                    else
+                        dst[(long long)rr * p.ncols + cc] = st[nt][e];
+                }
+            }
+        }
+    }
+}
+
+}  // namespace sd
+
+// ---------------------------------------------------------------------------
+// BF16-operand variant of the scan, used by the two reverse scans (gradient
+// tolerances admit BF16 contraction operands; the carried state itself stays
+// FP32 in registers).  Panels P, Q, R, R2, X2 and the outputs X and the state
+// checkpoints are BF16 in global memory.
+#include "sd_bf16.cuh"
+
+namespace sd {
+
+constexpr int LDTB = SCAN_NS + 8;  // pitch of [*][NS] BF16 shared buffers
+
+struct ScanParamsB {
+    const bf16* P;
+    const bf16* Q;
+    const bf16* R;
+    const bf16* R2;   // nullable
+    const bf16* X2;   // nullable
+    const float* lam; // [chunks][DP]
+    bf16* X;          // out [chunks][CL][DP]
+    bf16* ck;         // out [chunks][DP][DP]
+    const float* init;
+    float* fin;
+    int NC, reverse, transposed_io, nrows, ncols;
+};
+
+__device__ __forceinline__ void async_bslice(bf16* sm, const bf16* g, int col0) {
+    for (int idx = threadIdx.x; idx < CL * (SCAN_NS / 8); idx += NTHREADS) {
+        int i = idx / (SCAN_NS / 8), c8 = (idx % (SCAN_NS / 8)) << 3;
+        cp16(sm + i * LDTB + c8, g + i * DP + col0 + c8);
+    }
+}
+
+constexpr size_t SCAN_B_SMEM_BYTES = (size_t(3) * CL * LDB + size_t(3) * CL * LDTB + size_t(DP) * LDTB) * 2;
+
+__global__ void __launch_bounds__(NTHREADS, 1) k_state_scan_b(ScanParamsB p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
+    bf16* sR = sQ + CL * LDB;
+    bf16* sR2 = sR + CL * LDB;
+    bf16* sP = sR2 + CL * LDB;   // [CL][LDTB]
+    bf16* sX = sP + CL * LDTB;
+    bf16* sX2 = sX + CL * LDTB;
+    bf16* sSt = sX2 + CL * LDTB;  // [DP][LDTB]
+
+    const int col0 = blockIdx.x * SCAN_NS;
+    const int s = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const bool has2 = p.R2 != nullptr;
+    const long long base = (long long)s * p.NC;
+
+    float st[SCAN_NS / 8][4];
+    const int row_a = warp * 16 + g, row_b = row_a + 8;
+#pragma unroll
+    for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            int rr = (e < 2) ? row_a : row_b;
+            int cc = col0 + nt * 8 + 2 * t + (e & 1);
+            float v = 0.f;
+            if (p.init != nullptr && rr < p.nrows && cc < p.ncols) {
+                const float* src = p.init + (long long)s * p.nrows * p.ncols;
+                v = p.transposed_io ? src[(long long)cc * p.nrows + rr] : src[(long long)rr * p.ncols + cc];
+            }
+            st[nt][e] = v;
+        }
+    }
+
+    auto chunk_at = [&](int step) { return base + (p.reverse ? (p.NC - 1 - step) : step); };
+    auto issue_a = [&](int step) {
+        long long gi = chunk_at(step);
+        async_bpanel(sQ, bpanel_ptr(p.Q, gi));
+        async_bslice(sP, bpanel_ptr(p.P, gi), col0);
+    };
+    auto issue_b = [&](int step) {
+        long long gi = chunk_at(step);
+        async_bpanel(sR, bpanel_ptr(p.R, gi));
+        if (has2) {
+            async_bpanel(sR2, bpanel_ptr(p.R2, gi));
+            async_bslice(sX2, bpanel_ptr(p.X2, gi), col0);
+        }
+    };
+
+    issue_a(0);
+    cp_commit();
+    issue_b(0);
+    cp_commit();
+
+    for (int step = 0; step < p.NC; ++step) {
+        const long long gi = chunk_at(step);
+        const float* lam = p.lam + gi * DP;
+        const float la = lam[row_a], lb = lam[row_b];
+        {
+            bf16* ck = p.ck + gi * (long long)(DP * DP);
+#pragma unroll
+            for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
+                int cc = nt * 8 + 2 * t;
+                __nv_bfloat162 va = __floats2bfloat162_rn(st[nt][0], st[nt][1]);
+                __nv_bfloat162 vb = __floats2bfloat162_rn(st[nt][2], st[nt][3]);
+                *reinterpret_cast<__nv_bfloat162*>(sSt + row_a * LDTB + cc) = va;
+                *reinterpret_cast<__nv_bfloat162*>(sSt + row_b * LDTB + cc) = vb;
+                *reinterpret_cast<__nv_bfloat162*>(ck + row_a * DP + col0 + cc) = va;
+                *reinterpret_cast<__nv_bfloat162*>(ck + row_b * DP + col0 + cc) = vb;
+            }
+        }
+        cp_wait<1>();
+        __syncthreads();
+        {
+            float acc[4][4];
+            acc_zero<4>(acc);
+            const int r0 = (warp & 3) * 16, n0 = (warp >> 2) * 32;
+            warp_mma_bf16<4, false, false>(acc, sQ, LDB, sSt, LDTB, r0, n0, 0, DP);
+            bf16* xg = bpanel_ptr(p.X, gi);
+            warp_epi<4>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
+                float2 pv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sP + i * LDTB + j));
+                __nv_bfloat162 xv = __floats2bfloat162_rn(pv.x + v0, pv.y + v1);
+                *reinterpret_cast<__nv_bfloat162*>(sX + i * LDTB + j) = xv;
+                *reinterpret_cast<__nv_bfloat162*>(xg + i * DP + col0 + j) = xv;
+            });
+        }
+        __syncthreads();
+        if (step + 1 < p.NC) issue_a(step + 1);
+        cp_commit();
+        cp_wait<1>();
+        __syncthreads();
+        {
+#pragma unroll
+            for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
+                st[nt][0] *= la;
+                st[nt][1] *= la;
+                st[nt][2] *= lb;
+                st[nt][3] *= lb;
+            }
+            warp_mma_bf16<SCAN_NS / 8, true, false>(st, sR, LDB, sX, LDTB, warp * 16, 0, 0, CL);
+            if (has2) warp_mma_bf16<SCAN_NS / 8, true, false>(st, sR2, LDB, sX2, LDTB, warp * 16, 0, 0, CL);
+        }
+        __syncthreads();
+        if (step + 1 < p.NC) issue_b(step + 1);
+        cp_commit();
+    }
+    cp_wait<0>();
 
     if (p.fin != nullptr) {
         float* dst = p.fin + (long long)s * p.nrows * p.ncols;

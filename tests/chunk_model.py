@@ -190,7 +190,7 @@ class Model:
         saved = dict(loc=loc, Upd=Upd, W=W, Delta=Delta, Ct_ck=Ct_ck, d=d, Wd=Wd, Ud=Ud,
                      Zt=Zt, S_ck=S_ck, Xg=ext["Xg"], Aqd=ext["Aqd"], Dt=ext["Dt"])
         # the same quantities under the names the CUDA library gives its panels
-        saved["panels"] = dict(Lam=loc["lam"], Delta=Delta, Dprim=d, Zt=Zt, CtCk=Ct_ck, SCk=S_ck,
+        saved["panels"] = dict(Lam=loc["lam"], G=loc["G"], Delta=Delta, Dprim=d, Zt=Zt, CtCk=Ct_ck, SCk=S_ck,
                                Upd=Upd, Qc=-W, Ubar=loc["Ubar"], Wd=Wd, Ud=Ud, Dt=ext["Dt"],
                                Xg=ext["Xg"], Aqd=ext["Aqd"])
         yo = self._unchunks(y, B, T, H)
@@ -249,7 +249,7 @@ class Model:
         dDelta = s * dphi - (dphi * Delta).sum(-1, keepdim=True) * s / (RHO * RHO + src["n2"]) * Delta
         se, sw = loc["se"], loc["sw"]
         dkh = se * db
-        duPart, dkPart = duh.clone(), dkh + dd
+        duPart, dkPart, dDeltaSrc = duh.clone(), dkh + dd, dDelta.clone()
         dGPart = dG + dd * (d - kh)
         Xext = dDt * ext["Dt"]
         dG = dG - Xext
@@ -321,7 +321,7 @@ class Model:
         panels = dict(Pp=Pp, Qp=Qp, Ag=ext["ag"], Xg=ext["Xg"], Dyf=dyc, Dneg=ext["Dneg"], dR=dR,
                       dSeCk=dSe, A1=PX1 + dXg, A2=PX2 + dag, PY=PY, dDt=dDt,
                       SdS=(S_ck * dSe).sum(-1), duPart=duPart, dkPart=dkPart, dGPart=dGPart,
-                      dDelta=dDelta, DG=DG, Xext=Xext, Tpre=Tpre, Khat=kh, Ppp=Ppp, Qpp=Qpp,
+                      dDelta=dDeltaSrc, DG=DG, Xext=Xext, Tpre=Tpre, Khat=kh, Ppp=Ppp, Qpp=Qpp,
                       Rneg=-gam * loc["Ut"], dRr=dRr, dCeCk=dCe, dUbar=dUbar, dUt=dUt, Ti=Ti,
                       Tj=Tj, CdC=(Ct_ck * dCe).sum(-1))
         return grads, panels

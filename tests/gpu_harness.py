@@ -142,20 +142,16 @@ class RawRun:
         self.grads = g
 
     def panel(self, which, name):
-        """Fetch an intermediate panel as a CPU float tensor [chunks, rows, cols]."""
+        """Fetch an intermediate panel as a CPU float tensor [chunks, rows, cols] and its dtype tag."""
         lib = _lib.load()
         off, nbytes = ctypes.c_size_t(), ctypes.c_size_t()
         _lib.check(lib.sd_panel_info(ctypes.byref(self.shape), which, name.encode(),
                                      ctypes.byref(off), ctypes.byref(nbytes)))
+        kind = lib.sd_panel_kind(ctypes.byref(self.shape), which, name.encode())
         buf = (self.saved, self.fwd_scratch, getattr(self, "bwd_scratch", None))[which]
-        flat = buf[off.value: off.value + nbytes.value].view(torch.float32).cpu()
+        raw = buf[off.value: off.value + nbytes.value]
+        flat = (raw.view(torch.bfloat16) if kind >= 4 else raw.view(torch.float32)).float().cpu()
         L = lib.sd_chunk_tokens()
         chunks = self.shape.B * self.shape.H * ((self.shape.T + L - 1) // L)
-        per = flat.numel() // chunks
-        if per == 128:
-            return flat.view(chunks, 1, 128)
-        if per == L * L:
-            return flat.view(chunks, L, L)
-        if per == 128 * 128:
-            return flat.view(chunks, 128, 128)
-        return flat.view(chunks, L, 128)
+        dims = {0: (L, 128), 1: (L, L), 2: (128, 128), 3: (1, 128), 4: (L, 128), 5: (L, L), 6: (128, 128)}[kind]
+        return flat.view(chunks, *dims), ("bf16" if kind >= 4 else "f32")

@@ -9,7 +9,7 @@ from tests.chunk_model import Model
 from tests.gpu_harness import RawRun, make_inputs, model_inputs
 from tests.helpers import rel_l2
 
-SAVED = ("Lam", "Delta", "Dprim", "Zt", "CtCk", "SCk")
+SAVED = ("Lam", "G", "Delta", "Dprim", "Zt", "CtCk", "SCk")
 FWD = ("Upd", "Qc", "Ubar", "Wd", "Ud", "Dt", "Xg", "Aqd")
 BWD = ("Pp", "Qp", "Ag", "Xg", "Dyf", "Dneg", "dR", "dSeCk", "A1", "A2", "PY", "dDt", "SdS",
        "duPart", "dkPart", "dGPart", "DG", "Xext", "Tpre", "Khat", "dDelta", "Ppp", "Qpp", "Rneg",
@@ -51,11 +51,14 @@ def test_every_panel_matches_chunk_model(B, T, H, r, V):
     report, bad = [], []
     for which, names, ref in ((0, SAVED, saved["panels"]), (1, FWD, saved["panels"]), (2, BWD, bwd_panels)):
         for name in names:
-            err, spill = _compare(run.panel(which, name), ref[name])
-            report.append(f"{('saved', 'fwd', 'bwd')[which]:5s} {name:8s} rel={err:.2e} pad={spill:.1e}")
+            got, dtype = run.panel(which, name)
+            err, spill = _compare(got, ref[name])
+            report.append(f"{('saved', 'fwd', 'bwd')[which]:5s} {name:8s} {dtype:4s} rel={err:.2e} pad={spill:.1e}")
             if name == "Lam":
                 spill = 0.0  # channels beyond r carry exp(0) = 1, not zero
-            if not (err < 5e-3) or not (spill < 1e-6):
+            # FP32 panels come from TF32 contractions, BF16 panels from BF16 ones
+            tol = 1.5e-2 if (dtype == "bf16" or which == 2) else 5e-3
+            if not (err < tol) or not (spill < 1e-6):
                 bad.append(name)
     outs = dict(y=(run.y.float().cpu(), y), C_T=(run.C_T.cpu(), C_T), S_T=(run.S_T.cpu(), S_T))
     for name, (got, want) in outs.items():
