@@ -273,7 +273,7 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
         sp.lam = p.Lam; sp.X = p.Delta; sp.ck = p.CtCk;
         sp.init = a->C0; sp.fin = a->C_T;
         sp.NC = p.g.NC; sp.reverse = 0; sp.transposed_io = 1; sp.nrows = s->r; sp.ncols = s->r;
-        k_state_scan<<<scan_grid, NTHREADS, SCAN_SMEM_BYTES, stream>>>(sp);
+        k_state_scan<<<scan_grid, SCAN_THREADS, SCAN_SMEM_BYTES, stream>>>(sp);
     mark(stream);
     }
     k_primal_fwd<<<chunks, NTHREADS, PRIMAL_FWD_SMEM, stream>>>(p);
@@ -286,7 +286,7 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
         sp.lam = p.Lam; sp.X = p.Zt; sp.ck = p.SCk;
         sp.init = a->S0; sp.fin = a->S_T;
         sp.NC = p.g.NC; sp.reverse = 0; sp.transposed_io = 0; sp.nrows = s->r; sp.ncols = s->V;
-        k_state_scan<<<scan_grid, NTHREADS, SCAN_SMEM_BYTES, stream>>>(sp);
+        k_state_scan<<<scan_grid, SCAN_THREADS, SCAN_SMEM_BYTES, stream>>>(sp);
     mark(stream);
     }
     k_output_fwd<<<chunks, NTHREADS, OUTPUT_FWD_SMEM, stream>>>(p);
@@ -355,7 +355,7 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
         sp.lam = p.Lam; sp.X = p.dR; sp.ck = p.dSeCk;
         sp.init = a->dS_T; sp.fin = a->dS0;
         sp.NC = p.g.NC; sp.reverse = 1; sp.transposed_io = 0; sp.nrows = s->r; sp.ncols = s->V;
-        k_state_scan_b<<<scan_grid, NTHREADS, SCAN_B_SMEM_BYTES, stream>>>(sp);
+        k_state_scan_b<<<scan_grid, SCAN_THREADS, SCAN_B_SMEM_BYTES, stream>>>(sp);
     mark(stream);
     }
     k_exterior_pair_bwd<<<chunks, NTHREADS, EXT_PAIR_BWD_SMEM, stream>>>(p);
@@ -370,7 +370,7 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
         sp.lam = p.Lam; sp.X = p.dRr; sp.ck = p.dCeCk;
         sp.init = a->dC_T; sp.fin = a->dC0;
         sp.NC = p.g.NC; sp.reverse = 1; sp.transposed_io = 1; sp.nrows = s->r; sp.ncols = s->r;
-        k_state_scan_b<<<scan_grid, NTHREADS, SCAN_B_SMEM_BYTES, stream>>>(sp);
+        k_state_scan_b<<<scan_grid, SCAN_THREADS, SCAN_B_SMEM_BYTES, stream>>>(sp);
     mark(stream);
     }
     k_predictor_pair_bwd<<<chunks, NTHREADS, PRED_PAIR_BWD_SMEM, stream>>>(p);

@@ -45,6 +45,7 @@ __device__ __forceinline__ void norm_vjp8(const float (&dxh)[8], const float (&x
 // panels of DP columns, FP32 arithmetic in registers.  Mr[i][k] = M[k][i] for
 // k > i, zero elsewhere (same convention as trisolve<true>).
 __device__ __forceinline__ void trisolve_upper_b(const float* Mr, float sgn, bf16* P0, bf16* P1) {
+    if (threadIdx.x >= 2 * DP) return;  // one thread per right-hand-side column
     bf16* P = (threadIdx.x < DP) ? P0 : P1;
     const int col = threadIdx.x & (DP - 1);
     float x[CL];
@@ -99,7 +100,7 @@ __device__ __forceinline__ void epi_store_bpanel(float (&acc)[NTW][4], int r0, i
 // so that the reverse S scan is dR = P' + Q' dS.
 constexpr size_t EXT_PREP_BWD_SMEM = 5 * BSLOT_BYTES + BMAT_BYTES + MAT_BYTES;
 
-__global__ void __launch_bounds__(NTHREADS, 2) k_exterior_prep_bwd(BwdParams p) {
+__global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* b_xg = reinterpret_cast<bf16*>(smem_raw);
     bf16* b_ag = b_xg + BSLOT_ELEMS;
@@ -122,8 +123,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_exterior_prep_bwd(BwdParams p) 
         float GL[8];
         load8_panel(gG, CL - 1, c0, GL);
 #pragma unroll 1
-        for (int pp = 0; pp < CL / 16; ++pp) {
-            const int i = lr + 16 * pp;
+        for (int pp = 0; pp < ROW_PASSES; ++pp) {
+            const int i = lr + ROWS_PER_PASS * pp;
             float uh[8], kh[8], qh[8], dl[8], d[8], er[8], dy[8], G[8], se[8];
             load8_norm(p.u, ch, i, c0, r, uh);
             load8_norm(p.k, ch, i, c0, r, kh);
@@ -159,29 +160,29 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_exterior_prep_bwd(BwdParams p) 
     }
     __syncthreads();
     {
-        float a1[4][4], a2[4][4];
-        acc_zero<4>(a1);
-        acc_zero<4>(a2);
+        float a1[NT64][4], a2[NT64][4];
+        acc_zero<NT64>(a1);
+        acc_zero<NT64>(a2);
         const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
-        warp_mma_bf16<4, false, true>(a1, b_xg, LDB, b_dn, LDB, r0, n0, 0, DP);
-        warp_mma_bf16<4, false, true>(a2, b_ag, LDB, b_dn, LDB, r0, n0, 0, DP);
-        warp_epi<4>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
+        warp_mma_bf16<NT64, false, true>(a1, b_xg, LDB, b_dn, LDB, r0, n0, 0, DP);
+        warp_mma_bf16<NT64, false, true>(a2, b_ag, LDB, b_dn, LDB, r0, n0, 0, DP);
+        warp_epi<NT64>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
             *reinterpret_cast<__nv_bfloat162*>(b_aqd + i * LDM + j) =
                 __floats2bfloat162_rn((j <= i) ? v0 : 0.f, (j + 1 <= i) ? v1 : 0.f);
         });
-        warp_epi<4>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
+        warp_epi<NT64>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
             f_aedT[j * LDA + i] = (j < i) ? v0 : 0.f;
             f_aedT[(j + 1) * LDA + i] = (j + 1 < i) ? v1 : 0.f;
         });
     }
     __syncthreads();
     {
-        float acc[8][4];
-        acc_zero<8>(acc);
+        float acc[NT128][4];
+        acc_zero<NT128>(acc);
         const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
-        warp_mma_bf16<8, true, false>(acc, b_aqd, LDM, b_dy, LDB, r0, n0, r0, CL);
+        warp_mma_bf16<NT128, true, false>(acc, b_aqd, LDM, b_dy, LDB, r0, n0, r0, CL);
         __syncthreads();
-        warp_epi<8>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
+        warp_epi<NT128>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
             *reinterpret_cast<__nv_bfloat162*>(b_dy + i * LDB + j) = __floats2bfloat162_rn(v0, v1);
         });
     }
@@ -231,17 +232,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
     cp_wait<3>();
     __syncthreads();
     {
-        float a1[4][4], a2[4][4];
-        acc_zero<4>(a1);
-        acc_zero<4>(a2);
+        float a1[NT64][4], a2[NT64][4];
+        acc_zero<NT64>(a1);
+        acc_zero<NT64>(a2);
         const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
-        warp_mma_bf16<4, false, true>(a1, b_dy, LDB, b_zt, LDB, r0, n0, 0, DP);
-        warp_mma_bf16<4, false, true>(a2, b_dr, LDB, b_zt, LDB, r0, n0, 0, DP);
-        warp_epi<4>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
+        warp_mma_bf16<NT64, false, true>(a1, b_dy, LDB, b_zt, LDB, r0, n0, 0, DP);
+        warp_mma_bf16<NT64, false, true>(a2, b_dr, LDB, b_zt, LDB, r0, n0, 0, DP);
+        warp_epi<NT64>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
             *reinterpret_cast<__nv_bfloat162*>(b_daqd + i * LDM + j) =
                 __floats2bfloat162_rn((j <= i) ? v0 : 0.f, (j + 1 <= i) ? v1 : 0.f);
         });
-        warp_epi<4>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
+        warp_epi<NT64>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
             *reinterpret_cast<__nv_bfloat162*>(b_daed + i * LDM + j) =
                 __floats2bfloat162_rn((j < i) ? v0 : 0.f, (j + 1 < i) ? v1 : 0.f);
         });
@@ -250,46 +251,47 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
     __syncthreads();
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
     {
-        float a1[8][4], a2[8][4];
-        acc_zero<8>(a1);
-        acc_zero<8>(a2);
-        warp_mma_bf16<8, false, true>(a1, b_dy, LDB, b_S, LDB, r0, n0, 0, DP);
-        warp_mma_bf16<8, false, true>(a2, b_dr, LDB, b_S, LDB, r0, n0, 0, DP);
-        warp_mma_bf16<8, false, false>(a1, b_daqd, LDM, b_dn, LDB, r0, n0, 0, r0 + 16);
-        warp_mma_bf16<8, false, false>(a2, b_daed, LDM, b_dn, LDB, r0, n0, 0, r0 + 16);
-        epi_store_bpanel<8>(a1, r0, n0, bpanel_ptr(p.A1, ch.gi));
-        epi_store_bpanel<8>(a2, r0, n0, bpanel_ptr(p.A2, ch.gi));
+        float a1[NT128][4], a2[NT128][4];
+        acc_zero<NT128>(a1);
+        acc_zero<NT128>(a2);
+        warp_mma_bf16<NT128, false, true>(a1, b_dy, LDB, b_S, LDB, r0, n0, 0, DP);
+        warp_mma_bf16<NT128, false, true>(a2, b_dr, LDB, b_S, LDB, r0, n0, 0, DP);
+        warp_mma_bf16<NT128, false, false>(a1, b_daqd, LDM, b_dn, LDB, r0, n0, 0, r0 + 16);
+        warp_mma_bf16<NT128, false, false>(a2, b_daed, LDM, b_dn, LDB, r0, n0, 0, r0 + 16);
+        epi_store_bpanel<NT128>(a1, r0, n0, bpanel_ptr(p.A1, ch.gi));
+        epi_store_bpanel<NT128>(a2, r0, n0, bpanel_ptr(p.A2, ch.gi));
     }
     cp_wait<1>();
     __syncthreads();
     {
-        float acc[8][4];
-        acc_zero<8>(acc);
-        warp_mma_bf16<8, true, false>(acc, b_daqd, LDM, b_xg, LDB, r0, n0, r0, CL);
-        warp_mma_bf16<8, true, false>(acc, b_daed, LDM, b_ag, LDB, r0, n0, r0, CL);
-        epi_store_bpanel<8>(acc, r0, n0, bpanel_ptr(p.PY, ch.gi));
+        float acc[NT128][4];
+        acc_zero<NT128>(acc);
+        warp_mma_bf16<NT128, true, false>(acc, b_daqd, LDM, b_xg, LDB, r0, n0, r0, CL);
+        warp_mma_bf16<NT128, true, false>(acc, b_daed, LDM, b_ag, LDB, r0, n0, r0, CL);
+        epi_store_bpanel<NT128>(acc, r0, n0, bpanel_ptr(p.PY, ch.gi));
     }
     cp_wait<0>();
     __syncthreads();
     {
-        float acc[8][4];
-        acc_zero<8>(acc);
-        warp_mma_bf16<8, false, true>(acc, b_zt, LDB, b_dS, LDB, r0, n0, 0, DP);
-        epi_store_bpanel<8>(acc, r0, n0, bpanel_ptr(p.dDt, ch.gi));
+        float acc[NT128][4];
+        acc_zero<NT128>(acc);
+        warp_mma_bf16<NT128, false, true>(acc, b_zt, LDB, b_dS, LDB, r0, n0, 0, DP);
+        epi_store_bpanel<NT128>(acc, r0, n0, bpanel_ptr(p.dDt, ch.gi));
     }
     {
-        const int c = threadIdx.x >> 1, hf = threadIdx.x & 1;
+        const int c = threadIdx.x >> 2, qt = threadIdx.x & 3;  // four lanes per state row
         float acc = 0.f;
 #pragma unroll
-        for (int v8 = 0; v8 < CL; v8 += 8) {
+        for (int v8 = 0; v8 < DP / 4; v8 += 8) {
             float a[8], b[8];
-            load8_bsm(b_S, c, hf * CL + v8, a);
-            load8_bsm(b_dS, c, hf * CL + v8, b);
+            load8_bsm(b_S, c, qt * (DP / 4) + v8, a);
+            load8_bsm(b_dS, c, qt * (DP / 4) + v8, b);
 #pragma unroll
             for (int e = 0; e < 8; ++e) acc = fmaf(a[e], b[e], acc);
         }
         acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-        if (hf == 0) p.SdS[ch.gi * DP + c] = acc;
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        if (qt == 0) p.SdS[ch.gi * DP + c] = acc;
     }
 }
 
@@ -297,7 +299,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
 // Per-token reverse of the sources and of the gate factors of the exterior.
 // Writes the final gradients of q, values, erase_raw, write_raw and the
 // partial cotangents the predictor reverse still has to complete.
-__global__ void __launch_bounds__(NTHREADS, 2) k_sources_bwd(BwdParams p) {
+__global__ void __launch_bounds__(NTHREADS, 1) k_sources_bwd(BwdParams p) {
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r, V = p.g.V;
     const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
@@ -312,8 +314,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_sources_bwd(BwdParams p) {
     float GL[8];
     load8_panel(gG, CL - 1, c0, GL);
 #pragma unroll 1
-    for (int pp = 0; pp < CL / 16; ++pp) {
-        const int i = lr + 16 * pp;
+    for (int pp = 0; pp < ROW_PASSES; ++pp) {
+        const int i = lr + ROWS_PER_PASS * pp;
         float uh[8], kh[8], qh[8], dl[8], d[8], er[8], G[8], se[8];
         load8_norm(p.u, ch, i, c0, r, uh);
         load8_norm(p.k, ch, i, c0, r, kh);
@@ -403,7 +405,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_sources_bwd(BwdParams p) {
 //   Tpre = tril(K^ Delta^T)^T DG                         (-> d u^ after exp(-G))
 //   P'' = (I+Lm)^-T dDelta_loc,  Q'' = (I+Lm)^-T Ubar,  Rneg = -gamma U~.
 constexpr size_t PRIMAL_BWD_SMEM =
-    6 * BSLOT_BYTES + BSTATE_BYTES + 2 * BMAT_BYTES + MAT_BYTES + (2 * CL + 2 * CL) * sizeof(float);
+    6 * BSLOT_BYTES + BSTATE_BYTES + 2 * BMAT_BYTES + MAT_BYTES + (2 * CL + 4 * CL) * sizeof(float);
 
 __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -419,7 +421,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     float* f_lmT = reinterpret_cast<float*>(b_daqk + BMAT_ELEMS);
     float* s_rk = f_lmT + MAT_FLOATS;   // 1/|k| per row
     float* s_gam = s_rk + CL;
-    float* s_dot = s_gam + CL;          // [CL][2] partial dots of the norm VJP
+    float* s_dot = s_gam + CL;          // [CL][4] partial dots of the norm VJP
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r;
 
@@ -435,8 +437,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
         float GL[8];
         load8_panel(gG, CL - 1, c0, GL);
 #pragma unroll 1
-        for (int pp = 0; pp < CL / 16; ++pp) {
-            const int i = lr + 16 * pp;
+        for (int pp = 0; pp < ROW_PASSES; ++pp) {
+            const int i = lr + ROWS_PER_PASS * pp;
             float uh[8], kh[8], G[8], E[8], dl[8];
             load8_norm(p.u, ch, i, c0, r, uh);
             const float rk = load8_norm(p.k, ch, i, c0, r, kh);
@@ -471,23 +473,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     cp_wait<0>();
     __syncthreads();
     {
-        float a1[4][4], a2[4][4], a3[4][4];
-        acc_zero<4>(a1);
-        acc_zero<4>(a2);
-        acc_zero<4>(a3);
+        float a1[NT64][4], a2[NT64][4], a3[NT64][4];
+        acc_zero<NT64>(a1);
+        acc_zero<NT64>(a2);
+        acc_zero<NT64>(a3);
         const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
-        warp_mma_bf16<4, false, true>(a1, b_kh, LDB, b_dl, LDB, r0, n0, 0, DP);
-        warp_mma_bf16<4, false, true>(a2, b_dg, LDB, b_un, LDB, r0, n0, 0, DP);
-        warp_mma_bf16<4, false, true>(a3, b_ut, LDB, b_un, LDB, r0, n0, 0, DP);
-        warp_epi<4>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
+        warp_mma_bf16<NT64, false, true>(a1, b_kh, LDB, b_dl, LDB, r0, n0, 0, DP);
+        warp_mma_bf16<NT64, false, true>(a2, b_dg, LDB, b_un, LDB, r0, n0, 0, DP);
+        warp_mma_bf16<NT64, false, true>(a3, b_ut, LDB, b_un, LDB, r0, n0, 0, DP);
+        warp_epi<NT64>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
             *reinterpret_cast<__nv_bfloat162*>(b_aqk + i * LDM + j) =
                 __floats2bfloat162_rn((j <= i) ? v0 : 0.f, (j + 1 <= i) ? v1 : 0.f);
         });
-        warp_epi<4>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
+        warp_epi<NT64>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
             *reinterpret_cast<__nv_bfloat162*>(b_daqk + i * LDM + j) =
                 __floats2bfloat162_rn((j <= i) ? v0 : 0.f, (j + 1 <= i) ? v1 : 0.f);
         });
-        warp_epi<4>(a3, r0, n0, [&](int i, int j, float v0, float v1) {
+        warp_epi<NT64>(a3, r0, n0, [&](int i, int j, float v0, float v1) {
             float gm = s_gam[i];
             f_lmT[j * LDA + i] = (j < i) ? gm * v0 : 0.f;
             f_lmT[(j + 1) * LDA + i] = (j + 1 < i) ? gm * v1 : 0.f;
@@ -495,31 +497,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     }
     __syncthreads();
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
-    float accd[8][4];  // dAqk^T K^  (added to dDelta_src below)
-    acc_zero<8>(accd);
-    warp_mma_bf16<8, true, false>(accd, b_daqk, LDM, b_kh, LDB, r0, n0, r0, CL);
+    float accd[NT128][4];  // dAqk^T K^  (added to dDelta_src below)
+    acc_zero<NT128>(accd);
+    warp_mma_bf16<NT128, true, false>(accd, b_daqk, LDM, b_kh, LDB, r0, n0, r0, CL);
     {
-        float acc[8][4];
-        acc_zero<8>(acc);
-        warp_mma_bf16<8, true, false>(acc, b_aqk, LDM, b_dg, LDB, r0, n0, r0, CL);
-        epi_store_bpanel<8>(acc, r0, n0, bpanel_ptr(p.Tpre, ch.gi));
+        float acc[NT128][4];
+        acc_zero<NT128>(acc);
+        warp_mma_bf16<NT128, true, false>(acc, b_aqk, LDM, b_dg, LDB, r0, n0, r0, CL);
+        epi_store_bpanel<NT128>(acc, r0, n0, bpanel_ptr(p.Tpre, ch.gi));
     }
     {
         // dk^ and its norm VJP, in accumulator layout
-        float acc[8][4];
-        acc_zero<8>(acc);
-        warp_mma_bf16<8, false, false>(acc, b_dg, LDB, b_Ct, LDB, r0, n0, 0, DP);
-        warp_mma_bf16<8, false, false>(acc, b_daqk, LDM, b_dl, LDB, r0, n0, 0, r0 + 16);
+        float acc[NT128][4];
+        acc_zero<NT128>(acc);
+        warp_mma_bf16<NT128, false, false>(acc, b_dg, LDB, b_Ct, LDB, r0, n0, 0, DP);
+        warp_mma_bf16<NT128, false, false>(acc, b_daqk, LDM, b_dl, LDB, r0, n0, 0, r0 + 16);
         const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
         const int ia = r0 + g, ib = ia + 8;
         const float* gkp = panel_ptr(p.dkPart, ch.gi);
         const __nv_bfloat16* ka = row_bf16(p.k, ch, ia);
         const __nv_bfloat16* kb = row_bf16(p.k, ch, ib);
         const float rka = s_rk[ia], rkb = s_rk[ib];
-        float kha[8][2], khb[8][2];
+        float kha[NT128][2], khb[NT128][2];
         float dota = 0.f, dotb = 0.f;
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
+        for (int nt = 0; nt < NT128; ++nt) {
             const int j = n0 + nt * 8 + 2 * t;
             float2 pa = *reinterpret_cast<const float2*>(gkp + ia * DP + j);
             float2 pb = *reinterpret_cast<const float2*>(gkp + ib * DP + j);
@@ -537,19 +539,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
         dota += __shfl_xor_sync(0xffffffffu, dota, 2);
         dotb += __shfl_xor_sync(0xffffffffu, dotb, 1);
         dotb += __shfl_xor_sync(0xffffffffu, dotb, 2);
-        const int nh = threadIdx.x >> 7;
+        const int nq = threadIdx.x >> 7;  // column quarter of this warp
         if (t == 0) {
-            s_dot[ia * 2 + nh] = dota;
-            s_dot[ib * 2 + nh] = dotb;
+            s_dot[ia * 4 + nq] = dota;
+            s_dot[ib * 4 + nq] = dotb;
         }
         __syncthreads();
-        dota = s_dot[ia * 2] + s_dot[ia * 2 + 1];
-        dotb = s_dot[ib * 2] + s_dot[ib * 2 + 1];
+        dota = (s_dot[ia * 4] + s_dot[ia * 4 + 1]) + (s_dot[ia * 4 + 2] + s_dot[ia * 4 + 3]);
+        dotb = (s_dot[ib * 4] + s_dot[ib * 4 + 1]) + (s_dot[ib * 4 + 2] + s_dot[ib * 4 + 3]);
         __nv_bfloat16* dk = reinterpret_cast<__nv_bfloat16*>(p.dk);
         __nv_bfloat16* rowa = dk + (((long long)ch.b * p.g.T + ch.t0 + ia) * p.g.H + ch.hh) * (long long)r;
         __nv_bfloat16* rowb = dk + (((long long)ch.b * p.g.T + ch.t0 + ib) * p.g.H + ch.hh) * (long long)r;
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
+        for (int nt = 0; nt < NT128; ++nt) {
             const int j = n0 + nt * 8 + 2 * t;
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
@@ -566,7 +568,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     __syncthreads();
     {
         const float* gdd = panel_ptr(p.dDelta, ch.gi);
-        warp_epi<8>(accd, r0, n0, [&](int i, int j, float v0, float v1) {
+        warp_epi<NT128>(accd, r0, n0, [&](int i, int j, float v0, float v1) {
             float2 src = *reinterpret_cast<const float2*>(gdd + i * DP + j);
             *reinterpret_cast<__nv_bfloat162*>(b_dl + i * LDB + j) = __floats2bfloat162_rn(src.x + v0, src.y + v1);
         });
@@ -585,7 +587,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
 //   Ti = dN Uneg ,  Tj = dN^T U~   with dN = -gamma stril(dRr Delta^T),
 //   CdC[c] = sum_a Ct[c][a] dCt_end[c][a].
 constexpr size_t PRED_PAIR_BWD_SMEM =
-    4 * BSLOT_BYTES + 2 * BSTATE_BYTES + 2 * BMAT_BYTES + (CL + 2 * CL) * sizeof(float);
+    4 * BSLOT_BYTES + 2 * BSTATE_BYTES + 2 * BMAT_BYTES + (CL + 4 * CL) * sizeof(float);
 
 __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -598,7 +600,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p)
     bf16* b_N = b_dC + DP * LDB;
     bf16* b_dN = b_N + BMAT_ELEMS;
     float* s_gam = reinterpret_cast<float*>(b_dN + BMAT_ELEMS);
-    float* s_dot = s_gam + CL;  // [CL][2]
+    float* s_dot = s_gam + CL;  // [CL][4]
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r;
 
@@ -611,8 +613,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p)
         const float* gG = panel_ptr(p.Gp, ch.gi);
         const float* gDelta = panel_ptr(p.Delta, ch.gi);
 #pragma unroll 1
-        for (int pp = 0; pp < CL / 16; ++pp) {
-            const int i = lr + 16 * pp;
+        for (int pp = 0; pp < ROW_PASSES; ++pp) {
+            const int i = lr + ROWS_PER_PASS * pp;
             float uh[8], G[8], E[8], dl[8];
             load8_norm(p.u, ch, i, c0, r, uh);
             load8_panel(gG, i, c0, G);
@@ -638,17 +640,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p)
     cp_wait<0>();
     __syncthreads();
     {
-        float a1[4][4], a2[4][4];
-        acc_zero<4>(a1);
-        acc_zero<4>(a2);
+        float a1[NT64][4], a2[NT64][4];
+        acc_zero<NT64>(a1);
+        acc_zero<NT64>(a2);
         const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
-        warp_mma_bf16<4, false, true>(a1, b_ut, LDB, b_un, LDB, r0, n0, 0, DP);
-        warp_mma_bf16<4, false, true>(a2, b_dr, LDB, b_dl, LDB, r0, n0, 0, DP);
-        warp_epi<4>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
+        warp_mma_bf16<NT64, false, true>(a1, b_ut, LDB, b_un, LDB, r0, n0, 0, DP);
+        warp_mma_bf16<NT64, false, true>(a2, b_dr, LDB, b_dl, LDB, r0, n0, 0, DP);
+        warp_epi<NT64>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
             *reinterpret_cast<__nv_bfloat162*>(b_N + i * LDM + j) =
                 __floats2bfloat162_rn((j < i) ? v0 : 0.f, (j + 1 < i) ? v1 : 0.f);
         });
-        warp_epi<4>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
+        warp_epi<NT64>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
             float gm = -s_gam[i];
             *reinterpret_cast<__nv_bfloat162*>(b_dN + i * LDM + j) =
                 __floats2bfloat162_rn((j < i) ? gm * v0 : 0.f, (j + 1 < i) ? gm * v1 : 0.f);
@@ -657,42 +659,42 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p)
     __syncthreads();
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
     {   // dUbar[j][c] = sum_a Delta[j][a] dCt[c][a]
-        float acc[8][4];
-        acc_zero<8>(acc);
-        warp_mma_bf16<8, false, true>(acc, b_dl, LDB, b_dC, LDB, r0, n0, 0, DP);
-        epi_store_bpanel<8>(acc, r0, n0, bpanel_ptr(p.dUbar, ch.gi));
+        float acc[NT128][4];
+        acc_zero<NT128>(acc);
+        warp_mma_bf16<NT128, false, true>(acc, b_dl, LDB, b_dC, LDB, r0, n0, 0, DP);
+        epi_store_bpanel<NT128>(acc, r0, n0, bpanel_ptr(p.dUbar, ch.gi));
     }
     {   // dUt[i][c] = -gamma_i sum_a dRr[i][a] Ct[c][a]
-        float acc[8][4];
-        acc_zero<8>(acc);
-        warp_mma_bf16<8, false, true>(acc, b_dr, LDB, b_Ct, LDB, r0, n0, 0, DP);
+        float acc[NT128][4];
+        acc_zero<NT128>(acc);
+        warp_mma_bf16<NT128, false, true>(acc, b_dr, LDB, b_Ct, LDB, r0, n0, 0, DP);
         bf16* gout = bpanel_ptr(p.dUt, ch.gi);
-        warp_epi<8>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
+        warp_epi<NT128>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
             float gm = -s_gam[i];
             *reinterpret_cast<__nv_bfloat162*>(gout + i * DP + j) = __floats2bfloat162_rn(gm * v0, gm * v1);
         });
     }
     {   // Ti, Tj
-        float acc[8][4];
-        acc_zero<8>(acc);
-        warp_mma_bf16<8, false, false>(acc, b_dN, LDM, b_un, LDB, r0, n0, 0, r0 + 16);
-        epi_store_bpanel<8>(acc, r0, n0, bpanel_ptr(p.Ti, ch.gi));
-        acc_zero<8>(acc);
-        warp_mma_bf16<8, true, false>(acc, b_dN, LDM, b_ut, LDB, r0, n0, r0, CL);
-        epi_store_bpanel<8>(acc, r0, n0, bpanel_ptr(p.Tj, ch.gi));
+        float acc[NT128][4];
+        acc_zero<NT128>(acc);
+        warp_mma_bf16<NT128, false, false>(acc, b_dN, LDM, b_un, LDB, r0, n0, 0, r0 + 16);
+        epi_store_bpanel<NT128>(acc, r0, n0, bpanel_ptr(p.Ti, ch.gi));
+        acc_zero<NT128>(acc);
+        warp_mma_bf16<NT128, true, false>(acc, b_dN, LDM, b_ut, LDB, r0, n0, r0, CL);
+        epi_store_bpanel<NT128>(acc, r0, n0, bpanel_ptr(p.Tj, ch.gi));
     }
     {   // residual rows and dgamma_i = sum_a dRr[i][a] (h[i][a] - (U~ Ct)[i][a] - (N Delta)[i][a])
-        float acc[8][4];
-        acc_zero<8>(acc);
-        warp_mma_bf16<8, false, false>(acc, b_ut, LDB, b_Ct, LDB, r0, n0, 0, DP);
-        warp_mma_bf16<8, false, false>(acc, b_N, LDM, b_dl, LDB, r0, n0, 0, r0 + 16);
+        float acc[NT128][4];
+        acc_zero<NT128>(acc);
+        warp_mma_bf16<NT128, false, false>(acc, b_ut, LDB, b_Ct, LDB, r0, n0, 0, DP);
+        warp_mma_bf16<NT128, false, false>(acc, b_N, LDM, b_dl, LDB, r0, n0, 0, r0 + 16);
         const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
         const int ia = r0 + g, ib = ia + 8;
         const __nv_bfloat16* ha = row_bf16(p.h, ch, ia);
         const __nv_bfloat16* hb = row_bf16(p.h, ch, ib);
         float suma = 0.f, sumb = 0.f;
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
+        for (int nt = 0; nt < NT128; ++nt) {
             const int j = n0 + nt * 8 + 2 * t;
             __nv_bfloat162 da = *reinterpret_cast<const __nv_bfloat162*>(b_dr + ia * LDB + j);
             __nv_bfloat162 db = *reinterpret_cast<const __nv_bfloat162*>(b_dr + ib * LDB + j);
@@ -709,30 +711,32 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p)
         suma += __shfl_xor_sync(0xffffffffu, suma, 2);
         sumb += __shfl_xor_sync(0xffffffffu, sumb, 1);
         sumb += __shfl_xor_sync(0xffffffffu, sumb, 2);
-        const int nh = threadIdx.x >> 7;
+        const int nq = threadIdx.x >> 7;  // column quarter of this warp
         if (t == 0) {
-            s_dot[ia * 2 + nh] = suma;
-            s_dot[ib * 2 + nh] = sumb;
+            s_dot[ia * 4 + nq] = suma;
+            s_dot[ib * 4 + nq] = sumb;
         }
     }
     __syncthreads();
     if (threadIdx.x < CL && threadIdx.x < ch.nvalid) {
         const int i = threadIdx.x;
-        p.dgam[((long long)ch.b * p.g.T + ch.t0 + i) * p.g.H + ch.hh] = s_dot[i * 2] + s_dot[i * 2 + 1];
+        p.dgam[((long long)ch.b * p.g.T + ch.t0 + i) * p.g.H + ch.hh] =
+            (s_dot[i * 4] + s_dot[i * 4 + 1]) + (s_dot[i * 4 + 2] + s_dot[i * 4 + 3]);
     }
     {
-        const int c = threadIdx.x >> 1, hf = threadIdx.x & 1;
+        const int c = threadIdx.x >> 2, qt = threadIdx.x & 3;  // four lanes per state row
         float acc = 0.f;
 #pragma unroll
-        for (int v8 = 0; v8 < CL; v8 += 8) {
+        for (int v8 = 0; v8 < DP / 4; v8 += 8) {
             float a[8], b[8];
-            load8_bsm(b_Ct, c, hf * CL + v8, a);
-            load8_bsm(b_dC, c, hf * CL + v8, b);
+            load8_bsm(b_Ct, c, qt * (DP / 4) + v8, a);
+            load8_bsm(b_dC, c, qt * (DP / 4) + v8, b);
 #pragma unroll
             for (int e = 0; e < 8; ++e) acc = fmaf(a[e], b[e], acc);
         }
         acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-        if (hf == 0) p.CdC[ch.gi * DP + c] = acc;
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        if (qt == 0) p.CdC[ch.gi * DP + c] = acc;
     }
 }
 
@@ -742,7 +746,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p)
 // Writes the final gradients of u, h and log_decay.
 constexpr size_t GATE_CLOSURE_SMEM = 3 * SLOT_BYTES;
 
-__global__ void __launch_bounds__(NTHREADS, 2) k_gate_closure_bwd(BwdParams p) {
+__global__ void __launch_bounds__(NTHREADS, 1) k_gate_closure_bwd(BwdParams p) {
     extern __shared__ __align__(16) float smem[];
     float* s_dG = smem;
     float* s_dE = s_dG + SLOT_FLOATS;
@@ -755,8 +759,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_gate_closure_bwd(BwdParams p) {
         float GL[8];
         load8_panel(gG, CL - 1, c0, GL);
 #pragma unroll 1
-        for (int pp = 0; pp < CL / 16; ++pp) {
-            const int i = lr + 16 * pp;
+        for (int pp = 0; pp < ROW_PASSES; ++pp) {
+            const int i = lr + ROWS_PER_PASS * pp;
             float uh[8], G[8], E[8];
             const float rstd_u = load8_norm(p.u, ch, i, c0, r, uh);
             load8_panel(gG, i, c0, G);

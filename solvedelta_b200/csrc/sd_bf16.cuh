@@ -13,7 +13,7 @@ typedef __nv_bfloat16 bf16;
 
 constexpr int LDB = DP + 8;  // pitch of a [CL][DP] BF16 panel
 constexpr int LDM = CL + 8;  // pitch of a [CL][CL] BF16 matrix or a [DP][CL] half state
-constexpr int BSLOT_ELEMS = (CL * LDB > DP * LDM) ? CL * LDB : DP * LDM;
+constexpr int BSLOT_ELEMS = CL * LDB;  // one [CL][DP] BF16 panel
 constexpr int BMAT_ELEMS = CL * LDM;
 constexpr size_t BSLOT_BYTES = size_t(BSLOT_ELEMS) * 2;
 constexpr size_t BMAT_BYTES = size_t(BMAT_ELEMS) * 2;

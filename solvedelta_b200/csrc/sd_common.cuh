@@ -17,7 +17,11 @@ constexpr int DP = 128;       // padded channel width
 constexpr int LDP = DP + 4;   // shared-memory row pitch of a panel
 constexpr int LDA = CL + 4;   // row pitch of a CL x CL matrix
 constexpr int LDH = CL + 4;   // row pitch of a [DP][CL] half state (transposed read)
-constexpr int NTHREADS = 256;
+constexpr int NTHREADS = 512;            // threads of a chunk CTA (16 warps)
+constexpr int ROWS_PER_PASS = NTHREADS / 16;  // token rows covered by one row-wise pass
+constexpr int ROW_PASSES = CL / ROWS_PER_PASS;
+constexpr int NT128 = DP / 32;            // 8-column MMA tiles per warp for a CL x DP output
+constexpr int NT64 = CL / 32;             // ... for a CL x CL output
 constexpr float RHO = 0.625f; // radius of the residual-local frame
 constexpr float EXP_CLAMP = 80.0f;
 
@@ -250,12 +254,13 @@ __device__ __forceinline__ void warp_epi(float (&acc)[NTW][4], int r0, int n0, F
     }
 }
 
-// Warp tiling of a CL x N output over the 8 warps of a chunk CTA.
+// Warp tiling of a CL x N output over the 16 warps of a chunk CTA
+// (4 row tiles x 4 column quarters).
 template <int N>
 struct Tile64 {
-    static constexpr int NTW = N / 16;
+    static constexpr int NTW = N / 32;
     __device__ static __forceinline__ int r0() { return ((threadIdx.x >> 5) & 3) * 16; }
-    __device__ static __forceinline__ int n0() { return (threadIdx.x >> 7) * (N / 2); }
+    __device__ static __forceinline__ int n0() { return (threadIdx.x >> 7) * (N / 4); }
 };
 
 // ---- unit-triangular solves ------------------------------------------------
@@ -267,6 +272,7 @@ struct Tile64 {
 // Entries outside the stated triangle must be exactly zero.
 template <bool UPPER>
 __device__ __forceinline__ void trisolve(const float* Mr, float sgn, float* P0, float* P1) {
+    if (threadIdx.x >= 2 * DP) return;  // one thread per right-hand-side column
     float* P = (threadIdx.x < DP) ? P0 : P1;
     const int col = threadIdx.x & (DP - 1);
     float x[CL];
@@ -326,8 +332,8 @@ __device__ __forceinline__ void load_norm_panel(const Operand& op, const Chunk& 
                                                 float* rstd) {
     const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
 #pragma unroll
-    for (int p = 0; p < CL / 16; ++p) {
-        int i = lr + 16 * p;
+    for (int p = 0; p < ROW_PASSES; ++p) {
+        int i = lr + ROWS_PER_PASS * p;
         float x[8];
         load8_bf16(row_bf16(op, ch, i), c0, width, op.vec, i < ch.nvalid, x);
         float ss = 0.f;
@@ -344,8 +350,8 @@ __device__ __forceinline__ void load_norm_panel(const Operand& op, const Chunk& 
 __device__ __forceinline__ void load_raw_panel(const Operand& op, const Chunk& ch, int width, float* sm) {
     const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
 #pragma unroll
-    for (int p = 0; p < CL / 16; ++p) {
-        int i = lr + 16 * p;
+    for (int p = 0; p < ROW_PASSES; ++p) {
+        int i = lr + ROWS_PER_PASS * p;
         float x[8];
         load8_bf16(row_bf16(op, ch, i), c0, width, op.vec, i < ch.nvalid, x);
 #pragma unroll
@@ -356,8 +362,8 @@ __device__ __forceinline__ void load_raw_panel(const Operand& op, const Chunk& c
 __device__ __forceinline__ void load_f32_panel(const Operand& op, const Chunk& ch, int width, float* sm) {
     const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
 #pragma unroll
-    for (int p = 0; p < CL / 16; ++p) {
-        int i = lr + 16 * p;
+    for (int p = 0; p < ROW_PASSES; ++p) {
+        int i = lr + ROWS_PER_PASS * p;
         float x[8];
         load8_f32(row_f32(op, ch, i), c0, width, op.vec, i < ch.nvalid, x);
 #pragma unroll

@@ -126,12 +126,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
     }
     __syncthreads();
     {
-        float acc[4][4];
-        acc_zero<4>(acc);
+        float acc[NT64][4];
+        acc_zero<NT64>(acc);
         const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
-        warp_mma<4>(acc, r0, n0, 0, DP, [&](int i, int k) { return s_ut[i * LDP + k]; },
+        warp_mma<NT64>(acc, r0, n0, 0, DP, [&](int i, int k) { return s_ut[i * LDP + k]; },
                     [&](int k, int n) { return s_un[n * LDP + k]; });
-        warp_epi<4>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
+        warp_epi<NT64>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
             float gm = s_gam[i];
             s_lm[i * LDA + j] = (j < i) ? gm * v0 : 0.f;
             s_lm[i * LDA + j + 1] = (j + 1 < i) ? gm * v1 : 0.f;
@@ -216,31 +216,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
         s_un[i * LDP + c] *= clamp_exp_neg(s_G[i * LDP + c]);
     }
     {
-        float acc[4][4];
-        acc_zero<4>(acc);
+        float acc[NT64][4];
+        acc_zero<NT64>(acc);
         const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
-        warp_mma<4>(acc, r0, n0, 0, DP, [&](int i, int k) { return s_kh[i * LDP + k]; },
+        warp_mma<NT64>(acc, r0, n0, 0, DP, [&](int i, int k) { return s_kh[i * LDP + k]; },
                     [&](int k, int n) { return s_dl[n * LDP + k]; });
-        warp_epi<4>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
+        warp_epi<NT64>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
             s_aqk[i * LDA + j] = (j <= i) ? v0 : 0.f;
             s_aqk[i * LDA + j + 1] = (j + 1 <= i) ? v1 : 0.f;
         });
     }
     cp_wait<1>();
     __syncthreads();
-    float acc[8][4];
-    acc_zero<8>(acc);
+    float acc[NT128][4];
+    acc_zero<NT128>(acc);
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
-    warp_mma<8>(acc, r0, n0, 0, CL, [&](int i, int k) { return s_kh[i * LDP + k]; },
+    warp_mma<NT128>(acc, r0, n0, 0, CL, [&](int i, int k) { return s_kh[i * LDP + k]; },
                 [&](int k, int n) { return s_st0[n * LDH + k]; });
-    warp_mma<8>(acc, r0, n0, 0, r0 + 16, [&](int i, int k) { return s_aqk[i * LDA + k]; },
+    warp_mma<NT128>(acc, r0, n0, 0, r0 + 16, [&](int i, int k) { return s_aqk[i * LDA + k]; },
                 [&](int k, int n) { return s_un[k * LDP + n]; });
     cp_wait<0>();
     __syncthreads();
-    warp_mma<8>(acc, r0, n0, 0, CL, [&](int i, int k) { return s_kh[i * LDP + CL + k]; },
+    warp_mma<NT128>(acc, r0, n0, 0, CL, [&](int i, int k) { return s_kh[i * LDP + CL + k]; },
                 [&](int k, int n) { return s_st1[n * LDH + k]; });
     float* gd = panel_ptr(p.Dprim, ch.gi);
-    warp_epi<8>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
+    warp_epi<NT128>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
         float2 kh = *reinterpret_cast<const float2*>(s_kh + i * LDP + j);
         float2 G = *reinterpret_cast<const float2*>(s_G + i * LDP + j);
         *reinterpret_cast<float2*>(gd + i * DP + j) =
@@ -272,8 +272,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
         float GL[8];
         load8_panel(gG, CL - 1, c0, GL);
 #pragma unroll 1
-        for (int pp = 0; pp < CL / 16; ++pp) {
-            const int i = lr + 16 * pp;
+        for (int pp = 0; pp < ROW_PASSES; ++pp) {
+            const int i = lr + ROWS_PER_PASS * pp;
             float uh[8], kh[8], qh[8], dl[8], d[8], er[8], wr[8], v[8], G[8], se[8];
             load8_norm(p.u, ch, i, c0, r, uh);
             load8_norm(p.k, ch, i, c0, r, kh);
@@ -308,19 +308,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
     }
     __syncthreads();
     {
-        float a1[4][4], a2[4][4];
-        acc_zero<4>(a1);
-        acc_zero<4>(a2);
+        float a1[NT64][4], a2[NT64][4];
+        acc_zero<NT64>(a1);
+        acc_zero<NT64>(a2);
         const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
         auto fb = [&](int k, int n) { return s_dn[n * LDP + k]; };
-        warp_mma<4>(a1, r0, n0, 0, DP, [&](int i, int k) { return s_xg[i * LDP + k]; }, fb);
-        warp_mma<4>(a2, r0, n0, 0, DP, [&](int i, int k) { return s_ag[i * LDP + k]; }, fb);
+        warp_mma<NT64>(a1, r0, n0, 0, DP, [&](int i, int k) { return s_xg[i * LDP + k]; }, fb);
+        warp_mma<NT64>(a2, r0, n0, 0, DP, [&](int i, int k) { return s_ag[i * LDP + k]; }, fb);
         bf16* gAqd = bmat_ptr(p.Aqd, ch.gi);
-        warp_epi<4>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
+        warp_epi<NT64>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
             *reinterpret_cast<__nv_bfloat162*>(gAqd + i * CL + j) =
                 __floats2bfloat162_rn((j <= i) ? v0 : 0.f, (j + 1 <= i) ? v1 : 0.f);
         });
-        warp_epi<4>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
+        warp_epi<NT64>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
             s_aed[i * LDA + j] = (j < i) ? v0 : 0.f;
             s_aed[i * LDA + j + 1] = (j + 1 < i) ? v1 : 0.f;
         });
@@ -336,7 +336,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
 // Output rows: y = Xg S_c + tril(Aqd) Z~, BF16 operands (the result is BF16).
 constexpr size_t OUTPUT_FWD_SMEM = 2 * BSLOT_BYTES + BSTATE_BYTES + BMAT_BYTES;
 
-__global__ void __launch_bounds__(NTHREADS, 2) k_output_fwd(FwdParams p) {
+__global__ void __launch_bounds__(NTHREADS, 1) k_output_fwd(FwdParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* b_xg = reinterpret_cast<bf16*>(smem_raw);
     bf16* b_zt = b_xg + BSLOT_ELEMS;
@@ -352,13 +352,13 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_output_fwd(FwdParams p) {
     g2s_panel_f32_to_bf16(b_zt, panel_ptr(p.Zt, ch.gi));
     cp_wait<0>();
     __syncthreads();
-    float acc[8][4];
-    acc_zero<8>(acc);
+    float acc[NT128][4];
+    acc_zero<NT128>(acc);
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
-    warp_mma_bf16<8, false, false>(acc, b_xg, LDB, b_S, LDB, r0, n0, 0, DP);
-    warp_mma_bf16<8, false, false>(acc, b_aqd, LDM, b_zt, LDB, r0, n0, 0, r0 + 16);
+    warp_mma_bf16<NT128, false, false>(acc, b_xg, LDB, b_S, LDB, r0, n0, 0, DP);
+    warp_mma_bf16<NT128, false, false>(acc, b_aqd, LDM, b_zt, LDB, r0, n0, 0, r0 + 16);
     __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y);
-    warp_epi<8>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
+    warp_epi<NT128>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
         if (i >= ch.nvalid || j >= V) return;
         __nv_bfloat16* row = y + (((long long)ch.b * p.g.T + ch.t0 + i) * p.g.H + ch.hh) * (long long)V;
         if (j + 1 < V && (V & 1) == 0) {

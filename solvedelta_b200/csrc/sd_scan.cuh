@@ -16,6 +16,7 @@
 namespace sd {
 
 constexpr int SCAN_NS = 64;            // state columns per CTA
+constexpr int SCAN_THREADS = 256;      // 8 warps: one 16-row strip of the state slice each
 constexpr int LDT = SCAN_NS + 8;       // pitch of [*][NS] shared buffers
 
 struct ScanParams {
@@ -46,13 +47,13 @@ __device__ __forceinline__ void cp_async_wait() {
 }
 
 __device__ __forceinline__ void async_panel(float* sm, const float* g) {
-    for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += NTHREADS) {
+    for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += SCAN_THREADS) {
         int i = idx >> 5, c4 = (idx & 31) << 2;
         cp_async16(sm + i * LDP + c4, g + i * DP + c4);
     }
 }
 __device__ __forceinline__ void async_slice(float* sm, const float* g, int col0) {
-    for (int idx = threadIdx.x; idx < CL * (SCAN_NS / 4); idx += NTHREADS) {
+    for (int idx = threadIdx.x; idx < CL * (SCAN_NS / 4); idx += SCAN_THREADS) {
         int i = idx / (SCAN_NS / 4), c4 = (idx % (SCAN_NS / 4)) << 2;
         cp_async16(sm + i * LDT + c4, g + i * DP + col0 + c4);
     }
@@ -61,7 +62,7 @@ __device__ __forceinline__ void async_slice(float* sm, const float* g, int col0)
 constexpr size_t SCAN_SMEM_BYTES =
     (size_t(3) * CL * LDP + size_t(3) * CL * LDT + size_t(DP) * LDT) * sizeof(float);
 
-__global__ void __launch_bounds__(NTHREADS, 1) k_state_scan(ScanParams p) {
+__global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan(ScanParams p) {
     extern __shared__ __align__(16) float smem[];
     float* sQ = smem;
     float* sR = sQ + CL * LDP;
@@ -219,8 +220,14 @@ struct ScanParamsB {
     int NC, reverse, transposed_io, nrows, ncols;
 };
 
+__device__ __forceinline__ void async_bpanel_scan(bf16* sm, const bf16* g) {
+    for (int idx = threadIdx.x; idx < CL * (DP / 8); idx += SCAN_THREADS) {
+        int i = idx >> 4, c8 = (idx & 15) << 3;
+        cp16(sm + i * LDB + c8, g + i * DP + c8);
+    }
+}
 __device__ __forceinline__ void async_bslice(bf16* sm, const bf16* g, int col0) {
-    for (int idx = threadIdx.x; idx < CL * (SCAN_NS / 8); idx += NTHREADS) {
+    for (int idx = threadIdx.x; idx < CL * (SCAN_NS / 8); idx += SCAN_THREADS) {
         int i = idx / (SCAN_NS / 8), c8 = (idx % (SCAN_NS / 8)) << 3;
         cp16(sm + i * LDTB + c8, g + i * DP + col0 + c8);
     }
@@ -228,7 +235,7 @@ __device__ __forceinline__ void async_bslice(bf16* sm, const bf16* g, int col0) 
 
 constexpr size_t SCAN_B_SMEM_BYTES = (size_t(3) * CL * LDB + size_t(3) * CL * LDTB + size_t(DP) * LDTB) * 2;
 
-__global__ void __launch_bounds__(NTHREADS, 1) k_state_scan_b(ScanParamsB p) {
+__global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan_b(ScanParamsB p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
     bf16* sR = sQ + CL * LDB;
@@ -264,14 +271,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_state_scan_b(ScanParamsB p) {
     auto chunk_at = [&](int step) { return base + (p.reverse ? (p.NC - 1 - step) : step); };
     auto issue_a = [&](int step) {
         long long gi = chunk_at(step);
-        async_bpanel(sQ, bpanel_ptr(p.Q, gi));
+        async_bpanel_scan(sQ, bpanel_ptr(p.Q, gi));
         async_bslice(sP, bpanel_ptr(p.P, gi), col0);
     };
     auto issue_b = [&](int step) {
         long long gi = chunk_at(step);
-        async_bpanel(sR, bpanel_ptr(p.R, gi));
+        async_bpanel_scan(sR, bpanel_ptr(p.R, gi));
         if (has2) {
-            async_bpanel(sR2, bpanel_ptr(p.R2, gi));
+            async_bpanel_scan(sR2, bpanel_ptr(p.R2, gi));
             async_bslice(sX2, bpanel_ptr(p.X2, gi), col0);
         }
     };
