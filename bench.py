@@ -253,6 +253,9 @@ class DeviceStep:
     def stream(self):
         return ctypes.c_void_p(self.torch.cuda.current_stream().cuda_stream)
 
+    def forward_only(self):
+        self.lib_mod.check(self.lib.sd_forward(ctypes.byref(self.fa), self.stream()))
+
     def step(self):
         st = self.stream()
         self.lib_mod.check(self.lib.sd_forward(ctypes.byref(self.fa), st))
@@ -298,6 +301,7 @@ def run_ours(opts, rank, world, local_rank):
 
     import solvedelta_b200
     from solvedelta_b200 import SolveDeltaState, solvedelta_native
+    from solvedelta_b200.sharding import job_throughput, max_over_ranks, rank_seed
 
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback")
@@ -310,7 +314,7 @@ def run_ours(opts, rank, world, local_rank):
     if opts.case == "small":
         w.update(B=2, T=1024)
     B, T, H, r, V = w["B"], w["T"], w["H"], w["r"], w["V"]
-    cpu = make_cpu_inputs(B, T, H, r, V, seed=rank)
+    cpu = make_cpu_inputs(B, T, H, r, V, seed=rank_seed(0, rank))
     runner = DeviceStep(cpu, device)
 
     def barrier():
@@ -333,11 +337,19 @@ def run_ours(opts, rank, world, local_rank):
     barrier()
     ms_total = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
-    t = torch.tensor([ms_total], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = float(t.item()) / opts.steps
-    value = world * runner.tokens / (ms_step * 1e-3)
+    ms_step = max_over_ranks(ms_total, device) / opts.steps
+    value = job_throughput(runner.tokens, ms_step * 1e-3, world)
+
+    # ---- forward only (the kernel-level forward configuration), same inputs ----
+    for _ in range(3):
+        runner.forward_only()
+    barrier()
+    e0.record()
+    for _ in range(opts.steps):
+        runner.forward_only()
+    e1.record()
+    barrier()
+    fwd_ms = max_over_ranks(e0.elapsed_time(e1), device) / opts.steps
 
     # ---- per-kernel device times (rank 0) --------------------------------
     roofline, kernels = None, None
@@ -396,11 +408,8 @@ def run_ours(opts, rank, world, local_rank):
             e2e_step()
         e1.record()
         barrier()
-        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item()) / e2e_steps
-        e2e = {"value": world * runner.tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+        e2e_ms = max_over_ranks(e0.elapsed_time(e1), device) / e2e_steps
+        e2e = {"value": job_throughput(runner.tokens, e2e_ms * 1e-3, world), "unit": "tokens/s", "ms_per_step": e2e_ms,
                "steps": e2e_steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
 
     if rank == 0:
@@ -424,6 +433,8 @@ def run_ours(opts, rank, world, local_rank):
                        "arithmetic": "bf16 operands, tf32 tensor-core contractions, fp32 states"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": runner.launches * opts.steps,
             "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu_baseline,
+            "forward_only": {"ms_per_step": fwd_ms, "value": job_throughput(runner.tokens, fwd_ms * 1e-3, world),
+                             "unit": "tokens/s"},
         }
         print(json.dumps(line), flush=True)
     if world > 1:

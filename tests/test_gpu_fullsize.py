@@ -1,0 +1,98 @@
+"""Benchmark-size checks (B=8, H=8, T=4096, r=V=128) that do not need the CPU
+checker on the whole tensor: size-independent properties of the recurrence,
+plus the checker on two single streams of the full-length run."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import solvedelta_oracle as orc
+from solvedelta_b200 import SolveDeltaState, solvedelta_native
+from tests.helpers import max_rel, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+B, T, H, R, V = 8, 4096, 8, 128, 128
+NAMES = ("u", "h", "q", "keys", "values", "log_decay", "erase_raw", "write_raw", "geometry_write")
+
+
+@pytest.fixture(scope="module")
+def workload():
+    from bench import make_cpu_inputs
+
+    cpu = make_cpu_inputs(B, T, H, R, V, seed=0)
+    dev = {k: v.cuda() for k, v in cpu.items()}
+    return cpu, dev
+
+
+def _run(dev, *, lo=0, hi=T, state=None, scale_values=1.0):
+    args = [dev[n][:, lo:hi] for n in NAMES]
+    if scale_values != 1.0:
+        args[4] = args[4] * scale_values
+    if state is None:
+        state = SolveDeltaState(dev["C0"], dev["S0"])
+    with torch.no_grad():
+        return solvedelta_native(*args, initial_state=state, return_final_state=True)
+
+
+def test_split_continuation_is_bit_equal_at_full_length(workload):
+    _, dev = workload
+    y, fin = _run(dev)
+    y1, s1 = _run(dev, hi=T // 2)
+    y2, s2 = _run(dev, lo=T // 2, state=s1)
+    assert torch.equal(torch.cat([y1, y2], dim=1), y)
+    assert torch.equal(s2.predictor, fin.predictor) and torch.equal(s2.S, fin.S)
+    assert torch.isfinite(y).all()
+
+
+def test_memory_side_is_linear_in_values_and_initial_memory(workload):
+    # y and S are linear in (values, S0); a factor of two commutes with every rounding
+    _, dev = workload
+    y, fin = _run(dev)
+    y2, fin2 = _run(dev, state=SolveDeltaState(dev["C0"], 2.0 * dev["S0"]), scale_values=2.0)
+    assert torch.equal(y2.float(), 2.0 * y.float())
+    assert torch.equal(fin2.S, 2.0 * fin.S)
+    assert torch.equal(fin2.predictor, fin.predictor)  # the predictor never sees the values
+
+
+def test_streams_are_independent(workload):
+    _, dev = workload
+    y, fin = _run(dev)
+    perm = torch.tensor([3, 0, 7, 1, 6, 2, 5, 4], device="cuda")
+    shuffled = {k: v[perm] for k, v in dev.items()}
+    yp, finp = _run(shuffled)
+    assert torch.equal(yp, y[perm])
+    assert torch.equal(finp.S, fin.S[perm]) and torch.equal(finp.predictor, fin.predictor[perm])
+
+
+@pytest.mark.parametrize("b,h", [(0, 0), (7, 7)])
+def test_single_streams_of_the_full_run_match_the_checker(workload, b, h):
+    cpu, dev = workload
+    leaves = [dev[n].detach().clone().requires_grad_() for n in NAMES]
+    state = SolveDeltaState(dev["C0"].clone().requires_grad_(), dev["S0"].clone().requires_grad_())
+    y, fin = solvedelta_native(*leaves, initial_state=state, return_final_state=True)
+    grads = torch.autograd.grad((y, fin.predictor, fin.S), leaves + list(state),
+                                (dev["dy"], dev["dC_T"], dev["dS_T"]))
+    d = lambda x: x[b:b + 1, :, h:h + 1].double().numpy()
+    args = [d(cpu["u"]), d(cpu["h"]), d(cpu["q"]), d(cpu["keys"]), d(cpu["values"]), d(cpu["log_decay"]),
+            d(torch.sigmoid(cpu["erase_raw"].double())), d(torch.sigmoid(cpu["write_raw"].double())),
+            d(cpu["geometry_write"])]
+    st = (cpu["C0"][b:b + 1, h:h + 1].double().numpy(), cpu["S0"][b:b + 1, h:h + 1].double().numpy())
+    yo, so = orc.forward(*args, initial_state=st)
+    ref = orc.backward(*args, d(cpu["dy"]), dC_T=cpu["dC_T"][b:b + 1, h:h + 1].double().numpy(),
+                       dS_T=cpu["dS_T"][b:b + 1, h:h + 1].double().numpy(), initial_state=st)
+    sl = lambda x: x[b:b + 1, :, h:h + 1].detach().float().cpu().numpy()
+    assert max_rel(sl(y), yo) <= 2e-2
+    assert max_rel(fin.predictor[b:b + 1, h:h + 1].detach().cpu().numpy(), so.predictor) <= 1e-3
+    assert max_rel(fin.S[b:b + 1, h:h + 1].detach().cpu().numpy(), so.S) <= 1e-3
+    se = torch.sigmoid(cpu["erase_raw"].double()).numpy()[b:b + 1, :, h:h + 1, 0]
+    sw = torch.sigmoid(cpu["write_raw"].double()).numpy()[b:b + 1, :, h:h + 1, 0]
+    want = [ref["u"], ref["h"], ref["q"], ref["keys"][:, :, :, None], ref["values"][:, :, :, None],
+            ref["log_decay"], (ref["erase"] * se * (1 - se))[:, :, :, None],
+            (ref["write"] * sw * (1 - sw))[:, :, :, None], ref["geometry_write"]]
+    for name, g, w in zip(NAMES, grads[:9], want):
+        g = sl(g)
+        assert rel_l2(g, w) <= 3e-2, (name, rel_l2(g, w))
+        assert max_rel(g, w) <= 2e-2, (name, max_rel(g, w))
+    gC = grads[9][b:b + 1, h:h + 1].cpu().numpy()
+    gS = grads[10][b:b + 1, h:h + 1].cpu().numpy()
+    assert rel_l2(gC, ref["C0"]) <= 3e-2 and rel_l2(gS, ref["S0"]) <= 3e-2
