@@ -72,7 +72,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
@@ -323,12 +323,13 @@ def run_ours(opts, rank, world, local_rank):
         torch.cuda.synchronize()
 
     # ---- device-resident throughput ------------------------------------
-    for _ in range(max(opts.warmup, 3)):
-        runner.step()
-    barrier()
+    # the clock sampler runs from the warm-up on, so that its samples are taken under load
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(max(opts.warmup, 3)):
+        runner.step()
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(opts.steps):
@@ -444,8 +445,8 @@ def run_ours(opts, rank, world, local_rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--case", default="full", choices=["full", "small"],
                     help="small = B=2, T=1024 (for profiler captures); the reported metric is defined on full")

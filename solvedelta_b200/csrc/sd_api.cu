@@ -21,12 +21,12 @@ struct PanelDesc {
     int kind;
 };
 
-const PanelDesc kSaved[] = {{"Lam", 3}, {"G", 0}, {"Delta", 0}, {"Dprim", 0}, {"Zt", 0}, {"CtCk", 2}, {"SCk", 2}};
+const PanelDesc kSaved[] = {{"Lam", 3}, {"G", 0}, {"Delta", 0}, {"Dprim", 0}, {"Zt", 4}, {"CtCk", 2}, {"SCk", 6}};
 const PanelDesc kFwd[] = {{"Upd", 0}, {"Qc", 0}, {"Ubar", 0}, {"Wd", 0}, {"Ud", 0}, {"Dt", 0}, {"Xg", 4}, {"Aqd", 5}};
 const PanelDesc kBwd[] = {{"Pp", 4},     {"Qp", 4},     {"Ag", 4},     {"Xg", 4},     {"Dyf", 4},    {"Dneg", 4},
                           {"dR", 4},     {"dSeCk", 6},  {"A1", 4},     {"A2", 4},     {"PY", 4},     {"dDt", 4},
-                          {"SdS", 3},    {"duPart", 0}, {"dkPart", 0}, {"dGPart", 0}, {"dDelta", 0}, {"DG", 4},
-                          {"Xext", 0},   {"Tpre", 4},   {"Khat", 4},   {"Ppp", 4},    {"Qpp", 4},    {"Rneg", 4},
+                          {"SdS", 3},    {"duPart", 4}, {"dkPart", 4}, {"dGPart", 4}, {"dDelta", 4}, {"DG", 4},
+                          {"Xext", 4},   {"Tpre", 4},   {"Khat", 4},   {"Ppp", 4},    {"Qpp", 4},    {"Rneg", 4},
                           {"dRr", 4},    {"dCeCk", 6},  {"dUbar", 4},  {"dUt", 4},    {"Ti", 4},     {"Tj", 4},
                           {"CdC", 3}};
 
@@ -256,9 +256,9 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
     p.Gp = panel_at(kSaved, s, a->saved, "G");
     p.Delta = panel_at(kSaved, s, a->saved, "Delta");
     p.Dprim = panel_at(kSaved, s, a->saved, "Dprim");
-    p.Zt = panel_at(kSaved, s, a->saved, "Zt");
+    p.Zt = bpanel_at(kSaved, s, a->saved, "Zt");
     p.CtCk = panel_at(kSaved, s, a->saved, "CtCk");
-    p.SCk = panel_at(kSaved, s, a->saved, "SCk");
+    p.SCk = bpanel_at(kSaved, s, a->saved, "SCk");
     p.y = a->y;
 
     const int chunks = (int)total_chunks(s);
@@ -269,7 +269,7 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
     mark(stream);
     {
         ScanParams sp{};
-        sp.P = p.Upd; sp.Q = p.Qc; sp.R = p.Ubar; sp.R2 = nullptr; sp.X2 = nullptr;
+        sp.P = p.Upd; sp.Q = p.Qc; sp.R = p.Ubar;
         sp.lam = p.Lam; sp.X = p.Delta; sp.ck = p.CtCk;
         sp.init = a->C0; sp.fin = a->C_T;
         sp.NC = p.g.NC; sp.reverse = 0; sp.transposed_io = 1; sp.nrows = s->r; sp.ncols = s->r;
@@ -282,8 +282,8 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
     mark(stream);
     {
         ScanParams sp{};
-        sp.P = p.Ud; sp.Q = p.Wd; sp.R = p.Dt; sp.R2 = nullptr; sp.X2 = nullptr;
-        sp.lam = p.Lam; sp.X = p.Zt; sp.ck = p.SCk;
+        sp.P = p.Ud; sp.Q = p.Wd; sp.R = p.Dt;
+        sp.lam = p.Lam; sp.X = nullptr; sp.ck = nullptr; sp.Xb = p.Zt; sp.ckb = p.SCk;
         sp.init = a->S0; sp.fin = a->S_T;
         sp.NC = p.g.NC; sp.reverse = 0; sp.transposed_io = 0; sp.nrows = s->r; sp.ncols = s->V;
         k_state_scan<<<scan_grid, SCAN_THREADS, SCAN_SMEM_BYTES, stream>>>(sp);
@@ -328,16 +328,16 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
     p.Gp = panel_at(kSaved, s, sv, "G");
     p.Delta = panel_at(kSaved, s, sv, "Delta");
     p.Dprim = panel_at(kSaved, s, sv, "Dprim");
-    p.Zt = panel_at(kSaved, s, sv, "Zt");
+    p.Zt = bpanel_at(kSaved, s, sv, "Zt");
     p.CtCk = panel_at(kSaved, s, sv, "CtCk");
-    p.SCk = panel_at(kSaved, s, sv, "SCk");
+    p.SCk = bpanel_at(kSaved, s, sv, "SCk");
 #define SD_BP(field) p.field = panel_at(kBwd, s, a->scratch, #field)
 #define SD_BB(field) p.field = bpanel_at(kBwd, s, a->scratch, #field)
     SD_BB(Pp); SD_BB(Qp); SD_BB(Ag); SD_BB(Xg); SD_BB(Dyf); SD_BB(Dneg); SD_BB(dR); SD_BB(dSeCk);
     SD_BB(A1); SD_BB(A2); SD_BB(PY); SD_BB(dDt); SD_BB(DG); SD_BB(Tpre); SD_BB(Khat);
     SD_BB(Ppp); SD_BB(Qpp); SD_BB(Rneg); SD_BB(dRr); SD_BB(dCeCk);
     SD_BB(dUbar); SD_BB(dUt); SD_BB(Ti); SD_BB(Tj);
-    SD_BP(duPart); SD_BP(dkPart); SD_BP(dGPart); SD_BP(dDelta); SD_BP(Xext); SD_BP(SdS); SD_BP(CdC);
+    SD_BB(duPart); SD_BB(dkPart); SD_BB(dGPart); SD_BB(dDelta); SD_BB(Xext); SD_BP(SdS); SD_BP(CdC);
 #undef SD_BB
 #undef SD_BP
     p.du = a->du; p.dh = a->dh; p.dq = a->dq; p.dk = a->dkeys; p.dv = a->dvalues;

@@ -18,14 +18,16 @@ struct BwdParams {
     Geometry g;
     Operand u, h, q, k, v, er, wr, ld, gam, dy;
     // kept by forward (FP32)
-    const float *Lam, *Gp, *Delta, *Dprim, *Zt, *CtCk, *SCk;
+    const float *Lam, *Gp, *Delta, *Dprim, *CtCk;
+    const bf16 *Zt, *SCk;
     // backward scratch: BF16 contraction operands / scanned panels
     bf16 *Pp, *Qp, *Ag, *Xg, *Dyf, *Dneg, *dR, *dSeCk;
     bf16 *A1, *A2, *PY, *dDt, *DG, *Tpre, *Khat;
     bf16 *Ppp, *Qpp, *Rneg, *dRr, *dCeCk;
     bf16 *dUbar, *dUt, *Ti, *Tj;
-    // FP32 partial cotangents and reductions
-    float *duPart, *dkPart, *dGPart, *dDelta, *Xext, *SdS, *CdC;
+    // partial cotangents (BF16: they are final up to gradient tolerance) and FP32 reductions
+    bf16 *duPart, *dkPart, *dGPart, *dDelta, *Xext;
+    float *SdS, *CdC;
     // outputs
     void *du, *dh, *dq, *dk, *dv, *der, *dwr;
     float *dld, *dgam;
@@ -219,16 +221,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
 
     async_bpanel(b_dy, bpanel_ptr(p.Dyf, ch.gi));
     async_bpanel(b_dr, bpanel_ptr(p.dR, ch.gi));
+    async_bpanel(b_zt, bpanel_ptr(p.Zt, ch.gi));
     cp_commit();
     async_bpanel(b_dn, bpanel_ptr(p.Dneg, ch.gi));
+    async_bstate(b_S, bstate_ptr(p.SCk, ch.gi));
     cp_commit();
     async_bpanel(b_xg, bpanel_ptr(p.Xg, ch.gi));
     async_bpanel(b_ag, bpanel_ptr(p.Ag, ch.gi));
     cp_commit();
     async_bstate(b_dS, bstate_ptr(p.dSeCk, ch.gi));
     cp_commit();
-    g2s_panel_f32_to_bf16(b_zt, panel_ptr(p.Zt, ch.gi));
-    g2s_state_f32_to_bf16(b_S, state_ptr(p.SCk, ch.gi));
     cp_wait<3>();
     __syncthreads();
     {
@@ -375,12 +377,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_sources_bwd(BwdParams p) {
         norm_vjp8(dqh, qh, rstd_q, dq);
         store8_bf16(p.dq, p.g, ch, i, c0, r, dq);
         store8_bf16(p.der, p.g, ch, i, c0, r, der);
-        store8_panel(panel_ptr(p.duPart, ch.gi), i, c0, duh);
-        store8_panel(panel_ptr(p.dkPart, ch.gi), i, c0, dkp);
-        store8_panel(panel_ptr(p.dGPart, ch.gi), i, c0, dG);
-        store8_panel(panel_ptr(p.dDelta, ch.gi), i, c0, ddl);
+        store8_bpanel(bpanel_ptr(p.duPart, ch.gi), i, c0, duh);
+        store8_bpanel(bpanel_ptr(p.dkPart, ch.gi), i, c0, dkp);
+        store8_bpanel(bpanel_ptr(p.dGPart, ch.gi), i, c0, dG);
+        store8_bpanel(bpanel_ptr(p.dDelta, ch.gi), i, c0, ddl);
         store8_bpanel(bpanel_ptr(p.DG, ch.gi), i, c0, dg_);
-        store8_panel(panel_ptr(p.Xext, ch.gi), i, c0, xext);
+        store8_bpanel(bpanel_ptr(p.Xext, ch.gi), i, c0, xext);
         // value side: dv = sigmoid(write) dR, d write_raw = dR v sigmoid'(write)
         float wr[8], v[8], dr[8], dv[8], dwr[8];
         load8_bf16(row_bf16(p.wr, ch, i), c0, V, p.wr.vec, i < ch.nvalid, wr);
@@ -514,7 +516,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
         warp_mma_bf16<NT128, false, false>(acc, b_daqk, LDM, b_dl, LDB, r0, n0, 0, r0 + 16);
         const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
         const int ia = r0 + g, ib = ia + 8;
-        const float* gkp = panel_ptr(p.dkPart, ch.gi);
+        const bf16* gkp = bpanel_ptr(p.dkPart, ch.gi);
         const __nv_bfloat16* ka = row_bf16(p.k, ch, ia);
         const __nv_bfloat16* kb = row_bf16(p.k, ch, ib);
         const float rka = s_rk[ia], rkb = s_rk[ib];
@@ -523,8 +525,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
 #pragma unroll
         for (int nt = 0; nt < NT128; ++nt) {
             const int j = n0 + nt * 8 + 2 * t;
-            float2 pa = *reinterpret_cast<const float2*>(gkp + ia * DP + j);
-            float2 pb = *reinterpret_cast<const float2*>(gkp + ib * DP + j);
+            float2 pa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gkp + ia * DP + j));
+            float2 pb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gkp + ib * DP + j));
             acc[nt][0] += pa.x; acc[nt][1] += pa.y;
             acc[nt][2] += pb.x; acc[nt][3] += pb.y;
 #pragma unroll
@@ -567,9 +569,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     // every contraction that reads b_dl (Delta) is done: reuse it for dDelta_loc
     __syncthreads();
     {
-        const float* gdd = panel_ptr(p.dDelta, ch.gi);
+        const bf16* gdd = bpanel_ptr(p.dDelta, ch.gi);
         warp_epi<NT128>(accd, r0, n0, [&](int i, int j, float v0, float v1) {
-            float2 src = *reinterpret_cast<const float2*>(gdd + i * DP + j);
+            float2 src = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gdd + i * DP + j));
             *reinterpret_cast<__nv_bfloat162*>(b_dl + i * LDB + j) = __floats2bfloat162_rn(src.x + v0, src.y + v1);
         });
     }
@@ -771,14 +773,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_gate_closure_bwd(BwdParams p) {
                 for (int e = 0; e < 8; ++e) E[e] = 0.f;
             }
             float dup[8], tpre[8], dub[8], dut[8], ti[8], tj[8], dgp[8], xext[8], drr[8];
-            load8_panel(panel_ptr(p.duPart, ch.gi), i, c0, dup);
+            load8_bpanel(bpanel_ptr(p.duPart, ch.gi), i, c0, dup);
             load8_bpanel(bpanel_ptr(p.Tpre, ch.gi), i, c0, tpre);
             load8_bpanel(bpanel_ptr(p.dUbar, ch.gi), i, c0, dub);
             load8_bpanel(bpanel_ptr(p.dUt, ch.gi), i, c0, dut);
             load8_bpanel(bpanel_ptr(p.Ti, ch.gi), i, c0, ti);
             load8_bpanel(bpanel_ptr(p.Tj, ch.gi), i, c0, tj);
-            load8_panel(panel_ptr(p.dGPart, ch.gi), i, c0, dgp);
-            load8_panel(panel_ptr(p.Xext, ch.gi), i, c0, xext);
+            load8_bpanel(bpanel_ptr(p.dGPart, ch.gi), i, c0, dgp);
+            load8_bpanel(bpanel_ptr(p.Xext, ch.gi), i, c0, xext);
             load8_bpanel(bpanel_ptr(p.dRr, ch.gi), i, c0, drr);
             float duh[8], dE[8], dG[8], X[8];
 #pragma unroll

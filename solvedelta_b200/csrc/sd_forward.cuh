@@ -15,7 +15,8 @@ struct FwdParams {
     float *Upd, *Qc, *Ubar, *Wd, *Ud, *Dt;
     bf16 *Xg, *Aqd;  // operands of the output contraction only
     // kept for backward
-    float *Lam, *Gp, *Delta, *Dprim, *Zt, *CtCk, *SCk;
+    float *Lam, *Gp, *Delta, *Dprim, *CtCk;
+    bf16 *Zt, *SCk;  // only BF16 contractions read these
     void* y;
 };
 
@@ -347,9 +348,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_output_fwd(FwdParams p) {
 
     async_bpanel(b_xg, bpanel_ptr(p.Xg, ch.gi));
     async_bmat(b_aqd, bmat_ptr(p.Aqd, ch.gi));
+    async_bpanel(b_zt, bpanel_ptr(p.Zt, ch.gi));
+    {
+        const bf16* gS = p.SCk + ch.gi * (long long)(DP * DP);
+        for (int idx = threadIdx.x; idx < DP * (DP / 8); idx += NTHREADS) {
+            int i = idx >> 4, c8 = (idx & 15) << 3;
+            cp16(b_S + i * LDB + c8, gS + i * DP + c8);
+        }
+    }
     cp_commit();
-    g2s_state_f32_to_bf16(b_S, state_ptr(p.SCk, ch.gi));
-    g2s_panel_f32_to_bf16(b_zt, panel_ptr(p.Zt, ch.gi));
     cp_wait<0>();
     __syncthreads();
     float acc[NT128][4];

@@ -11,11 +11,13 @@
 // sequence; panels of the next chunk stream in through cp.async while the
 // current contraction runs.
 #pragma once
+#include "sd_bf16.cuh"
 #include "sd_common.cuh"
 
 namespace sd {
 
-constexpr int SCAN_NS = 64;            // state columns per CTA
+constexpr int SCAN_NS = 64;            // state columns per CTA (2 CTAs per stream)
+constexpr int SCAN_G1 = SCAN_NS / 16;  // 8-column tiles per warp in X = P + Q St
 constexpr int SCAN_THREADS = 256;      // 8 warps: one 16-row strip of the state slice each
 constexpr int LDT = SCAN_NS + 8;       // pitch of [*][NS] shared buffers
 
@@ -23,11 +25,11 @@ struct ScanParams {
     const float* P;    // [chunks][CL][DP]
     const float* Q;
     const float* R;
-    const float* R2;   // nullable
-    const float* X2;   // nullable (same column slicing as P)
     const float* lam;  // [chunks][DP]
-    float* X;          // out [chunks][CL][DP]
-    float* ck;         // out [chunks][DP][DP] state before the chunk's update
+    float* X;          // out [chunks][CL][DP]            (FP32; or null when Xb is set)
+    float* ck;         // out [chunks][DP][DP] state before the chunk's update (or null when ckb is set)
+    bf16* Xb;          // BF16 alternatives for consumers that only feed BF16 contractions
+    bf16* ckb;
     const float* init; // nullable: true-dimension state [S][rows][cols] (or transposed)
     float* fin;        // nullable
     int NC;            // chunks per stream
@@ -60,22 +62,22 @@ __device__ __forceinline__ void async_slice(float* sm, const float* g, int col0)
 }
 
 constexpr size_t SCAN_SMEM_BYTES =
-    (size_t(3) * CL * LDP + size_t(3) * CL * LDT + size_t(DP) * LDT) * sizeof(float);
+    (size_t(4) * CL * LDP + size_t(3) * CL * LDT + size_t(DP) * LDT) * sizeof(float);
 
+// FP32 panels, TF32 contractions: the two forward scans (no second update pair).
+// Panels of chunk step+1 are in flight (cp.async, two-deep ring) during the whole
+// of step, so the serial chain never waits for HBM.
 __global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan(ScanParams p) {
     extern __shared__ __align__(16) float smem[];
-    float* sQ = smem;
-    float* sR = sQ + CL * LDP;
-    float* sR2 = sR + CL * LDP;
-    float* sP = sR2 + CL * LDP;   // [CL][LDT]
-    float* sX = sP + CL * LDT;    // [CL][LDT]
-    float* sX2 = sX + CL * LDT;   // [CL][LDT]
-    float* sSt = sX2 + CL * LDT;  // [DP][LDT]
+    float* sQ = smem;                   // [2][CL][LDP]
+    float* sR = sQ + 2 * CL * LDP;      // [2][CL][LDP]
+    float* sP = sR + 2 * CL * LDP;      // [2][CL][LDT]
+    float* sX = sP + 2 * CL * LDT;      // [CL][LDT]
+    float* sSt = sX + CL * LDT;         // [DP][LDT]
 
     const int col0 = blockIdx.x * SCAN_NS;
     const int s = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const bool has2 = p.R2 != nullptr;
     const long long base = (long long)s * p.NC;
 
     // state slice: warp owns rows [16*warp, 16*warp+16), all NS columns
@@ -97,63 +99,76 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan(ScanParams p) {
     }
 
     auto chunk_at = [&](int step) { return base + (p.reverse ? (p.NC - 1 - step) : step); };
-    auto issue_a = [&](int step) {  // what the first contraction needs
-        long long gi = chunk_at(step);
-        async_panel(sQ, panel_ptr(p.Q, gi));
-        async_slice(sP, panel_ptr(p.P, gi), col0);
-    };
-    auto issue_b = [&](int step) {  // what the state update needs
-        long long gi = chunk_at(step);
-        async_panel(sR, panel_ptr(p.R, gi));
-        if (has2) {
-            async_panel(sR2, panel_ptr(p.R2, gi));
-            async_slice(sX2, panel_ptr(p.X2, gi), col0);
+    auto issue = [&](int step) {
+        if (step < p.NC) {
+            const long long gi = chunk_at(step);
+            const int b = step & 1;
+            async_panel(sQ + b * CL * LDP, panel_ptr(p.Q, gi));
+            async_slice(sP + b * CL * LDT, panel_ptr(p.P, gi), col0);
+            async_panel(sR + b * CL * LDP, panel_ptr(p.R, gi));
         }
+        cp_async_commit();
     };
-
-    issue_a(0);
-    cp_async_commit();
-    issue_b(0);
-    cp_async_commit();
+    issue(0);
+    issue(1);
 
     for (int step = 0; step < p.NC; ++step) {
         const long long gi = chunk_at(step);
+        const float* bQ = sQ + (step & 1) * CL * LDP;
+        const float* bR = sR + (step & 1) * CL * LDP;
+        const float* bP = sP + (step & 1) * CL * LDT;
         const float la = p.lam[gi * DP + row_a], lb = p.lam[gi * DP + row_b];
         // publish the state slice: shared copy for the contraction, global checkpoint
         {
-            float* ck = state_ptr(p.ck, gi);
 #pragma unroll
             for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
                 int cc = nt * 8 + 2 * t;
                 *reinterpret_cast<float2*>(sSt + row_a * LDT + cc) = make_float2(st[nt][0], st[nt][1]);
                 *reinterpret_cast<float2*>(sSt + row_b * LDT + cc) = make_float2(st[nt][2], st[nt][3]);
-                *reinterpret_cast<float2*>(ck + row_a * DP + col0 + cc) = make_float2(st[nt][0], st[nt][1]);
-                *reinterpret_cast<float2*>(ck + row_b * DP + col0 + cc) = make_float2(st[nt][2], st[nt][3]);
+            }
+            if (p.ckb != nullptr) {
+                bf16* ck = p.ckb + gi * (long long)(DP * DP);
+#pragma unroll
+                for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
+                    int cc = nt * 8 + 2 * t;
+                    *reinterpret_cast<__nv_bfloat162*>(ck + row_a * DP + col0 + cc) =
+                        __floats2bfloat162_rn(st[nt][0], st[nt][1]);
+                    *reinterpret_cast<__nv_bfloat162*>(ck + row_b * DP + col0 + cc) =
+                        __floats2bfloat162_rn(st[nt][2], st[nt][3]);
+                }
+            } else {
+                float* ck = state_ptr(p.ck, gi);
+#pragma unroll
+                for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
+                    int cc = nt * 8 + 2 * t;
+                    *reinterpret_cast<float2*>(ck + row_a * DP + col0 + cc) = make_float2(st[nt][0], st[nt][1]);
+                    *reinterpret_cast<float2*>(ck + row_b * DP + col0 + cc) = make_float2(st[nt][2], st[nt][3]);
+                }
             }
         }
-        cp_async_wait<1>();
+        cp_async_wait<1>();  // everything but the newest group: this step's panels have landed
         __syncthreads();
-        // X = P + Q St : warp tile 16 rows x 32 columns
+        // X = P + Q St : warp tile 16 rows x NS/2 columns
         {
-            float acc[4][4];
-            acc_zero<4>(acc);
-            const int r0 = (warp & 3) * 16, n0 = (warp >> 2) * 32;
-            warp_mma<4>(acc, r0, n0, 0, DP, [&](int i, int k) { return sQ[i * LDP + k]; },
-                        [&](int k, int n) { return sSt[k * LDT + n]; });
-            float* xg = panel_ptr(p.X, gi);
-            warp_epi<4>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
-                float2 pv = *reinterpret_cast<const float2*>(sP + i * LDT + j);
+            float acc[SCAN_G1][4];
+            acc_zero<SCAN_G1>(acc);
+            const int r0 = (warp & 3) * 16, n0 = (warp >> 2) * (SCAN_NS / 2);
+            warp_mma<SCAN_G1>(acc, r0, n0, 0, DP, [&](int i, int k) { return bQ[i * LDP + k]; },
+                              [&](int k, int n) { return sSt[k * LDT + n]; });
+            float* xg = p.X != nullptr ? panel_ptr(p.X, gi) : nullptr;
+            bf16* xb = p.Xb != nullptr ? bpanel_ptr(p.Xb, gi) : nullptr;
+            warp_epi<SCAN_G1>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
+                float2 pv = *reinterpret_cast<const float2*>(bP + i * LDT + j);
                 float2 xv = make_float2(pv.x + v0, pv.y + v1);
                 *reinterpret_cast<float2*>(sX + i * LDT + j) = xv;
-                *reinterpret_cast<float2*>(xg + i * DP + col0 + j) = xv;
+                if (xb != nullptr)
+                    *reinterpret_cast<__nv_bfloat162*>(xb + i * DP + col0 + j) = __floats2bfloat162_rn(xv.x, xv.y);
+                else
+                    *reinterpret_cast<float2*>(xg + i * DP + col0 + j) = xv;
             });
         }
         __syncthreads();
-        if (step + 1 < p.NC) issue_a(step + 1);
-        cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
-        // St = lam St + R^T X (+ R2^T X2) : warp tile 16 state rows x NS columns
+        // St = lam St + R^T X : warp tile 16 state rows x NS columns
         {
 #pragma unroll
             for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
@@ -162,15 +177,11 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan(ScanParams p) {
                 st[nt][2] *= lb;
                 st[nt][3] *= lb;
             }
-            warp_mma<SCAN_NS / 8>(st, warp * 16, 0, 0, CL, [&](int c, int j) { return sR[j * LDP + c]; },
+            warp_mma<SCAN_NS / 8>(st, warp * 16, 0, 0, CL, [&](int c, int j) { return bR[j * LDP + c]; },
                                   [&](int j, int n) { return sX[j * LDT + n]; });
-            if (has2)
-                warp_mma<SCAN_NS / 8>(st, warp * 16, 0, 0, CL, [&](int c, int j) { return sR2[j * LDP + c]; },
-                                      [&](int j, int n) { return sX2[j * LDT + n]; });
         }
-        __syncthreads();
-        if (step + 1 < p.NC) issue_b(step + 1);
-        cp_async_commit();
+        __syncthreads();  // this step's ring slot and sX are free again
+        issue(step + 2);
     }
     cp_async_wait<0>();
 
@@ -200,8 +211,6 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan(ScanParams p) {
 // tolerances admit BF16 contraction operands; the carried state itself stays
 // FP32 in registers).  Panels P, Q, R, R2, X2 and the outputs X and the state
 // checkpoints are BF16 in global memory.
-#include "sd_bf16.cuh"
-
 namespace sd {
 
 constexpr int LDTB = SCAN_NS + 8;  // pitch of [*][NS] BF16 shared buffers
@@ -233,17 +242,17 @@ __device__ __forceinline__ void async_bslice(bf16* sm, const bf16* g, int col0) 
     }
 }
 
-constexpr size_t SCAN_B_SMEM_BYTES = (size_t(3) * CL * LDB + size_t(3) * CL * LDTB + size_t(DP) * LDTB) * 2;
+constexpr size_t SCAN_B_SMEM_BYTES = (size_t(6) * CL * LDB + size_t(5) * CL * LDTB + size_t(DP) * LDTB) * 2;
 
 __global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan_b(ScanParamsB p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
-    bf16* sR = sQ + CL * LDB;
-    bf16* sR2 = sR + CL * LDB;
-    bf16* sP = sR2 + CL * LDB;   // [CL][LDTB]
-    bf16* sX = sP + CL * LDTB;
-    bf16* sX2 = sX + CL * LDTB;
-    bf16* sSt = sX2 + CL * LDTB;  // [DP][LDTB]
+    bf16* sQ = reinterpret_cast<bf16*>(smem_raw);  // [2][CL][LDB]
+    bf16* sR = sQ + 2 * CL * LDB;                  // [2][CL][LDB]
+    bf16* sR2 = sR + 2 * CL * LDB;                 // [2][CL][LDB]
+    bf16* sP = sR2 + 2 * CL * LDB;                 // [2][CL][LDTB]
+    bf16* sX2 = sP + 2 * CL * LDTB;                // [2][CL][LDTB]
+    bf16* sX = sX2 + 2 * CL * LDTB;                // [CL][LDTB]
+    bf16* sSt = sX + CL * LDTB;                    // [DP][LDTB]
 
     const int col0 = blockIdx.x * SCAN_NS;
     const int s = blockIdx.y;
@@ -269,27 +278,30 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan_b(ScanParamsB p)
     }
 
     auto chunk_at = [&](int step) { return base + (p.reverse ? (p.NC - 1 - step) : step); };
-    auto issue_a = [&](int step) {
-        long long gi = chunk_at(step);
-        async_bpanel_scan(sQ, bpanel_ptr(p.Q, gi));
-        async_bslice(sP, bpanel_ptr(p.P, gi), col0);
-    };
-    auto issue_b = [&](int step) {
-        long long gi = chunk_at(step);
-        async_bpanel_scan(sR, bpanel_ptr(p.R, gi));
-        if (has2) {
-            async_bpanel_scan(sR2, bpanel_ptr(p.R2, gi));
-            async_bslice(sX2, bpanel_ptr(p.X2, gi), col0);
+    auto issue = [&](int step) {
+        if (step < p.NC) {
+            const long long gi = chunk_at(step);
+            const int b = step & 1;
+            async_bpanel_scan(sQ + b * CL * LDB, bpanel_ptr(p.Q, gi));
+            async_bslice(sP + b * CL * LDTB, bpanel_ptr(p.P, gi), col0);
+            async_bpanel_scan(sR + b * CL * LDB, bpanel_ptr(p.R, gi));
+            if (has2) {
+                async_bpanel_scan(sR2 + b * CL * LDB, bpanel_ptr(p.R2, gi));
+                async_bslice(sX2 + b * CL * LDTB, bpanel_ptr(p.X2, gi), col0);
+            }
         }
+        cp_commit();
     };
-
-    issue_a(0);
-    cp_commit();
-    issue_b(0);
-    cp_commit();
+    issue(0);
+    issue(1);
 
     for (int step = 0; step < p.NC; ++step) {
         const long long gi = chunk_at(step);
+        const bf16* bQ = sQ + (step & 1) * CL * LDB;
+        const bf16* bR = sR + (step & 1) * CL * LDB;
+        const bf16* bR2 = sR2 + (step & 1) * CL * LDB;
+        const bf16* bP = sP + (step & 1) * CL * LDTB;
+        const bf16* bX2 = sX2 + (step & 1) * CL * LDTB;
         const float* lam = p.lam + gi * DP;
         const float la = lam[row_a], lb = lam[row_b];
         {
@@ -308,22 +320,18 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan_b(ScanParamsB p)
         cp_wait<1>();
         __syncthreads();
         {
-            float acc[4][4];
-            acc_zero<4>(acc);
-            const int r0 = (warp & 3) * 16, n0 = (warp >> 2) * 32;
-            warp_mma_bf16<4, false, false>(acc, sQ, LDB, sSt, LDTB, r0, n0, 0, DP);
+            float acc[SCAN_G1][4];
+            acc_zero<SCAN_G1>(acc);
+            const int r0 = (warp & 3) * 16, n0 = (warp >> 2) * (SCAN_NS / 2);
+            warp_mma_bf16<SCAN_G1, false, false>(acc, bQ, LDB, sSt, LDTB, r0, n0, 0, DP);
             bf16* xg = bpanel_ptr(p.X, gi);
-            warp_epi<4>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
-                float2 pv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sP + i * LDTB + j));
+            warp_epi<SCAN_G1>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
+                float2 pv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(bP + i * LDTB + j));
                 __nv_bfloat162 xv = __floats2bfloat162_rn(pv.x + v0, pv.y + v1);
                 *reinterpret_cast<__nv_bfloat162*>(sX + i * LDTB + j) = xv;
                 *reinterpret_cast<__nv_bfloat162*>(xg + i * DP + col0 + j) = xv;
             });
         }
-        __syncthreads();
-        if (step + 1 < p.NC) issue_a(step + 1);
-        cp_commit();
-        cp_wait<1>();
         __syncthreads();
         {
 #pragma unroll
@@ -333,12 +341,11 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan_b(ScanParamsB p)
                 st[nt][2] *= lb;
                 st[nt][3] *= lb;
             }
-            warp_mma_bf16<SCAN_NS / 8, true, false>(st, sR, LDB, sX, LDTB, warp * 16, 0, 0, CL);
-            if (has2) warp_mma_bf16<SCAN_NS / 8, true, false>(st, sR2, LDB, sX2, LDTB, warp * 16, 0, 0, CL);
+            warp_mma_bf16<SCAN_NS / 8, true, false>(st, bR, LDB, sX, LDTB, warp * 16, 0, 0, CL);
+            if (has2) warp_mma_bf16<SCAN_NS / 8, true, false>(st, bR2, LDB, bX2, LDTB, warp * 16, 0, 0, CL);
         }
         __syncthreads();
-        if (step + 1 < p.NC) issue_b(step + 1);
-        cp_commit();
+        issue(step + 2);
     }
     cp_wait<0>();
 
