@@ -150,6 +150,13 @@ int sd_backward_launches(const sd_shape *shape);
 int sd_profile_step(const sd_forward_args *fwd, const sd_backward_args *bwd, void *stream,
                     float *ms, int capacity, int *count);
 const char *sd_launch_name(int index);
+/*
+ * Diagnostic (no upstream counterpart): when `device_buffer` (at least
+ * 16*16 int64) is not NULL, one CTA of every chunk kernel records the SM
+ * clock at each of its phase boundaries into slot [launch index][phase];
+ * NULL switches the recording off.  Process-wide, not thread safe.
+ */
+void sd_debug_timeline(void *device_buffer);
 
 /*
  * Introspection for tests: offset and size of a named intermediate panel

@@ -106,7 +106,7 @@ EXPORTS = (
     "sd_saved_bytes", "sd_forward_scratch_bytes", "sd_backward_scratch_bytes",
     "sd_forward", "sd_backward", "sd_decode_step", "sd_forward_launches",
     "sd_backward_launches", "sd_panel_info", "sd_status_string", "sd_version",
-    "sd_chunk_tokens", "sd_profile_step", "sd_launch_name", "sd_forward_static", "sd_panel_kind",
+    "sd_chunk_tokens", "sd_profile_step", "sd_launch_name", "sd_forward_static", "sd_panel_kind", "sd_debug_timeline",
 )
 
 _lib = None
@@ -141,6 +141,8 @@ def load() -> ctypes.CDLL:
     lib.sd_panel_info.restype = ctypes.c_int
     lib.sd_panel_info.argtypes = [sp, ctypes.c_int, ctypes.c_char_p,
                                   ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)]
+    lib.sd_debug_timeline.restype = None
+    lib.sd_debug_timeline.argtypes = [ctypes.c_void_p]
     lib.sd_panel_kind.restype = ctypes.c_int
     lib.sd_panel_kind.argtypes = [sp, ctypes.c_int, ctypes.c_char_p]
     lib.sd_status_string.restype = ctypes.c_char_p

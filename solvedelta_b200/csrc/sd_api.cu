@@ -104,11 +104,30 @@ Operand make_operand(const sd_operand& o, int elem_bytes) {
     return r;
 }
 
+long long* g_dbg = nullptr;  // set by sd_debug_timeline (diagnostic)
+
+// True when every strided operand admits 16-byte vector access and the head
+// widths are multiples of eight: the kernels then use their branch-free loaders.
+bool all_fast(const Operand* ops, int n, const sd_shape& s) {
+    if ((s.r & 7) || (s.V & 7)) return false;
+    for (int i = 0; i < n; ++i)
+        if (!ops[i].vec) return false;
+    return true;
+}
+
 Geometry make_geometry(const sd_shape& s) {
     Geometry g;
     g.B = s.B; g.T = s.T; g.H = s.H; g.r = s.r; g.V = s.V;
     g.NC = (s.T + CL - 1) / CL;
+    g.dbg = nullptr;
+    g.dbg_block = 0;
     return g;
+}
+
+// slot k of the diagnostic buffer belongs to the k-th launch of a step
+void set_dbg(Geometry& g, int launch_index, int chunks) {
+    g.dbg = g_dbg ? g_dbg + 16 * launch_index : nullptr;
+    g.dbg_block = chunks > 300 ? chunks / 2 + 3 : 0;
 }
 
 template <class K>
@@ -124,17 +143,26 @@ cudaError_t configure_kernels() {
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64 && done[dev]) return cudaSuccess;
-    if ((e = allow_smem(k_prep_fwd, PREP_FWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_primal_fwd, PRIMAL_FWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_exterior_prep_fwd, EXT_PREP_FWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_output_fwd, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_prep_fwd<true>, PREP_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_prep_fwd<false>, PREP_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_primal_fwd<true>, PRIMAL_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_primal_fwd<false>, PRIMAL_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_prep_fwd<true>, EXT_PREP_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_prep_fwd<false>, EXT_PREP_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_output_fwd<true>, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_output_fwd<false>, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_state_scan, SCAN_SMEM_BYTES)) != cudaSuccess) return e;
     if ((e = allow_smem(k_state_scan_b, SCAN_B_SMEM_BYTES)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_exterior_prep_bwd, EXT_PREP_BWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_exterior_pair_bwd, EXT_PAIR_BWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_primal_bwd, PRIMAL_BWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_predictor_pair_bwd, PRED_PAIR_BWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_gate_closure_bwd, GATE_CLOSURE_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_prep_bwd<true>, EXT_PREP_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_prep_bwd<false>, EXT_PREP_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_pair_bwd<true>, EXT_PAIR_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_pair_bwd<false>, EXT_PAIR_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_primal_bwd<true>, PRIMAL_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_primal_bwd<false>, PRIMAL_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_predictor_pair_bwd<true>, PRED_PAIR_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_predictor_pair_bwd<false>, PRED_PAIR_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_gate_closure_bwd<true>, GATE_CLOSURE_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_gate_closure_bwd<false>, GATE_CLOSURE_SMEM)) != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) done[dev] = true;
     return cudaSuccess;
 }
@@ -264,8 +292,12 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
     const int chunks = (int)total_chunks(s);
     const int streams = s->B * s->H;
     const dim3 scan_grid(DP / SCAN_NS, streams);
+    const Operand fwd_ops[] = {p.u, p.h, p.q, p.k, p.v, p.er, p.wr, p.ld};
+    const bool fast = all_fast(fwd_ops, 8, *s);
 
-    k_prep_fwd<<<chunks, NTHREADS, PREP_FWD_SMEM, stream>>>(p);
+    set_dbg(p.g, 0, chunks);
+    if (fast) k_prep_fwd<true><<<chunks, NTHREADS, PREP_FWD_SMEM, stream>>>(p);
+    else k_prep_fwd<false><<<chunks, NTHREADS, PREP_FWD_SMEM, stream>>>(p);
     mark(stream);
     {
         ScanParams sp{};
@@ -276,9 +308,13 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
         k_state_scan<<<scan_grid, SCAN_THREADS, SCAN_SMEM_BYTES, stream>>>(sp);
     mark(stream);
     }
-    k_primal_fwd<<<chunks, NTHREADS, PRIMAL_FWD_SMEM, stream>>>(p);
+    set_dbg(p.g, 2, chunks);
+    if (fast) k_primal_fwd<true><<<chunks, NTHREADS, PRIMAL_FWD_SMEM, stream>>>(p);
+    else k_primal_fwd<false><<<chunks, NTHREADS, PRIMAL_FWD_SMEM, stream>>>(p);
     mark(stream);
-    k_exterior_prep_fwd<<<chunks, NTHREADS, EXT_PREP_FWD_SMEM, stream>>>(p);
+    set_dbg(p.g, 3, chunks);
+    if (fast) k_exterior_prep_fwd<true><<<chunks, NTHREADS, EXT_PREP_FWD_SMEM, stream>>>(p);
+    else k_exterior_prep_fwd<false><<<chunks, NTHREADS, EXT_PREP_FWD_SMEM, stream>>>(p);
     mark(stream);
     {
         ScanParams sp{};
@@ -289,7 +325,9 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
         k_state_scan<<<scan_grid, SCAN_THREADS, SCAN_SMEM_BYTES, stream>>>(sp);
     mark(stream);
     }
-    k_output_fwd<<<chunks, NTHREADS, OUTPUT_FWD_SMEM, stream>>>(p);
+    set_dbg(p.g, 5, chunks);
+    if (fast) k_output_fwd<true><<<chunks, NTHREADS, OUTPUT_FWD_SMEM, stream>>>(p);
+    else k_output_fwd<false><<<chunks, NTHREADS, OUTPUT_FWD_SMEM, stream>>>(p);
     mark(stream);
     return launch_status();
 }
@@ -346,8 +384,12 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
     const int chunks = (int)total_chunks(s);
     const int streams = s->B * s->H;
     const dim3 scan_grid(DP / SCAN_NS, streams);
+    const Operand bwd_ops[] = {p.u, p.h, p.q, p.k, p.v, p.er, p.wr, p.ld, p.dy};
+    const bool fast = all_fast(bwd_ops, 9, *s);
 
-    k_exterior_prep_bwd<<<chunks, NTHREADS, EXT_PREP_BWD_SMEM, stream>>>(p);
+    set_dbg(p.g, 6, chunks);
+    if (fast) k_exterior_prep_bwd<true><<<chunks, NTHREADS, EXT_PREP_BWD_SMEM, stream>>>(p);
+    else k_exterior_prep_bwd<false><<<chunks, NTHREADS, EXT_PREP_BWD_SMEM, stream>>>(p);
     mark(stream);
     {
         ScanParamsB sp{};
@@ -358,11 +400,17 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
         k_state_scan_b<<<scan_grid, SCAN_THREADS, SCAN_B_SMEM_BYTES, stream>>>(sp);
     mark(stream);
     }
-    k_exterior_pair_bwd<<<chunks, NTHREADS, EXT_PAIR_BWD_SMEM, stream>>>(p);
+    set_dbg(p.g, 8, chunks);
+    if (fast) k_exterior_pair_bwd<true><<<chunks, NTHREADS, EXT_PAIR_BWD_SMEM, stream>>>(p);
+    else k_exterior_pair_bwd<false><<<chunks, NTHREADS, EXT_PAIR_BWD_SMEM, stream>>>(p);
     mark(stream);
-    k_sources_bwd<<<chunks, NTHREADS, 0, stream>>>(p);
+    set_dbg(p.g, 9, chunks);
+    if (fast) k_sources_bwd<true><<<chunks, NTHREADS, 0, stream>>>(p);
+    else k_sources_bwd<false><<<chunks, NTHREADS, 0, stream>>>(p);
     mark(stream);
-    k_primal_bwd<<<chunks, NTHREADS, PRIMAL_BWD_SMEM, stream>>>(p);
+    set_dbg(p.g, 10, chunks);
+    if (fast) k_primal_bwd<true><<<chunks, NTHREADS, PRIMAL_BWD_SMEM, stream>>>(p);
+    else k_primal_bwd<false><<<chunks, NTHREADS, PRIMAL_BWD_SMEM, stream>>>(p);
     mark(stream);
     {
         ScanParamsB sp{};
@@ -373,12 +421,18 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
         k_state_scan_b<<<scan_grid, SCAN_THREADS, SCAN_B_SMEM_BYTES, stream>>>(sp);
     mark(stream);
     }
-    k_predictor_pair_bwd<<<chunks, NTHREADS, PRED_PAIR_BWD_SMEM, stream>>>(p);
+    set_dbg(p.g, 12, chunks);
+    if (fast) k_predictor_pair_bwd<true><<<chunks, NTHREADS, PRED_PAIR_BWD_SMEM, stream>>>(p);
+    else k_predictor_pair_bwd<false><<<chunks, NTHREADS, PRED_PAIR_BWD_SMEM, stream>>>(p);
     mark(stream);
-    k_gate_closure_bwd<<<chunks, NTHREADS, GATE_CLOSURE_SMEM, stream>>>(p);
+    set_dbg(p.g, 13, chunks);
+    if (fast) k_gate_closure_bwd<true><<<chunks, NTHREADS, GATE_CLOSURE_SMEM, stream>>>(p);
+    else k_gate_closure_bwd<false><<<chunks, NTHREADS, GATE_CLOSURE_SMEM, stream>>>(p);
     mark(stream);
     return launch_status();
 }
+
+void sd_debug_timeline(void* device_buffer) { g_dbg = reinterpret_cast<long long*>(device_buffer); }
 
 const char* sd_launch_name(int index) {
     const int n = (int)(sizeof(kLaunchNames) / sizeof(kLaunchNames[0]));

@@ -102,7 +102,10 @@ __device__ __forceinline__ void epi_store_bpanel(float (&acc)[NTW][4], int r0, i
 // so that the reverse S scan is dR = P' + Q' dS.
 constexpr size_t EXT_PREP_BWD_SMEM = 5 * BSLOT_BYTES + BMAT_BYTES + MAT_BYTES;
 
+template <bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) {
+    int ph = 0;
+    SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* b_xg = reinterpret_cast<bf16*>(smem_raw);
     bf16* b_ag = b_xg + BSLOT_ELEMS;
@@ -128,14 +131,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) 
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
             const int i = lr + ROWS_PER_PASS * pp;
             float uh[8], kh[8], qh[8], dl[8], d[8], er[8], dy[8], G[8], se[8];
-            load8_norm(p.u, ch, i, c0, r, uh);
-            load8_norm(p.k, ch, i, c0, r, kh);
-            load8_norm(p.q, ch, i, c0, r, qh);
+            load8_norm<FAST>(p.u, ch, i, c0, r, uh);
+            load8_norm<FAST>(p.k, ch, i, c0, r, kh);
+            load8_norm<FAST>(p.q, ch, i, c0, r, qh);
             load8_panel(gDelta, i, c0, dl);
             load8_panel(gd, i, c0, d);
             load8_panel(gG, i, c0, G);
-            load8_bf16(row_bf16(p.er, ch, i), c0, r, p.er.vec, i < ch.nvalid, er);
-            load8_bf16(row_bf16(p.dy, ch, i), c0, V, p.dy.vec, i < ch.nvalid, dy);
+            load8_bf16<FAST>(row_bf16(p.er, ch, i), c0, r, p.er.vec, i < ch.nvalid, er);
+            load8_bf16<FAST>(row_bf16(p.dy, ch, i), c0, V, p.dy.vec, i < ch.nvalid, dy);
 #pragma unroll
             for (int e = 0; e < 8; ++e) se[e] = sigmoidf_(er[e]);
             Sources src;
@@ -161,6 +164,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) 
         }
     }
     __syncthreads();
+    SD_PHASE(p.g, ph);
     {
         float a1[NT64][4], a2[NT64][4];
         acc_zero<NT64>(a1);
@@ -178,21 +182,26 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) 
         });
     }
     __syncthreads();
+    SD_PHASE(p.g, ph);
     {
         float acc[NT128][4];
         acc_zero<NT128>(acc);
         const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
         warp_mma_bf16<NT128, true, false>(acc, b_aqd, LDM, b_dy, LDB, r0, n0, r0, CL);
         __syncthreads();
+    SD_PHASE(p.g, ph);
         warp_epi<NT128>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
             *reinterpret_cast<__nv_bfloat162*>(b_dy + i * LDB + j) = __floats2bfloat162_rn(v0, v1);
         });
     }
     __syncthreads();
+    SD_PHASE(p.g, ph);
     trisolve_upper_b(f_aedT, -1.f, b_dy, b_dt);
     __syncthreads();
+    SD_PHASE(p.g, ph);
     s2g_bpanel(bpanel_ptr(p.Pp, ch.gi), b_dy);
     s2g_bpanel(bpanel_ptr(p.Qp, ch.gi), b_dt);
+    SD_PHASE(p.g, ph);
 }
 
 // ---------------------------------------------------------------------------
@@ -205,7 +214,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) 
 // FP32 panels kept by forward are converted.
 constexpr size_t EXT_PAIR_BWD_SMEM = 6 * BSLOT_BYTES + 2 * BSTATE_BYTES + 2 * BMAT_BYTES;
 
+template <bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) {
+    int ph = 0;
+    SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* b_dy = reinterpret_cast<bf16*>(smem_raw);
     bf16* b_zt = b_dy + BSLOT_ELEMS;
@@ -233,6 +245,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
     cp_commit();
     cp_wait<3>();
     __syncthreads();
+    SD_PHASE(p.g, ph);
     {
         float a1[NT64][4], a2[NT64][4];
         acc_zero<NT64>(a1);
@@ -251,6 +264,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
     }
     cp_wait<2>();
     __syncthreads();
+    SD_PHASE(p.g, ph);
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
     {
         float a1[NT128][4], a2[NT128][4];
@@ -265,6 +279,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
     }
     cp_wait<1>();
     __syncthreads();
+    SD_PHASE(p.g, ph);
     {
         float acc[NT128][4];
         acc_zero<NT128>(acc);
@@ -274,6 +289,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
     }
     cp_wait<0>();
     __syncthreads();
+    SD_PHASE(p.g, ph);
     {
         float acc[NT128][4];
         acc_zero<NT128>(acc);
@@ -295,13 +311,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
         acc += __shfl_xor_sync(0xffffffffu, acc, 2);
         if (qt == 0) p.SdS[ch.gi * DP + c] = acc;
     }
+    SD_PHASE(p.g, ph);
 }
 
 // ---------------------------------------------------------------------------
 // Per-token reverse of the sources and of the gate factors of the exterior.
 // Writes the final gradients of q, values, erase_raw, write_raw and the
 // partial cotangents the predictor reverse still has to complete.
+template <bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_sources_bwd(BwdParams p) {
+    int ph = 0;
+    SD_PHASE(p.g, ph);
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r, V = p.g.V;
     const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
@@ -319,13 +339,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_sources_bwd(BwdParams p) {
     for (int pp = 0; pp < ROW_PASSES; ++pp) {
         const int i = lr + ROWS_PER_PASS * pp;
         float uh[8], kh[8], qh[8], dl[8], d[8], er[8], G[8], se[8];
-        load8_norm(p.u, ch, i, c0, r, uh);
-        load8_norm(p.k, ch, i, c0, r, kh);
-        const float rstd_q = load8_norm(p.q, ch, i, c0, r, qh);
+        load8_norm<FAST>(p.u, ch, i, c0, r, uh);
+        load8_norm<FAST>(p.k, ch, i, c0, r, kh);
+        const float rstd_q = load8_norm<FAST>(p.q, ch, i, c0, r, qh);
         load8_panel(gDelta, i, c0, dl);
         load8_panel(gd, i, c0, d);
         load8_panel(gG, i, c0, G);
-        load8_bf16(row_bf16(p.er, ch, i), c0, r, p.er.vec, i < ch.nvalid, er);
+        load8_bf16<FAST>(row_bf16(p.er, ch, i), c0, r, p.er.vec, i < ch.nvalid, er);
 #pragma unroll
         for (int e = 0; e < 8; ++e) se[e] = sigmoidf_(er[e]);
         Sources src;
@@ -375,8 +395,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_sources_bwd(BwdParams p) {
         }
         float dq[8];
         norm_vjp8(dqh, qh, rstd_q, dq);
-        store8_bf16(p.dq, p.g, ch, i, c0, r, dq);
-        store8_bf16(p.der, p.g, ch, i, c0, r, der);
+        store8_bf16<FAST>(p.dq, p.g, ch, i, c0, r, dq);
+        store8_bf16<FAST>(p.der, p.g, ch, i, c0, r, der);
         store8_bpanel(bpanel_ptr(p.duPart, ch.gi), i, c0, duh);
         store8_bpanel(bpanel_ptr(p.dkPart, ch.gi), i, c0, dkp);
         store8_bpanel(bpanel_ptr(p.dGPart, ch.gi), i, c0, dG);
@@ -385,8 +405,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_sources_bwd(BwdParams p) {
         store8_bpanel(bpanel_ptr(p.Xext, ch.gi), i, c0, xext);
         // value side: dv = sigmoid(write) dR, d write_raw = dR v sigmoid'(write)
         float wr[8], v[8], dr[8], dv[8], dwr[8];
-        load8_bf16(row_bf16(p.wr, ch, i), c0, V, p.wr.vec, i < ch.nvalid, wr);
-        load8_bf16(row_bf16(p.v, ch, i), c0, V, p.v.vec, i < ch.nvalid, v);
+        load8_bf16<FAST>(row_bf16(p.wr, ch, i), c0, V, p.wr.vec, i < ch.nvalid, wr);
+        load8_bf16<FAST>(row_bf16(p.v, ch, i), c0, V, p.v.vec, i < ch.nvalid, v);
         load8_bpanel(gdR, i, c0, dr);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
@@ -394,9 +414,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_sources_bwd(BwdParams p) {
             dv[e] = sw * dr[e];
             dwr[e] = dr[e] * v[e] * sw * (1.f - sw);
         }
-        store8_bf16(p.dv, p.g, ch, i, c0, V, dv);
-        store8_bf16(p.dwr, p.g, ch, i, c0, V, dwr);
+        store8_bf16<FAST>(p.dv, p.g, ch, i, c0, V, dv);
+        store8_bf16<FAST>(p.dwr, p.g, ch, i, c0, V, dwr);
     }
+    SD_PHASE(p.g, ph);
 }
 
 // ---------------------------------------------------------------------------
@@ -409,7 +430,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_sources_bwd(BwdParams p) {
 constexpr size_t PRIMAL_BWD_SMEM =
     6 * BSLOT_BYTES + BSTATE_BYTES + 2 * BMAT_BYTES + MAT_BYTES + (2 * CL + 4 * CL) * sizeof(float);
 
+template <bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
+    int ph = 0;
+    SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* b_un = reinterpret_cast<bf16*>(smem_raw);
     bf16* b_ut = b_un + BSLOT_ELEMS;
@@ -442,15 +466,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
             const int i = lr + ROWS_PER_PASS * pp;
             float uh[8], kh[8], G[8], E[8], dl[8];
-            load8_norm(p.u, ch, i, c0, r, uh);
-            const float rk = load8_norm(p.k, ch, i, c0, r, kh);
+            load8_norm<FAST>(p.u, ch, i, c0, r, uh);
+            const float rk = load8_norm<FAST>(p.k, ch, i, c0, r, kh);
             load8_panel(gG, i, c0, G);
-            if (i > 0) {
-                load8_panel(gG, i - 1, c0, E);
-            } else {
+            load8_panel(gG, i > 0 ? i - 1 : 0, c0, E);  // E = G of the previous row (0 for the first)
 #pragma unroll
-                for (int e = 0; e < 8; ++e) E[e] = 0.f;
-            }
+            for (int e = 0; e < 8; ++e) E[e] = i > 0 ? E[e] : 0.f;
             load8_panel(gDelta, i, c0, dl);
             const float gm = (i < ch.nvalid) ? *row_f32(p.gam, ch, i) : 0.f;
             float un[8], ut[8], ub[8], rn[8];
@@ -474,6 +495,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     g2s_state_f32_to_bf16(b_Ct, state_ptr(p.CtCk, ch.gi));
     cp_wait<0>();
     __syncthreads();
+    SD_PHASE(p.g, ph);
     {
         float a1[NT64][4], a2[NT64][4], a3[NT64][4];
         acc_zero<NT64>(a1);
@@ -498,6 +520,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
         });
     }
     __syncthreads();
+    SD_PHASE(p.g, ph);
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
     float accd[NT128][4];  // dAqk^T K^  (added to dDelta_src below)
     acc_zero<NT128>(accd);
@@ -547,6 +570,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
             s_dot[ib * 4 + nq] = dotb;
         }
         __syncthreads();
+    SD_PHASE(p.g, ph);
         dota = (s_dot[ia * 4] + s_dot[ia * 4 + 1]) + (s_dot[ia * 4 + 2] + s_dot[ia * 4 + 3]);
         dotb = (s_dot[ib * 4] + s_dot[ib * 4 + 1]) + (s_dot[ib * 4 + 2] + s_dot[ib * 4 + 3]);
         __nv_bfloat16* dk = reinterpret_cast<__nv_bfloat16*>(p.dk);
@@ -568,6 +592,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     }
     // every contraction that reads b_dl (Delta) is done: reuse it for dDelta_loc
     __syncthreads();
+    SD_PHASE(p.g, ph);
     {
         const bf16* gdd = bpanel_ptr(p.dDelta, ch.gi);
         warp_epi<NT128>(accd, r0, n0, [&](int i, int j, float v0, float v1) {
@@ -576,10 +601,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
         });
     }
     __syncthreads();
+    SD_PHASE(p.g, ph);
     trisolve_upper_b(f_lmT, 1.f, b_dl, b_ub);
     __syncthreads();
+    SD_PHASE(p.g, ph);
     s2g_bpanel(bpanel_ptr(p.Ppp, ch.gi), b_dl);
     s2g_bpanel(bpanel_ptr(p.Qpp, ch.gi), b_ub);
+    SD_PHASE(p.g, ph);
 }
 
 // ---------------------------------------------------------------------------
@@ -591,7 +619,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
 constexpr size_t PRED_PAIR_BWD_SMEM =
     4 * BSLOT_BYTES + 2 * BSTATE_BYTES + 2 * BMAT_BYTES + (CL + 4 * CL) * sizeof(float);
 
+template <bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p) {
+    int ph = 0;
+    SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* b_ut = reinterpret_cast<bf16*>(smem_raw);
     bf16* b_un = b_ut + BSLOT_ELEMS;
@@ -618,14 +649,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p)
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
             const int i = lr + ROWS_PER_PASS * pp;
             float uh[8], G[8], E[8], dl[8];
-            load8_norm(p.u, ch, i, c0, r, uh);
+            load8_norm<FAST>(p.u, ch, i, c0, r, uh);
             load8_panel(gG, i, c0, G);
-            if (i > 0) {
-                load8_panel(gG, i - 1, c0, E);
-            } else {
+            load8_panel(gG, i > 0 ? i - 1 : 0, c0, E);  // E = G of the previous row (0 for the first)
 #pragma unroll
-                for (int e = 0; e < 8; ++e) E[e] = 0.f;
-            }
+            for (int e = 0; e < 8; ++e) E[e] = i > 0 ? E[e] : 0.f;
             load8_panel(gDelta, i, c0, dl);
             float un[8], ut[8];
 #pragma unroll
@@ -641,6 +669,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p)
     g2s_state_f32_to_bf16(b_Ct, state_ptr(p.CtCk, ch.gi));
     cp_wait<0>();
     __syncthreads();
+    SD_PHASE(p.g, ph);
     {
         float a1[NT64][4], a2[NT64][4];
         acc_zero<NT64>(a1);
@@ -659,6 +688,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p)
         });
     }
     __syncthreads();
+    SD_PHASE(p.g, ph);
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
     {   // dUbar[j][c] = sum_a Delta[j][a] dCt[c][a]
         float acc[NT128][4];
@@ -720,6 +750,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p)
         }
     }
     __syncthreads();
+    SD_PHASE(p.g, ph);
     if (threadIdx.x < CL && threadIdx.x < ch.nvalid) {
         const int i = threadIdx.x;
         p.dgam[((long long)ch.b * p.g.T + ch.t0 + i) * p.g.H + ch.hh] =
@@ -740,6 +771,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p)
         acc += __shfl_xor_sync(0xffffffffu, acc, 2);
         if (qt == 0) p.CdC[ch.gi * DP + c] = acc;
     }
+    SD_PHASE(p.g, ph);
 }
 
 // ---------------------------------------------------------------------------
@@ -748,7 +780,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p)
 // Writes the final gradients of u, h and log_decay.
 constexpr size_t GATE_CLOSURE_SMEM = 3 * SLOT_BYTES;
 
+template <bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_gate_closure_bwd(BwdParams p) {
+    int ph = 0;
+    SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) float smem[];
     float* s_dG = smem;
     float* s_dE = s_dG + SLOT_FLOATS;
@@ -764,14 +799,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_gate_closure_bwd(BwdParams p) {
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
             const int i = lr + ROWS_PER_PASS * pp;
             float uh[8], G[8], E[8];
-            const float rstd_u = load8_norm(p.u, ch, i, c0, r, uh);
+            const float rstd_u = load8_norm<FAST>(p.u, ch, i, c0, r, uh);
             load8_panel(gG, i, c0, G);
-            if (i > 0) {
-                load8_panel(gG, i - 1, c0, E);
-            } else {
+            load8_panel(gG, i > 0 ? i - 1 : 0, c0, E);  // E = G of the previous row (0 for the first)
 #pragma unroll
-                for (int e = 0; e < 8; ++e) E[e] = 0.f;
-            }
+            for (int e = 0; e < 8; ++e) E[e] = i > 0 ? E[e] : 0.f;
             float dup[8], tpre[8], dub[8], dut[8], ti[8], tj[8], dgp[8], xext[8], drr[8];
             load8_bpanel(bpanel_ptr(p.duPart, ch.gi), i, c0, dup);
             load8_bpanel(bpanel_ptr(p.Tpre, ch.gi), i, c0, tpre);
@@ -800,11 +832,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_gate_closure_bwd(BwdParams p) {
             const float gm = (i < ch.nvalid) ? *row_f32(p.gam, ch, i) : 0.f;
 #pragma unroll
             for (int e = 0; e < 8; ++e) dh[e] = gm * drr[e];
-            store8_bf16(p.du, p.g, ch, i, c0, r, du);
-            store8_bf16(p.dh, p.g, ch, i, c0, r, dh);
+            store8_bf16<FAST>(p.du, p.g, ch, i, c0, r, du);
+            store8_bf16<FAST>(p.dh, p.g, ch, i, c0, r, dh);
         }
     }
     __syncthreads();
+    SD_PHASE(p.g, ph);
     if (threadIdx.x < DP && threadIdx.x < r) {
         const int c = threadIdx.x;
         float xs = 0.f;
@@ -817,6 +850,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_gate_closure_bwd(BwdParams p) {
                     run - s_dE[i * LDP + c];
         }
     }
+    SD_PHASE(p.g, ph);
 }
 
 }  // namespace sd

@@ -38,7 +38,18 @@ struct Operand {
 
 struct Geometry {
     int B, T, H, r, V, NC;  // NC = chunks per stream
+    long long* dbg;         // diagnostic phase clock stamps of one CTA (null = off)
+    int dbg_block;
 };
+
+// Diagnostic: thread 0 of one chosen CTA records the SM clock at a phase boundary.
+#define SD_PHASE(g, ph)                                                                   \
+    do {                                                                                  \
+        if ((g).dbg != nullptr && (int)blockIdx.x == (g).dbg_block && threadIdx.x == 0 && \
+            (ph) < 16)                                                                    \
+            (g).dbg[(ph)] = clock64();                                                    \
+        ++(ph);                                                                           \
+    } while (0)
 
 struct Chunk {
     int s, c, b, hh, t0, nvalid;
@@ -103,8 +114,24 @@ __device__ __forceinline__ const float* row_f32(const Operand& op, const Chunk& 
 }
 
 // Eight consecutive channels of a BF16 row; channels >= width read as zero.
+// FAST: every operand is 16-byte aligned and the widths are multiples of 8, so the
+// access is one predicated vector load with no control flow around it -- the
+// compiler can then keep many independent loads in flight.
+template <bool FAST>
 __device__ __forceinline__ void load8_bf16(const __nv_bfloat16* row, int c0, int width, int vec, bool valid,
                                            float (&x)[8]) {
+    if (FAST) {
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (valid && c0 < width) raw = *reinterpret_cast<const uint4*>(row + c0);
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float2 f = __bfloat1622float2(p[e]);
+            x[2 * e] = f.x;
+            x[2 * e + 1] = f.y;
+        }
+        return;
+    }
     if (!valid || c0 >= width) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) x[e] = 0.f;
@@ -125,7 +152,18 @@ __device__ __forceinline__ void load8_bf16(const __nv_bfloat16* row, int c0, int
     }
 }
 
+template <bool FAST>
 __device__ __forceinline__ void load8_f32(const float* row, int c0, int width, int vec, bool valid, float (&x)[8]) {
+    if (FAST) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+        if (valid && c0 < width) {
+            a = *reinterpret_cast<const float4*>(row + c0);
+            b = *reinterpret_cast<const float4*>(row + c0 + 4);
+        }
+        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+        x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+        return;
+    }
     if (!valid || c0 >= width) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) x[e] = 0.f;
@@ -143,8 +181,19 @@ __device__ __forceinline__ void load8_f32(const float* row, int c0, int width, i
 }
 
 // Contiguous outputs [B,T,H,width]: eight channels of one row.
+template <bool FAST>
 __device__ __forceinline__ void store8_bf16(void* base, const Geometry& g, const Chunk& ch, int i, int c0,
                                             int width, const float (&x)[8]) {
+    if (FAST) {
+        __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(base) +
+                             (((long long)ch.b * g.T + ch.t0 + i) * g.H + ch.hh) * (long long)width;
+        uint4 raw;
+        __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) p[e] = __floats2bfloat162_rn(x[2 * e], x[2 * e + 1]);
+        if (i < ch.nvalid && c0 < width) *reinterpret_cast<uint4*>(row + c0) = raw;
+        return;
+    }
     if (i >= ch.nvalid || c0 >= width) return;
     __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(base) +
                          (((long long)ch.b * g.T + ch.t0 + i) * g.H + ch.hh) * (long long)width;
@@ -328,6 +377,7 @@ __device__ __forceinline__ void chunk_cumsum(float* sG) {
 
 // Loads a BF16 operand chunk, L2-normalises every row and stores it as FP32.
 // rstd (may be null) receives 1/|x| per row.
+template <bool FAST>
 __device__ __forceinline__ void load_norm_panel(const Operand& op, const Chunk& ch, int width, float* sm,
                                                 float* rstd) {
     const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
@@ -335,7 +385,7 @@ __device__ __forceinline__ void load_norm_panel(const Operand& op, const Chunk& 
     for (int p = 0; p < ROW_PASSES; ++p) {
         int i = lr + ROWS_PER_PASS * p;
         float x[8];
-        load8_bf16(row_bf16(op, ch, i), c0, width, op.vec, i < ch.nvalid, x);
+        load8_bf16<FAST>(row_bf16(op, ch, i), c0, width, op.vec, i < ch.nvalid, x);
         float ss = 0.f;
 #pragma unroll
         for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
@@ -347,25 +397,27 @@ __device__ __forceinline__ void load_norm_panel(const Operand& op, const Chunk& 
     }
 }
 
+template <bool FAST>
 __device__ __forceinline__ void load_raw_panel(const Operand& op, const Chunk& ch, int width, float* sm) {
     const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
 #pragma unroll
     for (int p = 0; p < ROW_PASSES; ++p) {
         int i = lr + ROWS_PER_PASS * p;
         float x[8];
-        load8_bf16(row_bf16(op, ch, i), c0, width, op.vec, i < ch.nvalid, x);
+        load8_bf16<FAST>(row_bf16(op, ch, i), c0, width, op.vec, i < ch.nvalid, x);
 #pragma unroll
         for (int e = 0; e < 8; ++e) sm[i * LDP + c0 + e] = x[e];
     }
 }
 
+template <bool FAST>
 __device__ __forceinline__ void load_f32_panel(const Operand& op, const Chunk& ch, int width, float* sm) {
     const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
 #pragma unroll
     for (int p = 0; p < ROW_PASSES; ++p) {
         int i = lr + ROWS_PER_PASS * p;
         float x[8];
-        load8_f32(row_f32(op, ch, i), c0, width, op.vec, i < ch.nvalid, x);
+        load8_f32<FAST>(row_f32(op, ch, i), c0, width, op.vec, i < ch.nvalid, x);
 #pragma unroll
         for (int e = 0; e < 8; ++e) sm[i * LDP + c0 + e] = x[e];
     }

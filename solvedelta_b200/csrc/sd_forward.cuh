@@ -58,9 +58,10 @@ __device__ __forceinline__ void sources_fwd(const float (&uh)[8], const float (&
 }
 
 // Eight channels of one normalised BF16 row, in registers.
+template <bool FAST>
 __device__ __forceinline__ float load8_norm(const Operand& op, const Chunk& ch, int i, int c0, int width,
                                             float (&x)[8]) {
-    load8_bf16(row_bf16(op, ch, i), c0, width, op.vec, i < ch.nvalid, x);
+    load8_bf16<FAST>(row_bf16(op, ch, i), c0, width, op.vec, i < ch.nvalid, x);
     float ss = 0.f;
 #pragma unroll
     for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
@@ -98,7 +99,10 @@ __device__ __forceinline__ void store8_smem(float* sm, int i, int c0, const floa
 // so that the C scan is  Delta = Upd + Qc Ct.
 constexpr size_t PREP_FWD_SMEM = 5 * SLOT_BYTES + MAT_BYTES + CL * sizeof(float);
 
+template <bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
+    int ph = 0;
+    SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) float smem[];
     float* s_uh = smem;
     float* s_G = s_uh + SLOT_FLOATS;
@@ -110,13 +114,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r;
 
-    load_norm_panel(p.u, ch, r, s_uh, nullptr);
-    load_f32_panel(p.ld, ch, r, s_G);
-    load_raw_panel(p.h, ch, r, s_h);
+    load_norm_panel<FAST>(p.u, ch, r, s_uh, nullptr);
+    load_f32_panel<FAST>(p.ld, ch, r, s_G);
+    load_raw_panel<FAST>(p.h, ch, r, s_h);
     load_gamma(p.gam, ch, s_gam);
     __syncthreads();
+    SD_PHASE(p.g, ph);
     chunk_cumsum(s_G);
     __syncthreads();
+    SD_PHASE(p.g, ph);
     for (int idx = threadIdx.x; idx < CL * DP; idx += NTHREADS) {
         int i = idx >> 7, c = idx & (DP - 1);
         float G = s_G[i * LDP + c];
@@ -126,6 +132,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
         s_un[i * LDP + c] = uh * clamp_exp_neg(G);
     }
     __syncthreads();
+    SD_PHASE(p.g, ph);
     {
         float acc[NT64][4];
         acc_zero<NT64>(acc);
@@ -139,6 +146,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
         });
     }
     __syncthreads();
+    SD_PHASE(p.g, ph);
     for (int idx = threadIdx.x; idx < CL * DP; idx += NTHREADS) {
         int i = idx >> 7, c = idx & (DP - 1);
         float gm = s_gam[i];
@@ -146,8 +154,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
         s_ut[i * LDP + c] *= gm;
     }
     __syncthreads();
+    SD_PHASE(p.g, ph);
     trisolve<false>(s_lm, 1.f, s_h, s_ut);
     __syncthreads();
+    SD_PHASE(p.g, ph);
     float* gUpd = panel_ptr(p.Upd, ch.gi);
     float* gQc = panel_ptr(p.Qc, ch.gi);
     float* gUbar = panel_ptr(p.Ubar, ch.gi);
@@ -167,6 +177,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
                         uh.w * __expf(GL.w - G.w));
     }
     if (threadIdx.x < DP) p.Lam[ch.gi * DP + threadIdx.x] = __expf(s_G[(CL - 1) * LDP + threadIdx.x]);
+    SD_PHASE(p.g, ph);
 }
 
 // ---------------------------------------------------------------------------
@@ -187,7 +198,10 @@ __device__ __forceinline__ void async_state_cols_f32(float* sm, const float* st,
     }
 }
 
+template <bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
+    int ph = 0;
+    SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) float smem[];
     float* s_kh = smem;
     float* s_un = s_kh + SLOT_FLOATS;
@@ -208,10 +222,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
     cp_commit();
     async_state_cols_f32(s_st1, ct, 1);
     cp_commit();
-    load_norm_panel(p.k, ch, r, s_kh, nullptr);
-    load_norm_panel(p.u, ch, r, s_un, nullptr);
+    load_norm_panel<FAST>(p.k, ch, r, s_kh, nullptr);
+    load_norm_panel<FAST>(p.u, ch, r, s_un, nullptr);
     cp_wait<2>();
     __syncthreads();
+    SD_PHASE(p.g, ph);
     for (int idx = threadIdx.x; idx < CL * DP; idx += NTHREADS) {
         int i = idx >> 7, c = idx & (DP - 1);
         s_un[i * LDP + c] *= clamp_exp_neg(s_G[i * LDP + c]);
@@ -229,6 +244,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
     }
     cp_wait<1>();
     __syncthreads();
+    SD_PHASE(p.g, ph);
     float acc[NT128][4];
     acc_zero<NT128>(acc);
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
@@ -238,6 +254,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
                 [&](int k, int n) { return s_un[k * LDP + n]; });
     cp_wait<0>();
     __syncthreads();
+    SD_PHASE(p.g, ph);
     warp_mma<NT128>(acc, r0, n0, 0, CL, [&](int i, int k) { return s_kh[i * LDP + CL + k]; },
                 [&](int k, int n) { return s_st1[n * LDH + k]; });
     float* gd = panel_ptr(p.Dprim, ch.gi);
@@ -247,6 +264,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
         *reinterpret_cast<float2*>(gd + i * DP + j) =
             make_float2(kh.x + __expf(G.x) * v0, kh.y + __expf(G.y) * v1);
     });
+    SD_PHASE(p.g, ph);
 }
 
 // ---------------------------------------------------------------------------
@@ -254,7 +272,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
 // the solved panels Wd = (I-Aed)^-1 ag, Ud = (I-Aed)^-1 Z for the S scan.
 constexpr size_t EXT_PREP_FWD_SMEM = 4 * SLOT_BYTES + MAT_BYTES;
 
+template <bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) {
+    int ph = 0;
+    SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) float smem[];
     float* s_xg = smem;
     float* s_ag = s_xg + SLOT_FLOATS;
@@ -276,14 +297,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
             const int i = lr + ROWS_PER_PASS * pp;
             float uh[8], kh[8], qh[8], dl[8], d[8], er[8], wr[8], v[8], G[8], se[8];
-            load8_norm(p.u, ch, i, c0, r, uh);
-            load8_norm(p.k, ch, i, c0, r, kh);
-            load8_norm(p.q, ch, i, c0, r, qh);
+            load8_norm<FAST>(p.u, ch, i, c0, r, uh);
+            load8_norm<FAST>(p.k, ch, i, c0, r, kh);
+            load8_norm<FAST>(p.q, ch, i, c0, r, qh);
             load8_panel(gDelta, i, c0, dl);
             load8_panel(gd, i, c0, d);
-            load8_bf16(row_bf16(p.er, ch, i), c0, r, p.er.vec, i < ch.nvalid, er);
-            load8_bf16(row_bf16(p.wr, ch, i), c0, V, p.wr.vec, i < ch.nvalid, wr);
-            load8_bf16(row_bf16(p.v, ch, i), c0, V, p.v.vec, i < ch.nvalid, v);
+            load8_bf16<FAST>(row_bf16(p.er, ch, i), c0, r, p.er.vec, i < ch.nvalid, er);
+            load8_bf16<FAST>(row_bf16(p.wr, ch, i), c0, V, p.wr.vec, i < ch.nvalid, wr);
+            load8_bf16<FAST>(row_bf16(p.v, ch, i), c0, V, p.v.vec, i < ch.nvalid, v);
             load8_panel(gG, i, c0, G);
 #pragma unroll
             for (int e = 0; e < 8; ++e) se[e] = sigmoidf_(er[e]);
@@ -308,6 +329,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
         }
     }
     __syncthreads();
+    SD_PHASE(p.g, ph);
     {
         float a1[NT64][4], a2[NT64][4];
         acc_zero<NT64>(a1);
@@ -327,17 +349,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
         });
     }
     __syncthreads();
+    SD_PHASE(p.g, ph);
     trisolve<false>(s_aed, -1.f, s_ag, s_z);
     __syncthreads();
+    SD_PHASE(p.g, ph);
     s2g_panel(panel_ptr(p.Wd, ch.gi), s_ag);
     s2g_panel(panel_ptr(p.Ud, ch.gi), s_z);
+    SD_PHASE(p.g, ph);
 }
 
 // ---------------------------------------------------------------------------
 // Output rows: y = Xg S_c + tril(Aqd) Z~, BF16 operands (the result is BF16).
 constexpr size_t OUTPUT_FWD_SMEM = 2 * BSLOT_BYTES + BSTATE_BYTES + BMAT_BYTES;
 
+template <bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_output_fwd(FwdParams p) {
+    int ph = 0;
+    SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* b_xg = reinterpret_cast<bf16*>(smem_raw);
     bf16* b_zt = b_xg + BSLOT_ELEMS;
@@ -359,6 +387,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_output_fwd(FwdParams p) {
     cp_commit();
     cp_wait<0>();
     __syncthreads();
+    SD_PHASE(p.g, ph);
     float acc[NT128][4];
     acc_zero<NT128>(acc);
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
@@ -375,6 +404,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_output_fwd(FwdParams p) {
             if (j + 1 < V) row[j + 1] = __float2bfloat16_rn(v1);
         }
     });
+    SD_PHASE(p.g, ph);
 }
 
 }  // namespace sd
