@@ -286,12 +286,12 @@ KERNEL_BYTES_PER_CHUNK = {
     "k_output_fwd": _B + _M + _F + _S + _B,                     # Xg,Aqd,Zt,S -> y
     "k_exterior_prep_bwd": 5 * _B + 3 * _F + 6 * _B,            # u,k,q,er,dy,G,Delta,d -> Ag,Xg,Dyf,Dneg,Pp,Qp
     "k_state_scan_b[dS]": 6 * _B + _T,
-    "k_exterior_pair_bwd": 5 * _B + _F + _S + _T + 4 * _B,      # Dyf,dR,Dneg,Xg,Ag,Zt,S,dSe -> A1,A2,PY,dDt
-    "k_sources_bwd": 6 * _B + 3 * _F + 5 * _B + 5 * _F + _B + 4 * _B,
+    # Dyf,dR,Dneg,Xg,Ag,Zt,S,dSe + u,k,q,er,wr,v,G,Delta,d -> 5 partial panels, DG, dq,der,dv,dwr
+    "k_exterior_pair_bwd": 6 * _B + 2 * _T + 6 * _B + 3 * _F + 6 * _B + 4 * _B,
     "k_primal_bwd": 2 * _B + 2 * _F + _B + _S + 2 * _F + 5 * _B + _B,
     "k_state_scan_b[dC]": 6 * _B + _T,
-    "k_predictor_pair_bwd": 2 * _B + 2 * _F + _B + _S + _T + 4 * _B,
-    "k_gate_closure_bwd": _B + _F + 3 * _F + 6 * _B + 2 * _B + _F,
+    # u,h,G,Delta,dRr,Ct,dCe,duPart,Tpre,dGPart,Xext -> du,dh,dlog_decay
+    "k_predictor_close_bwd": 2 * _B + 2 * _F + _B + _S + _T + 4 * _B + 2 * _B + _F,
 }
 
 

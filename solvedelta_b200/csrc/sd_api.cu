@@ -24,11 +24,10 @@ struct PanelDesc {
 const PanelDesc kSaved[] = {{"Lam", 3}, {"G", 0}, {"Delta", 0}, {"Dprim", 0}, {"Zt", 4}, {"CtCk", 2}, {"SCk", 6}};
 const PanelDesc kFwd[] = {{"Upd", 0}, {"Qc", 0}, {"Ubar", 0}, {"Wd", 0}, {"Ud", 0}, {"Dt", 0}, {"Xg", 4}, {"Aqd", 5}};
 const PanelDesc kBwd[] = {{"Pp", 4},     {"Qp", 4},     {"Ag", 4},     {"Xg", 4},     {"Dyf", 4},    {"Dneg", 4},
-                          {"dR", 4},     {"dSeCk", 6},  {"A1", 4},     {"A2", 4},     {"PY", 4},     {"dDt", 4},
+                          {"dR", 4},     {"dSeCk", 6},
                           {"SdS", 3},    {"duPart", 4}, {"dkPart", 4}, {"dGPart", 4}, {"dDelta", 4}, {"DG", 4},
                           {"Xext", 4},   {"Tpre", 4},   {"Khat", 4},   {"Ppp", 4},    {"Qpp", 4},    {"Rneg", 4},
-                          {"dRr", 4},    {"dCeCk", 6},  {"dUbar", 4},  {"dUt", 4},    {"Ti", 4},     {"Tj", 4},
-                          {"CdC", 3}};
+                          {"dRr", 4},    {"dCeCk", 6}};
 
 size_t kind_bytes(int kind) {
     switch (kind) {
@@ -159,10 +158,8 @@ cudaError_t configure_kernels() {
     if ((e = allow_smem(k_exterior_pair_bwd<false>, EXT_PAIR_BWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_primal_bwd<true>, PRIMAL_BWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_primal_bwd<false>, PRIMAL_BWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_predictor_pair_bwd<true>, PRED_PAIR_BWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_predictor_pair_bwd<false>, PRED_PAIR_BWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_gate_closure_bwd<true>, GATE_CLOSURE_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_gate_closure_bwd<false>, GATE_CLOSURE_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_predictor_close_bwd<true>, PRED_CLOSE_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_predictor_close_bwd<false>, PRED_CLOSE_BWD_SMEM)) != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) done[dev] = true;
     return cudaSuccess;
 }
@@ -179,8 +176,8 @@ inline void mark(cudaStream_t stream) {
 
 const char* const kLaunchNames[] = {
     "k_prep_fwd",          "k_state_scan[C]",     "k_primal_fwd",         "k_exterior_prep_fwd", "k_state_scan[S]",
-    "k_output_fwd",        "k_exterior_prep_bwd", "k_state_scan_b[dS]",   "k_exterior_pair_bwd", "k_sources_bwd",
-    "k_primal_bwd",        "k_state_scan_b[dC]",  "k_predictor_pair_bwd", "k_gate_closure_bwd"};
+    "k_output_fwd",        "k_exterior_prep_bwd", "k_state_scan_b[dS]",   "k_exterior_pair_bwd",
+    "k_primal_bwd",        "k_state_scan_b[dC]",  "k_predictor_close_bwd"};
 
 int launch_status() { return cudaGetLastError() == cudaSuccess ? SD_OK : SD_ERR_LAUNCH_FAILED; }
 
@@ -229,7 +226,7 @@ int sd_panel_kind(const sd_shape* shape, int which, const char* name) {
 }
 
 int sd_forward_launches(const sd_shape* shape) { return shape_ok(shape) ? 6 : 0; }
-int sd_backward_launches(const sd_shape* shape) { return shape_ok(shape) ? 8 : 0; }
+int sd_backward_launches(const sd_shape* shape) { return shape_ok(shape) ? 6 : 0; }
 int sd_chunk_tokens(void) { return CL; }
 int sd_version(void) { return 1; }
 
@@ -372,10 +369,9 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
 #define SD_BP(field) p.field = panel_at(kBwd, s, a->scratch, #field)
 #define SD_BB(field) p.field = bpanel_at(kBwd, s, a->scratch, #field)
     SD_BB(Pp); SD_BB(Qp); SD_BB(Ag); SD_BB(Xg); SD_BB(Dyf); SD_BB(Dneg); SD_BB(dR); SD_BB(dSeCk);
-    SD_BB(A1); SD_BB(A2); SD_BB(PY); SD_BB(dDt); SD_BB(DG); SD_BB(Tpre); SD_BB(Khat);
+    SD_BB(DG); SD_BB(Tpre); SD_BB(Khat);
     SD_BB(Ppp); SD_BB(Qpp); SD_BB(Rneg); SD_BB(dRr); SD_BB(dCeCk);
-    SD_BB(dUbar); SD_BB(dUt); SD_BB(Ti); SD_BB(Tj);
-    SD_BB(duPart); SD_BB(dkPart); SD_BB(dGPart); SD_BB(dDelta); SD_BB(Xext); SD_BP(SdS); SD_BP(CdC);
+    SD_BB(duPart); SD_BB(dkPart); SD_BB(dGPart); SD_BB(dDelta); SD_BB(Xext); SD_BP(SdS);
 #undef SD_BB
 #undef SD_BP
     p.du = a->du; p.dh = a->dh; p.dq = a->dq; p.dk = a->dkeys; p.dv = a->dvalues;
@@ -405,10 +401,6 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
     else k_exterior_pair_bwd<false><<<chunks, NTHREADS, EXT_PAIR_BWD_SMEM, stream>>>(p);
     mark(stream);
     set_dbg(p.g, 9, chunks);
-    if (fast) k_sources_bwd<true><<<chunks, NTHREADS, 0, stream>>>(p);
-    else k_sources_bwd<false><<<chunks, NTHREADS, 0, stream>>>(p);
-    mark(stream);
-    set_dbg(p.g, 10, chunks);
     if (fast) k_primal_bwd<true><<<chunks, NTHREADS, PRIMAL_BWD_SMEM, stream>>>(p);
     else k_primal_bwd<false><<<chunks, NTHREADS, PRIMAL_BWD_SMEM, stream>>>(p);
     mark(stream);
@@ -421,13 +413,9 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
         k_state_scan_b<<<scan_grid, SCAN_THREADS, SCAN_B_SMEM_BYTES, stream>>>(sp);
     mark(stream);
     }
-    set_dbg(p.g, 12, chunks);
-    if (fast) k_predictor_pair_bwd<true><<<chunks, NTHREADS, PRED_PAIR_BWD_SMEM, stream>>>(p);
-    else k_predictor_pair_bwd<false><<<chunks, NTHREADS, PRED_PAIR_BWD_SMEM, stream>>>(p);
-    mark(stream);
-    set_dbg(p.g, 13, chunks);
-    if (fast) k_gate_closure_bwd<true><<<chunks, NTHREADS, GATE_CLOSURE_SMEM, stream>>>(p);
-    else k_gate_closure_bwd<false><<<chunks, NTHREADS, GATE_CLOSURE_SMEM, stream>>>(p);
+    set_dbg(p.g, 11, chunks);
+    if (fast) k_predictor_close_bwd<true><<<chunks, NTHREADS, PRED_CLOSE_BWD_SMEM, stream>>>(p);
+    else k_predictor_close_bwd<false><<<chunks, NTHREADS, PRED_CLOSE_BWD_SMEM, stream>>>(p);
     mark(stream);
     return launch_status();
 }
@@ -441,7 +429,7 @@ const char* sd_launch_name(int index) {
 
 int sd_profile_step(const sd_forward_args* fwd, const sd_backward_args* bwd, void* stream_, float* ms,
                     int capacity, int* count) {
-    if (!fwd || !ms || !count || capacity < 14) return SD_ERR_INVALID_ARGUMENT;
+    if (!fwd || !ms || !count || capacity < 12) return SD_ERR_INVALID_ARGUMENT;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     LaunchRecorder rec;
     rec.n = 0;

@@ -1,8 +1,8 @@
 // Chunk-parallel backward kernels: one CTA per (stream, chunk).
 //
 // Pipeline: k_exterior_prep_bwd -> scan(dS, reverse) -> k_exterior_pair_bwd
-//           -> k_sources_bwd -> k_primal_bwd (also prepares the dC scan)
-//           -> scan(dC, reverse) -> k_predictor_pair_bwd -> k_gate_closure_bwd.
+//           (contractions + per-token source reverse) -> k_primal_bwd (also prepares the dC scan)
+//           -> scan(dC, reverse) -> k_predictor_close_bwd (contractions + gate closure).
 // Forward locals are recomputed from the raw inputs and the panels the forward
 // pass kept (G, Delta, d, Z~, the chunk-entry states and lam).  Gradients
 // tolerate BF16 operands, so every contraction here is BF16 x BF16 -> FP32 and
@@ -22,12 +22,11 @@ struct BwdParams {
     const bf16 *Zt, *SCk;
     // backward scratch: BF16 contraction operands / scanned panels
     bf16 *Pp, *Qp, *Ag, *Xg, *Dyf, *Dneg, *dR, *dSeCk;
-    bf16 *A1, *A2, *PY, *dDt, *DG, *Tpre, *Khat;
+    bf16 *DG, *Tpre, *Khat;
     bf16 *Ppp, *Qpp, *Rneg, *dRr, *dCeCk;
-    bf16 *dUbar, *dUt, *Ti, *Tj;
     // partial cotangents (BF16: they are final up to gradient tolerance) and FP32 reductions
     bf16 *duPart, *dkPart, *dGPart, *dDelta, *Xext;
-    float *SdS, *CdC;
+    float *SdS;
     // outputs
     void *du, *dh, *dq, *dk, *dv, *der, *dwr;
     float *dld, *dgam;
@@ -87,6 +86,13 @@ __device__ __forceinline__ void async_bstate(bf16* sm, const bf16* g) {
 __device__ __forceinline__ bf16* bstate_ptr(bf16* base, long long gi) { return base + gi * (long long)(DP * DP); }
 __device__ __forceinline__ const bf16* bstate_ptr(const bf16* base, long long gi) {
     return base + gi * (long long)(DP * DP);
+}
+
+template <int NTW>
+__device__ __forceinline__ void epi_store_bsm(float (&acc)[NTW][4], int r0, int n0, bf16* spanel) {
+    warp_epi<NTW>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
+        *reinterpret_cast<__nv_bfloat162*>(spanel + i * LDB + j) = __floats2bfloat162_rn(v0, v1);
+    });
 }
 
 template <int NTW>
@@ -205,13 +211,115 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) 
 }
 
 // ---------------------------------------------------------------------------
+// Per-token reverse of the sources and of the gate factors of the exterior.
+// Writes the final gradients of q, values, erase_raw, write_raw and the
+// partial cotangents the predictor reverse still has to complete.
+// A1, A2, PY, dDt and dR are read from the shared BF16 panels the contractions
+// of the same CTA just produced.
+template <bool FAST>
+__device__ __forceinline__ void sources_bwd_rows(const BwdParams& p, const Chunk& ch, const bf16* sA1,
+                                                 const bf16* sA2, const bf16* sPY, const bf16* sdDt,
+                                                 const bf16* sdR) {
+    const int r = p.g.r, V = p.g.V;
+    const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
+    const float* gDelta = panel_ptr(p.Delta, ch.gi);
+    const float* gd = panel_ptr(p.Dprim, ch.gi);
+    const float* gG = panel_ptr(p.Gp, ch.gi);
+    float GL[8];
+    load8_panel(gG, CL - 1, c0, GL);
+#pragma unroll 1
+    for (int pp = 0; pp < ROW_PASSES; ++pp) {
+        const int i = lr + ROWS_PER_PASS * pp;
+        float uh[8], kh[8], qh[8], dl[8], d[8], er[8], G[8], se[8];
+        load8_norm<FAST>(p.u, ch, i, c0, r, uh);
+        load8_norm<FAST>(p.k, ch, i, c0, r, kh);
+        const float rstd_q = load8_norm<FAST>(p.q, ch, i, c0, r, qh);
+        load8_panel(gDelta, i, c0, dl);
+        load8_panel(gd, i, c0, d);
+        load8_panel(gG, i, c0, G);
+        load8_bf16<FAST>(row_bf16(p.er, ch, i), c0, r, p.er.vec, i < ch.nvalid, er);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) se[e] = sigmoidf_(er[e]);
+        Sources src;
+        sources_fwd(uh, kh, qh, dl, se, src);
+        float a1[8], a2[8], py[8], ddt[8];
+        load8_bsm(sA1, i, c0, a1);
+        load8_bsm(sA2, i, c0, a2);
+        load8_bsm(sPY, i, c0, py);
+        load8_bsm(sdDt, i, c0, ddt);
+        float dchi[8], de[8], dd[8], dG[8], xext[8], dg_[8];
+        float dsb = 0.f, dsq = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            float ep = __expf(G[e]), en = clamp_exp_neg(G[e]), et = __expf(GL[e] - G[e]);
+            dchi[e] = ep * a1[e];
+            de[e] = -ep * a2[e];
+            dd[e] = en * py[e] + et * ddt[e];
+            float dneg = d[e] * en, dt = d[e] * et;
+            dG[e] = src.chi[e] * dchi[e] + src.e[e] * de[e] - dneg * py[e] + dd[e] * (d[e] - kh[e]);
+            xext[e] = ddt[e] * dt;
+            dg_[e] = dd[e] * ep;
+            dsb = fmaf(-de[e], src.phi[e], dsb);
+            dsq = fmaf(-dchi[e], src.phi[e], dsq);
+        }
+        dsb = row_sum16(dsb);
+        dsq = row_sum16(dsq);
+        const float inv_den = 1.f / src.den;
+        const float dden = -(dsb * src.sb + dsq * src.sq) * inv_den;
+        float db[8], dqh[8], dphi[8], duh[8];
+        float dot = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            db[e] = de[e] + dsb * inv_den * uh[e];
+            dqh[e] = dchi[e] + dsq * inv_den * uh[e];
+            dphi[e] = -de[e] * src.sb - dchi[e] * src.sq + dden * uh[e];
+            duh[e] = dsb * inv_den * src.b[e] + dsq * inv_den * qh[e] + dden * src.phi[e];
+            dot = fmaf(dphi[e], dl[e], dot);
+        }
+        dot = row_sum16(dot);
+        const float coef = dot * src.s / (RHO * RHO + src.n2);
+        float ddl[8], dkp[8], der[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            ddl[e] = src.s * dphi[e] - coef * dl[e];
+            dkp[e] = se[e] * db[e] + dd[e];
+            der[e] = db[e] * kh[e] * se[e] * (1.f - se[e]);
+        }
+        float dq[8];
+        norm_vjp8(dqh, qh, rstd_q, dq);
+        store8_bf16<FAST>(p.dq, p.g, ch, i, c0, r, dq);
+        store8_bf16<FAST>(p.der, p.g, ch, i, c0, r, der);
+        store8_bpanel(bpanel_ptr(p.duPart, ch.gi), i, c0, duh);
+        store8_bpanel(bpanel_ptr(p.dkPart, ch.gi), i, c0, dkp);
+        store8_bpanel(bpanel_ptr(p.dGPart, ch.gi), i, c0, dG);
+        store8_bpanel(bpanel_ptr(p.dDelta, ch.gi), i, c0, ddl);
+        store8_bpanel(bpanel_ptr(p.DG, ch.gi), i, c0, dg_);
+        store8_bpanel(bpanel_ptr(p.Xext, ch.gi), i, c0, xext);
+        // value side: dv = sigmoid(write) dR, d write_raw = dR v sigmoid'(write)
+        float wr[8], v[8], dr[8], dv[8], dwr[8];
+        load8_bf16<FAST>(row_bf16(p.wr, ch, i), c0, V, p.wr.vec, i < ch.nvalid, wr);
+        load8_bf16<FAST>(row_bf16(p.v, ch, i), c0, V, p.v.vec, i < ch.nvalid, v);
+        load8_bsm(sdR, i, c0, dr);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            float sw = sigmoidf_(wr[e]);
+            dv[e] = sw * dr[e];
+            dwr[e] = dr[e] * v[e] * sw * (1.f - sw);
+        }
+        store8_bf16<FAST>(p.dv, p.g, ch, i, c0, V, dv);
+        store8_bf16<FAST>(p.dwr, p.g, ch, i, c0, V, dwr);
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Pure contractions of the exterior reverse step (no gate factors):
 //   A1 = dy S^T + tril(dy Z~^T) Dneg        (-> d chi after exp(G))
 //   A2 = dR S^T + stril(dR Z~^T) Dneg       (-> d e)
 //   PY = tril(dy Z~^T)^T Xg + stril(dR Z~^T)^T ag
 //   dDt = Z~ dS_end^T ,  SdS[c] = sum_v S[c][v] dS_end[c][v]
-// Every operand is resident; the BF16 ones stream in with cp.async while the
-// FP32 panels kept by forward are converted.
+// Every operand is resident and streams in with cp.async.  The four results
+// stay in shared memory (over operands that are no longer needed) and the
+// per-token reverse of the sources runs on them in the same CTA.
 constexpr size_t EXT_PAIR_BWD_SMEM = 6 * BSLOT_BYTES + 2 * BSTATE_BYTES + 2 * BMAT_BYTES;
 
 template <bool FAST>
@@ -274,27 +382,27 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
         warp_mma_bf16<NT128, false, true>(a2, b_dr, LDB, b_S, LDB, r0, n0, 0, DP);
         warp_mma_bf16<NT128, false, false>(a1, b_daqd, LDM, b_dn, LDB, r0, n0, 0, r0 + 16);
         warp_mma_bf16<NT128, false, false>(a2, b_daed, LDM, b_dn, LDB, r0, n0, 0, r0 + 16);
-        epi_store_bpanel<NT128>(a1, r0, n0, bpanel_ptr(p.A1, ch.gi));
-        epi_store_bpanel<NT128>(a2, r0, n0, bpanel_ptr(p.A2, ch.gi));
+        cp_wait<1>();
+        __syncthreads();  // nobody reads dy / Dneg any more: A1 and A2 take their place
+        SD_PHASE(p.g, ph);
+        epi_store_bsm<NT128>(a1, r0, n0, b_dy);
+        epi_store_bsm<NT128>(a2, r0, n0, b_dn);
     }
-    cp_wait<1>();
-    __syncthreads();
-    SD_PHASE(p.g, ph);
     {
         float acc[NT128][4];
         acc_zero<NT128>(acc);
         warp_mma_bf16<NT128, true, false>(acc, b_daqd, LDM, b_xg, LDB, r0, n0, r0, CL);
         warp_mma_bf16<NT128, true, false>(acc, b_daed, LDM, b_ag, LDB, r0, n0, r0, CL);
-        epi_store_bpanel<NT128>(acc, r0, n0, bpanel_ptr(p.PY, ch.gi));
+        cp_wait<0>();
+        __syncthreads();  // Xg is free: PY takes its place
+        SD_PHASE(p.g, ph);
+        epi_store_bsm<NT128>(acc, r0, n0, b_xg);
     }
-    cp_wait<0>();
-    __syncthreads();
-    SD_PHASE(p.g, ph);
     {
         float acc[NT128][4];
         acc_zero<NT128>(acc);
         warp_mma_bf16<NT128, false, true>(acc, b_zt, LDB, b_dS, LDB, r0, n0, 0, DP);
-        epi_store_bpanel<NT128>(acc, r0, n0, bpanel_ptr(p.dDt, ch.gi));
+        epi_store_bsm<NT128>(acc, r0, n0, b_ag);  // ag was last read before the barrier above
     }
     {
         const int c = threadIdx.x >> 2, qt = threadIdx.x & 3;  // four lanes per state row
@@ -311,112 +419,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
         acc += __shfl_xor_sync(0xffffffffu, acc, 2);
         if (qt == 0) p.SdS[ch.gi * DP + c] = acc;
     }
+    __syncthreads();
     SD_PHASE(p.g, ph);
-}
-
-// ---------------------------------------------------------------------------
-// Per-token reverse of the sources and of the gate factors of the exterior.
-// Writes the final gradients of q, values, erase_raw, write_raw and the
-// partial cotangents the predictor reverse still has to complete.
-template <bool FAST>
-__global__ void __launch_bounds__(NTHREADS, 1) k_sources_bwd(BwdParams p) {
-    int ph = 0;
-    SD_PHASE(p.g, ph);
-    const Chunk ch = chunk_of(p.g, blockIdx.x);
-    const int r = p.g.r, V = p.g.V;
-    const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
-    const float* gDelta = panel_ptr(p.Delta, ch.gi);
-    const float* gd = panel_ptr(p.Dprim, ch.gi);
-    const float* gG = panel_ptr(p.Gp, ch.gi);
-    const bf16* gA1 = bpanel_ptr(p.A1, ch.gi);
-    const bf16* gA2 = bpanel_ptr(p.A2, ch.gi);
-    const bf16* gPY = bpanel_ptr(p.PY, ch.gi);
-    const bf16* gdDt = bpanel_ptr(p.dDt, ch.gi);
-    const bf16* gdR = bpanel_ptr(p.dR, ch.gi);
-    float GL[8];
-    load8_panel(gG, CL - 1, c0, GL);
-#pragma unroll 1
-    for (int pp = 0; pp < ROW_PASSES; ++pp) {
-        const int i = lr + ROWS_PER_PASS * pp;
-        float uh[8], kh[8], qh[8], dl[8], d[8], er[8], G[8], se[8];
-        load8_norm<FAST>(p.u, ch, i, c0, r, uh);
-        load8_norm<FAST>(p.k, ch, i, c0, r, kh);
-        const float rstd_q = load8_norm<FAST>(p.q, ch, i, c0, r, qh);
-        load8_panel(gDelta, i, c0, dl);
-        load8_panel(gd, i, c0, d);
-        load8_panel(gG, i, c0, G);
-        load8_bf16<FAST>(row_bf16(p.er, ch, i), c0, r, p.er.vec, i < ch.nvalid, er);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) se[e] = sigmoidf_(er[e]);
-        Sources src;
-        sources_fwd(uh, kh, qh, dl, se, src);
-        float a1[8], a2[8], py[8], ddt[8];
-        load8_bpanel(gA1, i, c0, a1);
-        load8_bpanel(gA2, i, c0, a2);
-        load8_bpanel(gPY, i, c0, py);
-        load8_bpanel(gdDt, i, c0, ddt);
-        float dchi[8], de[8], dd[8], dG[8], xext[8], dg_[8];
-        float dsb = 0.f, dsq = 0.f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            float ep = __expf(G[e]), en = clamp_exp_neg(G[e]), et = __expf(GL[e] - G[e]);
-            dchi[e] = ep * a1[e];
-            de[e] = -ep * a2[e];
-            dd[e] = en * py[e] + et * ddt[e];
-            float dneg = d[e] * en, dt = d[e] * et;
-            dG[e] = src.chi[e] * dchi[e] + src.e[e] * de[e] - dneg * py[e] + dd[e] * (d[e] - kh[e]);
-            xext[e] = ddt[e] * dt;
-            dg_[e] = dd[e] * ep;
-            dsb = fmaf(-de[e], src.phi[e], dsb);
-            dsq = fmaf(-dchi[e], src.phi[e], dsq);
-        }
-        dsb = row_sum16(dsb);
-        dsq = row_sum16(dsq);
-        const float inv_den = 1.f / src.den;
-        const float dden = -(dsb * src.sb + dsq * src.sq) * inv_den;
-        float db[8], dqh[8], dphi[8], duh[8];
-        float dot = 0.f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            db[e] = de[e] + dsb * inv_den * uh[e];
-            dqh[e] = dchi[e] + dsq * inv_den * uh[e];
-            dphi[e] = -de[e] * src.sb - dchi[e] * src.sq + dden * uh[e];
-            duh[e] = dsb * inv_den * src.b[e] + dsq * inv_den * qh[e] + dden * src.phi[e];
-            dot = fmaf(dphi[e], dl[e], dot);
-        }
-        dot = row_sum16(dot);
-        const float coef = dot * src.s / (RHO * RHO + src.n2);
-        float ddl[8], dkp[8], der[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            ddl[e] = src.s * dphi[e] - coef * dl[e];
-            dkp[e] = se[e] * db[e] + dd[e];
-            der[e] = db[e] * kh[e] * se[e] * (1.f - se[e]);
-        }
-        float dq[8];
-        norm_vjp8(dqh, qh, rstd_q, dq);
-        store8_bf16<FAST>(p.dq, p.g, ch, i, c0, r, dq);
-        store8_bf16<FAST>(p.der, p.g, ch, i, c0, r, der);
-        store8_bpanel(bpanel_ptr(p.duPart, ch.gi), i, c0, duh);
-        store8_bpanel(bpanel_ptr(p.dkPart, ch.gi), i, c0, dkp);
-        store8_bpanel(bpanel_ptr(p.dGPart, ch.gi), i, c0, dG);
-        store8_bpanel(bpanel_ptr(p.dDelta, ch.gi), i, c0, ddl);
-        store8_bpanel(bpanel_ptr(p.DG, ch.gi), i, c0, dg_);
-        store8_bpanel(bpanel_ptr(p.Xext, ch.gi), i, c0, xext);
-        // value side: dv = sigmoid(write) dR, d write_raw = dR v sigmoid'(write)
-        float wr[8], v[8], dr[8], dv[8], dwr[8];
-        load8_bf16<FAST>(row_bf16(p.wr, ch, i), c0, V, p.wr.vec, i < ch.nvalid, wr);
-        load8_bf16<FAST>(row_bf16(p.v, ch, i), c0, V, p.v.vec, i < ch.nvalid, v);
-        load8_bpanel(gdR, i, c0, dr);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            float sw = sigmoidf_(wr[e]);
-            dv[e] = sw * dr[e];
-            dwr[e] = dr[e] * v[e] * sw * (1.f - sw);
-        }
-        store8_bf16<FAST>(p.dv, p.g, ch, i, c0, V, dv);
-        store8_bf16<FAST>(p.dwr, p.g, ch, i, c0, V, dwr);
-    }
+    sources_bwd_rows<FAST>(p, ch, b_dy, b_dn, b_xg, b_ag, b_dr);
     SD_PHASE(p.g, ph);
 }
 
@@ -611,31 +616,45 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
 }
 
 // ---------------------------------------------------------------------------
-// Contractions of the predictor reverse that need the scanned dRr / dC:
+// Last kernel of the reverse pass: the contractions that need the scanned
+// dRr / dC, then the gate closure, in one CTA.
 //   dUbar = Delta dC_end ,  dUt = -gamma (dRr Ct^T) ,
 //   dgamma = rowsum(dRr * (h - U~ Ct - stril(N) Delta)) ,
 //   Ti = dN Uneg ,  Tj = dN^T U~   with dN = -gamma stril(dRr Delta^T),
-//   CdC[c] = sum_a Ct[c][a] dCt_end[c][a].
-constexpr size_t PRED_PAIR_BWD_SMEM =
-    4 * BSLOT_BYTES + 2 * BSTATE_BYTES + 2 * BMAT_BYTES + (CL + 4 * CL) * sizeof(float);
+//   CdC[c] = sum_a Ct[c][a] dCt_end[c][a];
+// then d u^, dG, dE are assembled per token and
+//   d log_decay = -dE + reverse_cumsum(dG), with dG[last] += dGL.
+// Writes the final gradients of u, h, gamma and log_decay.  The four
+// contraction results and the three FP32 closure panels overlay operands that
+// are dead by then.
+constexpr size_t PRED_CLOSE_BWD_SMEM =
+    4 * BSLOT_BYTES + 2 * BMAT_BYTES + 3 * size_t(CL) * LDP * 4 + (CL + 4 * CL + DP) * sizeof(float);
+static_assert(2 * BMAT_BYTES >= BSLOT_BYTES, "Tj overlays the two pair matrices");
+static_assert(3 * size_t(CL) * LDP * 4 >= 2 * BSTATE_BYTES, "closure panels overlay both BF16 states");
 
 template <bool FAST>
-__global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p) {
+__global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* b_ut = reinterpret_cast<bf16*>(smem_raw);
-    bf16* b_un = b_ut + BSLOT_ELEMS;
-    bf16* b_dl = b_un + BSLOT_ELEMS;
-    bf16* b_dr = b_dl + BSLOT_ELEMS;
-    bf16* b_Ct = b_dr + BSLOT_ELEMS;
-    bf16* b_dC = b_Ct + DP * LDB;
-    bf16* b_N = b_dC + DP * LDB;
+    bf16* b_ut = reinterpret_cast<bf16*>(smem_raw);   // U~      -> dUbar
+    bf16* b_un = b_ut + BSLOT_ELEMS;                   // Uneg    -> dUt
+    bf16* b_dl = b_un + BSLOT_ELEMS;                   // Delta   -> Ti
+    bf16* b_dr = b_dl + BSLOT_ELEMS;                   // dRr (kept)
+    bf16* b_N = b_dr + BSLOT_ELEMS;                    // N, dN   -> Tj
     bf16* b_dN = b_N + BMAT_ELEMS;
-    float* s_gam = reinterpret_cast<float*>(b_dN + BMAT_ELEMS);
-    float* s_dot = s_gam + CL;  // [CL][4]
+    unsigned char* region = reinterpret_cast<unsigned char*>(b_dN + BMAT_ELEMS);
+    bf16* b_Ct = reinterpret_cast<bf16*>(region);      // Ct, dC  -> dG, dE, X (FP32)
+    bf16* b_dC = b_Ct + DP * LDB;
+    float* s_dG = reinterpret_cast<float*>(region);
+    float* s_dE = s_dG + CL * LDP;
+    float* s_X = s_dE + CL * LDP;
+    float* s_gam = s_X + CL * LDP;
+    float* s_dot = s_gam + CL;   // [CL][4]
+    float* s_cdc = s_dot + 4 * CL;  // [DP]
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r;
+    const float* gG = panel_ptr(p.Gp, ch.gi);
 
     async_bpanel(b_dr, bpanel_ptr(p.dRr, ch.gi));
     async_bstate(b_dC, bstate_ptr(p.dCeCk, ch.gi));
@@ -643,7 +662,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p)
     load_gamma(p.gam, ch, s_gam);
     {
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
-        const float* gG = panel_ptr(p.Gp, ch.gi);
         const float* gDelta = panel_ptr(p.Delta, ch.gi);
 #pragma unroll 1
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
@@ -690,31 +708,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p)
     __syncthreads();
     SD_PHASE(p.g, ph);
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
-    {   // dUbar[j][c] = sum_a Delta[j][a] dCt[c][a]
-        float acc[NT128][4];
-        acc_zero<NT128>(acc);
-        warp_mma_bf16<NT128, false, true>(acc, b_dl, LDB, b_dC, LDB, r0, n0, 0, DP);
-        epi_store_bpanel<NT128>(acc, r0, n0, bpanel_ptr(p.dUbar, ch.gi));
-    }
-    {   // dUt[i][c] = -gamma_i sum_a dRr[i][a] Ct[c][a]
-        float acc[NT128][4];
-        acc_zero<NT128>(acc);
-        warp_mma_bf16<NT128, false, true>(acc, b_dr, LDB, b_Ct, LDB, r0, n0, 0, DP);
-        bf16* gout = bpanel_ptr(p.dUt, ch.gi);
-        warp_epi<NT128>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
-            float gm = -s_gam[i];
-            *reinterpret_cast<__nv_bfloat162*>(gout + i * DP + j) = __floats2bfloat162_rn(gm * v0, gm * v1);
-        });
-    }
-    {   // Ti, Tj
-        float acc[NT128][4];
-        acc_zero<NT128>(acc);
-        warp_mma_bf16<NT128, false, false>(acc, b_dN, LDM, b_un, LDB, r0, n0, 0, r0 + 16);
-        epi_store_bpanel<NT128>(acc, r0, n0, bpanel_ptr(p.Ti, ch.gi));
-        acc_zero<NT128>(acc);
-        warp_mma_bf16<NT128, true, false>(acc, b_dN, LDM, b_ut, LDB, r0, n0, r0, CL);
-        epi_store_bpanel<NT128>(acc, r0, n0, bpanel_ptr(p.Tj, ch.gi));
-    }
     {   // residual rows and dgamma_i = sum_a dRr[i][a] (h[i][a] - (U~ Ct)[i][a] - (N Delta)[i][a])
         float acc[NT128][4];
         acc_zero<NT128>(acc);
@@ -749,14 +742,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p)
             s_dot[ib * 4 + nq] = sumb;
         }
     }
-    __syncthreads();
-    SD_PHASE(p.g, ph);
-    if (threadIdx.x < CL && threadIdx.x < ch.nvalid) {
-        const int i = threadIdx.x;
-        p.dgam[((long long)ch.b * p.g.T + ch.t0 + i) * p.g.H + ch.hh] =
-            (s_dot[i * 4] + s_dot[i * 4 + 1]) + (s_dot[i * 4 + 2] + s_dot[i * 4 + 3]);
-    }
-    {
+    {   // CdC
         const int c = threadIdx.x >> 2, qt = threadIdx.x & 3;  // four lanes per state row
         float acc = 0.f;
 #pragma unroll
@@ -769,28 +755,36 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_pair_bwd(BwdParams p)
         }
         acc += __shfl_xor_sync(0xffffffffu, acc, 1);
         acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-        if (qt == 0) p.CdC[ch.gi * DP + c] = acc;
+        if (qt == 0) s_cdc[c] = acc;
     }
+    {
+        float aub[NT128][4], aut[NT128][4], ati[NT128][4], atj[NT128][4];
+        acc_zero<NT128>(aub);
+        acc_zero<NT128>(aut);
+        acc_zero<NT128>(ati);
+        acc_zero<NT128>(atj);
+        // dUbar[j][c] = sum_a Delta[j][a] dCt[c][a] ; dUt[i][c] = -gamma_i sum_a dRr[i][a] Ct[c][a]
+        warp_mma_bf16<NT128, false, true>(aub, b_dl, LDB, b_dC, LDB, r0, n0, 0, DP);
+        warp_mma_bf16<NT128, false, true>(aut, b_dr, LDB, b_Ct, LDB, r0, n0, 0, DP);
+        warp_mma_bf16<NT128, false, false>(ati, b_dN, LDM, b_un, LDB, r0, n0, 0, r0 + 16);
+        warp_mma_bf16<NT128, true, false>(atj, b_dN, LDM, b_ut, LDB, r0, n0, r0, CL);
+        __syncthreads();  // every contraction has read its operands: overlay the results
+        SD_PHASE(p.g, ph);
+        epi_store_bsm<NT128>(aub, r0, n0, b_ut);
+        warp_epi<NT128>(aut, r0, n0, [&](int i, int j, float v0, float v1) {
+            float gm = -s_gam[i];
+            *reinterpret_cast<__nv_bfloat162*>(b_un + i * LDB + j) = __floats2bfloat162_rn(gm * v0, gm * v1);
+        });
+        epi_store_bsm<NT128>(ati, r0, n0, b_dl);
+        epi_store_bsm<NT128>(atj, r0, n0, b_N);
+    }
+    if (threadIdx.x < CL && threadIdx.x < ch.nvalid) {
+        const int i = threadIdx.x;
+        p.dgam[((long long)ch.b * p.g.T + ch.t0 + i) * p.g.H + ch.hh] =
+            (s_dot[i * 4] + s_dot[i * 4 + 1]) + (s_dot[i * 4 + 2] + s_dot[i * 4 + 3]);
+    }
+    __syncthreads();
     SD_PHASE(p.g, ph);
-}
-
-// ---------------------------------------------------------------------------
-// Gate closure: assemble d u^, d G, d E, then
-//   d log_decay = -dE + reverse_cumsum(dG), with dG[last] += dGL.
-// Writes the final gradients of u, h and log_decay.
-constexpr size_t GATE_CLOSURE_SMEM = 3 * SLOT_BYTES;
-
-template <bool FAST>
-__global__ void __launch_bounds__(NTHREADS, 1) k_gate_closure_bwd(BwdParams p) {
-    int ph = 0;
-    SD_PHASE(p.g, ph);
-    extern __shared__ __align__(16) float smem[];
-    float* s_dG = smem;
-    float* s_dE = s_dG + SLOT_FLOATS;
-    float* s_X = s_dE + SLOT_FLOATS;
-    const Chunk ch = chunk_of(p.g, blockIdx.x);
-    const int r = p.g.r;
-    const float* gG = panel_ptr(p.Gp, ch.gi);
     {
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
         float GL[8];
@@ -807,13 +801,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_gate_closure_bwd(BwdParams p) {
             float dup[8], tpre[8], dub[8], dut[8], ti[8], tj[8], dgp[8], xext[8], drr[8];
             load8_bpanel(bpanel_ptr(p.duPart, ch.gi), i, c0, dup);
             load8_bpanel(bpanel_ptr(p.Tpre, ch.gi), i, c0, tpre);
-            load8_bpanel(bpanel_ptr(p.dUbar, ch.gi), i, c0, dub);
-            load8_bpanel(bpanel_ptr(p.dUt, ch.gi), i, c0, dut);
-            load8_bpanel(bpanel_ptr(p.Ti, ch.gi), i, c0, ti);
-            load8_bpanel(bpanel_ptr(p.Tj, ch.gi), i, c0, tj);
             load8_bpanel(bpanel_ptr(p.dGPart, ch.gi), i, c0, dgp);
             load8_bpanel(bpanel_ptr(p.Xext, ch.gi), i, c0, xext);
-            load8_bpanel(bpanel_ptr(p.dRr, ch.gi), i, c0, drr);
+            load8_bsm(b_ut, i, c0, dub);
+            load8_bsm(b_un, i, c0, dut);
+            load8_bsm(b_dl, i, c0, ti);
+            load8_bsm(b_N, i, c0, tj);
+            load8_bsm(b_dr, i, c0, drr);
             float duh[8], dE[8], dG[8], X[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
@@ -829,7 +823,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_gate_closure_bwd(BwdParams p) {
             store8_smem(s_X, i, c0, X);
             float du[8], dh[8];
             norm_vjp8(duh, uh, rstd_u, du);
-            const float gm = (i < ch.nvalid) ? *row_f32(p.gam, ch, i) : 0.f;
+            const float gm = s_gam[i];
 #pragma unroll
             for (int e = 0; e < 8; ++e) dh[e] = gm * drr[e];
             store8_bf16<FAST>(p.du, p.g, ch, i, c0, r, du);
@@ -842,7 +836,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_gate_closure_bwd(BwdParams p) {
         const int c = threadIdx.x;
         float xs = 0.f;
         for (int i = 0; i < CL; ++i) xs += s_X[i * LDP + c];
-        float run = __expf(gG[(CL - 1) * DP + c]) * (p.SdS[ch.gi * DP + c] + p.CdC[ch.gi * DP + c]) + xs;
+        float run = __expf(gG[(CL - 1) * DP + c]) * (p.SdS[ch.gi * DP + c] + s_cdc[c]) + xs;
         for (int i = CL - 1; i >= 0; --i) {
             run += s_dG[i * LDP + c];
             if (i < ch.nvalid)

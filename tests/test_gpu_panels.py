@@ -11,9 +11,9 @@ from tests.helpers import rel_l2
 
 SAVED = ("Lam", "G", "Delta", "Dprim", "Zt", "CtCk", "SCk")
 FWD = ("Upd", "Qc", "Ubar", "Wd", "Ud", "Dt", "Xg", "Aqd")
-BWD = ("Pp", "Qp", "Ag", "Xg", "Dyf", "Dneg", "dR", "dSeCk", "A1", "A2", "PY", "dDt", "SdS",
+BWD = ("Pp", "Qp", "Ag", "Xg", "Dyf", "Dneg", "dR", "dSeCk", "SdS",
        "duPart", "dkPart", "dGPart", "DG", "Xext", "Tpre", "Khat", "dDelta", "Ppp", "Qpp", "Rneg",
-       "dRr", "dCeCk", "dUbar", "dUt", "Ti", "Tj", "CdC")
+       "dRr", "dCeCk")
 
 
 def _pad(x):
