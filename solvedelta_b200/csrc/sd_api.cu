@@ -21,7 +21,7 @@ struct PanelDesc {
     int kind;
 };
 
-const PanelDesc kSaved[] = {{"Lam", 3}, {"G", 0}, {"Delta", 0}, {"Dprim", 0}, {"Zt", 4}, {"CtCk", 2}, {"SCk", 6}};
+const PanelDesc kSaved[] = {{"Lam", 3}, {"G", 0}, {"Delta", 0}, {"Dprim", 0}, {"Zt", 4}, {"CtCk", 2}, {"CtCkB", 6}, {"SCk", 6}};
 const PanelDesc kFwd[] = {{"Upd", 0}, {"Qc", 0}, {"Ubar", 0}, {"Wd", 0}, {"Ud", 0}, {"Dt", 0}, {"Xg", 4}, {"Aqd", 5}};
 const PanelDesc kBwd[] = {{"Pp", 4},     {"Qp", 4},     {"Ag", 4},     {"Xg", 4},     {"Dyf", 4},    {"Dneg", 4},
                           {"dR", 4},     {"dSeCk", 6},
@@ -299,7 +299,8 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
     {
         ScanParams sp{};
         sp.P = p.Upd; sp.Q = p.Qc; sp.R = p.Ubar;
-        sp.lam = p.Lam; sp.X = p.Delta; sp.ck = p.CtCk;
+        sp.lam = p.Lam; sp.X = p.Delta; sp.ck = p.CtCk; sp.Xb = nullptr;
+        sp.ckb = bpanel_at(kSaved, s, a->saved, "CtCkB");
         sp.init = a->C0; sp.fin = a->C_T;
         sp.NC = p.g.NC; sp.reverse = 0; sp.transposed_io = 1; sp.nrows = s->r; sp.ncols = s->r;
         k_state_scan<<<scan_grid, SCAN_THREADS, SCAN_SMEM_BYTES, stream>>>(sp);
@@ -365,6 +366,7 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
     p.Dprim = panel_at(kSaved, s, sv, "Dprim");
     p.Zt = bpanel_at(kSaved, s, sv, "Zt");
     p.CtCk = panel_at(kSaved, s, sv, "CtCk");
+    p.CtCkB = bpanel_at(kSaved, s, sv, "CtCkB");
     p.SCk = bpanel_at(kSaved, s, sv, "SCk");
 #define SD_BP(field) p.field = panel_at(kBwd, s, a->scratch, #field)
 #define SD_BB(field) p.field = bpanel_at(kBwd, s, a->scratch, #field)

@@ -19,7 +19,7 @@ struct BwdParams {
     Operand u, h, q, k, v, er, wr, ld, gam, dy;
     // kept by forward (FP32)
     const float *Lam, *Gp, *Delta, *Dprim, *CtCk;
-    const bf16 *Zt, *SCk;
+    const bf16 *Zt, *SCk, *CtCkB;
     // backward scratch: BF16 contraction operands / scanned panels
     bf16 *Pp, *Qp, *Ag, *Xg, *Dyf, *Dneg, *dR, *dSeCk;
     bf16 *DG, *Tpre, *Khat;
@@ -202,8 +202,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) 
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
-    trisolve_upper_b(f_aedT, -1.f, b_dy, b_dt);
-    __syncthreads();
+    trisolve_blocked<true, false>(f_aedT, -1.f, PanelBF16{b_dy, b_dt});
     SD_PHASE(p.g, ph);
     s2g_bpanel(bpanel_ptr(p.Pp, ch.gi), b_dy);
     s2g_bpanel(bpanel_ptr(p.Qp, ch.gi), b_dt);
@@ -457,6 +456,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     const int r = p.g.r;
 
     async_bpanel(b_dg, bpanel_ptr(p.DG, ch.gi));
+    async_bstate(b_Ct, bstate_ptr(p.CtCkB, ch.gi));
     cp_commit();
     load_gamma(p.gam, ch, s_gam);
     {
@@ -497,7 +497,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
             if ((threadIdx.x & 15) == 0) s_rk[i] = rk;
         }
     }
-    g2s_state_f32_to_bf16(b_Ct, state_ptr(p.CtCk, ch.gi));
     cp_wait<0>();
     __syncthreads();
     SD_PHASE(p.g, ph);
@@ -607,8 +606,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
-    trisolve_upper_b(f_lmT, 1.f, b_dl, b_ub);
-    __syncthreads();
+    trisolve_blocked<true, false>(f_lmT, 1.f, PanelBF16{b_dl, b_ub});
     SD_PHASE(p.g, ph);
     s2g_bpanel(bpanel_ptr(p.Ppp, ch.gi), b_dl);
     s2g_bpanel(bpanel_ptr(p.Qpp, ch.gi), b_ub);
@@ -658,6 +656,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
 
     async_bpanel(b_dr, bpanel_ptr(p.dRr, ch.gi));
     async_bstate(b_dC, bstate_ptr(p.dCeCk, ch.gi));
+    async_bstate(b_Ct, bstate_ptr(p.CtCkB, ch.gi));
     cp_commit();
     load_gamma(p.gam, ch, s_gam);
     {
@@ -684,7 +683,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
             store8_bsm(b_dl, i, c0, dl);
         }
     }
-    g2s_state_f32_to_bf16(b_Ct, state_ptr(p.CtCk, ch.gi));
     cp_wait<0>();
     __syncthreads();
     SD_PHASE(p.g, ph);

@@ -158,4 +158,133 @@ __device__ __forceinline__ void g2s_state_f32_to_bf16(bf16* sm, const float* st)
 }
 constexpr size_t BSTATE_BYTES = size_t(DP) * LDB * 2;  // a whole state in BF16
 
+// ---- blocked unit-triangular solve -------------------------------------------
+// Solves (I + sgn * T) X = RHS in place for the 2*DP columns of two shared panels,
+// T strictly triangular and stored by rows of the system in Mr (FP32, pitch LDA):
+//   UPPER == false: T lower  (Mr[i][k], k < i), rows solved first to last;
+//   UPPER == true : T upper  (Mr[i][k], k > i), rows solved last to first
+//                   (this is how a transposed lower system is passed in).
+// Entries outside the stated triangle must be exactly zero.
+// The 64 rows are cut into four 16-row blocks: the off-diagonal coupling
+// RHS_I -= sgn * T[I, solved] X[solved] runs on the tensor cores over all 16
+// warps (TF32, or split-TF32 "3x" when SPLIT for FP32-grade products), only the
+// 16x16 diagonal blocks are substituted on the FP32 pipes, one thread per column.
+struct PanelF32 {
+    float* p0;
+    float* p1;
+    __device__ __forceinline__ float get(int k, int n) const {
+        return (n < DP ? p0 : p1)[k * LDP + (n & (DP - 1))];
+    }
+    __device__ __forceinline__ void sub2(int i, int n, float v0, float v1) const {
+        float2* q = reinterpret_cast<float2*>((n < DP ? p0 : p1) + i * LDP + (n & (DP - 1)));
+        float2 o = *q;
+        *q = make_float2(o.x - v0, o.y - v1);
+    }
+    __device__ __forceinline__ float load(int i, int col) const { return get(i, col); }
+    __device__ __forceinline__ void store(int i, int col, float v) const {
+        (col < DP ? p0 : p1)[i * LDP + (col & (DP - 1))] = v;
+    }
+};
+struct PanelBF16 {
+    bf16* p0;
+    bf16* p1;
+    __device__ __forceinline__ float get(int k, int n) const {
+        return __bfloat162float((n < DP ? p0 : p1)[k * LDB + (n & (DP - 1))]);
+    }
+    __device__ __forceinline__ void sub2(int i, int n, float v0, float v1) const {
+        __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>((n < DP ? p0 : p1) + i * LDB + (n & (DP - 1)));
+        float2 o = __bfloat1622float2(*q);
+        *q = __floats2bfloat162_rn(o.x - v0, o.y - v1);
+    }
+    __device__ __forceinline__ float load(int i, int col) const { return get(i, col); }
+    __device__ __forceinline__ void store(int i, int col, float v) const {
+        (col < DP ? p0 : p1)[i * LDB + (col & (DP - 1))] = __float2bfloat16_rn(v);
+    }
+};
+
+template <bool UPPER, bool SPLIT, class Panel>
+__device__ __forceinline__ void trisolve_blocked(const float* Mr, float sgn, Panel P) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    constexpr int NB = CL / 16;
+#pragma unroll 1
+    for (int step = 0; step < NB; ++step) {
+        const int I = UPPER ? (NB - 1 - step) : step;
+        if (step > 0) {
+            // RHS[I] -= sgn * Mr[I rows][solved cols] * X[solved rows]; warp w owns columns 16w..16w+15
+            const int kbeg = UPPER ? 16 * (I + 1) : 0;
+            const int kend = UPPER ? CL : 16 * I;
+            const int r0 = 16 * I, n0 = 16 * warp;
+            float acc[2][4];
+            acc_zero<2>(acc);
+            for (int kk = kbeg; kk < kend; kk += 8) {
+                float af[4] = {Mr[(r0 + g) * LDA + kk + t], Mr[(r0 + g + 8) * LDA + kk + t],
+                               Mr[(r0 + g) * LDA + kk + t + 4], Mr[(r0 + g + 8) * LDA + kk + t + 4]};
+                uint32_t ah[4], al[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    ah[e] = f2tf32(af[e]);
+                    if (SPLIT) al[e] = f2tf32(af[e] - __uint_as_float(ah[e]));
+                }
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    float b0 = P.get(kk + t, n0 + nt * 8 + g), b1 = P.get(kk + t + 4, n0 + nt * 8 + g);
+                    uint32_t bh0 = f2tf32(b0), bh1 = f2tf32(b1);
+                    if (SPLIT) {
+                        uint32_t bl0 = f2tf32(b0 - __uint_as_float(bh0)), bl1 = f2tf32(b1 - __uint_as_float(bh1));
+                        mma_tf32(acc[nt], al[0], al[1], al[2], al[3], bh0, bh1);
+                        mma_tf32(acc[nt], ah[0], ah[1], ah[2], ah[3], bl0, bl1);
+                    }
+                    mma_tf32(acc[nt], ah[0], ah[1], ah[2], ah[3], bh0, bh1);
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const int j = n0 + nt * 8 + 2 * t;
+                P.sub2(r0 + g, j, sgn * acc[nt][0], sgn * acc[nt][1]);
+                P.sub2(r0 + g + 8, j, sgn * acc[nt][2], sgn * acc[nt][3]);
+            }
+            __syncthreads();
+        }
+        if (threadIdx.x < 2 * DP) {
+            // 16 x 16 diagonal block, one thread per right-hand-side column
+            const int col = threadIdx.x;
+            float x[16];
+#pragma unroll
+            for (int ii = 0; ii < 16; ++ii) x[ii] = P.load(16 * I + ii, col);
+            if (!UPPER) {
+#pragma unroll
+                for (int ii = 1; ii < 16; ++ii) {
+                    float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+                    for (int k4 = 0; k4 < ii; k4 += 4) {
+                        float4 m = *reinterpret_cast<const float4*>(Mr + (16 * I + ii) * LDA + 16 * I + k4);
+                        a0 = fmaf(m.x, x[k4], a0);
+                        a1 = fmaf(m.y, x[k4 + 1], a1);
+                        a0 = fmaf(m.z, x[k4 + 2], a0);
+                        a1 = fmaf(m.w, x[k4 + 3], a1);
+                    }
+                    x[ii] = fmaf(-sgn, a0 + a1, x[ii]);
+                }
+            } else {
+#pragma unroll
+                for (int ii = 14; ii >= 0; --ii) {
+                    float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+                    for (int k4 = ((ii + 1) & ~3); k4 < 16; k4 += 4) {
+                        float4 m = *reinterpret_cast<const float4*>(Mr + (16 * I + ii) * LDA + 16 * I + k4);
+                        a0 = fmaf(m.x, x[k4], a0);
+                        a1 = fmaf(m.y, x[k4 + 1], a1);
+                        a0 = fmaf(m.z, x[k4 + 2], a0);
+                        a1 = fmaf(m.w, x[k4 + 3], a1);
+                    }
+                    x[ii] = fmaf(-sgn, a0 + a1, x[ii]);
+                }
+            }
+#pragma unroll
+            for (int ii = 0; ii < 16; ++ii) P.store(16 * I + ii, col, x[ii]);
+        }
+        __syncthreads();
+    }
+}
+
 }  // namespace sd

@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan(ScanParams p) {
                 *reinterpret_cast<float2*>(sSt + row_a * LDT + cc) = make_float2(st[nt][0], st[nt][1]);
                 *reinterpret_cast<float2*>(sSt + row_b * LDT + cc) = make_float2(st[nt][2], st[nt][3]);
             }
-            if (p.ckb != nullptr) {
+            if (p.ckb != nullptr) {  // BF16 copy for the consumers that only contract in BF16
                 bf16* ck = p.ckb + gi * (long long)(DP * DP);
 #pragma unroll
                 for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
@@ -136,7 +136,8 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan(ScanParams p) {
                     *reinterpret_cast<__nv_bfloat162*>(ck + row_b * DP + col0 + cc) =
                         __floats2bfloat162_rn(st[nt][2], st[nt][3]);
                 }
-            } else {
+            }
+            if (p.ck != nullptr) {
                 float* ck = state_ptr(p.ck, gi);
 #pragma unroll
                 for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
