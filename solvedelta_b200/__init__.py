@@ -7,9 +7,11 @@ error types and autograd behaviour; the arithmetic runs in hand-written
 sm_100a CUDA kernels behind a C ABI (include/solvedelta_b200.h).
 """
 from ._lib import build, load
+from .packing import PackedSegments, build_packed_segments, pack_tokens, unpack_tokens
 from .ops import (
     SolveDeltaState,
     solvedelta_native,
+    solvedelta_segmented_native,
     solvedelta_residual_frame_native,
     solvedelta_zero_state,
 )
@@ -19,6 +21,11 @@ __all__ = [
     "build",
     "load",
     "solvedelta_native",
+    "solvedelta_segmented_native",
     "solvedelta_residual_frame_native",
+    "PackedSegments",
+    "build_packed_segments",
+    "pack_tokens",
+    "unpack_tokens",
     "solvedelta_zero_state",
 ]

@@ -22,6 +22,7 @@ from typing import NamedTuple, Optional, Tuple
 import torch
 
 from . import _lib
+from .packing import PackedSegments, pack_tokens, unpack_tokens
 
 
 class SolveDeltaState(NamedTuple):
@@ -295,9 +296,97 @@ def solvedelta_native(
         initial_state=initial_state, return_final_state=return_final_state)
 
 
+def _segment_rows(tensor: torch.Tensor, plan: PackedSegments, destination: torch.Tensor,
+                  padded_length: int) -> torch.Tensor:
+    """[B,T,...] -> [S,padded_length,...]: one row per segment, zero (neutral) tokens behind it."""
+    tokens = pack_tokens(tensor, plan).squeeze(0)
+    rows = tokens.new_zeros(plan.num_segments * padded_length, *tokens.shape[1:])
+    rows = rows.index_copy(0, destination, tokens)
+    return rows.view(plan.num_segments, padded_length, *tokens.shape[1:])
+
+
+def solvedelta_segmented_native(
+    u: torch.Tensor,
+    h: torch.Tensor,
+    q: torch.Tensor,
+    keys: torch.Tensor,
+    values: torch.Tensor,
+    associative_log_decay: torch.Tensor,
+    erase_raw: torch.Tensor,
+    write_raw: torch.Tensor,
+    geometry_write: torch.Tensor,
+    plan: PackedSegments,
+    *,
+    initial_state: Optional[SolveDeltaState] = None,
+    return_final_state: bool = False,
+) -> Tuple[torch.Tensor, Optional[SolveDeltaState]]:
+    """Masked / reset batches as one neutral-padded batch of reset-free segments.
+
+    Same contract as causallsso/ops/operator.py:96-193: invalid tokens produce
+    zero output and leave the state untouched, a reset token starts from the
+    zero state, the first segment of a batch row continues ``initial_state``
+    unless it opens with a reset, and the returned state of a row is that of
+    its last segment (or its initial state if the row has no valid token).
+    Zero raw operands are neutral for the recurrence (no decay, no write), so
+    segments are padded to the longest one without a mask inside the kernels.
+    """
+    batch, _, heads, rank = u.shape
+    value_dim = values.shape[-1]
+    if (plan.batch, plan.length) != tuple(u.shape[:2]):
+        raise ValueError("packed segment plan does not match the operator input")
+    if plan.num_tokens == 0:
+        output = values.new_zeros(batch, plan.length, heads, value_dim)
+        if not return_final_state:
+            return output, None
+        if initial_state is not None:
+            return output, initial_state
+        return output, solvedelta_zero_state(batch, heads, rank, value_dim, dtype=torch.float32,
+                                             device=u.device)
+
+    padded_length = plan.max_seqlen
+    position = torch.arange(plan.num_tokens, dtype=torch.long, device=u.device) - plan.cu_seqlens[plan.segment_ids]
+    destination = plan.segment_ids * padded_length + position
+    operands = [u, h, q, keys, values, associative_log_decay, erase_raw, write_raw]
+    rows = [_segment_rows(t, plan, destination, padded_length) for t in operands]
+    if geometry_write.shape == (batch, plan.length, heads):
+        gamma_rows = _segment_rows(geometry_write, plan, destination, padded_length)
+    else:
+        gamma_rows = geometry_write  # per-head rate: padded tokens have zero residual anyway
+
+    segment_initial = None
+    if initial_state is not None:
+        keep = plan.use_initial[:, None, None, None]
+        # index_select adds the cotangents of segments that share a batch row
+        predictor = initial_state.predictor.index_select(0, plan.segment_batch)
+        memory = initial_state.S.index_select(0, plan.segment_batch)
+        segment_initial = SolveDeltaState(
+            predictor=torch.where(keep, predictor, torch.zeros_like(predictor)),
+            S=torch.where(keep, memory, torch.zeros_like(memory)))
+
+    segment_output, segment_final = solvedelta_native(
+        *rows, gamma_rows, initial_state=segment_initial, return_final_state=return_final_state)
+    flat_out = segment_output.reshape(plan.num_segments * padded_length, heads, value_dim)
+    output = unpack_tokens(flat_out.index_select(0, destination).unsqueeze(0), plan)
+    if not return_final_state:
+        return output, None
+    if segment_final is None:
+        raise RuntimeError("segmented native owners did not return final state")
+    has_segment = (plan.last_segment >= 0)[:, None, None, None]
+    chosen = plan.last_segment.clamp_min(0)
+    predictor = segment_final.predictor.index_select(0, chosen)
+    memory = segment_final.S.index_select(0, chosen)
+    if initial_state is None:
+        base_predictor, base_memory = torch.zeros_like(predictor), torch.zeros_like(memory)
+    else:
+        base_predictor, base_memory = initial_state.predictor, initial_state.S
+    return output, SolveDeltaState(predictor=torch.where(has_segment, predictor, base_predictor),
+                                   S=torch.where(has_segment, memory, base_memory))
+
+
 __all__ = [
     "SolveDeltaState",
     "solvedelta_native",
+    "solvedelta_segmented_native",
     "solvedelta_residual_frame_native",
     "solvedelta_zero_state",
 ]

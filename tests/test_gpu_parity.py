@@ -260,3 +260,37 @@ def test_contract_errors_match_upstream_types():
         solvedelta_native(*a, initial_state=SolveDeltaState(dev["C0"][:, :, :8], dev["S0"]))
     with pytest.raises(TypeError, match="FP32"):
         solvedelta_native(*a, initial_state=SolveDeltaState(dev["C0"].double(), dev["S0"].double()))
+
+
+def test_segmented_masks_resets_and_vjp_match_checker():
+    """Masked tokens, a mid-row reset and an all-invalid batch row (upstream :932-1039)."""
+    from solvedelta_b200 import build_packed_segments, solvedelta_segmented_native
+
+    cpu, dev = make_inputs(2, 19, 1, 16, 16, seed=149, decay_scale=0.03, gamma_max=0.9)
+    valid = torch.tensor([[1, 1, 0, 1, 1, 1, 1, 0, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1], [0] * 19], dtype=torch.bool)
+    reset = torch.zeros_like(valid)
+    reset[0, 8] = True
+    plan = build_packed_segments(valid.cuda(), reset.cuda())
+    names = ("u", "h", "q", "keys", "values", "log_decay", "erase_raw", "write_raw", "geometry_write")
+    leaves = [dev[n].detach().clone().requires_grad_() for n in names]
+    state = SolveDeltaState(dev["C0"].clone().requires_grad_(), dev["S0"].clone().requires_grad_())
+    y, fin = solvedelta_segmented_native(*leaves, plan, initial_state=state, return_final_state=True)
+    yo, so = orc.forward(*oracle_args(cpu), initial_state=oracle_state(cpu), valid_mask=valid.numpy(),
+                         reset_mask=reset.numpy())
+    assert torch.equal(y[~valid.cuda()], torch.zeros_like(y[~valid.cuda()]))
+    assert max_rel(_np(y), yo) <= OUT_TOL
+    assert max_rel(_np(fin.predictor), so.predictor) <= 2e-3 and max_rel(_np(fin.S), so.S) <= 2e-3
+    # the all-invalid row returns its initial state untouched
+    assert torch.equal(fin.S[1], dev["S0"][1]) and torch.equal(fin.predictor[1], dev["C0"][1])
+    gen = torch.Generator().manual_seed(3)
+    dy = torch.randn(y.shape, generator=gen).to(torch.bfloat16)
+    dC, dS = torch.randn(fin.predictor.shape, generator=gen), torch.randn(fin.S.shape, generator=gen)
+    got = torch.autograd.grad((y, fin.predictor, fin.S), leaves + list(state), (dy.cuda(), dC.cuda(), dS.cuda()))
+    ref = orc.backward(*oracle_args(cpu), dy.double().numpy(), dC_T=dC.double().numpy(), dS_T=dS.double().numpy(),
+                       initial_state=oracle_state(cpu), valid_mask=valid.numpy(), reset_mask=reset.numpy())
+    d_er, d_wr = raw_gate_grads(cpu, ref)
+    want = [ref["u"], ref["h"], ref["q"], ref["keys"][:, :, :, None], ref["values"][:, :, :, None],
+            ref["log_decay"], d_er[:, :, :, None], d_wr[:, :, :, None], ref["geometry_write"], ref["C0"], ref["S0"]]
+    for name, g, w in zip(names + ("C0", "S0"), got, want):
+        assert torch.isfinite(g).all(), name
+        assert rel_l2(_np(g), w) <= GRAD_L2_TOL, (name, rel_l2(_np(g), w))
