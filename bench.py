@@ -279,19 +279,31 @@ KIB = 1024
 _F, _B, _S, _T, _M = 32 * KIB, 16 * KIB, 64 * KIB, 32 * KIB, 8 * KIB
 KERNEL_BYTES_PER_CHUNK = {
     "k_prep_fwd": 2 * _B + _F + 4 * _F,                         # u,h,g -> Upd,Qc,Ubar,G
-    "k_state_scan[C]": 4 * _F + _S,                             # P,Q,R -> X, ckpt
+    "k_state_scan[C]": 4 * _F + _S + _T,                        # P,Q,R -> X, FP32 + BF16 ckpt
     "k_primal_fwd": 2 * _B + 2 * _F + _S + _F,                  # u,k,G,Delta,Ct -> d
     "k_exterior_prep_fwd": 6 * _B + 3 * _F + 3 * _F + _B + _M,  # 6 operands,G,Delta,d -> Wd,Ud,Dt,Xg,Aqd
-    "k_state_scan[S]": 4 * _F + _S,
-    "k_output_fwd": _B + _M + _F + _S + _B,                     # Xg,Aqd,Zt,S -> y
+    "k_state_scan[S]": 3 * _F + _B + _T,                        # P,Q,R -> Z~ (BF16), BF16 ckpt
+    "k_output_fwd": _B + _M + _B + _T + _B,                     # Xg,Aqd,Zt,S -> y
     "k_exterior_prep_bwd": 5 * _B + 3 * _F + 6 * _B,            # u,k,q,er,dy,G,Delta,d -> Ag,Xg,Dyf,Dneg,Pp,Qp
     "k_state_scan_b[dS]": 6 * _B + _T,
     # Dyf,dR,Dneg,Xg,Ag,Zt,S,dSe + u,k,q,er,wr,v,G,Delta,d -> 5 partial panels, DG, dq,der,dv,dwr
     "k_exterior_pair_bwd": 6 * _B + 2 * _T + 6 * _B + 3 * _F + 6 * _B + 4 * _B,
-    "k_primal_bwd": 2 * _B + 2 * _F + _B + _S + 2 * _F + 5 * _B + _B,
+    # u,k,G,Delta,DG,Ct(bf16),dkPart,dDelta -> Khat,Rneg,Tpre,dk,Ppp,Qpp
+    "k_primal_bwd": 2 * _B + 2 * _F + _B + _T + 2 * _B + 6 * _B,
     "k_state_scan_b[dC]": 6 * _B + _T,
     # u,h,G,Delta,dRr,Ct,dCe,duPart,Tpre,dGPart,Xext -> du,dh,dlog_decay
-    "k_predictor_close_bwd": 2 * _B + 2 * _F + _B + _S + _T + 4 * _B + 2 * _B + _F,
+    "k_predictor_close_bwd": 2 * _B + 2 * _F + _B + _T + _T + 4 * _B + 2 * _B + _F,
+}
+
+
+# DRAM bytes per chunk task measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) on the
+# B=8, T=1024 case of this workload (profiles/chunk_kernels_B8_T1024_ncu_full.md); traffic is
+# proportional to the number of chunk tasks, so a full launch moves 4096 times these.
+KERNEL_DRAM_BYTES_PER_CHUNK = {
+    "k_prep_fwd": 145 * KIB, "k_state_scan[C]": 190 * KIB, "k_primal_fwd": 184 * KIB,
+    "k_exterior_prep_fwd": 284 * KIB, "k_state_scan[S]": 123 * KIB, "k_output_fwd": 80 * KIB,
+    "k_exterior_prep_bwd": 247 * KIB, "k_state_scan_b[dS]": 103 * KIB, "k_exterior_pair_bwd": 496 * KIB,
+    "k_primal_bwd": 249 * KIB, "k_state_scan_b[dC]": 104 * KIB, "k_predictor_close_bwd": 296 * KIB,
 }
 
 
@@ -315,6 +327,8 @@ def run_ours(opts, rank, world, local_rank):
     w = dict(WORKLOAD)
     if opts.case == "small":
         w.update(B=2, T=1024)
+    elif opts.case == "medium":
+        w.update(B=8, T=1024)
     B, T, H, r, V = w["B"], w["T"], w["H"], w["r"], w["V"]
     cpu = make_cpu_inputs(B, T, H, r, V, seed=rank_seed(0, rank))
     runner = DeviceStep(cpu, device)
@@ -370,7 +384,8 @@ def run_ours(opts, rank, world, local_rank):
         peak, peak_kind = _peaks()
         achieved = alg / (acc[top] * 1e-3) / 1e9
         roofline = {"bound": "hbm", "kernel": top, "achieved": round(achieved, 1), "peak": peak,
-                    "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": None,
+                    "unit": "GB/s", "frac": round(achieved / peak, 4),
+                    "traffic": KERNEL_DRAM_BYTES_PER_CHUNK.get(top, 0) * chunks or None,
                     "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": alg,
                     "launch_ms": round(acc[top], 4)}
         path_bytes = runner.tokens * H * BYTES_PER_TOKEN_HEAD + runner.streams * STATE_BYTES_PER_STREAM
@@ -481,8 +496,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--case", default="full", choices=["full", "small"],
-                    help="small = B=2, T=1024 (for profiler captures); the reported metric is defined on full")
+    ap.add_argument("--case", default="full", choices=["full", "medium", "small"],
+                    help="profiler captures only: medium = B=8, T=1024 (1024 chunk tasks, larger than L2), "
+                         "small = B=2, T=1024; the reported metric is defined on full")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg (profiler captures)")
     opts = ap.parse_args()
