@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
-    trisolve_blocked<false, true>(s_lm, 1.f, PanelF32{s_h, s_ut});
+    trisolve_blocked<false, false>(s_lm, 1.f, PanelF32{s_h, s_ut});
     SD_PHASE(p.g, ph);
     float* gUpd = panel_ptr(p.Upd, ch.gi);
     float* gQc = panel_ptr(p.Qc, ch.gi);
@@ -349,7 +349,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
-    trisolve_blocked<false, true>(s_aed, -1.f, PanelF32{s_ag, s_z});
+    trisolve_blocked<false, false>(s_aed, -1.f, PanelF32{s_ag, s_z});
     SD_PHASE(p.g, ph);
     s2g_panel(panel_ptr(p.Wd, ch.gi), s_ag);
     s2g_panel(panel_ptr(p.Ud, ch.gi), s_z);
