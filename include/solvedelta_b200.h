@@ -170,6 +170,83 @@ int sd_panel_info(const sd_shape *shape, int which, const char *name,
  * Negative = unknown name. */
 int sd_panel_kind(const sd_shape *shape, int which, const char *name);
 
+/* ------------------------------------------------------------------------
+ * Mixer glue on either side of the recurrence (all device pointers, BF16
+ * activations, FP32 parameters; every call is asynchronous on `stream`).
+ *
+ * sd_conv4_silu_*   depthwise causal convolution of width 4 + SiLU with a carried
+ *                   [B,D,3] state: causallsso/model.py:110-164 (_packed_conv; the
+ *                   CUDA branch calls the causal-conv1d extension, :119-136)
+ * sd_kda_gate_*     log_decay = -exp(A[h]) * softplus(raw + bias[h][c]):
+ *                   causallsso/model.py:375-390 (fused_kda_gate / its CPU formula)
+ * sd_norm_gate_*    y = x * rsqrt(mean(x^2)+eps) * w * sigmoid(gate) over rows of
+ *                   width V <= 128: causallsso/ops/norm_gate.py:19-43,162-217
+ */
+typedef struct {
+    int32_t B, T, D;
+    const void *x;                 /* BF16 [B,T,D] view, unit inner stride */
+    int64_t x_stride_b, x_stride_t;
+    const float *weight;           /* [D][4], tap 3 multiplies the current token */
+    const void *initial_state;     /* BF16 [B][D][3] or NULL (= zeros) */
+    void *y;                       /* out BF16 [B,T,D] contiguous */
+    void *final_state;             /* out BF16 [B][D][3] or NULL */
+} sd_conv4_forward_args;
+
+typedef struct {
+    int32_t B, T, D;
+    const void *x;
+    int64_t x_stride_b, x_stride_t;
+    const float *weight;
+    const void *initial_state;
+    const void *dy;                /* BF16 [B,T,D] contiguous */
+    void *dx;                      /* out BF16 [B,T,D] contiguous */
+    float *dweight;                /* out [D][4] */
+    void *dinitial_state;          /* out BF16 [B][D][3] or NULL */
+    void *scratch;                 /* sd_conv4_backward_scratch_bytes */
+    size_t scratch_bytes;
+} sd_conv4_backward_args;
+
+size_t sd_conv4_backward_scratch_bytes(int32_t B, int32_t T, int32_t D);
+int sd_conv4_silu_forward(const sd_conv4_forward_args *args, void *stream);
+int sd_conv4_silu_backward(const sd_conv4_backward_args *args, void *stream);
+
+typedef struct {
+    int64_t rows;                  /* B*T */
+    int32_t H, r;                  /* H*r <= 1024 */
+    const void *raw;               /* BF16 [rows][H][r] contiguous */
+    const float *log_rate;         /* A [H] */
+    const float *bias;             /* [H][r] */
+    float *log_decay;              /* out (forward) FP32 [rows][H][r] */
+    const float *dlog_decay;       /* backward input */
+    void *draw;                    /* backward out BF16 [rows][H][r] */
+    float *dlog_rate;              /* backward out [H] */
+    float *dbias;                  /* backward out [H][r] */
+    void *scratch;                 /* backward: sd_kda_gate_backward_scratch_bytes */
+    size_t scratch_bytes;
+} sd_kda_gate_args;
+
+size_t sd_kda_gate_backward_scratch_bytes(int64_t rows, int32_t H, int32_t r);
+int sd_kda_gate_forward(const sd_kda_gate_args *args, void *stream);
+int sd_kda_gate_backward(const sd_kda_gate_args *args, void *stream);
+
+typedef struct {
+    int64_t rows;                  /* B*T*H */
+    int32_t V;                     /* <= 128 */
+    float eps;
+    const void *x, *gate;          /* BF16 [rows][V] contiguous */
+    const float *weight;           /* [V] */
+    void *y;                       /* out (forward) BF16 [rows][V] */
+    const void *dy;                /* backward input BF16 */
+    void *dx, *dgate;              /* backward out BF16 */
+    float *dweight;                /* backward out [V] */
+    void *scratch;                 /* backward: sd_norm_gate_backward_scratch_bytes */
+    size_t scratch_bytes;
+} sd_norm_gate_args;
+
+size_t sd_norm_gate_backward_scratch_bytes(int64_t rows, int32_t V);
+int sd_norm_gate_forward(const sd_norm_gate_args *args, void *stream);
+int sd_norm_gate_backward(const sd_norm_gate_args *args, void *stream);
+
 const char *sd_status_string(int status);
 int sd_version(void);
 /* Tokens per chunk of the chunked scan (a private tuning constant upstream). */

@@ -7,6 +7,9 @@ error types and autograd behaviour; the arithmetic runs in hand-written
 sm_100a CUDA kernels behind a C ABI (include/solvedelta_b200.h).
 """
 from ._lib import build, load
+from .config import SolveDeltaConfig
+from .mixer_ops import conv4_silu, kda_decay_gate, rms_norm_gated
+from .model import RMSNormGated, SolveDelta, SolveDeltaLayerState
 from .packing import PackedSegments, build_packed_segments, pack_tokens, unpack_tokens
 from .ops import (
     SolveDeltaState,
@@ -17,6 +20,13 @@ from .ops import (
 )
 
 __all__ = [
+    "SolveDelta",
+    "SolveDeltaConfig",
+    "SolveDeltaLayerState",
+    "RMSNormGated",
+    "conv4_silu",
+    "kda_decay_gate",
+    "rms_norm_gated",
     "SolveDeltaState",
     "build",
     "load",

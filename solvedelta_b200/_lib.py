@@ -102,11 +102,45 @@ class DecodeArgs(ctypes.Structure):
         ("C", ctypes.c_void_p), ("S", ctypes.c_void_p), ("y", ctypes.c_void_p)])
 
 
+class Conv4ForwardArgs(ctypes.Structure):
+    _fields_ = [("B", ctypes.c_int32), ("T", ctypes.c_int32), ("D", ctypes.c_int32),
+                ("x", ctypes.c_void_p), ("x_stride_b", ctypes.c_int64), ("x_stride_t", ctypes.c_int64),
+                ("weight", ctypes.c_void_p), ("initial_state", ctypes.c_void_p), ("y", ctypes.c_void_p),
+                ("final_state", ctypes.c_void_p)]
+
+
+class Conv4BackwardArgs(ctypes.Structure):
+    _fields_ = [("B", ctypes.c_int32), ("T", ctypes.c_int32), ("D", ctypes.c_int32),
+                ("x", ctypes.c_void_p), ("x_stride_b", ctypes.c_int64), ("x_stride_t", ctypes.c_int64),
+                ("weight", ctypes.c_void_p), ("initial_state", ctypes.c_void_p), ("dy", ctypes.c_void_p),
+                ("dx", ctypes.c_void_p), ("dweight", ctypes.c_void_p), ("dinitial_state", ctypes.c_void_p),
+                ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t)]
+
+
+class KdaGateArgs(ctypes.Structure):
+    _fields_ = [("rows", ctypes.c_int64), ("H", ctypes.c_int32), ("r", ctypes.c_int32),
+                ("raw", ctypes.c_void_p), ("log_rate", ctypes.c_void_p), ("bias", ctypes.c_void_p),
+                ("log_decay", ctypes.c_void_p), ("dlog_decay", ctypes.c_void_p), ("draw", ctypes.c_void_p),
+                ("dlog_rate", ctypes.c_void_p), ("dbias", ctypes.c_void_p), ("scratch", ctypes.c_void_p),
+                ("scratch_bytes", ctypes.c_size_t)]
+
+
+class NormGateArgs(ctypes.Structure):
+    _fields_ = [("rows", ctypes.c_int64), ("V", ctypes.c_int32), ("eps", ctypes.c_float),
+                ("x", ctypes.c_void_p), ("gate", ctypes.c_void_p), ("weight", ctypes.c_void_p),
+                ("y", ctypes.c_void_p), ("dy", ctypes.c_void_p), ("dx", ctypes.c_void_p),
+                ("dgate", ctypes.c_void_p), ("dweight", ctypes.c_void_p), ("scratch", ctypes.c_void_p),
+                ("scratch_bytes", ctypes.c_size_t)]
+
+
 EXPORTS = (
     "sd_saved_bytes", "sd_forward_scratch_bytes", "sd_backward_scratch_bytes",
     "sd_forward", "sd_backward", "sd_decode_step", "sd_forward_launches",
     "sd_backward_launches", "sd_panel_info", "sd_status_string", "sd_version",
     "sd_chunk_tokens", "sd_profile_step", "sd_launch_name", "sd_forward_static", "sd_panel_kind", "sd_debug_timeline",
+    "sd_conv4_backward_scratch_bytes", "sd_conv4_silu_forward", "sd_conv4_silu_backward",
+    "sd_kda_gate_backward_scratch_bytes", "sd_kda_gate_forward", "sd_kda_gate_backward",
+    "sd_norm_gate_backward_scratch_bytes", "sd_norm_gate_forward", "sd_norm_gate_backward",
 )
 
 _lib = None
@@ -141,6 +175,17 @@ def load() -> ctypes.CDLL:
     lib.sd_panel_info.restype = ctypes.c_int
     lib.sd_panel_info.argtypes = [sp, ctypes.c_int, ctypes.c_char_p,
                                   ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)]
+    lib.sd_conv4_backward_scratch_bytes.restype = ctypes.c_size_t
+    lib.sd_conv4_backward_scratch_bytes.argtypes = [ctypes.c_int32] * 3
+    lib.sd_kda_gate_backward_scratch_bytes.restype = ctypes.c_size_t
+    lib.sd_kda_gate_backward_scratch_bytes.argtypes = [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32]
+    lib.sd_norm_gate_backward_scratch_bytes.restype = ctypes.c_size_t
+    lib.sd_norm_gate_backward_scratch_bytes.argtypes = [ctypes.c_int64, ctypes.c_int32]
+    for name, struct in (("sd_conv4_silu_forward", Conv4ForwardArgs), ("sd_conv4_silu_backward", Conv4BackwardArgs),
+                         ("sd_kda_gate_forward", KdaGateArgs), ("sd_kda_gate_backward", KdaGateArgs),
+                         ("sd_norm_gate_forward", NormGateArgs), ("sd_norm_gate_backward", NormGateArgs)):
+        getattr(lib, name).restype = ctypes.c_int
+        getattr(lib, name).argtypes = [ctypes.POINTER(struct), ctypes.c_void_p]
     lib.sd_debug_timeline.restype = None
     lib.sd_debug_timeline.argtypes = [ctypes.c_void_p]
     lib.sd_panel_kind.restype = ctypes.c_int

@@ -8,6 +8,7 @@
 #include "sd_common.cuh"
 #include "sd_decode.cuh"
 #include "sd_forward.cuh"
+#include "sd_mixer.cuh"
 #include "sd_scan.cuh"
 
 namespace {
@@ -488,6 +489,146 @@ int sd_forward_static(const sd_forward_args* a, void* stream_) {
     // Every panel of the workspace is written in full before any kernel reads
     // it, so nothing left by an earlier call has to be cleared.
     return sd_forward(&local, stream_);
+}
+
+// ---------------------------------------------------------------------------
+// Mixer glue
+namespace {
+int conv_tiles(int T) { return (T + CONV_TT - 1) / CONV_TT; }
+constexpr int GATE_ROWS_PER_BLOCK = 64;
+constexpr int NORM_ROWS_PER_BLOCK = 256;
+size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+}  // namespace
+
+size_t sd_conv4_backward_scratch_bytes(int32_t B, int32_t T, int32_t D) {
+    if (B <= 0 || T <= 0 || D <= 0) return 0;
+    return align256(size_t(B) * conv_tiles(T) * D * 4 * sizeof(float));
+}
+
+int sd_conv4_silu_forward(const sd_conv4_forward_args* a, void* stream_) {
+    if (!a || a->B <= 0 || a->T <= 0 || a->D <= 0 || !a->x || !a->weight || !a->y) return SD_ERR_INVALID_ARGUMENT;
+    ConvParams p{};
+    p.B = a->B; p.T = a->T; p.D = a->D;
+    p.x = reinterpret_cast<const __nv_bfloat16*>(a->x);
+    p.sb = a->x_stride_b; p.st = a->x_stride_t;
+    p.w = a->weight;
+    p.init = reinterpret_cast<const __nv_bfloat16*>(a->initial_state);
+    p.y = reinterpret_cast<__nv_bfloat16*>(a->y);
+    p.fin = reinterpret_cast<__nv_bfloat16*>(a->final_state);
+    dim3 grid((a->D + 2 * CONV_THREADS - 1) / (2 * CONV_THREADS), conv_tiles(a->T), a->B);
+    k_conv4_silu_fwd<<<grid, CONV_THREADS, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
+    return launch_status();
+}
+
+int sd_conv4_silu_backward(const sd_conv4_backward_args* a, void* stream_) {
+    if (!a || a->B <= 0 || a->T <= 0 || a->D <= 0 || !a->x || !a->weight || !a->dy || !a->dx || !a->dweight ||
+        !a->scratch)
+        return SD_ERR_INVALID_ARGUMENT;
+    if (a->scratch_bytes < sd_conv4_backward_scratch_bytes(a->B, a->T, a->D)) return SD_ERR_BUFFER_TOO_SMALL;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    ConvParams p{};
+    p.B = a->B; p.T = a->T; p.D = a->D;
+    p.x = reinterpret_cast<const __nv_bfloat16*>(a->x);
+    p.sb = a->x_stride_b; p.st = a->x_stride_t;
+    p.w = a->weight;
+    p.init = reinterpret_cast<const __nv_bfloat16*>(a->initial_state);
+    p.dy = reinterpret_cast<const __nv_bfloat16*>(a->dy);
+    p.dx = reinterpret_cast<__nv_bfloat16*>(a->dx);
+    p.dinit = reinterpret_cast<__nv_bfloat16*>(a->dinitial_state);
+    p.dw_part = reinterpret_cast<float*>(a->scratch);
+    const int tiles = conv_tiles(a->T);
+    dim3 grid((a->D + 2 * CONV_THREADS - 1) / (2 * CONV_THREADS), tiles, a->B);
+    k_conv4_silu_bwd<<<grid, CONV_THREADS, 0, stream>>>(p);
+    const long long n = (long long)a->D * 4;
+    k_column_sum<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p.dw_part, a->B * tiles, n, a->dweight);
+    return launch_status();
+}
+
+size_t sd_kda_gate_backward_scratch_bytes(int64_t rows, int32_t H, int32_t r) {
+    if (rows <= 0 || H <= 0 || r <= 0) return 0;
+    const size_t blocks = size_t((rows + GATE_ROWS_PER_BLOCK - 1) / GATE_ROWS_PER_BLOCK);
+    return align256((2 * blocks + 1) * size_t(H) * r * sizeof(float));
+}
+
+int sd_kda_gate_forward(const sd_kda_gate_args* a, void* stream_) {
+    if (!a || a->rows <= 0 || a->H <= 0 || a->r <= 0 || !a->raw || !a->log_rate || !a->bias || !a->log_decay)
+        return SD_ERR_INVALID_ARGUMENT;
+    GateParams p{};
+    p.N = a->rows; p.H = a->H; p.r = a->r;
+    p.raw = reinterpret_cast<const __nv_bfloat16*>(a->raw);
+    p.A = a->log_rate; p.bias = a->bias; p.out = a->log_decay;
+    const long long total = a->rows * a->H * a->r;
+    const unsigned blocks = (unsigned)((total + 256 * 8 - 1) / (256 * 8));
+    k_kda_gate_fwd<<<blocks ? blocks : 1, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
+    return launch_status();
+}
+
+int sd_kda_gate_backward(const sd_kda_gate_args* a, void* stream_) {
+    if (!a || a->rows <= 0 || a->H <= 0 || a->r <= 0 || !a->raw || !a->log_rate || !a->bias || !a->dlog_decay ||
+        !a->draw || !a->dlog_rate || !a->dbias || !a->scratch)
+        return SD_ERR_INVALID_ARGUMENT;
+    const int HR = a->H * a->r;
+    if (a->scratch_bytes < sd_kda_gate_backward_scratch_bytes(a->rows, a->H, a->r)) return SD_ERR_BUFFER_TOO_SMALL;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    const int blocks = (int)((a->rows + GATE_ROWS_PER_BLOCK - 1) / GATE_ROWS_PER_BLOCK);
+    GateParams p{};
+    p.N = a->rows; p.H = a->H; p.r = a->r;
+    p.raw = reinterpret_cast<const __nv_bfloat16*>(a->raw);
+    p.A = a->log_rate; p.bias = a->bias; p.dout = a->dlog_decay;
+    p.draw = reinterpret_cast<__nv_bfloat16*>(a->draw);
+    p.dbias_part = reinterpret_cast<float*>(a->scratch);
+    p.dA_part = p.dbias_part + (size_t)blocks * HR;
+    float* dA_cols = p.dA_part + (size_t)blocks * HR;
+    p.rows_per_block = GATE_ROWS_PER_BLOCK;
+    k_kda_gate_bwd<<<dim3(blocks, (HR + 255) / 256), 256, 0, stream>>>(p);
+    k_column_sum<<<(HR + 255) / 256, 256, 0, stream>>>(p.dbias_part, blocks, HR, a->dbias);
+    k_column_sum<<<(HR + 255) / 256, 256, 0, stream>>>(p.dA_part, blocks, HR, dA_cols);
+    k_group_sum<<<(a->H + 63) / 64, 64, 0, stream>>>(dA_cols, a->H, a->r, a->dlog_rate);
+    return launch_status();
+}
+
+size_t sd_norm_gate_backward_scratch_bytes(int64_t rows, int32_t V) {
+    if (rows <= 0 || V <= 0) return 0;
+    const size_t blocks = size_t((rows + NORM_ROWS_PER_BLOCK - 1) / NORM_ROWS_PER_BLOCK);
+    return align256(blocks * size_t(V) * sizeof(float));
+}
+
+int sd_norm_gate_forward(const sd_norm_gate_args* a, void* stream_) {
+    if (!a || a->rows <= 0 || a->V <= 0 || !a->x || !a->gate || !a->weight || !a->y) return SD_ERR_INVALID_ARGUMENT;
+    if (a->V > DP) return SD_ERR_UNSUPPORTED_SHAPE;
+    NormParams p{};
+    p.N = a->rows; p.V = a->V; p.eps = a->eps;
+    p.x = reinterpret_cast<const __nv_bfloat16*>(a->x);
+    p.gate = reinterpret_cast<const __nv_bfloat16*>(a->gate);
+    p.w = a->weight;
+    p.out = reinterpret_cast<__nv_bfloat16*>(a->y);
+    long long blocks = (a->rows + 15) / 16;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    k_norm_gate_fwd<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
+    return launch_status();
+}
+
+int sd_norm_gate_backward(const sd_norm_gate_args* a, void* stream_) {
+    if (!a || a->rows <= 0 || a->V <= 0 || !a->x || !a->gate || !a->weight || !a->dy || !a->dx || !a->dgate ||
+        !a->dweight || !a->scratch)
+        return SD_ERR_INVALID_ARGUMENT;
+    if (a->V > DP) return SD_ERR_UNSUPPORTED_SHAPE;
+    if (a->scratch_bytes < sd_norm_gate_backward_scratch_bytes(a->rows, a->V)) return SD_ERR_BUFFER_TOO_SMALL;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    const int blocks = (int)((a->rows + NORM_ROWS_PER_BLOCK - 1) / NORM_ROWS_PER_BLOCK);
+    NormParams p{};
+    p.N = a->rows; p.V = a->V; p.eps = a->eps;
+    p.x = reinterpret_cast<const __nv_bfloat16*>(a->x);
+    p.gate = reinterpret_cast<const __nv_bfloat16*>(a->gate);
+    p.w = a->weight;
+    p.dout = reinterpret_cast<const __nv_bfloat16*>(a->dy);
+    p.dx = reinterpret_cast<__nv_bfloat16*>(a->dx);
+    p.dgate = reinterpret_cast<__nv_bfloat16*>(a->dgate);
+    p.dw_part = reinterpret_cast<float*>(a->scratch);
+    p.rows_per_block = NORM_ROWS_PER_BLOCK;
+    k_norm_gate_bwd<<<blocks, 256, 0, stream>>>(p);
+    k_column_sum<<<(a->V + 255) / 256, 256, 0, stream>>>(p.dw_part, blocks, a->V, a->dweight);
+    return launch_status();
 }
 
 int sd_decode_step(const sd_decode_args* a, void* stream_) {

@@ -1,0 +1,306 @@
+// Mixer glue around the chunked recurrence: depthwise causal conv4 + SiLU,
+// the per-channel decay gate, and the sigmoid-gated RMSNorm, each with its
+// reverse.  All are one pass over their operands (HBM bound); parameter
+// gradients are reduced deterministically (per-CTA partials, then a column sum).
+//
+// Upstream counterparts: causallsso/model.py:110-164 (conv4 + SiLU with
+// [B,D,3] state), model.py:375-390 (decay gate -exp(A) softplus(raw + bias)),
+// causallsso/ops/norm_gate.py:19-43 (y = x rstd w sigmoid(gate)).
+#pragma once
+#include "sd_common.cuh"
+
+namespace sd {
+
+constexpr int CONV_TT = 64;        // tokens per CTA of the conv kernels
+constexpr int CONV_THREADS = 128;  // each thread owns two adjacent channels
+
+struct ConvParams {
+    int B, T, D;
+    const __nv_bfloat16* x;  // [B,T,D] view: element strides sb, st, unit inner stride
+    long long sb, st;
+    const float* w;              // [D][4]
+    const __nv_bfloat16* init;   // [B][D][3] or null
+    __nv_bfloat16* y;            // [B,T,D] contiguous
+    __nv_bfloat16* fin;          // [B][D][3] or null
+    // backward
+    const __nv_bfloat16* dy;     // [B,T,D] contiguous
+    __nv_bfloat16* dx;           // [B,T,D] contiguous
+    __nv_bfloat16* dinit;        // [B][D][3] or null
+    float* dw_part;              // [B * tiles][D][4]
+};
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + __expf(-z)); }
+__device__ __forceinline__ float silu_grad_f(float z) {
+    const float s = 1.f / (1.f + __expf(-z));
+    return s * (1.f + z * (1.f - s));
+}
+
+// input at (virtual) time t: the sequence for t >= 0, the carried state for -3 <= t < 0
+__device__ __forceinline__ float2 conv_input(const ConvParams& p, int b, int t, int d, bool two) {
+    float2 v = make_float2(0.f, 0.f);
+    if (t >= 0) {
+        if (t < p.T) {
+            const __nv_bfloat16* row = p.x + b * p.sb + (long long)t * p.st + d;
+            v.x = __bfloat162float(row[0]);
+            if (two) v.y = __bfloat162float(row[1]);
+        }
+    } else if (p.init != nullptr) {
+        const __nv_bfloat16* s = p.init + ((long long)b * p.D + d) * 3 + (t + 3);
+        v.x = __bfloat162float(s[0]);
+        if (two) v.y = __bfloat162float(s[3]);
+    }
+    return v;
+}
+
+__global__ void __launch_bounds__(CONV_THREADS) k_conv4_silu_fwd(ConvParams p) {
+    const int d = (blockIdx.x * CONV_THREADS + threadIdx.x) * 2;
+    const int t0 = blockIdx.y * CONV_TT, b = blockIdx.z;
+    if (d >= p.D) return;
+    const bool two = d + 1 < p.D;
+    float wa[4], wb[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        wa[j] = p.w[d * 4 + j];
+        wb[j] = two ? p.w[(d + 1) * 4 + j] : 0.f;
+    }
+    float2 x0 = conv_input(p, b, t0 - 3, d, two), x1 = conv_input(p, b, t0 - 2, d, two),
+           x2 = conv_input(p, b, t0 - 1, d, two);
+    const int t1 = min(t0 + CONV_TT, p.T);
+    for (int t = t0; t < t1; ++t) {
+        const float2 x3 = conv_input(p, b, t, d, two);
+        const float za = wa[0] * x0.x + wa[1] * x1.x + wa[2] * x2.x + wa[3] * x3.x;
+        const float zb = wb[0] * x0.y + wb[1] * x1.y + wb[2] * x2.y + wb[3] * x3.y;
+        __nv_bfloat16* out = p.y + ((long long)b * p.T + t) * p.D + d;
+        out[0] = __float2bfloat16_rn(silu_f(za));
+        if (two) out[1] = __float2bfloat16_rn(silu_f(zb));
+        x0 = x1; x1 = x2; x2 = x3;
+    }
+    if (p.fin != nullptr && t1 == p.T) {
+        // carried state = the last three inputs (the old state shows through when T < 3)
+        __nv_bfloat16* s = p.fin + ((long long)b * p.D + d) * 3;
+        s[0] = __float2bfloat16_rn(x0.x); s[1] = __float2bfloat16_rn(x1.x); s[2] = __float2bfloat16_rn(x2.x);
+        if (two) {
+            s[3] = __float2bfloat16_rn(x0.y); s[4] = __float2bfloat16_rn(x1.y); s[5] = __float2bfloat16_rn(x2.y);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(CONV_THREADS) k_conv4_silu_bwd(ConvParams p) {
+    const int d = (blockIdx.x * CONV_THREADS + threadIdx.x) * 2;
+    const int t0 = blockIdx.y * CONV_TT, b = blockIdx.z;
+    if (d >= p.D) return;
+    const bool two = d + 1 < p.D;
+    float wa[4], wb[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        wa[j] = p.w[d * 4 + j];
+        wb[j] = two ? p.w[(d + 1) * 4 + j] : 0.f;
+    }
+    // sliding windows: x[t-3..t] and g[t-3..t] with g = dy * silu'(pre); g is zero outside [0,T).
+    // dx[t-3] = w0 g[t] + w1 g[t-1] + w2 g[t-2] + w3 g[t-3]; tile 0 also emits t-3 < 0 (the state).
+    // (g of tokens before the tile only feeds gradients that the previous tile emits)
+    float2 x0 = conv_input(p, b, t0 - 3, d, two), x1 = conv_input(p, b, t0 - 2, d, two),
+           x2 = conv_input(p, b, t0 - 1, d, two);
+    float2 g0 = make_float2(0.f, 0.f), g1 = g0, g2 = g0;
+    float dwa[4] = {0.f, 0.f, 0.f, 0.f}, dwb[4] = {0.f, 0.f, 0.f, 0.f};
+    const int t_end = min(t0 + CONV_TT, p.T);
+    for (int t = t0; t < t_end + 3; ++t) {
+        const float2 x3 = conv_input(p, b, t, d, two);
+        float2 g3 = make_float2(0.f, 0.f);
+        if (t < p.T) {
+            const float za = wa[0] * x0.x + wa[1] * x1.x + wa[2] * x2.x + wa[3] * x3.x;
+            const float zb = wb[0] * x0.y + wb[1] * x1.y + wb[2] * x2.y + wb[3] * x3.y;
+            const __nv_bfloat16* go = p.dy + ((long long)b * p.T + t) * p.D + d;
+            g3.x = __bfloat162float(go[0]) * silu_grad_f(za);
+            if (two) g3.y = __bfloat162float(go[1]) * silu_grad_f(zb);
+            if (t >= t0 && t < t_end) {  // weight gradient: own tile only
+                dwa[0] += g3.x * x0.x; dwa[1] += g3.x * x1.x; dwa[2] += g3.x * x2.x; dwa[3] += g3.x * x3.x;
+                dwb[0] += g3.y * x0.y; dwb[1] += g3.y * x1.y; dwb[2] += g3.y * x2.y; dwb[3] += g3.y * x3.y;
+            }
+        }
+        const int tq = t - 3;  // the input whose gradient is now complete
+        const float da = wa[0] * g3.x + wa[1] * g2.x + wa[2] * g1.x + wa[3] * g0.x;
+        const float db = wb[0] * g3.y + wb[1] * g2.y + wb[2] * g1.y + wb[3] * g0.y;
+        if (tq >= t0 && tq < t_end) {
+            __nv_bfloat16* out = p.dx + ((long long)b * p.T + tq) * p.D + d;
+            out[0] = __float2bfloat16_rn(da);
+            if (two) out[1] = __float2bfloat16_rn(db);
+        } else if (tq < 0 && t0 == 0 && p.dinit != nullptr) {
+            __nv_bfloat16* s = p.dinit + ((long long)b * p.D + d) * 3 + (tq + 3);
+            s[0] = __float2bfloat16_rn(da);
+            if (two) s[3] = __float2bfloat16_rn(db);
+        }
+        x0 = x1; x1 = x2; x2 = x3;
+        g0 = g1; g1 = g2; g2 = g3;
+    }
+    float* part = p.dw_part + ((long long)(b * gridDim.y + blockIdx.y) * p.D + d) * 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        part[j] = dwa[j];
+        if (two) part[4 + j] = dwb[j];
+    }
+}
+
+// out[n] = sum_p partial[p][n]: deterministic column sum of per-CTA partials.
+__global__ void k_column_sum(const float* part, int P, long long N, float* out) {
+    const long long n = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= N) return;
+    float acc = 0.f;
+    for (int q = 0; q < P; ++q) acc += part[(long long)q * N + n];
+    out[n] = acc;
+}
+
+// out[g] = sum_c in[g*width + c]
+__global__ void k_group_sum(const float* in, int groups, int width, float* out) {
+    const int g = blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= groups) return;
+    float acc = 0.f;
+    for (int c = 0; c < width; ++c) acc += in[(long long)g * width + c];
+    out[g] = acc;
+}
+
+// ---- decay gate: log_decay = -exp(A[h]) * softplus(raw + bias[h][c]) ---------
+struct GateParams {
+    long long N;  // B*T rows
+    int H, r;
+    const __nv_bfloat16* raw;  // [N][H][r]
+    const float* A;            // [H]
+    const float* bias;         // [H][r]
+    float* out;                // [N][H][r]
+    const float* dout;         // backward
+    __nv_bfloat16* draw;
+    float* dA_part;            // [blocks][H]   (padded: one row of H*r + H per block, see host)
+    float* dbias_part;         // [blocks][H][r]
+    int rows_per_block;
+};
+
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(__expf(z)); }
+
+__global__ void k_kda_gate_fwd(GateParams p) {
+    const long long total = p.N * p.H * p.r;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int hc = (int)(i % (p.H * p.r));
+        const int h = hc / p.r;
+        const float z = __bfloat162float(p.raw[i]) + p.bias[hc];
+        p.out[i] = -__expf(p.A[h]) * softplus_f(z);
+    }
+}
+
+// blockIdx.x = block of rows, blockIdx.y = block of 256 (h, c) columns; one column per thread.
+__global__ void __launch_bounds__(256) k_kda_gate_bwd(GateParams p) {
+    const int hc = blockIdx.y * 256 + threadIdx.x, HR = p.H * p.r;
+    if (hc >= HR) return;
+    const int h = hc / p.r;
+    const float rate = -__expf(p.A[h]), bias = p.bias[hc];
+    const long long n0 = (long long)blockIdx.x * p.rows_per_block;
+    const long long n1 = (n0 + p.rows_per_block < p.N) ? n0 + p.rows_per_block : p.N;
+    float sum_b = 0.f, sum_a = 0.f;
+    for (long long n = n0; n < n1; ++n) {
+        const long long i = n * HR + hc;
+        const float z = __bfloat162float(p.raw[i]) + bias;
+        const float g = p.dout[i];
+        const float sig = 1.f / (1.f + __expf(-z));
+        const float dz = g * rate * sig;
+        p.draw[i] = __float2bfloat16_rn(dz);
+        sum_b += dz;
+        sum_a += g * rate * softplus_f(z);  // d/dA of -exp(A) softplus = out
+    }
+    p.dbias_part[(long long)blockIdx.x * HR + hc] = sum_b;
+    p.dA_part[(long long)blockIdx.x * HR + hc] = sum_a;  // summed over c on the host side of the ABI
+}
+
+// ---- sigmoid-gated RMSNorm over rows of width V <= 128 -------------------------
+struct NormParams {
+    long long N;  // rows
+    int V;
+    float eps;
+    const __nv_bfloat16* x;
+    const __nv_bfloat16* gate;
+    const float* w;
+    __nv_bfloat16* out;
+    const __nv_bfloat16* dout;
+    __nv_bfloat16* dx;
+    __nv_bfloat16* dgate;
+    float* dw_part;  // [blocks][V]
+    int rows_per_block;
+};
+
+// 16 lanes per row, 8 channels per lane; 256 threads = 16 rows at a time.
+__global__ void __launch_bounds__(256) k_norm_gate_fwd(NormParams p) {
+    const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
+    for (long long base = (long long)blockIdx.x * 16; base < p.N; base += (long long)gridDim.x * 16) {
+        const long long row = base + lr;
+        const bool live = row < p.N;
+        float x[8], g[8];
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const bool ok = live && c0 + e < p.V;
+            x[e] = ok ? __bfloat162float(p.x[row * p.V + c0 + e]) : 0.f;
+            g[e] = ok ? __bfloat162float(p.gate[row * p.V + c0 + e]) : 0.f;
+            ss = fmaf(x[e], x[e], ss);
+        }
+        ss = row_sum16(ss);
+        const float rstd = rsqrtf(ss / p.V + p.eps);
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            if (live && c0 + e < p.V)
+                p.out[row * p.V + c0 + e] = __float2bfloat16_rn(x[e] * rstd * p.w[c0 + e] * sigmoidf_(g[e]));
+    }
+}
+
+__global__ void __launch_bounds__(256) k_norm_gate_bwd(NormParams p) {
+    __shared__ float s_dw[16][DP];
+    const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
+    float dw[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const long long n0 = (long long)blockIdx.x * p.rows_per_block;
+    const long long n1 = (n0 + p.rows_per_block < p.N) ? n0 + p.rows_per_block : p.N;
+    for (long long base = n0; base < n1; base += 16) {
+        const long long row = base + lr;
+        const bool live = row < n1;
+        float x[8], g[8], dy[8];
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const bool ok = live && c0 + e < p.V;
+            x[e] = ok ? __bfloat162float(p.x[row * p.V + c0 + e]) : 0.f;
+            g[e] = ok ? __bfloat162float(p.gate[row * p.V + c0 + e]) : 0.f;
+            dy[e] = ok ? __bfloat162float(p.dout[row * p.V + c0 + e]) : 0.f;
+            ss = fmaf(x[e], x[e], ss);
+        }
+        ss = row_sum16(ss);
+        const float rstd = rsqrtf(ss / p.V + p.eps);
+        // y = xn * w * s with xn = x rstd, s = sigmoid(g)
+        float dxn[8], dot = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float s = sigmoidf_(g[e]);
+            const float wv = (c0 + e < p.V) ? p.w[c0 + e] : 0.f;
+            const float xn = x[e] * rstd;
+            dw[e] += dy[e] * xn * s;
+            dxn[e] = dy[e] * wv * s;
+            dot = fmaf(dxn[e], xn, dot);
+            g[e] = dy[e] * xn * wv * s * (1.f - s);  // d gate
+        }
+        dot = row_sum16(dot) / p.V;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            if (live && c0 + e < p.V) {
+                p.dx[row * p.V + c0 + e] = __float2bfloat16_rn((dxn[e] - x[e] * rstd * dot) * rstd);
+                p.dgate[row * p.V + c0 + e] = __float2bfloat16_rn(g[e]);
+            }
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s_dw[lr][c0 + e] = dw[e];
+    __syncthreads();
+    if (threadIdx.x < p.V) {
+        float acc = 0.f;
+#pragma unroll
+        for (int q = 0; q < 16; ++q) acc += s_dw[q][threadIdx.x];
+        p.dw_part[(long long)blockIdx.x * p.V + threadIdx.x] = acc;
+    }
+}
+
+}  // namespace sd

@@ -1,0 +1,145 @@
+"""SolveDelta mixer: fused input projection, conv4 + SiLU, decay / geometry
+gates, the chunked recurrence, sigmoid-gated RMSNorm and output projection.
+
+Same parameter names, projection layout and call signature as upstream's
+``SolveDelta`` (causallsso/model.py:27-474), so upstream state dicts load:
+``in_proj`` packs (q, k, v, u, h, erase_raw, write_raw, geometry_raw,
+decay_hidden, output_gate_hidden) and is padded to a multiple of 64 columns
+(model.py:39-60); q/k/v go through the conv, the other slices are read in
+place as strided views of the projection row; decay and geometry gates are
+evaluated in FP32.  The module-level name ``solvedelta_native`` is the call
+site upstream's tests patch (tests/model/test_modeling_solvedelta.py:343).
+
+GEMMs run through torch (cuBLAS); everything else is this package's CUDA
+library.  Inputs must be BF16 CUDA tensors: there is no CPU path here
+(upstream's CPU branch is model.py:430-462).
+"""
+from __future__ import annotations
+
+import math
+from typing import NamedTuple, Optional
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from .config import SolveDeltaConfig
+from .mixer_ops import conv4_silu, kda_decay_gate, rms_norm_gated
+from .ops import SolveDeltaState, solvedelta_native
+
+
+class SolveDeltaLayerState(NamedTuple):
+    operator: SolveDeltaState
+    conv: Optional[torch.Tensor]
+
+
+class RMSNormGated(nn.Module):
+    """y = RMSNorm(x) * weight * sigmoid(gate) (causallsso/ops/norm_gate.py:162-217)."""
+
+    def __init__(self, hidden_size: int, eps: float = 1e-6) -> None:
+        super().__init__()
+        self.hidden_size = hidden_size
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(hidden_size))
+
+    def forward(self, x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+        return rms_norm_gated(x, gate, self.weight, self.eps)
+
+
+class SolveDelta(nn.Module):
+    def __init__(self, config: SolveDeltaConfig) -> None:
+        super().__init__()
+        self.config = config
+        heads = config.num_heads
+        width = config.resolved_head_k_dim
+        value_width = config.resolved_head_v_dim
+        gate_rank = value_width
+        self.projection_sizes = (
+            heads * width, heads * width, heads * value_width,   # q, k, v (through the conv)
+            heads * width, heads * width,                         # u, h
+            heads * width, heads * value_width,                   # erase_raw, write_raw
+            heads, gate_rank, gate_rank)                          # geometry_raw, decay_hidden, gate_hidden
+        self.projection_width = sum(self.projection_sizes)
+        self.projection_padding = (-self.projection_width) % 64
+        self.in_proj = nn.Linear(config.hidden_size, self.projection_width + self.projection_padding,
+                                 bias=config.bias)
+        self.output_proj = nn.Linear(heads * value_width, config.hidden_size, bias=config.bias)
+        self.decay_proj = nn.Linear(gate_rank, heads * width, bias=False)
+        self.output_gate_proj = nn.Linear(gate_rank, heads * value_width, bias=True)
+        self.output_norm = RMSNormGated(value_width, eps=config.norm_eps)
+        if config.use_short_conv:
+            self.conv_weight = nn.Parameter(torch.empty(sum(self.projection_sizes[:3]), 4))
+            nn.init.kaiming_uniform_(self.conv_weight, a=5 ** 0.5)
+        self.geometry_write_bias = nn.Parameter(torch.full((heads,), math.log(9.0), dtype=torch.float32))
+        rate = torch.empty(heads, dtype=torch.float32).uniform_(1, 16)
+        self.associative_log_rate = nn.Parameter(rate.log())
+        step = torch.exp(torch.rand(heads, width, dtype=torch.float32) * (math.log(0.1) - math.log(0.001))
+                         + math.log(0.001)).clamp_min_(1e-4)
+        self.associative_decay_bias = nn.Parameter(step + torch.log(-torch.expm1(-step)))
+        for parameter in (self.geometry_write_bias, self.associative_log_rate, self.associative_decay_bias):
+            parameter._no_weight_decay = True
+
+    @staticmethod
+    def _linear(layer: nn.Linear, x: torch.Tensor) -> torch.Tensor:
+        bias = None if layer.bias is None else layer.bias.to(x.dtype)
+        return F.linear(x, layer.weight.to(x.dtype), bias)
+
+    def forward(self, hidden_states: torch.Tensor, *, initial_state: Optional[SolveDeltaLayerState] = None,
+                valid_mask: Optional[torch.Tensor] = None, reset_mask: Optional[torch.Tensor] = None,
+                geometry_enabled: bool = True, associative_decay_enabled: bool = True,
+                return_final_state: bool = False):
+        if hidden_states.ndim != 3:
+            raise ValueError("hidden_states must have shape [B,T,hidden_size]")
+        batch, length, hidden_width = hidden_states.shape
+        if hidden_width != self.config.hidden_size:
+            raise ValueError("hidden state width does not match the configuration")
+        if hidden_states.device.type != "cuda" or hidden_states.dtype != torch.bfloat16:
+            raise TypeError("the B200 mixer requires BF16 CUDA hidden states (no CPU path)")
+        if valid_mask is not None or reset_mask is not None:
+            raise NotImplementedError("masked / reset batches are not wired into the B200 mixer yet; "
+                                      "use solvedelta_segmented_native on the operator")
+        heads = self.config.num_heads
+        width = self.config.resolved_head_k_dim
+        value_width = self.config.resolved_head_v_dim
+        sizes = self.projection_sizes
+        row = self._linear(self.in_proj, hidden_states)          # [B,T,P] BF16, slices stay views
+        offsets = [0]
+        for size in sizes:
+            offsets.append(offsets[-1] + size)
+        piece = lambda i: row[..., offsets[i]:offsets[i + 1]]
+        conv_state = initial_state.conv if initial_state is not None else None
+        if self.config.use_short_conv:
+            qkv, final_conv = conv4_silu(row[..., :offsets[3]], self.conv_weight, conv_state, return_final_state)
+            q_raw, key_raw, value_raw = qkv.split(sizes[:3], dim=-1)
+        else:
+            q_raw, key_raw, value_raw = (F.silu(piece(i)) for i in range(3))
+            final_conv = None
+        view = lambda x, size: x.unflatten(-1, (heads, size))  # stays a view of the projection row
+        u, h = view(piece(3), width), view(piece(4), width)
+        q = view(q_raw, width)
+        keys = view(key_raw, width).unsqueeze(-2)
+        values = view(value_raw, value_width).unsqueeze(-2)
+        erase_raw = view(piece(5), width).unsqueeze(-2)
+        write_raw = view(piece(6), value_width).unsqueeze(-2)
+        associative_raw = self._linear(self.decay_proj, piece(8)).view(batch, length, heads, width)
+        output_gate = self._linear(self.output_gate_proj, piece(9)).view(batch, length, heads, value_width)
+        log_decay = kda_decay_gate(associative_raw, self.associative_log_rate, self.associative_decay_bias)
+        geometry_write = torch.sigmoid(piece(7).float() + self.geometry_write_bias.float().view(1, 1, heads))
+        if not geometry_enabled:
+            geometry_write = torch.zeros_like(geometry_write)
+        if not associative_decay_enabled:
+            log_decay = torch.zeros_like(log_decay)
+        operator_initial = initial_state.operator if initial_state is not None else None
+        output, operator_state = solvedelta_native(
+            u, h, q, keys, values, log_decay, erase_raw, write_raw, geometry_write,
+            initial_state=operator_initial, return_final_state=return_final_state)
+        normed = self.output_norm(output, output_gate)
+        result = self._linear(self.output_proj, normed.reshape(batch, length, heads * value_width))
+        if not return_final_state:
+            return result
+        if operator_state is None:
+            raise RuntimeError("operator did not return the requested final state")
+        return result, SolveDeltaLayerState(operator_state, final_conv)
+
+
+__all__ = ["RMSNormGated", "SolveDelta", "SolveDeltaLayerState"]

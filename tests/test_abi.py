@@ -18,7 +18,7 @@ def lib():
 def _declared_functions():
     text = open(_lib.HEADER_PATH).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(sd_[a-z_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(sd_[a-z0-9_]+)\s*\(", text)))
 
 
 def test_header_and_loader_agree():

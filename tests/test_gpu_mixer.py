@@ -1,0 +1,226 @@
+"""Mixer glue kernels and the SolveDelta mixer module on the GPU vs the FP64
+numpy checker (oracle/mixer_oracle.py, pinned to upstream vectors in
+tests/test_mixer_oracle.py).
+
+Cases follow upstream tests/model/test_modeling_solvedelta.py: projection
+layout (:321-341), forward/backward through the mixer (:343-420), state
+continuation across a split (:423-470).
+
+The checker sees exactly the numbers the GPU sees (inputs and weights rounded
+to the dtype the CUDA path reads), so the tolerance covers only the BF16
+activations in between: max relative error (max|a-b| / max|b|) <= 2e-2 on
+outputs and gradients, 1e-3 on FP32 operator states.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import mixer_oracle as mo
+from solvedelta_b200 import (SolveDelta, SolveDeltaConfig, SolveDeltaLayerState, SolveDeltaState, conv4_silu,
+                             kda_decay_gate, rms_norm_gated)
+from tests.helpers import max_rel, rel_l2
+from tests.mixer_helpers import golden_config, golden_params, load_mixer_golden
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-2
+STATE_TOL = 1e-3
+
+
+def _np(t):
+    return t.detach().double().cpu().numpy()
+
+
+def _bf16(x):
+    return torch.as_tensor(np.asarray(x)).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("B,T,D,stateful", [(2, 37, 96, True), (1, 1, 64, True), (3, 130, 328, False),
+                                            (2, 257, 1024, True)])
+def test_conv4_silu_matches_checker(B, T, D, stateful):
+    gen = torch.Generator().manual_seed(B * 1000 + T)
+    wide = torch.randn(B, T, D + 24, generator=gen).to(torch.bfloat16)  # x is a strided view of a wider row
+    w = (0.5 * torch.randn(D, 4, generator=gen)).float()
+    s0 = torch.randn(B, D, 3, generator=gen).to(torch.bfloat16) if stateful else None
+    dy = torch.randn(B, T, D, generator=gen).to(torch.bfloat16)
+    wide_g = wide.cuda().requires_grad_()
+    xg = wide_g[..., 8:8 + D]
+    wg = w.cuda().requires_grad_()
+    sg = None if s0 is None else s0.cuda().requires_grad_()
+    y, fin = conv4_silu(xg, wg, sg, return_final_state=True)
+    (y.float() * dy.cuda().float()).sum().backward()
+    yo, fo, saved = mo.conv4_silu_forward(_np(wide[..., 8:8 + D]), _np(w), None if s0 is None else _np(s0))
+    dxo, dwo, dso = mo.conv4_silu_backward(_np(dy), _np(w), saved)
+    assert max_rel(_np(y), yo) <= TOL
+    assert np.array_equal(_np(fin), fo)  # the state is a copy of BF16 inputs
+    dx = _np(wide_g.grad)
+    assert np.all(dx[..., :8] == 0) and np.all(dx[..., 8 + D:] == 0)
+    assert max_rel(dx[..., 8:8 + D], dxo) <= TOL
+    assert max_rel(_np(wg.grad), dwo) <= TOL
+    if stateful:
+        assert max_rel(_np(sg.grad), dso) <= TOL
+
+
+@pytest.mark.parametrize("shape", [(2, 19, 2, 16), (1, 130, 4, 64), (3, 64, 8, 128), (1, 70, 16, 128)])
+def test_kda_decay_gate_matches_checker(shape):
+    gen = torch.Generator().manual_seed(sum(shape))
+    H, r = shape[-2:]
+    raw = (2.0 * torch.randn(*shape, generator=gen)).to(torch.bfloat16)
+    log_rate = torch.empty(H).uniform_(0.0, 2.5, generator=gen)
+    bias = torch.randn(H, r, generator=gen)
+    dout = torch.randn(*shape, generator=gen)
+    rg, ag, bg = raw.cuda().requires_grad_(), log_rate.cuda().requires_grad_(), bias.cuda().requires_grad_()
+    out = kda_decay_gate(rg, ag, bg)
+    assert out.dtype == torch.float32
+    (out * dout.cuda()).sum().backward()
+    oo, saved = mo.kda_gate_forward(_np(raw), _np(log_rate), _np(bias))
+    draw, dA, db = mo.kda_gate_backward(_np(dout), saved)
+    assert max_rel(_np(out), oo) <= 1e-5
+    assert (out <= 0).all()
+    assert max_rel(_np(rg.grad), draw) <= TOL  # BF16 gradient
+    assert max_rel(_np(ag.grad), dA) <= 1e-4
+    assert max_rel(_np(bg.grad), db) <= 1e-4
+
+
+@pytest.mark.parametrize("shape", [(2, 19, 2, 16), (1, 130, 4, 64), (3, 64, 8, 128), (2, 5, 3, 40)])
+def test_rms_norm_gated_matches_checker(shape):
+    gen = torch.Generator().manual_seed(sum(shape) + 1)
+    V = shape[-1]
+    x = torch.randn(*shape, generator=gen).to(torch.bfloat16)
+    gate = (2.0 * torch.randn(*shape, generator=gen)).to(torch.bfloat16)
+    w = 1.0 + 0.3 * torch.randn(V, generator=gen)
+    dy = torch.randn(*shape, generator=gen).to(torch.bfloat16)
+    xg, gg, wg = x.cuda().requires_grad_(), gate.cuda().requires_grad_(), w.cuda().requires_grad_()
+    y = rms_norm_gated(xg, gg, wg, 1e-6)
+    (y.float() * dy.cuda().float()).sum().backward()
+    yo, saved = mo.norm_gate_forward(_np(x), _np(gate), _np(w), 1e-6)
+    dxo, dgo, dwo = mo.norm_gate_backward(_np(dy), _np(w), saved)
+    assert max_rel(_np(y), yo) <= TOL
+    assert max_rel(_np(xg.grad), dxo) <= TOL
+    assert max_rel(_np(gg.grad), dgo) <= TOL
+    assert max_rel(_np(wg.grad), dwo) <= 1e-3
+
+
+# ------------------------------------------------------------------ module
+
+LINEAR_WEIGHTS = ("in_proj.weight", "in_proj.bias", "output_proj.weight", "output_proj.bias", "decay_proj.weight",
+                  "output_gate_proj.weight", "output_gate_proj.bias")
+
+
+def _module_and_checker(cfg, params):
+    """GPU module holding `params`; checker holding the same numbers as the GPU reads them
+    (linear weights in BF16, conv / gate / norm parameters in FP32)."""
+    config = SolveDeltaConfig(hidden_size=cfg["hidden_size"], num_heads=cfg["num_heads"],
+                              head_k_dim=cfg["head_k_dim"], head_v_dim=cfg["head_v_dim"],
+                              use_short_conv=cfg.get("use_short_conv", True), bias=cfg.get("bias", False),
+                              norm_eps=cfg.get("norm_eps", 1e-6))
+    module = SolveDelta(config)
+    seen = {}
+    with torch.no_grad():
+        for name, param in module.named_parameters():
+            value = torch.as_tensor(np.asarray(params[name])).float()
+            if name in LINEAR_WEIGHTS:
+                value = value.to(torch.bfloat16).float()
+            param.copy_(value.reshape(param.shape))
+            seen[name] = _np(param)
+    assert set(seen) == set(params)
+    module = module.cuda()
+    checker = mo.MixerOracle(seen, hidden_size=config.hidden_size, num_heads=config.num_heads,
+                             head_k_dim=config.resolved_head_k_dim, head_v_dim=config.resolved_head_v_dim,
+                             use_short_conv=config.use_short_conv, norm_eps=config.norm_eps)
+    return module, checker
+
+
+def _compare_grads(module, pgrads, tol=TOL):
+    for name, param in module.named_parameters():
+        assert param.grad is not None, name
+        ref = pgrads[name]
+        got = _np(param.grad).reshape(ref.shape)
+        assert np.isfinite(got).all(), name
+        assert max_rel(got, ref) <= tol, (name, max_rel(got, ref))
+
+
+@pytest.mark.parametrize("name", ["mixer_small", "mixer_noconv_bias"])
+def test_mixer_module_matches_checker_on_upstream_parameters(name):
+    g = load_mixer_golden(name)
+    module, checker = _module_and_checker(golden_config(g), golden_params(g))
+    x = _bf16(g["in_x"])
+    dout = _bf16(g["dout"])
+    xg = x.cuda().requires_grad_()
+    out = module(xg)
+    assert out.dtype == torch.bfloat16 and out.shape == x.shape
+    (out.float() * dout.cuda().float()).sum().backward()
+    oo, _, _ = checker.forward(_np(x))
+    dxo, pg, _, _ = checker.backward(_np(dout))
+    assert max_rel(_np(out), oo) <= TOL
+    # The FP64 upstream output itself is within BF16 weight rounding of ours.
+    assert rel_l2(_np(out), g["out"]) <= 5e-2
+    assert max_rel(_np(xg.grad), dxo) <= TOL
+    _compare_grads(module, pg)
+
+
+def test_mixer_module_state_continuation():
+    g = load_mixer_golden("mixer_small_state")
+    module, checker = _module_and_checker(golden_config(g), golden_params(g))
+    x, dout = _bf16(g["in_x"]), _bf16(g["dout"])
+    conv0 = _bf16(g["in_conv0"])
+    C0, S0 = torch.as_tensor(g["in_C0"]).float(), torch.as_tensor(g["in_S0"]).float()
+    dC, dS = torch.as_tensor(g["dC_T"]).float(), torch.as_tensor(g["dS_T"]).float()
+    xg = x.cuda().requires_grad_()
+    c0g, s0g, cvg = C0.cuda().requires_grad_(), S0.cuda().requires_grad_(), conv0.cuda().requires_grad_()
+    out, fin = module(xg, initial_state=SolveDeltaLayerState(SolveDeltaState(c0g, s0g), cvg),
+                      return_final_state=True)
+    loss = ((out.float() * dout.cuda().float()).sum() + (fin.operator.predictor * dC.cuda()).sum()
+            + (fin.operator.S * dS.cuda()).sum())
+    loss.backward()
+    oo, fo, conv_T = checker.forward(_np(x), conv_state=_np(conv0), operator_state=(_np(C0), _np(S0)))
+    dxo, pg, dconv0, (dC0, dS0) = checker.backward(_np(dout), dC_T=_np(dC), dS_T=_np(dS))
+    assert max_rel(_np(out), oo) <= TOL
+    assert max_rel(_np(fin.operator.predictor), fo[0]) <= 5e-3  # BF16 activations feed the FP32 state
+    assert max_rel(_np(fin.operator.S), fo[1]) <= 5e-3
+    assert max_rel(_np(fin.conv), conv_T) <= 1e-2               # BF16 copy of the projection row
+    assert max_rel(_np(xg.grad), dxo) <= TOL
+    assert max_rel(_np(c0g.grad), dC0) <= TOL
+    assert max_rel(_np(s0g.grad), dS0) <= TOL
+    assert max_rel(_np(cvg.grad), dconv0) <= TOL
+    _compare_grads(module, pg)
+
+    # Split continuation: running [0,t) then [t,T) with the carried state equals one pass.
+    with torch.no_grad():
+        state0 = SolveDeltaLayerState(SolveDeltaState(C0.cuda(), S0.cuda()), conv0.cuda())
+        whole, fin_whole = module(x.cuda(), initial_state=state0, return_final_state=True)
+        a, mid = module(x.cuda()[:, :3], initial_state=state0, return_final_state=True)
+        b, fin_split = module(x.cuda()[:, 3:], initial_state=mid, return_final_state=True)
+    assert max_rel(_np(torch.cat([a, b], 1)), _np(whole)) <= TOL
+    assert torch.equal(fin_split.conv, fin_whole.conv)
+    assert max_rel(_np(fin_split.operator.S), _np(fin_whole.operator.S)) <= 5e-3
+
+
+def test_mixer_module_tiny_configuration():
+    """The upstream CPU-runnable configuration: hidden 256, 4 heads, 64/64, B=2, T=128."""
+    torch.manual_seed(5)
+    config = SolveDeltaConfig(hidden_size=256, num_heads=4, head_k_dim=64, head_v_dim=64)
+    module = SolveDelta(config)
+    assert module.projection_sizes == (256, 256, 256, 256, 256, 256, 256, 4, 64, 64)
+    params = {n: _np(p) for n, p in module.named_parameters()}
+    module, checker = _module_and_checker(dict(hidden_size=256, num_heads=4, head_k_dim=64, head_v_dim=64), params)
+    gen = torch.Generator().manual_seed(11)
+    x = torch.randn(2, 128, 256, generator=gen).to(torch.bfloat16)
+    dout = torch.randn(2, 128, 256, generator=gen).to(torch.bfloat16)
+    xg = x.cuda().requires_grad_()
+    out = module(xg)
+    (out.float() * dout.cuda().float()).sum().backward()
+    oo, _, _ = checker.forward(_np(x))
+    dxo, pg, _, _ = checker.backward(_np(dout))
+    assert max_rel(_np(out), oo) <= TOL
+    assert rel_l2(_np(xg.grad), dxo) <= 3e-2
+    assert max_rel(_np(xg.grad), dxo) <= TOL
+    _compare_grads(module, pg, tol=3e-2)
+
+
+def test_mixer_module_rejects_cpu_and_masks():
+    module = SolveDelta(SolveDeltaConfig(hidden_size=64, num_heads=2, head_k_dim=16, head_v_dim=16)).cuda()
+    with pytest.raises(TypeError):
+        module(torch.zeros(1, 4, 64))
+    with pytest.raises(ValueError):
+        module(torch.zeros(1, 4, 32, dtype=torch.bfloat16, device="cuda"))
