@@ -24,10 +24,10 @@ struct PanelDesc {
 
 const PanelDesc kSaved[] = {{"Lam", 3}, {"G", 0}, {"Delta", 0}, {"Dprim", 0}, {"Zt", 4}, {"CtCk", 2}, {"CtCkB", 6}, {"SCk", 6}};
 const PanelDesc kFwd[] = {{"Upd", 0}, {"Qc", 0}, {"Ubar", 0}, {"Wd", 0}, {"Ud", 0}, {"Dt", 0}, {"Xg", 4}, {"Aqd", 5}};
-const PanelDesc kBwd[] = {{"Pp", 4},     {"Qp", 4},     {"Ag", 4},     {"Xg", 4},     {"Dyf", 4},    {"Dneg", 4},
-                          {"dR", 4},     {"dSeCk", 6},
+const PanelDesc kBwd[] = {{"Pp", 4},     {"Qp", 4},     {"Ag", 4},     {"Xg", 4},     {"Dyf", 4},    {"Dcol", 4},
+                          {"Xr", 4},     {"Er", 4},     {"Chi", 4},    {"Ee", 4},     {"dR", 4},     {"dSeCk", 6},
                           {"SdS", 3},    {"duPart", 4}, {"dkPart", 4}, {"dGPart", 4}, {"dDelta", 4}, {"DG", 4},
-                          {"Xext", 4},   {"Tpre", 4},   {"Khat", 4},   {"Ppp", 4},    {"Qpp", 4},    {"Rneg", 4},
+                          {"Xext", 4},   {"Dd", 4},     {"Tu", 4},   {"Khat", 4},   {"Ppp", 4},    {"Qpp", 4},    {"Rneg", 4},
                           {"dRr", 4},    {"dCeCk", 6}};
 
 size_t kind_bytes(int kind) {
@@ -371,8 +371,9 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
     p.SCk = bpanel_at(kSaved, s, sv, "SCk");
 #define SD_BP(field) p.field = panel_at(kBwd, s, a->scratch, #field)
 #define SD_BB(field) p.field = bpanel_at(kBwd, s, a->scratch, #field)
-    SD_BB(Pp); SD_BB(Qp); SD_BB(Ag); SD_BB(Xg); SD_BB(Dyf); SD_BB(Dneg); SD_BB(dR); SD_BB(dSeCk);
-    SD_BB(DG); SD_BB(Tpre); SD_BB(Khat);
+    SD_BB(Pp); SD_BB(Qp); SD_BB(Ag); SD_BB(Xg); SD_BB(Dyf); SD_BB(Dcol); SD_BB(dR); SD_BB(dSeCk);
+    SD_BB(Xr); SD_BB(Er); SD_BB(Chi); SD_BB(Ee);
+    SD_BB(DG); SD_BB(Dd); SD_BB(Tu); SD_BB(Khat);
     SD_BB(Ppp); SD_BB(Qpp); SD_BB(Rneg); SD_BB(dRr); SD_BB(dCeCk);
     SD_BB(duPart); SD_BB(dkPart); SD_BB(dGPart); SD_BB(dDelta); SD_BB(Xext); SD_BP(SdS);
 #undef SD_BB

@@ -10,6 +10,7 @@
 #pragma once
 #include "sd_bf16.cuh"
 #include "sd_common.cuh"
+#include "sd_decay.cuh"
 #include "sd_forward.cuh"
 
 namespace sd {
@@ -21,8 +22,10 @@ struct BwdParams {
     const float *Lam, *Gp, *Delta, *Dprim, *CtCk;
     const bf16 *Zt, *SCk, *CtCkB;
     // backward scratch: BF16 contraction operands / scanned panels
-    bf16 *Pp, *Qp, *Ag, *Xg, *Dyf, *Dneg, *dR, *dSeCk;
-    bf16 *DG, *Tpre, *Khat;
+    bf16 *Pp, *Qp, *Ag, *Xg, *Dyf, *dR, *dSeCk;
+    bf16 *Xr, *Er, *Dcol;   // block-centred chi rowG, -e rowG, d col (operands of the centred contractions)
+    bf16 *Chi, *Ee;         // chi, -e themselves (diagonal blocks)
+    bf16 *DG, *Dd, *Tu, *Khat;
     bf16 *Ppp, *Qpp, *Rneg, *dRr, *dCeCk;
     // partial cotangents (BF16: they are final up to gradient tolerance) and FP32 reductions
     bf16 *duPart, *dkPart, *dGPart, *dDelta, *Xext;
@@ -103,90 +106,107 @@ __device__ __forceinline__ void epi_store_bpanel(float (&acc)[NTW][4], int r0, i
 }
 
 // ---------------------------------------------------------------------------
-// Recompute Xg, ag, Dneg, Dt, Aqd, Aed; solve the transposed system for
+// Recompute chi, e, Aqd, Aed (block-centred, like the forward pass); solve the transposed system for
 //   P' = (I-Aed)^-T (Aqd^T dy),  Q' = (I-Aed)^-T Dt
-// so that the reverse S scan is dR = P' + Q' dS.
-constexpr size_t EXT_PREP_BWD_SMEM = 5 * BSLOT_BYTES + BMAT_BYTES + MAT_BYTES;
+// so that the reverse S scan is dR = P' + Q' dS.  Leaves the centred panels the
+// next kernel contracts with, and chi / -e for its diagonal blocks.
+constexpr size_t EXT_PREP_BWD_SMEM = 5 * BSLOT_BYTES + BMAT_BYTES + MAT_BYTES + 3 * DP * sizeof(bf16);
 
 template <bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* b_xg = reinterpret_cast<bf16*>(smem_raw);
-    bf16* b_ag = b_xg + BSLOT_ELEMS;
-    bf16* b_dn = b_ag + BSLOT_ELEMS;
-    bf16* b_dy = b_dn + BSLOT_ELEMS;
+    bf16* b_xr = reinterpret_cast<bf16*>(smem_raw);
+    bf16* b_er = b_xr + BSLOT_ELEMS;
+    bf16* b_dc = b_er + BSLOT_ELEMS;
+    bf16* b_dy = b_dc + BSLOT_ELEMS;
     bf16* b_dt = b_dy + BSLOT_ELEMS;
     bf16* b_aqd = b_dt + BSLOT_ELEMS;
     float* f_aedT = reinterpret_cast<float*>(b_aqd + BMAT_ELEMS);
+    bf16* s_Mb = reinterpret_cast<bf16*>(f_aedT + MAT_FLOATS);
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r, V = p.g.V;
+    const float* gG = panel_ptr(p.Gp, ch.gi);
+    const float* gd = panel_ptr(p.Dprim, ch.gi);
+    pair_block_scales_bf16(s_Mb, [&](int i, int c) { return gG[i * DP + c]; });
     {
-        const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
+        const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8, l16 = threadIdx.x & 15;
         const float* gDelta = panel_ptr(p.Delta, ch.gi);
-        const float* gd = panel_ptr(p.Dprim, ch.gi);
-        const float* gG = panel_ptr(p.Gp, ch.gi);
         bf16* gAg = bpanel_ptr(p.Ag, ch.gi);
         bf16* gXg = bpanel_ptr(p.Xg, ch.gi);
         bf16* gDyf = bpanel_ptr(p.Dyf, ch.gi);
-        bf16* gDneg = bpanel_ptr(p.Dneg, ch.gi);
+        bf16* gXr = bpanel_ptr(p.Xr, ch.gi);
+        bf16* gEr = bpanel_ptr(p.Er, ch.gi);
+        bf16* gDc = bpanel_ptr(p.Dcol, ch.gi);
+        bf16* gChi = bpanel_ptr(p.Chi, ch.gi);
+        bf16* gEe = bpanel_ptr(p.Ee, ch.gi);
         float GL[8];
         load8_panel(gG, CL - 1, c0, GL);
 #pragma unroll 1
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
-            const int i = lr + ROWS_PER_PASS * pp;
-            float uh[8], kh[8], qh[8], dl[8], d[8], er[8], dy[8], G[8], se[8];
+            const int i = lr + ROWS_PER_PASS * pp, i0 = i & ~(BT - 1);
+            float uh[8], kh[8], qh[8], dl[8], d[8], er[8], dy[8], G[8], Gp[8], Ge[8], se[8];
             load8_norm<FAST>(p.u, ch, i, c0, r, uh);
             load8_norm<FAST>(p.k, ch, i, c0, r, kh);
             load8_norm<FAST>(p.q, ch, i, c0, r, qh);
             load8_panel(gDelta, i, c0, dl);
             load8_panel(gd, i, c0, d);
             load8_panel(gG, i, c0, G);
+            load8_panel(gG, i0 + BT - 1, c0, Ge);
+            load8_panel(gG, i0 ? i0 - 1 : 0, c0, Gp);
             load8_bf16<FAST>(row_bf16(p.er, ch, i), c0, r, p.er.vec, i < ch.nvalid, er);
             load8_bf16<FAST>(row_bf16(p.dy, ch, i), c0, V, p.dy.vec, i < ch.nvalid, dy);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) se[e] = sigmoidf_(er[e]);
+            for (int e = 0; e < 8; ++e) {
+                se[e] = sigmoidf_(er[e]);
+                if (i0 == 0) Gp[e] = 0.f;
+            }
             Sources src;
             sources_fwd(uh, kh, qh, dl, se, src);
-            float xg[8], ag[8], dn[8], dt[8];
+            float xg[8], ag[8], xr[8], ern[8], dc[8], dt[8];
+            float a[2][8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-                float ep = __expf(G[e]);
+                const float ep = __expf(G[e]), rw = __expf(G[e] - Gp[e]);
+                a[0][e] = src.chi[e];
+                a[1][e] = -src.e[e];
                 xg[e] = src.chi[e] * ep;
                 ag[e] = -src.e[e] * ep;
-                dn[e] = d[e] * clamp_exp_neg(G[e]);
+                xr[e] = src.chi[e] * rw;
+                ern[e] = -src.e[e] * rw;
+                dc[e] = d[e] * __expf(Ge[e] - G[e]);
                 dt[e] = d[e] * __expf(GL[e] - G[e]);
             }
-            store8_bsm(b_xg, i, c0, xg);
-            store8_bsm(b_ag, i, c0, ag);
-            store8_bsm(b_dn, i, c0, dn);
+            store8_bsm(b_xr, i, c0, xr);
+            store8_bsm(b_er, i, c0, ern);
+            store8_bsm(b_dc, i, c0, dc);
             store8_bsm(b_dy, i, c0, dy);
             store8_bsm(b_dt, i, c0, dt);
             store8_bpanel(gAg, i, c0, ag);
             store8_bpanel(gXg, i, c0, xg);
             store8_bpanel(gDyf, i, c0, dy);
-            store8_bpanel(gDneg, i, c0, dn);
+            store8_bpanel(gXr, i, c0, xr);
+            store8_bpanel(gEr, i, c0, ern);
+            store8_bpanel(gDc, i, c0, dc);
+            store8_bpanel(gChi, i, c0, a[0]);
+            store8_bpanel(gEe, i, c0, a[1]);
+            float out[2];
+            pair_diag_row<2, false>(i, a, G, [&](int j, float (&b)[8]) { load8_panel(gd, j, c0, b); },
+                                    [&](int j, float (&Gj)[8]) { load8_panel(gG, j, c0, Gj); }, out);
+            b_aqd[i * LDM + i0 + l16] = __float2bfloat16_rn(out[0]);
+            f_aedT[(i0 + l16) * LDA + i] = (i0 + l16 < i) ? out[1] : 0.f;
         }
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
-    {
-        float a1[NT64][4], a2[NT64][4];
-        acc_zero<NT64>(a1);
-        acc_zero<NT64>(a2);
-        const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
-        warp_mma_bf16<NT64, false, true>(a1, b_xg, LDB, b_dn, LDB, r0, n0, 0, DP);
-        warp_mma_bf16<NT64, false, true>(a2, b_ag, LDB, b_dn, LDB, r0, n0, 0, DP);
-        warp_epi<NT64>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
-            *reinterpret_cast<__nv_bfloat162*>(b_aqd + i * LDM + j) =
-                __floats2bfloat162_rn((j <= i) ? v0 : 0.f, (j + 1 <= i) ? v1 : 0.f);
-        });
-        warp_epi<NT64>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
-            f_aedT[j * LDA + i] = (j < i) ? v0 : 0.f;
-            f_aedT[(j + 1) * LDA + i] = (j + 1 < i) ? v1 : 0.f;
-        });
-    }
+    pair_offdiag_bf16(s_Mb, b_xr, b_dc, [&](int i, int j, float v0, float v1) {
+        *reinterpret_cast<__nv_bfloat162*>(b_aqd + i * LDM + j) = __floats2bfloat162_rn(v0, v1);
+    });
+    pair_offdiag_bf16(s_Mb, b_er, b_dc, [&](int i, int j, float v0, float v1) {
+        f_aedT[j * LDA + i] = v0;
+        f_aedT[(j + 1) * LDA + i] = v1;
+    });
     __syncthreads();
     SD_PHASE(p.g, ph);
     {
@@ -213,8 +233,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) 
 // Per-token reverse of the sources and of the gate factors of the exterior.
 // Writes the final gradients of q, values, erase_raw, write_raw and the
 // partial cotangents the predictor reverse still has to complete.
-// A1, A2, PY, dDt and dR are read from the shared BF16 panels the contractions
-// of the same CTA just produced.
+// d chi, -d e, the decay part of d d (all final), dDt and dR are read from the
+// shared BF16 panels the contractions of the same CTA just produced.
 template <bool FAST>
 __device__ __forceinline__ void sources_bwd_rows(const BwdParams& p, const Chunk& ch, const bf16* sA1,
                                                  const bf16* sA2, const bf16* sPY, const bf16* sdDt,
@@ -250,12 +270,12 @@ __device__ __forceinline__ void sources_bwd_rows(const BwdParams& p, const Chunk
         float dsb = 0.f, dsq = 0.f;
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-            float ep = __expf(G[e]), en = clamp_exp_neg(G[e]), et = __expf(GL[e] - G[e]);
-            dchi[e] = ep * a1[e];
-            de[e] = -ep * a2[e];
-            dd[e] = en * py[e] + et * ddt[e];
-            float dneg = d[e] * en, dt = d[e] * et;
-            dG[e] = src.chi[e] * dchi[e] + src.e[e] * de[e] - dneg * py[e] + dd[e] * (d[e] - kh[e]);
+            float ep = __expf(G[e]), et = __expf(GL[e] - G[e]);
+            dchi[e] = a1[e];
+            de[e] = -a2[e];
+            dd[e] = py[e] + et * ddt[e];
+            float dt = d[e] * et;
+            dG[e] = src.chi[e] * dchi[e] + src.e[e] * de[e] - d[e] * py[e] + dd[e] * (d[e] - kh[e]);
             xext[e] = ddt[e] * dt;
             dg_[e] = dd[e] * ep;
             dsb = fmaf(-de[e], src.phi[e], dsb);
@@ -293,6 +313,7 @@ __device__ __forceinline__ void sources_bwd_rows(const BwdParams& p, const Chunk
         store8_bpanel(bpanel_ptr(p.dGPart, ch.gi), i, c0, dG);
         store8_bpanel(bpanel_ptr(p.dDelta, ch.gi), i, c0, ddl);
         store8_bpanel(bpanel_ptr(p.DG, ch.gi), i, c0, dg_);
+        store8_bpanel(bpanel_ptr(p.Dd, ch.gi), i, c0, dd);
         store8_bpanel(bpanel_ptr(p.Xext, ch.gi), i, c0, xext);
         // value side: dv = sigmoid(write) dR, d write_raw = dR v sigmoid'(write)
         float wr[8], v[8], dr[8], dv[8], dwr[8];
@@ -311,45 +332,61 @@ __device__ __forceinline__ void sources_bwd_rows(const BwdParams& p, const Chunk
 }
 
 // ---------------------------------------------------------------------------
-// Pure contractions of the exterior reverse step (no gate factors):
-//   A1 = dy S^T + tril(dy Z~^T) Dneg        (-> d chi after exp(G))
-//   A2 = dR S^T + stril(dR Z~^T) Dneg       (-> d e)
-//   PY = tril(dy Z~^T)^T Xg + stril(dR Z~^T)^T ag
+// Contractions of the exterior reverse step.  With dAqd = tril(dy Z~^T), dAed = stril(dR Z~^T):
+//   d chi_i = exp(G_i) (dy S^T)_i + sum_{j<=i} dAqd_ij d_j exp(G_i - G_j)
+//   -d e_i  = exp(G_i) (dR S^T)_i + sum_{j<i}  dAed_ij d_j exp(G_i - G_j)
+//   ddp_j   = sum_{i>=j} (dAqd_ij chi_i - dAed_ij e_i) exp(G_i - G_j)     (decay part of d d)
 //   dDt = Z~ dS_end^T ,  SdS[c] = sum_v S[c][v] dS_end[c][v]
-// Every operand is resident and streams in with cp.async.  The four results
-// stay in shared memory (over operands that are no longer needed) and the
-// per-token reverse of the sources runs on them in the same CTA.
-constexpr size_t EXT_PAIR_BWD_SMEM = 6 * BSLOT_BYTES + 2 * BSTATE_BYTES + 2 * BMAT_BYTES;
+// The decay-weighted sums are block-centred: Horner accumulation over the blocks
+// off the diagonal on the tensor cores (the state term enters as the block before
+// the first), diagonal blocks directly.  Every operand streams in with cp.async.
+// The four results stay in shared memory (over operands that are no longer
+// needed) and the per-token reverse of the sources runs on them in the same CTA.
+constexpr size_t EXT_PAIR_BWD_SMEM =
+    6 * BSLOT_BYTES + 2 * BSTATE_BYTES + 2 * BMAT_BYTES + NBLK * DP * sizeof(float);
+
+// acc rows (i = r0+g, r0+g+8) x columns scaled by exp(x_i - ref) with x, ref rows of the prefix panel
+template <int NTW, class FX>
+__device__ __forceinline__ void epi_scale_store_bsm(float (&acc)[NTW][4], int r0, int n0, bf16* spanel, FX fx) {
+    warp_epi<NTW>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
+        const float2 f = fx(i, j);
+        *reinterpret_cast<__nv_bfloat162*>(spanel + i * LDB + j) = __floats2bfloat162_rn(f.x * v0, f.y * v1);
+    });
+}
 
 template <bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* b_dy = reinterpret_cast<bf16*>(smem_raw);
+    bf16* b_dy = reinterpret_cast<bf16*>(smem_raw);   // dy      -> d chi
     bf16* b_zt = b_dy + BSLOT_ELEMS;
     bf16* b_dr = b_zt + BSLOT_ELEMS;
-    bf16* b_dn = b_dr + BSLOT_ELEMS;
-    bf16* b_xg = b_dn + BSLOT_ELEMS;
-    bf16* b_ag = b_xg + BSLOT_ELEMS;
-    bf16* b_S = b_ag + BSLOT_ELEMS;
+    bf16* b_dc = b_dr + BSLOT_ELEMS;                   // d col   -> -d e
+    bf16* b_xr = b_dc + BSLOT_ELEMS;                   // chi row -> ddp
+    bf16* b_er = b_xr + BSLOT_ELEMS;                   // -e row  -> dDt
+    bf16* b_S = b_er + BSLOT_ELEMS;
     bf16* b_dS = b_S + DP * LDB;
     bf16* b_daqd = b_dS + DP * LDB;
     bf16* b_daed = b_daqd + BMAT_ELEMS;
+    float* s_beta = reinterpret_cast<float*>(b_daed + BMAT_ELEMS);
     const Chunk ch = chunk_of(p.g, blockIdx.x);
+    const float* gG = panel_ptr(p.Gp, ch.gi);
+    auto fG = [&](int i, int c) { return gG[i * DP + c]; };
 
     async_bpanel(b_dy, bpanel_ptr(p.Dyf, ch.gi));
     async_bpanel(b_dr, bpanel_ptr(p.dR, ch.gi));
     async_bpanel(b_zt, bpanel_ptr(p.Zt, ch.gi));
     cp_commit();
-    async_bpanel(b_dn, bpanel_ptr(p.Dneg, ch.gi));
+    async_bpanel(b_dc, bpanel_ptr(p.Dcol, ch.gi));
     async_bstate(b_S, bstate_ptr(p.SCk, ch.gi));
     cp_commit();
-    async_bpanel(b_xg, bpanel_ptr(p.Xg, ch.gi));
-    async_bpanel(b_ag, bpanel_ptr(p.Ag, ch.gi));
+    async_bpanel(b_xr, bpanel_ptr(p.Xr, ch.gi));
+    async_bpanel(b_er, bpanel_ptr(p.Er, ch.gi));
     cp_commit();
     async_bstate(b_dS, bstate_ptr(p.dSeCk, ch.gi));
     cp_commit();
+    block_betas(s_beta, fG);
     cp_wait<3>();
     __syncthreads();
     SD_PHASE(p.g, ph);
@@ -358,8 +395,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
         acc_zero<NT64>(a1);
         acc_zero<NT64>(a2);
         const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
-        warp_mma_bf16<NT64, false, true>(a1, b_dy, LDB, b_zt, LDB, r0, n0, 0, DP);
-        warp_mma_bf16<NT64, false, true>(a2, b_dr, LDB, b_zt, LDB, r0, n0, 0, DP);
+        if (n0 <= r0) {
+            warp_mma_bf16<NT64, false, true>(a1, b_dy, LDB, b_zt, LDB, r0, n0, 0, DP);
+            warp_mma_bf16<NT64, false, true>(a2, b_dr, LDB, b_zt, LDB, r0, n0, 0, DP);
+        }
         warp_epi<NT64>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
             *reinterpret_cast<__nv_bfloat162*>(b_daqd + i * LDM + j) =
                 __floats2bfloat162_rn((j <= i) ? v0 : 0.f, (j + 1 <= i) ? v1 : 0.f);
@@ -373,35 +412,56 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
     __syncthreads();
     SD_PHASE(p.g, ph);
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
+    const int I = r0 / BT;
+    // exp(G_i - Gprev_I) for the accumulator element pair (i, j), (i, j + 1)
+    auto row_factor = [&](int i, int j) {
+        const float2 G = *reinterpret_cast<const float2*>(gG + i * DP + j);
+        float2 Gp = make_float2(0.f, 0.f);
+        if (r0) Gp = *reinterpret_cast<const float2*>(gG + (r0 - 1) * DP + j);
+        return make_float2(__expf(G.x - Gp.x), __expf(G.y - Gp.y));
+    };
+    // exp(Gend_J - G_j) for rows of block J = I of the anti-causal result
+    auto col_factor = [&](int i, int j) {
+        const float2 G = *reinterpret_cast<const float2*>(gG + i * DP + j);
+        const float2 Ge = *reinterpret_cast<const float2*>(gG + (r0 + BT - 1) * DP + j);
+        return make_float2(__expf(Ge.x - G.x), __expf(Ge.y - G.y));
+    };
     {
         float a1[NT128][4], a2[NT128][4];
         acc_zero<NT128>(a1);
         acc_zero<NT128>(a2);
         warp_mma_bf16<NT128, false, true>(a1, b_dy, LDB, b_S, LDB, r0, n0, 0, DP);
         warp_mma_bf16<NT128, false, true>(a2, b_dr, LDB, b_S, LDB, r0, n0, 0, DP);
-        warp_mma_bf16<NT128, false, false>(a1, b_daqd, LDM, b_dn, LDB, r0, n0, 0, r0 + 16);
-        warp_mma_bf16<NT128, false, false>(a2, b_daed, LDM, b_dn, LDB, r0, n0, 0, r0 + 16);
+        for (int J = 0; J < I; ++J) {
+            scale_acc<NT128>(a1, s_beta + J * DP, n0);
+            scale_acc<NT128>(a2, s_beta + J * DP, n0);
+            warp_mma_bf16<NT128, false, false>(a1, b_daqd, LDM, b_dc, LDB, r0, n0, J * BT, J * BT + BT);
+            warp_mma_bf16<NT128, false, false>(a2, b_daed, LDM, b_dc, LDB, r0, n0, J * BT, J * BT + BT);
+        }
         cp_wait<1>();
-        __syncthreads();  // nobody reads dy / Dneg any more: A1 and A2 take their place
+        __syncthreads();  // nobody reads dy / d col any more: d chi and -d e take their place
         SD_PHASE(p.g, ph);
-        epi_store_bsm<NT128>(a1, r0, n0, b_dy);
-        epi_store_bsm<NT128>(a2, r0, n0, b_dn);
+        epi_scale_store_bsm<NT128>(a1, r0, n0, b_dy, row_factor);
+        epi_scale_store_bsm<NT128>(a2, r0, n0, b_dc, row_factor);
     }
     {
         float acc[NT128][4];
         acc_zero<NT128>(acc);
-        warp_mma_bf16<NT128, true, false>(acc, b_daqd, LDM, b_xg, LDB, r0, n0, r0, CL);
-        warp_mma_bf16<NT128, true, false>(acc, b_daed, LDM, b_ag, LDB, r0, n0, r0, CL);
+        for (int K = NBLK - 1; K > I; --K) {
+            if (K < NBLK - 1) scale_acc<NT128>(acc, s_beta + K * DP, n0);
+            warp_mma_bf16<NT128, true, false>(acc, b_daqd, LDM, b_xr, LDB, r0, n0, K * BT, K * BT + BT);
+            warp_mma_bf16<NT128, true, false>(acc, b_daed, LDM, b_er, LDB, r0, n0, K * BT, K * BT + BT);
+        }
         cp_wait<0>();
-        __syncthreads();  // Xg is free: PY takes its place
+        __syncthreads();  // chi row is free: the decay part of d d takes its place
         SD_PHASE(p.g, ph);
-        epi_store_bsm<NT128>(acc, r0, n0, b_xg);
+        epi_scale_store_bsm<NT128>(acc, r0, n0, b_xr, col_factor);
     }
     {
         float acc[NT128][4];
         acc_zero<NT128>(acc);
         warp_mma_bf16<NT128, false, true>(acc, b_zt, LDB, b_dS, LDB, r0, n0, 0, DP);
-        epi_store_bsm<NT128>(acc, r0, n0, b_ag);  // ag was last read before the barrier above
+        epi_store_bsm<NT128>(acc, r0, n0, b_er);  // -e row was last read before the barrier above
     }
     {
         const int c = threadIdx.x >> 2, qt = threadIdx.x & 3;  // four lanes per state row
@@ -420,48 +480,83 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
-    sources_bwd_rows<FAST>(p, ch, b_dy, b_dn, b_xg, b_ag, b_dr);
+    {   // diagonal blocks, one thread per (channel, block): d, chi, -e themselves from HBM (L2)
+        const float* gd = panel_ptr(p.Dprim, ch.gi);
+        const bf16* gChi = bpanel_ptr(p.Chi, ch.gi);
+        const bf16* gEe = bpanel_ptr(p.Ee, ch.gi);
+        float al[BT];
+        block_alphas(al, fG);
+        auto add_to = [](bf16* panel) {
+            return [panel](int i, int c, float v) {
+                bf16* q = panel + i * LDB + c;
+                *q = __float2bfloat16_rn(__bfloat162float(*q) + v);
+            };
+        };
+        auto fd = [&](int j, int c) { return gd[j * DP + c]; };
+        causal_diag<false, false>(al, [&](int i, int j) { return __bfloat162float(b_daqd[i * LDM + j]); }, fd,
+                                  add_to(b_dy));
+        causal_diag<false, true>(al, [&](int i, int j) { return __bfloat162float(b_daed[i * LDM + j]); }, fd,
+                                 add_to(b_dc));
+        anti_diag<false, false>(al, [&](int i, int j) { return __bfloat162float(b_daqd[i * LDM + j]); },
+                                [&](int i, int c) { return __bfloat162float(gChi[i * DP + c]); }, add_to(b_xr));
+        anti_diag<false, true>(al, [&](int i, int j) { return __bfloat162float(b_daed[i * LDM + j]); },
+                               [&](int i, int c) { return __bfloat162float(gEe[i * DP + c]); }, add_to(b_xr));
+    }
+    __syncthreads();
+    SD_PHASE(p.g, ph);
+    sources_bwd_rows<FAST>(p, ch, b_dy, b_dc, b_xr, b_er, b_dr);
     SD_PHASE(p.g, ph);
 }
 
 // ---------------------------------------------------------------------------
 // Reverse of the primal address d = k^ + C_t^T k^, and preparation of the dC
-// scan:
-//   dk^ = dkPart + DG Ct + tril(DG Uneg^T) Delta        -> final dkeys
-//   dDelta_loc = dDelta_src + tril(DG Uneg^T)^T K^
-//   Tpre = tril(K^ Delta^T)^T DG                         (-> d u^ after exp(-G))
+// scan.  With dd the cotangent of d, DG = dd exp(G), Aqk = tril(K^ Delta^T):
+//   dAqk_ij = sum_c dd_ic u^_jc exp(G_ic - G_jc)   (j <= i)
+//   dk^ = dkPart + DG Ct + dAqk Delta                                   -> final dkeys
+//   dDelta_loc = dDelta_src + dAqk^T K^
+//   t_u[j] = sum_{i>=j} Aqk_ij dd_i exp(G_i - G_j)                      (-> d u^, d log decay)
 //   P'' = (I+Lm)^-T dDelta_loc,  Q'' = (I+Lm)^-T Ubar,  Rneg = -gamma U~.
-constexpr size_t PRIMAL_BWD_SMEM =
-    6 * BSLOT_BYTES + BSTATE_BYTES + 2 * BMAT_BYTES + MAT_BYTES + (2 * CL + 4 * CL) * sizeof(float);
+// dAqk, the recomputed Lm and t_u are block-centred (tensor cores off the
+// diagonal blocks, direct evaluation on them).
+constexpr size_t PRIMAL_BWD_SMEM = 7 * BSLOT_BYTES + BSTATE_BYTES + 2 * BMAT_BYTES + MAT_BYTES +
+                                   (3 * CL + 4 * CL + NBLK * DP) * sizeof(float) + 3 * DP * sizeof(bf16);
 
 template <bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* b_un = reinterpret_cast<bf16*>(smem_raw);
-    bf16* b_ut = b_un + BSLOT_ELEMS;
-    bf16* b_ub = b_ut + BSLOT_ELEMS;   // Ubar, then Q''
+    bf16* b_uc = reinterpret_cast<bf16*>(smem_raw);   // u^ col
+    bf16* b_ur = b_uc + BSLOT_ELEMS;   // u^ rowE, then t_u off the diagonal blocks
+    bf16* b_ub = b_ur + BSLOT_ELEMS;   // Ubar, then Q''
     bf16* b_kh = b_ub + BSLOT_ELEMS;
     bf16* b_dl = b_kh + BSLOT_ELEMS;   // Delta, then dDelta_loc / P''
-    bf16* b_dg = b_dl + BSLOT_ELEMS;
-    bf16* b_Ct = b_dg + BSLOT_ELEMS;
+    bf16* b_dg = b_dl + BSLOT_ELEMS;   // dd exp(G)
+    bf16* b_ddr = b_dg + BSLOT_ELEMS;  // dd rowG
+    bf16* b_Ct = b_ddr + BSLOT_ELEMS;
     bf16* b_aqk = b_Ct + DP * LDB;
     bf16* b_daqk = b_aqk + BMAT_ELEMS;
     float* f_lmT = reinterpret_cast<float*>(b_daqk + BMAT_ELEMS);
     float* s_rk = f_lmT + MAT_FLOATS;   // 1/|k| per row
-    float* s_gam = s_rk + CL;
+    float* s_ru = s_rk + CL;            // 1/|u| per row
+    float* s_gam = s_ru + CL;
     float* s_dot = s_gam + CL;          // [CL][4] partial dots of the norm VJP
+    float* s_beta = s_dot + 4 * CL;
+    bf16* s_Mb = reinterpret_cast<bf16*>(s_beta + NBLK * DP);
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r;
+    const float* gG = panel_ptr(p.Gp, ch.gi);
+    const bf16* gDd = bpanel_ptr(p.Dd, ch.gi);
+    auto fG = [&](int i, int c) { return gG[i * DP + c]; };
 
     async_bpanel(b_dg, bpanel_ptr(p.DG, ch.gi));
     async_bstate(b_Ct, bstate_ptr(p.CtCkB, ch.gi));
     cp_commit();
     load_gamma(p.gam, ch, s_gam);
+    block_betas(s_beta, fG);
+    pair_block_scales_bf16(s_Mb, fG);
     {
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
-        const float* gG = panel_ptr(p.Gp, ch.gi);
         const float* gDelta = panel_ptr(p.Delta, ch.gi);
         bf16* gKhat = bpanel_ptr(p.Khat, ch.gi);
         bf16* gR = bpanel_ptr(p.Rneg, ch.gi);
@@ -469,59 +564,90 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
         load8_panel(gG, CL - 1, c0, GL);
 #pragma unroll 1
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
-            const int i = lr + ROWS_PER_PASS * pp;
-            float uh[8], kh[8], G[8], E[8], dl[8];
-            load8_norm<FAST>(p.u, ch, i, c0, r, uh);
+            const int i = lr + ROWS_PER_PASS * pp, i0 = i & ~(BT - 1);
+            float uh[8], kh[8], G[8], E[8], Gp[8], Ge[8], dl[8], dd[8];
+            const float ru = load8_norm<FAST>(p.u, ch, i, c0, r, uh);
             const float rk = load8_norm<FAST>(p.k, ch, i, c0, r, kh);
             load8_panel(gG, i, c0, G);
             load8_panel(gG, i > 0 ? i - 1 : 0, c0, E);  // E = G of the previous row (0 for the first)
-#pragma unroll
-            for (int e = 0; e < 8; ++e) E[e] = i > 0 ? E[e] : 0.f;
-            load8_panel(gDelta, i, c0, dl);
-            const float gm = (i < ch.nvalid) ? *row_f32(p.gam, ch, i) : 0.f;
-            float un[8], ut[8], ub[8], rn[8];
+            load8_panel(gG, i0 ? i0 - 1 : 0, c0, Gp);
+            load8_panel(gG, i0 + BT - 1, c0, Ge);
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-                un[e] = uh[e] * clamp_exp_neg(G[e]);
-                ut[e] = uh[e] * __expf(E[e]);
-                ub[e] = uh[e] * __expf(GL[e] - G[e]);
-                rn[e] = -gm * ut[e];
+                E[e] = i > 0 ? E[e] : 0.f;
+                Gp[e] = i0 ? Gp[e] : 0.f;
             }
-            store8_bsm(b_un, i, c0, un);
-            store8_bsm(b_ut, i, c0, ut);
+            load8_panel(gDelta, i, c0, dl);
+            load8_bpanel(gDd, i, c0, dd);
+            const float gm = (i < ch.nvalid) ? *row_f32(p.gam, ch, i) : 0.f;
+            float uc[8], ur[8], ub[8], rn[8], ddr[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                uc[e] = uh[e] * __expf(Ge[e] - G[e]);
+                ur[e] = uh[e] * __expf(E[e] - Gp[e]);
+                ub[e] = uh[e] * __expf(GL[e] - G[e]);
+                rn[e] = -gm * uh[e] * __expf(E[e]);
+                ddr[e] = dd[e] * __expf(G[e] - Gp[e]);
+            }
+            store8_bsm(b_uc, i, c0, uc);
+            store8_bsm(b_ur, i, c0, ur);
             store8_bsm(b_ub, i, c0, ub);
             store8_bsm(b_kh, i, c0, kh);
             store8_bsm(b_dl, i, c0, dl);
+            store8_bsm(b_ddr, i, c0, ddr);
             store8_bpanel(gKhat, i, c0, kh);
             store8_bpanel(gR, i, c0, rn);
-            if ((threadIdx.x & 15) == 0) s_rk[i] = rk;
+            if ((threadIdx.x & 15) == 0) {
+                s_rk[i] = rk;
+                s_ru[i] = ru;
+            }
         }
     }
     cp_wait<0>();
     __syncthreads();
     SD_PHASE(p.g, ph);
     {
-        float a1[NT64][4], a2[NT64][4], a3[NT64][4];
-        acc_zero<NT64>(a1);
-        acc_zero<NT64>(a2);
-        acc_zero<NT64>(a3);
         const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
-        warp_mma_bf16<NT64, false, true>(a1, b_kh, LDB, b_dl, LDB, r0, n0, 0, DP);
-        warp_mma_bf16<NT64, false, true>(a2, b_dg, LDB, b_un, LDB, r0, n0, 0, DP);
-        warp_mma_bf16<NT64, false, true>(a3, b_ut, LDB, b_un, LDB, r0, n0, 0, DP);
+        float a1[NT64][4];
+        acc_zero<NT64>(a1);
+        if (n0 <= r0) warp_mma_bf16<NT64, false, true>(a1, b_kh, LDB, b_dl, LDB, r0, n0, 0, DP);
         warp_epi<NT64>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
             *reinterpret_cast<__nv_bfloat162*>(b_aqk + i * LDM + j) =
                 __floats2bfloat162_rn((j <= i) ? v0 : 0.f, (j + 1 <= i) ? v1 : 0.f);
         });
-        warp_epi<NT64>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
-            *reinterpret_cast<__nv_bfloat162*>(b_daqk + i * LDM + j) =
-                __floats2bfloat162_rn((j <= i) ? v0 : 0.f, (j + 1 <= i) ? v1 : 0.f);
+        pair_offdiag_bf16(s_Mb, b_ddr, b_uc, [&](int i, int j, float v0, float v1) {
+            *reinterpret_cast<__nv_bfloat162*>(b_daqk + i * LDM + j) = __floats2bfloat162_rn(v0, v1);
         });
-        warp_epi<NT64>(a3, r0, n0, [&](int i, int j, float v0, float v1) {
+        pair_offdiag_bf16(s_Mb, b_ur, b_uc, [&](int i, int j, float v0, float v1) {
             float gm = s_gam[i];
-            f_lmT[j * LDA + i] = (j < i) ? gm * v0 : 0.f;
-            f_lmT[(j + 1) * LDA + i] = (j + 1 < i) ? gm * v1 : 0.f;
+            f_lmT[j * LDA + i] = gm * v0;
+            f_lmT[(j + 1) * LDA + i] = gm * v1;
         });
+    }
+    {   // diagonal blocks of dAqk and Lm
+        const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8, l16 = threadIdx.x & 15;
+        auto fu8 = [&](int j, float (&b)[8]) {
+            load8_bf16<FAST>(row_bf16(p.u, ch, j), c0, r, p.u.vec, j < ch.nvalid, b);
+            const float rs = s_ru[j];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) b[e] *= rs;
+        };
+        auto fg8 = [&](int j, float (&Gj)[8]) { load8_panel(gG, j, c0, Gj); };
+#pragma unroll 1
+        for (int pp = 0; pp < ROW_PASSES; ++pp) {
+            const int i = lr + ROWS_PER_PASS * pp, i0 = i & ~(BT - 1);
+            float a[1][8], G[8], E[8], out[1];
+            load8_panel(gG, i, c0, G);
+            load8_panel(gG, i > 0 ? i - 1 : 0, c0, E);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) E[e] = i > 0 ? E[e] : 0.f;
+            fu8(i, a[0]);
+            pair_diag_row<1, true>(i, a, E, fu8, fg8, out);
+            f_lmT[(i0 + l16) * LDA + i] = s_gam[i] * out[0];
+            load8_bpanel(gDd, i, c0, a[0]);
+            pair_diag_row<1, false>(i, a, G, fu8, fg8, out);
+            b_daqk[i * LDM + i0 + l16] = __float2bfloat16_rn(out[0]);
+        }
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
@@ -529,11 +655,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     float accd[NT128][4];  // dAqk^T K^  (added to dDelta_src below)
     acc_zero<NT128>(accd);
     warp_mma_bf16<NT128, true, false>(accd, b_daqk, LDM, b_kh, LDB, r0, n0, r0, CL);
-    {
+    {   // t_u off the diagonal blocks: Horner from the chunk end, then exp(Gend_J - G_j)
         float acc[NT128][4];
         acc_zero<NT128>(acc);
-        warp_mma_bf16<NT128, true, false>(acc, b_aqk, LDM, b_dg, LDB, r0, n0, r0, CL);
-        epi_store_bpanel<NT128>(acc, r0, n0, bpanel_ptr(p.Tpre, ch.gi));
+        for (int K = NBLK - 1; K * BT > r0; --K) {
+            if (K < NBLK - 1) scale_acc<NT128>(acc, s_beta + K * DP, n0);
+            warp_mma_bf16<NT128, true, false>(acc, b_aqk, LDM, b_ddr, LDB, r0, n0, K * BT, K * BT + BT);
+        }
+        epi_scale_store_bsm<NT128>(acc, r0, n0, b_ur, [&](int i, int j) {
+            const float2 G = *reinterpret_cast<const float2*>(gG + i * DP + j);
+            const float2 Ge = *reinterpret_cast<const float2*>(gG + (r0 + BT - 1) * DP + j);
+            return make_float2(__expf(Ge.x - G.x), __expf(Ge.y - G.y));
+        });
     }
     {
         // dk^ and its norm VJP, in accumulator layout
@@ -597,6 +730,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     // every contraction that reads b_dl (Delta) is done: reuse it for dDelta_loc
     __syncthreads();
     SD_PHASE(p.g, ph);
+    {   // diagonal blocks of t_u, one thread per (channel, block); the finished panel goes to HBM
+        bf16* gTu = bpanel_ptr(p.Tu, ch.gi);
+        float al[BT];
+        block_alphas(al, fG);
+        anti_diag<false, false>(al, [&](int i, int j) { return __bfloat162float(b_aqk[i * LDM + j]); },
+                                [&](int i, int c) { return __bfloat162float(gDd[i * DP + c]); },
+                                [&](int j, int c, float v) {
+                                    gTu[j * DP + c] = __float2bfloat16_rn(__bfloat162float(b_ur[j * LDB + c]) + v);
+                                });
+    }
     {
         const bf16* gdd = bpanel_ptr(p.dDelta, ch.gi);
         warp_epi<NT128>(accd, r0, n0, [&](int i, int j, float v0, float v1) {
@@ -618,16 +761,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
 // dRr / dC, then the gate closure, in one CTA.
 //   dUbar = Delta dC_end ,  dUt = -gamma (dRr Ct^T) ,
 //   dgamma = rowsum(dRr * (h - U~ Ct - stril(N) Delta)) ,
-//   Ti = dN Uneg ,  Tj = dN^T U~   with dN = -gamma stril(dRr Delta^T),
-//   CdC[c] = sum_a Ct[c][a] dCt_end[c][a];
+//   t_i[i] = sum_{j<i} dN_ij u^_j exp(E_i - G_j) ,  t_j[j] = sum_{i>j} dN_ij u^_i exp(E_i - G_j)
+//   with dN = -gamma stril(dRr Delta^T),   CdC[c] = sum_a Ct[c][a] dCt_end[c][a];
 // then d u^, dG, dE are assembled per token and
 //   d log_decay = -dE + reverse_cumsum(dG), with dG[last] += dGL.
-// Writes the final gradients of u, h, gamma and log_decay.  The four
-// contraction results and the three FP32 closure panels overlay operands that
-// are dead by then.
-constexpr size_t PRED_CLOSE_BWD_SMEM =
-    4 * BSLOT_BYTES + 2 * BMAT_BYTES + 3 * size_t(CL) * LDP * 4 + (CL + 4 * CL + DP) * sizeof(float);
-static_assert(2 * BMAT_BYTES >= BSLOT_BYTES, "Tj overlays the two pair matrices");
+// N, t_i and t_j are block-centred (tensor cores off the diagonal blocks,
+// direct evaluation on them).  Writes the final gradients of u, h, gamma and
+// log_decay.  The four contraction results and the three FP32 closure panels
+// overlay operands that are dead by then.
+constexpr size_t PRED_CLOSE_BWD_SMEM = 5 * BSLOT_BYTES + 2 * BMAT_BYTES + 3 * size_t(CL) * LDP * 4 +
+                                       (2 * CL + 4 * CL + DP + NBLK * DP) * sizeof(float) +
+                                       6 * DP * sizeof(bf16);
 static_assert(3 * size_t(CL) * LDP * 4 >= 2 * BSTATE_BYTES, "closure panels overlay both BF16 states");
 
 template <bool FAST>
@@ -635,11 +779,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
     int ph = 0;
     SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* b_ut = reinterpret_cast<bf16*>(smem_raw);   // U~      -> dUbar
-    bf16* b_un = b_ut + BSLOT_ELEMS;                   // Uneg    -> dUt
-    bf16* b_dl = b_un + BSLOT_ELEMS;                   // Delta   -> Ti
+    bf16* b_ur = reinterpret_cast<bf16*>(smem_raw);   // u^ rowE -> dUbar
+    bf16* b_uc = b_ur + BSLOT_ELEMS;                   // u^ col  -> dUt
+    bf16* b_dl = b_uc + BSLOT_ELEMS;                   // Delta   -> t_i
     bf16* b_dr = b_dl + BSLOT_ELEMS;                   // dRr (kept)
-    bf16* b_N = b_dr + BSLOT_ELEMS;                    // N, dN   -> Tj
+    bf16* b_tj = b_dr + BSLOT_ELEMS;                   // t_j
+    bf16* b_N = b_tj + BSLOT_ELEMS;
     bf16* b_dN = b_N + BMAT_ELEMS;
     unsigned char* region = reinterpret_cast<unsigned char*>(b_dN + BMAT_ELEMS);
     bf16* b_Ct = reinterpret_cast<bf16*>(region);      // Ct, dC  -> dG, dE, X (FP32)
@@ -648,68 +793,108 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
     float* s_dE = s_dG + CL * LDP;
     float* s_X = s_dE + CL * LDP;
     float* s_gam = s_X + CL * LDP;
-    float* s_dot = s_gam + CL;   // [CL][4]
+    float* s_ru = s_gam + CL;    // 1/|u| per row
+    float* s_dot = s_ru + CL;    // [CL][4]
     float* s_cdc = s_dot + 4 * CL;  // [DP]
+    float* s_beta = s_cdc + DP;
+    bf16* s_Mb = reinterpret_cast<bf16*>(s_beta + NBLK * DP);
+    bf16* s_pref = s_Mb + 3 * DP;   // exp(Gprev_I) for I = 1..3: U~ = (u^ rowE) .* pref along channels
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r;
     const float* gG = panel_ptr(p.Gp, ch.gi);
+    auto fG = [&](int i, int c) { return gG[i * DP + c]; };
 
     async_bpanel(b_dr, bpanel_ptr(p.dRr, ch.gi));
     async_bstate(b_dC, bstate_ptr(p.dCeCk, ch.gi));
     async_bstate(b_Ct, bstate_ptr(p.CtCkB, ch.gi));
     cp_commit();
     load_gamma(p.gam, ch, s_gam);
+    block_betas(s_beta, fG);
+    pair_block_scales_bf16(s_Mb, fG);
+    for (int idx = threadIdx.x; idx < 3 * DP; idx += NTHREADS) {
+        const int m = idx >> 7, c = idx & (DP - 1);
+        s_pref[idx] = __float2bfloat16_rn(__expf(gG[((m + 1) * BT - 1) * DP + c]));
+    }
     {
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
         const float* gDelta = panel_ptr(p.Delta, ch.gi);
 #pragma unroll 1
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
-            const int i = lr + ROWS_PER_PASS * pp;
-            float uh[8], G[8], E[8], dl[8];
-            load8_norm<FAST>(p.u, ch, i, c0, r, uh);
+            const int i = lr + ROWS_PER_PASS * pp, i0 = i & ~(BT - 1);
+            float uh[8], G[8], E[8], Gp[8], Ge[8], dl[8];
+            const float ru = load8_norm<FAST>(p.u, ch, i, c0, r, uh);
             load8_panel(gG, i, c0, G);
             load8_panel(gG, i > 0 ? i - 1 : 0, c0, E);  // E = G of the previous row (0 for the first)
-#pragma unroll
-            for (int e = 0; e < 8; ++e) E[e] = i > 0 ? E[e] : 0.f;
-            load8_panel(gDelta, i, c0, dl);
-            float un[8], ut[8];
+            load8_panel(gG, i0 ? i0 - 1 : 0, c0, Gp);
+            load8_panel(gG, i0 + BT - 1, c0, Ge);
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-                un[e] = uh[e] * clamp_exp_neg(G[e]);
-                ut[e] = uh[e] * __expf(E[e]);
+                E[e] = i > 0 ? E[e] : 0.f;
+                Gp[e] = i0 ? Gp[e] : 0.f;
             }
-            store8_bsm(b_un, i, c0, un);
-            store8_bsm(b_ut, i, c0, ut);
+            load8_panel(gDelta, i, c0, dl);
+            float uc[8], ur[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                uc[e] = uh[e] * __expf(Ge[e] - G[e]);
+                ur[e] = uh[e] * __expf(E[e] - Gp[e]);
+            }
+            store8_bsm(b_uc, i, c0, uc);
+            store8_bsm(b_ur, i, c0, ur);
             store8_bsm(b_dl, i, c0, dl);
+            if ((threadIdx.x & 15) == 0) s_ru[i] = ru;
         }
     }
     cp_wait<0>();
     __syncthreads();
     SD_PHASE(p.g, ph);
     {
-        float a1[NT64][4], a2[NT64][4];
-        acc_zero<NT64>(a1);
-        acc_zero<NT64>(a2);
         const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
-        warp_mma_bf16<NT64, false, true>(a1, b_ut, LDB, b_un, LDB, r0, n0, 0, DP);
-        warp_mma_bf16<NT64, false, true>(a2, b_dr, LDB, b_dl, LDB, r0, n0, 0, DP);
-        warp_epi<NT64>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
-            *reinterpret_cast<__nv_bfloat162*>(b_N + i * LDM + j) =
-                __floats2bfloat162_rn((j < i) ? v0 : 0.f, (j + 1 < i) ? v1 : 0.f);
+        pair_offdiag_bf16(s_Mb, b_ur, b_uc, [&](int i, int j, float v0, float v1) {
+            *reinterpret_cast<__nv_bfloat162*>(b_N + i * LDM + j) = __floats2bfloat162_rn(v0, v1);
         });
+        float a2[NT64][4];
+        acc_zero<NT64>(a2);
+        if (n0 <= r0) warp_mma_bf16<NT64, false, true>(a2, b_dr, LDB, b_dl, LDB, r0, n0, 0, DP);
         warp_epi<NT64>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
             float gm = -s_gam[i];
             *reinterpret_cast<__nv_bfloat162*>(b_dN + i * LDM + j) =
                 __floats2bfloat162_rn((j < i) ? gm * v0 : 0.f, (j + 1 < i) ? gm * v1 : 0.f);
         });
     }
+    // raw u^ rows: the BF16 operand times its stored 1/|u|
+    auto fu8 = [&](int j, int c0, float (&b)[8]) {
+        load8_bf16<FAST>(row_bf16(p.u, ch, j), c0, r, p.u.vec, j < ch.nvalid, b);
+        const float rs = s_ru[j];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) b[e] *= rs;
+    };
+    {   // diagonal blocks of N
+        const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8, l16 = threadIdx.x & 15;
+#pragma unroll 1
+        for (int pp = 0; pp < ROW_PASSES; ++pp) {
+            const int i = lr + ROWS_PER_PASS * pp, i0 = i & ~(BT - 1);
+            float a[1][8], E[8], out[1];
+            load8_panel(gG, i > 0 ? i - 1 : 0, c0, E);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) E[e] = i > 0 ? E[e] : 0.f;
+            fu8(i, c0, a[0]);
+            pair_diag_row<1, true>(i, a, E, [&](int j, float (&b)[8]) { fu8(j, c0, b); },
+                                   [&](int j, float (&Gj)[8]) { load8_panel(gG, j, c0, Gj); }, out);
+            b_N[i * LDM + i0 + l16] = __float2bfloat16_rn(out[0]);
+        }
+    }
     __syncthreads();
     SD_PHASE(p.g, ph);
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
+    const int I = r0 / BT;
     {   // residual rows and dgamma_i = sum_a dRr[i][a] (h[i][a] - (U~ Ct)[i][a] - (N Delta)[i][a])
         float acc[NT128][4];
         acc_zero<NT128>(acc);
-        warp_mma_bf16<NT128, false, false>(acc, b_ut, LDB, b_Ct, LDB, r0, n0, 0, DP);
+        if (I == 0)
+            warp_mma_bf16<NT128, false, false>(acc, b_ur, LDB, b_Ct, LDB, r0, n0, 0, DP);
+        else
+            warp_mma_bf16_kscale<NT128, false>(acc, b_ur, LDB, b_Ct, LDB, r0, n0, 0, DP, s_pref + (I - 1) * DP);
         warp_mma_bf16<NT128, false, false>(acc, b_N, LDM, b_dl, LDB, r0, n0, 0, r0 + 16);
         const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
         const int ia = r0 + g, ib = ia + 8;
@@ -764,22 +949,55 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
         // dUbar[j][c] = sum_a Delta[j][a] dCt[c][a] ; dUt[i][c] = -gamma_i sum_a dRr[i][a] Ct[c][a]
         warp_mma_bf16<NT128, false, true>(aub, b_dl, LDB, b_dC, LDB, r0, n0, 0, DP);
         warp_mma_bf16<NT128, false, true>(aut, b_dr, LDB, b_Ct, LDB, r0, n0, 0, DP);
-        warp_mma_bf16<NT128, false, false>(ati, b_dN, LDM, b_un, LDB, r0, n0, 0, r0 + 16);
-        warp_mma_bf16<NT128, true, false>(atj, b_dN, LDM, b_ut, LDB, r0, n0, r0, CL);
+        for (int J = 0; J < I; ++J) {   // t_i off the diagonal blocks, Horner from the chunk start
+            if (J > 0) scale_acc<NT128>(ati, s_beta + J * DP, n0);
+            warp_mma_bf16<NT128, false, false>(ati, b_dN, LDM, b_uc, LDB, r0, n0, J * BT, J * BT + BT);
+        }
+        for (int K = NBLK - 1; K > I; --K) {   // t_j off the diagonal blocks, Horner from the chunk end
+            if (K < NBLK - 1) scale_acc<NT128>(atj, s_beta + K * DP, n0);
+            warp_mma_bf16<NT128, true, false>(atj, b_dN, LDM, b_ur, LDB, r0, n0, K * BT, K * BT + BT);
+        }
         __syncthreads();  // every contraction has read its operands: overlay the results
         SD_PHASE(p.g, ph);
-        epi_store_bsm<NT128>(aub, r0, n0, b_ut);
+        epi_store_bsm<NT128>(aub, r0, n0, b_ur);
         warp_epi<NT128>(aut, r0, n0, [&](int i, int j, float v0, float v1) {
             float gm = -s_gam[i];
-            *reinterpret_cast<__nv_bfloat162*>(b_un + i * LDB + j) = __floats2bfloat162_rn(gm * v0, gm * v1);
+            *reinterpret_cast<__nv_bfloat162*>(b_uc + i * LDB + j) = __floats2bfloat162_rn(gm * v0, gm * v1);
         });
-        epi_store_bsm<NT128>(ati, r0, n0, b_dl);
-        epi_store_bsm<NT128>(atj, r0, n0, b_N);
+        epi_scale_store_bsm<NT128>(ati, r0, n0, b_dl, [&](int i, int j) {   // exp(E_i - Gprev_I)
+            float2 E = make_float2(0.f, 0.f), Gp = make_float2(0.f, 0.f);
+            if (i > 0) E = *reinterpret_cast<const float2*>(gG + (i - 1) * DP + j);
+            if (r0) Gp = *reinterpret_cast<const float2*>(gG + (r0 - 1) * DP + j);
+            return make_float2(__expf(E.x - Gp.x), __expf(E.y - Gp.y));
+        });
+        epi_scale_store_bsm<NT128>(atj, r0, n0, b_tj, [&](int i, int j) {   // exp(Gend_J - G_j)
+            const float2 G = *reinterpret_cast<const float2*>(gG + i * DP + j);
+            const float2 Ge = *reinterpret_cast<const float2*>(gG + (r0 + BT - 1) * DP + j);
+            return make_float2(__expf(Ge.x - G.x), __expf(Ge.y - G.y));
+        });
     }
     if (threadIdx.x < CL && threadIdx.x < ch.nvalid) {
         const int i = threadIdx.x;
         p.dgam[((long long)ch.b * p.g.T + ch.t0 + i) * p.g.H + ch.hh] =
             (s_dot[i * 4] + s_dot[i * 4 + 1]) + (s_dot[i * 4 + 2] + s_dot[i * 4 + 3]);
+    }
+    __syncthreads();
+    SD_PHASE(p.g, ph);
+    {   // diagonal blocks of t_i and t_j, one thread per (channel, block)
+        float al[BT];
+        block_alphas(al, fG);
+        auto fu = [&](int j, int c) {
+            return (j < ch.nvalid && c < r) ? __bfloat162float(row_bf16(p.u, ch, j)[c]) * s_ru[j] : 0.f;
+        };
+        auto fP = [&](int i, int j) { return __bfloat162float(b_dN[i * LDM + j]); };
+        auto add_to = [](bf16* panel) {
+            return [panel](int i, int c, float v) {
+                bf16* q = panel + i * LDB + c;
+                *q = __float2bfloat16_rn(__bfloat162float(*q) + v);
+            };
+        };
+        causal_diag<true, true>(al, fP, fu, add_to(b_dl));
+        anti_diag<true, true>(al, fP, fu, add_to(b_tj));
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
@@ -798,19 +1016,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
             for (int e = 0; e < 8; ++e) E[e] = i > 0 ? E[e] : 0.f;
             float dup[8], tpre[8], dub[8], dut[8], ti[8], tj[8], dgp[8], xext[8], drr[8];
             load8_bpanel(bpanel_ptr(p.duPart, ch.gi), i, c0, dup);
-            load8_bpanel(bpanel_ptr(p.Tpre, ch.gi), i, c0, tpre);
+            load8_bpanel(bpanel_ptr(p.Tu, ch.gi), i, c0, tpre);
             load8_bpanel(bpanel_ptr(p.dGPart, ch.gi), i, c0, dgp);
             load8_bpanel(bpanel_ptr(p.Xext, ch.gi), i, c0, xext);
-            load8_bsm(b_ut, i, c0, dub);
-            load8_bsm(b_un, i, c0, dut);
+            load8_bsm(b_ur, i, c0, dub);
+            load8_bsm(b_uc, i, c0, dut);
             load8_bsm(b_dl, i, c0, ti);
-            load8_bsm(b_N, i, c0, tj);
+            load8_bsm(b_tj, i, c0, tj);
             load8_bsm(b_dr, i, c0, drr);
             float duh[8], dE[8], dG[8], X[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-                float eE = __expf(E[e]), en = clamp_exp_neg(G[e]), et = __expf(GL[e] - G[e]);
-                float tu = en * tpre[e], t_i = eE * ti[e], t_j = en * tj[e];
+                const float eE = __expf(E[e]), et = __expf(GL[e] - G[e]);
+                const float tu = tpre[e], t_i = ti[e], t_j = tj[e];
                 duh[e] = dup[e] + tu + dub[e] * et + dut[e] * eE + t_i + t_j;
                 dE[e] = dut[e] * (uh[e] * eE) + uh[e] * t_i;
                 X[e] = xext[e] + dub[e] * (uh[e] * et);

@@ -68,6 +68,40 @@ __device__ __forceinline__ void warp_mma_bf16(float (&acc)[NTW][4], const bf16* 
     }
 }
 
+// Same contraction with the A operand scaled along k by mvec[k] (BF16, one value
+// per k; A not transposed): acc += (A .* mvec) * B.
+template <int NTW, bool TB>
+__device__ __forceinline__ void warp_mma_bf16_kscale(float (&acc)[NTW][4], const bf16* A, int lda, const bf16* B,
+                                                     int ldb, int r0, int n0, int kbeg, int kend, const bf16* mvec) {
+    const int lane = threadIdx.x & 31, j = lane >> 3, rr = lane & 7, t = lane & 3;
+#pragma unroll 2
+    for (int kk = kbeg; kk < kend; kk += 16) {
+        uint32_t a[4];
+        ldsm_x4(a, A + (r0 + (lane & 15)) * lda + kk + (lane >> 4) * 8);
+        {
+            // fragment registers 0,1 hold k = kk + 2t (+1), registers 2,3 hold k = kk + 8 + 2t (+1)
+            const __nv_bfloat162 mlo = *reinterpret_cast<const __nv_bfloat162*>(mvec + kk + 2 * t);
+            const __nv_bfloat162 mhi = *reinterpret_cast<const __nv_bfloat162*>(mvec + kk + 8 + 2 * t);
+            __nv_bfloat162* af = reinterpret_cast<__nv_bfloat162*>(a);
+            af[0] = __hmul2(af[0], mlo);
+            af[1] = __hmul2(af[1], mlo);
+            af[2] = __hmul2(af[2], mhi);
+            af[3] = __hmul2(af[3], mhi);
+        }
+#pragma unroll
+        for (int nt = 0; nt < NTW; nt += 2) {
+            uint32_t b[4];
+            if (TB) {
+                ldsm_x4(b, B + (n0 + (nt + (j >> 1)) * 8 + rr) * ldb + kk + (j & 1) * 8);
+            } else {
+                ldsm_x4_t(b, B + (kk + (j & 1) * 8 + rr) * ldb + n0 + (nt + (j >> 1)) * 8);
+            }
+            mma_bf16(acc[nt], a, b[0], b[1]);
+            mma_bf16(acc[nt + 1], a, b[2], b[3]);
+        }
+    }
+}
+
 // ---- movers -----------------------------------------------------------------
 __device__ __forceinline__ uint4 pack8_bf16(const float (&x)[8]) {
     uint4 raw;

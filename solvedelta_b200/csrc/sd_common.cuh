@@ -23,7 +23,6 @@ constexpr int ROW_PASSES = CL / ROWS_PER_PASS;
 constexpr int NT128 = DP / 32;            // 8-column MMA tiles per warp for a CL x DP output
 constexpr int NT64 = CL / 32;             // ... for a CL x CL output
 constexpr float RHO = 0.625f; // radius of the residual-local frame
-constexpr float EXP_CLAMP = 80.0f;
 
 constexpr int SLOT_FLOATS = (CL * LDP > DP * LDH) ? CL * LDP : DP * LDH;
 constexpr int MAT_FLOATS = CL * LDA;
@@ -86,11 +85,6 @@ __device__ __forceinline__ float* state_ptr(float* base, long long gi) {
 }
 __device__ __forceinline__ const float* state_ptr(const float* base, long long gi) {
     return base + gi * (long long)(DP * DP);
-}
-
-__device__ __forceinline__ float clamp_exp_neg(float G) {
-    // exp(-G) with the exponent clamped so that strong forgetting stays finite
-    return __expf(fminf(-G, EXP_CLAMP));
 }
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }

@@ -1,0 +1,240 @@
+// Block-centred decay factors for the intra-chunk contractions.
+//
+// A chunk of CL tokens is cut into NBLK blocks of BT tokens.  With G the
+// inclusive prefix of the log decay inside the chunk, E = G - g the exclusive
+// one, and Gprev_I / Gend_I the prefix just before / at the end of block I,
+// every decay-weighted term exp(x_i - G_j) (x = G or E, j <= i) is evaluated
+// from factors that never exceed one, so no reciprocal retention exp(-G) is
+// ever formed and arbitrarily strong forgetting stays exact:
+//   rowG_i = exp(G_i - Gprev_I),  rowE_i = exp(E_i - Gprev_I)    row side
+//   col_j  = exp(Gend_J - G_j)                                    column side
+//   beta_J = exp(Gend_J - Gprev_J)                                a whole block
+//   exp(x_i - G_j) = row_i * (prod_{J<K<I} beta_K) * col_j        for J < I
+// and inside one block (I == J) the exponent is evaluated directly.
+//
+// Three contraction forms use this:
+//   pair   A[i][j]   = sum_c a[i][c] b[j][c] exp(x_ic - G_jc)
+//   causal out[i][c] = sum_{j<=i} P[i][j] b[j][c] exp(x_ic - G_jc)
+//   anti   out[j][c] = sum_{i>=j} P[i][j] a[i][c] exp(x_ic - G_jc)
+// Off-diagonal blocks run on the tensor cores over row-/column-centred panels
+// (pair: the beta product scales the row operand along the contraction; causal
+// / anti: the accumulator is multiplied by beta between blocks, Horner-style).
+// The helpers here cover the factors and the diagonal blocks.
+//
+// Upstream counterpart: the centred cross-subchunk factorisation and direct
+// diagonal subchunks of causallsso/ops/residual_frame/vector_pair.py:1-16.
+#pragma once
+#include "sd_bf16.cuh"
+#include "sd_common.cuh"
+
+namespace sd {
+
+constexpr int BT = 16;          // tokens per decay block
+constexpr int NBLK = CL / BT;   // blocks per chunk
+
+// s_beta[J][c] = exp(Gend_J - Gprev_J); fg(i, c) returns the chunk prefix G.
+template <class FG>
+__device__ __forceinline__ void block_betas(float* s_beta, FG fg) {
+    for (int idx = threadIdx.x; idx < NBLK * DP; idx += NTHREADS) {
+        const int J = idx >> 7, c = idx & (DP - 1);
+        const float hi = fg(BT * J + BT - 1, c);
+        const float lo = J ? fg(BT * J - 1, c) : 0.f;
+        s_beta[idx] = __expf(hi - lo);
+    }
+}
+
+// Row-operand scale of an off-diagonal pair block (I, J), I - J >= 2:
+//   s_M[0] = beta_1 (blocks (2,0)),  s_M[1] = beta_2 ((3,1)),  s_M[2] = beta_1 beta_2 ((3,0)).
+template <class FG>
+__device__ __forceinline__ void pair_block_scales(float* s_M, FG fg) {
+    static_assert(NBLK == 4, "pair scale table is written for four blocks");
+    for (int idx = threadIdx.x; idx < 3 * DP; idx += NTHREADS) {
+        const int m = idx >> 7, c = idx & (DP - 1);
+        const float e0 = fg(BT - 1, c), e1 = fg(2 * BT - 1, c), e2 = fg(3 * BT - 1, c);
+        s_M[idx] = __expf(m == 0 ? e1 - e0 : (m == 1 ? e2 - e1 : e2 - e0));
+    }
+}
+__device__ __forceinline__ int pair_scale_index(int I, int J) {  // -1: adjacent blocks, no scale
+    return (I - J < 2) ? -1 : (I - J == 3 ? 2 : J);
+}
+
+// acc columns n0 + 8 nt + 2t (+1) *= vec[column]
+template <int NTW>
+__device__ __forceinline__ void scale_acc(float (&acc)[NTW][4], const float* vec, int n0) {
+    const int t = threadIdx.x & 3;
+#pragma unroll
+    for (int nt = 0; nt < NTW; ++nt) {
+        const float2 b = *reinterpret_cast<const float2*>(vec + n0 + nt * 8 + 2 * t);
+        acc[nt][0] *= b.x; acc[nt][1] *= b.y;
+        acc[nt][2] *= b.x; acc[nt][3] *= b.y;
+    }
+}
+
+// ---- off-diagonal blocks of a pair on the tensor cores (TF32) ------------------
+// Warp (I = row tile, J = column quarter) of the CL x CL tiling owns block (I, J).
+// fr(i, k): row-centred operand, fc(j, k): column-centred operand, k = channel.
+// fe(i, j, v0, v1) receives every element outside the diagonal blocks: the
+// contraction below them, zeros above.
+template <class FR, class FC, class FE>
+__device__ __forceinline__ void pair_offdiag_tf32(const float* s_M, FR fr, FC fc, FE fe) {
+    const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
+    const int I = r0 / BT, J = n0 / BT;
+    if (I == J) return;
+    float acc[NT64][4];
+    acc_zero<NT64>(acc);
+    if (J < I) {
+        const int m = pair_scale_index(I, J);
+        auto fb = [&](int k, int n) { return fc(n, k); };
+        if (m < 0) {
+            warp_mma<NT64>(acc, r0, n0, 0, DP, fr, fb);
+        } else {
+            const float* mv = s_M + m * DP;
+            warp_mma<NT64>(acc, r0, n0, 0, DP, [&](int i, int k) { return fr(i, k) * mv[k]; }, fb);
+        }
+    }
+    warp_epi<NT64>(acc, r0, n0, fe);
+}
+
+// BF16 copy of the pair scale table for the BF16 contractions.
+template <class FG>
+__device__ __forceinline__ void pair_block_scales_bf16(bf16* s_Mb, FG fg) {
+    static_assert(NBLK == 4, "pair scale table is written for four blocks");
+    for (int idx = threadIdx.x; idx < 3 * DP; idx += NTHREADS) {
+        const int m = idx >> 7, c = idx & (DP - 1);
+        const float e0 = fg(BT - 1, c), e1 = fg(2 * BT - 1, c), e2 = fg(3 * BT - 1, c);
+        s_Mb[idx] = __float2bfloat16_rn(__expf(m == 0 ? e1 - e0 : (m == 1 ? e2 - e1 : e2 - e0)));
+    }
+}
+
+// Off-diagonal pair blocks, BF16 operands in shared panels of pitch LDB:
+// R row-centred, C column-centred.  fe as for pair_offdiag_tf32.
+template <class FE>
+__device__ __forceinline__ void pair_offdiag_bf16(const bf16* s_Mb, const bf16* R, const bf16* C, FE fe) {
+    const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
+    const int I = r0 / BT, J = n0 / BT;
+    if (I == J) return;
+    float acc[NT64][4];
+    acc_zero<NT64>(acc);
+    if (J < I) {
+        const int m = pair_scale_index(I, J);
+        if (m < 0)
+            warp_mma_bf16<NT64, false, true>(acc, R, LDB, C, LDB, r0, n0, 0, DP);
+        else
+            warp_mma_bf16_kscale<NT64, true>(acc, R, LDB, C, LDB, r0, n0, 0, DP, s_Mb + m * DP);
+    }
+    warp_epi<NT64>(acc, r0, n0, fe);
+}
+
+// ---- diagonal blocks of a pair, row-wise mapping -----------------------------
+// The calling half-warp owns token row i and each lane eight channels of it:
+// a[n][8] are NA row operands sharing one exponent, x[8] the row prefix (G or E).
+// fb8(j, b) / fg8(j, G) fetch the same eight channels of column-side row j.
+// For every j of the row's own block with j <= i (j < i when STRICT):
+//   val[n] = sum_c a[n][c] b[j][c] exp(x[c] - G[j][c])
+// and lane (j mod BT) of the half-warp receives val in out[n]; other entries of the
+// block row are returned as zero.  All 32 lanes of the warp must call together
+// (the two rows of a warp lie in the same block).
+template <int NA, bool STRICT, class FB8, class FG8>
+__device__ __forceinline__ void pair_diag_row(int i, const float (&a)[NA][8], const float (&x)[8], FB8 fb8, FG8 fg8,
+                                              float (&out)[NA]) {
+    const int l16 = threadIdx.x & 15;
+    const int i0 = i & ~(BT - 1), ii = i & (BT - 1);
+    const int jmax = (ii | 1) - (STRICT ? 1 : 0);  // uniform over the warp's two rows (2w, 2w+1)
+#pragma unroll
+    for (int n = 0; n < NA; ++n) out[n] = 0.f;
+    for (int jj = 0; jj <= jmax; ++jj) {
+        float b[8], G[8], s[NA];
+        fb8(i0 + jj, b);
+        fg8(i0 + jj, G);
+        const bool live = STRICT ? (jj < ii) : (jj <= ii);
+#pragma unroll
+        for (int n = 0; n < NA; ++n) s[n] = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float w = live ? b[e] * __expf(fminf(x[e] - G[e], 0.f)) : 0.f;
+#pragma unroll
+            for (int n = 0; n < NA; ++n) s[n] = fmaf(a[n][e], w, s[n]);
+        }
+#pragma unroll
+        for (int n = 0; n < NA; ++n) {
+            const float v = row_sum16(s[n]);
+            if (l16 == jj) out[n] = v;
+        }
+    }
+}
+
+// ---- diagonal blocks of a causal / anti-causal sum, one thread per (channel, block) ----
+// Thread (c = tid mod DP, I = tid / DP) walks the BT x BT block I of P with the
+// retention exp(x_i - G_j) built as a running product of alpha_k = exp(g_k), so
+// only BT exponentials are taken per thread.
+//   XE: x is the exclusive prefix (the term j == i does not exist then).
+//   al: the thread's alphas (block_alphas);  fP(i, j): P[i][j];
+//   fv(j, c): column-side operand (causal) / row-side operand (anti);  fo(i, c, value).
+template <class FG>
+__device__ __forceinline__ void block_alphas(float (&al)[BT], FG fG) {
+    static_assert(NTHREADS == NBLK * DP, "one thread per (channel, block)");
+    const int c = threadIdx.x & (DP - 1), i0 = (threadIdx.x >> 7) * BT;
+    float prev = i0 ? fG(i0 - 1, c) : 0.f;
+#pragma unroll
+    for (int k = 0; k < BT; ++k) {
+        const float g = fG(i0 + k, c);
+        al[k] = __expf(g - prev);
+        prev = g;
+    }
+}
+
+template <bool XE, bool STRICT, class FP, class FV, class FO>
+__device__ __forceinline__ void causal_diag(const float (&al)[BT], FP fP, FV fv, FO fo) {
+    const int c = threadIdx.x & (DP - 1), i0 = (threadIdx.x >> 7) * BT;
+    float bv[BT];
+#pragma unroll
+    for (int k = 0; k < BT; ++k) bv[k] = fv(i0 + k, c);
+#pragma unroll
+    for (int ii = 0; ii < BT; ++ii) {
+        float acc = 0.f, rho = 1.f;
+        if (!XE) {
+#pragma unroll
+            for (int jj = ii; jj >= 0; --jj) {
+                if (!(STRICT && jj == ii)) acc = fmaf(fP(i0 + ii, i0 + jj) * bv[jj], rho, acc);
+                rho *= al[jj];
+            }
+        } else {
+#pragma unroll
+            for (int jj = ii - 1; jj >= 0; --jj) {
+                acc = fmaf(fP(i0 + ii, i0 + jj) * bv[jj], rho, acc);
+                rho *= al[jj];
+            }
+        }
+        fo(i0 + ii, c, acc);
+    }
+}
+
+template <bool XE, bool STRICT, class FP, class FV, class FO>
+__device__ __forceinline__ void anti_diag(const float (&al)[BT], FP fP, FV fv, FO fo) {
+    const int c = threadIdx.x & (DP - 1), i0 = (threadIdx.x >> 7) * BT;
+    float av[BT];
+#pragma unroll
+    for (int k = 0; k < BT; ++k) av[k] = fv(i0 + k, c);
+#pragma unroll
+    for (int jj = 0; jj < BT; ++jj) {
+        float acc = 0.f, rho = 1.f;
+        if (!XE) {
+            // exp(G_i - G_j): 1 at i == j, then times alpha_{i} for each further row
+#pragma unroll
+            for (int ii = jj; ii < BT; ++ii) {
+                if (ii > jj) rho *= al[ii];
+                if (!(STRICT && ii == jj)) acc = fmaf(fP(i0 + ii, i0 + jj) * av[ii], rho, acc);
+            }
+        } else {
+            // exp(E_i - G_j) = exp(G_{i-1} - G_j): 1 at i == j + 1
+#pragma unroll
+            for (int ii = jj + 1; ii < BT; ++ii) {
+                if (ii > jj + 1) rho *= al[ii - 1];
+                acc = fmaf(fP(i0 + ii, i0 + jj) * av[ii], rho, acc);
+            }
+        }
+        fo(i0 + jj, c, acc);
+    }
+}
+
+}  // namespace sd

@@ -5,6 +5,7 @@
 #pragma once
 #include "sd_bf16.cuh"
 #include "sd_common.cuh"
+#include "sd_decay.cuh"
 
 namespace sd {
 
@@ -97,7 +98,7 @@ __device__ __forceinline__ void store8_smem(float* sm, int i, int c0, const floa
 // Predictor preparation: pair matrix Lm, and the two solved panels
 //   Upd = (I+Lm)^-1 (gamma h),  W = (I+Lm)^-1 (gamma U~)   (stored negated as Qc)
 // so that the C scan is  Delta = Upd + Qc Ct.
-constexpr size_t PREP_FWD_SMEM = 5 * SLOT_BYTES + MAT_BYTES + CL * sizeof(float);
+constexpr size_t PREP_FWD_SMEM = 5 * SLOT_BYTES + MAT_BYTES + (CL + 3 * DP) * sizeof(float);
 
 template <bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
@@ -106,11 +107,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
     extern __shared__ __align__(16) float smem[];
     float* s_uh = smem;
     float* s_G = s_uh + SLOT_FLOATS;
-    float* s_ut = s_G + SLOT_FLOATS;
-    float* s_un = s_ut + SLOT_FLOATS;
+    float* s_ut = s_G + SLOT_FLOATS;   // u^ rowE (block-centred), then gamma U~ / W
+    float* s_un = s_ut + SLOT_FLOATS;  // u^ col  (block-centred)
     float* s_h = s_un + SLOT_FLOATS;
     float* s_lm = s_h + SLOT_FLOATS;
     float* s_gam = s_lm + MAT_FLOATS;
+    float* s_M = s_gam + CL;
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r;
 
@@ -123,35 +125,54 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
     chunk_cumsum(s_G);
     __syncthreads();
     SD_PHASE(p.g, ph);
+    auto fG = [&](int i, int c) { return s_G[i * LDP + c]; };
+    pair_block_scales(s_M, fG);
     for (int idx = threadIdx.x; idx < CL * DP; idx += NTHREADS) {
         int i = idx >> 7, c = idx & (DP - 1);
+        const int i0 = i & ~(BT - 1);
         float G = s_G[i * LDP + c];
         float E = i ? s_G[(i - 1) * LDP + c] : 0.f;
+        float Gprev = i0 ? s_G[(i0 - 1) * LDP + c] : 0.f;
+        float Gend = s_G[(i0 + BT - 1) * LDP + c];
         float uh = s_uh[i * LDP + c];
-        s_ut[i * LDP + c] = uh * __expf(E);
-        s_un[i * LDP + c] = uh * clamp_exp_neg(G);
+        s_ut[i * LDP + c] = uh * __expf(E - Gprev);
+        s_un[i * LDP + c] = uh * __expf(Gend - G);
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
+    // Lm = gamma stril(N), N[i][j] = sum_c u^_ic u^_jc exp(E_ic - G_jc)
+    pair_offdiag_tf32(s_M, [&](int i, int k) { return s_ut[i * LDP + k]; },
+                      [&](int j, int k) { return s_un[j * LDP + k]; },
+                      [&](int i, int j, float v0, float v1) {
+                          float gm = s_gam[i];
+                          *reinterpret_cast<float2*>(s_lm + i * LDA + j) = make_float2(gm * v0, gm * v1);
+                      });
     {
-        float acc[NT64][4];
-        acc_zero<NT64>(acc);
-        const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
-        warp_mma<NT64>(acc, r0, n0, 0, DP, [&](int i, int k) { return s_ut[i * LDP + k]; },
-                    [&](int k, int n) { return s_un[n * LDP + k]; });
-        warp_epi<NT64>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
-            float gm = s_gam[i];
-            s_lm[i * LDA + j] = (j < i) ? gm * v0 : 0.f;
-            s_lm[i * LDA + j + 1] = (j + 1 < i) ? gm * v1 : 0.f;
-        });
+        const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
+#pragma unroll 1
+        for (int pp = 0; pp < ROW_PASSES; ++pp) {
+            const int i = lr + ROWS_PER_PASS * pp;
+            float a[1][8], x[8], out[1];
+            load8_smem(s_uh, i, c0, a[0]);
+            if (i > 0) {
+                load8_smem(s_G, i - 1, c0, x);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] = 0.f;
+            }
+            pair_diag_row<1, true>(i, a, x, [&](int j, float (&b)[8]) { load8_smem(s_uh, j, c0, b); },
+                                   [&](int j, float (&G)[8]) { load8_smem(s_G, j, c0, G); }, out);
+            s_lm[i * LDA + (i & ~(BT - 1)) + (threadIdx.x & 15)] = s_gam[i] * out[0];
+        }
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
     for (int idx = threadIdx.x; idx < CL * DP; idx += NTHREADS) {
         int i = idx >> 7, c = idx & (DP - 1);
         float gm = s_gam[i];
+        float E = i ? s_G[(i - 1) * LDP + c] : 0.f;
         s_h[i * LDP + c] *= gm;
-        s_ut[i * LDP + c] *= gm;
+        s_ut[i * LDP + c] = gm * s_uh[i * LDP + c] * __expf(E);
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
@@ -181,8 +202,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
 
 // ---------------------------------------------------------------------------
 // Primal address d = k^ + C_t^T k^ for every token of the chunk:
-//   d = k^ + exp(G) * ( K^ Ct^T + tril(K^ Delta^T) (U^ exp(-G)) ).
-constexpr size_t PRIMAL_FWD_SMEM = 6 * SLOT_BYTES + MAT_BYTES;
+//   d_i = k^_i + exp(G_i) (K^ Ct^T)_i + sum_{j<=i} (k^_i . Delta_j) u^_j exp(G_i - G_j),
+// the decay-weighted sum in block-centred form (Horner over blocks, direct diagonal).
+constexpr size_t PRIMAL_FWD_SMEM = 6 * SLOT_BYTES + MAT_BYTES + NBLK * DP * sizeof(float);
 
 __device__ __forceinline__ void async_panel_f32(float* sm, const float* g) {
     for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += NTHREADS) {
@@ -209,6 +231,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
     float* s_st0 = s_dl + SLOT_FLOATS;
     float* s_st1 = s_st0 + SLOT_FLOATS;
     float* s_aqk = s_st1 + SLOT_FLOATS;
+    float* s_beta = s_aqk + MAT_FLOATS;
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r;
     const float* ct = state_ptr(p.CtCk, ch.gi);
@@ -226,22 +249,37 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
     cp_wait<2>();
     __syncthreads();
     SD_PHASE(p.g, ph);
-    for (int idx = threadIdx.x; idx < CL * DP; idx += NTHREADS) {
-        int i = idx >> 7, c = idx & (DP - 1);
-        s_un[i * LDP + c] *= clamp_exp_neg(s_G[i * LDP + c]);
-    }
+    auto fG = [&](int i, int c) { return s_G[i * LDP + c]; };
+    block_betas(s_beta, fG);
     {
         float acc[NT64][4];
         acc_zero<NT64>(acc);
         const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
-        warp_mma<NT64>(acc, r0, n0, 0, DP, [&](int i, int k) { return s_kh[i * LDP + k]; },
-                    [&](int k, int n) { return s_dl[n * LDP + k]; });
+        if (n0 <= r0)
+            warp_mma<NT64>(acc, r0, n0, 0, DP, [&](int i, int k) { return s_kh[i * LDP + k]; },
+                        [&](int k, int n) { return s_dl[n * LDP + k]; });
         warp_epi<NT64>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
             s_aqk[i * LDA + j] = (j <= i) ? v0 : 0.f;
             s_aqk[i * LDA + j + 1] = (j + 1 <= i) ? v1 : 0.f;
         });
     }
-    cp_wait<1>();
+    __syncthreads();
+    SD_PHASE(p.g, ph);
+    // diagonal blocks directly (Delta is dead: its slot takes the result), then centre u^ on its block end
+    {
+        float al[BT];
+        block_alphas(al, fG);
+        causal_diag<false, false>(al, [&](int i, int j) { return s_aqk[i * LDA + j]; },
+                                  [&](int j, int c) { return s_un[j * LDP + c]; },
+                                  [&](int i, int c, float v) { s_dl[i * LDP + c] = v; });
+    }
+    {
+        const int c = threadIdx.x & (DP - 1), i0 = (threadIdx.x >> 7) * BT;
+        const float Gend = s_G[(i0 + BT - 1) * LDP + c];
+#pragma unroll
+        for (int k = 0; k < BT; ++k) s_un[(i0 + k) * LDP + c] *= __expf(Gend - s_G[(i0 + k) * LDP + c]);
+    }
+    cp_wait<0>();
     __syncthreads();
     SD_PHASE(p.g, ph);
     float acc[NT128][4];
@@ -249,53 +287,63 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
     warp_mma<NT128>(acc, r0, n0, 0, CL, [&](int i, int k) { return s_kh[i * LDP + k]; },
                 [&](int k, int n) { return s_st0[n * LDH + k]; });
-    warp_mma<NT128>(acc, r0, n0, 0, r0 + 16, [&](int i, int k) { return s_aqk[i * LDA + k]; },
-                [&](int k, int n) { return s_un[k * LDP + n]; });
-    cp_wait<0>();
-    __syncthreads();
-    SD_PHASE(p.g, ph);
     warp_mma<NT128>(acc, r0, n0, 0, CL, [&](int i, int k) { return s_kh[i * LDP + CL + k]; },
                 [&](int k, int n) { return s_st1[n * LDH + k]; });
+    for (int J = 0; J * BT < r0; ++J) {
+        scale_acc<NT128>(acc, s_beta + J * DP, n0);
+        warp_mma<NT128>(acc, r0, n0, J * BT, J * BT + BT, [&](int i, int k) { return s_aqk[i * LDA + k]; },
+                    [&](int k, int n) { return s_un[k * LDP + n]; });
+    }
+    SD_PHASE(p.g, ph);
     float* gd = panel_ptr(p.Dprim, ch.gi);
     warp_epi<NT128>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
         float2 kh = *reinterpret_cast<const float2*>(s_kh + i * LDP + j);
         float2 G = *reinterpret_cast<const float2*>(s_G + i * LDP + j);
+        float2 Gp = make_float2(0.f, 0.f);
+        if (r0) Gp = *reinterpret_cast<const float2*>(s_G + (r0 - 1) * LDP + j);
+        float2 dg = *reinterpret_cast<const float2*>(s_dl + i * LDP + j);
         *reinterpret_cast<float2*>(gd + i * DP + j) =
-            make_float2(kh.x + __expf(G.x) * v0, kh.y + __expf(G.y) * v1);
+            make_float2(kh.x + __expf(G.x - Gp.x) * v0 + dg.x, kh.y + __expf(G.y - Gp.y) * v1 + dg.y);
     });
     SD_PHASE(p.g, ph);
 }
 
 // ---------------------------------------------------------------------------
-// Exterior preparation: sources (e, chi, z), the pair matrices Aqd / Aed and
-// the solved panels Wd = (I-Aed)^-1 ag, Ud = (I-Aed)^-1 Z for the S scan.
-constexpr size_t EXT_PREP_FWD_SMEM = 4 * SLOT_BYTES + MAT_BYTES;
+// Exterior preparation: sources (e, chi, z), the pair matrices
+//   Aqd[i][j] = sum_c chi_ic d_jc exp(G_ic - G_jc) (j <= i),  Aed likewise with -e (j < i)
+// in block-centred form, and the solved panels Wd = (I-Aed)^-1 ag, Ud = (I-Aed)^-1 Z
+// for the S scan (ag = -e exp(G), referenced to the chunk start like the scan itself).
+constexpr size_t EXT_PREP_FWD_SMEM = 5 * SLOT_BYTES + MAT_BYTES + 3 * DP * sizeof(float);
 
 template <bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) float smem[];
-    float* s_xg = smem;
-    float* s_ag = s_xg + SLOT_FLOATS;
-    float* s_dn = s_ag + SLOT_FLOATS;
-    float* s_z = s_dn + SLOT_FLOATS;
+    float* s_xr = smem;                  // chi rowG   (block-centred row operand)
+    float* s_er = s_xr + SLOT_FLOATS;    // -e rowG
+    float* s_dc = s_er + SLOT_FLOATS;    // d col      (block-centred column operand)
+    float* s_ag = s_dc + SLOT_FLOATS;    // -e exp(G)  -> Wd
+    float* s_z = s_ag + SLOT_FLOATS;     // z          -> Ud
     float* s_aed = s_z + SLOT_FLOATS;
+    float* s_M = s_aed + MAT_FLOATS;
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r, V = p.g.V;
+    const float* gG = panel_ptr(p.Gp, ch.gi);
+    const float* gd = panel_ptr(p.Dprim, ch.gi);
+    bf16* gAqd = bmat_ptr(p.Aqd, ch.gi);
+    pair_block_scales(s_M, [&](int i, int c) { return gG[i * DP + c]; });
     {
-        const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
+        const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8, l16 = threadIdx.x & 15;
         const float* gDelta = panel_ptr(p.Delta, ch.gi);
-        const float* gd = panel_ptr(p.Dprim, ch.gi);
         float* gDt = panel_ptr(p.Dt, ch.gi);
         bf16* gXg = bpanel_ptr(p.Xg, ch.gi);
-        const float* gG = panel_ptr(p.Gp, ch.gi);
         float GL[8];
         load8_panel(gG, CL - 1, c0, GL);
 #pragma unroll 1
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
-            const int i = lr + ROWS_PER_PASS * pp;
-            float uh[8], kh[8], qh[8], dl[8], d[8], er[8], wr[8], v[8], G[8], se[8];
+            const int i = lr + ROWS_PER_PASS * pp, i0 = i & ~(BT - 1);
+            float uh[8], kh[8], qh[8], dl[8], d[8], er[8], wr[8], v[8], G[8], Gp[8], Ge[8], se[8];
             load8_norm<FAST>(p.u, ch, i, c0, r, uh);
             load8_norm<FAST>(p.k, ch, i, c0, r, kh);
             load8_norm<FAST>(p.q, ch, i, c0, r, qh);
@@ -305,47 +353,57 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
             load8_bf16<FAST>(row_bf16(p.wr, ch, i), c0, V, p.wr.vec, i < ch.nvalid, wr);
             load8_bf16<FAST>(row_bf16(p.v, ch, i), c0, V, p.v.vec, i < ch.nvalid, v);
             load8_panel(gG, i, c0, G);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) se[e] = sigmoidf_(er[e]);
-            Sources src;
-            sources_fwd(uh, kh, qh, dl, se, src);
-            float xg[8], ag[8], dn[8], z[8], dt[8];
+            load8_panel(gG, i0 + BT - 1, c0, Ge);
+            load8_panel(gG, i0 ? i0 - 1 : 0, c0, Gp);
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-                float ep = __expf(G[e]);
+                se[e] = sigmoidf_(er[e]);
+                if (i0 == 0) Gp[e] = 0.f;
+            }
+            Sources src;
+            sources_fwd(uh, kh, qh, dl, se, src);
+            float xg[8], ag[8], xr[8], ern[8], dc[8], z[8], dt[8];
+            float a[2][8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float ep = __expf(G[e]), rw = __expf(G[e] - Gp[e]);
                 xg[e] = src.chi[e] * ep;
                 ag[e] = -src.e[e] * ep;
-                dn[e] = d[e] * clamp_exp_neg(G[e]);
+                xr[e] = src.chi[e] * rw;
+                ern[e] = -src.e[e] * rw;
+                dc[e] = d[e] * __expf(Ge[e] - G[e]);
                 dt[e] = d[e] * __expf(GL[e] - G[e]);
                 z[e] = sigmoidf_(wr[e]) * v[e];
+                a[0][e] = src.chi[e];
+                a[1][e] = -src.e[e];
             }
-            store8_smem(s_xg, i, c0, xg);
+            store8_smem(s_xr, i, c0, xr);
+            store8_smem(s_er, i, c0, ern);
+            store8_smem(s_dc, i, c0, dc);
             store8_smem(s_ag, i, c0, ag);
-            store8_smem(s_dn, i, c0, dn);
             store8_smem(s_z, i, c0, z);
             store8_panel(gDt, i, c0, dt);
             store8_bpanel(gXg, i, c0, xg);
+            // diagonal blocks: exp(G_i - G_j) directly; both pairs share the exponentials
+            float out[2];
+            pair_diag_row<2, false>(i, a, G, [&](int j, float (&b)[8]) { load8_panel(gd, j, c0, b); },
+                                    [&](int j, float (&Gj)[8]) { load8_panel(gG, j, c0, Gj); }, out);
+            gAqd[i * CL + i0 + l16] = __float2bfloat16_rn(out[0]);
+            s_aed[i * LDA + i0 + l16] = (i0 + l16 < i) ? out[1] : 0.f;
         }
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
     {
-        float a1[NT64][4], a2[NT64][4];
-        acc_zero<NT64>(a1);
-        acc_zero<NT64>(a2);
-        const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
-        auto fb = [&](int k, int n) { return s_dn[n * LDP + k]; };
-        warp_mma<NT64>(a1, r0, n0, 0, DP, [&](int i, int k) { return s_xg[i * LDP + k]; }, fb);
-        warp_mma<NT64>(a2, r0, n0, 0, DP, [&](int i, int k) { return s_ag[i * LDP + k]; }, fb);
-        bf16* gAqd = bmat_ptr(p.Aqd, ch.gi);
-        warp_epi<NT64>(a1, r0, n0, [&](int i, int j, float v0, float v1) {
-            *reinterpret_cast<__nv_bfloat162*>(gAqd + i * CL + j) =
-                __floats2bfloat162_rn((j <= i) ? v0 : 0.f, (j + 1 <= i) ? v1 : 0.f);
-        });
-        warp_epi<NT64>(a2, r0, n0, [&](int i, int j, float v0, float v1) {
-            s_aed[i * LDA + j] = (j < i) ? v0 : 0.f;
-            s_aed[i * LDA + j + 1] = (j + 1 < i) ? v1 : 0.f;
-        });
+        auto fc = [&](int j, int k) { return s_dc[j * LDP + k]; };
+        pair_offdiag_tf32(s_M, [&](int i, int k) { return s_xr[i * LDP + k]; }, fc,
+                          [&](int i, int j, float v0, float v1) {
+                              *reinterpret_cast<__nv_bfloat162*>(gAqd + i * CL + j) = __floats2bfloat162_rn(v0, v1);
+                          });
+        pair_offdiag_tf32(s_M, [&](int i, int k) { return s_er[i * LDP + k]; }, fc,
+                          [&](int i, int j, float v0, float v1) {
+                              *reinterpret_cast<float2*>(s_aed + i * LDA + j) = make_float2(v0, v1);
+                          });
     }
     __syncthreads();
     SD_PHASE(p.g, ph);

@@ -13,13 +13,26 @@ Backward stages: ext_prep -> scan(dS) -> ext_main -> scan(dC) -> pred_main.
 All four scans share one recurrence:
   X = P + Q @ St ; checkpoint St ; St = lam * St + R^T X (+ R2^T X2).
 The predictor state is carried transposed, Ct[c, a] = C[a, c].
+
+Decay-weighted intra-chunk terms never form a reciprocal-retention factor
+exp(-G) (it overflows under strong forgetting).  A chunk is cut into blocks
+of BT = 16 tokens.  With Gprev / Gend the prefix at the start / end of a
+block, every factor used is bounded by one:
+  rowG_i = exp(G_i - Gprev_I), rowE_i = exp(E_i - Gprev_I)   (row side)
+  col_j  = exp(Gend_J - G_j)                                  (column side)
+  beta_J = exp(Gend_J - Gprev_J)                              (whole block)
+Off-diagonal block pairs (I > J) are contractions of row- and column-centred
+panels with the product of the betas strictly between them; the diagonal
+blocks evaluate exp(x_i - G_j) <= 1 directly.  `pair`, `csum` and `asum`
+below are the three forms the kernels use (same block order, same Horner
+accumulation over blocks).
 """
 from __future__ import annotations
 
 import torch
 
 RHO = 5.0 / 8.0
-EXP_CLAMP = 80.0
+BT = 16  # tokens per decay block
 
 
 def _round_operand(x, mode):
@@ -118,18 +131,102 @@ class Model:
         loc["GL"] = G[:, :, -1:, :]
         loc["lam"] = torch.exp(loc["GL"]).squeeze(2)  # [S,NC,r]
         loc["epos"] = torch.exp(G)
-        loc["eneg"] = torch.exp(torch.clamp(-G, max=EXP_CLAMP))
         loc["eE"] = torch.exp(loc["E"])
         loc["etail"] = torch.exp(loc["GL"] - G)
         loc["Ut"] = loc["uh"] * loc["eE"]          # U-tilde
-        loc["Uneg"] = loc["uh"] * loc["eneg"]
         loc["Ubar"] = loc["uh"] * loc["etail"]
         tri = torch.ones(L, L, dtype=dt)
         loc["stril"] = torch.tril(tri, -1)
         loc["tril"] = torch.tril(tri)
-        loc["N"] = self.mm(loc["Ut"], loc["Uneg"].transpose(-1, -2)) * loc["stril"]
+        # block-centred decay factors
+        bt = min(BT, L)
+        nb = L // bt
+        loc["bt"], loc["nb"] = bt, nb
+        Gb = G.reshape(G.shape[0], NC, nb, bt, -1)
+        gend = Gb[:, :, :, -1:, :]                                    # [S,NC,nb,1,r]
+        gprev = torch.cat([torch.zeros_like(gend[:, :, :1]), gend[:, :, :-1]], dim=2)
+        flat = lambda x: x.expand(-1, -1, -1, bt, -1).reshape(G.shape)
+        loc["rowG"] = torch.exp(G - flat(gprev))
+        loc["rowE"] = torch.exp(loc["E"] - flat(gprev))
+        loc["col"] = torch.exp(flat(gend) - G)
+        loc["beta"] = torch.exp(gend - gprev).squeeze(3)              # [S,NC,nb,r]
+        loc["N"] = self.pair(loc, loc["uh"], loc["uh"], xe=True, strict=True)
         loc["Lm"] = gam * loc["N"]
         return loc
+
+    # ---- block-centred decay contractions ---------------------------------
+    def _blk(self, loc, x, I):
+        bt = loc["bt"]
+        return x[:, :, I * bt:(I + 1) * bt]
+
+    def _rho(self, loc, I, xe):
+        """exp(x_i - G_j) <= 1 for i, j inside block I (entries above the diagonal are unused)."""
+        G = self._blk(loc, loc["G"], I)
+        x = self._blk(loc, loc["E"] if xe else loc["G"], I)
+        return torch.exp(torch.clamp(x.unsqueeze(3) - G.unsqueeze(2), max=0.0))  # [S,NC,i,j,c]
+
+    def pair(self, loc, a, b, xe, strict):
+        """[L,L]: sum_c a[i,c] b[j,c] exp(x[i,c] - G[j,c]) for j <= i (j < i if strict)."""
+        nb, bt = loc["nb"], loc["bt"]
+        R = a * (loc["rowE"] if xe else loc["rowG"])
+        Cc = b * loc["col"]
+        out = torch.zeros(a.shape[0], a.shape[1], self.L, self.L, dtype=a.dtype)
+        mask = torch.tril(torch.ones(bt, bt, dtype=a.dtype), -1 if strict else 0)
+        for I in range(nb):
+            for J in range(I):
+                M = torch.ones_like(loc["beta"][:, :, 0])
+                for K in range(J + 1, I):
+                    M = M * loc["beta"][:, :, K]
+                blk = self.mm(self._blk(loc, R, I) * M.unsqueeze(2), self._blk(loc, Cc, J).transpose(-1, -2))
+                out[:, :, I * bt:(I + 1) * bt, J * bt:(J + 1) * bt] = blk
+            rho = self._rho(loc, I, xe)
+            diag = torch.einsum("snic,snjc,snijc->snij", self._blk(loc, a, I), self._blk(loc, b, I), rho)
+            out[:, :, I * bt:(I + 1) * bt, I * bt:(I + 1) * bt] = diag * mask
+        return out
+
+    def csum(self, loc, P, b, xe, strict, state=None):
+        """[L,r]: sum_{j<=i} P[i,j] b[j,c] exp(x[i,c] - G[j,c]) (+ exp(x[i,c]) state[i,c]).
+        Blocks below the diagonal accumulate Horner-style from the chunk start."""
+        nb, bt = loc["nb"], loc["bt"]
+        Cc = b * loc["col"]
+        rowf = loc["rowE"] if xe else loc["rowG"]
+        mask = torch.tril(torch.ones(bt, bt, dtype=P.dtype), -1 if strict else 0)
+        outs = []
+        for I in range(nb):
+            PI = self._blk(loc, P, I)
+            acc = self._blk(loc, state, I) if state is not None else None
+            for J in range(I):
+                if acc is not None:
+                    acc = acc * loc["beta"][:, :, J].unsqueeze(2)
+                term = self.mm(PI[..., J * bt:(J + 1) * bt], self._blk(loc, Cc, J))
+                acc = term if acc is None else acc + term
+            rho = self._rho(loc, I, xe)
+            diag = torch.einsum("snij,snjc,snijc->snic", PI[..., I * bt:(I + 1) * bt] * mask,
+                                self._blk(loc, b, I), rho)
+            res = diag if acc is None else self._blk(loc, rowf, I) * acc + diag
+            outs.append(res)
+        return torch.cat(outs, dim=2)
+
+    def asum(self, loc, P, a, xe, strict):
+        """[L,r]: out[j,c] = sum_{i>=j} P[i,j] a[i,c] exp(x[i,c] - G[j,c]); Horner from the chunk end."""
+        nb, bt = loc["nb"], loc["bt"]
+        R = a * (loc["rowE"] if xe else loc["rowG"])
+        mask = torch.tril(torch.ones(bt, bt, dtype=P.dtype), -1 if strict else 0)
+        outs = []
+        for J in range(nb):
+            acc = None
+            for I in range(nb - 1, J, -1):
+                if acc is not None:
+                    acc = acc * loc["beta"][:, :, I].unsqueeze(2)
+                PIJ = self._blk(loc, P, I)[..., J * bt:(J + 1) * bt]
+                term = self.mm(PIJ.transpose(-1, -2), self._blk(loc, R, I))
+                acc = term if acc is None else acc + term
+            rho = self._rho(loc, J, xe)
+            PJJ = self._blk(loc, P, J)[..., J * bt:(J + 1) * bt] * mask
+            diag = torch.einsum("snij,snic,snijc->snjc", PJJ, self._blk(loc, a, J), rho)
+            res = diag if acc is None else self._blk(loc, loc["col"], J) * acc + diag
+            outs.append(res)
+        return torch.cat(outs, dim=2)
 
     def _sources(self, loc, Delta):
         """Per-token frame covector, dual address e and query chi."""
@@ -149,10 +246,9 @@ class Model:
         out = {}
         out["Xg"] = src["chi"] * loc["epos"]
         out["ag"] = -src["e"] * loc["epos"]
-        out["Dneg"] = d * loc["eneg"]
         out["Dt"] = d * loc["etail"]
-        out["Aqd"] = self.mm(out["Xg"], out["Dneg"].transpose(-1, -2)) * loc["tril"]
-        out["Aed"] = self.mm(out["ag"], out["Dneg"].transpose(-1, -2)) * loc["stril"]
+        out["Aqd"] = self.pair(loc, src["chi"], d, xe=False, strict=False)
+        out["Aed"] = self.pair(loc, -src["e"], d, xe=False, strict=True)
         return out
 
     # ---- forward --------------------------------------------------------
@@ -173,10 +269,9 @@ class Model:
         Ct0 = torch.zeros(S_, r, r, dtype=dt) if C0 is None else C0.to(dt).reshape(S_, r, r).transpose(-1, -2)
         Delta, Ct_ck, Ct_fin = self._scan(Upd, -W, loc["Ubar"], loc["lam"], Ct0)
         # mid
-        act1 = self.mm(loc["kh"], Ct_ck.transpose(-1, -2)) * loc["epos"]
         Aqk = self.mm(loc["kh"], Delta.transpose(-1, -2)) * loc["tril"]
-        act2 = loc["epos"] * self.mm(Aqk, loc["Uneg"])
-        d = loc["kh"] + act1 + act2
+        d = loc["kh"] + self.csum(loc, Aqk, loc["uh"], xe=False, strict=False,
+                                  state=self.mm(loc["kh"], Ct_ck.transpose(-1, -2)))
         src = self._sources(loc, Delta)
         ext = self._exterior_locals(loc, d, src)
         rhs = torch.cat([ext["ag"], loc["z"]], dim=-1)
@@ -225,13 +320,12 @@ class Model:
         dXg = self.mm(dyc, S_ck.transpose(-1, -2))
         dag = self.mm(dR, S_ck.transpose(-1, -2))
         dDt = self.mm(Zt, dSe.transpose(-1, -2))
-        PX1 = self.mm(dAqd, ext["Dneg"])
-        PX2 = self.mm(dAed, ext["Dneg"])
-        dchi = loc["epos"] * (PX1 + dXg)
-        de = -loc["epos"] * (PX2 + dag)
-        PY = self.mm(dAqd.transpose(-1, -2), ext["Xg"]) + self.mm(dAed.transpose(-1, -2), ext["ag"])
-        dd = loc["eneg"] * PY + dDt * loc["etail"]
-        dG = src["chi"] * dchi + src["e"] * de - ext["Dneg"] * PY
+        dchi = self.csum(loc, dAqd, d, xe=False, strict=False, state=dXg)
+        de = -self.csum(loc, dAed, d, xe=False, strict=True, state=dag)
+        ddp = self.asum(loc, dAqd, src["chi"], xe=False, strict=False) + \
+            self.asum(loc, dAed, -src["e"], xe=False, strict=True)
+        dd = ddp + dDt * loc["etail"]
+        dG = src["chi"] * dchi + src["e"] * de - d * ddp
         dGL = loc["lam"] * (S_ck * dSe).sum(-1) + (dDt * ext["Dt"]).sum(2)  # [S,NC,r]
         # sources backward
         phi, den, sb, sq, b = src["phi"], src["den"], src["sb"], src["sq"], src["b"]
@@ -261,10 +355,9 @@ class Model:
         dkh = dkh + dd
         DG = dact * loc["epos"]
         dkh = dkh + self.mm(DG, Ct_ck)
-        dAqk = self.mm(DG, loc["Uneg"].transpose(-1, -2)) * loc["tril"]
+        dAqk = self.pair(loc, dact, uh, xe=False, strict=False)
         Aqk = self.mm(kh, Delta.transpose(-1, -2)) * loc["tril"]
-        Tpre = self.mm(Aqk.transpose(-1, -2), DG)
-        t_u = loc["eneg"] * Tpre
+        t_u = self.asum(loc, Aqk, dact, xe=False, strict=False)
         duh = duh + t_u
         dG = dG + dact * (d - kh) - uh * t_u
         dkh = dkh + self.mm(dAqk, Delta)
@@ -289,10 +382,8 @@ class Model:
         duh = duh + dUt * loc["eE"]
         dE = dUt * loc["Ut"]
         dN = gam * dLm
-        Ti = self.mm(dN, loc["Uneg"])
-        Tj = self.mm(dN.transpose(-1, -2), loc["Ut"])
-        t_i = loc["eE"] * Ti
-        t_j = loc["eneg"] * Tj
+        t_i = self.csum(loc, dN, uh, xe=True, strict=True)
+        t_j = self.asum(loc, dN, uh, xe=True, strict=True)
         duh = duh + t_i + t_j
         dE = dE + uh * t_i
         dG = dG - uh * t_j
@@ -318,10 +409,10 @@ class Model:
             C0=dCt0.transpose(-1, -2).reshape(B, H, r, r),
             S0=dS0.reshape(B, H, r, V),
         )
-        panels = dict(Pp=Pp, Qp=Qp, Ag=ext["ag"], Xg=ext["Xg"], Dyf=dyc, Dneg=ext["Dneg"], dR=dR,
-                      dSeCk=dSe, A1=PX1 + dXg, A2=PX2 + dag, PY=PY, dDt=dDt,
+        panels = dict(Pp=Pp, Qp=Qp, Ag=ext["ag"], Xg=ext["Xg"], Dyf=dyc, dR=dR,
+                      dSeCk=dSe, dDt=dDt, Chi=src["chi"], Ee=-src["e"],
                       SdS=(S_ck * dSe).sum(-1), duPart=duPart, dkPart=dkPart, dGPart=dGPart,
-                      dDelta=dDeltaSrc, DG=DG, Xext=Xext, Tpre=Tpre, Khat=kh, Ppp=Ppp, Qpp=Qpp,
-                      Rneg=-gam * loc["Ut"], dRr=dRr, dCeCk=dCe, dUbar=dUbar, dUt=dUt, Ti=Ti,
-                      Tj=Tj, CdC=(Ct_ck * dCe).sum(-1))
+                      dDelta=dDeltaSrc, DG=DG, Dd=dact, Xext=Xext, Tu=t_u, Khat=kh, Ppp=Ppp, Qpp=Qpp,
+                      Rneg=-gam * loc["Ut"], dRr=dRr, dCeCk=dCe, dUbar=dUbar, dUt=dUt,
+                      CdC=(Ct_ck * dCe).sum(-1))
         return grads, panels

@@ -51,3 +51,38 @@ def test_chunk_forward_and_vjp_equal_token_recurrence(name, chunk):
         expect["C0"], expect["S0"] = ref["C0"], ref["S0"]
     for key, val in expect.items():
         assert rel_l2(grads[key].numpy(), val) < 1e-9, key
+
+
+@pytest.mark.parametrize("scale", [0.4, 3.0, 16.0])
+def test_chunk_algebra_is_exact_under_strong_forgetting(scale):
+    """Per-token log decays down to -16 (upstream tests/core/test_rebuild_semantics.py:411
+    runs its exterior owner at decay_scale 16): the chunk prefix reaches -1000, far past
+    what a reciprocal-retention factor could hold.  Per-channel rates span four decades."""
+    rng = np.random.default_rng(int(scale * 10))
+    B, T, H, r, V = 1, 150, 2, 16, 16
+    rate = scale * np.exp(rng.uniform(np.log(1e-3), 0.0, size=(1, 1, H, r)))
+    g = -rate * (0.75 + 0.25 * rng.random((B, T, H, r)))
+    u, h, q, k = (rng.standard_normal((B, T, H, r)) for _ in range(4))
+    v = rng.standard_normal((B, T, H, V))
+    er, wr = rng.standard_normal((B, T, H, r)), rng.standard_normal((B, T, H, V))
+    gam = 1 / (1 + np.exp(-(rng.standard_normal((B, T, H)) + 1.0)))
+    C0, S0 = 0.2 * rng.standard_normal((B, H, r, r)), 0.5 * rng.standard_normal((B, H, r, V))
+    dy, dC, dS = rng.standard_normal((B, T, H, V)), rng.standard_normal(C0.shape), rng.standard_normal(S0.shape)
+    sig = lambda x: 1 / (1 + np.exp(-x))
+    args = (u, h, q, k, v, g, sig(er), sig(wr), gam)
+    yo, so = orc.forward(*args, initial_state=(C0, S0))
+    ref = orc.backward(*args, dy, dC_T=dC, dS_T=dS, initial_state=(C0, S0))
+    t = torch.from_numpy
+    inp = dict(u=t(u), h=t(h), q=t(q), k=t(k), v=t(v), g=t(g), erase_raw=t(er), write_raw=t(wr), gamma=t(gam))
+    model = Model(chunk=64)
+    y, C_T, S_T, saved = model.forward(inp, t(C0), t(S0))
+    assert rel_l2(y.numpy(), yo) < 1e-9
+    assert rel_l2(C_T.numpy(), so.predictor) < 1e-9
+    assert rel_l2(S_T.numpy(), so.S) < 1e-9
+    grads, _ = model.backward(inp, saved, t(dy), t(dC), t(dS))
+    expect = dict(u=ref["u"], h=ref["h"], q=ref["q"], k=ref["keys"], v=ref["values"], g=ref["log_decay"],
+                  erase_raw=ref["erase"] * sig(er) * (1 - sig(er)), write_raw=ref["write"] * sig(wr) * (1 - sig(wr)),
+                  gamma=ref["geometry_write"], C0=ref["C0"], S0=ref["S0"])
+    for key, val in expect.items():
+        assert np.isfinite(grads[key].numpy()).all(), key
+        assert rel_l2(grads[key].numpy(), val) < 1e-8, key

@@ -11,8 +11,8 @@ from tests.helpers import rel_l2
 
 SAVED = ("Lam", "G", "Delta", "Dprim", "Zt", "CtCk", "SCk")
 FWD = ("Upd", "Qc", "Ubar", "Wd", "Ud", "Dt", "Xg", "Aqd")
-BWD = ("Pp", "Qp", "Ag", "Xg", "Dyf", "Dneg", "dR", "dSeCk", "SdS",
-       "duPart", "dkPart", "dGPart", "DG", "Xext", "Tpre", "Khat", "dDelta", "Ppp", "Qpp", "Rneg",
+BWD = ("Pp", "Qp", "Ag", "Xg", "Dyf", "Chi", "Ee", "dR", "dSeCk", "SdS",
+       "duPart", "dkPart", "dGPart", "DG", "Dd", "Xext", "Tu", "Khat", "dDelta", "Ppp", "Qpp", "Rneg",
        "dRr", "dCeCk")
 
 

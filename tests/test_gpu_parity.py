@@ -229,6 +229,37 @@ def test_extreme_forgetting_remains_finite():
         assert torch.isfinite(g).all()
 
 
+def _strong_decay_inputs(B, T, H, r, V, scale, seed):
+    """Per-channel decay rates spread over four decades up to `scale` nats per token
+    (upstream runs its exterior owner at decay_scale 16, tests/core/test_rebuild_semantics.py:411)."""
+    cpu, dev = make_inputs(B, T, H, r, V, seed=seed, gamma_max=0.9)
+    gen = torch.Generator().manual_seed(seed + 1)
+    rate = scale * torch.exp(torch.rand(1, 1, H, r, generator=gen) * np.log(1e-4))
+    cpu["log_decay"] = -rate * (0.75 + 0.25 * torch.rand(B, T, H, r, generator=gen))
+    cpu["C0"], cpu["S0"] = 10 * cpu["C0"], 10 * cpu["S0"]
+    for n in ("log_decay", "C0", "S0"):
+        dev[n] = cpu[n].cuda()
+    return cpu, dev
+
+
+@pytest.mark.parametrize("scale", [1.5, 16.0])
+@pytest.mark.parametrize("T,H,r,V", [(150, 2, 16, 16), (200, 1, 128, 128)])
+def test_strong_forgetting_forward_matches_checker(scale, T, H, r, V):
+    # chunk prefixes reach -1000: exact only without reciprocal-retention factors
+    cpu, dev = _strong_decay_inputs(1, T, H, r, V, scale, seed=41)
+    leaves, state, y, fin = _native(dev, grad=False)
+    _check_forward(cpu, y, fin)
+
+
+@pytest.mark.parametrize("scale", [1.5, 16.0])
+@pytest.mark.parametrize("T,H,r,V", [(150, 2, 16, 16), (200, 1, 128, 128)])
+def test_strong_forgetting_full_vjp_matches_checker(scale, T, H, r, V):
+    cpu, dev = _strong_decay_inputs(1, T, H, r, V, scale, seed=43)
+    leaves, state, y, fin = _native(dev, grad=True)
+    _check_forward(cpu, y, fin)
+    _check_vjp(cpu, leaves, state, y, fin)
+
+
 def test_return_final_state_false_and_none_cotangents():
     cpu, dev = make_inputs(1, 70, 1, 16, 16, seed=25)
     leaves, state, y, fin = _native(dev, grad=True, return_final_state=False)
