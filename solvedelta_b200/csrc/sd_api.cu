@@ -22,8 +22,9 @@ struct PanelDesc {
     int kind;
 };
 
-const PanelDesc kSaved[] = {{"Lam", 3}, {"G", 0}, {"Delta", 0}, {"Dprim", 0}, {"Zt", 4}, {"CtCk", 2}, {"CtCkB", 6}, {"SCk", 6}};
-const PanelDesc kFwd[] = {{"Upd", 0}, {"Qc", 0}, {"Ubar", 0}, {"Wd", 0}, {"Ud", 0}, {"Dt", 0}, {"Xg", 4}, {"Aqd", 5}};
+const PanelDesc kSaved[] = {{"Lam", 3}, {"G", 0}, {"Delta", 0}, {"Dprim", 0}, {"Zt", 4}, {"CtCk", 2}, {"CtCkB", 6}, {"SCk", 6},
+                            {"N", 1}, {"Aed", 1}, {"Aqd", 5}};
+const PanelDesc kFwd[] = {{"Upd", 0}, {"Qc", 0}, {"Ubar", 0}, {"Wd", 0}, {"Ud", 0}, {"Dt", 0}, {"Xg", 4}};
 const PanelDesc kBwd[] = {{"Pp", 4},     {"Qp", 4},     {"Ag", 4},     {"Xg", 4},     {"Dyf", 4},    {"Dcol", 4},
                           {"Xr", 4},     {"Er", 4},     {"Chi", 4},    {"Ee", 4},     {"dR", 4},     {"dSeCk", 6},
                           {"SdS", 3},    {"duPart", 4}, {"dkPart", 4}, {"dGPart", 4}, {"dDelta", 4}, {"DG", 4},
@@ -277,7 +278,9 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
     p.Ud = panel_at(kFwd, s, a->scratch, "Ud");
     p.Dt = panel_at(kFwd, s, a->scratch, "Dt");
     p.Xg = bpanel_at(kFwd, s, a->scratch, "Xg");
-    p.Aqd = bpanel_at(kFwd, s, a->scratch, "Aqd");
+    p.Aqd = bpanel_at(kSaved, s, a->saved, "Aqd");
+    p.Npair = panel_at(kSaved, s, a->saved, "N");
+    p.Aed = panel_at(kSaved, s, a->saved, "Aed");
     p.Lam = panel_at(kSaved, s, a->saved, "Lam");
     p.Gp = panel_at(kSaved, s, a->saved, "G");
     p.Delta = panel_at(kSaved, s, a->saved, "Delta");
@@ -369,6 +372,9 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
     p.CtCk = panel_at(kSaved, s, sv, "CtCk");
     p.CtCkB = bpanel_at(kSaved, s, sv, "CtCkB");
     p.SCk = bpanel_at(kSaved, s, sv, "SCk");
+    p.Npair = panel_at(kSaved, s, sv, "N");
+    p.Aed = panel_at(kSaved, s, sv, "Aed");
+    p.Aqd = bpanel_at(kSaved, s, sv, "Aqd");
 #define SD_BP(field) p.field = panel_at(kBwd, s, a->scratch, #field)
 #define SD_BB(field) p.field = bpanel_at(kBwd, s, a->scratch, #field)
     SD_BB(Pp); SD_BB(Qp); SD_BB(Ag); SD_BB(Xg); SD_BB(Dyf); SD_BB(Dcol); SD_BB(dR); SD_BB(dSeCk);

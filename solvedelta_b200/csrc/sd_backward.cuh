@@ -20,7 +20,8 @@ struct BwdParams {
     Operand u, h, q, k, v, er, wr, ld, gam, dy;
     // kept by forward (FP32)
     const float *Lam, *Gp, *Delta, *Dprim, *CtCk;
-    const bf16 *Zt, *SCk, *CtCkB;
+    const float *Npair, *Aed;   // pair matrices N and Aed of the forward pass, [CL][CL]
+    const bf16 *Zt, *SCk, *CtCkB, *Aqd;
     // backward scratch: BF16 contraction operands / scanned panels
     bf16 *Pp, *Qp, *Ag, *Xg, *Dyf, *dR, *dSeCk;
     bf16 *Xr, *Er, *Dcol;   // block-centred chi rowG, -e rowG, d col (operands of the centred contractions)
@@ -91,6 +92,21 @@ __device__ __forceinline__ const bf16* bstate_ptr(const bf16* base, long long gi
     return base + gi * (long long)(DP * DP);
 }
 
+// Mr[j][i] = scale(i) * M[i][j] for a dense FP32 [CL][CL] matrix in global memory
+// (a strictly lower M arrives as the "rows of the transposed system" the solves expect).
+template <class FS>
+__device__ __forceinline__ void g2s_mat_transposed(float* Mr, const float* M, FS scale) {
+    for (int idx = threadIdx.x; idx < CL * (CL / 4); idx += NTHREADS) {
+        const int j4 = (idx >> 6) << 2, i = idx & (CL - 1);   // consecutive threads: consecutive i (conflict-free stores)
+        const float4 v = *reinterpret_cast<const float4*>(M + i * CL + j4);
+        const float sc = scale(i);
+        Mr[(j4 + 0) * LDA + i] = sc * v.x;
+        Mr[(j4 + 1) * LDA + i] = sc * v.y;
+        Mr[(j4 + 2) * LDA + i] = sc * v.z;
+        Mr[(j4 + 3) * LDA + i] = sc * v.w;
+    }
+}
+
 template <int NTW>
 __device__ __forceinline__ void epi_store_bsm(float (&acc)[NTW][4], int r0, int n0, bf16* spanel) {
     warp_epi<NTW>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
@@ -106,32 +122,30 @@ __device__ __forceinline__ void epi_store_bpanel(float (&acc)[NTW][4], int r0, i
 }
 
 // ---------------------------------------------------------------------------
-// Recompute chi, e, Aqd, Aed (block-centred, like the forward pass); solve the transposed system for
+// Recompute chi and e; with Aqd and Aed of the forward pass solve the transposed system for
 //   P' = (I-Aed)^-T (Aqd^T dy),  Q' = (I-Aed)^-T Dt
-// so that the reverse S scan is dR = P' + Q' dS.  Leaves the centred panels the
-// next kernel contracts with, and chi / -e for its diagonal blocks.
-constexpr size_t EXT_PREP_BWD_SMEM = 5 * BSLOT_BYTES + BMAT_BYTES + MAT_BYTES + 3 * DP * sizeof(bf16);
+// so that the reverse S scan is dR = P' + Q' dS.  Leaves the block-centred panels the
+// next kernel contracts with, and chi / -e themselves for its diagonal blocks.
+constexpr size_t EXT_PREP_BWD_SMEM = 2 * BSLOT_BYTES + BMAT_BYTES + MAT_BYTES;
 
 template <bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* b_xr = reinterpret_cast<bf16*>(smem_raw);
-    bf16* b_er = b_xr + BSLOT_ELEMS;
-    bf16* b_dc = b_er + BSLOT_ELEMS;
-    bf16* b_dy = b_dc + BSLOT_ELEMS;
+    bf16* b_dy = reinterpret_cast<bf16*>(smem_raw);
     bf16* b_dt = b_dy + BSLOT_ELEMS;
     bf16* b_aqd = b_dt + BSLOT_ELEMS;
     float* f_aedT = reinterpret_cast<float*>(b_aqd + BMAT_ELEMS);
-    bf16* s_Mb = reinterpret_cast<bf16*>(f_aedT + MAT_FLOATS);
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r, V = p.g.V;
     const float* gG = panel_ptr(p.Gp, ch.gi);
     const float* gd = panel_ptr(p.Dprim, ch.gi);
-    pair_block_scales_bf16(s_Mb, [&](int i, int c) { return gG[i * DP + c]; });
+    async_bmat(b_aqd, bmat_ptr(p.Aqd, ch.gi));
+    cp_commit();
+    g2s_mat_transposed(f_aedT, mat_ptr(p.Aed, ch.gi), [](int) { return 1.f; });
     {
-        const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8, l16 = threadIdx.x & 15;
+        const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
         const float* gDelta = panel_ptr(p.Delta, ch.gi);
         bf16* gAg = bpanel_ptr(p.Ag, ch.gi);
         bf16* gXg = bpanel_ptr(p.Xg, ch.gi);
@@ -164,13 +178,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) 
             }
             Sources src;
             sources_fwd(uh, kh, qh, dl, se, src);
-            float xg[8], ag[8], xr[8], ern[8], dc[8], dt[8];
-            float a[2][8];
+            float xg[8], ag[8], xr[8], ern[8], dc[8], dt[8], chi[8], ee[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const float ep = __expf(G[e]), rw = __expf(G[e] - Gp[e]);
-                a[0][e] = src.chi[e];
-                a[1][e] = -src.e[e];
+                chi[e] = src.chi[e];
+                ee[e] = -src.e[e];
                 xg[e] = src.chi[e] * ep;
                 ag[e] = -src.e[e] * ep;
                 xr[e] = src.chi[e] * rw;
@@ -178,9 +191,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) 
                 dc[e] = d[e] * __expf(Ge[e] - G[e]);
                 dt[e] = d[e] * __expf(GL[e] - G[e]);
             }
-            store8_bsm(b_xr, i, c0, xr);
-            store8_bsm(b_er, i, c0, ern);
-            store8_bsm(b_dc, i, c0, dc);
             store8_bsm(b_dy, i, c0, dy);
             store8_bsm(b_dt, i, c0, dt);
             store8_bpanel(gAg, i, c0, ag);
@@ -189,24 +199,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) 
             store8_bpanel(gXr, i, c0, xr);
             store8_bpanel(gEr, i, c0, ern);
             store8_bpanel(gDc, i, c0, dc);
-            store8_bpanel(gChi, i, c0, a[0]);
-            store8_bpanel(gEe, i, c0, a[1]);
-            float out[2];
-            pair_diag_row<2, false>(i, a, G, [&](int j, float (&b)[8]) { load8_panel(gd, j, c0, b); },
-                                    [&](int j, float (&Gj)[8]) { load8_panel(gG, j, c0, Gj); }, out);
-            b_aqd[i * LDM + i0 + l16] = __float2bfloat16_rn(out[0]);
-            f_aedT[(i0 + l16) * LDA + i] = (i0 + l16 < i) ? out[1] : 0.f;
+            store8_bpanel(gChi, i, c0, chi);
+            store8_bpanel(gEe, i, c0, ee);
         }
     }
-    __syncthreads();
-    SD_PHASE(p.g, ph);
-    pair_offdiag_bf16(s_Mb, b_xr, b_dc, [&](int i, int j, float v0, float v1) {
-        *reinterpret_cast<__nv_bfloat162*>(b_aqd + i * LDM + j) = __floats2bfloat162_rn(v0, v1);
-    });
-    pair_offdiag_bf16(s_Mb, b_er, b_dc, [&](int i, int j, float v0, float v1) {
-        f_aedT[j * LDA + i] = v0;
-        f_aedT[(j + 1) * LDA + i] = v1;
-    });
+    cp_wait<0>();
     __syncthreads();
     SD_PHASE(p.g, ph);
     {
@@ -493,14 +490,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
             };
         };
         auto fd = [&](int j, int c) { return gd[j * DP + c]; };
-        causal_diag<false, false>(al, [&](int i, int j) { return __bfloat162float(b_daqd[i * LDM + j]); }, fd,
-                                  add_to(b_dy));
-        causal_diag<false, true>(al, [&](int i, int j) { return __bfloat162float(b_daed[i * LDM + j]); }, fd,
-                                 add_to(b_dc));
-        anti_diag<false, false>(al, [&](int i, int j) { return __bfloat162float(b_daqd[i * LDM + j]); },
-                                [&](int i, int c) { return __bfloat162float(gChi[i * DP + c]); }, add_to(b_xr));
-        anti_diag<false, true>(al, [&](int i, int j) { return __bfloat162float(b_daed[i * LDM + j]); },
-                               [&](int i, int c) { return __bfloat162float(gEe[i * DP + c]); }, add_to(b_xr));
+        diag_sweep<false, false, true, true>(
+            al, [&](int i, int i0, float (&row)[BT]) { prow16_bf16(b_daqd, LDM, i, i0, row); }, fd,
+            [&](int i, int c) { return __bfloat162float(gChi[i * DP + c]); }, add_to(b_dy), add_to(b_xr));
+        diag_sweep<false, true, true, true>(
+            al, [&](int i, int i0, float (&row)[BT]) { prow16_bf16(b_daed, LDM, i, i0, row); }, fd,
+            [&](int i, int c) { return __bfloat162float(gEe[i * DP + c]); }, add_to(b_dc), add_to(b_xr));
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
@@ -516,8 +511,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
 //   dDelta_loc = dDelta_src + dAqk^T K^
 //   t_u[j] = sum_{i>=j} Aqk_ij dd_i exp(G_i - G_j)                      (-> d u^, d log decay)
 //   P'' = (I+Lm)^-T dDelta_loc,  Q'' = (I+Lm)^-T Ubar,  Rneg = -gamma U~.
-// dAqk, the recomputed Lm and t_u are block-centred (tensor cores off the
-// diagonal blocks, direct evaluation on them).
+// dAqk and t_u are block-centred (tensor cores off the diagonal blocks, direct
+// evaluation on them); Lm = gamma N comes from the pair matrix the forward pass kept.
 constexpr size_t PRIMAL_BWD_SMEM = 7 * BSLOT_BYTES + BSTATE_BYTES + 2 * BMAT_BYTES + MAT_BYTES +
                                    (3 * CL + 4 * CL + NBLK * DP) * sizeof(float) + 3 * DP * sizeof(bf16);
 
@@ -606,6 +601,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     cp_wait<0>();
     __syncthreads();
     SD_PHASE(p.g, ph);
+    // Lm^T = (gamma N)^T from the pair matrix the forward pass kept (read by the solve at the end)
+    g2s_mat_transposed(f_lmT, mat_ptr(p.Npair, ch.gi), [&](int i) { return s_gam[i]; });
     {
         const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
         float a1[NT64][4];
@@ -618,13 +615,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
         pair_offdiag_bf16(s_Mb, b_ddr, b_uc, [&](int i, int j, float v0, float v1) {
             *reinterpret_cast<__nv_bfloat162*>(b_daqk + i * LDM + j) = __floats2bfloat162_rn(v0, v1);
         });
-        pair_offdiag_bf16(s_Mb, b_ur, b_uc, [&](int i, int j, float v0, float v1) {
-            float gm = s_gam[i];
-            f_lmT[j * LDA + i] = gm * v0;
-            f_lmT[(j + 1) * LDA + i] = gm * v1;
-        });
     }
-    {   // diagonal blocks of dAqk and Lm
+    {   // diagonal blocks of dAqk
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8, l16 = threadIdx.x & 15;
         auto fu8 = [&](int j, float (&b)[8]) {
             load8_bf16<FAST>(row_bf16(p.u, ch, j), c0, r, p.u.vec, j < ch.nvalid, b);
@@ -636,14 +628,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
 #pragma unroll 1
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
             const int i = lr + ROWS_PER_PASS * pp, i0 = i & ~(BT - 1);
-            float a[1][8], G[8], E[8], out[1];
+            float a[1][8], G[8], out[1];
             load8_panel(gG, i, c0, G);
-            load8_panel(gG, i > 0 ? i - 1 : 0, c0, E);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) E[e] = i > 0 ? E[e] : 0.f;
-            fu8(i, a[0]);
-            pair_diag_row<1, true>(i, a, E, fu8, fg8, out);
-            f_lmT[(i0 + l16) * LDA + i] = s_gam[i] * out[0];
             load8_bpanel(gDd, i, c0, a[0]);
             pair_diag_row<1, false>(i, a, G, fu8, fg8, out);
             b_daqk[i * LDM + i0 + l16] = __float2bfloat16_rn(out[0]);
@@ -734,11 +720,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
         bf16* gTu = bpanel_ptr(p.Tu, ch.gi);
         float al[BT];
         block_alphas(al, fG);
-        anti_diag<false, false>(al, [&](int i, int j) { return __bfloat162float(b_aqk[i * LDM + j]); },
-                                [&](int i, int c) { return __bfloat162float(gDd[i * DP + c]); },
-                                [&](int j, int c, float v) {
-                                    gTu[j * DP + c] = __float2bfloat16_rn(__bfloat162float(b_ur[j * LDB + c]) + v);
-                                });
+        auto none = [](int, int) { return 0.f; };
+        auto sink = [](int, int, float) {};
+        diag_sweep<false, false, false, true>(
+            al, [&](int i, int i0, float (&row)[BT]) { prow16_bf16(b_aqk, LDM, i, i0, row); }, none,
+            [&](int i, int c) { return __bfloat162float(gDd[i * DP + c]); }, sink,
+            [&](int j, int c, float v) {
+                gTu[j * DP + c] = __float2bfloat16_rn(__bfloat162float(b_ur[j * LDB + c]) + v);
+            });
     }
     {
         const bf16* gdd = bpanel_ptr(p.dDelta, ch.gi);
@@ -765,8 +754,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
 //   with dN = -gamma stril(dRr Delta^T),   CdC[c] = sum_a Ct[c][a] dCt_end[c][a];
 // then d u^, dG, dE are assembled per token and
 //   d log_decay = -dE + reverse_cumsum(dG), with dG[last] += dGL.
-// N, t_i and t_j are block-centred (tensor cores off the diagonal blocks,
-// direct evaluation on them).  Writes the final gradients of u, h, gamma and
+// t_i and t_j are block-centred (tensor cores off the diagonal blocks, direct
+// evaluation on them); N comes from the forward pass.  Writes the final gradients of u, h, gamma and
 // log_decay.  The four contraction results and the three FP32 closure panels
 // overlay operands that are dead by then.
 constexpr size_t PRED_CLOSE_BWD_SMEM = 5 * BSLOT_BYTES + 2 * BMAT_BYTES + 3 * size_t(CL) * LDP * 4 +
@@ -810,7 +799,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
     cp_commit();
     load_gamma(p.gam, ch, s_gam);
     block_betas(s_beta, fG);
-    pair_block_scales_bf16(s_Mb, fG);
     for (int idx = threadIdx.x; idx < 3 * DP; idx += NTHREADS) {
         const int m = idx >> 7, c = idx & (DP - 1);
         s_pref[idx] = __float2bfloat16_rn(__expf(gG[((m + 1) * BT - 1) * DP + c]));
@@ -850,9 +838,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
     SD_PHASE(p.g, ph);
     {
         const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
-        pair_offdiag_bf16(s_Mb, b_ur, b_uc, [&](int i, int j, float v0, float v1) {
-            *reinterpret_cast<__nv_bfloat162*>(b_N + i * LDM + j) = __floats2bfloat162_rn(v0, v1);
-        });
         float a2[NT64][4];
         acc_zero<NT64>(a2);
         if (n0 <= r0) warp_mma_bf16<NT64, false, true>(a2, b_dr, LDB, b_dl, LDB, r0, n0, 0, DP);
@@ -862,26 +847,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
                 __floats2bfloat162_rn((j < i) ? gm * v0 : 0.f, (j + 1 < i) ? gm * v1 : 0.f);
         });
     }
-    // raw u^ rows: the BF16 operand times its stored 1/|u|
-    auto fu8 = [&](int j, int c0, float (&b)[8]) {
-        load8_bf16<FAST>(row_bf16(p.u, ch, j), c0, r, p.u.vec, j < ch.nvalid, b);
-        const float rs = s_ru[j];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) b[e] *= rs;
-    };
-    {   // diagonal blocks of N
-        const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8, l16 = threadIdx.x & 15;
-#pragma unroll 1
-        for (int pp = 0; pp < ROW_PASSES; ++pp) {
-            const int i = lr + ROWS_PER_PASS * pp, i0 = i & ~(BT - 1);
-            float a[1][8], E[8], out[1];
-            load8_panel(gG, i > 0 ? i - 1 : 0, c0, E);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) E[e] = i > 0 ? E[e] : 0.f;
-            fu8(i, c0, a[0]);
-            pair_diag_row<1, true>(i, a, E, [&](int j, float (&b)[8]) { fu8(j, c0, b); },
-                                   [&](int j, float (&Gj)[8]) { load8_panel(gG, j, c0, Gj); }, out);
-            b_N[i * LDM + i0 + l16] = __float2bfloat16_rn(out[0]);
+    {   // N of the forward pass -> BF16 operand
+        const float* gN = mat_ptr(p.Npair, ch.gi);
+        for (int idx = threadIdx.x; idx < CL * (CL / 4); idx += NTHREADS) {
+            const int i = idx >> 4, j4 = (idx & 15) << 2;
+            const float4 v = *reinterpret_cast<const float4*>(gN + i * CL + j4);
+            *reinterpret_cast<__nv_bfloat162*>(b_N + i * LDM + j4) = __floats2bfloat162_rn(v.x, v.y);
+            *reinterpret_cast<__nv_bfloat162*>(b_N + i * LDM + j4 + 2) = __floats2bfloat162_rn(v.z, v.w);
         }
     }
     __syncthreads();
@@ -989,15 +961,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
         auto fu = [&](int j, int c) {
             return (j < ch.nvalid && c < r) ? __bfloat162float(row_bf16(p.u, ch, j)[c]) * s_ru[j] : 0.f;
         };
-        auto fP = [&](int i, int j) { return __bfloat162float(b_dN[i * LDM + j]); };
         auto add_to = [](bf16* panel) {
             return [panel](int i, int c, float v) {
                 bf16* q = panel + i * LDB + c;
                 *q = __float2bfloat16_rn(__bfloat162float(*q) + v);
             };
         };
-        causal_diag<true, true>(al, fP, fu, add_to(b_dl));
-        anti_diag<true, true>(al, fP, fu, add_to(b_tj));
+        diag_sweep<true, true, true, true>(
+            al, [&](int i, int i0, float (&row)[BT]) { prow16_bf16(b_dN, LDM, i, i0, row); }, fu, fu,
+            add_to(b_dl), add_to(b_tj));
     }
     __syncthreads();
     SD_PHASE(p.g, ph);

@@ -125,6 +125,42 @@ __device__ __forceinline__ void pair_offdiag_bf16(const bf16* s_Mb, const bf16* 
     warp_epi<NT64>(acc, r0, n0, fe);
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Sum over the 16 lanes of a half-warp of 16 per-lane values at once: lane l of
+// the half-warp ends with the total of v[l].  15 shuffles instead of 64.
+__device__ __forceinline__ float transpose_sum16(float (&v)[BT]) {
+    static_assert(BT == 16, "written for 16 lanes");
+    const int l = threadIdx.x & 15;
+    const bool b3 = l & 8, b2 = l & 4, b1 = l & 2, b0 = l & 1;
+    float w8[8], w4[4], w2[2];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float send = b3 ? v[k] : v[k + 8];
+        const float keep = b3 ? v[k + 8] : v[k];
+        w8[k] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float send = b2 ? w8[k] : w8[k + 4];
+        const float keep = b2 ? w8[k + 4] : w8[k];
+        w4[k] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const float send = b1 ? w4[k] : w4[k + 2];
+        const float keep = b1 ? w4[k + 2] : w4[k];
+        w2[k] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+    }
+    const float send = b0 ? w2[0] : w2[1];
+    const float keep = b0 ? w2[1] : w2[0];
+    return keep + __shfl_xor_sync(0xffffffffu, send, 1);
+}
+
 // ---- diagonal blocks of a pair, row-wise mapping -----------------------------
 // The calling half-warp owns token row i and each lane eight channels of it:
 // a[n][8] are NA row operands sharing one exponent, x[8] the row prefix (G or E).
@@ -137,30 +173,36 @@ __device__ __forceinline__ void pair_offdiag_bf16(const bf16* s_Mb, const bf16* 
 template <int NA, bool STRICT, class FB8, class FG8>
 __device__ __forceinline__ void pair_diag_row(int i, const float (&a)[NA][8], const float (&x)[8], FB8 fb8, FG8 fg8,
                                               float (&out)[NA]) {
-    const int l16 = threadIdx.x & 15;
+    constexpr float LOG2E = 1.4426950408889634f;
     const int i0 = i & ~(BT - 1), ii = i & (BT - 1);
     const int jmax = (ii | 1) - (STRICT ? 1 : 0);  // uniform over the warp's two rows (2w, 2w+1)
+    float xs[8], part[NA][BT];
 #pragma unroll
-    for (int n = 0; n < NA; ++n) out[n] = 0.f;
-    for (int jj = 0; jj <= jmax; ++jj) {
-        float b[8], G[8], s[NA];
-        fb8(i0 + jj, b);
-        fg8(i0 + jj, G);
-        const bool live = STRICT ? (jj < ii) : (jj <= ii);
+    for (int e = 0; e < 8; ++e) xs[e] = x[e] * LOG2E;
 #pragma unroll
-        for (int n = 0; n < NA; ++n) s[n] = 0.f;
+    for (int jj = 0; jj < BT; ++jj) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const float w = live ? b[e] * __expf(fminf(x[e] - G[e], 0.f)) : 0.f;
+        for (int n = 0; n < NA; ++n) part[n][jj] = 0.f;
+        if (jj <= jmax) {  // warp-uniform
+            float b[8], G[8], s[NA];
+            fb8(i0 + jj, b);
+            fg8(i0 + jj, G);
 #pragma unroll
-            for (int n = 0; n < NA; ++n) s[n] = fmaf(a[n][e], w, s[n]);
-        }
+            for (int n = 0; n < NA; ++n) s[n] = 0.f;
 #pragma unroll
-        for (int n = 0; n < NA; ++n) {
-            const float v = row_sum16(s[n]);
-            if (l16 == jj) out[n] = v;
+            for (int e = 0; e < 8; ++e) {
+                // exp(x - G) as 2^((x - G) log2 e); the exponent is <= 0 for every live pair
+                const float w = b[e] * ex2_approx(fmaf(-G[e], LOG2E, xs[e]));
+#pragma unroll
+                for (int n = 0; n < NA; ++n) s[n] = fmaf(a[n][e], w, s[n]);
+            }
+            const bool live = STRICT ? (jj < ii) : (jj <= ii);
+#pragma unroll
+            for (int n = 0; n < NA; ++n) part[n][jj] = live ? s[n] : 0.f;
         }
     }
+#pragma unroll
+    for (int n = 0; n < NA; ++n) out[n] = transpose_sum16(part[n]);
 }
 
 // ---- diagonal blocks of a causal / anti-causal sum, one thread per (channel, block) ----
@@ -168,8 +210,6 @@ __device__ __forceinline__ void pair_diag_row(int i, const float (&a)[NA][8], co
 // retention exp(x_i - G_j) built as a running product of alpha_k = exp(g_k), so
 // only BT exponentials are taken per thread.
 //   XE: x is the exclusive prefix (the term j == i does not exist then).
-//   al: the thread's alphas (block_alphas);  fP(i, j): P[i][j];
-//   fv(j, c): column-side operand (causal) / row-side operand (anti);  fo(i, c, value).
 template <class FG>
 __device__ __forceinline__ void block_alphas(float (&al)[BT], FG fG) {
     static_assert(NTHREADS == NBLK * DP, "one thread per (channel, block)");
@@ -183,57 +223,65 @@ __device__ __forceinline__ void block_alphas(float (&al)[BT], FG fG) {
     }
 }
 
-template <bool XE, bool STRICT, class FP, class FV, class FO>
-__device__ __forceinline__ void causal_diag(const float (&al)[BT], FP fP, FV fv, FO fo) {
+// One sweep over the thread's BT x BT diagonal block of P serving both directions:
+//   CAUSAL: oc(i, c, sum_{j<=i} P[i][j] b[j] rho_ij)      ANTI: oa(j, c, sum_{i>=j} P[i][j] a[i] rho_ij)
+// with rho_ij = exp(x_i - G_j) built by a running product of the alphas (al).
+//   XE: x is the exclusive prefix (j < i only);  STRICT: the term j == i is skipped.
+//   fP16(i, i0, row): the BT entries P[i][i0 .. i0+BT) (the same address for every thread of a warp);
+//   fb(j, c) / fa(i, c): column-side / row-side operand themselves (not centred).
+template <bool XE, bool STRICT, bool CAUSAL, bool ANTI, class FP16, class FB, class FA, class FOC, class FOA>
+__device__ __forceinline__ void diag_sweep(const float (&al)[BT], FP16 fP16, FB fb, FA fa, FOC oc, FOA oa) {
     const int c = threadIdx.x & (DP - 1), i0 = (threadIdx.x >> 7) * BT;
-    float bv[BT];
+    float bv[BT], accA[BT];
 #pragma unroll
-    for (int k = 0; k < BT; ++k) bv[k] = fv(i0 + k, c);
+    for (int k = 0; k < BT; ++k) {
+        bv[k] = CAUSAL ? fb(i0 + k, c) : 0.f;
+        accA[k] = 0.f;
+    }
 #pragma unroll
     for (int ii = 0; ii < BT; ++ii) {
-        float acc = 0.f, rho = 1.f;
-        if (!XE) {
+        float prow[BT];
+        fP16(i0 + ii, i0, prow);
+        const float av = ANTI ? fa(i0 + ii, c) : 0.f;
+        float accC = 0.f, rho = 1.f;
 #pragma unroll
-            for (int jj = ii; jj >= 0; --jj) {
-                if (!(STRICT && jj == ii)) acc = fmaf(fP(i0 + ii, i0 + jj) * bv[jj], rho, acc);
-                rho *= al[jj];
+        for (int jj = XE ? ii - 1 : ii; jj >= 0; --jj) {
+            if (!(STRICT && jj == ii)) {
+                const float pr = prow[jj] * rho;
+                if (CAUSAL) accC = fmaf(pr, bv[jj], accC);
+                if (ANTI) accA[jj] = fmaf(pr, av, accA[jj]);
             }
-        } else {
-#pragma unroll
-            for (int jj = ii - 1; jj >= 0; --jj) {
-                acc = fmaf(fP(i0 + ii, i0 + jj) * bv[jj], rho, acc);
-                rho *= al[jj];
-            }
+            rho *= al[jj];
         }
-        fo(i0 + ii, c, acc);
+        if (CAUSAL) oc(i0 + ii, c, accC);
+    }
+    if (ANTI) {
+#pragma unroll
+        for (int jj = 0; jj < BT; ++jj) oa(i0 + jj, c, accA[jj]);
     }
 }
 
-template <bool XE, bool STRICT, class FP, class FV, class FO>
-__device__ __forceinline__ void anti_diag(const float (&al)[BT], FP fP, FV fv, FO fo) {
-    const int c = threadIdx.x & (DP - 1), i0 = (threadIdx.x >> 7) * BT;
-    float av[BT];
+// Row segment loaders for diag_sweep.
+__device__ __forceinline__ void prow16_f32(const float* M, int ld, int i, int i0, float (&row)[BT]) {
+    const float4* q = reinterpret_cast<const float4*>(M + i * ld + i0);
 #pragma unroll
-    for (int k = 0; k < BT; ++k) av[k] = fv(i0 + k, c);
+    for (int k = 0; k < BT / 4; ++k) {
+        const float4 v = q[k];
+        row[4 * k] = v.x; row[4 * k + 1] = v.y; row[4 * k + 2] = v.z; row[4 * k + 3] = v.w;
+    }
+}
+__device__ __forceinline__ void prow16_bf16(const bf16* M, int ld, int i, int i0, float (&row)[BT]) {
+    const uint4* q = reinterpret_cast<const uint4*>(M + i * ld + i0);
 #pragma unroll
-    for (int jj = 0; jj < BT; ++jj) {
-        float acc = 0.f, rho = 1.f;
-        if (!XE) {
-            // exp(G_i - G_j): 1 at i == j, then times alpha_{i} for each further row
+    for (int k = 0; k < BT / 8; ++k) {
+        const uint4 raw = q[k];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
-            for (int ii = jj; ii < BT; ++ii) {
-                if (ii > jj) rho *= al[ii];
-                if (!(STRICT && ii == jj)) acc = fmaf(fP(i0 + ii, i0 + jj) * av[ii], rho, acc);
-            }
-        } else {
-            // exp(E_i - G_j) = exp(G_{i-1} - G_j): 1 at i == j + 1
-#pragma unroll
-            for (int ii = jj + 1; ii < BT; ++ii) {
-                if (ii > jj + 1) rho *= al[ii - 1];
-                acc = fmaf(fP(i0 + ii, i0 + jj) * av[ii], rho, acc);
-            }
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h[e]);
+            row[8 * k + 2 * e] = f.x;
+            row[8 * k + 2 * e + 1] = f.y;
         }
-        fo(i0 + jj, c, acc);
     }
 }
 

@@ -14,9 +14,11 @@ struct FwdParams {
     Operand u, h, q, k, v, er, wr, ld, gam;
     // forward scratch
     float *Upd, *Qc, *Ubar, *Wd, *Ud, *Dt;
-    bf16 *Xg, *Aqd;  // operands of the output contraction only
+    bf16 *Xg;        // operand of the output contraction only
+    bf16 *Aqd;       // pair matrix of the output contraction, kept for backward
     // kept for backward
     float *Lam, *Gp, *Delta, *Dprim, *CtCk;
+    float *Npair, *Aed;  // pair matrices N = Lm / gamma and Aed, [CL][CL]
     bf16 *Zt, *SCk;  // only BF16 contractions read these
     void* y;
 };
@@ -140,12 +142,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
-    // Lm = gamma stril(N), N[i][j] = sum_c u^_ic u^_jc exp(E_ic - G_jc)
+    // Lm = gamma stril(N), N[i][j] = sum_c u^_ic u^_jc exp(E_ic - G_jc); N itself is kept for backward
+    float* gN = mat_ptr(p.Npair, ch.gi);
     pair_offdiag_tf32(s_M, [&](int i, int k) { return s_ut[i * LDP + k]; },
                       [&](int j, int k) { return s_un[j * LDP + k]; },
                       [&](int i, int j, float v0, float v1) {
                           float gm = s_gam[i];
                           *reinterpret_cast<float2*>(s_lm + i * LDA + j) = make_float2(gm * v0, gm * v1);
+                          *reinterpret_cast<float2*>(gN + i * CL + j) = make_float2(v0, v1);
                       });
     {
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
@@ -162,7 +166,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
             }
             pair_diag_row<1, true>(i, a, x, [&](int j, float (&b)[8]) { load8_smem(s_uh, j, c0, b); },
                                    [&](int j, float (&G)[8]) { load8_smem(s_G, j, c0, G); }, out);
-            s_lm[i * LDA + (i & ~(BT - 1)) + (threadIdx.x & 15)] = s_gam[i] * out[0];
+            const int j = (i & ~(BT - 1)) + (threadIdx.x & 15);
+            s_lm[i * LDA + j] = s_gam[i] * out[0];
+            gN[i * CL + j] = out[0];
         }
     }
     __syncthreads();
@@ -269,9 +275,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
     {
         float al[BT];
         block_alphas(al, fG);
-        causal_diag<false, false>(al, [&](int i, int j) { return s_aqk[i * LDA + j]; },
-                                  [&](int j, int c) { return s_un[j * LDP + c]; },
-                                  [&](int i, int c, float v) { s_dl[i * LDP + c] = v; });
+        auto none = [](int, int) { return 0.f; };
+        auto sink = [](int, int, float) {};
+        diag_sweep<false, false, true, false>(
+            al, [&](int i, int i0, float (&row)[BT]) { prow16_f32(s_aqk, LDA, i, i0, row); },
+            [&](int j, int c) { return s_un[j * LDP + c]; }, none,
+            [&](int i, int c, float v) { s_dl[i * LDP + c] = v; }, sink);
     }
     {
         const int c = threadIdx.x & (DP - 1), i0 = (threadIdx.x >> 7) * BT;
@@ -332,6 +341,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
     const float* gG = panel_ptr(p.Gp, ch.gi);
     const float* gd = panel_ptr(p.Dprim, ch.gi);
     bf16* gAqd = bmat_ptr(p.Aqd, ch.gi);
+    float* gAed = mat_ptr(p.Aed, ch.gi);
     pair_block_scales(s_M, [&](int i, int c) { return gG[i * DP + c]; });
     {
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8, l16 = threadIdx.x & 15;
@@ -390,6 +400,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
                                     [&](int j, float (&Gj)[8]) { load8_panel(gG, j, c0, Gj); }, out);
             gAqd[i * CL + i0 + l16] = __float2bfloat16_rn(out[0]);
             s_aed[i * LDA + i0 + l16] = (i0 + l16 < i) ? out[1] : 0.f;
+            gAed[i * CL + i0 + l16] = (i0 + l16 < i) ? out[1] : 0.f;
         }
     }
     __syncthreads();
@@ -403,6 +414,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
         pair_offdiag_tf32(s_M, [&](int i, int k) { return s_er[i * LDP + k]; }, fc,
                           [&](int i, int j, float v0, float v1) {
                               *reinterpret_cast<float2*>(s_aed + i * LDA + j) = make_float2(v0, v1);
+                              *reinterpret_cast<float2*>(gAed + i * CL + j) = make_float2(v0, v1);
                           });
     }
     __syncthreads();

@@ -287,7 +287,7 @@ class Model:
         # the same quantities under the names the CUDA library gives its panels
         saved["panels"] = dict(Lam=loc["lam"], G=loc["G"], Delta=Delta, Dprim=d, Zt=Zt, CtCk=Ct_ck, SCk=S_ck,
                                Upd=Upd, Qc=-W, Ubar=loc["Ubar"], Wd=Wd, Ud=Ud, Dt=ext["Dt"],
-                               Xg=ext["Xg"], Aqd=ext["Aqd"])
+                               Xg=ext["Xg"], Aqd=ext["Aqd"], N=loc["N"], Aed=ext["Aed"])
         yo = self._unchunks(y, B, T, H)
         C_T = Ct_fin.transpose(-1, -2).reshape(B, H, r, r)
         S_T = S_fin.reshape(B, H, r, V)

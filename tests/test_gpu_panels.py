@@ -9,8 +9,8 @@ from tests.chunk_model import Model
 from tests.gpu_harness import RawRun, make_inputs, model_inputs
 from tests.helpers import rel_l2
 
-SAVED = ("Lam", "G", "Delta", "Dprim", "Zt", "CtCk", "SCk")
-FWD = ("Upd", "Qc", "Ubar", "Wd", "Ud", "Dt", "Xg", "Aqd")
+SAVED = ("Lam", "G", "Delta", "Dprim", "Zt", "CtCk", "SCk", "N", "Aed", "Aqd")
+FWD = ("Upd", "Qc", "Ubar", "Wd", "Ud", "Dt", "Xg")
 BWD = ("Pp", "Qp", "Ag", "Xg", "Dyf", "Chi", "Ee", "dR", "dSeCk", "SdS",
        "duPart", "dkPart", "dGPart", "DG", "Dd", "Xext", "Tu", "Khat", "dDelta", "Ppp", "Qpp", "Rneg",
        "dRr", "dCeCk")
