@@ -96,7 +96,12 @@ class MixerOracle:
     """params: dict with the upstream parameter names (numpy, any float dtype)."""
 
     def __init__(self, params, *, hidden_size, num_heads, head_k_dim, head_v_dim, use_short_conv=True,
-                 norm_eps=1e-6):
+                 norm_eps=1e-6, activation_rounding=None):
+        """``activation_rounding``: optional callable applied to every activation a
+        reduced-precision implementation stores between two kernels (projection row,
+        conv output, gate pre-activations, operator output, normalised output); the
+        adjoint treats it as the identity.  None = exact FP64 (the upstream CPU path)."""
+        self.rnd = activation_rounding if activation_rounding is not None else (lambda z: z)
         self.p = {k: np.asarray(v, dtype=np.float64) for k, v in params.items()}
         self.hidden, self.H, self.r, self.V = hidden_size, num_heads, head_k_dim, head_v_dim
         self.conv = use_short_conv
@@ -115,6 +120,7 @@ class MixerOracle:
         row = x @ p["in_proj.weight"].T
         if "in_proj.bias" in p:
             row = row + p["in_proj.bias"]
+        row = self.rnd(row)
         c = {"x": x, "row": row}
         Dc = sum(self.sizes[:3])
         if self.conv:
@@ -124,6 +130,7 @@ class MixerOracle:
             qkv = pre * _sigmoid(pre)
             c.update(pre=pre)
             final_conv = None
+        qkv = self.rnd(qkv)
         q = qkv[..., :H * r].reshape(B, T, H, r)
         k = qkv[..., H * r:2 * H * r].reshape(B, T, H, r)
         v = qkv[..., 2 * H * r:].reshape(B, T, H, V)
@@ -133,13 +140,15 @@ class MixerOracle:
         wr = self._piece(row, 6).reshape(B, T, H, V)
         graw = self._piece(row, 7)
         dhid, ghid = self._piece(row, 8), self._piece(row, 9)
-        araw = (dhid @ p["decay_proj.weight"].T).reshape(B, T, H, r)
-        gate = (ghid @ p["output_gate_proj.weight"].T + p["output_gate_proj.bias"]).reshape(B, T, H, V)
+        araw = self.rnd((dhid @ p["decay_proj.weight"].T).reshape(B, T, H, r))
+        gate = self.rnd((ghid @ p["output_gate_proj.weight"].T + p["output_gate_proj.bias"]).reshape(B, T, H, V))
         log_decay, c["gate_saved"] = kda_gate_forward(araw, p["associative_log_rate"], p["associative_decay_bias"])
         gamma = _sigmoid(graw + p["geometry_write_bias"].reshape(1, 1, H))
         erase, write = _sigmoid(er), _sigmoid(wr)
         o, fin = orc.forward(u, h, q, k, v, log_decay, erase, write, gamma, initial_state=operator_state)
+        o = self.rnd(o)
         y, c["norm_saved"] = norm_gate_forward(o, gate, p["output_norm.weight"], self.eps)
+        y = self.rnd(y)
         out = y.reshape(B, T, H * V) @ p["output_proj.weight"].T
         if "output_proj.bias" in p:
             out = out + p["output_proj.bias"]
@@ -148,9 +157,16 @@ class MixerOracle:
         self.cache = c
         return out, fin, final_conv
 
-    def backward(self, dout, dC_T=None, dS_T=None, dconv_T=None):
+    def backward(self, dout, dC_T=None, dS_T=None, dconv_T=None, operator_grads=None):
         """Returns (dx, dict of parameter gradients, d conv_state or None, operator-state grads).
-        dC_T/dS_T/dconv_T are cotangents of the final operator and conv states."""
+        dC_T/dS_T/dconv_T are cotangents of the final operator and conv states.
+
+        ``operator_grads``: optional dict of gradients with respect to the operator's
+        operands (u, h, q, keys, values, log_decay, erase_raw, write_raw, geometry_write,
+        C0, S0) to chain through the glue instead of the checker's own operator VJP --
+        used to check the glue's adjoint separately from the operator's.  The
+        operator gradients actually used are left in ``self.operator_grads``
+        (erase / write with respect to the raw logits) and ``self.do``."""
         p, c, H, r, V = self.p, self.cache, self.H, self.r, self.V
         B, T = c["B"], c["T"]
         g = {}
@@ -161,15 +177,24 @@ class MixerOracle:
             g["output_proj.bias"] = dout.sum((0, 1))
         dy = (dout @ p["output_proj.weight"]).reshape(B, T, H, V)
         do, dgate, g["output_norm.weight"] = norm_gate_backward(dy, p["output_norm.weight"], c["norm_saved"])
-        og = orc.backward(c["u"], c["h"], c["q"], c["k"], c["v"], c["log_decay"], c["erase"], c["write"],
-                          c["gamma"], do, dC_T=dC_T, dS_T=dS_T, initial_state=c["operator_state"])
+        self.do = do
+        if operator_grads is None:
+            og = orc.backward(c["u"], c["h"], c["q"], c["k"], c["v"], c["log_decay"], c["erase"], c["write"],
+                              c["gamma"], do, dC_T=dC_T, dS_T=dS_T, initial_state=c["operator_state"])
+            og["erase_raw"] = og["erase"] * c["erase"] * (1 - c["erase"])
+            og["write_raw"] = og["write"] * c["write"] * (1 - c["write"])
+        else:
+            og = {k: np.asarray(v, dtype=np.float64) for k, v in operator_grads.items()}
+            og.setdefault("C0", None)
+            og.setdefault("S0", None)
+        self.operator_grads = og
         drow = np.zeros_like(c["row"])
         put = lambda i, val: drow.__setitem__((Ellipsis, slice(self.offsets[i], self.offsets[i + 1])),
                                               val.reshape(B, T, -1))
         put(3, og["u"])
         put(4, og["h"])
-        put(5, og["erase"] * c["erase"] * (1 - c["erase"]))
-        put(6, og["write"] * c["write"] * (1 - c["write"]))
+        put(5, og["erase_raw"])
+        put(6, og["write_raw"])
         dgraw = og["geometry_write"] * c["gamma"] * (1 - c["gamma"])
         put(7, dgraw)
         g["geometry_write_bias"] = dgraw.sum((0, 1))

@@ -522,13 +522,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* b_uc = reinterpret_cast<bf16*>(smem_raw);   // u^ col
-    bf16* b_ur = b_uc + BSLOT_ELEMS;   // u^ rowE, then t_u off the diagonal blocks
+    bf16* b_ur = b_uc + BSLOT_ELEMS;   // u^ itself (diagonal blocks), then t_u off the diagonal blocks
     bf16* b_ub = b_ur + BSLOT_ELEMS;   // Ubar, then Q''
     bf16* b_kh = b_ub + BSLOT_ELEMS;
     bf16* b_dl = b_kh + BSLOT_ELEMS;   // Delta, then dDelta_loc / P''
     bf16* b_dg = b_dl + BSLOT_ELEMS;   // dd exp(G)
     bf16* b_ddr = b_dg + BSLOT_ELEMS;  // dd rowG
-    bf16* b_Ct = b_ddr + BSLOT_ELEMS;
+    bf16* b_Ct = b_ddr + BSLOT_ELEMS;  // arrives after the pair phase; until then its place holds
+    float* s_G = reinterpret_cast<float*>(b_Ct);   // the FP32 chunk prefix [CL][LDP] for the diagonal blocks
+    static_assert(size_t(CL) * LDP * 4 <= BSTATE_BYTES, "the prefix panel fits in the state slot");
     bf16* b_aqk = b_Ct + DP * LDB;
     bf16* b_daqk = b_aqk + BMAT_ELEMS;
     float* f_lmT = reinterpret_cast<float*>(b_daqk + BMAT_ELEMS);
@@ -545,7 +547,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     auto fG = [&](int i, int c) { return gG[i * DP + c]; };
 
     async_bpanel(b_dg, bpanel_ptr(p.DG, ch.gi));
-    async_bstate(b_Ct, bstate_ptr(p.CtCkB, ch.gi));
+    async_panel_f32(s_G, gG);
     cp_commit();
     load_gamma(p.gam, ch, s_gam);
     block_betas(s_beta, fG);
@@ -575,17 +577,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
             load8_panel(gDelta, i, c0, dl);
             load8_bpanel(gDd, i, c0, dd);
             const float gm = (i < ch.nvalid) ? *row_f32(p.gam, ch, i) : 0.f;
-            float uc[8], ur[8], ub[8], rn[8], ddr[8];
+            float uc[8], ub[8], rn[8], ddr[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 uc[e] = uh[e] * __expf(Ge[e] - G[e]);
-                ur[e] = uh[e] * __expf(E[e] - Gp[e]);
                 ub[e] = uh[e] * __expf(GL[e] - G[e]);
                 rn[e] = -gm * uh[e] * __expf(E[e]);
                 ddr[e] = dd[e] * __expf(G[e] - Gp[e]);
             }
             store8_bsm(b_uc, i, c0, uc);
-            store8_bsm(b_ur, i, c0, ur);
+            store8_bsm(b_ur, i, c0, uh);
             store8_bsm(b_ub, i, c0, ub);
             store8_bsm(b_kh, i, c0, kh);
             store8_bsm(b_dl, i, c0, dl);
@@ -618,18 +619,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     }
     {   // diagonal blocks of dAqk
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8, l16 = threadIdx.x & 15;
-        auto fu8 = [&](int j, float (&b)[8]) {
-            load8_bf16<FAST>(row_bf16(p.u, ch, j), c0, r, p.u.vec, j < ch.nvalid, b);
-            const float rs = s_ru[j];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) b[e] *= rs;
-        };
-        auto fg8 = [&](int j, float (&Gj)[8]) { load8_panel(gG, j, c0, Gj); };
+        auto fu8 = [&](int j, float (&b)[8]) { load8_bsm(b_ur, j, c0, b); };
+        auto fg8 = [&](int j, float (&Gj)[8]) { load8_smem(s_G, j, c0, Gj); };
 #pragma unroll 1
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
             const int i = lr + ROWS_PER_PASS * pp, i0 = i & ~(BT - 1);
             float a[1][8], G[8], out[1];
-            load8_panel(gG, i, c0, G);
+            load8_smem(s_G, i, c0, G);
             load8_bpanel(gDd, i, c0, a[0]);
             pair_diag_row<1, false>(i, a, G, fu8, fg8, out);
             b_daqk[i * LDM + i0 + l16] = __float2bfloat16_rn(out[0]);
@@ -637,6 +633,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
+    async_bstate(b_Ct, bstate_ptr(p.CtCkB, ch.gi));   // the prefix panel is dead: the state takes its place
+    cp_commit();
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
     float accd[NT128][4];  // dAqk^T K^  (added to dDelta_src below)
     acc_zero<NT128>(accd);
@@ -654,6 +652,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
             return make_float2(__expf(Ge.x - G.x), __expf(Ge.y - G.y));
         });
     }
+    cp_wait<0>();
+    __syncthreads();
     {
         // dk^ and its norm VJP, in accumulator layout
         float acc[NT128][4];

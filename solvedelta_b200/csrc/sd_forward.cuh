@@ -322,7 +322,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
 //   Aqd[i][j] = sum_c chi_ic d_jc exp(G_ic - G_jc) (j <= i),  Aed likewise with -e (j < i)
 // in block-centred form, and the solved panels Wd = (I-Aed)^-1 ag, Ud = (I-Aed)^-1 Z
 // for the S scan (ag = -e exp(G), referenced to the chunk start like the scan itself).
-constexpr size_t EXT_PREP_FWD_SMEM = 5 * SLOT_BYTES + MAT_BYTES + 3 * DP * sizeof(float);
+constexpr size_t EXT_PREP_FWD_SMEM = 6 * SLOT_BYTES + MAT_BYTES + 3 * DP * sizeof(float);
 
 template <bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) {
@@ -331,40 +331,44 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
     extern __shared__ __align__(16) float smem[];
     float* s_xr = smem;                  // chi rowG   (block-centred row operand)
     float* s_er = s_xr + SLOT_FLOATS;    // -e rowG
-    float* s_dc = s_er + SLOT_FLOATS;    // d col      (block-centred column operand)
-    float* s_ag = s_dc + SLOT_FLOATS;    // -e exp(G)  -> Wd
+    float* s_d = s_er + SLOT_FLOATS;     // d itself (the column operand d col is formed on the fly)
+    float* s_G = s_d + SLOT_FLOATS;      // chunk prefix of the log decay
+    float* s_ag = s_G + SLOT_FLOATS;     // -e exp(G)  -> Wd
     float* s_z = s_ag + SLOT_FLOATS;     // z          -> Ud
     float* s_aed = s_z + SLOT_FLOATS;
     float* s_M = s_aed + MAT_FLOATS;
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r, V = p.g.V;
-    const float* gG = panel_ptr(p.Gp, ch.gi);
-    const float* gd = panel_ptr(p.Dprim, ch.gi);
     bf16* gAqd = bmat_ptr(p.Aqd, ch.gi);
     float* gAed = mat_ptr(p.Aed, ch.gi);
-    pair_block_scales(s_M, [&](int i, int c) { return gG[i * DP + c]; });
+    async_panel_f32(s_G, panel_ptr(p.Gp, ch.gi));
+    async_panel_f32(s_d, panel_ptr(p.Dprim, ch.gi));
+    cp_commit();
+    cp_wait<0>();
+    __syncthreads();
+    SD_PHASE(p.g, ph);
+    pair_block_scales(s_M, [&](int i, int c) { return s_G[i * LDP + c]; });
     {
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8, l16 = threadIdx.x & 15;
         const float* gDelta = panel_ptr(p.Delta, ch.gi);
         float* gDt = panel_ptr(p.Dt, ch.gi);
         bf16* gXg = bpanel_ptr(p.Xg, ch.gi);
         float GL[8];
-        load8_panel(gG, CL - 1, c0, GL);
+        load8_smem(s_G, CL - 1, c0, GL);
 #pragma unroll 1
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
             const int i = lr + ROWS_PER_PASS * pp, i0 = i & ~(BT - 1);
-            float uh[8], kh[8], qh[8], dl[8], d[8], er[8], wr[8], v[8], G[8], Gp[8], Ge[8], se[8];
+            float uh[8], kh[8], qh[8], dl[8], d[8], er[8], wr[8], v[8], G[8], Gp[8], se[8];
             load8_norm<FAST>(p.u, ch, i, c0, r, uh);
             load8_norm<FAST>(p.k, ch, i, c0, r, kh);
             load8_norm<FAST>(p.q, ch, i, c0, r, qh);
             load8_panel(gDelta, i, c0, dl);
-            load8_panel(gd, i, c0, d);
             load8_bf16<FAST>(row_bf16(p.er, ch, i), c0, r, p.er.vec, i < ch.nvalid, er);
             load8_bf16<FAST>(row_bf16(p.wr, ch, i), c0, V, p.wr.vec, i < ch.nvalid, wr);
             load8_bf16<FAST>(row_bf16(p.v, ch, i), c0, V, p.v.vec, i < ch.nvalid, v);
-            load8_panel(gG, i, c0, G);
-            load8_panel(gG, i0 + BT - 1, c0, Ge);
-            load8_panel(gG, i0 ? i0 - 1 : 0, c0, Gp);
+            load8_smem(s_d, i, c0, d);
+            load8_smem(s_G, i, c0, G);
+            load8_smem(s_G, i0 ? i0 - 1 : 0, c0, Gp);
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 se[e] = sigmoidf_(er[e]);
@@ -372,7 +376,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
             }
             Sources src;
             sources_fwd(uh, kh, qh, dl, se, src);
-            float xg[8], ag[8], xr[8], ern[8], dc[8], z[8], dt[8];
+            float xg[8], ag[8], xr[8], ern[8], z[8], dt[8];
             float a[2][8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
@@ -381,7 +385,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
                 ag[e] = -src.e[e] * ep;
                 xr[e] = src.chi[e] * rw;
                 ern[e] = -src.e[e] * rw;
-                dc[e] = d[e] * __expf(Ge[e] - G[e]);
                 dt[e] = d[e] * __expf(GL[e] - G[e]);
                 z[e] = sigmoidf_(wr[e]) * v[e];
                 a[0][e] = src.chi[e];
@@ -389,15 +392,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
             }
             store8_smem(s_xr, i, c0, xr);
             store8_smem(s_er, i, c0, ern);
-            store8_smem(s_dc, i, c0, dc);
             store8_smem(s_ag, i, c0, ag);
             store8_smem(s_z, i, c0, z);
             store8_panel(gDt, i, c0, dt);
             store8_bpanel(gXg, i, c0, xg);
             // diagonal blocks: exp(G_i - G_j) directly; both pairs share the exponentials
             float out[2];
-            pair_diag_row<2, false>(i, a, G, [&](int j, float (&b)[8]) { load8_panel(gd, j, c0, b); },
-                                    [&](int j, float (&Gj)[8]) { load8_panel(gG, j, c0, Gj); }, out);
+            pair_diag_row<2, false>(i, a, G, [&](int j, float (&b)[8]) { load8_smem(s_d, j, c0, b); },
+                                    [&](int j, float (&Gj)[8]) { load8_smem(s_G, j, c0, Gj); }, out);
             gAqd[i * CL + i0 + l16] = __float2bfloat16_rn(out[0]);
             s_aed[i * LDA + i0 + l16] = (i0 + l16 < i) ? out[1] : 0.f;
             gAed[i * CL + i0 + l16] = (i0 + l16 < i) ? out[1] : 0.f;
@@ -406,7 +408,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
     __syncthreads();
     SD_PHASE(p.g, ph);
     {
-        auto fc = [&](int j, int k) { return s_dc[j * LDP + k]; };
+        // column operand d_j exp(Gend_J - G_j), centred on the end of its block
+        auto fc = [&](int j, int k) {
+            return s_d[j * LDP + k] * __expf(s_G[(j | (BT - 1)) * LDP + k] - s_G[j * LDP + k]);
+        };
         pair_offdiag_tf32(s_M, [&](int i, int k) { return s_xr[i * LDP + k]; }, fc,
                           [&](int i, int j, float v0, float v1) {
                               *reinterpret_cast<__nv_bfloat162*>(gAqd + i * CL + j) = __floats2bfloat162_rn(v0, v1);
