@@ -275,24 +275,26 @@ class DeviceStep:
 # the kernel counted once.
 KIB = 1024
 # f = FP32 panel 32 KiB, b = BF16 panel or BF16 operand chunk 16 KiB, s = FP32 state 64 KiB,
-# t = BF16 state 32 KiB, m = BF16 pair matrix 8 KiB
-_F, _B, _S, _T, _M = 32 * KIB, 16 * KIB, 64 * KIB, 32 * KIB, 8 * KIB
+# t = BF16 state 32 KiB, m = BF16 pair matrix 8 KiB, p = FP32 pair matrix 16 KiB
+_F, _B, _S, _T, _M, _P = 32 * KIB, 16 * KIB, 64 * KIB, 32 * KIB, 8 * KIB, 16 * KIB
 KERNEL_BYTES_PER_CHUNK = {
-    "k_prep_fwd": 2 * _B + _F + 4 * _F,                         # u,h,g -> Upd,Qc,Ubar,G
+    "k_prep_fwd": 2 * _B + _F + 4 * _F + _P,                    # u,h,g -> Upd,Qc,Ubar,G,N
     "k_state_scan[C]": 4 * _F + _S + _T,                        # P,Q,R -> X, FP32 + BF16 ckpt
     "k_primal_fwd": 2 * _B + 2 * _F + _S + _F,                  # u,k,G,Delta,Ct -> d
-    "k_exterior_prep_fwd": 6 * _B + 3 * _F + 3 * _F + _B + _M,  # 6 operands,G,Delta,d -> Wd,Ud,Dt,Xg,Aqd
+    # 6 operands,G,Delta,d -> Wd,Ud,Dt,Xg,Aqd,Aed
+    "k_exterior_prep_fwd": 6 * _B + 3 * _F + 3 * _F + _B + _M + _P,
     "k_state_scan[S]": 3 * _F + _B + _T,                        # P,Q,R -> Z~ (BF16), BF16 ckpt
     "k_output_fwd": _B + _M + _B + _T + _B,                     # Xg,Aqd,Zt,S -> y
-    "k_exterior_prep_bwd": 5 * _B + 3 * _F + 6 * _B,            # u,k,q,er,dy,G,Delta,d -> Ag,Xg,Dyf,Dneg,Pp,Qp
+    # u,k,q,er,dy,G,Delta,d,Aqd,Aed -> Ag,Xg,Dyf,Dcol,Xr,Er,Chi,Ee,Pp,Qp
+    "k_exterior_prep_bwd": 5 * _B + 3 * _F + _M + _P + 10 * _B,
     "k_state_scan_b[dS]": 6 * _B + _T,
-    # Dyf,dR,Dneg,Xg,Ag,Zt,S,dSe + u,k,q,er,wr,v,G,Delta,d -> 5 partial panels, DG, dq,der,dv,dwr
-    "k_exterior_pair_bwd": 6 * _B + 2 * _T + 6 * _B + 3 * _F + 6 * _B + 4 * _B,
-    # u,k,G,Delta,DG,Ct(bf16),dkPart,dDelta -> Khat,Rneg,Tpre,dk,Ppp,Qpp
-    "k_primal_bwd": 2 * _B + 2 * _F + _B + _T + 2 * _B + 6 * _B,
+    # Dyf,dR,Zt,Dcol,Xr,Er,Chi,Ee,S,dSe + u,k,q,er,wr,v,G,Delta,d -> 5 partial panels, DG,Dd, dq,der,dv,dwr
+    "k_exterior_pair_bwd": 8 * _B + 2 * _T + 6 * _B + 3 * _F + 7 * _B + 4 * _B,
+    # u,k,G,Delta,DG,Dd,Ct(bf16),N,dkPart,dDelta -> Khat,Rneg,Tu,dk,Ppp,Qpp
+    "k_primal_bwd": 2 * _B + 2 * _F + 2 * _B + _T + _P + 2 * _B + 6 * _B,
     "k_state_scan_b[dC]": 6 * _B + _T,
-    # u,h,G,Delta,dRr,Ct,dCe,duPart,Tpre,dGPart,Xext -> du,dh,dlog_decay
-    "k_predictor_close_bwd": 2 * _B + 2 * _F + _B + _T + _T + 4 * _B + 2 * _B + _F,
+    # u,h,G,Delta,dRr,Ct,dCe,N,duPart,Tu,dGPart,Xext -> du,dh,dlog_decay
+    "k_predictor_close_bwd": 2 * _B + 2 * _F + _B + _T + _T + _P + 4 * _B + 2 * _B + _F,
 }
 
 
@@ -305,6 +307,62 @@ KERNEL_DRAM_BYTES_PER_CHUNK = {
     "k_exterior_prep_bwd": 247 * KIB, "k_state_scan_b[dS]": 103 * KIB, "k_exterior_pair_bwd": 496 * KIB,
     "k_primal_bwd": 249 * KIB, "k_state_scan_b[dC]": 104 * KIB, "k_predictor_close_bwd": 296 * KIB,
 }
+
+
+def time_mixer_glue(B, T, H, r, V, device, reps=10):
+    """Device time of the mixer glue kernels around the operator at the workload's shape
+    (conv over the q|k|v slice of a projection row, decay gate, gated RMSNorm), forward and
+    reverse, with the HBM bandwidth their one-pass algorithmic bytes amount to.  Every
+    operand is larger than the 126 MB L2."""
+    import torch
+
+    from solvedelta_b200 import conv4_silu, kda_decay_gate, rms_norm_gated
+
+    peak, _ = _peaks()
+    gen = torch.Generator(device="cpu").manual_seed(3)
+    D = 2 * H * r + H * V
+    row = torch.randn(B, T, D + 64, generator=gen).to(torch.bfloat16).to(device)
+    x = row[..., :D].requires_grad_()
+    w = (0.5 * torch.randn(D, 4, generator=gen)).to(device).requires_grad_()
+    raw = torch.randn(B, T, H, r, generator=gen).to(torch.bfloat16).to(device).requires_grad_()
+    A = torch.zeros(H, device=device).requires_grad_()
+    bias = torch.zeros(H, r, device=device).requires_grad_()
+    o = torch.randn(B, T, H, V, generator=gen).to(torch.bfloat16).to(device).requires_grad_()
+    gate = torch.randn(B, T, H, V, generator=gen).to(torch.bfloat16).to(device).requires_grad_()
+    nw = torch.ones(V, device=device).requires_grad_()
+    n_conv, n_gate, n_norm = B * T * D, B * T * H * r, B * T * H * V
+    cases = {
+        "conv4_silu": (lambda: conv4_silu(x, w)[0], (x, w), 2 * n_conv * 2, 3 * n_conv * 2),
+        "kda_decay_gate": (lambda: kda_decay_gate(raw, A, bias), (raw, A, bias), n_gate * (2 + 4), n_gate * (2 + 4 + 2)),
+        "rms_norm_gated": (lambda: rms_norm_gated(o, gate, nw, 1e-6), (o, gate, nw), 3 * n_norm * 2, 5 * n_norm * 2),
+    }
+    out = {}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for name, (fn, leaves, fwd_bytes, bwd_bytes) in cases.items():
+        y = fn()
+        dy = torch.randn_like(y)
+        for _ in range(3):
+            torch.autograd.grad(fn(), leaves, dy)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            y = fn()
+        e1.record()
+        torch.cuda.synchronize()
+        fwd_ms = e0.elapsed_time(e1) / reps
+        e0.record()
+        for _ in range(reps):
+            torch.autograd.grad(fn(), leaves, dy)
+        e1.record()
+        torch.cuda.synchronize()
+        both_ms = e0.elapsed_time(e1) / reps
+        bwd_ms = max(both_ms - fwd_ms, 1e-6)
+        out[name] = {"fwd_ms": round(fwd_ms, 4), "bwd_ms": round(bwd_ms, 4),
+                     "fwd_gbs": round(fwd_bytes / fwd_ms / 1e6, 1), "bwd_gbs": round(bwd_bytes / bwd_ms / 1e6, 1),
+                     "fwd_frac": round(fwd_bytes / fwd_ms / 1e6 / peak, 3),
+                     "bwd_frac": round(bwd_bytes / bwd_ms / 1e6 / peak, 3)}
+    out["shape"] = f"B={B}, T={T}, conv channels {D}, gate/norm rows {B * T * H} x {r}; timed through the autograd wrappers"
+    return out
 
 
 def run_ours(opts, rank, world, local_rank):
@@ -461,6 +519,10 @@ def run_ours(opts, rank, world, local_rank):
                "ms_per_step": e2e_ms, "steps": e2e_steps, "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h_bytes[0], "pipelined": "3 streams, 2 slots"}
 
+    glue = None
+    if world == 1 and not opts.skip_glue:
+        glue = time_mixer_glue(B, T, H, r, V, device)
+
     if rank == 0:
         cpu_baseline = None
         if world == 1 and not opts.skip_cpu:
@@ -484,6 +546,7 @@ def run_ours(opts, rank, world, local_rank):
             "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu_baseline,
             "forward_only": {"ms_per_step": fwd_ms, "value": job_throughput(runner.tokens, fwd_ms * 1e-3, world),
                              "unit": "tokens/s"},
+            "mixer_glue": glue,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -501,6 +564,7 @@ def main():
                          "small = B=2, T=1024; the reported metric is defined on full")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg (profiler captures)")
+    ap.add_argument("--skip-glue", action="store_true", help="skip the mixer glue kernels (profiler captures)")
     opts = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

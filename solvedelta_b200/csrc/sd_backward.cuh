@@ -623,7 +623,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
         auto fg8 = [&](int j, float (&Gj)[8]) { load8_smem(s_G, j, c0, Gj); };
 #pragma unroll 1
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
-            const int i = lr + ROWS_PER_PASS * pp, i0 = i & ~(BT - 1);
+            const int i = balanced_row(lr, pp), i0 = i & ~(BT - 1);
             float a[1][8], G[8], out[1];
             load8_smem(s_G, i, c0, G);
             load8_bpanel(gDd, i, c0, a[0]);

@@ -161,6 +161,15 @@ __device__ __forceinline__ float transpose_sum16(float (&v)[BT]) {
     return keep + __shfl_xor_sync(0xffffffffu, send, 1);
 }
 
+// Token row of pass pp for the half-warp lr = tid / 16 when a row-wise loop also walks the
+// diagonal blocks of a pair: the work of row i grows with its position in its block, so the
+// second pass mirrors the position (15 - ii) -- every warp then carries the same total work
+// and the rows of a warp stay an adjacent pair of one block.
+__device__ __forceinline__ int balanced_row(int lr, int pp) {
+    static_assert(ROW_PASSES == 2 && ROWS_PER_PASS == 2 * BT, "written for two passes of two blocks");
+    return pp == 0 ? lr : ROWS_PER_PASS + ((lr & BT) | (BT - 1 - (lr & (BT - 1))));
+}
+
 // ---- diagonal blocks of a pair, row-wise mapping -----------------------------
 // The calling half-warp owns token row i and each lane eight channels of it:
 // a[n][8] are NA row operands sharing one exponent, x[8] the row prefix (G or E).

@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
 #pragma unroll 1
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
-            const int i = lr + ROWS_PER_PASS * pp;
+            const int i = balanced_row(lr, pp);
             float a[1][8], x[8], out[1];
             load8_smem(s_uh, i, c0, a[0]);
             if (i > 0) {
@@ -357,7 +357,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
         load8_smem(s_G, CL - 1, c0, GL);
 #pragma unroll 1
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
-            const int i = lr + ROWS_PER_PASS * pp, i0 = i & ~(BT - 1);
+            const int i = balanced_row(lr, pp), i0 = i & ~(BT - 1);
             float uh[8], kh[8], qh[8], dl[8], d[8], er[8], wr[8], v[8], G[8], Gp[8], se[8];
             load8_norm<FAST>(p.u, ch, i, c0, r, uh);
             load8_norm<FAST>(p.k, ch, i, c0, r, kh);

@@ -37,6 +37,11 @@ def test_struct_sizes_match_header():
     assert ctypes.sizeof(_lib.ForwardArgs) == 24 + 9 * 32 + 5 * 8 + 4 * 8
     assert ctypes.sizeof(_lib.BackwardArgs) == 24 + 10 * 32 + 2 * 8 + 4 * 8 + 11 * 8
     assert ctypes.sizeof(_lib.DecodeArgs) == 24 + 9 * 32 + 3 * 8
+    # mixer glue: three int32 (padded to 16) + pointers / strides / sizes of 8 bytes each
+    assert ctypes.sizeof(_lib.Conv4ForwardArgs) == 16 + 7 * 8
+    assert ctypes.sizeof(_lib.Conv4BackwardArgs) == 16 + 11 * 8
+    assert ctypes.sizeof(_lib.KdaGateArgs) == 16 + 10 * 8
+    assert ctypes.sizeof(_lib.NormGateArgs) == 16 + 10 * 8
 
 
 def test_workspace_queries_scale_with_chunks(lib):
@@ -64,6 +69,16 @@ def test_argument_errors_are_status_codes(lib):
     dec = _lib.DecodeArgs()
     dec.shape = _lib.Shape(1, 2, 1, 16, 16)
     assert lib.sd_decode_step(ctypes.byref(dec), None) == -1  # T must be 1
+    assert lib.sd_conv4_silu_forward(None, None) == -1
+    assert lib.sd_conv4_silu_backward(None, None) == -1
+    assert lib.sd_kda_gate_forward(None, None) == -1
+    assert lib.sd_kda_gate_backward(None, None) == -1
+    assert lib.sd_norm_gate_forward(None, None) == -1
+    assert lib.sd_norm_gate_backward(None, None) == -1
+    assert lib.sd_conv4_silu_forward(ctypes.byref(_lib.Conv4ForwardArgs(1, 4, 8)), None) == -1  # null operands
+    assert lib.sd_conv4_backward_scratch_bytes(2, 130, 96) >= 2 * 3 * 96 * 4 * 4
+    assert lib.sd_kda_gate_backward_scratch_bytes(0, 2, 16) == 0
+    assert lib.sd_norm_gate_backward_scratch_bytes(300, 64) >= 2 * 64 * 4
     assert lib.sd_status_string(0) == b"ok"
     assert b"128" in lib.sd_status_string(-2)
     off, size = ctypes.c_size_t(), ctypes.c_size_t()
