@@ -565,8 +565,14 @@ int sd_kda_gate_forward(const sd_kda_gate_args* a, void* stream_) {
     p.raw = reinterpret_cast<const __nv_bfloat16*>(a->raw);
     p.A = a->log_rate; p.bias = a->bias; p.out = a->log_decay;
     const long long total = a->rows * a->H * a->r;
-    const unsigned blocks = (unsigned)((total + 256 * 8 - 1) / (256 * 8));
-    k_kda_gate_fwd<<<blocks ? blocks : 1, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
+    const bool vec = (a->r & 7) == 0 && ((reinterpret_cast<uintptr_t>(a->raw) | reinterpret_cast<uintptr_t>(a->bias) |
+                                          reinterpret_cast<uintptr_t>(a->log_decay)) & 15) == 0;
+    long long blocks = (total + 256 * 8 - 1) / (256 * 8);
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (vec)
+        k_kda_gate_fwd_v8<<<(unsigned)(blocks ? blocks : 1), 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
+    else
+        k_kda_gate_fwd<<<(unsigned)(blocks ? blocks : 1), 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
     return launch_status();
 }
 
@@ -587,7 +593,17 @@ int sd_kda_gate_backward(const sd_kda_gate_args* a, void* stream_) {
     p.dA_part = p.dbias_part + (size_t)blocks * HR;
     float* dA_cols = p.dA_part + (size_t)blocks * HR;
     p.rows_per_block = GATE_ROWS_PER_BLOCK;
-    k_kda_gate_bwd<<<dim3(blocks, (HR + 255) / 256), 256, 0, stream>>>(p);
+    const bool vec = (a->r & 7) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(a->raw) | reinterpret_cast<uintptr_t>(a->bias) |
+                       reinterpret_cast<uintptr_t>(a->dlog_decay) | reinterpret_cast<uintptr_t>(a->draw)) & 15) == 0;
+    if (vec) {
+        int cgb = HR / 8;   // column groups per CTA: a power of two that divides 256, or 256
+        if (cgb >= 256) cgb = 256;
+        else { int q = 1; while (q * 2 <= cgb) q *= 2; cgb = q; }
+        k_kda_gate_bwd_v8<<<dim3(blocks, (HR / 8 + cgb - 1) / cgb), 256, 0, stream>>>(p, cgb);
+    } else {
+        k_kda_gate_bwd<<<dim3(blocks, (HR + 255) / 256), 256, 0, stream>>>(p);
+    }
     k_column_sum<<<(HR + 255) / 256, 256, 0, stream>>>(p.dbias_part, blocks, HR, a->dbias);
     k_column_sum<<<(HR + 255) / 256, 256, 0, stream>>>(p.dA_part, blocks, HR, dA_cols);
     k_group_sum<<<(a->H + 63) / 64, 64, 0, stream>>>(dA_cols, a->H, a->r, a->dlog_rate);

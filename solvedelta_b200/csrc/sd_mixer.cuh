@@ -187,6 +187,30 @@ __global__ void k_kda_gate_fwd(GateParams p) {
     }
 }
 
+// Eight consecutive elements per thread (r % 8 == 0, 16-byte aligned operands).
+__global__ void __launch_bounds__(256) k_kda_gate_fwd_v8(GateParams p) {
+    const long long total8 = p.N * p.H * p.r / 8;
+    const int HR = p.H * p.r;
+    for (long long i8 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i8 < total8;
+         i8 += (long long)gridDim.x * blockDim.x) {
+        const long long i = i8 * 8;
+        const int hc = (int)(i % HR);
+        const float rate = -__expf(p.A[hc / p.r]);   // r % 8 == 0: the eight share a head
+        const uint4 raw = *reinterpret_cast<const uint4*>(p.raw + i);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const float4 b0 = *reinterpret_cast<const float4*>(p.bias + hc);
+        const float4 b1 = *reinterpret_cast<const float4*>(p.bias + hc + 4);
+        const float2 f0 = __bfloat1622float2(h[0]), f1 = __bfloat1622float2(h[1]);
+        const float2 f2 = __bfloat1622float2(h[2]), f3 = __bfloat1622float2(h[3]);
+        *reinterpret_cast<float4*>(p.out + i) =
+            make_float4(rate * softplus_f(f0.x + b0.x), rate * softplus_f(f0.y + b0.y),
+                        rate * softplus_f(f1.x + b0.z), rate * softplus_f(f1.y + b0.w));
+        *reinterpret_cast<float4*>(p.out + i + 4) =
+            make_float4(rate * softplus_f(f2.x + b1.x), rate * softplus_f(f2.y + b1.y),
+                        rate * softplus_f(f3.x + b1.z), rate * softplus_f(f3.y + b1.w));
+    }
+}
+
 // blockIdx.x = block of rows, blockIdx.y = block of 256 (h, c) columns; one column per thread.
 __global__ void __launch_bounds__(256) k_kda_gate_bwd(GateParams p) {
     const int hc = blockIdx.y * 256 + threadIdx.x, HR = p.H * p.r;
@@ -210,6 +234,70 @@ __global__ void __launch_bounds__(256) k_kda_gate_bwd(GateParams p) {
     p.dA_part[(long long)blockIdx.x * HR + hc] = sum_a;  // summed over c on the host side of the ABI
 }
 
+// Eight consecutive columns per thread (H*r % 8 == 0, r % 8 == 0).  blockDim = 256 threads =
+// cgb column groups x (256 / cgb) row lanes; blockIdx.x = block of rows, blockIdx.y = block of
+// column groups.  Row lanes are summed through shared memory in a fixed order.
+__global__ void __launch_bounds__(256) k_kda_gate_bwd_v8(GateParams p, int cgb) {
+    __shared__ float s_part[256 * 16];
+    const int HR = p.H * p.r;
+    const int cg = threadIdx.x % cgb, lane = threadIdx.x / cgb, lanes = 256 / cgb;
+    const int hc = (blockIdx.y * cgb + cg) * 8;
+    const bool live = hc < HR;
+    float sb[8], sa[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sb[e] = sa[e] = 0.f;
+    if (live) {
+        const float rate = -__expf(p.A[hc / p.r]);
+        const float4 b0 = *reinterpret_cast<const float4*>(p.bias + hc);
+        const float4 b1 = *reinterpret_cast<const float4*>(p.bias + hc + 4);
+        const float bias[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        const long long n0 = (long long)blockIdx.x * p.rows_per_block;
+        const long long n1 = (n0 + p.rows_per_block < p.N) ? n0 + p.rows_per_block : p.N;
+#pragma unroll 2
+        for (long long n = n0 + lane; n < n1; n += lanes) {
+            const long long i = n * HR + hc;
+            const uint4 raw = *reinterpret_cast<const uint4*>(p.raw + i);
+            const float4 g0 = *reinterpret_cast<const float4*>(p.dout + i);
+            const float4 g1 = *reinterpret_cast<const float4*>(p.dout + i + 4);
+            const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            float dz[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float2 f = __bfloat1622float2(h[e >> 1]);
+                const float z = ((e & 1) ? f.y : f.x) + bias[e];
+                const float sig = 1.f / (1.f + __expf(-z));
+                dz[e] = g[e] * rate * sig;
+                sb[e] += dz[e];
+                sa[e] += g[e] * rate * softplus_f(z);
+            }
+            uint4 outv;
+            __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&outv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] = __floats2bfloat162_rn(dz[2 * e], dz[2 * e + 1]);
+            *reinterpret_cast<uint4*>(p.draw + i) = outv;
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        s_part[threadIdx.x * 16 + e] = sb[e];
+        s_part[threadIdx.x * 16 + 8 + e] = sa[e];
+    }
+    __syncthreads();
+    if (lane == 0 && live) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            float tb = 0.f, ta = 0.f;
+            for (int l = 0; l < lanes; ++l) {
+                tb += s_part[(l * cgb + cg) * 16 + e];
+                ta += s_part[(l * cgb + cg) * 16 + 8 + e];
+            }
+            p.dbias_part[(long long)blockIdx.x * HR + hc + e] = tb;
+            p.dA_part[(long long)blockIdx.x * HR + hc + e] = ta;
+        }
+    }
+}
+
 // ---- sigmoid-gated RMSNorm over rows of width V <= 128 -------------------------
 struct NormParams {
     long long N;  // rows
@@ -226,27 +314,56 @@ struct NormParams {
     int rows_per_block;
 };
 
+// Eight channels of a BF16 row starting at c0; channels >= V read as zero.  One 16-byte
+// access when V is a multiple of eight (rows then start on 16-byte boundaries).
+__device__ __forceinline__ void norm_load8(const __nv_bfloat16* row, int c0, int V, bool live, float (&x)[8]) {
+    if ((V & 7) == 0) {
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (live && c0 < V) raw = *reinterpret_cast<const uint4*>(row + c0);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h[e]);
+            x[2 * e] = f.x;
+            x[2 * e + 1] = f.y;
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = (live && c0 + e < V) ? __bfloat162float(row[c0 + e]) : 0.f;
+    }
+}
+__device__ __forceinline__ void norm_store8(__nv_bfloat16* row, int c0, int V, bool live, const float (&x)[8]) {
+    if (!live || c0 >= V) return;
+    if ((V & 7) == 0) {
+        uint4 raw;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(x[2 * e], x[2 * e + 1]);
+        *reinterpret_cast<uint4*>(row + c0) = raw;
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            if (c0 + e < V) row[c0 + e] = __float2bfloat16_rn(x[e]);
+    }
+}
+
 // 16 lanes per row, 8 channels per lane; 256 threads = 16 rows at a time.
 __global__ void __launch_bounds__(256) k_norm_gate_fwd(NormParams p) {
     const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
     for (long long base = (long long)blockIdx.x * 16; base < p.N; base += (long long)gridDim.x * 16) {
         const long long row = base + lr;
         const bool live = row < p.N;
-        float x[8], g[8];
+        float x[8], g[8], y[8];
         float ss = 0.f;
+        norm_load8(p.x + row * p.V, c0, p.V, live, x);
+        norm_load8(p.gate + row * p.V, c0, p.V, live, g);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const bool ok = live && c0 + e < p.V;
-            x[e] = ok ? __bfloat162float(p.x[row * p.V + c0 + e]) : 0.f;
-            g[e] = ok ? __bfloat162float(p.gate[row * p.V + c0 + e]) : 0.f;
-            ss = fmaf(x[e], x[e], ss);
-        }
+        for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
         ss = row_sum16(ss);
         const float rstd = rsqrtf(ss / p.V + p.eps);
 #pragma unroll
-        for (int e = 0; e < 8; ++e)
-            if (live && c0 + e < p.V)
-                p.out[row * p.V + c0 + e] = __float2bfloat16_rn(x[e] * rstd * p.w[c0 + e] * sigmoidf_(g[e]));
+        for (int e = 0; e < 8; ++e) y[e] = (c0 + e < p.V) ? x[e] * rstd * p.w[c0 + e] * sigmoidf_(g[e]) : 0.f;
+        norm_store8(p.out + row * p.V, c0, p.V, live, y);
     }
 }
 
@@ -261,14 +378,11 @@ __global__ void __launch_bounds__(256) k_norm_gate_bwd(NormParams p) {
         const bool live = row < n1;
         float x[8], g[8], dy[8];
         float ss = 0.f;
+        norm_load8(p.x + row * p.V, c0, p.V, live, x);
+        norm_load8(p.gate + row * p.V, c0, p.V, live, g);
+        norm_load8(p.dout + row * p.V, c0, p.V, live, dy);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const bool ok = live && c0 + e < p.V;
-            x[e] = ok ? __bfloat162float(p.x[row * p.V + c0 + e]) : 0.f;
-            g[e] = ok ? __bfloat162float(p.gate[row * p.V + c0 + e]) : 0.f;
-            dy[e] = ok ? __bfloat162float(p.dout[row * p.V + c0 + e]) : 0.f;
-            ss = fmaf(x[e], x[e], ss);
-        }
+        for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
         ss = row_sum16(ss);
         const float rstd = rsqrtf(ss / p.V + p.eps);
         // y = xn * w * s with xn = x rstd, s = sigmoid(g)
@@ -284,13 +398,11 @@ __global__ void __launch_bounds__(256) k_norm_gate_bwd(NormParams p) {
             g[e] = dy[e] * xn * wv * s * (1.f - s);  // d gate
         }
         dot = row_sum16(dot) / p.V;
+        float dx[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            if (live && c0 + e < p.V) {
-                p.dx[row * p.V + c0 + e] = __float2bfloat16_rn((dxn[e] - x[e] * rstd * dot) * rstd);
-                p.dgate[row * p.V + c0 + e] = __float2bfloat16_rn(g[e]);
-            }
-        }
+        for (int e = 0; e < 8; ++e) dx[e] = (dxn[e] - x[e] * rstd * dot) * rstd;
+        norm_store8(p.dx + row * p.V, c0, p.V, live, dx);
+        norm_store8(p.dgate + row * p.V, c0, p.V, live, g);
     }
 #pragma unroll
     for (int e = 0; e < 8; ++e) s_dw[lr][c0 + e] = dw[e];
