@@ -383,6 +383,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
     cp_commit();
     async_bstate(b_dS, bstate_ptr(p.dSeCk, ch.gi));
     cp_commit();
+    // what the diagonal sweeps and the per-token reverse read from HBM much later
+    prefetch_region(panel_ptr(p.Dprim, ch.gi), CL * DP * 4);
+    prefetch_region(panel_ptr(p.Delta, ch.gi), CL * DP * 4);
+    prefetch_region(bpanel_ptr(p.Chi, ch.gi), CL * DP * 2);
+    prefetch_region(bpanel_ptr(p.Ee, ch.gi), CL * DP * 2);
+    prefetch_rows(p.u, ch, 2, p.g.r * 2);
+    prefetch_rows(p.k, ch, 2, p.g.r * 2);
+    prefetch_rows(p.q, ch, 2, p.g.r * 2);
+    prefetch_rows(p.er, ch, 2, p.g.r * 2);
+    prefetch_rows(p.wr, ch, 2, p.g.V * 2);
+    prefetch_rows(p.v, ch, 2, p.g.V * 2);
     block_betas(s_beta, fG);
     cp_wait<3>();
     __syncthreads();

@@ -204,6 +204,28 @@ __device__ __forceinline__ void store8_bf16(void* base, const Geometry& g, const
     }
 }
 
+// ---- L2 prefetch of what a later phase of the same CTA reads from HBM --------
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+// a dense region of `bytes` bytes (128-byte lines), all threads of the CTA
+__device__ __forceinline__ void prefetch_region(const void* base, int bytes) {
+    const char* b = reinterpret_cast<const char*>(base);
+    for (int off = threadIdx.x * 128; off < bytes; off += NTHREADS * 128) prefetch_l2(b + off);
+}
+// the CL token rows of a strided operand chunk (row_bytes per row)
+__device__ __forceinline__ void prefetch_rows(const Operand& op, const Chunk& ch, int elem_bytes, int row_bytes) {
+    const int lines = (row_bytes + 127) / 128;
+    for (int idx = threadIdx.x; idx < CL * lines; idx += NTHREADS) {
+        const int i = idx / lines, l = idx - i * lines;
+        if (i < ch.nvalid) {
+            const char* row = reinterpret_cast<const char*>(op.ptr) +
+                              (ch.b * op.sb + (long long)(ch.t0 + i) * op.st + ch.hh * op.sh) * elem_bytes;
+            prefetch_l2(row + l * 128);
+        }
+    }
+}
+
 // ---- dense panel movement -------------------------------------------------
 __device__ __forceinline__ void g2s_panel(float* sm, const float* g) {
     for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += NTHREADS) {
