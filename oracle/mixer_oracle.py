@@ -53,6 +53,52 @@ def conv4_silu_backward(dy, weight, saved, dfinal=None):
     return dext[:, 3:], dw, dext[:, :3].transpose(0, 2, 1).copy()
 
 
+def conv4_silu_masked_forward(x, weight, state=None, valid_mask=None, reset_mask=None):
+    """The masked token loop of causallsso/model.py:146-164: a reset (on a valid token) zeroes the
+    state first, an invalid token yields zero and leaves the state untouched.  Returns
+    (y, final_state, saved)."""
+    x = np.asarray(x, dtype=np.float64)
+    B, T, D = x.shape
+    state = np.zeros((B, D, 3)) if state is None else np.asarray(state, dtype=np.float64).copy()
+    valid = np.ones((B, T), bool) if valid_mask is None else np.asarray(valid_mask, bool)
+    reset = (np.zeros((B, T), bool) if reset_mask is None else np.asarray(reset_mask, bool)) & valid
+    y = np.zeros_like(x)
+    windows, pres = [], []
+    for t in range(T):
+        state = np.where(reset[:, t, None, None], 0.0, state)
+        window = np.concatenate([state, x[:, t, :, None]], axis=-1)      # [B,D,4]
+        pre = (window * weight[None]).sum(-1)
+        y[:, t] = np.where(valid[:, t, None], pre * _sigmoid(pre), 0.0)
+        state = np.where(valid[:, t, None, None], window[..., 1:], state)
+        windows.append(window)
+        pres.append(pre)
+    return y, state, (windows, pres, valid, reset)
+
+
+def conv4_silu_masked_backward(dy, weight, saved, dfinal=None):
+    """Adjoint of the masked loop.  Returns (dx, dweight, dstate)."""
+    windows, pres, valid, reset = saved
+    dy = np.asarray(dy, dtype=np.float64)
+    B, T, D = dy.shape
+    dstate = np.zeros((B, D, 3)) if dfinal is None else np.asarray(dfinal, dtype=np.float64).copy()
+    dx = np.zeros_like(dy)
+    dw = np.zeros_like(weight)
+    for t in range(T - 1, -1, -1):
+        v = valid[:, t, None, None]
+        # state_after = valid ? window[..., 1:] : state_before
+        dwindow = np.zeros((B, D, 4))
+        dwindow[..., 1:] = np.where(v, dstate, 0.0)
+        dstate_before = np.where(v, 0.0, dstate)
+        s = _sigmoid(pres[t])
+        dpre = np.where(valid[:, t, None], dy[:, t], 0.0) * s * (1 + pres[t] * (1 - s))
+        dwindow += dpre[..., None] * weight[None]
+        dw += (dpre[..., None] * windows[t]).sum(0)
+        dx[:, t] = dwindow[..., 3]
+        dstate_before = dstate_before + dwindow[..., :3]
+        dstate = np.where(reset[:, t, None, None], 0.0, dstate_before)
+    return dx, dw, dstate
+
+
 def kda_gate_forward(raw, log_rate, bias):
     """-exp(log_rate[h]) * softplus(raw + bias[h,c]); raw [...,H,r].  model.py:383-390."""
     H, r = raw.shape[-2:]
@@ -113,7 +159,7 @@ class MixerOracle:
     def _piece(self, row, i):
         return row[..., self.offsets[i]:self.offsets[i + 1]]
 
-    def forward(self, x, conv_state=None, operator_state=None):
+    def forward(self, x, conv_state=None, operator_state=None, valid_mask=None, reset_mask=None):
         p, H, r, V = self.p, self.H, self.r, self.V
         x = np.asarray(x, dtype=np.float64)
         B, T, _ = x.shape
@@ -124,7 +170,11 @@ class MixerOracle:
         c = {"x": x, "row": row}
         Dc = sum(self.sizes[:3])
         if self.conv:
-            qkv, final_conv, c["conv_saved"] = conv4_silu_forward(row[..., :Dc], p["conv_weight"], conv_state)
+            if valid_mask is None and reset_mask is None:
+                qkv, final_conv, c["conv_saved"] = conv4_silu_forward(row[..., :Dc], p["conv_weight"], conv_state)
+            else:
+                qkv, final_conv, c["conv_saved"] = conv4_silu_masked_forward(
+                    row[..., :Dc], p["conv_weight"], conv_state, valid_mask, reset_mask)
         else:
             pre = row[..., :Dc]
             qkv = pre * _sigmoid(pre)
@@ -145,7 +195,8 @@ class MixerOracle:
         log_decay, c["gate_saved"] = kda_gate_forward(araw, p["associative_log_rate"], p["associative_decay_bias"])
         gamma = _sigmoid(graw + p["geometry_write_bias"].reshape(1, 1, H))
         erase, write = _sigmoid(er), _sigmoid(wr)
-        o, fin = orc.forward(u, h, q, k, v, log_decay, erase, write, gamma, initial_state=operator_state)
+        o, fin = orc.forward(u, h, q, k, v, log_decay, erase, write, gamma, initial_state=operator_state,
+                             valid_mask=valid_mask, reset_mask=reset_mask)
         o = self.rnd(o)
         y, c["norm_saved"] = norm_gate_forward(o, gate, p["output_norm.weight"], self.eps)
         y = self.rnd(y)
@@ -153,7 +204,8 @@ class MixerOracle:
         if "output_proj.bias" in p:
             out = out + p["output_proj.bias"]
         c.update(q=q, k=k, v=v, u=u, h=h, log_decay=log_decay, gamma=gamma, erase=erase, write=write, y=y,
-                 dhid=dhid, ghid=ghid, operator_state=operator_state, B=B, T=T)
+                 dhid=dhid, ghid=ghid, operator_state=operator_state, B=B, T=T,
+                 masks=(valid_mask, reset_mask))
         self.cache = c
         return out, fin, final_conv
 
@@ -180,7 +232,8 @@ class MixerOracle:
         self.do = do
         if operator_grads is None:
             og = orc.backward(c["u"], c["h"], c["q"], c["k"], c["v"], c["log_decay"], c["erase"], c["write"],
-                              c["gamma"], do, dC_T=dC_T, dS_T=dS_T, initial_state=c["operator_state"])
+                              c["gamma"], do, dC_T=dC_T, dS_T=dS_T, initial_state=c["operator_state"],
+                              valid_mask=c["masks"][0], reset_mask=c["masks"][1])
             og["erase_raw"] = og["erase"] * c["erase"] * (1 - c["erase"])
             og["write_raw"] = og["write"] * c["write"] * (1 - c["write"])
         else:
@@ -212,8 +265,9 @@ class MixerOracle:
         Dc = dqkv.shape[-1]
         dconv_state = None
         if self.conv:
-            drow[..., :Dc], g["conv_weight"], dconv_state = conv4_silu_backward(
-                dqkv, p["conv_weight"], c["conv_saved"], dconv_T)
+            unmasked = c["masks"][0] is None and c["masks"][1] is None
+            conv_vjp = conv4_silu_backward if unmasked else conv4_silu_masked_backward
+            drow[..., :Dc], g["conv_weight"], dconv_state = conv_vjp(dqkv, p["conv_weight"], c["conv_saved"], dconv_T)
         else:
             pre = c["pre"]
             s = _sigmoid(pre)

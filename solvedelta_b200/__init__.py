@@ -8,7 +8,7 @@ sm_100a CUDA kernels behind a C ABI (include/solvedelta_b200.h).
 """
 from ._lib import build, load
 from .config import SolveDeltaConfig
-from .mixer_ops import conv4_silu, kda_decay_gate, rms_norm_gated
+from .mixer_ops import conv4_silu, conv4_silu_segmented, kda_decay_gate, rms_norm_gated
 from .model import RMSNormGated, SolveDelta, SolveDeltaLayerState
 from .packing import PackedSegments, build_packed_segments, pack_tokens, unpack_tokens
 from .ops import (
@@ -25,6 +25,7 @@ __all__ = [
     "SolveDeltaLayerState",
     "RMSNormGated",
     "conv4_silu",
+    "conv4_silu_segmented",
     "kda_decay_gate",
     "rms_norm_gated",
     "SolveDeltaState",

@@ -85,6 +85,55 @@ def conv4_silu(x: torch.Tensor, weight: torch.Tensor, initial_state: Optional[to
     return _Conv4Silu.apply(x, weight, initial_state, return_final_state)
 
 
+def conv4_silu_segmented(x: torch.Tensor, weight: torch.Tensor, plan, initial_state: Optional[torch.Tensor] = None,
+                         return_final_state: bool = False) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """Masked / reset batches: the conv of causallsso/model.py:146-164 with masks, run as one batch
+    of reset-free segments (plan from ``build_packed_segments``).  Invalid tokens give zero output and
+    leave the state untouched, a reset token starts from the zero state, the first segment of a batch
+    row continues ``initial_state`` unless it opens with a reset; the returned state of a row holds its
+    last three valid inputs since the last reset (older slots show the carried state or zeros through).
+    Host-side index plumbing around ``conv4_silu`` (upstream does the same around causal_conv1d,
+    model.py:166-273)."""
+    from .packing import pack_tokens, unpack_tokens
+
+    _require_bf16_cuda("x", x)
+    batch, length, channels = x.shape
+    if (plan.batch, plan.length) != (batch, length):
+        raise ValueError("packed segment plan does not match the conv input")
+    if initial_state is not None and initial_state.shape != (batch, channels, 3):
+        raise ValueError("conv initial state must have shape [B,D,3]")
+    if plan.num_tokens == 0:
+        output = x.new_zeros(batch, length, channels)
+        if not return_final_state:
+            return output, None
+        return output, (initial_state if initial_state is not None else x.new_zeros(batch, channels, 3))
+    padded = plan.max_seqlen
+    position = torch.arange(plan.num_tokens, dtype=torch.long, device=x.device) - plan.cu_seqlens[plan.segment_ids]
+    destination = plan.segment_ids * padded + position
+    tokens = pack_tokens(x, plan).squeeze(0)
+    rows = tokens.new_zeros(plan.num_segments * padded, channels).index_copy(0, destination, tokens)
+    rows = rows.view(plan.num_segments, padded, channels)
+    segment_initial = None
+    if initial_state is not None:
+        carried = initial_state.to(torch.bfloat16).index_select(0, plan.segment_batch)
+        segment_initial = torch.where(plan.use_initial[:, None, None], carried, torch.zeros_like(carried))
+    segment_out, _ = conv4_silu(rows, weight, segment_initial, False)
+    flat = segment_out.reshape(plan.num_segments * padded, channels)
+    output = unpack_tokens(flat.index_select(0, destination).unsqueeze(0), plan)
+    if not return_final_state:
+        return output, None
+    with torch.no_grad():
+        # state of a segment = the three inputs before position len in [carried state | segment tokens]
+        start = segment_initial if segment_initial is not None else rows.new_zeros(plan.num_segments, channels, 3)
+        extended = torch.cat((start.transpose(1, 2), rows.detach()), dim=1)            # [S, 3 + padded, D]
+        take = plan.segment_lengths.long()[:, None] + torch.arange(3, device=x.device)[None, :]
+        final = extended.gather(1, take[:, :, None].expand(-1, -1, channels)).transpose(1, 2)  # [S, D, 3]
+        chosen = final.index_select(0, plan.last_segment.clamp_min(0))
+        base = initial_state.to(torch.bfloat16) if initial_state is not None else torch.zeros_like(chosen)
+        state = torch.where((plan.last_segment >= 0)[:, None, None], chosen, base).contiguous()
+    return output, state
+
+
 class _KdaGate(torch.autograd.Function):
     @staticmethod
     def forward(ctx, raw, log_rate, bias):
@@ -175,4 +224,4 @@ def rms_norm_gated(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, ep
     return _NormGate.apply(x, gate, weight, eps)
 
 
-__all__ = ["conv4_silu", "kda_decay_gate", "rms_norm_gated"]
+__all__ = ["conv4_silu", "conv4_silu_segmented", "kda_decay_gate", "rms_norm_gated"]

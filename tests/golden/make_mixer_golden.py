@@ -32,6 +32,15 @@ CASES = {
     "mixer_small_state": (dict(hidden_size=64, num_heads=2, head_k_dim=16, head_v_dim=16), 2, 7, True),
     "mixer_noconv_bias": (dict(hidden_size=48, num_heads=3, head_k_dim=8, head_v_dim=16,
                                use_short_conv=False, bias=True), 1, 9, False),
+    # valid / reset masks (pattern of upstream tests/core/test_rebuild_semantics.py:319-329 stretched to
+    # 12 tokens, plus a row that opens invalid and a one-token segment), carried states
+    "mixer_masks_state": (dict(hidden_size=64, num_heads=2, head_k_dim=16, head_v_dim=16), 3, 12, True),
+}
+
+MASKS = {
+    "mixer_masks_state": (
+        [[1, 1, 0, 1, 1, 1, 0, 0, 1, 1, 1, 1], [0, 0, 1, 1, 1, 1, 1, 0, 1, 1, 0, 0], [0] * 12],
+        [[0, 0, 0, 1, 0, 0, 0, 1, 0, 0, 1, 1], [0, 0, 1, 0, 0, 0, 0, 0, 0, 1, 0, 0], [0] * 12]),
 }
 
 
@@ -60,13 +69,18 @@ def make_case(name, SolveDelta, SolveDeltaConfig, SolveDeltaLayerState, SolveDel
         record["cfg_" + key] = np.asarray(value)
     record["cfg_norm_eps"] = np.asarray(config.norm_eps)
     leaves = {"x": x}
+    masks = {}
+    if name in MASKS:
+        valid, reset = (torch.tensor(m, dtype=torch.bool) for m in MASKS[name])
+        masks = dict(valid_mask=valid, reset_mask=reset)
+        record["valid_mask"], record["reset_mask"] = valid.numpy(), reset.numpy()
     if stateful:
         c0 = (0.2 * torch.randn(batch, heads, rank, rank, dtype=torch.float64)).requires_grad_()
         s0 = (0.5 * torch.randn(batch, heads, rank, vdim, dtype=torch.float64)).requires_grad_()
         conv0 = torch.randn(batch, 2 * heads * rank + heads * vdim, 3, dtype=torch.float64).requires_grad_()
         leaves.update(C0=c0, S0=s0, conv0=conv0)
         initial = SolveDeltaLayerState(SolveDeltaState(c0, s0), conv0)
-        out, final = module(x, initial_state=initial, return_final_state=True)
+        out, final = module(x, initial_state=initial, return_final_state=True, **masks)
         cot = {"dout": torch.randn_like(out), "dC_T": torch.randn_like(final.operator.predictor),
                "dS_T": torch.randn_like(final.operator.S), "dconv_T": torch.randn_like(final.conv)}
         loss = ((out * cot["dout"]).sum() + (final.operator.predictor * cot["dC_T"]).sum()
@@ -74,7 +88,7 @@ def make_case(name, SolveDelta, SolveDeltaConfig, SolveDeltaLayerState, SolveDel
         record.update(C_T=final.operator.predictor.detach().numpy(), S_T=final.operator.S.detach().numpy(),
                       conv_T=final.conv.detach().numpy())
     else:
-        out = module(x)
+        out = module(x, **masks)
         cot = {"dout": torch.randn_like(out)}
         loss = (out * cot["dout"]).sum()
     loss.backward()

@@ -257,6 +257,46 @@ def test_mixer_module_state_continuation(monkeypatch):
     assert max_rel(_np(fin_split.operator.S), _np(fin_whole.operator.S)) <= 5e-3
 
 
+def test_mixer_module_masks_and_resets(monkeypatch):
+    """valid / reset masks with carried conv and operator states (upstream mask semantics,
+    causallsso/model.py:146-164 and reference.py:156-227), against the masked checker."""
+    g = load_mixer_golden("mixer_masks_state")
+    module, checker = _module_and_checker(golden_config(g), golden_params(g))
+    x, dout = _bf16(g["in_x"]), _bf16(g["dout"])
+    conv0 = _bf16(g["in_conv0"])
+    C0, S0 = torch.as_tensor(g["in_C0"]).float(), torch.as_tensor(g["in_S0"]).float()
+    dC, dS = torch.as_tensor(g["dC_T"]).float(), torch.as_tensor(g["dS_T"]).float()
+    valid, reset = torch.as_tensor(g["valid_mask"]), torch.as_tensor(g["reset_mask"])
+    xg = x.cuda().requires_grad_()
+    c0g, s0g, cvg = C0.cuda().requires_grad_(), S0.cuda().requires_grad_(), conv0.cuda().requires_grad_()
+    out, fin = module(xg, initial_state=SolveDeltaLayerState(SolveDeltaState(c0g, s0g), cvg),
+                      valid_mask=valid.cuda(), reset_mask=reset.cuda(), return_final_state=True)
+    loss = ((out.float() * dout.cuda().float()).sum() + (fin.operator.predictor * dC.cuda()).sum()
+            + (fin.operator.S * dS.cuda()).sum())
+    loss.backward()
+    oo, fo, conv_T = checker.forward(_np(x), conv_state=_np(conv0), operator_state=(_np(C0), _np(S0)),
+                                     valid_mask=g["valid_mask"], reset_mask=g["reset_mask"])
+    assert max_rel(_np(out), oo) <= TOL
+    # invalid tokens: the operator and the conv contribute nothing, the output is the bias-free projection of zero
+    assert float(out[~valid.cuda()].abs().max()) == 0.0
+    assert max_rel(_np(fin.operator.predictor), fo[0]) <= 5e-3
+    assert max_rel(_np(fin.operator.S), fo[1]) <= 5e-3
+    assert max_rel(_np(fin.conv), conv_T) <= 1e-2
+    # a row without valid tokens hands its states through untouched
+    assert torch.equal(fin.conv[2], conv0.cuda()[2])
+    assert torch.equal(fin.operator.S[2], S0.cuda()[2])
+    dx, pg, dconv0, (dC0, dS0) = checker.backward(_np(dout), dC_T=_np(dC), dS_T=_np(dS))
+    # end-to-end gradients of the tensors whose sums do not cancel: input, states
+    assert rel_l2(_np(xg.grad), dx) <= 5e-2
+    assert max_rel(_np(c0g.grad), dC0) <= TOL
+    assert max_rel(_np(s0g.grad), dS0) <= TOL
+    assert rel_l2(_np(cvg.grad), dconv0) <= 5e-2
+    assert float(xg.grad[2].abs().max()) == 0.0
+    for name in ("in_proj.weight", "output_proj.weight", "conv_weight", "output_norm.weight"):
+        got = _np(dict(module.named_parameters())[name].grad).reshape(pg[name].shape)
+        assert rel_l2(got, pg[name]) <= 5e-2, (name, rel_l2(got, pg[name]))
+
+
 def test_mixer_module_tiny_configuration(monkeypatch):
     """The upstream CPU-runnable configuration: hidden 256, 4 heads, 64/64, B=2, T=128."""
     torch.manual_seed(5)
@@ -277,7 +317,7 @@ def test_mixer_module_tiny_configuration(monkeypatch):
     _check_backward_in_two_steps(module, checker, spy, xg, dout)
 
 
-def test_mixer_module_rejects_cpu_and_masks():
+def test_mixer_module_rejects_cpu_inputs():
     module = SolveDelta(SolveDeltaConfig(hidden_size=64, num_heads=2, head_k_dim=16, head_v_dim=16)).cuda()
     with pytest.raises(TypeError):
         module(torch.zeros(1, 4, 64))

@@ -9,7 +9,7 @@ import pytest
 from tests.helpers import max_rel
 from tests.mixer_helpers import load_mixer_golden, oracle_from_golden
 
-CASES = ["mixer_small", "mixer_small_state", "mixer_noconv_bias"]
+CASES = ["mixer_small", "mixer_small_state", "mixer_noconv_bias", "mixer_masks_state"]
 TOL = 5e-6
 
 
@@ -20,7 +20,8 @@ def test_mixer_oracle_matches_upstream(name):
     stateful = "in_C0" in g
     out, fin, conv_T = orc.forward(
         g["in_x"], conv_state=g.get("in_conv0"),
-        operator_state=(g["in_C0"], g["in_S0"]) if stateful else None)
+        operator_state=(g["in_C0"], g["in_S0"]) if stateful else None,
+        valid_mask=g.get("valid_mask"), reset_mask=g.get("reset_mask"))
     assert max_rel(out, g["out"]) < TOL
     if stateful:
         assert max_rel(fin[0], g["C_T"]) < TOL
