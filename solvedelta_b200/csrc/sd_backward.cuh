@@ -340,7 +340,7 @@ __device__ __forceinline__ void sources_bwd_rows(const BwdParams& p, const Chunk
 // The four results stay in shared memory (over operands that are no longer
 // needed) and the per-token reverse of the sources runs on them in the same CTA.
 constexpr size_t EXT_PAIR_BWD_SMEM =
-    6 * BSLOT_BYTES + 2 * BSTATE_BYTES + 2 * BMAT_BYTES + NBLK * DP * sizeof(float);
+    6 * BSLOT_BYTES + 2 * BSTATE_BYTES + 2 * BMAT_BYTES + (NBLK * DP + 16) * sizeof(float);
 
 // acc rows (i = r0+g, r0+g+8) x columns scaled by exp(x_i - ref) with x, ref rows of the prefix panel
 template <int NTW, class FX>
@@ -367,6 +367,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
     bf16* b_daqd = b_dS + DP * LDB;
     bf16* b_daed = b_daqd + BMAT_ELEMS;
     float* s_beta = reinterpret_cast<float*>(b_daed + BMAT_ELEMS);
+    int* s_fastw = reinterpret_cast<int*>(s_beta + NBLK * DP);
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const float* gG = panel_ptr(p.Gp, ch.gi);
     auto fG = [&](int i, int c) { return gG[i * DP + c]; };
@@ -394,7 +395,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
     prefetch_rows(p.er, ch, 2, p.g.r * 2);
     prefetch_rows(p.wr, ch, 2, p.g.V * 2);
     prefetch_rows(p.v, ch, 2, p.g.V * 2);
-    block_betas(s_beta, fG);
+    block_decay_tables(s_beta, nullptr, s_fastw, fG);
     cp_wait<3>();
     __syncthreads();
     SD_PHASE(p.g, ph);
@@ -421,17 +422,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
     SD_PHASE(p.g, ph);
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
     const int I = r0 / BT;
-    // exp(G_i - Gprev_I) for the accumulator element pair (i, j), (i, j + 1)
+    // a fast diagonal block is one more Horner step, and the sum is then referenced to the other end of the block
+    const bool fast = block_is_fast(s_fastw, I);
+    // exp(G_i - G_ref) for the accumulator element pair (i, j), (i, j + 1); ref < 0: the chunk start
     auto row_factor = [&](int i, int j) {
+        const int ref = fast ? r0 + BT - 1 : r0 - 1;
         const float2 G = *reinterpret_cast<const float2*>(gG + i * DP + j);
         float2 Gp = make_float2(0.f, 0.f);
-        if (r0) Gp = *reinterpret_cast<const float2*>(gG + (r0 - 1) * DP + j);
+        if (ref >= 0) Gp = *reinterpret_cast<const float2*>(gG + ref * DP + j);
         return make_float2(__expf(G.x - Gp.x), __expf(G.y - Gp.y));
     };
-    // exp(Gend_J - G_j) for rows of block J = I of the anti-causal result
+    // exp(G_ref - G_j) for rows of block J = I of the anti-causal result
     auto col_factor = [&](int i, int j) {
+        const int ref = fast ? r0 - 1 : r0 + BT - 1;
         const float2 G = *reinterpret_cast<const float2*>(gG + i * DP + j);
-        const float2 Ge = *reinterpret_cast<const float2*>(gG + (r0 + BT - 1) * DP + j);
+        float2 Ge = make_float2(0.f, 0.f);
+        if (ref >= 0) Ge = *reinterpret_cast<const float2*>(gG + ref * DP + j);
         return make_float2(__expf(Ge.x - G.x), __expf(Ge.y - G.y));
     };
     {
@@ -440,7 +446,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
         acc_zero<NT128>(a2);
         warp_mma_bf16<NT128, false, true>(a1, b_dy, LDB, b_S, LDB, r0, n0, 0, DP);
         warp_mma_bf16<NT128, false, true>(a2, b_dr, LDB, b_S, LDB, r0, n0, 0, DP);
-        for (int J = 0; J < I; ++J) {
+        for (int J = 0; J < I + (fast ? 1 : 0); ++J) {
             scale_acc<NT128>(a1, s_beta + J * DP, n0);
             scale_acc<NT128>(a2, s_beta + J * DP, n0);
             warp_mma_bf16<NT128, false, false>(a1, b_daqd, LDM, b_dc, LDB, r0, n0, J * BT, J * BT + BT);
@@ -455,8 +461,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
     {
         float acc[NT128][4];
         acc_zero<NT128>(acc);
-        for (int K = NBLK - 1; K > I; --K) {
-            if (K < NBLK - 1) scale_acc<NT128>(acc, s_beta + K * DP, n0);
+        bool first = true;
+        for (int K = NBLK - 1; K >= I + (fast ? 0 : 1); --K) {
+            if (!first) scale_acc<NT128>(acc, s_beta + K * DP, n0);
+            first = false;
             warp_mma_bf16<NT128, true, false>(acc, b_daqd, LDM, b_xr, LDB, r0, n0, K * BT, K * BT + BT);
             warp_mma_bf16<NT128, true, false>(acc, b_daed, LDM, b_er, LDB, r0, n0, K * BT, K * BT + BT);
         }
@@ -488,7 +496,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
-    {   // diagonal blocks, one thread per (channel, block): d, chi, -e themselves from HBM (L2)
+    if (!block_is_fast(s_fastw, threadIdx.x >> 7)) {
+        // diagonal blocks that are not fast, one thread per (channel, block): d, chi, -e themselves from HBM (L2)
         const float* gd = panel_ptr(p.Dprim, ch.gi);
         const bf16* gChi = bpanel_ptr(p.Chi, ch.gi);
         const bf16* gEe = bpanel_ptr(p.Ee, ch.gi);
@@ -525,7 +534,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
 // dAqk and t_u are block-centred (tensor cores off the diagonal blocks, direct
 // evaluation on them); Lm = gamma N comes from the pair matrix the forward pass kept.
 constexpr size_t PRIMAL_BWD_SMEM = 7 * BSLOT_BYTES + BSTATE_BYTES + 2 * BMAT_BYTES + MAT_BYTES +
-                                   (3 * CL + 4 * CL + NBLK * DP) * sizeof(float) + 3 * DP * sizeof(bf16);
+                                   (3 * CL + 4 * CL + NBLK * DP + 16) * sizeof(float) +
+                                   (3 + NBLK) * DP * sizeof(bf16);
 
 template <bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
@@ -550,7 +560,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     float* s_gam = s_ru + CL;
     float* s_dot = s_gam + CL;          // [CL][4] partial dots of the norm VJP
     float* s_beta = s_dot + 4 * CL;
-    bf16* s_Mb = reinterpret_cast<bf16*>(s_beta + NBLK * DP);
+    int* s_fastw = reinterpret_cast<int*>(s_beta + NBLK * DP);
+    bf16* s_Mb = reinterpret_cast<bf16*>(s_fastw + 16);
+    bf16* s_ibeta_b = s_Mb + 3 * DP;
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r;
     const float* gG = panel_ptr(p.Gp, ch.gi);
@@ -561,7 +573,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     async_panel_f32(s_G, gG);
     cp_commit();
     load_gamma(p.gam, ch, s_gam);
-    block_betas(s_beta, fG);
+    block_decay_tables(s_beta, nullptr, s_fastw, fG);
+    {   // BF16 copy of 1 / beta for the fast diagonal pair blocks (0 where the block is not fast)
+        const int J = threadIdx.x >> 7, c = threadIdx.x & (DP - 1);
+        const float d = fG(BT * J + BT - 1, c) - (J ? fG(BT * J - 1, c) : 0.f);
+        s_ibeta_b[threadIdx.x] = __float2bfloat16_rn(d >= -FAST_BLOCK_NATS ? __expf(-d) : 0.f);
+    }
     pair_block_scales_bf16(s_Mb, fG);
     {
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
@@ -624,17 +641,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
             *reinterpret_cast<__nv_bfloat162*>(b_aqk + i * LDM + j) =
                 __floats2bfloat162_rn((j <= i) ? v0 : 0.f, (j + 1 <= i) ? v1 : 0.f);
         });
-        pair_offdiag_bf16(s_Mb, b_ddr, b_uc, [&](int i, int j, float v0, float v1) {
+        pair_blocks_bf16<false>(s_Mb, s_ibeta_b, s_fastw, b_ddr, b_uc, [&](int i, int j, float v0, float v1) {
             *reinterpret_cast<__nv_bfloat162*>(b_daqk + i * LDM + j) = __floats2bfloat162_rn(v0, v1);
         });
     }
-    {   // diagonal blocks of dAqk
+    {   // diagonal blocks of dAqk that are not fast
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8, l16 = threadIdx.x & 15;
         auto fu8 = [&](int j, float (&b)[8]) { load8_bsm(b_ur, j, c0, b); };
         auto fg8 = [&](int j, float (&Gj)[8]) { load8_smem(s_G, j, c0, Gj); };
 #pragma unroll 1
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
             const int i = balanced_row(lr, pp), i0 = i & ~(BT - 1);
+            if (block_is_fast(s_fastw, i / BT)) continue;
             float a[1][8], G[8], out[1];
             load8_smem(s_G, i, c0, G);
             load8_bpanel(gDd, i, c0, a[0]);
@@ -650,16 +668,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     float accd[NT128][4];  // dAqk^T K^  (added to dDelta_src below)
     acc_zero<NT128>(accd);
     warp_mma_bf16<NT128, true, false>(accd, b_daqk, LDM, b_kh, LDB, r0, n0, r0, CL);
-    {   // t_u off the diagonal blocks: Horner from the chunk end, then exp(Gend_J - G_j)
+    const bool fast = block_is_fast(s_fastw, r0 / BT);
+    {   // t_u: Horner from the chunk end (a fast diagonal block is its last step), then exp(G_ref - G_j)
         float acc[NT128][4];
         acc_zero<NT128>(acc);
-        for (int K = NBLK - 1; K * BT > r0; --K) {
-            if (K < NBLK - 1) scale_acc<NT128>(acc, s_beta + K * DP, n0);
+        bool first = true;
+        for (int K = NBLK - 1; K * BT >= r0 + (fast ? 0 : BT); --K) {
+            if (!first) scale_acc<NT128>(acc, s_beta + K * DP, n0);
+            first = false;
             warp_mma_bf16<NT128, true, false>(acc, b_aqk, LDM, b_ddr, LDB, r0, n0, K * BT, K * BT + BT);
         }
+        const int ref = fast ? r0 - 1 : r0 + BT - 1;
         epi_scale_store_bsm<NT128>(acc, r0, n0, b_ur, [&](int i, int j) {
             const float2 G = *reinterpret_cast<const float2*>(gG + i * DP + j);
-            const float2 Ge = *reinterpret_cast<const float2*>(gG + (r0 + BT - 1) * DP + j);
+            float2 Ge = make_float2(0.f, 0.f);
+            if (ref >= 0) Ge = *reinterpret_cast<const float2*>(gG + ref * DP + j);
             return make_float2(__expf(Ge.x - G.x), __expf(Ge.y - G.y));
         });
     }
@@ -727,18 +750,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     // every contraction that reads b_dl (Delta) is done: reuse it for dDelta_loc
     __syncthreads();
     SD_PHASE(p.g, ph);
-    {   // diagonal blocks of t_u, one thread per (channel, block); the finished panel goes to HBM
+    {   // diagonal blocks of t_u that are not fast, one thread per (channel, block); the finished panel goes to HBM
         bf16* gTu = bpanel_ptr(p.Tu, ch.gi);
-        float al[BT];
-        block_alphas(al, fG);
-        auto none = [](int, int) { return 0.f; };
-        auto sink = [](int, int, float) {};
-        diag_sweep<false, false, false, true>(
-            al, [&](int i, int i0, float (&row)[BT]) { prow16_bf16(b_aqk, LDM, i, i0, row); }, none,
-            [&](int i, int c) { return __bfloat162float(gDd[i * DP + c]); }, sink,
-            [&](int j, int c, float v) {
-                gTu[j * DP + c] = __float2bfloat16_rn(__bfloat162float(b_ur[j * LDB + c]) + v);
-            });
+        if (block_is_fast(s_fastw, threadIdx.x >> 7)) {
+            const int c = threadIdx.x & (DP - 1), j0 = (threadIdx.x >> 7) * BT;
+#pragma unroll
+            for (int k = 0; k < BT; ++k) gTu[(j0 + k) * DP + c] = b_ur[(j0 + k) * LDB + c];
+        } else {
+            float al[BT];
+            block_alphas(al, fG);
+            auto none = [](int, int) { return 0.f; };
+            auto sink = [](int, int, float) {};
+            diag_sweep<false, false, false, true>(
+                al, [&](int i, int i0, float (&row)[BT]) { prow16_bf16(b_aqk, LDM, i, i0, row); }, none,
+                [&](int i, int c) { return __bfloat162float(gDd[i * DP + c]); }, sink,
+                [&](int j, int c, float v) {
+                    gTu[j * DP + c] = __float2bfloat16_rn(__bfloat162float(b_ur[j * LDB + c]) + v);
+                });
+        }
     }
     {
         const bf16* gdd = bpanel_ptr(p.dDelta, ch.gi);
@@ -770,7 +799,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
 // log_decay.  The four contraction results and the three FP32 closure panels
 // overlay operands that are dead by then.
 constexpr size_t PRED_CLOSE_BWD_SMEM = 5 * BSLOT_BYTES + 2 * BMAT_BYTES + 3 * size_t(CL) * LDP * 4 +
-                                       (2 * CL + 4 * CL + DP + NBLK * DP) * sizeof(float) +
+                                       (2 * CL + 4 * CL + DP + NBLK * DP + 16) * sizeof(float) +
                                        6 * DP * sizeof(bf16);
 static_assert(3 * size_t(CL) * LDP * 4 >= 2 * BSTATE_BYTES, "closure panels overlay both BF16 states");
 
@@ -797,7 +826,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
     float* s_dot = s_ru + CL;    // [CL][4]
     float* s_cdc = s_dot + 4 * CL;  // [DP]
     float* s_beta = s_cdc + DP;
-    bf16* s_Mb = reinterpret_cast<bf16*>(s_beta + NBLK * DP);
+    int* s_fastw = reinterpret_cast<int*>(s_beta + NBLK * DP);
+    bf16* s_Mb = reinterpret_cast<bf16*>(s_fastw + 16);
     bf16* s_pref = s_Mb + 3 * DP;   // exp(Gprev_I) for I = 1..3: U~ = (u^ rowE) .* pref along channels
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r;
@@ -809,7 +839,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
     async_bstate(b_Ct, bstate_ptr(p.CtCkB, ch.gi));
     cp_commit();
     load_gamma(p.gam, ch, s_gam);
-    block_betas(s_beta, fG);
+    block_decay_tables(s_beta, nullptr, s_fastw, fG);
     for (int idx = threadIdx.x; idx < 3 * DP; idx += NTHREADS) {
         const int m = idx >> 7, c = idx & (DP - 1);
         s_pref[idx] = __float2bfloat16_rn(__expf(gG[((m + 1) * BT - 1) * DP + c]));
@@ -871,6 +901,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
     SD_PHASE(p.g, ph);
     const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
     const int I = r0 / BT;
+    const bool fast = block_is_fast(s_fastw, I);
     {   // residual rows and dgamma_i = sum_a dRr[i][a] (h[i][a] - (U~ Ct)[i][a] - (N Delta)[i][a])
         float acc[NT128][4];
         acc_zero<NT128>(acc);
@@ -932,12 +963,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
         // dUbar[j][c] = sum_a Delta[j][a] dCt[c][a] ; dUt[i][c] = -gamma_i sum_a dRr[i][a] Ct[c][a]
         warp_mma_bf16<NT128, false, true>(aub, b_dl, LDB, b_dC, LDB, r0, n0, 0, DP);
         warp_mma_bf16<NT128, false, true>(aut, b_dr, LDB, b_Ct, LDB, r0, n0, 0, DP);
-        for (int J = 0; J < I; ++J) {   // t_i off the diagonal blocks, Horner from the chunk start
+        // t_i: Horner from the chunk start, t_j: from the chunk end; a fast diagonal block is the last step
+        for (int J = 0; J < I + (fast ? 1 : 0); ++J) {
             if (J > 0) scale_acc<NT128>(ati, s_beta + J * DP, n0);
             warp_mma_bf16<NT128, false, false>(ati, b_dN, LDM, b_uc, LDB, r0, n0, J * BT, J * BT + BT);
         }
-        for (int K = NBLK - 1; K > I; --K) {   // t_j off the diagonal blocks, Horner from the chunk end
-            if (K < NBLK - 1) scale_acc<NT128>(atj, s_beta + K * DP, n0);
+        bool first = true;
+        for (int K = NBLK - 1; K >= I + (fast ? 0 : 1); --K) {
+            if (!first) scale_acc<NT128>(atj, s_beta + K * DP, n0);
+            first = false;
             warp_mma_bf16<NT128, true, false>(atj, b_dN, LDM, b_ur, LDB, r0, n0, K * BT, K * BT + BT);
         }
         __syncthreads();  // every contraction has read its operands: overlay the results
@@ -947,15 +981,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
             float gm = -s_gam[i];
             *reinterpret_cast<__nv_bfloat162*>(b_uc + i * LDB + j) = __floats2bfloat162_rn(gm * v0, gm * v1);
         });
-        epi_scale_store_bsm<NT128>(ati, r0, n0, b_dl, [&](int i, int j) {   // exp(E_i - Gprev_I)
+        epi_scale_store_bsm<NT128>(ati, r0, n0, b_dl, [&](int i, int j) {   // exp(E_i - G_ref)
+            const int ref = fast ? r0 + BT - 1 : r0 - 1;
             float2 E = make_float2(0.f, 0.f), Gp = make_float2(0.f, 0.f);
             if (i > 0) E = *reinterpret_cast<const float2*>(gG + (i - 1) * DP + j);
-            if (r0) Gp = *reinterpret_cast<const float2*>(gG + (r0 - 1) * DP + j);
+            if (ref >= 0) Gp = *reinterpret_cast<const float2*>(gG + ref * DP + j);
             return make_float2(__expf(E.x - Gp.x), __expf(E.y - Gp.y));
         });
-        epi_scale_store_bsm<NT128>(atj, r0, n0, b_tj, [&](int i, int j) {   // exp(Gend_J - G_j)
+        epi_scale_store_bsm<NT128>(atj, r0, n0, b_tj, [&](int i, int j) {   // exp(G_ref - G_j)
+            const int ref = fast ? r0 - 1 : r0 + BT - 1;
             const float2 G = *reinterpret_cast<const float2*>(gG + i * DP + j);
-            const float2 Ge = *reinterpret_cast<const float2*>(gG + (r0 + BT - 1) * DP + j);
+            float2 Ge = make_float2(0.f, 0.f);
+            if (ref >= 0) Ge = *reinterpret_cast<const float2*>(gG + ref * DP + j);
             return make_float2(__expf(Ge.x - G.x), __expf(Ge.y - G.y));
         });
     }
@@ -966,7 +1003,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
-    {   // diagonal blocks of t_i and t_j, one thread per (channel, block)
+    if (!block_is_fast(s_fastw, threadIdx.x >> 7)) {
+        // diagonal blocks of t_i and t_j that are not fast, one thread per (channel, block)
         float al[BT];
         block_alphas(al, fG);
         auto fu = [&](int j, int c) {

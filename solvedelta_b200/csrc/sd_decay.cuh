@@ -32,6 +32,33 @@ namespace sd {
 constexpr int BT = 16;          // tokens per decay block
 constexpr int NBLK = CL / BT;   // blocks per chunk
 
+// Fast blocks.  Inside one block the reciprocal form is harmless as long as the block
+// forgets less than FAST_BLOCK_NATS in every channel: exp(Gprev_I - G_j) <= e^60 then, and
+// the diagonal block is one more tensor-core block (pair: the row operand scaled by
+// 1 / beta_I along the contraction; causal / anti: one more Horner step, with the final
+// factor referenced to the other end of the block).  A block that forgets more takes the
+// direct evaluation.  The choice is per block and uniform over a warp tile.
+constexpr float FAST_BLOCK_NATS = 60.f;
+
+// One thread per (block J, channel c): s_beta = exp(Gend_J - Gprev_J), s_ibeta = its
+// reciprocal (0 where the block is not fast), s_fastw[warp] = every channel of the warp's
+// slice is fast.  Needs a __syncthreads() before the tables are read.
+template <class FG>
+__device__ __forceinline__ void block_decay_tables(float* s_beta, float* s_ibeta, int* s_fastw, FG fg) {
+    static_assert(NTHREADS == NBLK * DP, "one thread per (block, channel)");
+    const int J = threadIdx.x >> 7, c = threadIdx.x & (DP - 1);
+    const float d = fg(BT * J + BT - 1, c) - (J ? fg(BT * J - 1, c) : 0.f);
+    const bool ok = d >= -FAST_BLOCK_NATS;
+    if (s_beta != nullptr) s_beta[threadIdx.x] = __expf(d);
+    if (s_ibeta != nullptr) s_ibeta[threadIdx.x] = ok ? __expf(-d) : 0.f;
+    const int all = __all_sync(0xffffffffu, ok);
+    if ((threadIdx.x & 31) == 0) s_fastw[threadIdx.x >> 5] = all;
+}
+// block I is fast: all four warps of its channel slices agreed
+__device__ __forceinline__ bool block_is_fast(const int* s_fastw, int I) {
+    return (s_fastw[4 * I] & s_fastw[4 * I + 1] & s_fastw[4 * I + 2] & s_fastw[4 * I + 3]) != 0;
+}
+
 // s_beta[J][c] = exp(Gend_J - Gprev_J); fg(i, c) returns the chunk prefix G.
 template <class FG>
 __device__ __forceinline__ void block_betas(float* s_beta, FG fg) {
@@ -70,29 +97,38 @@ __device__ __forceinline__ void scale_acc(float (&acc)[NTW][4], const float* vec
     }
 }
 
-// ---- off-diagonal blocks of a pair on the tensor cores (TF32) ------------------
+// ---- blocks of a pair on the tensor cores (TF32) --------------------------------
 // Warp (I = row tile, J = column quarter) of the CL x CL tiling owns block (I, J).
 // fr(i, k): row-centred operand, fc(j, k): column-centred operand, k = channel.
-// fe(i, j, v0, v1) receives every element outside the diagonal blocks: the
-// contraction below them, zeros above.
-template <class FR, class FC, class FE>
-__device__ __forceinline__ void pair_offdiag_tf32(const float* s_M, FR fr, FC fc, FE fe) {
+// fe(i, j, v0, v1) receives every element of the blocks below the diagonal (the
+// contraction), above it (zeros) and of the FAST diagonal blocks (masked to j <= i,
+// or j < i when STRICT); diagonal blocks that are not fast are left untouched.
+template <bool STRICT, class FR, class FC, class FE>
+__device__ __forceinline__ void pair_blocks_tf32(const float* s_M, const float* s_ibeta, const int* s_fastw, FR fr,
+                                                 FC fc, FE fe) {
     const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
     const int I = r0 / BT, J = n0 / BT;
-    if (I == J) return;
+    if (I == J && !block_is_fast(s_fastw, I)) return;   // left to the direct evaluation
     float acc[NT64][4];
     acc_zero<NT64>(acc);
-    if (J < I) {
+    if (J <= I) {
         const int m = pair_scale_index(I, J);
         auto fb = [&](int k, int n) { return fc(n, k); };
-        if (m < 0) {
+        if (J < I && m < 0) {
             warp_mma<NT64>(acc, r0, n0, 0, DP, fr, fb);
         } else {
-            const float* mv = s_M + m * DP;
+            // beta product between the blocks, or 1 / beta_I inside a fast diagonal block
+            const float* mv = (J == I) ? s_ibeta + I * DP : s_M + m * DP;
             warp_mma<NT64>(acc, r0, n0, 0, DP, [&](int i, int k) { return fr(i, k) * mv[k]; }, fb);
         }
     }
-    warp_epi<NT64>(acc, r0, n0, fe);
+    if (I == J) {
+        warp_epi<NT64>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
+            fe(i, j, (STRICT ? j < i : j <= i) ? v0 : 0.f, (STRICT ? j + 1 < i : j + 1 <= i) ? v1 : 0.f);
+        });
+    } else {
+        warp_epi<NT64>(acc, r0, n0, fe);
+    }
 }
 
 // BF16 copy of the pair scale table for the BF16 contractions.
@@ -106,23 +142,31 @@ __device__ __forceinline__ void pair_block_scales_bf16(bf16* s_Mb, FG fg) {
     }
 }
 
-// Off-diagonal pair blocks, BF16 operands in shared panels of pitch LDB:
-// R row-centred, C column-centred.  fe as for pair_offdiag_tf32.
-template <class FE>
-__device__ __forceinline__ void pair_offdiag_bf16(const bf16* s_Mb, const bf16* R, const bf16* C, FE fe) {
+// Pair blocks, BF16 operands in shared panels of pitch LDB: R row-centred, C column-centred,
+// s_ibeta_b the BF16 copy of 1 / beta.  fe as for pair_blocks_tf32.
+template <bool STRICT, class FE>
+__device__ __forceinline__ void pair_blocks_bf16(const bf16* s_Mb, const bf16* s_ibeta_b, const int* s_fastw,
+                                                 const bf16* R, const bf16* C, FE fe) {
     const int r0 = Tile64<CL>::r0(), n0 = Tile64<CL>::n0();
     const int I = r0 / BT, J = n0 / BT;
-    if (I == J) return;
+    if (I == J && !block_is_fast(s_fastw, I)) return;
     float acc[NT64][4];
     acc_zero<NT64>(acc);
-    if (J < I) {
+    if (J <= I) {
         const int m = pair_scale_index(I, J);
-        if (m < 0)
+        if (J < I && m < 0)
             warp_mma_bf16<NT64, false, true>(acc, R, LDB, C, LDB, r0, n0, 0, DP);
         else
-            warp_mma_bf16_kscale<NT64, true>(acc, R, LDB, C, LDB, r0, n0, 0, DP, s_Mb + m * DP);
+            warp_mma_bf16_kscale<NT64, true>(acc, R, LDB, C, LDB, r0, n0, 0, DP,
+                                             (J == I) ? s_ibeta_b + I * DP : s_Mb + m * DP);
     }
-    warp_epi<NT64>(acc, r0, n0, fe);
+    if (I == J) {
+        warp_epi<NT64>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
+            fe(i, j, (STRICT ? j < i : j <= i) ? v0 : 0.f, (STRICT ? j + 1 < i : j + 1 <= i) ? v1 : 0.f);
+        });
+    } else {
+        warp_epi<NT64>(acc, r0, n0, fe);
+    }
 }
 
 __device__ __forceinline__ float ex2_approx(float x) {

@@ -100,7 +100,7 @@ __device__ __forceinline__ void store8_smem(float* sm, int i, int c0, const floa
 // Predictor preparation: pair matrix Lm, and the two solved panels
 //   Upd = (I+Lm)^-1 (gamma h),  W = (I+Lm)^-1 (gamma U~)   (stored negated as Qc)
 // so that the C scan is  Delta = Upd + Qc Ct.
-constexpr size_t PREP_FWD_SMEM = 5 * SLOT_BYTES + MAT_BYTES + (CL + 3 * DP) * sizeof(float);
+constexpr size_t PREP_FWD_SMEM = 5 * SLOT_BYTES + MAT_BYTES + (CL + 3 * DP + NBLK * DP + 16) * sizeof(float);
 
 template <bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
@@ -115,6 +115,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
     float* s_lm = s_h + SLOT_FLOATS;
     float* s_gam = s_lm + MAT_FLOATS;
     float* s_M = s_gam + CL;
+    float* s_ibeta = s_M + 3 * DP;
+    int* s_fastw = reinterpret_cast<int*>(s_ibeta + NBLK * DP);
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r;
 
@@ -129,6 +131,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
     SD_PHASE(p.g, ph);
     auto fG = [&](int i, int c) { return s_G[i * LDP + c]; };
     pair_block_scales(s_M, fG);
+    block_decay_tables(nullptr, s_ibeta, s_fastw, fG);
     for (int idx = threadIdx.x; idx < CL * DP; idx += NTHREADS) {
         int i = idx >> 7, c = idx & (DP - 1);
         const int i0 = i & ~(BT - 1);
@@ -144,18 +147,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
     SD_PHASE(p.g, ph);
     // Lm = gamma stril(N), N[i][j] = sum_c u^_ic u^_jc exp(E_ic - G_jc); N itself is kept for backward
     float* gN = mat_ptr(p.Npair, ch.gi);
-    pair_offdiag_tf32(s_M, [&](int i, int k) { return s_ut[i * LDP + k]; },
-                      [&](int j, int k) { return s_un[j * LDP + k]; },
-                      [&](int i, int j, float v0, float v1) {
-                          float gm = s_gam[i];
-                          *reinterpret_cast<float2*>(s_lm + i * LDA + j) = make_float2(gm * v0, gm * v1);
-                          *reinterpret_cast<float2*>(gN + i * CL + j) = make_float2(v0, v1);
-                      });
+    pair_blocks_tf32<true>(s_M, s_ibeta, s_fastw, [&](int i, int k) { return s_ut[i * LDP + k]; },
+                           [&](int j, int k) { return s_un[j * LDP + k]; },
+                           [&](int i, int j, float v0, float v1) {
+                               float gm = s_gam[i];
+                               *reinterpret_cast<float2*>(s_lm + i * LDA + j) = make_float2(gm * v0, gm * v1);
+                               *reinterpret_cast<float2*>(gN + i * CL + j) = make_float2(v0, v1);
+                           });
     {
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
 #pragma unroll 1
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
             const int i = balanced_row(lr, pp);
+            if (block_is_fast(s_fastw, i / BT)) continue;   // that diagonal block ran on the tensor cores
             float a[1][8], x[8], out[1];
             load8_smem(s_uh, i, c0, a[0]);
             if (i > 0) {
@@ -210,7 +214,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
 // Primal address d = k^ + C_t^T k^ for every token of the chunk:
 //   d_i = k^_i + exp(G_i) (K^ Ct^T)_i + sum_{j<=i} (k^_i . Delta_j) u^_j exp(G_i - G_j),
 // the decay-weighted sum in block-centred form (Horner over blocks, direct diagonal).
-constexpr size_t PRIMAL_FWD_SMEM = 6 * SLOT_BYTES + MAT_BYTES + NBLK * DP * sizeof(float);
+constexpr size_t PRIMAL_FWD_SMEM = 6 * SLOT_BYTES + MAT_BYTES + (NBLK * DP + 16) * sizeof(float);
 
 __device__ __forceinline__ void async_panel_f32(float* sm, const float* g) {
     for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += NTHREADS) {
@@ -238,6 +242,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
     float* s_st1 = s_st0 + SLOT_FLOATS;
     float* s_aqk = s_st1 + SLOT_FLOATS;
     float* s_beta = s_aqk + MAT_FLOATS;
+    int* s_fastw = reinterpret_cast<int*>(s_beta + NBLK * DP);
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r;
     const float* ct = state_ptr(p.CtCk, ch.gi);
@@ -256,7 +261,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
     __syncthreads();
     SD_PHASE(p.g, ph);
     auto fG = [&](int i, int c) { return s_G[i * LDP + c]; };
-    block_betas(s_beta, fG);
+    block_decay_tables(s_beta, nullptr, s_fastw, fG);
     {
         float acc[NT64][4];
         acc_zero<NT64>(acc);
@@ -272,7 +277,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
     __syncthreads();
     SD_PHASE(p.g, ph);
     // diagonal blocks directly (Delta is dead: its slot takes the result), then centre u^ on its block end
-    {
+    if (!block_is_fast(s_fastw, threadIdx.x >> 7)) {
         float al[BT];
         block_alphas(al, fG);
         auto none = [](int, int) { return 0.f; };
@@ -298,19 +303,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
                 [&](int k, int n) { return s_st0[n * LDH + k]; });
     warp_mma<NT128>(acc, r0, n0, 0, CL, [&](int i, int k) { return s_kh[i * LDP + CL + k]; },
                 [&](int k, int n) { return s_st1[n * LDH + k]; });
-    for (int J = 0; J * BT < r0; ++J) {
+    // a fast diagonal block is one more Horner step; the sum is then referenced to the block end
+    const bool fast = block_is_fast(s_fastw, r0 / BT);
+    for (int J = 0; J * BT < r0 + (fast ? BT : 0); ++J) {
         scale_acc<NT128>(acc, s_beta + J * DP, n0);
         warp_mma<NT128>(acc, r0, n0, J * BT, J * BT + BT, [&](int i, int k) { return s_aqk[i * LDA + k]; },
                     [&](int k, int n) { return s_un[k * LDP + n]; });
     }
     SD_PHASE(p.g, ph);
     float* gd = panel_ptr(p.Dprim, ch.gi);
+    const int ref = fast ? r0 + BT - 1 : r0 - 1;   // row whose prefix the accumulated sum is referenced to
     warp_epi<NT128>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
         float2 kh = *reinterpret_cast<const float2*>(s_kh + i * LDP + j);
         float2 G = *reinterpret_cast<const float2*>(s_G + i * LDP + j);
-        float2 Gp = make_float2(0.f, 0.f);
-        if (r0) Gp = *reinterpret_cast<const float2*>(s_G + (r0 - 1) * LDP + j);
-        float2 dg = *reinterpret_cast<const float2*>(s_dl + i * LDP + j);
+        float2 Gp = make_float2(0.f, 0.f), dg = make_float2(0.f, 0.f);
+        if (ref >= 0) Gp = *reinterpret_cast<const float2*>(s_G + ref * LDP + j);
+        if (!fast) dg = *reinterpret_cast<const float2*>(s_dl + i * LDP + j);
         *reinterpret_cast<float2*>(gd + i * DP + j) =
             make_float2(kh.x + __expf(G.x - Gp.x) * v0 + dg.x, kh.y + __expf(G.y - Gp.y) * v1 + dg.y);
     });
@@ -322,7 +330,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
 //   Aqd[i][j] = sum_c chi_ic d_jc exp(G_ic - G_jc) (j <= i),  Aed likewise with -e (j < i)
 // in block-centred form, and the solved panels Wd = (I-Aed)^-1 ag, Ud = (I-Aed)^-1 Z
 // for the S scan (ag = -e exp(G), referenced to the chunk start like the scan itself).
-constexpr size_t EXT_PREP_FWD_SMEM = 6 * SLOT_BYTES + MAT_BYTES + 3 * DP * sizeof(float);
+constexpr size_t EXT_PREP_FWD_SMEM = 6 * SLOT_BYTES + MAT_BYTES + (3 * DP + NBLK * DP + 16) * sizeof(float);
 
 template <bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) {
@@ -331,12 +339,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
     extern __shared__ __align__(16) float smem[];
     float* s_xr = smem;                  // chi rowG   (block-centred row operand)
     float* s_er = s_xr + SLOT_FLOATS;    // -e rowG
-    float* s_d = s_er + SLOT_FLOATS;     // d itself (the column operand d col is formed on the fly)
+    float* s_d = s_er + SLOT_FLOATS;     // d itself for the diagonal rows, then the column operand d col
     float* s_G = s_d + SLOT_FLOATS;      // chunk prefix of the log decay
     float* s_ag = s_G + SLOT_FLOATS;     // -e exp(G)  -> Wd
     float* s_z = s_ag + SLOT_FLOATS;     // z          -> Ud
     float* s_aed = s_z + SLOT_FLOATS;
     float* s_M = s_aed + MAT_FLOATS;
+    float* s_ibeta = s_M + 3 * DP;
+    int* s_fastw = reinterpret_cast<int*>(s_ibeta + NBLK * DP);
     const Chunk ch = chunk_of(p.g, blockIdx.x);
     const int r = p.g.r, V = p.g.V;
     bf16* gAqd = bmat_ptr(p.Aqd, ch.gi);
@@ -348,6 +358,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
     __syncthreads();
     SD_PHASE(p.g, ph);
     pair_block_scales(s_M, [&](int i, int c) { return s_G[i * LDP + c]; });
+    block_decay_tables(nullptr, s_ibeta, s_fastw, [&](int i, int c) { return s_G[i * LDP + c]; });
+    __syncthreads();
     {
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8, l16 = threadIdx.x & 15;
         const float* gDelta = panel_ptr(p.Delta, ch.gi);
@@ -396,31 +408,42 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
             store8_smem(s_z, i, c0, z);
             store8_panel(gDt, i, c0, dt);
             store8_bpanel(gXg, i, c0, xg);
-            // diagonal blocks: exp(G_i - G_j) directly; both pairs share the exponentials
-            float out[2];
-            pair_diag_row<2, false>(i, a, G, [&](int j, float (&b)[8]) { load8_smem(s_d, j, c0, b); },
-                                    [&](int j, float (&Gj)[8]) { load8_smem(s_G, j, c0, Gj); }, out);
-            gAqd[i * CL + i0 + l16] = __float2bfloat16_rn(out[0]);
-            s_aed[i * LDA + i0 + l16] = (i0 + l16 < i) ? out[1] : 0.f;
-            gAed[i * CL + i0 + l16] = (i0 + l16 < i) ? out[1] : 0.f;
+            // diagonal blocks that are not fast: exp(G_i - G_j) directly; both pairs share the exponentials
+            if (!block_is_fast(s_fastw, i / BT)) {
+                float out[2];
+                pair_diag_row<2, false>(i, a, G, [&](int j, float (&b)[8]) { load8_smem(s_d, j, c0, b); },
+                                        [&](int j, float (&Gj)[8]) { load8_smem(s_G, j, c0, Gj); }, out);
+                gAqd[i * CL + i0 + l16] = __float2bfloat16_rn(out[0]);
+                s_aed[i * LDA + i0 + l16] = (i0 + l16 < i) ? out[1] : 0.f;
+                gAed[i * CL + i0 + l16] = (i0 + l16 < i) ? out[1] : 0.f;
+            }
         }
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
+    // the diagonal rows are done with d itself: centre it on the end of its block, d_j exp(Gend_J - G_j)
+    for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += NTHREADS) {
+        const int j = idx >> 5, c4 = (idx & 31) << 2;
+        float4 d = *reinterpret_cast<const float4*>(s_d + j * LDP + c4);
+        const float4 G = *reinterpret_cast<const float4*>(s_G + j * LDP + c4);
+        const float4 Ge = *reinterpret_cast<const float4*>(s_G + (j | (BT - 1)) * LDP + c4);
+        d.x *= __expf(Ge.x - G.x); d.y *= __expf(Ge.y - G.y);
+        d.z *= __expf(Ge.z - G.z); d.w *= __expf(Ge.w - G.w);
+        *reinterpret_cast<float4*>(s_d + j * LDP + c4) = d;
+    }
+    __syncthreads();
     {
-        // column operand d_j exp(Gend_J - G_j), centred on the end of its block
-        auto fc = [&](int j, int k) {
-            return s_d[j * LDP + k] * __expf(s_G[(j | (BT - 1)) * LDP + k] - s_G[j * LDP + k]);
-        };
-        pair_offdiag_tf32(s_M, [&](int i, int k) { return s_xr[i * LDP + k]; }, fc,
-                          [&](int i, int j, float v0, float v1) {
-                              *reinterpret_cast<__nv_bfloat162*>(gAqd + i * CL + j) = __floats2bfloat162_rn(v0, v1);
-                          });
-        pair_offdiag_tf32(s_M, [&](int i, int k) { return s_er[i * LDP + k]; }, fc,
-                          [&](int i, int j, float v0, float v1) {
-                              *reinterpret_cast<float2*>(s_aed + i * LDA + j) = make_float2(v0, v1);
-                              *reinterpret_cast<float2*>(gAed + i * CL + j) = make_float2(v0, v1);
-                          });
+        auto fc = [&](int j, int k) { return s_d[j * LDP + k]; };
+        pair_blocks_tf32<false>(s_M, s_ibeta, s_fastw, [&](int i, int k) { return s_xr[i * LDP + k]; }, fc,
+                                [&](int i, int j, float v0, float v1) {
+                                    *reinterpret_cast<__nv_bfloat162*>(gAqd + i * CL + j) =
+                                        __floats2bfloat162_rn(v0, v1);
+                                });
+        pair_blocks_tf32<true>(s_M, s_ibeta, s_fastw, [&](int i, int k) { return s_er[i * LDP + k]; }, fc,
+                               [&](int i, int j, float v0, float v1) {
+                                   *reinterpret_cast<float2*>(s_aed + i * LDA + j) = make_float2(v0, v1);
+                                   *reinterpret_cast<float2*>(gAed + i * CL + j) = make_float2(v0, v1);
+                               });
     }
     __syncthreads();
     SD_PHASE(p.g, ph);

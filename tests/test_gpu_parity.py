@@ -258,6 +258,21 @@ def test_strong_forgetting_full_vjp_matches_checker(scale, T, H, r, V):
     _check_vjp(cpu, leaves, state, y, fin)
 
 
+def test_forgetting_bursts_mix_fast_and_direct_blocks():
+    """Mild decay with bursts of 16 nats per token: inside one chunk some 16-token blocks take the
+    tensor-core path for their diagonal block and others the direct evaluation."""
+    cpu, dev = make_inputs(1, 200, 2, 32, 32, seed=47)
+    ld = cpu["log_decay"].clone()
+    ld[:, 40:60] = -16.0 * (0.75 + 0.25 * torch.rand(1, 20, 2, 32, generator=torch.Generator().manual_seed(3)))
+    ld[:, 100:131, 1] = -9.0
+    ld[:, 190:, :, :8] = -30.0
+    cpu["log_decay"] = ld
+    dev["log_decay"] = ld.cuda()
+    leaves, state, y, fin = _native(dev, grad=True)
+    _check_forward(cpu, y, fin)
+    _check_vjp(cpu, leaves, state, y, fin)
+
+
 def test_return_final_state_false_and_none_cotangents():
     cpu, dev = make_inputs(1, 70, 1, 16, 16, seed=25)
     leaves, state, y, fin = _native(dev, grad=True, return_final_state=False)
