@@ -360,6 +360,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
     pair_block_scales(s_M, [&](int i, int c) { return s_G[i * LDP + c]; });
     block_decay_tables(nullptr, s_ibeta, s_fastw, [&](int i, int c) { return s_G[i * LDP + c]; });
     __syncthreads();
+    // with no block left to the direct evaluation nobody needs d itself: each row is centred as it is read
+    const bool all_fast = block_is_fast(s_fastw, 0) && block_is_fast(s_fastw, 1) && block_is_fast(s_fastw, 2) &&
+                          block_is_fast(s_fastw, 3);
     {
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8, l16 = threadIdx.x & 15;
         const float* gDelta = panel_ptr(p.Delta, ch.gi);
@@ -408,6 +411,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
             store8_smem(s_z, i, c0, z);
             store8_panel(gDt, i, c0, dt);
             store8_bpanel(gXg, i, c0, xg);
+            if (all_fast) {
+                float Ge[8], dc[8];
+                load8_smem(s_G, i0 + BT - 1, c0, Ge);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) dc[e] = d[e] * __expf(Ge[e] - G[e]);
+                store8_smem(s_d, i, c0, dc);
+            }
             // diagonal blocks that are not fast: exp(G_i - G_j) directly; both pairs share the exponentials
             if (!block_is_fast(s_fastw, i / BT)) {
                 float out[2];
@@ -422,16 +432,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
     __syncthreads();
     SD_PHASE(p.g, ph);
     // the diagonal rows are done with d itself: centre it on the end of its block, d_j exp(Gend_J - G_j)
-    for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += NTHREADS) {
-        const int j = idx >> 5, c4 = (idx & 31) << 2;
-        float4 d = *reinterpret_cast<const float4*>(s_d + j * LDP + c4);
-        const float4 G = *reinterpret_cast<const float4*>(s_G + j * LDP + c4);
-        const float4 Ge = *reinterpret_cast<const float4*>(s_G + (j | (BT - 1)) * LDP + c4);
-        d.x *= __expf(Ge.x - G.x); d.y *= __expf(Ge.y - G.y);
-        d.z *= __expf(Ge.z - G.z); d.w *= __expf(Ge.w - G.w);
-        *reinterpret_cast<float4*>(s_d + j * LDP + c4) = d;
+    if (!all_fast) {
+        for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += NTHREADS) {
+            const int j = idx >> 5, c4 = (idx & 31) << 2;
+            float4 d = *reinterpret_cast<const float4*>(s_d + j * LDP + c4);
+            const float4 G = *reinterpret_cast<const float4*>(s_G + j * LDP + c4);
+            const float4 Ge = *reinterpret_cast<const float4*>(s_G + (j | (BT - 1)) * LDP + c4);
+            d.x *= __expf(Ge.x - G.x); d.y *= __expf(Ge.y - G.y);
+            d.z *= __expf(Ge.z - G.z); d.w *= __expf(Ge.w - G.w);
+            *reinterpret_cast<float4*>(s_d + j * LDP + c4) = d;
+        }
+        __syncthreads();
     }
-    __syncthreads();
     {
         auto fc = [&](int j, int k) { return s_d[j * LDP + k]; };
         pair_blocks_tf32<false>(s_M, s_ibeta, s_fastw, [&](int i, int k) { return s_xr[i * LDP + k]; }, fc,
