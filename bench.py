@@ -302,10 +302,10 @@ KERNEL_BYTES_PER_CHUNK = {
 # B=8, T=1024 case of this workload (profiles/chunk_kernels_B8_T1024_ncu_full.md); traffic is
 # proportional to the number of chunk tasks, so a full launch moves 4096 times these.
 KERNEL_DRAM_BYTES_PER_CHUNK = {
-    "k_prep_fwd": 154 * KIB, "k_state_scan[C]": 185 * KIB, "k_primal_fwd": 180 * KIB,
-    "k_exterior_prep_fwd": 289 * KIB, "k_state_scan[S]": 121 * KIB, "k_output_fwd": 76 * KIB,
-    "k_exterior_prep_bwd": 320 * KIB, "k_state_scan_b[dS]": 103 * KIB, "k_exterior_pair_bwd": 663 * KIB,
-    "k_primal_bwd": 278 * KIB, "k_state_scan_b[dC]": 101 * KIB, "k_predictor_close_bwd": 305 * KIB,
+    "k_prep_fwd": 154 * KIB, "k_state_scan[C]": 184 * KIB, "k_primal_fwd": 180 * KIB,
+    "k_exterior_prep_fwd": 288 * KIB, "k_state_scan[S]": 121 * KIB, "k_output_fwd": 75 * KIB,
+    "k_exterior_prep_bwd": 321 * KIB, "k_state_scan_b[dS]": 103 * KIB, "k_exterior_pair_bwd": 542 * KIB,
+    "k_primal_bwd": 278 * KIB, "k_state_scan_b[dC]": 102 * KIB, "k_predictor_close_bwd": 305 * KIB,
 }
 
 
