@@ -114,7 +114,9 @@ def run_case(ref, name, args, *, state=None, valid=None, reset=None, seed=29, ra
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/SolveDelta")
+    root = sys.argv[1]
     ref = load_reference(root)
 
     run_case(ref, "seed7_dense", seed7_inputs())
