@@ -512,6 +512,12 @@ size_t sd_conv4_backward_scratch_bytes(int32_t B, int32_t T, int32_t D) {
     return align256(size_t(B) * conv_tiles(T) * D * 4 * sizeof(float));
 }
 
+// channel pairs can move as 4-byte accesses: even widths and strides, 4-byte aligned bases
+static bool conv_pairs_ok(const ConvParams& p) {
+    auto al = [](const void* q) { return q == nullptr || (reinterpret_cast<uintptr_t>(q) & 3) == 0; };
+    return (p.D & 1) == 0 && (p.sb & 1) == 0 && (p.st & 1) == 0 && al(p.x) && al(p.y) && al(p.dy) && al(p.dx);
+}
+
 int sd_conv4_silu_forward(const sd_conv4_forward_args* a, void* stream_) {
     if (!a || a->B <= 0 || a->T <= 0 || a->D <= 0 || !a->x || !a->weight || !a->y) return SD_ERR_INVALID_ARGUMENT;
     ConvParams p{};
@@ -523,7 +529,10 @@ int sd_conv4_silu_forward(const sd_conv4_forward_args* a, void* stream_) {
     p.y = reinterpret_cast<__nv_bfloat16*>(a->y);
     p.fin = reinterpret_cast<__nv_bfloat16*>(a->final_state);
     dim3 grid((a->D + 2 * CONV_THREADS - 1) / (2 * CONV_THREADS), conv_tiles(a->T), a->B);
-    k_conv4_silu_fwd<<<grid, CONV_THREADS, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
+    if (conv_pairs_ok(p))
+        k_conv4_silu_fwd<true><<<grid, CONV_THREADS, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
+    else
+        k_conv4_silu_fwd<false><<<grid, CONV_THREADS, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
     return launch_status();
 }
 
@@ -545,7 +554,10 @@ int sd_conv4_silu_backward(const sd_conv4_backward_args* a, void* stream_) {
     p.dw_part = reinterpret_cast<float*>(a->scratch);
     const int tiles = conv_tiles(a->T);
     dim3 grid((a->D + 2 * CONV_THREADS - 1) / (2 * CONV_THREADS), tiles, a->B);
-    k_conv4_silu_bwd<<<grid, CONV_THREADS, 0, stream>>>(p);
+    if (conv_pairs_ok(p))
+        k_conv4_silu_bwd<true><<<grid, CONV_THREADS, 0, stream>>>(p);
+    else
+        k_conv4_silu_bwd<false><<<grid, CONV_THREADS, 0, stream>>>(p);
     const long long n = (long long)a->D * 4;
     k_column_sum<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p.dw_part, a->B * tiles, n, a->dweight);
     return launch_status();

@@ -52,6 +52,27 @@ __device__ __forceinline__ float2 conv_input(const ConvParams& p, int b, int t, 
     return v;
 }
 
+// Two adjacent channels of one token of the sequence (t in [0, T)); PAIR: the pair is read /
+// written as one 4-byte access (even strides and 4-byte aligned bases).
+template <bool PAIR>
+__device__ __forceinline__ float2 load_pair(const __nv_bfloat16* row, bool two) {
+    if (PAIR) return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(row));
+    return make_float2(__bfloat162float(row[0]), two ? __bfloat162float(row[1]) : 0.f);
+}
+template <bool PAIR>
+__device__ __forceinline__ void store_pair(__nv_bfloat16* row, bool two, float a, float b) {
+    if (PAIR) {
+        *reinterpret_cast<__nv_bfloat162*>(row) = __floats2bfloat162_rn(a, b);
+    } else {
+        row[0] = __float2bfloat16_rn(a);
+        if (two) row[1] = __float2bfloat16_rn(b);
+    }
+}
+
+constexpr int CONV_BATCH = 4;      // forward: tokens whose loads are issued together
+constexpr int CONV_BATCH_BWD = 1;  // reverse: more registers per token; batching cost occupancy and time
+
+template <bool PAIR>
 __global__ void __launch_bounds__(CONV_THREADS) k_conv4_silu_fwd(ConvParams p) {
     const int d = (blockIdx.x * CONV_THREADS + threadIdx.x) * 2;
     const int t0 = blockIdx.y * CONV_TT, b = blockIdx.z;
@@ -66,14 +87,25 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv4_silu_fwd(ConvParams p) {
     float2 x0 = conv_input(p, b, t0 - 3, d, two), x1 = conv_input(p, b, t0 - 2, d, two),
            x2 = conv_input(p, b, t0 - 1, d, two);
     const int t1 = min(t0 + CONV_TT, p.T);
-    for (int t = t0; t < t1; ++t) {
-        const float2 x3 = conv_input(p, b, t, d, two);
-        const float za = wa[0] * x0.x + wa[1] * x1.x + wa[2] * x2.x + wa[3] * x3.x;
-        const float zb = wb[0] * x0.y + wb[1] * x1.y + wb[2] * x2.y + wb[3] * x3.y;
-        __nv_bfloat16* out = p.y + ((long long)b * p.T + t) * p.D + d;
-        out[0] = __float2bfloat16_rn(silu_f(za));
-        if (two) out[1] = __float2bfloat16_rn(silu_f(zb));
-        x0 = x1; x1 = x2; x2 = x3;
+    const __nv_bfloat16* xin = p.x + b * p.sb + d;
+    __nv_bfloat16* yout = p.y + (long long)b * p.T * p.D + d;
+    for (int ts = t0; ts < t1; ts += CONV_BATCH) {
+        float2 xs[CONV_BATCH];
+#pragma unroll
+        for (int k = 0; k < CONV_BATCH; ++k) {   // every token of a tile lies inside the sequence; only the tail is predicated
+            xs[k] = make_float2(0.f, 0.f);
+            if (ts + k < t1) xs[k] = load_pair<PAIR>(xin + (long long)(ts + k) * p.st, two);
+        }
+#pragma unroll
+        for (int k = 0; k < CONV_BATCH; ++k) {
+            if (ts + k < t1) {
+                const float2 x3 = xs[k];
+                const float za = wa[0] * x0.x + wa[1] * x1.x + wa[2] * x2.x + wa[3] * x3.x;
+                const float zb = wb[0] * x0.y + wb[1] * x1.y + wb[2] * x2.y + wb[3] * x3.y;
+                store_pair<PAIR>(yout + (long long)(ts + k) * p.D, two, silu_f(za), silu_f(zb));
+                x0 = x1; x1 = x2; x2 = x3;
+            }
+        }
     }
     if (p.fin != nullptr && t1 == p.T) {
         // carried state = the last three inputs (the old state shows through when T < 3)
@@ -85,6 +117,7 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv4_silu_fwd(ConvParams p) {
     }
 }
 
+template <bool PAIR>
 __global__ void __launch_bounds__(CONV_THREADS) k_conv4_silu_bwd(ConvParams p) {
     const int d = (blockIdx.x * CONV_THREADS + threadIdx.x) * 2;
     const int t0 = blockIdx.y * CONV_TT, b = blockIdx.z;
@@ -104,34 +137,51 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv4_silu_bwd(ConvParams p) {
     float2 g0 = make_float2(0.f, 0.f), g1 = g0, g2 = g0;
     float dwa[4] = {0.f, 0.f, 0.f, 0.f}, dwb[4] = {0.f, 0.f, 0.f, 0.f};
     const int t_end = min(t0 + CONV_TT, p.T);
-    for (int t = t0; t < t_end + 3; ++t) {
-        const float2 x3 = conv_input(p, b, t, d, two);
-        float2 g3 = make_float2(0.f, 0.f);
-        if (t < p.T) {
-            const float za = wa[0] * x0.x + wa[1] * x1.x + wa[2] * x2.x + wa[3] * x3.x;
-            const float zb = wb[0] * x0.y + wb[1] * x1.y + wb[2] * x2.y + wb[3] * x3.y;
-            const __nv_bfloat16* go = p.dy + ((long long)b * p.T + t) * p.D + d;
-            g3.x = __bfloat162float(go[0]) * silu_grad_f(za);
-            if (two) g3.y = __bfloat162float(go[1]) * silu_grad_f(zb);
-            if (t >= t0 && t < t_end) {  // weight gradient: own tile only
-                dwa[0] += g3.x * x0.x; dwa[1] += g3.x * x1.x; dwa[2] += g3.x * x2.x; dwa[3] += g3.x * x3.x;
-                dwb[0] += g3.y * x0.y; dwb[1] += g3.y * x1.y; dwb[2] += g3.y * x2.y; dwb[3] += g3.y * x3.y;
+    const int t_last = min(t_end + 3, p.T);   // tokens past the tile still feed its last three gradients
+    const __nv_bfloat16* xin = p.x + b * p.sb + d;
+    const __nv_bfloat16* gin = p.dy + (long long)b * p.T * p.D + d;
+    __nv_bfloat16* dxout = p.dx + (long long)b * p.T * p.D + d;
+    for (int ts = t0; ts < t_end + 3; ts += CONV_BATCH_BWD) {
+        float2 xs[CONV_BATCH_BWD], gs[CONV_BATCH_BWD];
+#pragma unroll
+        for (int k = 0; k < CONV_BATCH_BWD; ++k) {
+            xs[k] = make_float2(0.f, 0.f);
+            gs[k] = make_float2(0.f, 0.f);
+            if (ts + k < t_last) {
+                xs[k] = load_pair<PAIR>(xin + (long long)(ts + k) * p.st, two);
+                gs[k] = load_pair<PAIR>(gin + (long long)(ts + k) * p.D, two);
             }
         }
-        const int tq = t - 3;  // the input whose gradient is now complete
-        const float da = wa[0] * g3.x + wa[1] * g2.x + wa[2] * g1.x + wa[3] * g0.x;
-        const float db = wb[0] * g3.y + wb[1] * g2.y + wb[2] * g1.y + wb[3] * g0.y;
-        if (tq >= t0 && tq < t_end) {
-            __nv_bfloat16* out = p.dx + ((long long)b * p.T + tq) * p.D + d;
-            out[0] = __float2bfloat16_rn(da);
-            if (two) out[1] = __float2bfloat16_rn(db);
-        } else if (tq < 0 && t0 == 0 && p.dinit != nullptr) {
-            __nv_bfloat16* s = p.dinit + ((long long)b * p.D + d) * 3 + (tq + 3);
-            s[0] = __float2bfloat16_rn(da);
-            if (two) s[3] = __float2bfloat16_rn(db);
+#pragma unroll
+        for (int k = 0; k < CONV_BATCH_BWD; ++k) {
+            const int t = ts + k;
+            if (t < t_end + 3) {
+                const float2 x3 = xs[k];
+                float2 g3 = make_float2(0.f, 0.f);
+                if (t < p.T) {
+                    const float za = wa[0] * x0.x + wa[1] * x1.x + wa[2] * x2.x + wa[3] * x3.x;
+                    const float zb = wb[0] * x0.y + wb[1] * x1.y + wb[2] * x2.y + wb[3] * x3.y;
+                    g3.x = gs[k].x * silu_grad_f(za);
+                    g3.y = gs[k].y * silu_grad_f(zb);
+                    if (t < t_end) {  // weight gradient: own tile only
+                        dwa[0] += g3.x * x0.x; dwa[1] += g3.x * x1.x; dwa[2] += g3.x * x2.x; dwa[3] += g3.x * x3.x;
+                        dwb[0] += g3.y * x0.y; dwb[1] += g3.y * x1.y; dwb[2] += g3.y * x2.y; dwb[3] += g3.y * x3.y;
+                    }
+                }
+                const int tq = t - 3;  // the input whose gradient is now complete
+                const float da = wa[0] * g3.x + wa[1] * g2.x + wa[2] * g1.x + wa[3] * g0.x;
+                const float db = wb[0] * g3.y + wb[1] * g2.y + wb[2] * g1.y + wb[3] * g0.y;
+                if (tq >= t0 && tq < t_end) {
+                    store_pair<PAIR>(dxout + (long long)tq * p.D, two, da, db);
+                } else if (tq < 0 && t0 == 0 && p.dinit != nullptr) {
+                    __nv_bfloat16* s = p.dinit + ((long long)b * p.D + d) * 3 + (tq + 3);
+                    s[0] = __float2bfloat16_rn(da);
+                    if (two) s[3] = __float2bfloat16_rn(db);
+                }
+                x0 = x1; x1 = x2; x2 = x3;
+                g0 = g1; g1 = g2; g2 = g3;
+            }
         }
-        x0 = x1; x1 = x2; x2 = x3;
-        g0 = g1; g1 = g2; g2 = g3;
     }
     float* part = p.dw_part + ((long long)(b * gridDim.y + blockIdx.y) * p.D + d) * 4;
 #pragma unroll
