@@ -46,33 +46,6 @@ __device__ __forceinline__ void norm_vjp8(const float (&dxh)[8], const float (&x
     for (int e = 0; e < 8; ++e) dx[e] = (dxh[e] - dot * xh[e]) * rstd;
 }
 
-// Transposed unit-triangular solve on BF16 panels: (I + sgn*M)^T X = RHS, two
-// panels of DP columns, FP32 arithmetic in registers.  Mr[i][k] = M[k][i] for
-// k > i, zero elsewhere (same convention as trisolve<true>).
-__device__ __forceinline__ void trisolve_upper_b(const float* Mr, float sgn, bf16* P0, bf16* P1) {
-    if (threadIdx.x >= 2 * DP) return;  // one thread per right-hand-side column
-    bf16* P = (threadIdx.x < DP) ? P0 : P1;
-    const int col = threadIdx.x & (DP - 1);
-    float x[CL];
-#pragma unroll
-    for (int i = 0; i < CL; ++i) x[i] = __bfloat162float(P[i * LDB + col]);
-#pragma unroll
-    for (int i = CL - 2; i >= 0; --i) {
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;  // independent chains
-#pragma unroll
-        for (int k4 = ((i + 1) & ~3); k4 < CL; k4 += 4) {
-            float4 m = *reinterpret_cast<const float4*>(Mr + i * LDA + k4);
-            a0 = fmaf(m.x, x[k4], a0);
-            a1 = fmaf(m.y, x[k4 + 1], a1);
-            a2 = fmaf(m.z, x[k4 + 2], a2);
-            a3 = fmaf(m.w, x[k4 + 3], a3);
-        }
-        x[i] = fmaf(-sgn, (a0 + a1) + (a2 + a3), x[i]);
-    }
-#pragma unroll
-    for (int i = 0; i < CL; ++i) P[i * LDB + col] = __float2bfloat16_rn(x[i]);
-}
-
 // shared BF16 panel -> dense BF16 global panel
 __device__ __forceinline__ void s2g_bpanel(bf16* g, const bf16* sm) {
     for (int idx = threadIdx.x; idx < CL * (DP / 8); idx += NTHREADS) {
@@ -111,13 +84,6 @@ template <int NTW>
 __device__ __forceinline__ void epi_store_bsm(float (&acc)[NTW][4], int r0, int n0, bf16* spanel) {
     warp_epi<NTW>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
         *reinterpret_cast<__nv_bfloat162*>(spanel + i * LDB + j) = __floats2bfloat162_rn(v0, v1);
-    });
-}
-
-template <int NTW>
-__device__ __forceinline__ void epi_store_bpanel(float (&acc)[NTW][4], int r0, int n0, bf16* gpanel) {
-    warp_epi<NTW>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
-        *reinterpret_cast<__nv_bfloat162*>(gpanel + i * DP + j) = __floats2bfloat162_rn(v0, v1);
     });
 }
 

@@ -166,30 +166,6 @@ __device__ __forceinline__ void async_bmat(bf16* sm, const bf16* g) {
         cp16(sm + i * LDM + c8, g + i * CL + c8);
     }
 }
-// dense FP32 global panel -> BF16 shared panel (through registers)
-__device__ __forceinline__ void g2s_panel_f32_to_bf16(bf16* sm, const float* g) {
-    for (int idx = threadIdx.x; idx < CL * (DP / 8); idx += NTHREADS) {
-        int i = idx >> 4, c8 = (idx & 15) << 3;
-        float x[8];
-        float4 a = *reinterpret_cast<const float4*>(g + i * DP + c8);
-        float4 b = *reinterpret_cast<const float4*>(g + i * DP + c8 + 4);
-        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
-        x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
-        *reinterpret_cast<uint4*>(sm + i * LDB + c8) = pack8_bf16(x);
-    }
-}
-// whole FP32 state [DP][DP] -> BF16 shared [DP][LDB]
-__device__ __forceinline__ void g2s_state_f32_to_bf16(bf16* sm, const float* st) {
-    for (int idx = threadIdx.x; idx < DP * (DP / 8); idx += NTHREADS) {
-        int i = idx >> 4, c8 = (idx & 15) << 3;
-        float x[8];
-        float4 a = *reinterpret_cast<const float4*>(st + i * DP + c8);
-        float4 b = *reinterpret_cast<const float4*>(st + i * DP + c8 + 4);
-        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
-        x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
-        *reinterpret_cast<uint4*>(sm + i * LDB + c8) = pack8_bf16(x);
-    }
-}
 constexpr size_t BSTATE_BYTES = size_t(DP) * LDB * 2;  // a whole state in BF16
 
 // ---- blocked unit-triangular solve -------------------------------------------

@@ -227,43 +227,12 @@ __device__ __forceinline__ void prefetch_rows(const Operand& op, const Chunk& ch
 }
 
 // ---- dense panel movement -------------------------------------------------
-__device__ __forceinline__ void g2s_panel(float* sm, const float* g) {
-    for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += NTHREADS) {
-        int i = idx >> 5, c4 = (idx & 31) << 2;
-        *reinterpret_cast<float4*>(sm + i * LDP + c4) = *reinterpret_cast<const float4*>(g + i * DP + c4);
-    }
-}
 __device__ __forceinline__ void s2g_panel(float* g, const float* sm) {
     for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += NTHREADS) {
         int i = idx >> 5, c4 = (idx & 31) << 2;
         *reinterpret_cast<float4*>(g + i * DP + c4) = *reinterpret_cast<const float4*>(sm + i * LDP + c4);
     }
 }
-__device__ __forceinline__ void g2s_mat(float* sm, const float* g) {
-    for (int idx = threadIdx.x; idx < CL * (CL / 4); idx += NTHREADS) {
-        int i = idx >> 4, c4 = (idx & 15) << 2;
-        *reinterpret_cast<float4*>(sm + i * LDA + c4) = *reinterpret_cast<const float4*>(g + i * CL + c4);
-    }
-}
-__device__ __forceinline__ void s2g_mat(float* g, const float* sm) {
-    for (int idx = threadIdx.x; idx < CL * (CL / 4); idx += NTHREADS) {
-        int i = idx >> 4, c4 = (idx & 15) << 2;
-        *reinterpret_cast<float4*>(g + i * CL + c4) = *reinterpret_cast<const float4*>(sm + i * LDA + c4);
-    }
-}
-// Rows [half*64, half*64+64) of a [DP][DP] state -> panel-shaped slot [CL][LDP].
-__device__ __forceinline__ void g2s_state_rows(float* sm, const float* st, int half) {
-    g2s_panel(sm, st + half * CL * DP);
-}
-// Columns [half*64, half*64+64) of a [DP][DP] state -> slot [DP][LDH].
-__device__ __forceinline__ void g2s_state_cols(float* sm, const float* st, int half) {
-    for (int idx = threadIdx.x; idx < DP * (CL / 4); idx += NTHREADS) {
-        int rrow = idx >> 4, c4 = (idx & 15) << 2;
-        *reinterpret_cast<float4*>(sm + rrow * LDH + c4) =
-            *reinterpret_cast<const float4*>(st + rrow * DP + half * CL + c4);
-    }
-}
-
 // ---- TF32 tensor-core contraction on shared-memory operands --------------
 __device__ __forceinline__ uint32_t f2tf32(float x) {
     uint32_t y;
@@ -327,54 +296,6 @@ struct Tile64 {
     __device__ static __forceinline__ int r0() { return ((threadIdx.x >> 5) & 3) * 16; }
     __device__ static __forceinline__ int n0() { return (threadIdx.x >> 7) * (N / 4); }
 };
-
-// ---- unit-triangular solves ------------------------------------------------
-// Solves (I + sgn * M) X = RHS in place for the 2*DP columns of two panels.
-// Mr is stored by rows of the system actually solved:
-//   UPPER == false: Mr[i][k] = M[i][k], non-zero only for k < i.
-//   UPPER == true : Mr[i][k] = M[k][i], non-zero only for k > i
-//                   (the transposed system), solved from the last row up.
-// Entries outside the stated triangle must be exactly zero.
-template <bool UPPER>
-__device__ __forceinline__ void trisolve(const float* Mr, float sgn, float* P0, float* P1) {
-    if (threadIdx.x >= 2 * DP) return;  // one thread per right-hand-side column
-    float* P = (threadIdx.x < DP) ? P0 : P1;
-    const int col = threadIdx.x & (DP - 1);
-    float x[CL];
-#pragma unroll
-    for (int i = 0; i < CL; ++i) x[i] = P[i * LDP + col];
-    if (!UPPER) {
-#pragma unroll
-        for (int i = 1; i < CL; ++i) {
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;  // independent chains
-#pragma unroll
-            for (int k4 = 0; k4 < i; k4 += 4) {
-                float4 m = *reinterpret_cast<const float4*>(Mr + i * LDA + k4);
-                a0 = fmaf(m.x, x[k4], a0);
-                a1 = fmaf(m.y, x[k4 + 1], a1);
-                a2 = fmaf(m.z, x[k4 + 2], a2);
-                a3 = fmaf(m.w, x[k4 + 3], a3);
-            }
-            x[i] = fmaf(-sgn, (a0 + a1) + (a2 + a3), x[i]);
-        }
-    } else {
-#pragma unroll
-        for (int i = CL - 2; i >= 0; --i) {
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;  // independent chains
-#pragma unroll
-            for (int k4 = ((i + 1) & ~3); k4 < CL; k4 += 4) {
-                float4 m = *reinterpret_cast<const float4*>(Mr + i * LDA + k4);
-                a0 = fmaf(m.x, x[k4], a0);
-                a1 = fmaf(m.y, x[k4 + 1], a1);
-                a2 = fmaf(m.z, x[k4 + 2], a2);
-                a3 = fmaf(m.w, x[k4 + 3], a3);
-            }
-            x[i] = fmaf(-sgn, (a0 + a1) + (a2 + a3), x[i]);
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < CL; ++i) P[i * LDP + col] = x[i];
-}
 
 // ---- chunk-local gate algebra ----------------------------------------------
 // In place: sG[i][c] <- sum_{j<=i} g[j][c].  Call with all threads; needs a

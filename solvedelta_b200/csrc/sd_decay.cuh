@@ -59,17 +59,6 @@ __device__ __forceinline__ bool block_is_fast(const int* s_fastw, int I) {
     return (s_fastw[4 * I] & s_fastw[4 * I + 1] & s_fastw[4 * I + 2] & s_fastw[4 * I + 3]) != 0;
 }
 
-// s_beta[J][c] = exp(Gend_J - Gprev_J); fg(i, c) returns the chunk prefix G.
-template <class FG>
-__device__ __forceinline__ void block_betas(float* s_beta, FG fg) {
-    for (int idx = threadIdx.x; idx < NBLK * DP; idx += NTHREADS) {
-        const int J = idx >> 7, c = idx & (DP - 1);
-        const float hi = fg(BT * J + BT - 1, c);
-        const float lo = J ? fg(BT * J - 1, c) : 0.f;
-        s_beta[idx] = __expf(hi - lo);
-    }
-}
-
 // Row-operand scale of an off-diagonal pair block (I, J), I - J >= 2:
 //   s_M[0] = beta_1 (blocks (2,0)),  s_M[1] = beta_2 ((3,1)),  s_M[2] = beta_1 beta_2 ((3,0)).
 template <class FG>
