@@ -365,6 +365,48 @@ def time_mixer_glue(B, T, H, r, V, device, reps=10):
     return out
 
 
+def time_mixer_module(B, T, H, r, V, device, reps=5):
+    """Forward + backward of the SolveDelta mixer (projections through cuBLAS, glue kernels, operator)
+    at the layer shape of the reference's 24-layer configuration: hidden 1024, conv on, random init."""
+    import torch
+
+    from solvedelta_b200 import SolveDelta, SolveDeltaConfig
+
+    hidden = 1024
+    torch.manual_seed(0)
+    module = SolveDelta(SolveDeltaConfig(hidden_size=hidden, num_heads=H, head_k_dim=r, head_v_dim=V)).to(device)
+    gen = torch.Generator(device="cpu").manual_seed(4)
+    x = torch.randn(B, T, hidden, generator=gen).to(torch.bfloat16).to(device).requires_grad_()
+    dout = torch.randn(B, T, hidden, generator=gen).to(torch.bfloat16).to(device)
+    params = [p for p in module.parameters()]
+
+    def step():
+        out = module(x)
+        torch.autograd.grad(out, [x] + params, dout)
+
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    with torch.no_grad():
+        e0.record()
+        for _ in range(reps):
+            module(x)
+        e1.record()
+        torch.cuda.synchronize()
+    fwd_ms = e0.elapsed_time(e1) / reps
+    return {"ms_per_step": round(ms, 3), "value": round(B * T / (ms * 1e-3), 1), "unit": "tokens/s",
+            "forward_ms": round(fwd_ms, 3),
+            "shape": f"hidden {hidden}, {H} heads, {r}/{V}, B={B}, T={T}, in_proj {hidden}->{module.in_proj.out_features}, "
+                     "fwd + bwd (input and all parameter gradients)"}
+
+
 def run_ours(opts, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -520,8 +562,26 @@ def run_ours(opts, rank, world, local_rank):
                "d2h_bytes_per_step": d2h_bytes[0], "pipelined": "3 streams, 2 slots"}
 
     glue = None
+    gamma_zero = None
+    mixer = None
     if world == 1 and not opts.skip_glue:
         glue = time_mixer_glue(B, T, H, r, V, device)
+        mixer = time_mixer_module(B, T, H, r, V, device)
+        # geometry write rate 0: the operator reduces to the GDN2 edit (same launches, same traffic)
+        cpu0 = dict(cpu)
+        cpu0["geometry_write"] = torch.zeros_like(cpu["geometry_write"])
+        runner0 = DeviceStep(cpu0, device)
+        for _ in range(3):
+            runner0.step()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(10):
+            runner0.step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms0 = e0.elapsed_time(e1) / 10
+        gamma_zero = {"ms_per_step": ms0, "value": runner0.tokens / (ms0 * 1e-3), "unit": "tokens/s"}
+        del runner0
 
     if rank == 0:
         cpu_baseline = None
@@ -546,7 +606,7 @@ def run_ours(opts, rank, world, local_rank):
             "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu_baseline,
             "forward_only": {"ms_per_step": fwd_ms, "value": job_throughput(runner.tokens, fwd_ms * 1e-3, world),
                              "unit": "tokens/s"},
-            "mixer_glue": glue,
+            "mixer_glue": glue, "mixer_module": mixer, "gamma_zero": gamma_zero,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

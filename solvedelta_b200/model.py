@@ -34,6 +34,40 @@ class SolveDeltaLayerState(NamedTuple):
     conv: Optional[torch.Tensor]
 
 
+class _SplitRow(torch.autograd.Function):
+    """Slices of the fused projection row as views (no copy), with a backward that writes every
+    slice gradient once into one row-shaped buffer.  Plain slicing would make autograd allocate and
+    add one zero-filled full row per slice (ten rows of 7488 columns per token for the mixer)."""
+
+    @staticmethod
+    def forward(ctx, row, sizes):
+        ctx.sizes = sizes
+        ctx.row_shape, ctx.row_dtype, ctx.row_device = row.shape, row.dtype, row.device
+        ctx.set_materialize_grads(False)
+        pieces, start = [], 0
+        for size in sizes:
+            pieces.append(row[..., start:start + size])
+            start += size
+        return tuple(pieces)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        if all(g is None for g in grads):
+            return None, None
+        drow = torch.empty(ctx.row_shape, dtype=ctx.row_dtype, device=ctx.row_device)
+        start = 0
+        for size, grad in zip(ctx.sizes, grads):
+            target = drow[..., start:start + size]
+            if grad is None:
+                target.zero_()
+            else:
+                target.copy_(grad)
+            start += size
+        if start < ctx.row_shape[-1]:
+            drow[..., start:].zero_()   # padding columns of the projection
+        return drow, None
+
+
 class RMSNormGated(nn.Module):
     """y = RMSNorm(x) * weight * sigmoid(gate) (causallsso/ops/norm_gate.py:162-217)."""
 
@@ -111,17 +145,20 @@ class SolveDelta(nn.Module):
         value_width = self.config.resolved_head_v_dim
         sizes = self.projection_sizes
         row = self._linear(self.in_proj, hidden_states)          # [B,T,P] BF16, slices stay views
-        offsets = [0]
-        for size in sizes:
-            offsets.append(offsets[-1] + size)
-        piece = lambda i: row[..., offsets[i]:offsets[i + 1]]
         conv_state = initial_state.conv if initial_state is not None else None
         if self.config.use_short_conv:
+            # q | k | v stay one slice: the conv reads it in place
+            split = _SplitRow.apply(row, (sum(sizes[:3]),) + tuple(sizes[3:]))
+            qkv_in = split[0]
+            pieces = (None, None, None) + tuple(split[1:])
+        else:
+            pieces = _SplitRow.apply(row, tuple(sizes))
+        piece = lambda i: pieces[i]
+        if self.config.use_short_conv:
             if packed_segments is None:
-                qkv, final_conv = conv4_silu(row[..., :offsets[3]], self.conv_weight, conv_state,
-                                             return_final_state)
+                qkv, final_conv = conv4_silu(qkv_in, self.conv_weight, conv_state, return_final_state)
             else:
-                qkv, final_conv = conv4_silu_segmented(row[..., :offsets[3]], self.conv_weight, packed_segments,
+                qkv, final_conv = conv4_silu_segmented(qkv_in, self.conv_weight, packed_segments,
                                                        conv_state, return_final_state)
             q_raw, key_raw, value_raw = qkv.split(sizes[:3], dim=-1)
         else:
