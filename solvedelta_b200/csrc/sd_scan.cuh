@@ -65,8 +65,8 @@ constexpr size_t SCAN_SMEM_BYTES =
     (size_t(4) * CL * LDP + size_t(3) * CL * LDT + size_t(DP) * LDT) * sizeof(float);
 
 // FP32 panels, TF32 contractions: the two forward scans (no second update pair).
-// Panels of chunk step+1 are in flight (cp.async, two-deep ring) during the whole
-// of step, so the serial chain never waits for HBM.
+// Panels of chunk step+1 are in flight (cp.async, two-slot ring) during the whole
+// of step, so the serial chain never waits for HBM; two barriers per step.
 __global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan(ScanParams p) {
     extern __shared__ __align__(16) float smem[];
     float* sQ = smem;                   // [2][CL][LDP]
@@ -110,7 +110,6 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan(ScanParams p) {
         cp_async_commit();
     };
     issue(0);
-    issue(1);
 
     for (int step = 0; step < p.NC; ++step) {
         const long long gi = chunk_at(step);
@@ -147,8 +146,11 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan(ScanParams p) {
                 }
             }
         }
-        cp_async_wait<1>();  // everything but the newest group: this step's panels have landed
+        cp_async_wait<0>();  // this step's panels have landed
         __syncthreads();
+        // every warp is past the previous step, so its ring slot is free: the next step's panels
+        // stream in during the whole of this one
+        issue(step + 1);
         // X = P + Q St : warp tile 16 rows x NS/2 columns
         {
             float acc[SCAN_G1][4];
@@ -181,8 +183,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan(ScanParams p) {
             warp_mma<SCAN_NS / 8>(st, warp * 16, 0, 0, CL, [&](int c, int j) { return bR[j * LDP + c]; },
                                   [&](int j, int n) { return sX[j * LDT + n]; });
         }
-        __syncthreads();  // this step's ring slot and sX are free again
-        issue(step + 2);
+        // no barrier here: the next step's first barrier orders these reads before anything is overwritten
     }
     cp_async_wait<0>();
 
@@ -294,7 +295,6 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan_b(ScanParamsB p)
         cp_commit();
     };
     issue(0);
-    issue(1);
 
     for (int step = 0; step < p.NC; ++step) {
         const long long gi = chunk_at(step);
@@ -318,8 +318,9 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan_b(ScanParamsB p)
                 *reinterpret_cast<__nv_bfloat162*>(ck + row_b * DP + col0 + cc) = vb;
             }
         }
-        cp_wait<1>();
+        cp_wait<0>();
         __syncthreads();
+        issue(step + 1);   // the previous step's ring slot is free: prefetch during the whole of this step
         {
             float acc[SCAN_G1][4];
             acc_zero<SCAN_G1>(acc);
@@ -345,8 +346,6 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan_b(ScanParamsB p)
             warp_mma_bf16<SCAN_NS / 8, true, false>(st, bR, LDB, sX, LDTB, warp * 16, 0, 0, CL);
             if (has2) warp_mma_bf16<SCAN_NS / 8, true, false>(st, bR2, LDB, bX2, LDTB, warp * 16, 0, 0, CL);
         }
-        __syncthreads();
-        issue(step + 2);
     }
     cp_wait<0>();
 
