@@ -158,6 +158,12 @@ const char *sd_launch_name(int index);
  */
 void sd_debug_timeline(void *device_buffer);
 
+/* Waits for the device and returns its fault word: 0 when every bounded wait
+ * inside the kernels completed, 1 or 2 when a tensor-core completion barrier
+ * of the state scan ran out of polls (the results of that launch are then
+ * undefined), -1 when the device could not be read. */
+int sd_device_fault(void);
+
 /*
  * Introspection for tests: offset and size of a named intermediate panel
  * inside the saved (which = 0), forward-scratch (1) or backward-scratch (2)

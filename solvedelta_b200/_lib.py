@@ -137,7 +137,7 @@ EXPORTS = (
     "sd_saved_bytes", "sd_forward_scratch_bytes", "sd_backward_scratch_bytes",
     "sd_forward", "sd_backward", "sd_decode_step", "sd_forward_launches",
     "sd_backward_launches", "sd_panel_info", "sd_status_string", "sd_version",
-    "sd_chunk_tokens", "sd_profile_step", "sd_launch_name", "sd_forward_static", "sd_panel_kind", "sd_debug_timeline",
+    "sd_chunk_tokens", "sd_profile_step", "sd_launch_name", "sd_forward_static", "sd_panel_kind", "sd_debug_timeline", "sd_device_fault",
     "sd_conv4_backward_scratch_bytes", "sd_conv4_silu_forward", "sd_conv4_silu_backward",
     "sd_kda_gate_backward_scratch_bytes", "sd_kda_gate_forward", "sd_kda_gate_backward",
     "sd_norm_gate_backward_scratch_bytes", "sd_norm_gate_forward", "sd_norm_gate_backward",
@@ -186,6 +186,8 @@ def load() -> ctypes.CDLL:
                          ("sd_norm_gate_forward", NormGateArgs), ("sd_norm_gate_backward", NormGateArgs)):
         getattr(lib, name).restype = ctypes.c_int
         getattr(lib, name).argtypes = [ctypes.POINTER(struct), ctypes.c_void_p]
+    lib.sd_device_fault.restype = ctypes.c_int
+    lib.sd_device_fault.argtypes = []
     lib.sd_debug_timeline.restype = None
     lib.sd_debug_timeline.argtypes = [ctypes.c_void_p]
     lib.sd_panel_kind.restype = ctypes.c_int

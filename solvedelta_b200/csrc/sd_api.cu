@@ -1,6 +1,7 @@
 // C ABI of the SolveDelta chunked recurrence for B200 (sm_100a).
 // Declarations and the upstream interfaces they replace: include/solvedelta_b200.h
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "../../include/solvedelta_b200.h"
@@ -10,6 +11,7 @@
 #include "sd_forward.cuh"
 #include "sd_mixer.cuh"
 #include "sd_scan.cuh"
+#include "sd_scan_tc.cuh"
 
 namespace {
 
@@ -107,6 +109,16 @@ Operand make_operand(const sd_operand& o, int elem_bytes) {
 
 long long* g_dbg = nullptr;  // set by sd_debug_timeline (diagnostic)
 
+// Fault word of the tensor-memory scan: a bounded mbarrier wait that ran out stores 1 (first
+// contraction) or 2 (second) here; sd_device_fault reads it back.
+__device__ int g_scan_fault_word = 0;
+int* g_scan_fault_ptr[64] = {};
+int* scan_fault_ptr() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    return g_scan_fault_ptr[dev];
+}
+
 // True when every strided operand admits 16-byte vector access and the head
 // widths are multiples of eight: the kernels then use their branch-free loaders.
 bool all_fast(const Operand* ops, int n, const sd_shape& s) {
@@ -152,7 +164,12 @@ cudaError_t configure_kernels() {
     if ((e = allow_smem(k_exterior_prep_fwd<false>, EXT_PREP_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_output_fwd<true>, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_output_fwd<false>, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_state_scan, SCAN_SMEM_BYTES)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_state_scan_tc, SCAN_TC_SMEM_BYTES)) != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) {
+        void* w = nullptr;
+        if ((e = cudaGetSymbolAddress(&w, g_scan_fault_word)) != cudaSuccess) return e;
+        g_scan_fault_ptr[dev] = static_cast<int*>(w);
+    }
     if ((e = allow_smem(k_state_scan_b, SCAN_B_SMEM_BYTES)) != cudaSuccess) return e;
     if ((e = allow_smem(k_exterior_prep_bwd<true>, EXT_PREP_BWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_exterior_prep_bwd<false>, EXT_PREP_BWD_SMEM)) != cudaSuccess) return e;
@@ -307,7 +324,7 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
         sp.ckb = bpanel_at(kSaved, s, a->saved, "CtCkB");
         sp.init = a->C0; sp.fin = a->C_T;
         sp.NC = p.g.NC; sp.reverse = 0; sp.transposed_io = 1; sp.nrows = s->r; sp.ncols = s->r;
-        k_state_scan<<<scan_grid, SCAN_THREADS, SCAN_SMEM_BYTES, stream>>>(sp);
+        k_state_scan_tc<<<scan_grid, TC_THREADS, SCAN_TC_SMEM_BYTES, stream>>>(sp, scan_fault_ptr(), g_dbg ? g_dbg + 16 * 1 : nullptr);
     mark(stream);
     }
     set_dbg(p.g, 2, chunks);
@@ -324,7 +341,7 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
         sp.lam = p.Lam; sp.X = nullptr; sp.ck = nullptr; sp.Xb = p.Zt; sp.ckb = p.SCk;
         sp.init = a->S0; sp.fin = a->S_T;
         sp.NC = p.g.NC; sp.reverse = 0; sp.transposed_io = 0; sp.nrows = s->r; sp.ncols = s->V;
-        k_state_scan<<<scan_grid, SCAN_THREADS, SCAN_SMEM_BYTES, stream>>>(sp);
+        k_state_scan_tc<<<scan_grid, TC_THREADS, SCAN_TC_SMEM_BYTES, stream>>>(sp, scan_fault_ptr(), g_dbg ? g_dbg + 16 * 4 : nullptr);
     mark(stream);
     }
     set_dbg(p.g, 5, chunks);
@@ -431,6 +448,13 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
 }
 
 void sd_debug_timeline(void* device_buffer) { g_dbg = reinterpret_cast<long long*>(device_buffer); }
+
+int sd_device_fault(void) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    int word = 0;
+    if (cudaMemcpyFromSymbol(&word, g_scan_fault_word, sizeof(int)) != cudaSuccess) return -1;
+    return word;
+}
 
 const char* sd_launch_name(int index) {
     const int n = (int)(sizeof(kLaunchNames) / sizeof(kLaunchNames[0]));

@@ -239,6 +239,16 @@ __device__ __forceinline__ uint32_t f2tf32(float x) {
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ float round_tf32(float x) { return __uint_as_float(f2tf32(x)); }
+// a [CL][DP] shared panel to global memory, rounded to TF32 on the way
+__device__ __forceinline__ void s2g_panel_tf32(float* g, const float* sm) {
+    for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += NTHREADS) {
+        int i = idx >> 5, c4 = (idx & 31) << 2;
+        float4 v = *reinterpret_cast<const float4*>(sm + i * LDP + c4);
+        *reinterpret_cast<float4*>(g + i * DP + c4) =
+            make_float4(round_tf32(v.x), round_tf32(v.y), round_tf32(v.z), round_tf32(v.w));
+    }
+}
 __device__ __forceinline__ void mma_tf32(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
     asm volatile(

@@ -201,7 +201,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
         float4 GL = *reinterpret_cast<const float4*>(s_G + (CL - 1) * LDP + c4);
         *reinterpret_cast<float4*>(gUpd + i * DP + c4) = up;
         *reinterpret_cast<float4*>(gG + i * DP + c4) = G;
-        *reinterpret_cast<float4*>(gQc + i * DP + c4) = make_float4(-w.x, -w.y, -w.z, -w.w);
+        // contraction operands of the state scan leave here already rounded to TF32
+        *reinterpret_cast<float4*>(gQc + i * DP + c4) =
+            make_float4(round_tf32(-w.x), round_tf32(-w.y), round_tf32(-w.z), round_tf32(-w.w));
         *reinterpret_cast<float4*>(gUbar + i * DP + c4) =
             make_float4(uh.x * __expf(GL.x - G.x), uh.y * __expf(GL.y - G.y), uh.z * __expf(GL.z - G.z),
                         uh.w * __expf(GL.w - G.w));
@@ -461,7 +463,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
     SD_PHASE(p.g, ph);
     trisolve_blocked<false, false>(s_aed, -1.f, PanelF32{s_ag, s_z});
     SD_PHASE(p.g, ph);
-    s2g_panel(panel_ptr(p.Wd, ch.gi), s_ag);
+    s2g_panel_tf32(panel_ptr(p.Wd, ch.gi), s_ag);   // a contraction operand of the state scan
     s2g_panel(panel_ptr(p.Ud, ch.gi), s_z);
     SD_PHASE(p.g, ph);
 }

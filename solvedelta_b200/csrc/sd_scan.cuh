@@ -7,9 +7,10 @@
 // St is a [DP][NS] column slice of the carried state (the predictor state is
 // carried transposed, St[c][a] = C[a][c], so that both C and S decay by rows).
 // Column slices never exchange data, so a stream is split over DP/NS CTAs.
-// The slice lives in tensor-core accumulator registers for the whole
-// sequence; panels of the next chunk stream in through cp.async while the
-// current contraction runs.
+// The two forward scans (FP32 panels, TF32 contractions) run on tensor memory,
+// k_state_scan_tc; the two reverse scans (BF16 panels) keep the slice in
+// mma.sync accumulator registers, k_state_scan_b below.  In both, panels of the
+// next chunk stream in through cp.async while the current contraction runs.
 #pragma once
 #include "sd_bf16.cuh"
 #include "sd_common.cuh"
@@ -19,7 +20,6 @@ namespace sd {
 constexpr int SCAN_NS = 64;            // state columns per CTA (2 CTAs per stream)
 constexpr int SCAN_G1 = SCAN_NS / 16;  // 8-column tiles per warp in X = P + Q St
 constexpr int SCAN_THREADS = 256;      // 8 warps: one 16-row strip of the state slice each
-constexpr int LDT = SCAN_NS + 8;       // pitch of [*][NS] shared buffers
 
 struct ScanParams {
     const float* P;    // [chunks][CL][DP]
@@ -46,164 +46,6 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N));
-}
-
-__device__ __forceinline__ void async_panel(float* sm, const float* g) {
-    for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += SCAN_THREADS) {
-        int i = idx >> 5, c4 = (idx & 31) << 2;
-        cp_async16(sm + i * LDP + c4, g + i * DP + c4);
-    }
-}
-__device__ __forceinline__ void async_slice(float* sm, const float* g, int col0) {
-    for (int idx = threadIdx.x; idx < CL * (SCAN_NS / 4); idx += SCAN_THREADS) {
-        int i = idx / (SCAN_NS / 4), c4 = (idx % (SCAN_NS / 4)) << 2;
-        cp_async16(sm + i * LDT + c4, g + i * DP + col0 + c4);
-    }
-}
-
-constexpr size_t SCAN_SMEM_BYTES =
-    (size_t(4) * CL * LDP + size_t(3) * CL * LDT + size_t(DP) * LDT) * sizeof(float);
-
-// FP32 panels, TF32 contractions: the two forward scans (no second update pair).
-// Panels of chunk step+1 are in flight (cp.async, two-slot ring) during the whole
-// of step, so the serial chain never waits for HBM; two barriers per step.
-__global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan(ScanParams p) {
-    extern __shared__ __align__(16) float smem[];
-    float* sQ = smem;                   // [2][CL][LDP]
-    float* sR = sQ + 2 * CL * LDP;      // [2][CL][LDP]
-    float* sP = sR + 2 * CL * LDP;      // [2][CL][LDT]
-    float* sX = sP + 2 * CL * LDT;      // [CL][LDT]
-    float* sSt = sX + CL * LDT;         // [DP][LDT]
-
-    const int col0 = blockIdx.x * SCAN_NS;
-    const int s = blockIdx.y;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const long long base = (long long)s * p.NC;
-
-    // state slice: warp owns rows [16*warp, 16*warp+16), all NS columns
-    float st[SCAN_NS / 8][4];
-    const int row_a = warp * 16 + g, row_b = row_a + 8;
-#pragma unroll
-    for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            int rr = (e < 2) ? row_a : row_b;
-            int cc = col0 + nt * 8 + 2 * t + (e & 1);
-            float v = 0.f;
-            if (p.init != nullptr && rr < p.nrows && cc < p.ncols) {
-                const float* src = p.init + (long long)s * p.nrows * p.ncols;
-                v = p.transposed_io ? src[(long long)cc * p.nrows + rr] : src[(long long)rr * p.ncols + cc];
-            }
-            st[nt][e] = v;
-        }
-    }
-
-    auto chunk_at = [&](int step) { return base + (p.reverse ? (p.NC - 1 - step) : step); };
-    auto issue = [&](int step) {
-        if (step < p.NC) {
-            const long long gi = chunk_at(step);
-            const int b = step & 1;
-            async_panel(sQ + b * CL * LDP, panel_ptr(p.Q, gi));
-            async_slice(sP + b * CL * LDT, panel_ptr(p.P, gi), col0);
-            async_panel(sR + b * CL * LDP, panel_ptr(p.R, gi));
-        }
-        cp_async_commit();
-    };
-    issue(0);
-
-    for (int step = 0; step < p.NC; ++step) {
-        const long long gi = chunk_at(step);
-        const float* bQ = sQ + (step & 1) * CL * LDP;
-        const float* bR = sR + (step & 1) * CL * LDP;
-        const float* bP = sP + (step & 1) * CL * LDT;
-        const float la = p.lam[gi * DP + row_a], lb = p.lam[gi * DP + row_b];
-        // publish the state slice: shared copy for the contraction, global checkpoint
-        {
-#pragma unroll
-            for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
-                int cc = nt * 8 + 2 * t;
-                *reinterpret_cast<float2*>(sSt + row_a * LDT + cc) = make_float2(st[nt][0], st[nt][1]);
-                *reinterpret_cast<float2*>(sSt + row_b * LDT + cc) = make_float2(st[nt][2], st[nt][3]);
-            }
-            if (p.ckb != nullptr) {  // BF16 copy for the consumers that only contract in BF16
-                bf16* ck = p.ckb + gi * (long long)(DP * DP);
-#pragma unroll
-                for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
-                    int cc = nt * 8 + 2 * t;
-                    *reinterpret_cast<__nv_bfloat162*>(ck + row_a * DP + col0 + cc) =
-                        __floats2bfloat162_rn(st[nt][0], st[nt][1]);
-                    *reinterpret_cast<__nv_bfloat162*>(ck + row_b * DP + col0 + cc) =
-                        __floats2bfloat162_rn(st[nt][2], st[nt][3]);
-                }
-            }
-            if (p.ck != nullptr) {
-                float* ck = state_ptr(p.ck, gi);
-#pragma unroll
-                for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
-                    int cc = nt * 8 + 2 * t;
-                    *reinterpret_cast<float2*>(ck + row_a * DP + col0 + cc) = make_float2(st[nt][0], st[nt][1]);
-                    *reinterpret_cast<float2*>(ck + row_b * DP + col0 + cc) = make_float2(st[nt][2], st[nt][3]);
-                }
-            }
-        }
-        cp_async_wait<0>();  // this step's panels have landed
-        __syncthreads();
-        // every warp is past the previous step, so its ring slot is free: the next step's panels
-        // stream in during the whole of this one
-        issue(step + 1);
-        // X = P + Q St : warp tile 16 rows x NS/2 columns
-        {
-            float acc[SCAN_G1][4];
-            acc_zero<SCAN_G1>(acc);
-            const int r0 = (warp & 3) * 16, n0 = (warp >> 2) * (SCAN_NS / 2);
-            warp_mma<SCAN_G1>(acc, r0, n0, 0, DP, [&](int i, int k) { return bQ[i * LDP + k]; },
-                              [&](int k, int n) { return sSt[k * LDT + n]; });
-            float* xg = p.X != nullptr ? panel_ptr(p.X, gi) : nullptr;
-            bf16* xb = p.Xb != nullptr ? bpanel_ptr(p.Xb, gi) : nullptr;
-            warp_epi<SCAN_G1>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
-                float2 pv = *reinterpret_cast<const float2*>(bP + i * LDT + j);
-                float2 xv = make_float2(pv.x + v0, pv.y + v1);
-                *reinterpret_cast<float2*>(sX + i * LDT + j) = xv;
-                if (xb != nullptr)
-                    *reinterpret_cast<__nv_bfloat162*>(xb + i * DP + col0 + j) = __floats2bfloat162_rn(xv.x, xv.y);
-                else
-                    *reinterpret_cast<float2*>(xg + i * DP + col0 + j) = xv;
-            });
-        }
-        __syncthreads();
-        // St = lam St + R^T X : warp tile 16 state rows x NS columns
-        {
-#pragma unroll
-            for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
-                st[nt][0] *= la;
-                st[nt][1] *= la;
-                st[nt][2] *= lb;
-                st[nt][3] *= lb;
-            }
-            warp_mma<SCAN_NS / 8>(st, warp * 16, 0, 0, CL, [&](int c, int j) { return bR[j * LDP + c]; },
-                                  [&](int j, int n) { return sX[j * LDT + n]; });
-        }
-        // no barrier here: the next step's first barrier orders these reads before anything is overwritten
-    }
-    cp_async_wait<0>();
-
-    if (p.fin != nullptr) {
-        float* dst = p.fin + (long long)s * p.nrows * p.ncols;
-#pragma unroll
-        for (int nt = 0; nt < SCAN_NS / 8; ++nt) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                int rr = (e < 2) ? row_a : row_b;
-                int cc = col0 + nt * 8 + 2 * t + (e & 1);
-                if (rr < p.nrows && cc < p.ncols) {
-                    if (p.transposed_io)
-                        dst[(long long)cc * p.nrows + rr] = st[nt][e];
-                    else
-                        dst[(long long)rr * p.ncols + cc] = st[nt][e];
-                }
-            }
-        }
-    }
 }
 
 }  // namespace sd

@@ -1,0 +1,371 @@
+// The forward chunk-state scan on the fifth-generation tensor cores (tcgen05).
+//
+// Same recurrence, ScanParams and launch grid as k_state_scan:
+//     X  = P + Q * St ;  checkpoint St ;  St = diag(lam) St + R^T X
+// A CTA carries a [DP][NS] column slice of one stream's state.  The slice
+// lives in tensor memory as the accumulator of the update contraction (lane =
+// state row p, column = slice column c); the step's X is a second
+// accumulator, held transposed (lane = slice column, column = token):
+//     X^T[c][tok] = sum_p St[p][c] * Q[tok][p]       M=128 (64 used) N=64 K=128
+//     St [p][c]  += sum_t R[tok][p] * X[tok][c]      M=128           N=64 K=64
+// All four operands are K-major in shared memory, in the unswizzled canonical
+// layout of 8 x 16-byte core matrices (the first contraction's M is padded to
+// 128: rows 64..127 of its A operand alias whatever follows in shared memory
+// and only feed accumulator lanes nobody reads).  Q [tok][p] is staged by
+// cp.async as it lies.  X^T is written by the thread that holds the row after
+// tcgen05.ld, four consecutive tokens to a 16-byte chunk.  The state, held by
+// rows, is written element by element into the transposed operand, with the
+// K-chunk pitch padded to 144 bytes so that a warp's 32 rows hit 32 banks.
+// R [tok][p], whose contraction index is the slow one in global memory, is
+// turned through registers: each thread loads one column of it, coalesced
+// over the warp, and writes it as 16-byte chunks of its own row.  The decay
+// diag(lam) is one scalar per thread, applied on the way back into tensor
+// memory; checkpoints and X go to global memory from the same registers.
+// Operands are rounded to TF32 (round to nearest) before the tensor core,
+// which would truncate, sees them: the state, X and R in registers here, Q by
+// the kernels that write the Q panels.
+//
+// Every mbarrier wait is bounded: a wait that runs out raises the fault word
+// the host reads back, the thread stops waiting for the rest of the launch,
+// and the kernel still walks to its end and frees its tensor memory.
+#pragma once
+#include "sd_scan.cuh"
+
+namespace sd {
+
+constexpr int TC_THREADS = 256;           // 8 warps: lane quarter = warp % 4, column half = warp / 4
+constexpr int TC_TMEM_COLS = 128;         // 64 state-slice columns + 64 X^T columns
+constexpr int TC_X_COL = SCAN_NS;         // first tensor-memory column of X^T
+constexpr unsigned TC_CORE = 128;         // bytes of one 8 x 16-byte core matrix
+constexpr unsigned TC_KP_SBO = (DP / 4) * TC_CORE;  // K = state rows (Q, state): bytes between 8-row groups
+constexpr unsigned TC_KT_SBO = (CL / 4) * TC_CORE;  // K = tokens (X, R): bytes between 8-row groups
+constexpr unsigned TC_PANEL_BYTES = CL * DP * 4;    // one [CL][DP] or [DP][CL] operand
+constexpr unsigned TC_S_LBO = TC_CORE + 16;         // padded K-chunk pitch of the transposed state operand
+constexpr unsigned TC_S_SBO = (DP / 4) * TC_S_LBO;  // its bytes between 8-row groups
+constexpr unsigned TC_S_BYTES = (SCAN_NS / 8) * TC_S_SBO;   // the 64 rows that are written
+constexpr unsigned TC_X_BYTES = SCAN_NS * CL * 4;
+// Q ring, state operand, X operand, R operand.  The padded A operand of the first contraction reaches
+// 2 * TC_S_BYTES past the start of the state operand, which must stay inside this allocation.
+constexpr size_t SCAN_TC_SMEM_BYTES = size_t(2) * TC_PANEL_BYTES + TC_S_BYTES + TC_X_BYTES + TC_PANEL_BYTES;
+static_assert(2 * TC_S_BYTES <= TC_S_BYTES + TC_X_BYTES + TC_PANEL_BYTES, "padded operand rows leave the allocation");
+constexpr int TC_WAIT_LIMIT = 1 << 20;    // polls of one mbarrier before the wait is given up
+
+__device__ __forceinline__ unsigned tc_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+// Shared-memory matrix descriptor, no swizzle: start address, leading and stride byte offsets in 16-byte units.
+__device__ __forceinline__ unsigned long long tc_desc(unsigned addr, unsigned lbo, unsigned sbo) {
+    return (unsigned long long)((addr >> 4) & 0x3FFF) | ((unsigned long long)((lbo >> 4) & 0x3FFF) << 16) |
+           ((unsigned long long)((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46);
+}
+// Instruction descriptor: FP32 accumulator, TF32 operands, both K-major, M = 128.
+__device__ __forceinline__ unsigned tc_idesc(int n) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((unsigned)(n >> 3) << 17) | ((128u >> 4) << 24);
+}
+__device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned long long da, unsigned long long db, unsigned idesc,
+                                       unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Bounded wait on one phase of an mbarrier; false when the limit ran out.
+__device__ __forceinline__ bool tc_wait(unsigned bar, unsigned parity) {
+    for (int it = 0; it < TC_WAIT_LIMIT; ++it) {
+        unsigned ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+// 32 consecutive 32-bit tensor-memory columns of this thread's lane.
+__device__ __forceinline__ void tc_ld32(unsigned taddr, float* r) {
+    unsigned* u = reinterpret_cast<unsigned*>(r);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31}, [%32];"
+        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
+          "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]), "=r"(u[16]),
+          "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]), "=r"(u[24]),
+          "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tc_st32(unsigned taddr, const float* r) {
+    const unsigned* u = reinterpret_cast<const unsigned*>(r);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31};" ::"r"(u[0]),
+        "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]), "r"(u[8]), "r"(u[9]), "r"(u[10]),
+        "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15]), "r"(u[16]), "r"(u[17]), "r"(u[18]), "r"(u[19]),
+        "r"(u[20]), "r"(u[21]), "r"(u[22]), "r"(u[23]), "r"(u[24]), "r"(u[25]), "r"(u[26]), "r"(u[27]), "r"(u[28]),
+        "r"(u[29]), "r"(u[30]), "r"(u[31]), "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// One full 32-byte sector per thread (256-bit store; the address is 32-byte aligned).
+__device__ __forceinline__ void tc_store32(void* g, const unsigned (&w)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(g), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                 "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                 : "memory");
+}
+
+__device__ __forceinline__ float tc_round(float x) { return __uint_as_float(f2tf32(x)); }
+
+// Chunk walk of the staged Q panel: chunk (tok, p4) -> core matrix (tok/8, p4), row tok%8.  The eight
+// lanes of a quarter warp take the eight rows of one core matrix (128 contiguous bytes: one pass over
+// the banks), the four quarter warps four neighbouring K chunks (64 contiguous bytes of each global row).
+__device__ __forceinline__ void tc_q_chunk(int idx, int& tok, int& p4) {
+    const int l = idx & 31, r = idx >> 5;
+    tok = (r >> 3) * 8 + (l & 7);
+    p4 = (r & 7) * 4 + (l >> 3);
+}
+__device__ __forceinline__ void tc_stage_q(unsigned char* sm, const float* g) {
+    for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += TC_THREADS) {
+        int tok, p4;
+        tc_q_chunk(idx, tok, p4);
+        cp_async16(sm + (tok >> 3) * TC_KP_SBO + p4 * TC_CORE + (tok & 7) * 16, g + tok * DP + p4 * 4);
+    }
+}
+
+// Diagnostic: thread 0 of CTA (0,0) records the SM clock at the phase boundaries of its ninth step.
+#define TC_STAMP(k)                                                                              \
+    do {                                                                                         \
+        if (dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0 && step == 8)       \
+            dbg[k] = clock64();                                                                  \
+    } while (0)
+
+__global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, int* fault, long long* dbg) {
+    extern __shared__ __align__(128) unsigned char tsm[];
+    unsigned char* sQ = tsm;                          // [2] B of the first contraction (rows = tokens, K = state rows)
+    unsigned char* sS = sQ + 2 * TC_PANEL_BYTES;      // A of the first: slice^T        (rows = slice columns, K = state rows)
+    unsigned char* sX = sS + TC_S_BYTES;              // B of the second: X^T           (rows = slice columns, K = tokens)
+    unsigned char* sR = sX + TC_X_BYTES;              // A of the second: R^T           (rows = state rows, K = tokens)
+    __shared__ __align__(8) unsigned long long bars[2];
+    __shared__ unsigned s_tmem;
+
+    const int col0 = blockIdx.x * SCAN_NS;
+    const int s = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quarter = warp & 3, half = warp >> 2;
+    // This thread's tensor-memory lane: state row p for the state accumulator and for the R column
+    // it turns; slice column c for the X^T accumulator (lanes 0..63 only).
+    const int row = quarter * 32 + lane;
+    const bool has_x = quarter < 2;
+    const long long base = (long long)s * p.NC;
+
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&bars[0])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&bars[1])));
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(&s_tmem)),
+                     "r"(TC_TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    auto chunk_at = [&](int step) { return base + (p.reverse ? (p.NC - 1 - step) : step); };
+    auto issue = [&](int step) {
+        if (step < p.NC) tc_stage_q(sQ + (step & 1) * TC_PANEL_BYTES, panel_ptr(p.Q, chunk_at(step)));
+        cp_async_commit();
+    };
+    issue(0);
+
+    // this thread's part of the slice: state row `row`, slice columns [32*half, 32*half+32)
+    float st[32];
+    const int c0 = half * 32;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        float v = 0.f;
+        int cc = col0 + c0 + j;
+        if (p.init != nullptr && row < p.nrows && cc < p.ncols) {
+            const float* src = p.init + (long long)s * p.nrows * p.ncols;
+            v = p.transposed_io ? src[(long long)cc * p.nrows + row] : src[(long long)row * p.ncols + cc];
+        }
+        st[j] = v;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tbase = s_tmem;
+    const unsigned t_state = tbase + ((unsigned)(quarter * 32) << 16) + c0;
+    const unsigned t_x = tbase + ((unsigned)(quarter * 32) << 16) + TC_X_COL + half * 32;
+    const unsigned bar1 = tc_smem(&bars[0]), bar2 = tc_smem(&bars[1]);
+    const unsigned idesc = tc_idesc(SCAN_NS);   // N = 64 for both: tokens, then slice columns
+    const unsigned own_row = (row >> 3) * TC_KT_SBO + (row & 7) * 16;                 // this thread's row of sR (and sX)
+    const unsigned own_col = (row >> 2) * TC_S_LBO + (row & 3) * 4;                   // its K position in the state operand
+    bool alive = true;   // cleared by the first wait that runs out
+
+    cp_async_wait<0>();
+
+    for (int step = 0; step < p.NC; ++step) {
+        const long long gi = chunk_at(step);
+        const int b = step & 1;
+        TC_STAMP(0);
+        const float lam = p.lam[gi * DP + row];
+        // the slice, transposed and rounded, as this step's A operand
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const int c = c0 + j;
+            *reinterpret_cast<float*>(sS + (c >> 3) * TC_S_SBO + (c & 7) * 16 + own_col) = tc_round(st[j]);
+        }
+        tc_fence_async_smem();
+        tc_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+            const unsigned aS = tc_smem(sS), bQ = tc_smem(sQ + b * TC_PANEL_BYTES);
+#pragma unroll
+            for (int ks = 0; ks < DP / 8; ++ks)
+                tc_mma(tbase + TC_X_COL, tc_desc(aS + ks * 2 * TC_S_LBO, TC_S_LBO, TC_S_SBO),
+                       tc_desc(bQ + ks * 2 * TC_CORE, TC_CORE, TC_KP_SBO), idesc, ks > 0);
+            tc_commit(bar1);
+        }
+        __syncwarp();
+        TC_STAMP(1);
+        // behind the first contraction: prefetch, this thread's R (and P) values, checkpoints, decay
+        issue(step + 1);
+        if (step + 2 < p.NC) {   // R and the P slice of the step after next: one 128-byte line per thread
+            const long long gn = chunk_at(step + 2);
+            prefetch_l2(reinterpret_cast<const char*>(panel_ptr(p.R, gn)) + tid * 128);
+            if (tid < 2 * CL)
+                prefetch_l2(reinterpret_cast<const char*>(panel_ptr(p.P, gn) + (tid >> 1) * DP + col0) + (tid & 1) * 128);
+        }
+        float rv[32], pv[32];
+        {
+            const float* rg = panel_ptr(p.R, gi) + (half * 32) * DP + row;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) rv[j] = rg[j * DP];
+            if (has_x) {
+                const float* pg = panel_ptr(p.P, gi) + (half * 32) * DP + col0 + row;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) pv[j] = pg[j * DP];
+            }
+        }
+        TC_STAMP(2);
+        if (p.ckb != nullptr) {
+            bf16* ck = p.ckb + gi * (long long)(DP * DP) + row * DP + col0 + c0;
+#pragma unroll
+            for (int j16 = 0; j16 < 2; ++j16) {
+                unsigned w[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(st[16 * j16 + 2 * e], st[16 * j16 + 2 * e + 1]);
+                    w[e] = *reinterpret_cast<unsigned*>(&h2);
+                }
+                tc_store32(ck + 16 * j16, w);
+            }
+        }
+        if (p.ck != nullptr) {
+            float* ck = state_ptr(p.ck, gi) + row * DP + col0 + c0;
+#pragma unroll
+            for (int j8 = 0; j8 < 4; ++j8) {
+                unsigned w[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) w[e] = __float_as_uint(st[8 * j8 + e]);
+                tc_store32(ck + 8 * j8, w);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) st[j] *= lam;
+        TC_STAMP(3);
+        tc_st32(t_state, st);
+        tc_wait_st();
+        TC_STAMP(4);
+        // R^T as the second contraction's A operand (the previous step's second contraction has completed)
+#pragma unroll
+        for (int j4 = 0; j4 < 8; ++j4) {
+            float4 v = make_float4(tc_round(rv[4 * j4]), tc_round(rv[4 * j4 + 1]), tc_round(rv[4 * j4 + 2]),
+                                   tc_round(rv[4 * j4 + 3]));
+            *reinterpret_cast<float4*>(sR + own_row + (half * 8 + j4) * TC_CORE) = v;
+        }
+
+        TC_STAMP(5);
+        if (alive && !tc_wait(bar1, step & 1)) {
+            alive = false;
+            atomicExch(fault, 1);
+        }
+        tc_fence_after();
+        TC_STAMP(6);
+        if (has_x) {   // warp-uniform: lanes 0..63 of the X^T accumulator
+            float x[32];
+            tc_ld32(t_x, x);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) x[j] += pv[j];
+            if (p.Xb != nullptr) {
+                bf16* xb = bpanel_ptr(p.Xb, gi) + (half * 32) * DP + col0 + row;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) xb[j * DP] = __float2bfloat16_rn(x[j]);
+            } else {
+                float* xg = panel_ptr(p.X, gi) + (half * 32) * DP + col0 + row;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) xg[j * DP] = x[j];
+            }
+#pragma unroll
+            for (int j4 = 0; j4 < 8; ++j4) {
+                float4 v = make_float4(tc_round(x[4 * j4]), tc_round(x[4 * j4 + 1]), tc_round(x[4 * j4 + 2]),
+                                       tc_round(x[4 * j4 + 3]));
+                *reinterpret_cast<float4*>(sX + own_row + (half * 8 + j4) * TC_CORE) = v;
+            }
+        }
+        tc_fence_async_smem();
+        tc_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+            const unsigned aR = tc_smem(sR), bX = tc_smem(sX);
+#pragma unroll
+            for (int ks = 0; ks < CL / 8; ++ks)
+                tc_mma(tbase, tc_desc(aR + ks * 2 * TC_CORE, TC_CORE, TC_KT_SBO),
+                       tc_desc(bX + ks * 2 * TC_CORE, TC_CORE, TC_KT_SBO), idesc, 1u);
+            tc_commit(bar2);
+        }
+        __syncwarp();
+        TC_STAMP(7);
+        cp_async_wait<0>();   // the next step's panels, in flight since the top of this step
+        TC_STAMP(8);
+        if (alive && !tc_wait(bar2, step & 1)) {
+            alive = false;
+            atomicExch(fault, 2);
+        }
+        tc_fence_after();
+        tc_ld32(t_state, st);
+        tc_wait_ld();
+        TC_STAMP(9);
+    }
+
+    if (p.fin != nullptr) {
+        float* dst = p.fin + (long long)s * p.nrows * p.ncols;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            int cc = col0 + c0 + j;
+            if (row < p.nrows && cc < p.ncols) {
+                if (p.transposed_io)
+                    dst[(long long)cc * p.nrows + row] = st[j];
+                else
+                    dst[(long long)row * p.ncols + cc] = st[j];
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tbase), "r"(TC_TMEM_COLS));
+}
+
+}  // namespace sd

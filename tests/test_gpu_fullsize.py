@@ -96,3 +96,12 @@ def test_single_streams_of_the_full_run_match_the_checker(workload, b, h):
     gC = grads[9][b:b + 1, h:h + 1].cpu().numpy()
     gS = grads[10][b:b + 1, h:h + 1].cpu().numpy()
     assert rel_l2(gC, ref["C0"]) <= 3e-2 and rel_l2(gS, ref["S0"]) <= 3e-2
+
+
+@pytest.mark.gpu
+def test_no_bounded_wait_ran_out(workload):
+    """Every device-side wait of the kernels is bounded; none of them may have given up during a full-size run."""
+    from solvedelta_b200 import _lib
+
+    _run(workload[1])
+    assert _lib.load().sd_device_fault() == 0
