@@ -249,11 +249,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, i
         {
             const float* rg = panel_ptr(p.R, gi) + (half * 32) * DP + row;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) rv[j] = rg[j * DP];
+            for (int j = 0; j < 32; ++j) rv[j] = __ldcg(rg + j * DP);
             if (has_x) {
                 const float* pg = panel_ptr(p.P, gi) + (half * 32) * DP + col0 + row;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) pv[j] = pg[j * DP];
+                for (int j = 0; j < 32; ++j) pv[j] = __ldcg(pg + j * DP);
             }
         }
         TC_STAMP(2);
@@ -314,7 +314,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, i
             } else {
                 float* xg = panel_ptr(p.X, gi) + (half * 32) * DP + col0 + row;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) xg[j * DP] = x[j];
+                for (int j = 0; j < 32; ++j) __stcg(xg + j * DP, x[j]);
             }
 #pragma unroll
             for (int j4 = 0; j4 < 8; ++j4) {
