@@ -10,6 +10,8 @@ from ._lib import build, load
 from .config import SolveDeltaConfig
 from .mixer_ops import conv4_silu, conv4_silu_segmented, kda_decay_gate, rms_norm_gated
 from .model import RMSNormGated, SolveDelta, SolveDeltaLayerState
+from .modeling import (SolveDeltaBlock, SolveDeltaCache, SolveDeltaCacheAdapter, SolveDeltaForCausalLM,
+                       SolveDeltaMLP, SolveDeltaModel)
 from .packing import PackedSegments, build_packed_segments, pack_tokens, unpack_tokens
 from .ops import (
     SolveDeltaState,
@@ -20,6 +22,12 @@ from .ops import (
 )
 
 __all__ = [
+    "SolveDeltaBlock",
+    "SolveDeltaCache",
+    "SolveDeltaCacheAdapter",
+    "SolveDeltaForCausalLM",
+    "SolveDeltaMLP",
+    "SolveDeltaModel",
     "SolveDelta",
     "SolveDeltaConfig",
     "SolveDeltaLayerState",

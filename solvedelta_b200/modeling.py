@@ -1,0 +1,347 @@
+"""The causal LM around the SolveDelta mixer and its decode cache.
+
+Mirror of upstream ``causallsso/modeling_solvedelta.py:31-501`` for
+attention-free models: the same module tree and parameter names
+(``model.embeddings``, ``model.layers.N.{mixer_norm,mixer.mixer,mlp_norm,mlp}``,
+``model.norm``, ``lm_head``), so an upstream ``state_dict`` loads as it is; the
+same packed gate/up MLP, pre-norm residual blocks, label shift and loss; the
+same cache entries per layer, ``{"recurrent_state": (C, S), "conv_state":
+[B, D, 3]}``.  The mixer is this package's CUDA one, everything around it is
+PyTorch (cuBLAS GEMMs, elementwise glue): activations are BF16 on a CUDA
+device, and there is no CPU path.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from .config import SolveDeltaConfig
+from .ops import SolveDeltaState
+from .model import SolveDelta, SolveDeltaLayerState
+
+FP32_PARAMETERS = ("geometry_write_bias", "associative_log_rate", "associative_decay_bias")
+
+
+class SolveDeltaCache:
+    """Per-layer decode state (the part of upstream's FLA ``Cache`` this model uses,
+    modeling_solvedelta.py:104-115,184-192): ``cache[layer]`` is a dict with
+    ``recurrent_state`` = (C [B,H,r,r], S [B,H,r,V]) and ``conv_state`` [B,D,3]."""
+
+    def __init__(self) -> None:
+        self.states: List[Dict[str, Any]] = []
+        self._seen_tokens = 0
+
+    @classmethod
+    def from_legacy_cache(cls, past: Optional[Sequence[Dict[str, Any]]] = None) -> "SolveDeltaCache":
+        cache = cls()
+        if past is not None:
+            cache.states = [dict(state) for state in past]
+        return cache
+
+    def to_legacy_cache(self) -> Tuple[Dict[str, Any], ...]:
+        return tuple(self.states)
+
+    def __getitem__(self, layer_idx: int) -> Dict[str, Any]:
+        if layer_idx >= len(self.states):
+            raise KeyError(f"Cache only has {len(self.states)} layers, attempted to access layer {layer_idx}")
+        return self.states[layer_idx]
+
+    def __len__(self) -> int:
+        return len(self.states)
+
+    def __iter__(self):
+        return iter(self.states)
+
+    def get_seq_length(self, layer_idx: int = 0) -> int:
+        return self._seen_tokens if len(self.states) > layer_idx else 0
+
+    def update(self, layer_idx: int, recurrent_state, conv_state, offset: int = 1) -> Dict[str, Any]:
+        if layer_idx == 0:
+            self._seen_tokens += offset
+        state = {"recurrent_state": recurrent_state, "attn_state": None, "conv_state": conv_state,
+                 "ffn_state": None}
+        if layer_idx < len(self.states):
+            self.states[layer_idx] = state
+        elif layer_idx == len(self.states):
+            self.states.append(state)
+        else:
+            raise ValueError("cache layers must be filled in order")
+        return state
+
+
+def _state_from_cache(last_state: Optional[Dict[str, Any]]) -> Optional[SolveDeltaLayerState]:
+    if last_state is None:
+        return None
+    recurrent_state = last_state.get("recurrent_state")
+    if recurrent_state is None:
+        return None
+    if not isinstance(recurrent_state, (tuple, list)) or len(recurrent_state) != 2:
+        raise ValueError("SolveDelta cache recurrent_state must contain (predictor,S)")
+    return SolveDeltaLayerState(operator=SolveDeltaState(*recurrent_state), conv=last_state.get("conv_state"))
+
+
+def segment_reset_mask(hidden_states: torch.Tensor, cu_seqlens: torch.Tensor) -> torch.Tensor:
+    """Reset mask of a packed batch [1,T,D]: True at every sequence start (modeling_solvedelta.py:118-134)."""
+    if hidden_states.shape[0] != 1:
+        raise ValueError("explicit cu_seqlens require packed hidden states [1,T,D]")
+    if cu_seqlens.ndim != 1 or cu_seqlens.numel() < 2:
+        raise ValueError("cu_seqlens must be one-dimensional with at least two entries")
+    if cu_seqlens.dtype not in (torch.int32, torch.int64):
+        raise TypeError("cu_seqlens must have int32 or int64 dtype")
+    starts = cu_seqlens[:-1].to(device=hidden_states.device, dtype=torch.long)
+    reset_mask = torch.zeros((1, hidden_states.shape[1]), dtype=torch.bool, device=hidden_states.device)
+    return reset_mask.scatter(1, starts.unsqueeze(0), True)
+
+
+class SolveDeltaMLP(nn.Module):
+    """Gated MLP with one common-input gate/up projection (modeling_solvedelta.py:31-101)."""
+
+    def __init__(self, hidden_size: int, hidden_ratio: Optional[int] = None,
+                 intermediate_size: Optional[int] = None, hidden_act: str = "swish",
+                 powglu_power: float = 3.0) -> None:
+        super().__init__()
+        if hidden_ratio is None:
+            hidden_ratio = 4
+        if intermediate_size is None:
+            intermediate_size = int(hidden_size * hidden_ratio * 2 / 3)
+            intermediate_size = 256 * ((intermediate_size + 255) // 256)
+        if hidden_act not in ("swish", "powlu"):
+            raise ValueError(f"Unsupported hidden_act: {hidden_act}")
+        self.hidden_size = hidden_size
+        self.hidden_ratio = hidden_ratio
+        self.intermediate_size = intermediate_size
+        self.hidden_act = hidden_act
+        self.powglu_power = powglu_power
+        self.gate_up_proj = nn.Linear(hidden_size, 2 * intermediate_size, bias=False)
+        self.down_proj = nn.Linear(intermediate_size, hidden_size, bias=False)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        gate, value = self.gate_up_proj(x).chunk(2, dim=-1)
+        if self.hidden_act == "swish":
+            activated = F.silu(gate)
+        else:
+            sigmoid = torch.sigmoid(gate)
+            positive = gate > 0
+            safe = torch.where(positive, gate, torch.ones_like(gate))
+            exponent = self.powglu_power / (torch.sqrt(safe) + 1.0)
+            activated = torch.where(positive, torch.exp(exponent * torch.log(safe)) * sigmoid, gate * sigmoid)
+        return self.down_proj(activated * value)
+
+
+class SolveDeltaCacheAdapter(nn.Module):
+    """Layer/cache boundary around the mixer (modeling_solvedelta.py:137-194): attention mask ->
+    valid mask, ``cu_seqlens`` -> reset mask, cache entry <-> ``SolveDeltaLayerState``."""
+
+    def __init__(self, config: SolveDeltaConfig, layer_idx: int) -> None:
+        super().__init__()
+        self.layer_idx = layer_idx
+        self.mixer = SolveDelta(config)
+
+    def forward(self, hidden_states: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
+                past_key_values: Optional[SolveDeltaCache] = None, use_cache: Optional[bool] = False,
+                **kwargs) -> Tuple[torch.Tensor, Optional[SolveDeltaCache]]:
+        batch, length, _ = hidden_states.shape
+        last_state = None
+        if past_key_values is not None and len(past_key_values) > self.layer_idx:
+            last_state = past_key_values[self.layer_idx]
+        initial_state = _state_from_cache(last_state)
+
+        valid_mask = None
+        if attention_mask is not None:
+            if attention_mask.ndim != 2 or attention_mask.shape[0] != batch:
+                raise ValueError("attention_mask must have shape [B,T]")
+            if attention_mask.shape[1] < length:
+                raise ValueError("attention_mask is shorter than the current input")
+            valid_mask = attention_mask[:, -length:].to(torch.bool)
+
+        reset_mask = kwargs.get("solvedelta_reset_mask")
+        cu_seqlens = kwargs.get("cu_seqlens")
+        if reset_mask is None and cu_seqlens is not None:
+            reset_mask = segment_reset_mask(hidden_states, cu_seqlens)
+        if reset_mask is not None:
+            if reset_mask.shape != (batch, length) or reset_mask.dtype != torch.bool:
+                raise ValueError("solvedelta_reset_mask must be bool [B,T]")
+            if initial_state is not None and cu_seqlens is not None:
+                reset_mask = reset_mask.clone()
+                reset_mask[0, 0] = False
+
+        cache_requested = bool(use_cache and past_key_values is not None)
+        result = self.mixer(hidden_states, initial_state=initial_state, valid_mask=valid_mask,
+                            reset_mask=reset_mask, return_final_state=cache_requested)
+        if cache_requested:
+            output, final_state = result
+            past_key_values.update(self.layer_idx, recurrent_state=tuple(final_state.operator),
+                                   conv_state=final_state.conv, offset=length)
+        else:
+            output = result
+        return output, past_key_values
+
+
+class SolveDeltaBlock(nn.Module):
+    """Pre-norm residual block: mixer, then MLP (modeling_solvedelta.py:197-255)."""
+
+    def __init__(self, config: SolveDeltaConfig, layer_idx: int) -> None:
+        super().__init__()
+        self.config = config
+        self.layer_idx = layer_idx
+        self.mixer_norm = nn.RMSNorm(config.hidden_size, eps=config.norm_eps)
+        self.mixer = SolveDeltaCacheAdapter(config, layer_idx)
+        self.mlp_norm = nn.RMSNorm(config.hidden_size, eps=config.norm_eps)
+        self.mlp = SolveDeltaMLP(hidden_size=config.hidden_size, hidden_ratio=config.hidden_ratio,
+                                 intermediate_size=config.intermediate_size, hidden_act=config.hidden_act)
+
+    def forward(self, hidden_states: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
+                past_key_values: Optional[SolveDeltaCache] = None, use_cache: Optional[bool] = False,
+                **kwargs) -> Tuple[torch.Tensor, Optional[SolveDeltaCache]]:
+        residual = hidden_states
+        hidden_states = self.mixer_norm(hidden_states)
+        hidden_states, past_key_values = self.mixer(hidden_states, attention_mask=attention_mask,
+                                                    past_key_values=past_key_values, use_cache=use_cache,
+                                                    **kwargs)
+        hidden_states = residual + hidden_states
+        residual = hidden_states
+        hidden_states = self.mlp(self.mlp_norm(hidden_states))
+        return residual + hidden_states, past_key_values
+
+
+@dataclass
+class SolveDeltaModelOutput:
+    last_hidden_state: torch.Tensor
+    past_key_values: Optional[SolveDeltaCache] = None
+    hidden_states: Optional[Tuple[torch.Tensor, ...]] = None
+
+
+@dataclass
+class SolveDeltaCausalLMOutput:
+    loss: Optional[torch.Tensor] = None
+    logits: Optional[torch.Tensor] = None
+    past_key_values: Optional[SolveDeltaCache] = None
+    hidden_states: Optional[Tuple[torch.Tensor, ...]] = None
+
+
+class SolveDeltaModel(nn.Module):
+    """Embedding, the stack of blocks, final norm (modeling_solvedelta.py:283-397)."""
+
+    def __init__(self, config: SolveDeltaConfig) -> None:
+        super().__init__()
+        self.config = config
+        self.padding_idx = config.pad_token_id
+        self.vocab_size = config.vocab_size
+        self.embeddings = nn.Embedding(config.vocab_size, config.hidden_size, self.padding_idx)
+        self.layers = nn.ModuleList(SolveDeltaBlock(config, i) for i in range(config.num_hidden_layers))
+        self.norm = nn.RMSNorm(config.hidden_size, eps=config.norm_eps)
+
+    def forward(self, input_ids: Optional[torch.Tensor] = None, attention_mask: Optional[torch.Tensor] = None,
+                inputs_embeds: Optional[torch.Tensor] = None,
+                past_key_values: Union[SolveDeltaCache, Sequence[Dict[str, Any]], None] = None,
+                use_cache: Optional[bool] = None, output_hidden_states: bool = False,
+                **kwargs) -> SolveDeltaModelOutput:
+        if input_ids is not None and inputs_embeds is not None:
+            raise ValueError("specify either input_ids or inputs_embeds, not both")
+        if input_ids is None and inputs_embeds is None:
+            raise ValueError("input_ids or inputs_embeds is required")
+        if use_cache is None:
+            use_cache = self.config.use_cache if not self.training else False
+        hidden_states = self.embeddings(input_ids) if inputs_embeds is None else inputs_embeds
+        if use_cache and not isinstance(past_key_values, SolveDeltaCache):
+            past_key_values = SolveDeltaCache.from_legacy_cache(past_key_values)
+        elif not use_cache:
+            past_key_values = None
+        cu_seqlens = kwargs.get("cu_seqlens")
+        if cu_seqlens is not None and "solvedelta_reset_mask" not in kwargs:
+            kwargs["solvedelta_reset_mask"] = segment_reset_mask(hidden_states, cu_seqlens)
+        collected = () if output_hidden_states else None
+        for layer in self.layers:
+            if output_hidden_states:
+                collected += (hidden_states,)
+            hidden_states, past_key_values = layer(hidden_states, attention_mask=attention_mask,
+                                                   past_key_values=past_key_values, use_cache=use_cache,
+                                                   **kwargs)
+        hidden_states = self.norm(hidden_states)
+        if output_hidden_states:
+            collected += (hidden_states,)
+        return SolveDeltaModelOutput(hidden_states, past_key_values, collected)
+
+
+class SolveDeltaForCausalLM(nn.Module):
+    """Language-model head, label shift and loss over ``SolveDeltaModel``
+    (modeling_solvedelta.py:400-501).  ``prepare()`` puts a freshly built or loaded
+    model into the layout the CUDA mixer wants: BF16 weights on the device, the three
+    scalar parameter families of every mixer kept in FP32."""
+
+    ignore_index = -100
+
+    def __init__(self, config: SolveDeltaConfig) -> None:
+        super().__init__()
+        self.config = config
+        self.model = SolveDeltaModel(config)
+        self.vocab_size = config.vocab_size
+        self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
+        self.apply(self._init_weights)
+        if config.tie_word_embeddings:
+            self.lm_head.weight = self.model.embeddings.weight
+
+    def _init_weights(self, module: nn.Module) -> None:
+        if isinstance(module, nn.Linear):
+            nn.init.normal_(module.weight, mean=0.0, std=self.config.initializer_range)
+            if module.bias is not None:
+                nn.init.zeros_(module.bias)
+        elif isinstance(module, nn.Embedding):
+            nn.init.normal_(module.weight, mean=0.0, std=self.config.initializer_range)
+            if module.padding_idx is not None:
+                with torch.no_grad():
+                    module.weight[module.padding_idx].zero_()
+
+    def prepare(self, device: Union[str, torch.device] = "cuda") -> "SolveDeltaForCausalLM":
+        self.to(device)
+        for name, parameter in self.named_parameters():
+            keep = name.rsplit(".", 1)[-1] in FP32_PARAMETERS
+            parameter.data = parameter.data.to(torch.float32 if keep else torch.bfloat16)
+        return self
+
+    def get_input_embeddings(self):
+        return self.model.embeddings
+
+    def get_output_embeddings(self):
+        return self.lm_head
+
+    def forward(self, input_ids: Optional[torch.Tensor] = None, attention_mask: Optional[torch.Tensor] = None,
+                inputs_embeds: Optional[torch.Tensor] = None,
+                past_key_values: Union[SolveDeltaCache, Sequence[Dict[str, Any]], None] = None,
+                labels: Optional[torch.Tensor] = None, use_cache: Optional[bool] = None,
+                output_hidden_states: bool = False, logits_to_keep: Optional[int] = 0,
+                **kwargs) -> SolveDeltaCausalLMOutput:
+        outputs = self.model(input_ids=input_ids, attention_mask=attention_mask, inputs_embeds=inputs_embeds,
+                             past_key_values=past_key_values, use_cache=use_cache,
+                             output_hidden_states=output_hidden_states, **kwargs)
+        hidden_states = outputs.last_hidden_state
+        keep_all = labels is not None or logits_to_keep in (None, 0)
+        logits = self.lm_head(hidden_states if keep_all else hidden_states[:, -logits_to_keep:])
+        loss = None
+        if labels is not None:
+            labels = labels.to(hidden_states.device)
+            shifted = torch.cat((labels[..., 1:], torch.full_like(labels[:, :1], self.ignore_index)), dim=1)
+            loss = F.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), shifted.reshape(-1),
+                                   ignore_index=self.ignore_index)
+        return SolveDeltaCausalLMOutput(loss, logits, outputs.past_key_values, outputs.hidden_states)
+
+    @torch.no_grad()
+    def generate(self, input_ids: torch.Tensor, max_new_tokens: int) -> torch.Tensor:
+        """Greedy decoding through the cache: one prefill, then one-token steps."""
+        step = self(input_ids=input_ids, use_cache=True, logits_to_keep=1)
+        cache, tokens = step.past_key_values, [input_ids]
+        for _ in range(max_new_tokens):
+            nxt = step.logits[:, -1].argmax(dim=-1, keepdim=True)
+            tokens.append(nxt)
+            step = self(input_ids=nxt, past_key_values=cache, use_cache=True, logits_to_keep=1)
+            cache = step.past_key_values
+        return torch.cat(tokens, dim=1)
+
+
+__all__ = ["SolveDeltaBlock", "SolveDeltaCache", "SolveDeltaCacheAdapter", "SolveDeltaCausalLMOutput",
+           "SolveDeltaForCausalLM", "SolveDeltaMLP", "SolveDeltaModel", "SolveDeltaModelOutput",
+           "segment_reset_mask"]

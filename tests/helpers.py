@@ -11,9 +11,9 @@ OPERANDS = ("u", "h", "q", "keys", "values", "log_decay", "erase", "write", "geo
 
 
 def golden_names():
-    """Operator-level vectors (the mixer_* files hold whole-module vectors, see mixer_helpers)."""
+    """Operator-level vectors (the mixer_* and model_* files hold whole-module vectors)."""
     names = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
-    return [n for n in names if not n.startswith("mixer_")]
+    return [n for n in names if not n.startswith(("mixer_", "model_"))]
 
 
 def load_golden(name):

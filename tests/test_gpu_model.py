@@ -1,0 +1,186 @@
+"""The causal LM on the GPU: against the vectors upstream's own model produced (tiny
+configuration), against the numpy checker on BF16-rounded weights, and through the
+properties upstream tests on the full model (cached continuation == single pass,
+packed sequences == separate sequences)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle.model_oracle import ModelOracle
+from solvedelta_b200 import SolveDeltaConfig, SolveDeltaForCausalLM
+from solvedelta_b200.modeling import FP32_PARAMETERS
+from tests.helpers import load_golden, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+# Relative L2 of whole tensors.  Activations and weights are BF16 end to end: on the tiny golden
+# configuration (64 wide) the numpy checker, made to round where the device stores BF16, already
+# sits 2.5e-2 from upstream's FP64 logits, so the device is held to 2e-2 against that checker and
+# to 4e-2 against the FP64 vectors; gradients cross the model twice (measured 2e-2 to 7e-2, the
+# decay-gate families of the first layer, where the operator's admissible error meets cancellation,
+# 1.2e-1) and are held to 1.5e-1 with the direction (cosine) to 0.99.
+LOGIT_TOL = 2e-2
+FP64_LOGIT_TOL = 4e-2
+GRAD_TOL = 1.5e-1
+GRAD_COS = 0.99
+
+
+def _bf16_round(a):
+    return torch.from_numpy(np.asarray(a, dtype=np.float64)).to(torch.bfloat16).double().numpy()
+
+
+@pytest.fixture(scope="module")
+def tiny():
+    z = load_golden("model_tiny")
+    cfg = {k[4:]: z[k].item() for k in z if k.startswith("cfg_")}
+    params = {k[6:]: z[k] for k in z if k.startswith("param_")}
+    model = SolveDeltaForCausalLM(SolveDeltaConfig(**cfg))
+    model.load_state_dict({k: torch.from_numpy(v) for k, v in params.items()}, strict=True)
+    model.prepare("cuda")
+    rounded = {k: (v if k.rsplit(".", 1)[-1] in FP32_PARAMETERS else _bf16_round(v)) for k, v in params.items()}
+    return z, cfg, params, rounded, model
+
+
+def test_prepare_keeps_scalar_families_in_fp32(tiny):
+    *_, model = tiny
+    for name, p in model.named_parameters():
+        want = torch.float32 if name.rsplit(".", 1)[-1] in FP32_PARAMETERS else torch.bfloat16
+        assert p.dtype == want and p.is_cuda, name
+
+
+def test_logits_and_loss_match_upstream_vectors(tiny):
+    z, cfg, params, rounded, model = tiny
+    ids = torch.from_numpy(z["input_ids"]).cuda()
+    model.train()
+    out = model(input_ids=ids, labels=ids)
+    logits = out.logits.detach().float().cpu().numpy()
+    assert rel_l2(logits, z["logits"]) < FP64_LOGIT_TOL
+    assert abs(out.loss.item() - float(z["loss"])) < 3e-2
+    # the checker on the weights the device really holds, rounding where the device stores BF16
+    want, want_loss, _ = ModelOracle(rounded, cfg, activation_rounding=_bf16_round).forward(
+        z["input_ids"], labels=z["input_ids"])
+    assert rel_l2(logits, want) < LOGIT_TOL
+    assert abs(out.loss.item() - want_loss) < 1e-2
+
+
+def test_parameter_gradients_match_upstream_vectors(tiny):
+    z, cfg, params, rounded, model = tiny
+    ids = torch.from_numpy(z["input_ids"]).cuda()
+    model.train()
+    model.zero_grad(set_to_none=True)
+    model(input_ids=ids, labels=ids).loss.backward()
+    report, bad = [], []
+    for name, p in model.named_parameters():
+        want = z["pgrad_" + name].astype(np.float64)
+        got = p.grad.double().cpu().numpy()
+        err = rel_l2(got, want)
+        cos = float((got * want).sum() / max(np.linalg.norm(got) * np.linalg.norm(want), 1e-300))
+        report.append(f"{name:55s} rel={err:.3e} cos={cos:.5f}")
+        if err > GRAD_TOL or cos < GRAD_COS:
+            bad.append(name)
+    print("\n".join(report))
+    assert not bad, "gradients off: " + ", ".join(bad) + "\n" + "\n".join(report)
+
+
+def test_cached_steps_match_upstream_vectors(tiny):
+    z, cfg, params, rounded, model = tiny
+    ids = torch.from_numpy(z["input_ids"]).cuda()
+    prefill = int(z["prefill"])
+    model.eval()
+    with torch.no_grad():
+        step = model(input_ids=ids[:, :prefill], use_cache=True)
+        cache, pieces = step.past_key_values, [step.logits]
+        for t in range(prefill, ids.shape[1]):
+            step = model(input_ids=ids[:, t:t + 1], past_key_values=cache, use_cache=True)
+            cache = step.past_key_values
+            pieces.append(step.logits)
+    got = torch.cat(pieces, dim=1).float().cpu().numpy()
+    assert rel_l2(got, z["logits_cached"]) < FP64_LOGIT_TOL
+    assert cache.get_seq_length() == ids.shape[1] and len(cache) == cfg["num_hidden_layers"]
+    for layer in range(cfg["num_hidden_layers"]):
+        C, S = cache[layer]["recurrent_state"]
+        assert C.dtype == torch.float32 and S.dtype == torch.float32
+        # twelve tokens of BF16 inputs into 16-wide states
+        assert rel_l2(C.cpu().numpy(), z[f"cache_{layer}_C"]) < 6e-2
+        assert rel_l2(S.cpu().numpy(), z[f"cache_{layer}_S"]) < 6e-2
+        assert rel_l2(cache[layer]["conv_state"].float().cpu().numpy(), z[f"cache_{layer}_conv"]) < 2e-2
+
+
+@pytest.fixture(scope="module")
+def medium():
+    torch.manual_seed(5)
+    config = SolveDeltaConfig(hidden_size=256, num_heads=2, head_k_dim=64, head_v_dim=128, num_hidden_layers=3,
+                              vocab_size=512, initializer_range=0.05)
+    return config, SolveDeltaForCausalLM(config).prepare("cuda").eval()
+
+
+def test_cached_continuation_equals_single_pass(medium):
+    """Prefill, a block, then one-token steps reproduce the single pass (upstream tests/model:235-301)."""
+    config, model = medium
+    ids = torch.randint(0, config.vocab_size, (2, 300), device="cuda")
+    with torch.no_grad():
+        full = model(input_ids=ids).logits.float()
+        step = model(input_ids=ids[:, :200], use_cache=True)
+        cache, pieces = step.past_key_values, [step.logits]
+        step = model(input_ids=ids[:, 200:290], past_key_values=cache, use_cache=True)
+        pieces.append(step.logits)
+        for t in range(290, 300):
+            step = model(input_ids=ids[:, t:t + 1], past_key_values=step.past_key_values, use_cache=True)
+            pieces.append(step.logits)
+    got = torch.cat(pieces, dim=1).float()
+    assert rel_l2(got.cpu().numpy(), full.cpu().numpy()) < LOGIT_TOL
+    assert (got.argmax(-1) == full.argmax(-1)).float().mean().item() > 0.97
+
+
+def test_packed_sequences_equal_separate_sequences(medium):
+    config, model = medium
+    lengths = [70, 130, 45]
+    seqs = [torch.randint(0, config.vocab_size, (1, n), device="cuda") for n in lengths]
+    packed = torch.cat(seqs, dim=1)
+    cu = torch.tensor([0, 70, 200, 245], dtype=torch.int32, device="cuda")
+    with torch.no_grad():
+        together = model(input_ids=packed, cu_seqlens=cu).logits.float()
+        apart = torch.cat([model(input_ids=s).logits.float() for s in seqs], dim=1)
+    assert rel_l2(together.cpu().numpy(), apart.cpu().numpy()) < LOGIT_TOL
+
+
+def test_padding_mask_leaves_valid_tokens_unchanged(medium):
+    config, model = medium
+    ids = torch.randint(0, config.vocab_size, (2, 96), device="cuda")
+    mask = torch.ones(2, 96, dtype=torch.bool, device="cuda")
+    mask[1, :20] = False  # left padding on the second row
+    with torch.no_grad():
+        masked = model(input_ids=ids, attention_mask=mask).logits.float()
+        alone = model(input_ids=ids[1:, 20:]).logits.float()
+    assert rel_l2(masked[1:, 20:].cpu().numpy(), alone.cpu().numpy()) < LOGIT_TOL
+
+
+def test_greedy_generation_follows_the_single_pass(medium):
+    config, model = medium
+    prompt = torch.randint(0, config.vocab_size, (2, 50), device="cuda")
+    out = model.generate(prompt, max_new_tokens=6)
+    assert out.shape == (2, 56) and torch.equal(out[:, :50], prompt)
+    with torch.no_grad():
+        logits = model(input_ids=out[:, :-1]).logits.float()
+    # each generated token is (up to BF16 ties) the argmax of the single pass over its prefix
+    agree = (logits[:, 49:].argmax(-1) == out[:, 50:]).float().mean().item()
+    assert agree >= 5 / 6
+
+
+def test_training_step_reduces_the_loss(medium):
+    config, _ = medium
+    torch.manual_seed(9)
+    model = SolveDeltaForCausalLM(config).prepare("cuda").train()
+    ids = torch.randint(0, config.vocab_size, (2, 128), device="cuda")
+    master = [p.detach().float().clone() for p in model.parameters()]
+    losses = []
+    for _ in range(8):
+        model.zero_grad(set_to_none=True)
+        loss = model(input_ids=ids, labels=ids).loss
+        loss.backward()
+        losses.append(loss.item())
+        with torch.no_grad():
+            for p, m in zip(model.parameters(), master):
+                m.add_(p.grad.float(), alpha=-0.05)
+                p.copy_(m.to(p.dtype))
+    assert all(np.isfinite(losses)) and losses[-1] < losses[0] - 0.05, losses
