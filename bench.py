@@ -407,6 +407,111 @@ def time_mixer_module(B, T, H, r, V, device, reps=5):
                      "fwd + bwd (input and all parameter gradients)"}
 
 
+def time_causal_lm(device, train_steps=3, decode_steps=256):
+    """The reference's 24-layer model (hidden 1024, 8 heads of 128/128, conv4, vocabulary 32000, random
+    init) through this package's causal LM: one training step (B=8, T=2048: forward, loss, backward,
+    fused AdamW on FP32 master weights, BF16 copy back) and long-context serving (prefill of 32768 random
+    tokens at B=1, then one-token cached steps).  Uniform random token ids, as the reference's do."""
+    import torch
+
+    from solvedelta_b200 import SolveDeltaConfig, SolveDeltaForCausalLM
+
+    torch.manual_seed(0)
+    config = SolveDeltaConfig(hidden_size=1024, num_heads=8, head_k_dim=128, head_v_dim=128,
+                              num_hidden_layers=24, vocab_size=32000)
+    model = SolveDeltaForCausalLM(config).prepare(device).train()
+    params = list(model.parameters())
+    master = [p.detach().float().clone().requires_grad_() for p in params]
+    optimizer = torch.optim.AdamW(master, lr=1e-4, fused=True)
+    B, T = 8, 2048
+    ids = torch.randint(0, config.vocab_size, (B, T), device=device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def train_step():
+        for p in params:
+            p.grad = None
+        loss = model(input_ids=ids, labels=ids).loss
+        loss.backward()
+        for m, p in zip(master, params):
+            m.grad = p.grad.float()
+        optimizer.step()
+        with torch.no_grad():
+            for m, p in zip(master, params):
+                p.copy_(m)
+        return loss
+
+    for _ in range(2):
+        train_step()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(train_steps):
+        loss = train_step()
+    e1.record()
+    torch.cuda.synchronize()
+    train_ms = e0.elapsed_time(e1) / train_steps
+    peak_gb = torch.cuda.max_memory_allocated(device) / 2 ** 30
+    out = {"parameters": sum(p.numel() for p in params),
+           "train": {"ms_per_step": round(train_ms, 1), "value": round(B * T / (train_ms * 1e-3), 1),
+                     "unit": "tokens/s", "shape": f"B={B}, T={T}, fwd + loss + bwd + AdamW (FP32 master weights)",
+                     "loss": round(float(loss), 4), "peak_memory_gib": round(peak_gb, 1)}}
+    del optimizer, master
+    for p in params:
+        p.grad = None
+    model.eval()
+    torch.cuda.empty_cache()
+    prompt = torch.randint(0, config.vocab_size, (1, 32768), device=device)
+    with torch.no_grad():
+        model(input_ids=prompt[:, :4096], use_cache=True, logits_to_keep=1)   # warm-up
+        torch.cuda.synchronize()
+        e0.record()
+        step = model(input_ids=prompt, use_cache=True, logits_to_keep=1)
+        e1.record()
+        torch.cuda.synchronize()
+        prefill_ms = e0.elapsed_time(e1)
+        cache = step.past_key_values
+        token = step.logits[:, -1].argmax(-1, keepdim=True)
+        for _ in range(8):
+            step = model(input_ids=token, past_key_values=cache, use_cache=True, logits_to_keep=1)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(decode_steps):
+            step = model(input_ids=token, past_key_values=cache, use_cache=True, logits_to_keep=1)
+            token = step.logits[:, -1].argmax(-1, keepdim=True)
+        e1.record()
+        torch.cuda.synchronize()
+        decode_ms = e0.elapsed_time(e1) / decode_steps
+        from solvedelta_b200 import GraphedDecoder
+
+        decoder = GraphedDecoder(model, cache, 1)
+        for _ in range(8):
+            decoder.step(token)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(decode_steps):
+            token = decoder.step(token)[:, -1].argmax(-1, keepdim=True)
+        e1.record()
+        torch.cuda.synchronize()
+        graphed_ms = e0.elapsed_time(e1) / decode_steps
+    del cache, decoder, step
+    torch.cuda.empty_cache()
+    wide = torch.randint(0, config.vocab_size, (16, 32768), device=device)
+    with torch.no_grad():
+        e0.record()
+        model(input_ids=wide, use_cache=True, logits_to_keep=1)
+        e1.record()
+        torch.cuda.synchronize()
+    wide_ms = e0.elapsed_time(e1)
+    out["prefill_b16"] = {"ms": round(wide_ms, 1), "value": round(16 * 32768 / (wide_ms * 1e-3), 1), "unit": "tokens/s",
+                          "shape": "B=16, T=32768, last-token logits",
+                          "peak_memory_gib": round(torch.cuda.max_memory_allocated(device) / 2 ** 30, 1)}
+    out["prefill"] = {"ms": round(prefill_ms, 1), "value": round(32768 / (prefill_ms * 1e-3), 1), "unit": "tokens/s",
+                      "shape": "B=1, T=32768, last-token logits"}
+    out["decode"] = {"ms_per_token": round(decode_ms, 3), "value": round(1.0 / (decode_ms * 1e-3), 1),
+                     "unit": "tokens/s", "shape": f"B=1, {decode_steps} cached one-token steps after the prefill",
+                     "graphed_ms_per_token": round(graphed_ms, 3), "graphed_value": round(1.0 / (graphed_ms * 1e-3), 1)}
+    return out
+
+
 def run_ours(opts, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -582,6 +687,10 @@ def run_ours(opts, rank, world, local_rank):
         ms0 = e0.elapsed_time(e1) / 10
         gamma_zero = {"ms_per_step": ms0, "value": runner0.tokens / (ms0 * 1e-3), "unit": "tokens/s"}
         del runner0
+    causal_lm = None
+    if world == 1 and not opts.skip_glue and not opts.skip_model:
+        torch.cuda.empty_cache()
+        causal_lm = time_causal_lm(device)
 
     if rank == 0:
         cpu_baseline = None
@@ -606,7 +715,7 @@ def run_ours(opts, rank, world, local_rank):
             "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu_baseline,
             "forward_only": {"ms_per_step": fwd_ms, "value": job_throughput(runner.tokens, fwd_ms * 1e-3, world),
                              "unit": "tokens/s"},
-            "mixer_glue": glue, "mixer_module": mixer, "gamma_zero": gamma_zero,
+            "mixer_glue": glue, "mixer_module": mixer, "gamma_zero": gamma_zero, "causal_lm": causal_lm,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -625,6 +734,7 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg (profiler captures)")
     ap.add_argument("--skip-glue", action="store_true", help="skip the mixer glue kernels (profiler captures)")
+    ap.add_argument("--skip-model", action="store_true", help="skip the 24-layer causal LM legs")
     opts = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -10,7 +10,7 @@ from ._lib import build, load
 from .config import SolveDeltaConfig
 from .mixer_ops import conv4_silu, conv4_silu_segmented, kda_decay_gate, rms_norm_gated
 from .model import RMSNormGated, SolveDelta, SolveDeltaLayerState
-from .modeling import (SolveDeltaBlock, SolveDeltaCache, SolveDeltaCacheAdapter, SolveDeltaForCausalLM,
+from .modeling import (GraphedDecoder, SolveDeltaBlock, SolveDeltaCache, SolveDeltaCacheAdapter, SolveDeltaForCausalLM,
                        SolveDeltaMLP, SolveDeltaModel)
 from .packing import PackedSegments, build_packed_segments, pack_tokens, unpack_tokens
 from .ops import (
@@ -22,6 +22,7 @@ from .ops import (
 )
 
 __all__ = [
+    "GraphedDecoder",
     "SolveDeltaBlock",
     "SolveDeltaCache",
     "SolveDeltaCacheAdapter",

@@ -330,18 +330,85 @@ class SolveDeltaForCausalLM(nn.Module):
         return SolveDeltaCausalLMOutput(loss, logits, outputs.past_key_values, outputs.hidden_states)
 
     @torch.no_grad()
-    def generate(self, input_ids: torch.Tensor, max_new_tokens: int) -> torch.Tensor:
-        """Greedy decoding through the cache: one prefill, then one-token steps."""
+    def generate(self, input_ids: torch.Tensor, max_new_tokens: int, graphed: bool = False) -> torch.Tensor:
+        """Greedy decoding through the cache: one prefill, then one-token steps (replayed from a
+        CUDA graph when ``graphed``)."""
         step = self(input_ids=input_ids, use_cache=True, logits_to_keep=1)
         cache, tokens = step.past_key_values, [input_ids]
+        logits = step.logits
+        decoder = GraphedDecoder(self, cache, input_ids.shape[0]) if graphed and max_new_tokens > 0 else None
         for _ in range(max_new_tokens):
-            nxt = step.logits[:, -1].argmax(dim=-1, keepdim=True)
+            nxt = logits[:, -1].argmax(dim=-1, keepdim=True)
             tokens.append(nxt)
-            step = self(input_ids=nxt, past_key_values=cache, use_cache=True, logits_to_keep=1)
-            cache = step.past_key_values
+            if decoder is not None:
+                logits = decoder.step(nxt)
+            else:
+                logits = self(input_ids=nxt, past_key_values=cache, use_cache=True, logits_to_keep=1).logits
         return torch.cat(tokens, dim=1)
 
 
-__all__ = ["SolveDeltaBlock", "SolveDeltaCache", "SolveDeltaCacheAdapter", "SolveDeltaCausalLMOutput",
+class GraphedDecoder:
+    """One-token cached steps replayed from a CUDA graph.
+
+    A decode step is a few hundred small launches (24 layers of projections, glue kernels and the
+    one-token operator kernel), so its cost at small batch is launch and host time.  The step is captured
+    once on static buffers (token ids in, logits out, the cache updated in place inside the graph) and
+    replayed per token.  Build it from the cache a prefill returned; ``cache`` stays valid and current."""
+
+    def __init__(self, model: "SolveDeltaForCausalLM", cache: SolveDeltaCache, batch: int) -> None:
+        self.model = model
+        device = next(model.parameters()).device
+        self.token = torch.zeros(batch, 1, dtype=torch.long, device=device)
+        self.cache = cache
+        # static storage for every state; the cache entries point at it from now on
+        self.static = []
+        for state in cache.states:
+            C, S = state["recurrent_state"]
+            entry = (C.clone(), S.clone(), None if state["conv_state"] is None else state["conv_state"].clone())
+            self.static.append(entry)
+        self._point_cache_at_static()
+        seen = cache._seen_tokens
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side), torch.no_grad():
+            backup = [tuple(None if t is None else t.clone() for t in entry) for entry in self.static]
+            for _ in range(2):          # warm-up: lazy initialisation must not fall inside the capture
+                self._step()
+            for entry, saved in zip(self.static, backup):
+                for t, b in zip(entry, saved):
+                    if t is not None:
+                        t.copy_(b)
+        torch.cuda.current_stream(device).wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.no_grad(), torch.cuda.graph(self.graph):
+            self.logits = self._step()
+        # the capture itself executes nothing; undo the bookkeeping of warm-up and capture
+        cache._seen_tokens = seen
+
+    def _point_cache_at_static(self) -> None:
+        for state, (C, S, conv) in zip(self.cache.states, self.static):
+            state["recurrent_state"] = (C, S)
+            state["conv_state"] = conv
+
+    def _step(self) -> torch.Tensor:
+        out = self.model(input_ids=self.token, past_key_values=self.cache, use_cache=True, logits_to_keep=1)
+        for state, (C, S, conv) in zip(self.cache.states, self.static):
+            new_C, new_S = state["recurrent_state"]
+            C.copy_(new_C)
+            S.copy_(new_S)
+            if conv is not None:
+                conv.copy_(state["conv_state"])
+        self._point_cache_at_static()
+        return out.logits
+
+    def step(self, token: torch.Tensor) -> torch.Tensor:
+        """``token`` [B,1] -> logits [B,1,vocab] (a static buffer: read it before the next step)."""
+        self.token.copy_(token)
+        self.graph.replay()
+        self.cache._seen_tokens += 1
+        return self.logits
+
+
+__all__ = ["GraphedDecoder", "SolveDeltaBlock", "SolveDeltaCache", "SolveDeltaCacheAdapter", "SolveDeltaCausalLMOutput",
            "SolveDeltaForCausalLM", "SolveDeltaMLP", "SolveDeltaModel", "SolveDeltaModelOutput",
            "segment_reset_mask"]

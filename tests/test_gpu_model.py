@@ -167,6 +167,34 @@ def test_greedy_generation_follows_the_single_pass(medium):
     assert agree >= 5 / 6
 
 
+def test_graphed_decode_equals_eager_decode(medium):
+    """The captured one-token step, replayed, gives what the eager cached steps give, and leaves
+    the cache where they leave it."""
+    config, model = medium
+    prompt = torch.randint(0, config.vocab_size, (2, 77), device="cuda")
+    eager = model.generate(prompt, max_new_tokens=12)
+    graphed = model.generate(prompt, max_new_tokens=12, graphed=True)
+    assert torch.equal(eager, graphed)
+    from solvedelta_b200 import GraphedDecoder
+
+    with torch.no_grad():
+        a = model(input_ids=prompt, use_cache=True, logits_to_keep=1)
+        b = model(input_ids=prompt, use_cache=True, logits_to_keep=1)
+        decoder = GraphedDecoder(model, b.past_key_values, 2)
+        token = a.logits[:, -1].argmax(-1, keepdim=True)
+        cache = a.past_key_values
+        for _ in range(5):
+            want = model(input_ids=token, past_key_values=cache, use_cache=True, logits_to_keep=1).logits
+            got = decoder.step(token)
+            assert torch.equal(got, want)
+            token = want[:, -1].argmax(-1, keepdim=True)
+    assert b.past_key_values.get_seq_length() == cache.get_seq_length() == 82
+    for x, y in zip(cache, b.past_key_values):
+        assert torch.equal(x["recurrent_state"][0], y["recurrent_state"][0])
+        assert torch.equal(x["recurrent_state"][1], y["recurrent_state"][1])
+        assert torch.equal(x["conv_state"], y["conv_state"])
+
+
 def test_training_step_reduces_the_loss(medium):
     config, _ = medium
     torch.manual_seed(9)
