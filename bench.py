@@ -453,7 +453,7 @@ def time_causal_lm(device, train_steps=3, decode_steps=256):
     out = {"parameters": sum(p.numel() for p in params),
            "train": {"ms_per_step": round(train_ms, 1), "value": round(B * T / (train_ms * 1e-3), 1),
                      "unit": "tokens/s", "shape": f"B={B}, T={T}, fwd + loss + bwd + AdamW (FP32 master weights)",
-                     "loss": round(float(loss), 4), "peak_memory_gib": round(peak_gb, 1)}}
+                     "loss": round(float(loss.detach()), 4), "peak_memory_gib": round(peak_gb, 1)}}
     del optimizer, master
     for p in params:
         p.grad = None
