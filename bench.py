@@ -457,6 +457,32 @@ def time_causal_lm(device, train_steps=3, decode_steps=256):
     del optimizer, master
     for p in params:
         p.grad = None
+    torch.cuda.empty_cache()
+    # the same step with forward, chunked fixed-denominator loss and backward replayed from one CUDA
+    # graph, AdamW on the FP32 masters outside it
+    from solvedelta_b200 import BF16ShadowWeights, SolveDeltaGraphedTrainingStep
+
+    torch.cuda.reset_peak_memory_stats(device)
+    shadows = BF16ShadowWeights(model, lambda masters: torch.optim.AdamW(masters, lr=1e-4, fused=True))
+    graphed = SolveDeltaGraphedTrainingStep(model, ids, ids, num_warmup_iters=2)
+    for _ in range(2):
+        graphed(ids, ids)
+        shadows.optimizer.step()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(train_steps):
+        gloss = graphed(ids, ids)
+        shadows.optimizer.step()
+    e1.record()
+    torch.cuda.synchronize()
+    graphed_ms = e0.elapsed_time(e1) / train_steps
+    out["train_graphed"] = {"ms_per_step": round(graphed_ms, 1), "value": round(B * T / (graphed_ms * 1e-3), 1),
+                            "unit": "tokens/s", "loss": round(float(gloss), 4),
+                            "shape": "same step: CUDA-graph replay of fwd + chunked loss + bwd, AdamW outside",
+                            "peak_memory_gib": round(torch.cuda.max_memory_allocated(device) / 2 ** 30, 1)}
+    del graphed, shadows
+    for p in params:
+        p.grad = None
     model.eval()
     torch.cuda.empty_cache()
     prompt = torch.randint(0, config.vocab_size, (1, 32768), device=device)

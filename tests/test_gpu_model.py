@@ -212,3 +212,70 @@ def test_training_step_reduces_the_loss(medium):
                 m.add_(p.grad.float(), alpha=-0.05)
                 p.copy_(m.to(p.dtype))
     assert all(np.isfinite(losses)) and losses[-1] < losses[0] - 0.05, losses
+
+
+def _fresh_medium(seed):
+    torch.manual_seed(seed)
+    config = SolveDeltaConfig(hidden_size=256, num_heads=2, head_k_dim=64, head_v_dim=128, num_hidden_layers=2,
+                              vocab_size=512, initializer_range=0.05)
+    return config, SolveDeltaForCausalLM(config).prepare("cuda").train()
+
+
+def test_chunked_fixed_denominator_loss_equals_the_model_loss():
+    from solvedelta_b200 import causal_lm_loss
+
+    config, model = _fresh_medium(3)
+    ids = torch.randint(0, config.vocab_size, (2, 96), device="cuda")
+    plain = model(input_ids=ids, labels=ids).loss
+    plain.backward()
+    want = [p.grad.float().clone() for p in model.parameters()]
+    model.zero_grad(set_to_none=True)
+    fused = causal_lm_loss(model, ids, ids, total=2 * 95, num_chunks=5)
+    fused.backward()
+    assert abs(fused.item() - plain.item()) < 2e-3
+    for (name, p), w in zip(model.named_parameters(), want):
+        assert rel_l2(p.grad.float().cpu().numpy(), w.cpu().numpy()) < 2e-2, name
+
+
+def test_graphed_training_step_equals_the_eager_step():
+    from solvedelta_b200 import SolveDeltaGraphedTrainingStep, causal_lm_loss
+
+    config, model = _fresh_medium(4)
+    ids = [torch.randint(0, config.vocab_size, (2, 128), device="cuda") for _ in range(3)]
+    step = SolveDeltaGraphedTrainingStep(model, ids[0], ids[0], num_chunks=4)
+    assert all(p.grad is not None and not p.grad.any() for p in model.parameters())
+    # two replays accumulate two micro-batches
+    loss_a = step(ids[1], ids[1]).clone()
+    loss_b = step(ids[2], ids[2]).clone()
+    got = [p.grad.clone() for p in model.parameters()]
+    model.zero_grad(set_to_none=True)
+    want_a = causal_lm_loss(model, ids[1], ids[1], total=2 * 127, num_chunks=4)
+    want_a.backward()
+    want_b = causal_lm_loss(model, ids[2], ids[2], total=2 * 127, num_chunks=4)
+    want_b.backward()
+    assert loss_a.item() == want_a.item() and loss_b.item() == want_b.item()
+    for (name, p), g in zip(model.named_parameters(), got):
+        assert torch.equal(p.grad, g), name   # same kernels in the same order: bit-equal
+    with pytest.raises(ValueError):
+        step(ids[1][:, :64], ids[1][:, :64])
+    with pytest.raises(TypeError):
+        step(ids[1].int(), ids[1])
+    model.eval()
+    with pytest.raises(RuntimeError):
+        step(ids[1], ids[1])
+
+
+def test_graphed_steps_with_master_weights_train():
+    from solvedelta_b200 import BF16ShadowWeights, SolveDeltaGraphedTrainingStep
+
+    config, model = _fresh_medium(6)
+    ids = torch.randint(0, config.vocab_size, (2, 128), device="cuda")
+    shadows = BF16ShadowWeights(model, lambda masters: torch.optim.AdamW(masters, lr=2e-3, fused=True))
+    step = SolveDeltaGraphedTrainingStep(model, ids, ids)
+    losses = []
+    for _ in range(10):
+        losses.append(step(ids, ids).item())
+        shadows.optimizer.step()
+        shadows.assert_current()
+    assert all(np.isfinite(losses)) and losses[-1] < losses[0] - 0.3, losses
+    assert shadows.nbytes == 4 * sum(p.numel() for p in model.parameters())

@@ -1,0 +1,113 @@
+"""Host-side logic of the training helpers: the fixed-denominator chunked linear + cross entropy,
+the FP32 master weights, and gradient averaging over a two-rank gloo group (CPU)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+import torch.nn.functional as F
+from torch import nn
+
+from solvedelta_b200.training import BF16ShadowWeights, allreduce_gradients, fixed_dense_linear_cross_entropy
+
+
+@pytest.mark.parametrize("chunks,with_bias", [(1, False), (3, True), (8, False), (50, True)])
+def test_fixed_denominator_loss_equals_cross_entropy(chunks, with_bias):
+    gen = torch.Generator().manual_seed(chunks)
+    x = torch.randn(3, 7, 10, dtype=torch.float64, generator=gen, requires_grad=True)
+    w = torch.randn(13, 10, dtype=torch.float64, generator=gen, requires_grad=True)
+    b = torch.randn(13, dtype=torch.float64, generator=gen, requires_grad=True) if with_bias else None
+    target = torch.randint(0, 13, (3, 7), generator=gen)
+    target[0, 2] = -100
+    target[2, 6] = -100
+    total = 19   # a constant of the batch shape, here the true count
+    cot = torch.tensor(0.7, dtype=torch.float64)
+    loss = fixed_dense_linear_cross_entropy(x, target, w, b, total=total, num_chunks=chunks)
+    grads = torch.autograd.grad(loss, [t for t in (x, w, b) if t is not None], cot.float())
+    ref = F.cross_entropy(F.linear(x, w, b).reshape(-1, 13), target.reshape(-1), ignore_index=-100, reduction="sum") / total
+    ref_grads = torch.autograd.grad(ref, [t for t in (x, w, b) if t is not None], cot)
+    assert abs(loss.item() - ref.item()) < 1e-6
+    for got, want in zip(grads, ref_grads):
+        assert got.shape == want.shape and got.dtype == want.dtype
+        # the weight and bias gradients pass through an FP32 accumulator
+        assert (got - want).abs().max().item() < 1e-6 * max(1.0, want.abs().max().item())
+
+
+def test_fixed_denominator_loss_checks_its_arguments():
+    x, w = torch.randn(2, 3, 4), torch.randn(5, 4)
+    t = torch.zeros(2, 3, dtype=torch.long)
+    with pytest.raises(ValueError):
+        fixed_dense_linear_cross_entropy(x, t, w, total=0)
+    with pytest.raises(ValueError):
+        fixed_dense_linear_cross_entropy(x, t[:, :2], w, total=6)
+    with pytest.raises(ValueError):
+        fixed_dense_linear_cross_entropy(x, t, torch.randn(5, 3), total=6)
+    # no gradient requested: nothing but the loss is formed
+    assert fixed_dense_linear_cross_entropy(x, t, w, total=6).requires_grad is False
+
+
+def test_master_weights_own_the_update():
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(8, 8), nn.Linear(8, 4)).to(torch.bfloat16)
+    shadows = BF16ShadowWeights(model, lambda masters: torch.optim.SGD(masters, lr=0.5))
+    assert all(m.dtype == torch.float32 for m in shadows.masters)
+    assert shadows.nbytes == sum(p.numel() for p in model.parameters()) * 4
+    before = [m.detach().clone() for m in shadows.masters]
+    x = torch.randn(5, 8).to(torch.bfloat16)
+    for _ in range(2):   # two accumulated micro-batches
+        model(x).float().pow(2).sum().backward()
+    grads = [p.grad.float().clone() for p in model.parameters()]
+    shadows.optimizer.step()
+    shadows.assert_current()
+    for m, m0, g, p in zip(shadows.masters, before, grads, model.parameters()):
+        assert torch.allclose(m, m0 - 0.5 * g)                       # the FP32 master took the full-precision step
+        assert torch.equal(p.detach(), m.detach().to(torch.bfloat16))  # the model holds its BF16 rounding
+        assert p.grad is not None and not p.grad.any()               # cleared in place (storage kept)
+    # a change made to the masters by hand reaches the model through refresh()
+    with torch.no_grad():
+        shadows.masters[0].add_(1.0)
+    shadows.refresh()
+    assert torch.equal(model[0].weight.detach(), shadows.masters[0].detach().to(torch.bfloat16))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _allreduce_worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    params = [nn.Parameter(torch.zeros(3, 2)), nn.Parameter(torch.zeros(5)), nn.Parameter(torch.zeros(4)),
+              nn.Parameter(torch.zeros(2, dtype=torch.float64))]
+    params[0].grad = torch.full((3, 2), float(rank + 1))
+    params[1].grad = torch.arange(5, dtype=torch.float32) * (rank + 1)
+    # params[2] has no gradient on any rank
+    params[3].grad = torch.tensor([1.0, -2.0], dtype=torch.float64) * (rank + 1)
+    issued = allreduce_gradients(params)
+    torch.save({"issued": issued, "grads": [None if p.grad is None else p.grad for p in params]},
+               os.path.join(out_dir, f"rank{rank}.pt"))
+    dist.destroy_process_group()
+
+
+def test_gradients_are_averaged_over_two_ranks(tmp_path):
+    world = 2
+    mp.spawn(_allreduce_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for rank in range(world):
+        got = torch.load(os.path.join(tmp_path, f"rank{rank}.pt"))
+        assert got["issued"] == 2   # one flat bucket per gradient dtype
+        g0, g1, g2, g3 = got["grads"]
+        assert torch.equal(g0, torch.full((3, 2), 1.5))
+        assert torch.equal(g1, torch.arange(5, dtype=torch.float32) * 1.5)
+        assert g2 is None
+        assert torch.equal(g3, torch.tensor([1.5, -3.0], dtype=torch.float64))
+
+
+def test_allreduce_is_a_no_op_without_a_group():
+    p = nn.Parameter(torch.zeros(2))
+    p.grad = torch.ones(2)
+    assert allreduce_gradients([p]) == 0 and torch.equal(p.grad, torch.ones(2))
