@@ -17,8 +17,9 @@
 // rows, is written element by element into the transposed operand, with the
 // K-chunk pitch padded to 144 bytes so that a warp's 32 rows hit 32 banks.
 // R [tok][p], whose contraction index is the slow one in global memory, is
-// turned through registers: each thread loads one column of it, coalesced
-// over the warp, and writes it as 16-byte chunks of its own row.  The decay
+// turned through registers: a thread loads columns of it, coalesced over the
+// warp, and writes each as 16-byte chunks of one operand row (the warps
+// without X^T rows do this, two columns per thread).  The decay
 // diag(lam) is one scalar per thread, applied on the way back into tensor
 // memory; checkpoints and X go to global memory from the same registers.
 // Operands are rounded to TF32 (round to nearest) before the tensor core,
@@ -245,16 +246,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, i
             if (tid < 2 * CL)
                 prefetch_l2(reinterpret_cast<const char*>(panel_ptr(p.P, gn) + (tid >> 1) * DP + col0) + (tid & 1) * 128);
         }
-        float rv[32], pv[32];
-        {
+        // The warps that own X^T rows (lane quarters 0 and 1) load P and later run the X epilogue; the
+        // other two quarters turn R, for two state rows each (their own and the one 64 below).
+        float rv[32], rv2[32], pv[32];
+        if (has_x) {
+            const float* pg = panel_ptr(p.P, gi) + (half * 32) * DP + col0 + row;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) pv[j] = __ldcg(pg + j * DP);
+        } else {
             const float* rg = panel_ptr(p.R, gi) + (half * 32) * DP + row;
 #pragma unroll
             for (int j = 0; j < 32; ++j) rv[j] = __ldcg(rg + j * DP);
-            if (has_x) {
-                const float* pg = panel_ptr(p.P, gi) + (half * 32) * DP + col0 + row;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) pv[j] = __ldcg(pg + j * DP);
-            }
+            for (int j = 0; j < 32; ++j) rv2[j] = __ldcg(rg + j * DP - 64);
         }
         TC_STAMP(2);
         if (p.ckb != nullptr) {
@@ -287,11 +291,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, i
         tc_wait_st();
         TC_STAMP(4);
         // R^T as the second contraction's A operand (the previous step's second contraction has completed)
+        if (!has_x) {
 #pragma unroll
-        for (int j4 = 0; j4 < 8; ++j4) {
-            float4 v = make_float4(tc_round(rv[4 * j4]), tc_round(rv[4 * j4 + 1]), tc_round(rv[4 * j4 + 2]),
-                                   tc_round(rv[4 * j4 + 3]));
-            *reinterpret_cast<float4*>(sR + own_row + (half * 8 + j4) * TC_CORE) = v;
+            for (int j4 = 0; j4 < 8; ++j4) {
+                float4 v = make_float4(tc_round(rv[4 * j4]), tc_round(rv[4 * j4 + 1]), tc_round(rv[4 * j4 + 2]),
+                                       tc_round(rv[4 * j4 + 3]));
+                *reinterpret_cast<float4*>(sR + own_row + (half * 8 + j4) * TC_CORE) = v;
+                float4 w = make_float4(tc_round(rv2[4 * j4]), tc_round(rv2[4 * j4 + 1]), tc_round(rv2[4 * j4 + 2]),
+                                       tc_round(rv2[4 * j4 + 3]));
+                *reinterpret_cast<float4*>(sR + own_row - 8 * TC_KT_SBO + (half * 8 + j4) * TC_CORE) = w;
+            }
         }
 
         TC_STAMP(5);
