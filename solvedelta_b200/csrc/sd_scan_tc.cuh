@@ -34,7 +34,9 @@
 
 namespace sd {
 
-constexpr int TC_THREADS = 256;           // 8 warps: lane quarter = warp % 4, column half = warp / 4
+constexpr int TC_PARTS = 2;               // warps per lane quarter: each takes 64/TC_PARTS columns (or tokens)
+constexpr int TC_N = 64 / TC_PARTS;        // columns of the state slice, or tokens of X^T, per thread
+constexpr int TC_THREADS = 128 * TC_PARTS; // lane quarter = warp % 4, part = warp / 4
 constexpr int TC_TMEM_COLS = 128;         // 64 state-slice columns + 64 X^T columns
 constexpr int TC_X_COL = SCAN_NS;         // first tensor-memory column of X^T
 constexpr unsigned TC_CORE = 128;         // bytes of one 8 x 16-byte core matrix
@@ -116,6 +118,33 @@ __device__ __forceinline__ void tc_st32(unsigned taddr, const float* r) {
         "r"(u[29]), "r"(u[30]), "r"(u[31]), "r"(taddr)
         : "memory");
 }
+// 16-column forms of the two moves above
+__device__ __forceinline__ void tc_ld16(unsigned taddr, float* r) {
+    unsigned* u = reinterpret_cast<unsigned*>(r);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
+          "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tc_st16(unsigned taddr, const float* r) {
+    const unsigned* u = reinterpret_cast<const unsigned*>(r);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15};" ::"r"(u[0]),
+        "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]), "r"(u[8]), "r"(u[9]), "r"(u[10]),
+        "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15]), "r"(taddr)
+        : "memory");
+}
+template <int N>
+__device__ __forceinline__ void tc_ld(unsigned taddr, float* r) {
+    static_assert(N == 16 || N == 32, "16 or 32 columns per move");
+    if (N == 32) tc_ld32(taddr, r); else tc_ld16(taddr, r);
+}
+template <int N>
+__device__ __forceinline__ void tc_st(unsigned taddr, const float* r) {
+    static_assert(N == 16 || N == 32, "16 or 32 columns per move");
+    if (N == 32) tc_st32(taddr, r); else tc_st16(taddr, r);
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -163,7 +192,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, i
     const int col0 = blockIdx.x * SCAN_NS;
     const int s = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int quarter = warp & 3, half = warp >> 2;
+    const int quarter = warp & 3, part = warp >> 2;
     // This thread's tensor-memory lane: state row p for the state accumulator and for the R column
     // it turns; slice column c for the X^T accumulator (lanes 0..63 only).
     const int row = quarter * 32 + lane;
@@ -186,11 +215,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, i
     };
     issue(0);
 
-    // this thread's part of the slice: state row `row`, slice columns [32*half, 32*half+32)
-    float st[32];
-    const int c0 = half * 32;
+    // this thread's part of the slice: state row `row`, slice columns [TC_N*part, TC_N*part+TC_N)
+    float st[TC_N];
+    const int c0 = part * TC_N;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
+    for (int j = 0; j < TC_N; ++j) {
         float v = 0.f;
         int cc = col0 + c0 + j;
         if (p.init != nullptr && row < p.nrows && cc < p.ncols) {
@@ -204,7 +233,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, i
     tc_fence_after();
     const unsigned tbase = s_tmem;
     const unsigned t_state = tbase + ((unsigned)(quarter * 32) << 16) + c0;
-    const unsigned t_x = tbase + ((unsigned)(quarter * 32) << 16) + TC_X_COL + half * 32;
+    const unsigned t_x = tbase + ((unsigned)(quarter * 32) << 16) + TC_X_COL + part * TC_N;
     const unsigned bar1 = tc_smem(&bars[0]), bar2 = tc_smem(&bars[1]);
     const unsigned idesc = tc_idesc(SCAN_NS);   // N = 64 for both: tokens, then slice columns
     const unsigned own_row = (row >> 3) * TC_KT_SBO + (row & 7) * 16;                 // this thread's row of sR (and sX)
@@ -220,7 +249,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, i
         const float lam = p.lam[gi * DP + row];
         // the slice, transposed and rounded, as this step's A operand
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
+        for (int j = 0; j < TC_N; ++j) {
             const int c = c0 + j;
             *reinterpret_cast<float*>(sS + (c >> 3) * TC_S_SBO + (c & 7) * 16 + own_col) = tc_round(st[j]);
         }
@@ -242,29 +271,32 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, i
         issue(step + 1);
         if (step + 2 < p.NC) {   // R and the P slice of the step after next: one 128-byte line per thread
             const long long gn = chunk_at(step + 2);
-            prefetch_l2(reinterpret_cast<const char*>(panel_ptr(p.R, gn)) + tid * 128);
-            if (tid < 2 * CL)
-                prefetch_l2(reinterpret_cast<const char*>(panel_ptr(p.P, gn) + (tid >> 1) * DP + col0) + (tid & 1) * 128);
+            if (tid < CL * DP * 4 / 128)
+                prefetch_l2(reinterpret_cast<const char*>(panel_ptr(p.R, gn)) + tid * 128);
+            else if (tid < CL * DP * 4 / 128 + 2 * CL) {
+                const int l = tid - CL * DP * 4 / 128;
+                prefetch_l2(reinterpret_cast<const char*>(panel_ptr(p.P, gn) + (l >> 1) * DP + col0) + (l & 1) * 128);
+            }
         }
         // The warps that own X^T rows (lane quarters 0 and 1) load P and later run the X epilogue; the
         // other two quarters turn R, for two state rows each (their own and the one 64 below).
-        float rv[32], rv2[32], pv[32];
+        float rv[TC_N], rv2[TC_N], pv[TC_N];
         if (has_x) {
-            const float* pg = panel_ptr(p.P, gi) + (half * 32) * DP + col0 + row;
+            const float* pg = panel_ptr(p.P, gi) + (part * TC_N) * DP + col0 + row;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) pv[j] = __ldcg(pg + j * DP);
+            for (int j = 0; j < TC_N; ++j) pv[j] = __ldcg(pg + j * DP);
         } else {
-            const float* rg = panel_ptr(p.R, gi) + (half * 32) * DP + row;
+            const float* rg = panel_ptr(p.R, gi) + (part * TC_N) * DP + row;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) rv[j] = __ldcg(rg + j * DP);
+            for (int j = 0; j < TC_N; ++j) rv[j] = __ldcg(rg + j * DP);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) rv2[j] = __ldcg(rg + j * DP - 64);
+            for (int j = 0; j < TC_N; ++j) rv2[j] = __ldcg(rg + j * DP - 64);
         }
         TC_STAMP(2);
         if (p.ckb != nullptr) {
             bf16* ck = p.ckb + gi * (long long)(DP * DP) + row * DP + col0 + c0;
 #pragma unroll
-            for (int j16 = 0; j16 < 2; ++j16) {
+            for (int j16 = 0; j16 < TC_N / 16; ++j16) {
                 unsigned w[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
@@ -277,7 +309,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, i
         if (p.ck != nullptr) {
             float* ck = state_ptr(p.ck, gi) + row * DP + col0 + c0;
 #pragma unroll
-            for (int j8 = 0; j8 < 4; ++j8) {
+            for (int j8 = 0; j8 < TC_N / 8; ++j8) {
                 unsigned w[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) w[e] = __float_as_uint(st[8 * j8 + e]);
@@ -285,21 +317,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, i
             }
         }
 #pragma unroll
-        for (int j = 0; j < 32; ++j) st[j] *= lam;
+        for (int j = 0; j < TC_N; ++j) st[j] *= lam;
         TC_STAMP(3);
-        tc_st32(t_state, st);
+        tc_st<TC_N>(t_state, st);
         tc_wait_st();
         TC_STAMP(4);
         // R^T as the second contraction's A operand (the previous step's second contraction has completed)
         if (!has_x) {
 #pragma unroll
-            for (int j4 = 0; j4 < 8; ++j4) {
+            for (int j4 = 0; j4 < TC_N / 4; ++j4) {
                 float4 v = make_float4(tc_round(rv[4 * j4]), tc_round(rv[4 * j4 + 1]), tc_round(rv[4 * j4 + 2]),
                                        tc_round(rv[4 * j4 + 3]));
-                *reinterpret_cast<float4*>(sR + own_row + (half * 8 + j4) * TC_CORE) = v;
+                *reinterpret_cast<float4*>(sR + own_row + (part * (TC_N / 4) + j4) * TC_CORE) = v;
                 float4 w = make_float4(tc_round(rv2[4 * j4]), tc_round(rv2[4 * j4 + 1]), tc_round(rv2[4 * j4 + 2]),
                                        tc_round(rv2[4 * j4 + 3]));
-                *reinterpret_cast<float4*>(sR + own_row - 8 * TC_KT_SBO + (half * 8 + j4) * TC_CORE) = w;
+                *reinterpret_cast<float4*>(sR + own_row - 8 * TC_KT_SBO + (part * (TC_N / 4) + j4) * TC_CORE) = w;
             }
         }
 
@@ -311,25 +343,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, i
         tc_fence_after();
         TC_STAMP(6);
         if (has_x) {   // warp-uniform: lanes 0..63 of the X^T accumulator
-            float x[32];
-            tc_ld32(t_x, x);
+            float x[TC_N];
+            tc_ld<TC_N>(t_x, x);
             tc_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) x[j] += pv[j];
+            for (int j = 0; j < TC_N; ++j) x[j] += pv[j];
             if (p.Xb != nullptr) {
-                bf16* xb = bpanel_ptr(p.Xb, gi) + (half * 32) * DP + col0 + row;
+                bf16* xb = bpanel_ptr(p.Xb, gi) + (part * TC_N) * DP + col0 + row;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) xb[j * DP] = __float2bfloat16_rn(x[j]);
+                for (int j = 0; j < TC_N; ++j) xb[j * DP] = __float2bfloat16_rn(x[j]);
             } else {
-                float* xg = panel_ptr(p.X, gi) + (half * 32) * DP + col0 + row;
+                float* xg = panel_ptr(p.X, gi) + (part * TC_N) * DP + col0 + row;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) __stcg(xg + j * DP, x[j]);
+                for (int j = 0; j < TC_N; ++j) __stcg(xg + j * DP, x[j]);
             }
 #pragma unroll
-            for (int j4 = 0; j4 < 8; ++j4) {
+            for (int j4 = 0; j4 < TC_N / 4; ++j4) {
                 float4 v = make_float4(tc_round(x[4 * j4]), tc_round(x[4 * j4 + 1]), tc_round(x[4 * j4 + 2]),
                                        tc_round(x[4 * j4 + 3]));
-                *reinterpret_cast<float4*>(sX + own_row + (half * 8 + j4) * TC_CORE) = v;
+                *reinterpret_cast<float4*>(sX + own_row + (part * (TC_N / 4) + j4) * TC_CORE) = v;
             }
         }
         tc_fence_async_smem();
@@ -353,7 +385,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, i
             atomicExch(fault, 2);
         }
         tc_fence_after();
-        tc_ld32(t_state, st);
+        tc_ld<TC_N>(t_state, st);
         tc_wait_ld();
         TC_STAMP(9);
     }
@@ -361,7 +393,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, i
     if (p.fin != nullptr) {
         float* dst = p.fin + (long long)s * p.nrows * p.ncols;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
+        for (int j = 0; j < TC_N; ++j) {
             int cc = col0 + c0 + j;
             if (row < p.nrows && cc < p.ncols) {
                 if (p.transposed_io)
