@@ -449,11 +449,13 @@ def time_causal_lm(device, train_steps=3, decode_steps=256):
     e1.record()
     torch.cuda.synchronize()
     train_ms = e0.elapsed_time(e1) / train_steps
+    loss_value = float(loss.detach())
+    del loss    # a live autograd graph would keep this stream's gradient accumulators alive into the capture below
     peak_gb = torch.cuda.max_memory_allocated(device) / 2 ** 30
     out = {"parameters": sum(p.numel() for p in params),
            "train": {"ms_per_step": round(train_ms, 1), "value": round(B * T / (train_ms * 1e-3), 1),
                      "unit": "tokens/s", "shape": f"B={B}, T={T}, fwd + loss + bwd + AdamW (FP32 master weights)",
-                     "loss": round(float(loss.detach()), 4), "peak_memory_gib": round(peak_gb, 1)}}
+                     "loss": round(loss_value, 4), "peak_memory_gib": round(peak_gb, 1)}}
     del optimizer, master
     for p in params:
         p.grad = None

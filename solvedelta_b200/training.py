@@ -190,6 +190,11 @@ class SolveDeltaGraphedTrainingStep:
     (cuda_graph.py:125-150).  With ``distributed=True`` the call ends with ``allreduce_gradients``
     over ``process_group`` unless made inside ``no_sync()``.
 
+    Build it before any eager backward of the same model, or after every tensor that still holds such
+    a backward's graph (a kept loss) has been freed: gradient accumulators created on another stream
+    and kept alive by an old graph break the capture (upstream cuda_graph.py:133-137 captures before
+    wrapping in DDP for the same reason).
+
     Limits, as upstream's: CUDA token ids and labels of one fixed shape, no masks, resets or cache,
     model in training mode, replay on the stream that built the helper; labels carry no ignored
     positions beyond the shift (the loss denominator is the constant B*(T-1))."""
@@ -227,8 +232,15 @@ class SolveDeltaGraphedTrainingStep:
             if p.grad is None:
                 p.grad = torch.zeros_like(p)
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self.loss = self._forward_backward()
+        try:
+            with torch.cuda.graph(self.graph):
+                self.loss = self._forward_backward()
+        except RuntimeError as error:
+            raise RuntimeError(
+                "capturing the training step failed.  The usual cause: an autograd graph from an earlier "
+                "backward on another stream is still alive (a loss or output tensor that was kept), so the "
+                "parameters' gradient accumulators still belong to that stream; free it (del loss) before "
+                "building this helper") from error
         with torch.no_grad():
             for p, g in zip(self.params, held):
                 p.grad.zero_() if g is None else p.grad.copy_(g)
