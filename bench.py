@@ -750,6 +750,62 @@ def run_ours(opts, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_model_ddp(opts, rank, world, local_rank):
+    """Side measurement, not the headline metric: the reference's 24-layer training step data-parallel
+    over the ranks (B=8, T=2048 per rank; graphed forward + loss + backward, one flat gradient all-reduce
+    over NCCL, AdamW on FP32 masters), tokens/s of the whole job, max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from solvedelta_b200 import BF16ShadowWeights, SolveDeltaConfig, SolveDeltaForCausalLM, SolveDeltaGraphedTrainingStep
+    from solvedelta_b200.sharding import max_over_ranks
+
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    torch.manual_seed(0)   # the same initial weights on every rank
+    config = SolveDeltaConfig(hidden_size=1024, num_heads=8, head_k_dim=128, head_v_dim=128,
+                              num_hidden_layers=24, vocab_size=32000)
+    model = SolveDeltaForCausalLM(config).prepare(device).train()
+    B, T = 8, 2048
+    gen = torch.Generator(device="cpu").manual_seed(100 + rank)
+    ids = torch.randint(0, config.vocab_size, (B, T), generator=gen).to(device)
+    shadows = BF16ShadowWeights(model, lambda masters: torch.optim.AdamW(masters, lr=1e-4, fused=True))
+    step = SolveDeltaGraphedTrainingStep(model, ids, ids, num_warmup_iters=2, distributed=world > 1)
+    for _ in range(max(opts.warmup, 3)):
+        step(ids, ids)
+        shadows.optimizer.step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(opts.steps):
+        loss = step(ids, ids)
+        shadows.optimizer.step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = max_over_ranks(e0.elapsed_time(e1) / opts.steps, device) if world > 1 else e0.elapsed_time(e1) / opts.steps
+    # every rank must hold the same weights after the averaged updates
+    probe = model.lm_head.weight.float().sum().reshape(1)
+    if world > 1:
+        gathered = [torch.zeros_like(probe) for _ in range(world)]
+        dist.all_gather(gathered, probe)
+        same = all(torch.equal(g, gathered[0]) for g in gathered)
+    else:
+        same = True
+    if rank == 0:
+        print(json.dumps({"metric": "SolveDelta CausalLM training tokens/s (24 layers, hidden 1024, vocab 32000)",
+                          "value": world * B * T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+                          "steps": opts.steps, "ms_per_step": ms, "scaling": "weak", "dtype": "bf16",
+                          "data": "synthetic", "loss": float(loss), "weights_equal_across_ranks": same,
+                          "config": {"workload": f"B={B}, T={T} per GPU; graphed fwd + chunked loss + bwd, one flat "
+                                                 "NCCL gradient all-reduce, fused AdamW on FP32 masters"}}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -763,12 +819,17 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg (profiler captures)")
     ap.add_argument("--skip-glue", action="store_true", help="skip the mixer glue kernels (profiler captures)")
     ap.add_argument("--skip-model", action="store_true", help="skip the 24-layer causal LM legs")
+    ap.add_argument("--model-ddp", action="store_true",
+                    help="side measurement: only the data-parallel 24-layer training step at the launched world size")
     opts = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if opts.impl == "reference":
         run_reference(opts, rank, world)
+        return
+    if opts.model_ddp:
+        run_model_ddp(opts, rank, world, local_rank)
         return
     run_ours(opts, rank, world, local_rank)
 
