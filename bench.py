@@ -540,6 +540,17 @@ def time_causal_lm(device, train_steps=3, decode_steps=256):
     return out
 
 
+def _side_leg(fn, *args):
+    """Side measurements must not cost the headline line: a failure is reported in their place."""
+    try:
+        return fn(*args)
+    except Exception as error:  # noqa: BLE001 - reported, not swallowed
+        import traceback
+
+        traceback.print_exc(file=sys.stderr)
+        return {"error": f"{type(error).__name__}: {error}"[:300]}
+
+
 def run_ours(opts, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -698,8 +709,8 @@ def run_ours(opts, rank, world, local_rank):
     gamma_zero = None
     mixer = None
     if world == 1 and not opts.skip_glue:
-        glue = time_mixer_glue(B, T, H, r, V, device)
-        mixer = time_mixer_module(B, T, H, r, V, device)
+        glue = _side_leg(time_mixer_glue, B, T, H, r, V, device)
+        mixer = _side_leg(time_mixer_module, B, T, H, r, V, device)
         # geometry write rate 0: the operator reduces to the GDN2 edit (same launches, same traffic)
         cpu0 = dict(cpu)
         cpu0["geometry_write"] = torch.zeros_like(cpu["geometry_write"])
@@ -718,7 +729,7 @@ def run_ours(opts, rank, world, local_rank):
     causal_lm = None
     if world == 1 and not opts.skip_glue and not opts.skip_model:
         torch.cuda.empty_cache()
-        causal_lm = time_causal_lm(device)
+        causal_lm = _side_leg(time_causal_lm, device)
 
     if rank == 0:
         cpu_baseline = None
