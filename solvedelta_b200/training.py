@@ -243,7 +243,10 @@ class SolveDeltaGraphedTrainingStep:
                 "building this helper") from error
         with torch.no_grad():
             for p, g in zip(self.params, held):
-                p.grad.zero_() if g is None else p.grad.copy_(g)
+                if g is None:
+                    p.grad.zero_()
+                else:
+                    p.grad.copy_(g)
 
     def _forward_backward(self) -> torch.Tensor:
         loss = causal_lm_loss(self.model, self._ids, self._labels, total=self.total, num_chunks=self.num_chunks)
