@@ -113,6 +113,32 @@ long long* g_dbg = nullptr;  // set by sd_debug_timeline (diagnostic)
 // contraction) or 2 (second) here; sd_device_fault reads it back.
 __device__ int g_scan_fault_word = 0;
 int* g_scan_fault_ptr[64] = {};
+// Tensor map of a [chunks][CL][DP] FP32 panel array for the scan's tiled load: dimensions (4 elements,
+// CL rows, DP/4 K-chunks, chunks) with byte strides (row pitch, 16, panel size), box = one whole panel.
+// cuTensorMapEncodeTiled is a driver function; it is reached through the runtime so that the library
+// links against the runtime alone.
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                      const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                      CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+bool make_panel_map(CUtensorMap* map, const float* panels, long long chunks) {
+    static TensorMapEncodeFn encode = nullptr;
+    if (encode == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult found;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found) != cudaSuccess ||
+            found != cudaDriverEntryPointSuccess || fn == nullptr)
+            return false;
+        encode = reinterpret_cast<TensorMapEncodeFn>(fn);
+    }
+    const cuuint64_t dims[4] = {4, (cuuint64_t)CL, (cuuint64_t)(DP / 4), (cuuint64_t)chunks};
+    const cuuint64_t strides[3] = {(cuuint64_t)DP * 4, 16, (cuuint64_t)CL * DP * 4};
+    const cuuint32_t box[4] = {4, (cuuint32_t)CL, (cuuint32_t)(DP / 4), 1};
+    const cuuint32_t elem[4] = {1, 1, 1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(panels), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int* scan_fault_ptr() {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
@@ -324,7 +350,10 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
         sp.ckb = bpanel_at(kSaved, s, a->saved, "CtCkB");
         sp.init = a->C0; sp.fin = a->C_T;
         sp.NC = p.g.NC; sp.reverse = 0; sp.transposed_io = 1; sp.nrows = s->r; sp.ncols = s->r;
-        k_state_scan_tc<<<scan_grid, TC_THREADS, SCAN_TC_SMEM_BYTES, stream>>>(sp, scan_fault_ptr(), g_dbg ? g_dbg + 16 * 1 : nullptr);
+        CUtensorMap qmap;
+        if (!make_panel_map(&qmap, sp.Q, total_chunks(s))) return SD_ERR_LAUNCH_FAILED;
+        k_state_scan_tc<<<scan_grid, TC_THREADS, SCAN_TC_SMEM_BYTES, stream>>>(sp, qmap, scan_fault_ptr(),
+                                                                               g_dbg ? g_dbg + 16 * 1 : nullptr);
     mark(stream);
     }
     set_dbg(p.g, 2, chunks);
@@ -341,7 +370,10 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
         sp.lam = p.Lam; sp.X = nullptr; sp.ck = nullptr; sp.Xb = p.Zt; sp.ckb = p.SCk;
         sp.init = a->S0; sp.fin = a->S_T;
         sp.NC = p.g.NC; sp.reverse = 0; sp.transposed_io = 0; sp.nrows = s->r; sp.ncols = s->V;
-        k_state_scan_tc<<<scan_grid, TC_THREADS, SCAN_TC_SMEM_BYTES, stream>>>(sp, scan_fault_ptr(), g_dbg ? g_dbg + 16 * 4 : nullptr);
+        CUtensorMap qmap;
+        if (!make_panel_map(&qmap, sp.Q, total_chunks(s))) return SD_ERR_LAUNCH_FAILED;
+        k_state_scan_tc<<<scan_grid, TC_THREADS, SCAN_TC_SMEM_BYTES, stream>>>(sp, qmap, scan_fault_ptr(),
+                                                                               g_dbg ? g_dbg + 16 * 4 : nullptr);
     mark(stream);
     }
     set_dbg(p.g, 5, chunks);

@@ -11,8 +11,10 @@
 // All four operands are K-major in shared memory, in the unswizzled canonical
 // layout of 8 x 16-byte core matrices (the first contraction's M is padded to
 // 128: rows 64..127 of its A operand alias whatever follows in shared memory
-// and only feed accumulator lanes nobody reads).  Q [tok][p] is staged by
-// cp.async as it lies.  X^T is written by the thread that holds the row after
+// and only feed accumulator lanes nobody reads).  Q [tok][p] arrives by ONE
+// tiled TMA load per chunk (cp.async.bulk.tensor.4d, completion counted on an
+// mbarrier): the tensor map lists the 16-byte K-chunk as a dimension of its own,
+// so the panel lands as [K-chunk][row][4 elements], which is the canonical layout.  X^T is written by the thread that holds the row after
 // tcgen05.ld, four consecutive tokens to a 16-byte chunk.  The state, held by
 // rows, is written element by element into the transposed operand, with the
 // K-chunk pitch padded to 144 bytes so that a warp's 32 rows hit 32 banks.
@@ -30,6 +32,8 @@
 // the host reads back, the thread stops waiting for the rest of the launch,
 // and the kernel still walks to its end and frees its tensor memory.
 #pragma once
+#include <cuda.h>   // CUtensorMap (types only: the encoder is reached through the runtime's driver entry point)
+
 #include "sd_scan.cuh"
 
 namespace sd {
@@ -40,7 +44,8 @@ constexpr int TC_THREADS = 128 * TC_PARTS; // lane quarter = warp % 4, part = wa
 constexpr int TC_TMEM_COLS = 128;         // 64 state-slice columns + 64 X^T columns
 constexpr int TC_X_COL = SCAN_NS;         // first tensor-memory column of X^T
 constexpr unsigned TC_CORE = 128;         // bytes of one 8 x 16-byte core matrix
-constexpr unsigned TC_KP_SBO = (DP / 4) * TC_CORE;  // K = state rows (Q, state): bytes between 8-row groups
+constexpr unsigned TC_Q_LBO = CL * 16;               // Q landed by TMA: K-chunk pitch (all 64 rows of one 16-byte chunk)
+constexpr unsigned TC_Q_SBO = 8 * 16;                // ... and the pitch of its 8-row groups
 constexpr unsigned TC_KT_SBO = (CL / 4) * TC_CORE;  // K = tokens (X, R): bytes between 8-row groups
 constexpr unsigned TC_PANEL_BYTES = CL * DP * 4;    // one [CL][DP] or [DP][CL] operand
 constexpr unsigned TC_S_LBO = TC_CORE + 16;         // padded K-chunk pitch of the transposed state operand
@@ -157,20 +162,16 @@ __device__ __forceinline__ void tc_store32(void* g, const unsigned (&w)[8]) {
 
 __device__ __forceinline__ float tc_round(float x) { return __uint_as_float(f2tf32(x)); }
 
-// Chunk walk of the staged Q panel: chunk (tok, p4) -> core matrix (tok/8, p4), row tok%8.  The eight
-// lanes of a quarter warp take the eight rows of one core matrix (128 contiguous bytes: one pass over
-// the banks), the four quarter warps four neighbouring K chunks (64 contiguous bytes of each global row).
-__device__ __forceinline__ void tc_q_chunk(int idx, int& tok, int& p4) {
-    const int l = idx & 31, r = idx >> 5;
-    tok = (r >> 3) * 8 + (l & 7);
-    p4 = (r & 7) * 4 + (l >> 3);
-}
-__device__ __forceinline__ void tc_stage_q(unsigned char* sm, const float* g) {
-    for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += TC_THREADS) {
-        int tok, p4;
-        tc_q_chunk(idx, tok, p4);
-        cp_async16(sm + (tok >> 3) * TC_KP_SBO + p4 * TC_CORE + (tok & 7) * 16, g + tok * DP + p4 * 4);
-    }
+// One tiled TMA load lands the [CL][DP] panel Q of chunk `chunk` as a K-major unswizzled operand:
+// the map's dimensions are (4 elements, CL rows, DP/4 K-chunks, chunks), so shared memory receives
+// [K-chunk][row][4 elements].  Completion is counted in bytes on `bar`.
+__device__ __forceinline__ void tc_load_q(unsigned char* sm, const CUtensorMap* map, int chunk, unsigned bar) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(TC_PANEL_BYTES) : "memory");
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+            tc_smem(sm)),
+        "l"(reinterpret_cast<unsigned long long>(map)), "r"(0), "r"(0), "r"(0), "r"(chunk), "r"(bar)
+        : "memory");
 }
 
 // Diagnostic: thread 0 of CTA (0,0) records the SM clock at the phase boundaries of its ninth step.
@@ -180,13 +181,14 @@ __device__ __forceinline__ void tc_stage_q(unsigned char* sm, const float* g) {
             dbg[k] = clock64();                                                                  \
     } while (0)
 
-__global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, int* fault, long long* dbg) {
+__global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, const __grid_constant__ CUtensorMap qmap, int* fault,
+                                                                  long long* dbg) {
     extern __shared__ __align__(128) unsigned char tsm[];
     unsigned char* sQ = tsm;                          // [2] B of the first contraction (rows = tokens, K = state rows)
     unsigned char* sS = sQ + 2 * TC_PANEL_BYTES;      // A of the first: slice^T        (rows = slice columns, K = state rows)
     unsigned char* sX = sS + TC_S_BYTES;              // B of the second: X^T           (rows = slice columns, K = tokens)
     unsigned char* sR = sX + TC_X_BYTES;              // A of the second: R^T           (rows = state rows, K = tokens)
-    __shared__ __align__(8) unsigned long long bars[2];
+    __shared__ __align__(8) unsigned long long bars[4];   // two contraction barriers, two Q ring slots
     __shared__ unsigned s_tmem;
 
     const int col0 = blockIdx.x * SCAN_NS;
@@ -202,6 +204,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, i
     if (tid == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&bars[0])));
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&bars[1])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&bars[2])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&bars[3])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(&s_tmem)),
@@ -209,11 +214,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, i
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
     auto chunk_at = [&](int step) { return base + (p.reverse ? (p.NC - 1 - step) : step); };
+    // thread 0 alone moves Q: one tiled load per chunk into the two-slot ring
     auto issue = [&](int step) {
-        if (step < p.NC) tc_stage_q(sQ + (step & 1) * TC_PANEL_BYTES, panel_ptr(p.Q, chunk_at(step)));
-        cp_async_commit();
+        if (tid == 0 && step < p.NC)
+            tc_load_q(sQ + (step & 1) * TC_PANEL_BYTES, &qmap, (int)chunk_at(step), tc_smem(&bars[2 + (step & 1)]));
     };
-    issue(0);
 
     // this thread's part of the slice: state row `row`, slice columns [TC_N*part, TC_N*part+TC_N)
     float st[TC_N];
@@ -239,8 +244,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, i
     const unsigned own_row = (row >> 3) * TC_KT_SBO + (row & 7) * 16;                 // this thread's row of sR (and sX)
     const unsigned own_col = (row >> 2) * TC_S_LBO + (row & 3) * 4;                   // its K position in the state operand
     bool alive = true;   // cleared by the first wait that runs out
-
-    cp_async_wait<0>();
+    issue(0);
 
     for (int step = 0; step < p.NC; ++step) {
         const long long gi = chunk_at(step);
@@ -253,6 +257,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, i
             const int c = c0 + j;
             *reinterpret_cast<float*>(sS + (c >> 3) * TC_S_SBO + (c & 7) * 16 + own_col) = tc_round(st[j]);
         }
+        if (alive && !tc_wait(tc_smem(&bars[2 + b]), (step >> 1) & 1)) {   // this step's Q has landed
+            alive = false;
+            atomicExch(fault, 3);
+        }
         tc_fence_async_smem();
         tc_fence_before();
         __syncthreads();
@@ -262,7 +270,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, i
 #pragma unroll
             for (int ks = 0; ks < DP / 8; ++ks)
                 tc_mma(tbase + TC_X_COL, tc_desc(aS + ks * 2 * TC_S_LBO, TC_S_LBO, TC_S_SBO),
-                       tc_desc(bQ + ks * 2 * TC_CORE, TC_CORE, TC_KP_SBO), idesc, ks > 0);
+                       tc_desc(bQ + ks * 2 * TC_Q_LBO, TC_Q_LBO, TC_Q_SBO), idesc, ks > 0);
             tc_commit(bar1);
         }
         __syncwarp();
@@ -378,7 +386,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, i
         }
         __syncwarp();
         TC_STAMP(7);
-        cp_async_wait<0>();   // the next step's panels, in flight since the top of this step
         TC_STAMP(8);
         if (alive && !tc_wait(bar2, step & 1)) {
             alive = false;
