@@ -120,21 +120,38 @@ int* g_scan_fault_ptr[64] = {};
 typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                       const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                       CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-bool make_panel_map(CUtensorMap* map, const float* panels, long long chunks) {
+TensorMapEncodeFn tensor_map_encoder() {
     static TensorMapEncodeFn encode = nullptr;
     if (encode == nullptr) {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult found;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found) != cudaSuccess ||
-            found != cudaDriverEntryPointSuccess || fn == nullptr)
-            return false;
-        encode = reinterpret_cast<TensorMapEncodeFn>(fn);
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found) == cudaSuccess &&
+            found == cudaDriverEntryPointSuccess)
+            encode = reinterpret_cast<TensorMapEncodeFn>(fn);
     }
+    return encode;
+}
+bool make_panel_map(CUtensorMap* map, const float* panels, long long chunks) {
+    const TensorMapEncodeFn encode = tensor_map_encoder();
+    if (encode == nullptr) return false;
     const cuuint64_t dims[4] = {4, (cuuint64_t)CL, (cuuint64_t)(DP / 4), (cuuint64_t)chunks};
     const cuuint64_t strides[3] = {(cuuint64_t)DP * 4, 16, (cuuint64_t)CL * DP * 4};
     const cuuint32_t box[4] = {4, (cuuint32_t)CL, (cuuint32_t)(DP / 4), 1};
     const cuuint32_t elem[4] = {1, 1, 1, 1};
     return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(panels), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The same panel array as rows of DP columns: dimensions (DP, CL, chunks), box (`cols`, CL, 1).
+bool make_row_map(CUtensorMap* map, const float* panels, long long chunks, int cols) {
+    const TensorMapEncodeFn encode = tensor_map_encoder();
+    if (encode == nullptr) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)DP, (cuuint64_t)CL, (cuuint64_t)chunks};
+    const cuuint64_t strides[2] = {(cuuint64_t)DP * 4, (cuuint64_t)CL * DP * 4};
+    const cuuint32_t box[3] = {(cuuint32_t)cols, (cuuint32_t)CL, 1};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(panels), dims, strides, box, elem,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -350,9 +367,11 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
         sp.ckb = bpanel_at(kSaved, s, a->saved, "CtCkB");
         sp.init = a->C0; sp.fin = a->C_T;
         sp.NC = p.g.NC; sp.reverse = 0; sp.transposed_io = 1; sp.nrows = s->r; sp.ncols = s->r;
-        CUtensorMap qmap;
-        if (!make_panel_map(&qmap, sp.Q, total_chunks(s))) return SD_ERR_LAUNCH_FAILED;
-        k_state_scan_tc<<<scan_grid, TC_THREADS, SCAN_TC_SMEM_BYTES, stream>>>(sp, qmap, scan_fault_ptr(),
+        CUtensorMap qmap, rmap, pmap;
+        if (!make_panel_map(&qmap, sp.Q, total_chunks(s)) || !make_row_map(&rmap, sp.R, total_chunks(s), DP) ||
+            !make_row_map(&pmap, sp.P, total_chunks(s), SCAN_NS))
+            return SD_ERR_LAUNCH_FAILED;
+        k_state_scan_tc<<<scan_grid, TC_THREADS, SCAN_TC_SMEM_BYTES, stream>>>(sp, qmap, rmap, pmap, scan_fault_ptr(),
                                                                                g_dbg ? g_dbg + 16 * 1 : nullptr);
     mark(stream);
     }
@@ -370,9 +389,11 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
         sp.lam = p.Lam; sp.X = nullptr; sp.ck = nullptr; sp.Xb = p.Zt; sp.ckb = p.SCk;
         sp.init = a->S0; sp.fin = a->S_T;
         sp.NC = p.g.NC; sp.reverse = 0; sp.transposed_io = 0; sp.nrows = s->r; sp.ncols = s->V;
-        CUtensorMap qmap;
-        if (!make_panel_map(&qmap, sp.Q, total_chunks(s))) return SD_ERR_LAUNCH_FAILED;
-        k_state_scan_tc<<<scan_grid, TC_THREADS, SCAN_TC_SMEM_BYTES, stream>>>(sp, qmap, scan_fault_ptr(),
+        CUtensorMap qmap, rmap, pmap;
+        if (!make_panel_map(&qmap, sp.Q, total_chunks(s)) || !make_row_map(&rmap, sp.R, total_chunks(s), DP) ||
+            !make_row_map(&pmap, sp.P, total_chunks(s), SCAN_NS))
+            return SD_ERR_LAUNCH_FAILED;
+        k_state_scan_tc<<<scan_grid, TC_THREADS, SCAN_TC_SMEM_BYTES, stream>>>(sp, qmap, rmap, pmap, scan_fault_ptr(),
                                                                                g_dbg ? g_dbg + 16 * 4 : nullptr);
     mark(stream);
     }

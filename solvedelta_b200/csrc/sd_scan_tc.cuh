@@ -54,7 +54,10 @@ constexpr unsigned TC_S_BYTES = (SCAN_NS / 8) * TC_S_SBO;   // the 64 rows that 
 constexpr unsigned TC_X_BYTES = SCAN_NS * CL * 4;
 // Q ring, state operand, X operand, R operand.  The padded A operand of the first contraction reaches
 // 2 * TC_S_BYTES past the start of the state operand, which must stay inside this allocation.
-constexpr size_t SCAN_TC_SMEM_BYTES = size_t(2) * TC_PANEL_BYTES + TC_S_BYTES + TC_X_BYTES + TC_PANEL_BYTES;
+constexpr size_t SCAN_TC_OPERAND_BYTES = size_t(2) * TC_PANEL_BYTES + TC_S_BYTES + TC_X_BYTES + TC_PANEL_BYTES;
+constexpr unsigned TC_RAW_P_BYTES = CL * SCAN_NS * 4;   // the P slice as it lies, [CL][NS]
+// ... followed by R as it lies ([CL][DP]) and the P slice, both landed by TMA one step ahead
+constexpr size_t SCAN_TC_SMEM_BYTES = SCAN_TC_OPERAND_BYTES + TC_PANEL_BYTES + TC_RAW_P_BYTES;
 static_assert(2 * TC_S_BYTES <= TC_S_BYTES + TC_X_BYTES + TC_PANEL_BYTES, "padded operand rows leave the allocation");
 constexpr int TC_WAIT_LIMIT = 1 << 20;    // polls of one mbarrier before the wait is given up
 
@@ -174,6 +177,25 @@ __device__ __forceinline__ void tc_load_q(unsigned char* sm, const CUtensorMap* 
         : "memory");
 }
 
+// Row-major tiled loads (map dimensions: DP columns, CL rows, chunks): all of R, and the CTA's
+// NS-column slice of P, both counted on `bar`.
+__device__ __forceinline__ void tc_load_rp(unsigned char* sR_raw, unsigned char* sP_raw, const CUtensorMap* rmap,
+                                           const CUtensorMap* pmap, int chunk, int col0, unsigned bar) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+                 "r"(TC_PANEL_BYTES + TC_RAW_P_BYTES)
+                 : "memory");
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+            tc_smem(sR_raw)),
+        "l"(reinterpret_cast<unsigned long long>(rmap)), "r"(0), "r"(0), "r"(chunk), "r"(bar)
+        : "memory");
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+            tc_smem(sP_raw)),
+        "l"(reinterpret_cast<unsigned long long>(pmap)), "r"(col0), "r"(0), "r"(chunk), "r"(bar)
+        : "memory");
+}
+
 // Diagnostic: thread 0 of CTA (0,0) records the SM clock at the phase boundaries of its ninth step.
 #define TC_STAMP(k)                                                                              \
     do {                                                                                         \
@@ -181,14 +203,18 @@ __device__ __forceinline__ void tc_load_q(unsigned char* sm, const CUtensorMap* 
             dbg[k] = clock64();                                                                  \
     } while (0)
 
-__global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, const __grid_constant__ CUtensorMap qmap, int* fault,
+__global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, const __grid_constant__ CUtensorMap qmap,
+                                                                  const __grid_constant__ CUtensorMap rmap,
+                                                                  const __grid_constant__ CUtensorMap pmap, int* fault,
                                                                   long long* dbg) {
     extern __shared__ __align__(128) unsigned char tsm[];
     unsigned char* sQ = tsm;                          // [2] B of the first contraction (rows = tokens, K = state rows)
     unsigned char* sS = sQ + 2 * TC_PANEL_BYTES;      // A of the first: slice^T        (rows = slice columns, K = state rows)
     unsigned char* sX = sS + TC_S_BYTES;              // B of the second: X^T           (rows = slice columns, K = tokens)
     unsigned char* sR = sX + TC_X_BYTES;              // A of the second: R^T           (rows = state rows, K = tokens)
-    __shared__ __align__(8) unsigned long long bars[4];   // two contraction barriers, two Q ring slots
+    unsigned char* sRraw = tsm + SCAN_TC_OPERAND_BYTES;   // R as it lies, [CL][DP]
+    unsigned char* sPraw = sRraw + TC_PANEL_BYTES;        // the P slice as it lies, [CL][NS]
+    __shared__ __align__(8) unsigned long long bars[5];   // two contraction barriers, two Q ring slots, R/P
     __shared__ unsigned s_tmem;
 
     const int col0 = blockIdx.x * SCAN_NS;
@@ -206,6 +232,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, c
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&bars[1])));
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&bars[2])));
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&bars[3])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&bars[4])));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -245,6 +272,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, c
     const unsigned own_col = (row >> 2) * TC_S_LBO + (row & 3) * 4;                   // its K position in the state operand
     bool alive = true;   // cleared by the first wait that runs out
     issue(0);
+    auto issue_rp = [&](int step) {   // single slot: called once every thread is past its reads of the previous one
+        if (tid == 0 && step < p.NC)
+            tc_load_rp(sRraw, sPraw, &rmap, &pmap, (int)chunk_at(step), col0, tc_smem(&bars[4]));
+    };
+    issue_rp(0);
 
     for (int step = 0; step < p.NC; ++step) {
         const long long gi = chunk_at(step);
@@ -277,28 +309,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, c
         TC_STAMP(1);
         // behind the first contraction: prefetch, this thread's R (and P) values, checkpoints, decay
         issue(step + 1);
-        if (step + 2 < p.NC) {   // R and the P slice of the step after next: one 128-byte line per thread
-            const long long gn = chunk_at(step + 2);
-            if (tid < CL * DP * 4 / 128)
-                prefetch_l2(reinterpret_cast<const char*>(panel_ptr(p.R, gn)) + tid * 128);
-            else if (tid < CL * DP * 4 / 128 + 2 * CL) {
-                const int l = tid - CL * DP * 4 / 128;
-                prefetch_l2(reinterpret_cast<const char*>(panel_ptr(p.P, gn) + (l >> 1) * DP + col0) + (l & 1) * 128);
-            }
+        // The warps that own X^T rows (lane quarters 0 and 1) take their P values and later run the X
+        // epilogue; the other two quarters turn R, for two state rows each (their own and the one 64
+        // below).  Both read the panels as TMA landed them: rows of consecutive columns, one lane each.
+        if (alive && !tc_wait(tc_smem(&bars[4]), step & 1)) {
+            alive = false;
+            atomicExch(fault, 4);
         }
-        // The warps that own X^T rows (lane quarters 0 and 1) load P and later run the X epilogue; the
-        // other two quarters turn R, for two state rows each (their own and the one 64 below).
         float rv[TC_N], rv2[TC_N], pv[TC_N];
         if (has_x) {
-            const float* pg = panel_ptr(p.P, gi) + (part * TC_N) * DP + col0 + row;
+            const float* ps = reinterpret_cast<const float*>(sPraw) + (part * TC_N) * SCAN_NS + row;
 #pragma unroll
-            for (int j = 0; j < TC_N; ++j) pv[j] = __ldcg(pg + j * DP);
+            for (int j = 0; j < TC_N; ++j) pv[j] = ps[j * SCAN_NS];
         } else {
-            const float* rg = panel_ptr(p.R, gi) + (part * TC_N) * DP + row;
+            const float* rs = reinterpret_cast<const float*>(sRraw) + (part * TC_N) * DP + row;
 #pragma unroll
-            for (int j = 0; j < TC_N; ++j) rv[j] = __ldcg(rg + j * DP);
+            for (int j = 0; j < TC_N; ++j) rv[j] = rs[j * DP];
 #pragma unroll
-            for (int j = 0; j < TC_N; ++j) rv2[j] = __ldcg(rg + j * DP - 64);
+            for (int j = 0; j < TC_N; ++j) rv2[j] = rs[j * DP - 64];
         }
         TC_STAMP(2);
         if (p.ckb != nullptr) {
@@ -375,6 +403,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, c
         tc_fence_async_smem();
         tc_fence_before();
         __syncthreads();
+        issue_rp(step + 1);   // every thread has taken its R and P values of this step
         if (tid == 0) {
             tc_fence_after();
             const unsigned aR = tc_smem(sR), bX = tc_smem(sX);
