@@ -214,7 +214,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, c
     unsigned char* sR = sX + TC_X_BYTES;              // A of the second: R^T           (rows = state rows, K = tokens)
     unsigned char* sRraw = tsm + SCAN_TC_OPERAND_BYTES;   // R as it lies, [CL][DP]
     unsigned char* sPraw = sRraw + TC_PANEL_BYTES;        // the P slice as it lies, [CL][NS]
-    __shared__ __align__(8) unsigned long long bars[5];   // two contraction barriers, two Q ring slots, R/P
+    __shared__ __align__(8) unsigned long long bars[6];   // two contractions, two Q slots, R/P landed, R/P taken
     __shared__ unsigned s_tmem;
 
     const int col0 = blockIdx.x * SCAN_NS;
@@ -233,6 +233,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, c
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&bars[2])));
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&bars[3])));
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&bars[4])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(tc_smem(&bars[5])), "r"(TC_THREADS));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -328,6 +329,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, c
 #pragma unroll
             for (int j = 0; j < TC_N; ++j) rv2[j] = rs[j * DP - 64];
         }
+        // every thread reports that it holds its values; thread 0 then refills the slot for the next step
+        // right away instead of after the second barrier (the load gets most of a step to land)
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(&bars[5])) : "memory");
+        if (tid == 0) {
+            if (alive && !tc_wait(tc_smem(&bars[5]), step & 1)) {
+                alive = false;
+                atomicExch(fault, 5);
+            }
+            issue_rp(step + 1);
+        }
+        __syncwarp();
         TC_STAMP(2);
         if (p.ckb != nullptr) {
             bf16* ck = p.ckb + gi * (long long)(DP * DP) + row * DP + col0 + c0;
@@ -403,7 +415,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, c
         tc_fence_async_smem();
         tc_fence_before();
         __syncthreads();
-        issue_rp(step + 1);   // every thread has taken its R and P values of this step
         if (tid == 0) {
             tc_fence_after();
             const unsigned aR = tc_smem(sR), bX = tc_smem(sX);
