@@ -19,9 +19,10 @@
 // rows, is written element by element into the transposed operand, with the
 // K-chunk pitch padded to 144 bytes so that a warp's 32 rows hit 32 banks.
 // R [tok][p], whose contraction index is the slow one in global memory, is
-// turned through registers: a thread loads columns of it, coalesced over the
-// warp, and writes each as 16-byte chunks of one operand row (the warps
-// without X^T rows do this, two columns per thread).  The decay
+// landed as it lies by a tiled TMA load (with the CTA's slice of P) and turned
+// through registers: a thread reads columns of it, one lane per column, and
+// writes each as 16-byte chunks of one operand row (the warps without X^T
+// rows do this, two columns per thread).  The decay
 // diag(lam) is one scalar per thread, applied on the way back into tensor
 // memory; checkpoints and X go to global memory from the same registers.
 // Operands are rounded to TF32 (round to nearest) before the tensor core,
