@@ -278,7 +278,11 @@ __device__ __forceinline__ void sources_bwd_rows(const BwdParams& p, const Chunk
         store8_bpanel(bpanel_ptr(p.DG, ch.gi), i, c0, dg_);
         store8_bpanel(bpanel_ptr(p.Dd, ch.gi), i, c0, dd);
         store8_bpanel(bpanel_ptr(p.Xext, ch.gi), i, c0, xext);
-        // value side: dv = sigmoid(write) dR, d write_raw = dR v sigmoid'(write)
+    }
+    // value side: dv = sigmoid(write) dR, d write_raw = dR v sigmoid'(write)
+#pragma unroll
+    for (int pp = 0; pp < ROW_PASSES; ++pp) {
+        const int i = lr + ROWS_PER_PASS * pp;
         float wr[8], v[8], dr[8], dv[8], dwr[8];
         load8_bf16<FAST>(row_bf16(p.wr, ch, i), c0, V, p.wr.vec, i < ch.nvalid, wr);
         load8_bf16<FAST>(row_bf16(p.v, ch, i), c0, V, p.v.vec, i < ch.nvalid, v);

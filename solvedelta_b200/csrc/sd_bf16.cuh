@@ -174,25 +174,27 @@ constexpr size_t BSTATE_BYTES = size_t(DP) * LDB * 2;  // a whole state in BF16
 //   UPPER == false: T lower  (Mr[i][k], k < i), rows solved first to last;
 //   UPPER == true : T upper  (Mr[i][k], k > i), rows solved last to first
 //                   (this is how a transposed lower system is passed in).
-// Entries outside the stated triangle must be exactly zero.
-// The 64 rows are cut into four 16-row blocks: the off-diagonal coupling
-// RHS_I -= sgn * T[I, solved] X[solved] runs on the tensor cores over all 16
-// warps (TF32, or split-TF32 "3x" when SPLIT for FP32-grade products), only the
-// 16x16 diagonal blocks are substituted on the FP32 pipes, one thread per column.
+// Entries outside the stated triangle must be exactly zero.  Mr is consumed: its
+// 16 x 16 diagonal blocks are replaced by (I + sgn T_II)^-1 - I.
+// The 64 rows are cut into four 16-row blocks.  First the four diagonal blocks are
+// inverted by substitution (one warp per block, one lane per column of the inverse).
+// After that every warp owns 16 of the 256 right-hand-side columns for the whole
+// solve and never waits for another warp: per block it subtracts the coupling with the
+// blocks already solved and applies the inverted diagonal block, both on the tensor
+// cores (TF32; split-TF32 "3x" coupling when SPLIT).  The identity part of the
+// inverse is added from the FP32 registers, so only the correction (T_II^-1 - I) r
+// sees TF32 operand rounding.
 struct PanelF32 {
     float* p0;
     float* p1;
     __device__ __forceinline__ float get(int k, int n) const {
         return (n < DP ? p0 : p1)[k * LDP + (n & (DP - 1))];
     }
-    __device__ __forceinline__ void sub2(int i, int n, float v0, float v1) const {
-        float2* q = reinterpret_cast<float2*>((n < DP ? p0 : p1) + i * LDP + (n & (DP - 1)));
-        float2 o = *q;
-        *q = make_float2(o.x - v0, o.y - v1);
+    __device__ __forceinline__ float2 get2(int i, int n) const {
+        return *reinterpret_cast<const float2*>((n < DP ? p0 : p1) + i * LDP + (n & (DP - 1)));
     }
-    __device__ __forceinline__ float load(int i, int col) const { return get(i, col); }
-    __device__ __forceinline__ void store(int i, int col, float v) const {
-        (col < DP ? p0 : p1)[i * LDP + (col & (DP - 1))] = v;
+    __device__ __forceinline__ void put2(int i, int n, float v0, float v1) const {
+        *reinterpret_cast<float2*>((n < DP ? p0 : p1) + i * LDP + (n & (DP - 1))) = make_float2(v0, v1);
     }
 };
 struct PanelBF16 {
@@ -201,29 +203,81 @@ struct PanelBF16 {
     __device__ __forceinline__ float get(int k, int n) const {
         return __bfloat162float((n < DP ? p0 : p1)[k * LDB + (n & (DP - 1))]);
     }
-    __device__ __forceinline__ void sub2(int i, int n, float v0, float v1) const {
-        __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>((n < DP ? p0 : p1) + i * LDB + (n & (DP - 1)));
-        float2 o = __bfloat1622float2(*q);
-        *q = __floats2bfloat162_rn(o.x - v0, o.y - v1);
+    __device__ __forceinline__ float2 get2(int i, int n) const {
+        return __bfloat1622float2(
+            *reinterpret_cast<const __nv_bfloat162*>((n < DP ? p0 : p1) + i * LDB + (n & (DP - 1))));
     }
-    __device__ __forceinline__ float load(int i, int col) const { return get(i, col); }
-    __device__ __forceinline__ void store(int i, int col, float v) const {
-        (col < DP ? p0 : p1)[i * LDB + (col & (DP - 1))] = __float2bfloat16_rn(v);
+    __device__ __forceinline__ void put2(int i, int n, float v0, float v1) const {
+        *reinterpret_cast<__nv_bfloat162*>((n < DP ? p0 : p1) + i * LDB + (n & (DP - 1))) =
+            __floats2bfloat162_rn(v0, v1);
     }
 };
 
 template <bool UPPER, bool SPLIT, class Panel>
-__device__ __forceinline__ void trisolve_blocked(const float* Mr, float sgn, Panel P) {
+__device__ __forceinline__ void trisolve_blocked(float* Mr, float sgn, Panel P) {
+    static_assert(NTHREADS == 2 * DP * 2, "16 warps of 16 right-hand-side columns each");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     constexpr int NB = CL / 16;
+    // ---- the four diagonal blocks: D_I <- (I + sgn T_II)^-1 - I, in place -------------
+    if (warp < NB) {
+        float* D = Mr + (16 * warp) * LDA + 16 * warp;
+        const int j = lane & 15;   // column of the inverse (both half-warps compute the same block)
+        float x[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) x[i] = (i == j) ? 1.f : 0.f;
+        if (!UPPER) {
+#pragma unroll
+            for (int i = 1; i < 16; ++i) {
+                float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+                for (int k4 = 0; k4 < i; k4 += 4) {
+                    const float4 m = *reinterpret_cast<const float4*>(D + i * LDA + k4);
+                    a0 = fmaf(m.x, x[k4], a0);
+                    a1 = fmaf(m.y, x[k4 + 1], a1);
+                    a0 = fmaf(m.z, x[k4 + 2], a0);
+                    a1 = fmaf(m.w, x[k4 + 3], a1);
+                }
+                x[i] = (i > j) ? -sgn * (a0 + a1) : x[i];
+            }
+        } else {
+#pragma unroll
+            for (int i = 14; i >= 0; --i) {
+                float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+                for (int k4 = ((i + 1) & ~3); k4 < 16; k4 += 4) {
+                    const float4 m = *reinterpret_cast<const float4*>(D + i * LDA + k4);
+                    a0 = fmaf(m.x, x[k4], a0);
+                    a1 = fmaf(m.y, x[k4 + 1], a1);
+                    a0 = fmaf(m.z, x[k4 + 2], a0);
+                    a1 = fmaf(m.w, x[k4 + 3], a1);
+                }
+                x[i] = (i < j) ? -sgn * (a0 + a1) : x[i];
+            }
+        }
+        __syncwarp();   // every lane has read the block before anyone overwrites it
+        if (lane < 16) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) D[i * LDA + j] = (i == j) ? 0.f : x[i];
+        }
+    }
+    __syncthreads();
+    // ---- warp-local sweep over this warp's 16 columns ---------------------------------
+    const int n0 = 16 * warp;
 #pragma unroll 1
     for (int step = 0; step < NB; ++step) {
         const int I = UPPER ? (NB - 1 - step) : step;
+        const int r0 = 16 * I;
+        float rr[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const int j = n0 + nt * 8 + 2 * t;
+            const float2 a = P.get2(r0 + g, j), b = P.get2(r0 + g + 8, j);
+            rr[nt][0] = a.x; rr[nt][1] = a.y; rr[nt][2] = b.x; rr[nt][3] = b.y;
+        }
         if (step > 0) {
-            // RHS[I] -= sgn * Mr[I rows][solved cols] * X[solved rows]; warp w owns columns 16w..16w+15
+            // r = RHS[I] - sgn * Mr[I rows][solved cols] * X[solved rows]
             const int kbeg = UPPER ? 16 * (I + 1) : 0;
             const int kend = UPPER ? CL : 16 * I;
-            const int r0 = 16 * I, n0 = 16 * warp;
             float acc[2][4];
             acc_zero<2>(acc);
             for (int kk = kbeg; kk < kend; kk += 8) {
@@ -249,52 +303,41 @@ __device__ __forceinline__ void trisolve_blocked(const float* Mr, float sgn, Pan
             }
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) rr[nt][e] = fmaf(-sgn, acc[nt][e], rr[nt][e]);
                 const int j = n0 + nt * 8 + 2 * t;
-                P.sub2(r0 + g, j, sgn * acc[nt][0], sgn * acc[nt][1]);
-                P.sub2(r0 + g + 8, j, sgn * acc[nt][2], sgn * acc[nt][3]);
+                P.put2(r0 + g, j, rr[nt][0], rr[nt][1]);
+                P.put2(r0 + g + 8, j, rr[nt][2], rr[nt][3]);
             }
-            __syncthreads();
+            __syncwarp();
         }
-        if (threadIdx.x < 2 * DP) {
-            // 16 x 16 diagonal block, one thread per right-hand-side column
-            const int col = threadIdx.x;
-            float x[16];
+        {
+            // X[I] = r + (D_I) r : the block's own rows, K = 16
+            float acc[2][4];
+            acc_zero<2>(acc);
 #pragma unroll
-            for (int ii = 0; ii < 16; ++ii) x[ii] = P.load(16 * I + ii, col);
-            if (!UPPER) {
+            for (int kk = 0; kk < 16; kk += 8) {
+                const uint32_t a0 = f2tf32(Mr[(r0 + g) * LDA + r0 + kk + t]);
+                const uint32_t a1 = f2tf32(Mr[(r0 + g + 8) * LDA + r0 + kk + t]);
+                const uint32_t a2 = f2tf32(Mr[(r0 + g) * LDA + r0 + kk + t + 4]);
+                const uint32_t a3 = f2tf32(Mr[(r0 + g + 8) * LDA + r0 + kk + t + 4]);
 #pragma unroll
-                for (int ii = 1; ii < 16; ++ii) {
-                    float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-                    for (int k4 = 0; k4 < ii; k4 += 4) {
-                        float4 m = *reinterpret_cast<const float4*>(Mr + (16 * I + ii) * LDA + 16 * I + k4);
-                        a0 = fmaf(m.x, x[k4], a0);
-                        a1 = fmaf(m.y, x[k4 + 1], a1);
-                        a0 = fmaf(m.z, x[k4 + 2], a0);
-                        a1 = fmaf(m.w, x[k4 + 3], a1);
-                    }
-                    x[ii] = fmaf(-sgn, a0 + a1, x[ii]);
-                }
-            } else {
-#pragma unroll
-                for (int ii = 14; ii >= 0; --ii) {
-                    float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-                    for (int k4 = ((ii + 1) & ~3); k4 < 16; k4 += 4) {
-                        float4 m = *reinterpret_cast<const float4*>(Mr + (16 * I + ii) * LDA + 16 * I + k4);
-                        a0 = fmaf(m.x, x[k4], a0);
-                        a1 = fmaf(m.y, x[k4 + 1], a1);
-                        a0 = fmaf(m.z, x[k4 + 2], a0);
-                        a1 = fmaf(m.w, x[k4 + 3], a1);
-                    }
-                    x[ii] = fmaf(-sgn, a0 + a1, x[ii]);
+                for (int nt = 0; nt < 2; ++nt) {
+                    const uint32_t b0 = f2tf32(P.get(r0 + kk + t, n0 + nt * 8 + g));
+                    const uint32_t b1 = f2tf32(P.get(r0 + kk + t + 4, n0 + nt * 8 + g));
+                    mma_tf32(acc[nt], a0, a1, a2, a3, b0, b1);
                 }
             }
 #pragma unroll
-            for (int ii = 0; ii < 16; ++ii) P.store(16 * I + ii, col, x[ii]);
+            for (int nt = 0; nt < 2; ++nt) {
+                const int j = n0 + nt * 8 + 2 * t;
+                P.put2(r0 + g, j, rr[nt][0] + acc[nt][0], rr[nt][1] + acc[nt][1]);
+                P.put2(r0 + g + 8, j, rr[nt][2] + acc[nt][2], rr[nt][3] + acc[nt][3]);
+            }
+            __syncwarp();
         }
-        __syncthreads();
     }
+    __syncthreads();
 }
 
 }  // namespace sd

@@ -87,7 +87,8 @@ __device__ __forceinline__ const float* state_ptr(const float* base, long long g
     return base + gi * (long long)(DP * DP);
 }
 
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
+// 1 / (1 + exp(-x)) with the fast reciprocal (2 ulp): exp(-x) = inf gives exactly 0.
+__device__ __forceinline__ float sigmoidf_(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
 // ---- half-warp (16 lanes = one token row) reductions ---------------------
 __device__ __forceinline__ float row_sum16(float v) {
