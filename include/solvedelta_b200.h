@@ -71,6 +71,13 @@ typedef struct {
     size_t saved_bytes;
     void *scratch;                      /* temporary (sd_forward_scratch_bytes) */
     size_t scratch_bytes;
+    /* Token masks, one byte per token, contiguous [B,T]; either may be NULL.  A token whose
+     * valid byte is 0 takes no part: zero output, state and gradients untouched.  A valid token
+     * whose reset byte is non-zero starts from the zero state.  Replaces the gather into
+     * reset-free segments of causallsso/ops/operator.py:96-193 (semantics:
+     * causallsso/reference.py:157-164,216-226); handled inside the kernels, no host work. */
+    const unsigned char *valid_mask;
+    const unsigned char *reset_mask;
 } sd_forward_args;
 
 typedef struct {
@@ -87,6 +94,8 @@ typedef struct {
     float *dlog_decay;                  /* FP32 [B,T,H,r] */
     float *dgamma;                      /* FP32 [B,T,H] */
     float *dC0, *dS0;                   /* FP32 or NULL */
+    const unsigned char *valid_mask;    /* the masks the forward call was given (or NULL) */
+    const unsigned char *reset_mask;
 } sd_backward_args;
 
 typedef struct {

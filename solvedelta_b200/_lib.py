@@ -82,7 +82,8 @@ class ForwardArgs(ctypes.Structure):
         ("C0", ctypes.c_void_p), ("S0", ctypes.c_void_p), ("y", ctypes.c_void_p),
         ("C_T", ctypes.c_void_p), ("S_T", ctypes.c_void_p),
         ("saved", ctypes.c_void_p), ("saved_bytes", ctypes.c_size_t),
-        ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t)])
+        ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t),
+        ("valid_mask", ctypes.c_void_p), ("reset_mask", ctypes.c_void_p)])
 
 
 class BackwardArgs(ctypes.Structure):
@@ -94,7 +95,8 @@ class BackwardArgs(ctypes.Structure):
         ("dkeys", ctypes.c_void_p), ("dvalues", ctypes.c_void_p),
         ("derase_raw", ctypes.c_void_p), ("dwrite_raw", ctypes.c_void_p),
         ("dlog_decay", ctypes.c_void_p), ("dgamma", ctypes.c_void_p),
-        ("dC0", ctypes.c_void_p), ("dS0", ctypes.c_void_p)])
+        ("dC0", ctypes.c_void_p), ("dS0", ctypes.c_void_p),
+        ("valid_mask", ctypes.c_void_p), ("reset_mask", ctypes.c_void_p)])
 
 
 class DecodeArgs(ctypes.Structure):

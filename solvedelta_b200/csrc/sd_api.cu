@@ -175,6 +175,8 @@ Geometry make_geometry(const sd_shape& s) {
     Geometry g;
     g.B = s.B; g.T = s.T; g.H = s.H; g.r = s.r; g.V = s.V;
     g.NC = (s.T + CL - 1) / CL;
+    g.valid = nullptr;
+    g.reset = nullptr;
     g.dbg = nullptr;
     g.dbg_block = 0;
     return g;
@@ -322,6 +324,8 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
     const sd_shape* s = &a->shape;
     FwdParams p;
     p.g = make_geometry(*s);
+    p.g.valid = a->valid_mask;
+    p.g.reset = a->reset_mask;
     p.u = make_operand(a->u, 2);
     p.h = make_operand(a->h, 2);
     p.q = make_operand(a->q, 2);
@@ -423,6 +427,8 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
     const sd_shape* s = &a->shape;
     BwdParams p;
     p.g = make_geometry(*s);
+    p.g.valid = a->valid_mask;
+    p.g.reset = a->reset_mask;
     p.u = make_operand(a->u, 2);
     p.h = make_operand(a->h, 2);
     p.q = make_operand(a->q, 2);

@@ -135,8 +135,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) 
             load8_panel(gG, i, c0, G);
             load8_panel(gG, i0 + BT - 1, c0, Ge);
             load8_panel(gG, i0 ? i0 - 1 : 0, c0, Gp);
-            load8_bf16<FAST>(row_bf16(p.er, ch, i), c0, r, p.er.vec, i < ch.nvalid, er);
-            load8_bf16<FAST>(row_bf16(p.dy, ch, i), c0, V, p.dy.vec, i < ch.nvalid, dy);
+            load8_bf16<FAST>(row_bf16(p.er, ch, i), c0, r, p.er.vec, ch.ok(i), er);
+            load8_bf16<FAST>(row_bf16(p.dy, ch, i), c0, V, p.dy.vec, ch.ok(i), dy);
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 se[e] = sigmoidf_(er[e]);
@@ -219,7 +219,7 @@ __device__ __forceinline__ void sources_bwd_rows(const BwdParams& p, const Chunk
         load8_panel(gDelta, i, c0, dl);
         load8_panel(gd, i, c0, d);
         load8_panel(gG, i, c0, G);
-        load8_bf16<FAST>(row_bf16(p.er, ch, i), c0, r, p.er.vec, i < ch.nvalid, er);
+        load8_bf16<FAST>(row_bf16(p.er, ch, i), c0, r, p.er.vec, ch.ok(i), er);
 #pragma unroll
         for (int e = 0; e < 8; ++e) se[e] = sigmoidf_(er[e]);
         Sources src;
@@ -284,8 +284,8 @@ __device__ __forceinline__ void sources_bwd_rows(const BwdParams& p, const Chunk
     for (int pp = 0; pp < ROW_PASSES; ++pp) {
         const int i = lr + ROWS_PER_PASS * pp;
         float wr[8], v[8], dr[8], dv[8], dwr[8];
-        load8_bf16<FAST>(row_bf16(p.wr, ch, i), c0, V, p.wr.vec, i < ch.nvalid, wr);
-        load8_bf16<FAST>(row_bf16(p.v, ch, i), c0, V, p.v.vec, i < ch.nvalid, v);
+        load8_bf16<FAST>(row_bf16(p.wr, ch, i), c0, V, p.wr.vec, ch.ok(i), wr);
+        load8_bf16<FAST>(row_bf16(p.v, ch, i), c0, V, p.v.vec, ch.ok(i), v);
         load8_bsm(sdR, i, c0, dr);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
@@ -569,12 +569,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
             load8_panel(gG, i0 + BT - 1, c0, Ge);
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-                E[e] = i > 0 ? E[e] : 0.f;
+                E[e] = (i > 0 ? E[e] : 0.f) - ch.eoff(i);
                 Gp[e] = i0 ? Gp[e] : 0.f;
             }
             load8_panel(gDelta, i, c0, dl);
             load8_bpanel(gDd, i, c0, dd);
-            const float gm = (i < ch.nvalid) ? *row_f32(p.gam, ch, i) : 0.f;
+            const float gm = ch.ok(i) ? *row_f32(p.gam, ch, i) : 0.f;
             float uc[8], ub[8], rn[8], ddr[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
@@ -681,8 +681,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
             acc[nt][2] += pb.x; acc[nt][3] += pb.y;
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                kha[nt][e] = (ia < ch.nvalid && j + e < r) ? __bfloat162float(ka[j + e]) * rka : 0.f;
-                khb[nt][e] = (ib < ch.nvalid && j + e < r) ? __bfloat162float(kb[j + e]) * rkb : 0.f;
+                kha[nt][e] = (ch.ok(ia) && j + e < r) ? __bfloat162float(ka[j + e]) * rka : 0.f;
+                khb[nt][e] = (ch.ok(ib) && j + e < r) ? __bfloat162float(kb[j + e]) * rkb : 0.f;
             }
             dota = fmaf(acc[nt][0], kha[nt][0], fmaf(acc[nt][1], kha[nt][1], dota));
             dotb = fmaf(acc[nt][2], khb[nt][0], fmaf(acc[nt][3], khb[nt][1], dotb));
@@ -710,9 +710,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
             for (int e = 0; e < 2; ++e) {
                 if (j + e < r) {
                     if (ia < ch.nvalid)
-                        rowa[j + e] = __float2bfloat16_rn((acc[nt][e] - dota * kha[nt][e]) * rka);
+                        rowa[j + e] = __float2bfloat16_rn(ch.ok(ia) ? (acc[nt][e] - dota * kha[nt][e]) * rka : 0.f);
                     if (ib < ch.nvalid)
-                        rowb[j + e] = __float2bfloat16_rn((acc[nt][2 + e] - dotb * khb[nt][e]) * rkb);
+                        rowb[j + e] = __float2bfloat16_rn(ch.ok(ib) ? (acc[nt][2 + e] - dotb * khb[nt][e]) * rkb : 0.f);
                 }
             }
         }
@@ -828,7 +828,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
             load8_panel(gG, i0 + BT - 1, c0, Ge);
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-                E[e] = i > 0 ? E[e] : 0.f;
+                E[e] = (i > 0 ? E[e] : 0.f) - ch.eoff(i);
                 Gp[e] = i0 ? Gp[e] : 0.f;
             }
             load8_panel(gDelta, i, c0, dl);
@@ -893,8 +893,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
             float2 fa = __bfloat1622float2(da), fb = __bfloat1622float2(db);
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                float h_a = (ia < ch.nvalid && j + e < r) ? __bfloat162float(ha[j + e]) : 0.f;
-                float h_b = (ib < ch.nvalid && j + e < r) ? __bfloat162float(hb[j + e]) : 0.f;
+                float h_a = (ch.ok(ia) && j + e < r) ? __bfloat162float(ha[j + e]) : 0.f;
+                float h_b = (ch.ok(ib) && j + e < r) ? __bfloat162float(hb[j + e]) : 0.f;
                 suma = fmaf(e ? fa.y : fa.x, h_a - acc[nt][e], suma);
                 sumb = fmaf(e ? fb.y : fb.x, h_b - acc[nt][2 + e], sumb);
             }
@@ -955,6 +955,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
             const int ref = fast ? r0 + BT - 1 : r0 - 1;
             float2 E = make_float2(0.f, 0.f), Gp = make_float2(0.f, 0.f);
             if (i > 0) E = *reinterpret_cast<const float2*>(gG + (i - 1) * DP + j);
+            E.x -= ch.eoff(i);
+            E.y -= ch.eoff(i);
             if (ref >= 0) Gp = *reinterpret_cast<const float2*>(gG + ref * DP + j);
             return make_float2(__expf(E.x - Gp.x), __expf(E.y - Gp.y));
         });
@@ -969,7 +971,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
     if (threadIdx.x < CL && threadIdx.x < ch.nvalid) {
         const int i = threadIdx.x;
         p.dgam[((long long)ch.b * p.g.T + ch.t0 + i) * p.g.H + ch.hh] =
-            (s_dot[i * 4] + s_dot[i * 4 + 1]) + (s_dot[i * 4 + 2] + s_dot[i * 4 + 3]);
+            ch.ok(i) ? (s_dot[i * 4] + s_dot[i * 4 + 1]) + (s_dot[i * 4 + 2] + s_dot[i * 4 + 3]) : 0.f;
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
@@ -978,7 +980,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
         float al[BT];
         block_alphas(al, fG);
         auto fu = [&](int j, int c) {
-            return (j < ch.nvalid && c < r) ? __bfloat162float(row_bf16(p.u, ch, j)[c]) * s_ru[j] : 0.f;
+            return (ch.ok(j) && c < r) ? __bfloat162float(row_bf16(p.u, ch, j)[c]) * s_ru[j] : 0.f;
         };
         auto add_to = [](bf16* panel) {
             return [panel](int i, int c, float v) {
@@ -988,7 +990,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
         };
         diag_sweep<true, true, true, true>(
             al, [&](int i, int i0, float (&row)[BT]) { prow16_bf16(b_dN, LDM, i, i0, row); }, fu, fu,
-            add_to(b_dl), add_to(b_tj));
+            add_to(b_dl), add_to(b_tj), ch.rm);
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
@@ -1004,7 +1006,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
             load8_panel(gG, i, c0, G);
             load8_panel(gG, i > 0 ? i - 1 : 0, c0, E);  // E = G of the previous row (0 for the first)
 #pragma unroll
-            for (int e = 0; e < 8; ++e) E[e] = i > 0 ? E[e] : 0.f;
+            for (int e = 0; e < 8; ++e) E[e] = (i > 0 ? E[e] : 0.f) - ch.eoff(i);
             float dup[8], tpre[8], dub[8], dut[8], ti[8], tj[8], dgp[8], xext[8], drr[8];
             load8_bpanel(bpanel_ptr(p.duPart, ch.gi), i, c0, dup);
             load8_bpanel(bpanel_ptr(p.Tu, ch.gi), i, c0, tpre);
@@ -1046,9 +1048,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
         float run = __expf(gG[(CL - 1) * DP + c]) * (p.SdS[ch.gi * DP + c] + s_cdc[c]) + xs;
         for (int i = CL - 1; i >= 0; --i) {
             run += s_dG[i * LDP + c];
+            // a masked token has no gradient; nor does the decay of a reset token, which multiplies the zero state
             if (i < ch.nvalid)
                 p.dld[(((long long)ch.b * p.g.T + ch.t0 + i) * p.g.H + ch.hh) * (long long)r + c] =
-                    run - s_dE[i * LDP + c];
+                    (ch.ok(i) && !ch.rst(i)) ? run - s_dE[i * LDP + c] : 0.f;
         }
     }
     SD_PHASE(p.g, ph);

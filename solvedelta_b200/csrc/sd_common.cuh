@@ -35,8 +35,17 @@ struct Operand {
     int vec;               // 1 when 16-byte vector access is legal
 };
 
+// A reset token starts from the zero state.  It is carried as RESET_NATS of extra forgetting in
+// the token's log decay: exp(-RESET_NATS) is exactly zero in FP32, so every decay-weighted term
+// that would cross the reset vanishes -- pair entries, the carried-in state, the carried-out
+// contributions of earlier tokens, the chunk's retention -- while terms inside one segment only
+// see differences of the prefix, in which the offset cancels.
+constexpr float RESET_NATS = 128.f;
+
 struct Geometry {
     int B, T, H, r, V, NC;  // NC = chunks per stream
+    const unsigned char* valid;  // [B][T] bytes, 0 = token takes no part (null: every token is valid)
+    const unsigned char* reset;  // [B][T] bytes, 1 = token starts from the zero state (null: none)
     long long* dbg;         // diagnostic phase clock stamps of one CTA (null = off)
     int dbg_block;
 };
@@ -53,6 +62,12 @@ struct Geometry {
 struct Chunk {
     int s, c, b, hh, t0, nvalid;
     long long gi;  // global chunk index s * NC + c
+    unsigned long long vm;  // bit i: token row i exists and is valid
+    unsigned long long rm;  // bit i: token row i is a (valid) reset token
+    __device__ __forceinline__ bool ok(int i) const { return (vm >> i) & 1ull; }
+    __device__ __forceinline__ bool rst(int i) const { return (rm >> i) & 1ull; }
+    // what the exclusive prefix E_i = G_{i-1} of a reset row still lacks: the reset belongs to row i itself
+    __device__ __forceinline__ float eoff(int i) const { return rst(i) ? RESET_NATS : 0.f; }
 };
 
 __device__ __forceinline__ Chunk chunk_of(const Geometry& g, int idx) {
@@ -65,6 +80,23 @@ __device__ __forceinline__ Chunk chunk_of(const Geometry& g, int idx) {
     ch.t0 = ch.c * CL;
     int left = g.T - ch.t0;
     ch.nvalid = left < CL ? left : CL;
+    if (g.valid == nullptr && g.reset == nullptr) {
+        ch.vm = ch.nvalid >= CL ? ~0ull : ((1ull << ch.nvalid) - 1ull);
+        ch.rm = 0ull;
+    } else {
+        // every warp reads the chunk's 64 mask bytes (all threads call chunk_of together)
+        const int lane = threadIdx.x & 31;
+        const unsigned char* vp = g.valid ? g.valid + (long long)ch.b * g.T + ch.t0 : nullptr;
+        const unsigned char* rp = g.reset ? g.reset + (long long)ch.b * g.T + ch.t0 : nullptr;
+        const bool v0 = lane < ch.nvalid && (vp == nullptr || vp[lane] != 0);
+        const bool v1 = lane + 32 < ch.nvalid && (vp == nullptr || vp[lane + 32] != 0);
+        const bool r0 = v0 && rp != nullptr && rp[lane] != 0;
+        const bool r1 = v1 && rp != nullptr && rp[lane + 32] != 0;
+        ch.vm = (unsigned long long)__ballot_sync(0xffffffffu, v0) |
+                ((unsigned long long)__ballot_sync(0xffffffffu, v1) << 32);
+        ch.rm = (unsigned long long)__ballot_sync(0xffffffffu, r0) |
+                ((unsigned long long)__ballot_sync(0xffffffffu, r1) << 32);
+    }
     return ch;
 }
 
@@ -186,10 +218,19 @@ __device__ __forceinline__ void store8_bf16(void* base, const Geometry& g, const
         __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&raw);
 #pragma unroll
         for (int e = 0; e < 4; ++e) p[e] = __floats2bfloat162_rn(x[2 * e], x[2 * e + 1]);
+        if (!ch.ok(i)) raw = make_uint4(0u, 0u, 0u, 0u);   // a masked token: exact zeros
         if (i < ch.nvalid && c0 < width) *reinterpret_cast<uint4*>(row + c0) = raw;
         return;
     }
     if (i >= ch.nvalid || c0 >= width) return;
+    if (!ch.ok(i)) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            if (c0 + e < width)
+                (reinterpret_cast<__nv_bfloat16*>(base) +
+                 (((long long)ch.b * g.T + ch.t0 + i) * g.H + ch.hh) * (long long)width)[c0 + e] = __float2bfloat16_rn(0.f);
+        return;
+    }
     __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(base) +
                          (((long long)ch.b * g.T + ch.t0 + i) * g.H + ch.hh) * (long long)width;
     if ((width & 7) == 0) {
@@ -219,7 +260,7 @@ __device__ __forceinline__ void prefetch_rows(const Operand& op, const Chunk& ch
     const int lines = (row_bytes + 127) / 128;
     for (int idx = threadIdx.x; idx < CL * lines; idx += NTHREADS) {
         const int i = idx / lines, l = idx - i * lines;
-        if (i < ch.nvalid) {
+        if (ch.ok(i)) {
             const char* row = reinterpret_cast<const char*>(op.ptr) +
                               (ch.b * op.sb + (long long)(ch.t0 + i) * op.st + ch.hh * op.sh) * elem_bytes;
             prefetch_l2(row + l * 128);
@@ -333,7 +374,7 @@ __device__ __forceinline__ void load_norm_panel(const Operand& op, const Chunk& 
     for (int p = 0; p < ROW_PASSES; ++p) {
         int i = lr + ROWS_PER_PASS * p;
         float x[8];
-        load8_bf16<FAST>(row_bf16(op, ch, i), c0, width, op.vec, i < ch.nvalid, x);
+        load8_bf16<FAST>(row_bf16(op, ch, i), c0, width, op.vec, ch.ok(i), x);
         float ss = 0.f;
 #pragma unroll
         for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
@@ -352,7 +393,7 @@ __device__ __forceinline__ void load_raw_panel(const Operand& op, const Chunk& c
     for (int p = 0; p < ROW_PASSES; ++p) {
         int i = lr + ROWS_PER_PASS * p;
         float x[8];
-        load8_bf16<FAST>(row_bf16(op, ch, i), c0, width, op.vec, i < ch.nvalid, x);
+        load8_bf16<FAST>(row_bf16(op, ch, i), c0, width, op.vec, ch.ok(i), x);
 #pragma unroll
         for (int e = 0; e < 8; ++e) sm[i * LDP + c0 + e] = x[e];
     }
@@ -365,7 +406,7 @@ __device__ __forceinline__ void load_f32_panel(const Operand& op, const Chunk& c
     for (int p = 0; p < ROW_PASSES; ++p) {
         int i = lr + ROWS_PER_PASS * p;
         float x[8];
-        load8_f32<FAST>(row_f32(op, ch, i), c0, width, op.vec, i < ch.nvalid, x);
+        load8_f32<FAST>(row_f32(op, ch, i), c0, width, op.vec, ch.ok(i), x);
 #pragma unroll
         for (int e = 0; e < 8; ++e) sm[i * LDP + c0 + e] = x[e];
     }
@@ -374,7 +415,7 @@ __device__ __forceinline__ void load_f32_panel(const Operand& op, const Chunk& c
 __device__ __forceinline__ void load_gamma(const Operand& op, const Chunk& ch, float* sg) {
     if (threadIdx.x < CL) {
         int i = threadIdx.x;
-        sg[i] = (i < ch.nvalid) ? *row_f32(op, ch, i) : 0.f;
+        sg[i] = ch.ok(i) ? *row_f32(op, ch, i) : 0.f;
     }
 }
 

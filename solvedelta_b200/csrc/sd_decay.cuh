@@ -271,8 +271,11 @@ __device__ __forceinline__ void block_alphas(float (&al)[BT], FG fG) {
 //   XE: x is the exclusive prefix (j < i only);  STRICT: the term j == i is skipped.
 //   fP16(i, i0, row): the BT entries P[i][i0 .. i0+BT) (the same address for every thread of a warp);
 //   fb(j, c) / fa(i, c): column-side / row-side operand themselves (not centred).
+//   reset_rows: bit i set when token row i is a reset token.  Only the exclusive prefix needs it (XE): the
+//   reset belongs to row i itself, which the running product over rows j+1 .. i-1 does not contain.
 template <bool XE, bool STRICT, bool CAUSAL, bool ANTI, class FP16, class FB, class FA, class FOC, class FOA>
-__device__ __forceinline__ void diag_sweep(const float (&al)[BT], FP16 fP16, FB fb, FA fa, FOC oc, FOA oa) {
+__device__ __forceinline__ void diag_sweep(const float (&al)[BT], FP16 fP16, FB fb, FA fa, FOC oc, FOA oa,
+                                           unsigned long long reset_rows = 0ull) {
     const int c = threadIdx.x & (DP - 1), i0 = (threadIdx.x >> 7) * BT;
     float bv[BT], accA[BT];
 #pragma unroll
@@ -285,7 +288,7 @@ __device__ __forceinline__ void diag_sweep(const float (&al)[BT], FP16 fP16, FB 
         float prow[BT];
         fP16(i0 + ii, i0, prow);
         const float av = ANTI ? fa(i0 + ii, c) : 0.f;
-        float accC = 0.f, rho = 1.f;
+        float accC = 0.f, rho = (XE && ((reset_rows >> (i0 + ii)) & 1ull)) ? 0.f : 1.f;
 #pragma unroll
         for (int jj = XE ? ii - 1 : ii; jj >= 0; --jj) {
             if (!(STRICT && jj == ii)) {

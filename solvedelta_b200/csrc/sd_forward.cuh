@@ -64,7 +64,7 @@ __device__ __forceinline__ void sources_fwd(const float (&uh)[8], const float (&
 template <bool FAST>
 __device__ __forceinline__ float load8_norm(const Operand& op, const Chunk& ch, int i, int c0, int width,
                                             float (&x)[8]) {
-    load8_bf16<FAST>(row_bf16(op, ch, i), c0, width, op.vec, i < ch.nvalid, x);
+    load8_bf16<FAST>(row_bf16(op, ch, i), c0, width, op.vec, ch.ok(i), x);
     float ss = 0.f;
 #pragma unroll
     for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
@@ -124,6 +124,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
     load_f32_panel<FAST>(p.ld, ch, r, s_G);
     load_raw_panel<FAST>(p.h, ch, r, s_h);
     load_gamma(p.gam, ch, s_gam);
+    if (ch.rm != 0ull) {   // block-uniform: a reset token forgets RESET_NATS more (each thread patches what it loaded)
+        const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
+#pragma unroll
+        for (int pp = 0; pp < ROW_PASSES; ++pp) {
+            const int i = lr + ROWS_PER_PASS * pp;
+            if (ch.rst(i)) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) s_G[i * LDP + c0 + e] -= RESET_NATS;
+            }
+        }
+    }
     __syncthreads();
     SD_PHASE(p.g, ph);
     chunk_cumsum(s_G);
@@ -136,7 +147,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
         int i = idx >> 7, c = idx & (DP - 1);
         const int i0 = i & ~(BT - 1);
         float G = s_G[i * LDP + c];
-        float E = i ? s_G[(i - 1) * LDP + c] : 0.f;
+        float E = (i ? s_G[(i - 1) * LDP + c] : 0.f) - ch.eoff(i);
         float Gprev = i0 ? s_G[(i0 - 1) * LDP + c] : 0.f;
         float Gend = s_G[(i0 + BT - 1) * LDP + c];
         float uh = s_uh[i * LDP + c];
@@ -168,6 +179,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) x[e] = 0.f;
             }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) x[e] -= ch.eoff(i);
             pair_diag_row<1, true>(i, a, x, [&](int j, float (&b)[8]) { load8_smem(s_uh, j, c0, b); },
                                    [&](int j, float (&G)[8]) { load8_smem(s_G, j, c0, G); }, out);
             const int j = (i & ~(BT - 1)) + (threadIdx.x & 15);
@@ -180,7 +193,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
     for (int idx = threadIdx.x; idx < CL * DP; idx += NTHREADS) {
         int i = idx >> 7, c = idx & (DP - 1);
         float gm = s_gam[i];
-        float E = i ? s_G[(i - 1) * LDP + c] : 0.f;
+        float E = (i ? s_G[(i - 1) * LDP + c] : 0.f) - ch.eoff(i);
         s_h[i * LDP + c] *= gm;
         s_ut[i * LDP + c] = gm * s_uh[i * LDP + c] * __expf(E);
     }
@@ -380,9 +393,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
             load8_norm<FAST>(p.k, ch, i, c0, r, kh);
             load8_norm<FAST>(p.q, ch, i, c0, r, qh);
             load8_panel(gDelta, i, c0, dl);
-            load8_bf16<FAST>(row_bf16(p.er, ch, i), c0, r, p.er.vec, i < ch.nvalid, er);
-            load8_bf16<FAST>(row_bf16(p.wr, ch, i), c0, V, p.wr.vec, i < ch.nvalid, wr);
-            load8_bf16<FAST>(row_bf16(p.v, ch, i), c0, V, p.v.vec, i < ch.nvalid, v);
+            load8_bf16<FAST>(row_bf16(p.er, ch, i), c0, r, p.er.vec, ch.ok(i), er);
+            load8_bf16<FAST>(row_bf16(p.wr, ch, i), c0, V, p.wr.vec, ch.ok(i), wr);
+            load8_bf16<FAST>(row_bf16(p.v, ch, i), c0, V, p.v.vec, ch.ok(i), v);
             load8_smem(s_d, i, c0, d);
             load8_smem(s_G, i, c0, G);
             load8_smem(s_G, i0 ? i0 - 1 : 0, c0, Gp);
@@ -506,6 +519,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_output_fwd(FwdParams p) {
     __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y);
     warp_epi<NT128>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
         if (i >= ch.nvalid || j >= V) return;
+        if (!ch.ok(i)) v0 = v1 = 0.f;   // a masked token: exact zeros
         __nv_bfloat16* row = y + (((long long)ch.b * p.g.T + ch.t0 + i) * p.g.H + ch.hh) * (long long)V;
         if (j + 1 < V && (V & 1) == 0) {
             *reinterpret_cast<__nv_bfloat162*>(row + j) = __floats2bfloat162_rn(v0, v1);

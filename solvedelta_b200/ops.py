@@ -22,7 +22,7 @@ from typing import NamedTuple, Optional, Tuple
 import torch
 
 from . import _lib
-from .packing import PackedSegments, pack_tokens, unpack_tokens
+from .packing import PackedSegments
 
 
 class SolveDeltaState(NamedTuple):
@@ -75,12 +75,20 @@ def _fill_operands(args, tensors):
     args.gamma = _gamma_operand(gam)
 
 
+def _mask_bytes(mask: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """bool [B,T] -> the same bytes as uint8 (a view, no copy when contiguous)."""
+    if mask is None:
+        return None
+    return mask.contiguous().view(torch.uint8)
+
+
 class _SolveDeltaFunction(torch.autograd.Function):
-    """forward(u,h,q,k,v,log_decay,erase_raw,write_raw,gamma[B,T,H],C0|None,S0|None)
-    -> (y, C_T, S_T); k,v,erase_raw,write_raw are the 4-D views without the edit axis."""
+    """forward(u,h,q,k,v,log_decay,erase_raw,write_raw,gamma[B,T,H],C0|None,S0|None,valid|None,reset|None)
+    -> (y, C_T, S_T); k,v,erase_raw,write_raw are the 4-D views without the edit axis; valid / reset
+    are uint8 [B,T] token masks applied inside the kernels."""
 
     @staticmethod
-    def forward(ctx, u, h, q, k, v, log_decay, erase_raw, write_raw, gamma, C0, S0):
+    def forward(ctx, u, h, q, k, v, log_decay, erase_raw, write_raw, gamma, C0, S0, valid=None, reset=None):
         lib = _lib.load()
         device = u.device
         B, T, H, r = u.shape
@@ -101,9 +109,11 @@ class _SolveDeltaFunction(torch.autograd.Function):
             args.y, args.C_T, args.S_T = y.data_ptr(), C_T.data_ptr(), S_T.data_ptr()
             args.saved, args.saved_bytes = saved.data_ptr(), saved.numel()
             args.scratch, args.scratch_bytes = scratch.data_ptr(), scratch.numel()
+            args.valid_mask, args.reset_mask = _ptr(valid), _ptr(reset)
             _lib.check(lib.sd_forward(ctypes.byref(args), _stream_ptr(device)))
         ctx.set_materialize_grads(False)
         ctx.has_state = (C0 is not None, S0 is not None)
+        ctx.masks = (valid, reset)
         ctx.save_for_backward(u, h, q, k, v, log_decay, erase_raw, write_raw, gamma, saved)
         return y, C_T, S_T
 
@@ -147,10 +157,12 @@ class _SolveDeltaFunction(torch.autograd.Function):
             args.derase_raw, args.dwrite_raw = der.data_ptr(), dwr.data_ptr()
             args.dlog_decay, args.dgamma = dld.data_ptr(), dgam.data_ptr()
             args.dC0, args.dS0 = dC0.data_ptr(), dS0.data_ptr()
+            valid, reset = ctx.masks
+            args.valid_mask, args.reset_mask = _ptr(valid), _ptr(reset)
             _lib.check(lib.sd_backward(ctypes.byref(args), _stream_ptr(device)))
         has_C0, has_S0 = ctx.has_state
         return (du, dh, dq, dk, dv, dld, der, dwr, dgam,
-                dC0 if has_C0 else None, dS0 if has_S0 else None)
+                dC0 if has_C0 else None, dS0 if has_S0 else None, None, None)
 
 
 def _decode_step(u, h, q, k, v, log_decay, erase_raw, write_raw, gamma, C0, S0):
@@ -185,6 +197,8 @@ def solvedelta_residual_frame_native(
     *,
     initial_state: Optional[SolveDeltaState] = None,
     return_final_state: bool = True,
+    _valid_mask: Optional[torch.Tensor] = None,
+    _reset_mask: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, Optional[SolveDeltaState]]:
     """Dense BF16 path from raw gate logits.
 
@@ -249,7 +263,8 @@ def solvedelta_residual_frame_native(
         return output, solvedelta_zero_state(batch, heads, rank, value_dim, dtype=torch.float32,
                                              device=u.device)
 
-    if length == 1 and not torch.is_grad_enabled():
+    masked = _valid_mask is not None or _reset_mask is not None
+    if length == 1 and not torch.is_grad_enabled() and not masked:
         # single-token recurrent inference (causallsso/ops/residual_frame/operator.py:198-216)
         y, C, S = _decode_step(u, h, q, k4, v4, associative_log_decay, er4, wr4, geometry_write,
                                predictor_initial, memory_initial)
@@ -257,7 +272,7 @@ def solvedelta_residual_frame_native(
 
     y, C_T, S_T = _SolveDeltaFunction.apply(
         u, h, q, k4, v4, associative_log_decay, er4, wr4, geometry_write,
-        predictor_initial, memory_initial)
+        predictor_initial, memory_initial, _mask_bytes(_valid_mask), _mask_bytes(_reset_mask))
     if not return_final_state:
         return y, None
     return y, SolveDeltaState(predictor=C_T, S=S_T)
@@ -296,15 +311,6 @@ def solvedelta_native(
         initial_state=initial_state, return_final_state=return_final_state)
 
 
-def _segment_rows(tensor: torch.Tensor, plan: PackedSegments, destination: torch.Tensor,
-                  padded_length: int) -> torch.Tensor:
-    """[B,T,...] -> [S,padded_length,...]: one row per segment, zero (neutral) tokens behind it."""
-    tokens = pack_tokens(tensor, plan).squeeze(0)
-    rows = tokens.new_zeros(plan.num_segments * padded_length, *tokens.shape[1:])
-    rows = rows.index_copy(0, destination, tokens)
-    return rows.view(plan.num_segments, padded_length, *tokens.shape[1:])
-
-
 def solvedelta_segmented_native(
     u: torch.Tensor,
     h: torch.Tensor,
@@ -320,67 +326,25 @@ def solvedelta_segmented_native(
     initial_state: Optional[SolveDeltaState] = None,
     return_final_state: bool = False,
 ) -> Tuple[torch.Tensor, Optional[SolveDeltaState]]:
-    """Masked / reset batches as one neutral-padded batch of reset-free segments.
+    """Masked / reset batches, same contract as causallsso/ops/operator.py:96-193.
 
-    Same contract as causallsso/ops/operator.py:96-193: invalid tokens produce
-    zero output and leave the state untouched, a reset token starts from the
-    zero state, the first segment of a batch row continues ``initial_state``
-    unless it opens with a reset, and the returned state of a row is that of
-    its last segment (or its initial state if the row has no valid token).
-    Zero raw operands are neutral for the recurrence (no decay, no write), so
-    segments are padded to the longest one without a mask inside the kernels.
+    Invalid tokens produce zero output and leave the state untouched, a reset token
+    starts from the zero state, the returned state of a batch row is the one after its
+    last valid token (its initial state if it has none).  Upstream gathers the valid
+    tokens into a padded batch of reset-free segments and scatters the result back;
+    here the kernels read the two token masks of ``plan`` themselves (a masked token is
+    a neutral token, a reset is extra forgetting that no decay-weighted term survives),
+    so the operands stay where they are and the call does no host work.
     """
-    batch, _, heads, rank = u.shape
-    value_dim = values.shape[-1]
-    if (plan.batch, plan.length) != tuple(u.shape[:2]):
+    batch, length, heads, rank = u.shape
+    if (plan.batch, plan.length) != (batch, length):
         raise ValueError("packed segment plan does not match the operator input")
-    if plan.num_tokens == 0:
-        output = values.new_zeros(batch, plan.length, heads, value_dim)
-        if not return_final_state:
-            return output, None
-        if initial_state is not None:
-            return output, initial_state
-        return output, solvedelta_zero_state(batch, heads, rank, value_dim, dtype=torch.float32,
-                                             device=u.device)
-
-    padded_length = plan.max_seqlen
-    position = torch.arange(plan.num_tokens, dtype=torch.long, device=u.device) - plan.cu_seqlens[plan.segment_ids]
-    destination = plan.segment_ids * padded_length + position
-    operands = [u, h, q, keys, values, associative_log_decay, erase_raw, write_raw]
-    rows = [_segment_rows(t, plan, destination, padded_length) for t in operands]
-    if geometry_write.shape == (batch, plan.length, heads):
-        gamma_rows = _segment_rows(geometry_write, plan, destination, padded_length)
-    else:
-        gamma_rows = geometry_write  # per-head rate: padded tokens have zero residual anyway
-
-    segment_initial = None
-    if initial_state is not None:
-        keep = plan.use_initial[:, None, None, None]
-        # index_select adds the cotangents of segments that share a batch row
-        predictor = initial_state.predictor.index_select(0, plan.segment_batch)
-        memory = initial_state.S.index_select(0, plan.segment_batch)
-        segment_initial = SolveDeltaState(
-            predictor=torch.where(keep, predictor, torch.zeros_like(predictor)),
-            S=torch.where(keep, memory, torch.zeros_like(memory)))
-
-    segment_output, segment_final = solvedelta_native(
-        *rows, gamma_rows, initial_state=segment_initial, return_final_state=return_final_state)
-    flat_out = segment_output.reshape(plan.num_segments * padded_length, heads, value_dim)
-    output = unpack_tokens(flat_out.index_select(0, destination).unsqueeze(0), plan)
-    if not return_final_state:
-        return output, None
-    if segment_final is None:
-        raise RuntimeError("segmented native owners did not return final state")
-    has_segment = (plan.last_segment >= 0)[:, None, None, None]
-    chosen = plan.last_segment.clamp_min(0)
-    predictor = segment_final.predictor.index_select(0, chosen)
-    memory = segment_final.S.index_select(0, chosen)
-    if initial_state is None:
-        base_predictor, base_memory = torch.zeros_like(predictor), torch.zeros_like(memory)
-    else:
-        base_predictor, base_memory = initial_state.predictor, initial_state.S
-    return output, SolveDeltaState(predictor=torch.where(has_segment, predictor, base_predictor),
-                                   S=torch.where(has_segment, memory, base_memory))
+    if plan.valid_mask is None or plan.reset_mask is None:
+        raise ValueError("the segment plan carries no token masks (build it with build_packed_segments)")
+    return solvedelta_residual_frame_native(
+        u, h, q, keys, values, associative_log_decay, erase_raw, write_raw, geometry_write,
+        initial_state=initial_state, return_final_state=return_final_state,
+        _valid_mask=plan.valid_mask, _reset_mask=plan.reset_mask)
 
 
 __all__ = [

@@ -31,6 +31,8 @@ class PackedSegments:
     segment_batch_cpu: torch.Tensor
     use_initial_cpu: torch.Tensor
     last_segment: torch.Tensor     # [B] last segment of each batch row, -1 if the row has none
+    valid_mask: torch.Tensor = None  # the two bool [B,T] masks the plan was built from: the operator
+    reset_mask: torch.Tensor = None  # kernels read them directly (the gathers above serve the conv)
 
     @property
     def num_tokens(self) -> int:
@@ -68,7 +70,8 @@ def build_packed_segments(valid_mask: torch.Tensor, reset_mask: torch.Tensor) ->
             cu_seqlens=zero.to(device), cu_seqlens_cpu=zero,
             segment_batch_cpu=torch.empty(0, dtype=torch.long),
             use_initial_cpu=torch.empty(0, dtype=torch.bool),
-            last_segment=torch.full((batch,), -1, dtype=torch.long, device=device))
+            last_segment=torch.full((batch,), -1, dtype=torch.long, device=device),
+            valid_mask=valid_mask, reset_mask=reset_mask)
 
     row = indices // length
     resets_here = reset_mask.reshape(-1)[indices]
@@ -92,7 +95,8 @@ def build_packed_segments(valid_mask: torch.Tensor, reset_mask: torch.Tensor) ->
         batch=batch, length=length, indices=indices, segment_ids=segment_ids,
         segment_batch=segment_batch, use_initial=use_initial, segment_lengths=segment_lengths,
         cu_seqlens=cu_cpu.to(device), cu_seqlens_cpu=cu_cpu, segment_batch_cpu=host[:, 1],
-        use_initial_cpu=host[:, 2].bool(), last_segment=last_segment)
+        use_initial_cpu=host[:, 2].bool(), last_segment=last_segment,
+        valid_mask=valid_mask, reset_mask=reset_mask)
 
 
 def pack_tokens(tensor: torch.Tensor, plan: PackedSegments) -> torch.Tensor:

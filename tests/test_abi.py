@@ -34,8 +34,8 @@ def test_struct_sizes_match_header():
     # int32 x5, padded to 8 before the first pointer-bearing operand
     assert ctypes.sizeof(_lib.Shape) == 20
     assert ctypes.sizeof(_lib.Operand) == 32
-    assert ctypes.sizeof(_lib.ForwardArgs) == 24 + 9 * 32 + 5 * 8 + 4 * 8
-    assert ctypes.sizeof(_lib.BackwardArgs) == 24 + 10 * 32 + 2 * 8 + 4 * 8 + 11 * 8
+    assert ctypes.sizeof(_lib.ForwardArgs) == 24 + 9 * 32 + 5 * 8 + 4 * 8 + 2 * 8
+    assert ctypes.sizeof(_lib.BackwardArgs) == 24 + 10 * 32 + 2 * 8 + 4 * 8 + 11 * 8 + 2 * 8
     assert ctypes.sizeof(_lib.DecodeArgs) == 24 + 9 * 32 + 3 * 8
     # mixer glue: three int32 (padded to 16) + pointers / strides / sizes of 8 bytes each
     assert ctypes.sizeof(_lib.Conv4ForwardArgs) == 16 + 7 * 8
