@@ -15,8 +15,12 @@ seed+rank.  Rank 0 prints one JSON line.
              (pinned) buffers: host->device copies of every operand and
              device->host copies of the output and all gradients are inside the
              timed region.
-`roofline`   dominant kernel: algorithmic bytes per launch / measured launch
-             time, against the measured HBM peak.
+`roofline`   `frac` is the whole path: compulsory HBM bytes of one step / step
+             time, against the measured HBM peak.  `kernel_frac` is the same
+             ratio for the dominant kernel alone on its own inputs and
+             outputs; `traffic_per_step` sums the DRAM bytes of all launches
+             (from the ncu table under profiles/), `traffic_ratio` divides
+             that by the compulsory bytes.
 `cpu_baseline`  the FP64 CPU checker (a port of the upstream token loop) timed
              on the host cores on a bounded sample of the same workload.
 
@@ -39,6 +43,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 WORKLOAD = dict(B=8, H=8, T=4096, r=128, V=128)
+REPEATS = 3   # timed repeats of the block of --steps steps
 METRIC = "solvedelta_fwd_bwd_tokens_per_s"
 # compulsory HBM bytes of one token of one head, forward + backward:
 # fwd reads 7 BF16 vectors + FP32 decay + gamma, writes y; bwd reads the same
@@ -262,11 +267,14 @@ class DeviceStep:
         self.lib_mod.check(self.lib.sd_backward(ctypes.byref(self.ba), st))
 
     def profile(self):
+        """Device time of every launch of one step, from the profiling build of the library (an event
+        between launches); the timed legs above run the product build."""
+        diag = self.lib_mod.load_diagnostics()
         ms = (ctypes.c_float * 40)()
         count = ctypes.c_int(0)
-        self.lib_mod.check(self.lib.sd_profile_step(ctypes.byref(self.fa), ctypes.byref(self.ba), self.stream(),
-                                                    ms, 40, ctypes.byref(count)))
-        return [(self.lib.sd_launch_name(i).decode(), float(ms[i])) for i in range(count.value)]
+        self.lib_mod.check(diag.sd_profile_step(ctypes.byref(self.fa), ctypes.byref(self.ba), self.stream(),
+                                                ms, 40, ctypes.byref(count)))
+        return [(diag.sd_launch_name(i).decode(), float(ms[i])) for i in range(count.value)]
 
 
 # Algorithmic HBM bytes one launch of each kernel must move, per chunk of 64
@@ -298,15 +306,57 @@ KERNEL_BYTES_PER_CHUNK = {
 }
 
 
-# DRAM bytes per chunk task measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) on the
-# B=8, T=1024 case of this workload (profiles/chunk_kernels_B8_T1024_ncu_full.md); traffic is
-# proportional to the number of chunk tasks, so a full launch moves 4096 times these.
-KERNEL_DRAM_BYTES_PER_CHUNK = {
-    "k_prep_fwd": 154 * KIB, "k_state_scan[C]": 184 * KIB, "k_primal_fwd": 180 * KIB,
-    "k_exterior_prep_fwd": 288 * KIB, "k_state_scan[S]": 121 * KIB, "k_output_fwd": 75 * KIB,
-    "k_exterior_prep_bwd": 321 * KIB, "k_state_scan_b[dS]": 103 * KIB, "k_exterior_pair_bwd": 542 * KIB,
-    "k_primal_bwd": 278 * KIB, "k_state_scan_b[dC]": 102 * KIB, "k_predictor_close_bwd": 305 * KIB,
-}
+# DRAM bytes per chunk task of every kernel, as ncu measured them (dram__bytes_read.sum +
+# dram__bytes_write.sum on the B=8, T=1024 case; traffic is proportional to the number of chunk tasks).
+# The table is a text file written by `python bench.py --summarize-ncu <ncu csv>`; without it the
+# traffic figures of the line are null.
+DRAM_TABLE = os.path.join(ROOT, "profiles", "dram_bytes_per_chunk_task.txt")
+
+
+def load_dram_table(path=DRAM_TABLE):
+    table = {}
+    if not os.path.exists(path):
+        return table
+    with open(path) as f:
+        for line in f:
+            parts = line.split()
+            if len(parts) >= 2 and not line.startswith("#"):
+                try:
+                    table[parts[0]] = float(parts[1]) * KIB
+                except ValueError:
+                    continue
+    return table
+
+
+def summarize_ncu(csv_path, tasks):
+    """ncu --csv log with dram__bytes_read.sum / dram__bytes_write.sum / gpu__time_duration.sum of the
+    launches of ONE fwd+bwd step -> the text table load_dram_table reads (KiB per chunk task)."""
+    import csv
+
+    with open(csv_path) as f:
+        rows = list(csv.DictReader(l for l in f if l.startswith('"')))
+    per_launch, order = {}, []
+    for row in rows:
+        key = row["ID"]
+        if key not in per_launch:
+            per_launch[key] = {"name": row["Kernel Name"]}
+            order.append(key)
+        val = float(row["Metric Value"].replace(",", ""))
+        unit = row.get("Metric Unit", "")
+        scale = {"Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9, "byte": 1.0}.get(unit, 1.0)
+        per_launch[key][row["Metric Name"]] = val * scale
+    scans = iter(("k_state_scan[C]", "k_state_scan[S]"))
+    scans_b = iter(("k_state_scan_b[dS]", "k_state_scan_b[dC]"))
+    print("# kernel  KiB-per-chunk-task (DRAM read + write, ncu)  time-us")
+    for key in order:
+        m = per_launch[key]
+        name = m["name"].split("(")[0].replace("void ", "").split("<")[0].replace("sd::", "")
+        if name == "k_state_scan_tc":
+            name = next(scans)
+        elif name == "k_state_scan_b":
+            name = next(scans_b)
+        total = m.get("dram__bytes_read.sum", 0.0) + m.get("dram__bytes_write.sum", 0.0)
+        print(f"{name} {total / tasks / KIB:.1f} {m.get('gpu__time_duration.sum', 0.0) / 1e3:.1f}")
 
 
 def time_mixer_glue(B, T, H, r, V, device, reps=10):
@@ -591,14 +641,18 @@ def run_ours(opts, rank, world, local_rank):
         runner.step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(opts.steps):
-        runner.step()
-    e1.record()
-    barrier()
-    ms_total = e0.elapsed_time(e1)
+    # the block of `--steps` steps is timed REPEATS times, each between a barrier + synchronize on both
+    # sides and taken as the max over ranks; the line reports the median block and the spread
+    block_ms = []
+    for _ in range(REPEATS):
+        e0.record()
+        for _ in range(opts.steps):
+            runner.step()
+        e1.record()
+        barrier()
+        block_ms.append(max_over_ranks(e0.elapsed_time(e1), device) / opts.steps)
     clocks = sampler.stop() if rank == 0 else None
-    ms_step = max_over_ranks(ms_total, device) / opts.steps
+    ms_step = sorted(block_ms)[len(block_ms) // 2]
     value = job_throughput(runner.tokens, ms_step * 1e-3, world)
 
     # ---- forward only (the kernel-level forward configuration), same inputs ----
@@ -617,6 +671,7 @@ def run_ours(opts, rank, world, local_rank):
     if rank == 0:
         acc = {}
         reps = 3
+        runner.profile()   # first use of the profiling build: module load and kernel attributes stay out of the average
         for _ in range(reps):
             for name, ms in runner.profile():
                 acc[name] = acc.get(name, 0.0) + ms / reps
@@ -626,16 +681,22 @@ def run_ours(opts, rank, world, local_rank):
         chunks = runner.streams * ((T + 63) // 64)
         alg = KERNEL_BYTES_PER_CHUNK[top] * chunks
         peak, peak_kind = _peaks()
-        achieved = alg / (acc[top] * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "kernel": top, "achieved": round(achieved, 1), "peak": peak,
-                    "unit": "GB/s", "frac": round(achieved / peak, 4),
-                    "traffic": KERNEL_DRAM_BYTES_PER_CHUNK.get(top, 0) * chunks or None,
-                    "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": alg,
-                    "launch_ms": round(acc[top], 4)}
+        kernel_achieved = alg / (acc[top] * 1e-3) / 1e9
         path_bytes = runner.tokens * H * BYTES_PER_TOKEN_HEAD + runner.streams * STATE_BYTES_PER_STREAM
-        roofline["path"] = {"algorithmic_bytes_per_step": path_bytes,
-                            "achieved": round(path_bytes / (ms_step * 1e-3) / 1e9, 1),
-                            "frac": round(path_bytes / (ms_step * 1e-3) / 1e9 / peak, 4)}
+        path_achieved = path_bytes / (ms_step * 1e-3) / 1e9
+        dram = load_dram_table()
+        step_traffic = sum(dram.get(k, 0.0) for k in acc) * chunks if all(k in dram for k in acc) else None
+        # `frac` is the whole path (compulsory bytes of a step / step time / peak); the dominant kernel's own
+        # figure, on its own inputs and outputs, sits beside it as kernel_frac
+        roofline = {"bound": "hbm", "achieved": round(path_achieved, 1), "peak": peak, "unit": "GB/s",
+                    "frac": round(path_achieved / peak, 4), "peak_kind": f"of {peak_kind}",
+                    "algorithmic_bytes_per_step": path_bytes,
+                    "traffic": int(dram[top] * chunks) if top in dram else None,
+                    "traffic_per_step": int(step_traffic) if step_traffic else None,
+                    "traffic_ratio": round(step_traffic / path_bytes, 2) if step_traffic else None,
+                    "kernel": top, "kernel_achieved": round(kernel_achieved, 1),
+                    "kernel_frac": round(kernel_achieved / peak, 4),
+                    "kernel_algorithmic_bytes_per_launch": alg, "kernel_launch_ms": round(acc[top], 4)}
 
     # ---- end to end through the public entry point with host buffers -------
     # Every step copies all operands from pinned host memory to the device, runs
@@ -731,6 +792,10 @@ def run_ours(opts, rank, world, local_rank):
         torch.cuda.empty_cache()
         causal_lm = _side_leg(time_causal_lm, device)
 
+    # every bounded wait inside the kernels completed (this synchronises; the timed regions are over)
+    from solvedelta_b200._lib import check_device_fault
+    check_device_fault()
+
     if rank == 0:
         cpu_baseline = None
         if world == 1 and not opts.skip_cpu:
@@ -749,7 +814,13 @@ def run_ours(opts, rank, world, local_rank):
             "config": {"workload": f"operator fwd+bwd, B={B} per GPU, H={H}, T={T}, r=V={r}, chunk=64, "
                                    "non-zero C0/S0 and state cotangents",
                        "l2": "inputs of one step (0.7 GB) exceed the 126 MB L2; no flush needed",
-                       "arithmetic": "bf16 operands, tf32 tensor-core contractions, fp32 states"},
+                       "arithmetic": "bf16 operands, tf32 tensor-core contractions, fp32 states",
+                       "tolerance": "parity tests: norm-wise max relative error max|a-b|/max|b| per tensor, "
+                                    "2e-2 outputs and gradients, 1e-3 FP32 states; relative L2 3e-2 on gradients",
+                       "timing": f"median of {REPEATS} blocks of --steps steps",
+                       "cpu_arm": "C/OpenMP port of the upstream FP64 token loop on a bounded sample "
+                                  "(see cpu_baseline.sample); not the same config as the GPU arm"},
+            "ms_per_step_min": min(block_ms), "ms_per_step_max": max(block_ms), "repeats": REPEATS,
             "clocks": clocks, "e2e": e2e, "gpu_launches": runner.launches * opts.steps,
             "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu_baseline,
             "forward_only": {"ms_per_step": fwd_ms, "value": job_throughput(runner.tokens, fwd_ms * 1e-3, world),
@@ -830,9 +901,15 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg (profiler captures)")
     ap.add_argument("--skip-glue", action="store_true", help="skip the mixer glue kernels (profiler captures)")
     ap.add_argument("--skip-model", action="store_true", help="skip the 24-layer causal LM legs")
+    ap.add_argument("--summarize-ncu", metavar="CSV", default=None,
+                    help="no GPU work: turn an ncu --csv log of one step's launches (medium case, 1024 chunk tasks) "
+                         "into the DRAM table of profiles/ on stdout")
     ap.add_argument("--model-ddp", action="store_true",
                     help="side measurement: only the data-parallel 24-layer training step at the launched world size")
     opts = ap.parse_args()
+    if opts.summarize_ncu:
+        summarize_ncu(opts.summarize_ncu, tasks=8 * 8 * (1024 // 64))
+        return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -150,28 +150,20 @@ int sd_forward_launches(const sd_shape *shape);
 int sd_backward_launches(const sd_shape *shape);
 
 /*
- * Diagnostic (no upstream counterpart): runs sd_forward and, when `bwd` is not
- * NULL, sd_backward, with a CUDA event between launches, waits for the stream
- * and returns the device time of every launch in milliseconds (`count`
- * entries, in launch order; sd_launch_name gives their names).  Not thread
- * safe; not for use inside stream capture.
+ * Device fault word.  Every wait inside the kernels is bounded; a wait that runs out does
+ * not hang the GPU: it stores a code here, the kernel walks to its end, and the results of
+ * that launch are undefined.  Codes (all from the tensor-memory state scan): 1 = the first
+ * contraction of a step (X = P + Q St) never completed, 2 = the second (state update),
+ * 3 = a step's Q panel never landed, 4 = its R / P panels never landed, 5 = the slot of
+ * the R / P panels was never released.  No upstream counterpart.
+ *
+ * sd_device_fault waits for the device and returns the word (0 = no fault, -1 = the device
+ * could not be read); the word stays set until sd_device_fault_clear() (which also waits
+ * for the device) puts it back to 0.  Callers that already synchronise -- the end of a
+ * training step, of a generation loop, of a benchmark -- should read it there.
  */
-int sd_profile_step(const sd_forward_args *fwd, const sd_backward_args *bwd, void *stream,
-                    float *ms, int capacity, int *count);
-const char *sd_launch_name(int index);
-/*
- * Diagnostic (no upstream counterpart): when `device_buffer` (at least
- * 16*16 int64) is not NULL, one CTA of every chunk kernel records the SM
- * clock at each of its phase boundaries into slot [launch index][phase];
- * NULL switches the recording off.  Process-wide, not thread safe.
- */
-void sd_debug_timeline(void *device_buffer);
-
-/* Waits for the device and returns its fault word: 0 when every bounded wait
- * inside the kernels completed, 1 or 2 when a tensor-core completion barrier
- * of the state scan ran out of polls (the results of that launch are then
- * undefined), -1 when the device could not be read. */
 int sd_device_fault(void);
+int sd_device_fault_clear(void);
 
 /*
  * Introspection for tests: offset and size of a named intermediate panel

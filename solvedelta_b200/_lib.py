@@ -17,6 +17,9 @@ _ROOT = os.path.dirname(_PKG)
 _SRC = os.path.join(_PKG, "csrc")
 _BUILD = os.path.join(_PKG, "_build")
 LIB_PATH = os.path.join(_BUILD, "libsolvedelta_b200.so")
+# the profiling build: same sources with -DSD_DIAGNOSTICS (phase clock stamps, per-launch events);
+# only bench.py's per-kernel breakdown loads it
+DIAG_LIB_PATH = os.path.join(_BUILD, "libsolvedelta_b200_diag.so")
 HEADER_PATH = os.path.join(_ROOT, "include", "solvedelta_b200.h")
 
 NVCC_FLAGS = [
@@ -40,27 +43,29 @@ def _nvcc():
     return None
 
 
-def is_stale() -> bool:
-    if not os.path.exists(LIB_PATH):
+def is_stale(path: str = LIB_PATH) -> bool:
+    if not os.path.exists(path):
         return True
-    built = os.path.getmtime(LIB_PATH)
+    built = os.path.getmtime(path)
     return any(os.path.getmtime(s) > built for s in _sources())
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile csrc/*.cu into the in-tree shared library (sm_100a only)."""
-    if not force and not is_stale():
-        return LIB_PATH
+    """Compile csrc/*.cu into the in-tree shared libraries (sm_100a only): the product library and
+    its profiling twin."""
     nvcc = _nvcc()
-    if nvcc is None:
-        raise RuntimeError("nvcc not found: cannot build libsolvedelta_b200.so")
-    os.makedirs(_BUILD, exist_ok=True)
-    units = [os.path.join(_SRC, n) for n in sorted(os.listdir(_SRC)) if n.endswith(".cu")]
-    cmd = [nvcc, *NVCC_FLAGS, "-o", LIB_PATH, *units]
-    if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-    subprocess.check_call(cmd)
+    for path, extra in ((LIB_PATH, []), (DIAG_LIB_PATH, ["-DSD_DIAGNOSTICS"])):
+        if not force and not is_stale(path):
+            continue
+        if nvcc is None:
+            raise RuntimeError("nvcc not found: cannot build " + os.path.basename(path))
+        os.makedirs(_BUILD, exist_ok=True)
+        units = [os.path.join(_SRC, n) for n in sorted(os.listdir(_SRC)) if n.endswith(".cu")]
+        cmd = [nvcc, *NVCC_FLAGS, *extra, "-o", path, *units]
+        if verbose:
+            cmd.insert(1, "-Xptxas")
+            cmd.insert(2, "-v")
+        subprocess.check_call(cmd)
     return LIB_PATH
 
 
@@ -139,13 +144,33 @@ EXPORTS = (
     "sd_saved_bytes", "sd_forward_scratch_bytes", "sd_backward_scratch_bytes",
     "sd_forward", "sd_backward", "sd_decode_step", "sd_forward_launches",
     "sd_backward_launches", "sd_panel_info", "sd_status_string", "sd_version",
-    "sd_chunk_tokens", "sd_profile_step", "sd_launch_name", "sd_forward_static", "sd_panel_kind", "sd_debug_timeline", "sd_device_fault",
+    "sd_chunk_tokens", "sd_forward_static", "sd_panel_kind", "sd_device_fault", "sd_device_fault_clear",
     "sd_conv4_backward_scratch_bytes", "sd_conv4_silu_forward", "sd_conv4_silu_backward",
     "sd_kda_gate_backward_scratch_bytes", "sd_kda_gate_forward", "sd_kda_gate_backward",
     "sd_norm_gate_backward_scratch_bytes", "sd_norm_gate_forward", "sd_norm_gate_backward",
 )
 
 _lib = None
+_diag = None
+
+
+def load_diagnostics() -> ctypes.CDLL:
+    """The profiling build (-DSD_DIAGNOSTICS): everything the product library exports plus
+    sd_profile_step / sd_launch_name / sd_debug_timeline.  Only measurement code loads it."""
+    global _diag
+    if _diag is None:
+        if not os.path.exists(DIAG_LIB_PATH):
+            raise RuntimeError(f"{DIAG_LIB_PATH} is missing: run solvedelta_b200.build()")
+        _diag = _declare(ctypes.CDLL(DIAG_LIB_PATH))
+        _diag.sd_debug_timeline.restype = None
+        _diag.sd_debug_timeline.argtypes = [ctypes.c_void_p]
+        _diag.sd_profile_step.restype = ctypes.c_int
+        _diag.sd_profile_step.argtypes = [ctypes.POINTER(ForwardArgs), ctypes.POINTER(BackwardArgs),
+                                          ctypes.c_void_p, ctypes.POINTER(ctypes.c_float), ctypes.c_int,
+                                          ctypes.POINTER(ctypes.c_int)]
+        _diag.sd_launch_name.restype = ctypes.c_char_p
+        _diag.sd_launch_name.argtypes = [ctypes.c_int]
+    return _diag
 
 
 def load() -> ctypes.CDLL:
@@ -157,7 +182,11 @@ def load() -> ctypes.CDLL:
         raise RuntimeError(
             f"{LIB_PATH} is missing: build it with `python -c 'import solvedelta_b200; "
             "solvedelta_b200.build()'` (needs nvcc); there is no fallback path")
-    lib = ctypes.CDLL(LIB_PATH)
+    _lib = _declare(ctypes.CDLL(LIB_PATH))
+    return _lib
+
+
+def _declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     sp = ctypes.POINTER(Shape)
     for name in ("sd_saved_bytes", "sd_forward_scratch_bytes", "sd_backward_scratch_bytes"):
         getattr(lib, name).restype = ctypes.c_size_t
@@ -190,22 +219,26 @@ def load() -> ctypes.CDLL:
         getattr(lib, name).argtypes = [ctypes.POINTER(struct), ctypes.c_void_p]
     lib.sd_device_fault.restype = ctypes.c_int
     lib.sd_device_fault.argtypes = []
-    lib.sd_debug_timeline.restype = None
-    lib.sd_debug_timeline.argtypes = [ctypes.c_void_p]
+    lib.sd_device_fault_clear.restype = ctypes.c_int
+    lib.sd_device_fault_clear.argtypes = []
     lib.sd_panel_kind.restype = ctypes.c_int
     lib.sd_panel_kind.argtypes = [sp, ctypes.c_int, ctypes.c_char_p]
     lib.sd_status_string.restype = ctypes.c_char_p
     lib.sd_status_string.argtypes = [ctypes.c_int]
-    lib.sd_profile_step.restype = ctypes.c_int
-    lib.sd_profile_step.argtypes = [ctypes.POINTER(ForwardArgs), ctypes.POINTER(BackwardArgs),
-                                    ctypes.c_void_p, ctypes.POINTER(ctypes.c_float), ctypes.c_int,
-                                    ctypes.POINTER(ctypes.c_int)]
-    lib.sd_launch_name.restype = ctypes.c_char_p
-    lib.sd_launch_name.argtypes = [ctypes.c_int]
     lib.sd_version.restype = ctypes.c_int
     lib.sd_chunk_tokens.restype = ctypes.c_int
-    _lib = lib
     return lib
+
+
+def check_device_fault() -> None:
+    """Read the device fault word (this waits for the device) and raise if a bounded wait inside a
+    kernel ran out: the results of that launch are undefined.  The word is cleared on the way out."""
+    lib = load()
+    word = lib.sd_device_fault()
+    if word != 0:
+        lib.sd_device_fault_clear()
+        raise RuntimeError(f"solvedelta_b200: device fault word {word} (a bounded wait inside a kernel ran out; "
+                           "the results of that launch are undefined)")
 
 
 def check(status: int) -> None:

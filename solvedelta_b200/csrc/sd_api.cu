@@ -5,6 +5,7 @@
 #include <cstring>
 
 #include "../../include/solvedelta_b200.h"
+#include "sd_diagnostics.h"
 #include "sd_backward.cuh"
 #include "sd_common.cuh"
 #include "sd_decode.cuh"
@@ -107,10 +108,13 @@ Operand make_operand(const sd_operand& o, int elem_bytes) {
     return r;
 }
 
-long long* g_dbg = nullptr;  // set by sd_debug_timeline (diagnostic)
+#ifdef SD_DIAGNOSTICS
+long long* g_dbg = nullptr;  // set by sd_debug_timeline (profiling build only)
+#endif
 
-// Fault word of the tensor-memory scan: a bounded mbarrier wait that ran out stores 1 (first
-// contraction) or 2 (second) here; sd_device_fault reads it back.
+// Fault word of the tensor-memory scan: a bounded mbarrier wait that ran out stores its code here
+// (1 / 2: first / second contraction, 3: Q landed, 4: R and P landed, 5: R / P slot released);
+// sd_device_fault reads it back, sd_device_fault_clear resets it.
 __device__ int g_scan_fault_word = 0;
 int* g_scan_fault_ptr[64] = {};
 // Tensor map of a [chunks][CL][DP] FP32 panel array for the scan's tiled load: dimensions (4 elements,
@@ -156,6 +160,36 @@ bool make_row_map(CUtensorMap* map, const float* panels, long long chunks, int c
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The three tensor maps of one tensor-memory scan launch.  Encoding a map is a driver call; a thread that
+// runs the same buffers again (a training loop on preallocated workspace, a replayed benchmark step) finds
+// them in a small per-thread cache keyed on the panel pointers and the chunk count.
+struct ScanMaps {
+    const void *q, *r, *p;
+    long long chunks;
+    CUtensorMap qmap, rmap, pmap;
+};
+bool scan_maps(const ScanParams& sp, long long chunks, const ScanMaps** out) {
+    constexpr int SLOTS = 4;
+    thread_local ScanMaps cache[SLOTS] = {};
+    thread_local int next = 0;
+    for (int i = 0; i < SLOTS; ++i)
+        if (cache[i].q == sp.Q && cache[i].r == sp.R && cache[i].p == sp.P && cache[i].chunks == chunks &&
+            chunks != 0) {
+            *out = &cache[i];
+            return true;
+        }
+    ScanMaps& m = cache[next];
+    next = (next + 1) % SLOTS;
+    m.q = nullptr;
+    m.chunks = 0;
+    if (!make_panel_map(&m.qmap, sp.Q, chunks) || !make_row_map(&m.rmap, sp.R, chunks, DP) ||
+        !make_row_map(&m.pmap, sp.P, chunks, SCAN_NS))
+        return false;
+    m.q = sp.Q; m.r = sp.R; m.p = sp.P; m.chunks = chunks;
+    *out = &m;
+    return true;
+}
+
 int* scan_fault_ptr() {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
@@ -177,15 +211,31 @@ Geometry make_geometry(const sd_shape& s) {
     g.NC = (s.T + CL - 1) / CL;
     g.valid = nullptr;
     g.reset = nullptr;
+#ifdef SD_DIAGNOSTICS
     g.dbg = nullptr;
     g.dbg_block = 0;
+#endif
     return g;
 }
 
+#ifdef SD_DIAGNOSTICS
 // slot k of the diagnostic buffer belongs to the k-th launch of a step
 void set_dbg(Geometry& g, int launch_index, int chunks) {
     g.dbg = g_dbg ? g_dbg + 16 * launch_index : nullptr;
     g.dbg_block = chunks > 300 ? chunks / 2 + 3 : 0;
+}
+long long* scan_dbg(int launch_index) { return g_dbg ? g_dbg + 16 * launch_index : nullptr; }
+#else
+inline void set_dbg(Geometry&, int, int) {}
+inline long long* scan_dbg(int) { return nullptr; }
+#endif
+
+bool launch_scan_tc(const ScanParams& sp, long long chunks, dim3 grid, cudaStream_t stream, long long* dbg) {
+    const ScanMaps* m = nullptr;
+    if (!scan_maps(sp, chunks, &m)) return false;
+    k_state_scan_tc<<<grid, TC_THREADS, SCAN_TC_SMEM_BYTES, stream>>>(sp, m->qmap, m->rmap, m->pmap, scan_fault_ptr(),
+                                                                      dbg);
+    return true;
 }
 
 template <class K>
@@ -228,7 +278,8 @@ cudaError_t configure_kernels() {
     return cudaSuccess;
 }
 
-// Diagnostic launch recorder used by sd_profile_step only (not thread safe).
+#ifdef SD_DIAGNOSTICS
+// Launch recorder used by sd_profile_step only (profiling build; not thread safe).
 struct LaunchRecorder {
     cudaEvent_t ev[40];
     int n;
@@ -237,11 +288,16 @@ LaunchRecorder* g_rec = nullptr;
 inline void mark(cudaStream_t stream) {
     if (g_rec != nullptr && g_rec->n < 40) cudaEventRecord(g_rec->ev[g_rec->n++], stream);
 }
+#else
+inline void mark(cudaStream_t) {}
+#endif
 
+#ifdef SD_DIAGNOSTICS
 const char* const kLaunchNames[] = {
     "k_prep_fwd",          "k_state_scan[C]",     "k_primal_fwd",         "k_exterior_prep_fwd", "k_state_scan[S]",
     "k_output_fwd",        "k_exterior_prep_bwd", "k_state_scan_b[dS]",   "k_exterior_pair_bwd",
     "k_primal_bwd",        "k_state_scan_b[dC]",  "k_predictor_close_bwd"};
+#endif
 
 int launch_status() { return cudaGetLastError() == cudaSuccess ? SD_OK : SD_ERR_LAUNCH_FAILED; }
 
@@ -356,7 +412,7 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
 
     const int chunks = (int)total_chunks(s);
     const int streams = s->B * s->H;
-    const dim3 scan_grid(DP / SCAN_NS, streams);
+    const dim3 scan_grid((DP / SCAN_NS) * streams);
     const Operand fwd_ops[] = {p.u, p.h, p.q, p.k, p.v, p.er, p.wr, p.ld};
     const bool fast = all_fast(fwd_ops, 8, *s);
 
@@ -371,13 +427,8 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
         sp.ckb = bpanel_at(kSaved, s, a->saved, "CtCkB");
         sp.init = a->C0; sp.fin = a->C_T;
         sp.NC = p.g.NC; sp.reverse = 0; sp.transposed_io = 1; sp.nrows = s->r; sp.ncols = s->r;
-        CUtensorMap qmap, rmap, pmap;
-        if (!make_panel_map(&qmap, sp.Q, total_chunks(s)) || !make_row_map(&rmap, sp.R, total_chunks(s), DP) ||
-            !make_row_map(&pmap, sp.P, total_chunks(s), SCAN_NS))
-            return SD_ERR_LAUNCH_FAILED;
-        k_state_scan_tc<<<scan_grid, TC_THREADS, SCAN_TC_SMEM_BYTES, stream>>>(sp, qmap, rmap, pmap, scan_fault_ptr(),
-                                                                               g_dbg ? g_dbg + 16 * 1 : nullptr);
-    mark(stream);
+        if (!launch_scan_tc(sp, total_chunks(s), scan_grid, stream, scan_dbg(1))) return SD_ERR_LAUNCH_FAILED;
+        mark(stream);
     }
     set_dbg(p.g, 2, chunks);
     if (fast) k_primal_fwd<true><<<chunks, NTHREADS, PRIMAL_FWD_SMEM, stream>>>(p);
@@ -393,13 +444,8 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
         sp.lam = p.Lam; sp.X = nullptr; sp.ck = nullptr; sp.Xb = p.Zt; sp.ckb = p.SCk;
         sp.init = a->S0; sp.fin = a->S_T;
         sp.NC = p.g.NC; sp.reverse = 0; sp.transposed_io = 0; sp.nrows = s->r; sp.ncols = s->V;
-        CUtensorMap qmap, rmap, pmap;
-        if (!make_panel_map(&qmap, sp.Q, total_chunks(s)) || !make_row_map(&rmap, sp.R, total_chunks(s), DP) ||
-            !make_row_map(&pmap, sp.P, total_chunks(s), SCAN_NS))
-            return SD_ERR_LAUNCH_FAILED;
-        k_state_scan_tc<<<scan_grid, TC_THREADS, SCAN_TC_SMEM_BYTES, stream>>>(sp, qmap, rmap, pmap, scan_fault_ptr(),
-                                                                               g_dbg ? g_dbg + 16 * 4 : nullptr);
-    mark(stream);
+        if (!launch_scan_tc(sp, total_chunks(s), scan_grid, stream, scan_dbg(4))) return SD_ERR_LAUNCH_FAILED;
+        mark(stream);
     }
     set_dbg(p.g, 5, chunks);
     if (fast) k_output_fwd<true><<<chunks, NTHREADS, OUTPUT_FWD_SMEM, stream>>>(p);
@@ -465,7 +511,7 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
 
     const int chunks = (int)total_chunks(s);
     const int streams = s->B * s->H;
-    const dim3 scan_grid(DP / SCAN_NS, streams);
+    const dim3 scan_grid((DP / SCAN_NS) * streams);
     const Operand bwd_ops[] = {p.u, p.h, p.q, p.k, p.v, p.er, p.wr, p.ld, p.dy};
     const bool fast = all_fast(bwd_ops, 9, *s);
 
@@ -506,7 +552,10 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
     return launch_status();
 }
 
+#ifdef SD_DIAGNOSTICS
 void sd_debug_timeline(void* device_buffer) { g_dbg = reinterpret_cast<long long*>(device_buffer); }
+
+#endif
 
 int sd_device_fault(void) {
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
@@ -515,6 +564,13 @@ int sd_device_fault(void) {
     return word;
 }
 
+int sd_device_fault_clear(void) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    const int zero = 0;
+    return cudaMemcpyToSymbol(g_scan_fault_word, &zero, sizeof(int)) == cudaSuccess ? 0 : -1;
+}
+
+#ifdef SD_DIAGNOSTICS
 const char* sd_launch_name(int index) {
     const int n = (int)(sizeof(kLaunchNames) / sizeof(kLaunchNames[0]));
     return (index >= 0 && index < n) ? kLaunchNames[index] : "";
@@ -545,6 +601,8 @@ int sd_profile_step(const sd_forward_args* fwd, const sd_backward_args* bwd, voi
     if (e != cudaSuccess) return SD_ERR_LAUNCH_FAILED;
     return status;
 }
+
+#endif  // SD_DIAGNOSTICS
 
 // ---------------------------------------------------------------------------
 // Forward pass on library-owned scratch, for hosts that must not allocate.

@@ -990,7 +990,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
         };
         diag_sweep<true, true, true, true>(
             al, [&](int i, int i0, float (&row)[BT]) { prow16_bf16(b_dN, LDM, i, i0, row); }, fu, fu,
-            add_to(b_dl), add_to(b_tj), ch.rm);
+            add_to(b_dl), add_to(b_tj), ch.reset_rows());
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
@@ -1046,12 +1046,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
         float xs = 0.f;
         for (int i = 0; i < CL; ++i) xs += s_X[i * LDP + c];
         float run = __expf(gG[(CL - 1) * DP + c]) * (p.SdS[ch.gi * DP + c] + s_cdc[c]) + xs;
+        // a masked token has no gradient; nor does the decay of a reset token, which multiplies the zero state
+        const unsigned long long keep = ch.valid_rows() & ~ch.reset_rows();
         for (int i = CL - 1; i >= 0; --i) {
             run += s_dG[i * LDP + c];
-            // a masked token has no gradient; nor does the decay of a reset token, which multiplies the zero state
             if (i < ch.nvalid)
                 p.dld[(((long long)ch.b * p.g.T + ch.t0 + i) * p.g.H + ch.hh) * (long long)r + c] =
-                    (ch.ok(i) && !ch.rst(i)) ? run - s_dE[i * LDP + c] : 0.f;
+                    ((keep >> i) & 1ull) ? run - s_dE[i * LDP + c] : 0.f;
         }
     }
     SD_PHASE(p.g, ph);

@@ -46,11 +46,15 @@ struct Geometry {
     int B, T, H, r, V, NC;  // NC = chunks per stream
     const unsigned char* valid;  // [B][T] bytes, 0 = token takes no part (null: every token is valid)
     const unsigned char* reset;  // [B][T] bytes, 1 = token starts from the zero state (null: none)
-    long long* dbg;         // diagnostic phase clock stamps of one CTA (null = off)
+#ifdef SD_DIAGNOSTICS
+    long long* dbg;         // phase clock stamps of one CTA (null = off); profiling build only
     int dbg_block;
+#endif
 };
 
-// Diagnostic: thread 0 of one chosen CTA records the SM clock at a phase boundary.
+// Profiling build (-DSD_DIAGNOSTICS): thread 0 of one chosen CTA records the SM clock at a phase
+// boundary.  The shipped build compiles the stamps out.
+#ifdef SD_DIAGNOSTICS
 #define SD_PHASE(g, ph)                                                                   \
     do {                                                                                  \
         if ((g).dbg != nullptr && (int)blockIdx.x == (g).dbg_block && threadIdx.x == 0 && \
@@ -58,12 +62,17 @@ struct Geometry {
             (g).dbg[(ph)] = clock64();                                                    \
         ++(ph);                                                                           \
     } while (0)
+#else
+#define SD_PHASE(g, ph) do { (void)(ph); } while (0)
+#endif
 
 struct Chunk {
     int s, c, b, hh, t0, nvalid;
     long long gi;  // global chunk index s * NC + c
     unsigned long long vm;  // bit i: token row i exists and is valid
     unsigned long long rm;  // bit i: token row i is a (valid) reset token
+    __device__ __forceinline__ unsigned long long valid_rows() const { return vm; }
+    __device__ __forceinline__ unsigned long long reset_rows() const { return rm; }
     __device__ __forceinline__ bool ok(int i) const { return (vm >> i) & 1ull; }
     __device__ __forceinline__ bool rst(int i) const { return (rm >> i) & 1ull; }
     // what the exclusive prefix E_i = G_{i-1} of a reset row still lacks: the reset belongs to row i itself
@@ -84,7 +93,8 @@ __device__ __forceinline__ Chunk chunk_of(const Geometry& g, int idx) {
         ch.vm = ch.nvalid >= CL ? ~0ull : ((1ull << ch.nvalid) - 1ull);
         ch.rm = 0ull;
     } else {
-        // every warp reads the chunk's 64 mask bytes (all threads call chunk_of together)
+        // every warp reads the chunk's 64 mask bytes (all threads call chunk_of together); the ballots are
+        // warp-uniform values
         const int lane = threadIdx.x & 31;
         const unsigned char* vp = g.valid ? g.valid + (long long)ch.b * g.T + ch.t0 : nullptr;
         const unsigned char* rp = g.reset ? g.reset + (long long)ch.b * g.T + ch.t0 : nullptr;

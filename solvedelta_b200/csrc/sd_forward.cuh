@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
     load_f32_panel<FAST>(p.ld, ch, r, s_G);
     load_raw_panel<FAST>(p.h, ch, r, s_h);
     load_gamma(p.gam, ch, s_gam);
-    if (ch.rm != 0ull) {   // block-uniform: a reset token forgets RESET_NATS more (each thread patches what it loaded)
+    if (ch.reset_rows() != 0ull) {   // block-uniform: a reset token forgets RESET_NATS more (each thread patches what it loaded)
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
 #pragma unroll
         for (int pp = 0; pp < ROW_PASSES; ++pp) {

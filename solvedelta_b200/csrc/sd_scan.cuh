@@ -98,8 +98,8 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) k_state_scan_b(ScanParamsB p)
     bf16* sX = sX2 + 2 * CL * LDTB;                // [CL][LDTB]
     bf16* sSt = sX + CL * LDTB;                    // [DP][LDTB]
 
-    const int col0 = blockIdx.x * SCAN_NS;
-    const int s = blockIdx.y;
+    const int col0 = (blockIdx.x % (DP / SCAN_NS)) * SCAN_NS;   // grid.x = stream * (DP / NS) + column slice
+    const int s = blockIdx.x / (DP / SCAN_NS);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const bool has2 = p.R2 != nullptr;
     const long long base = (long long)s * p.NC;

@@ -197,12 +197,16 @@ __device__ __forceinline__ void tc_load_rp(unsigned char* sR_raw, unsigned char*
         : "memory");
 }
 
-// Diagnostic: thread 0 of CTA (0,0) records the SM clock at the phase boundaries of its ninth step.
+// Profiling build only: thread 0 of the first CTA records the SM clock at the phase boundaries of its ninth step.
+#ifdef SD_DIAGNOSTICS
 #define TC_STAMP(k)                                                                              \
     do {                                                                                         \
-        if (dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0 && step == 8)       \
+        if (dbg != nullptr && blockIdx.x == 0 && tid == 0 && step == 8)                          \
             dbg[k] = clock64();                                                                  \
     } while (0)
+#else
+#define TC_STAMP(k) do { } while (0)
+#endif
 
 __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, const __grid_constant__ CUtensorMap qmap,
                                                                   const __grid_constant__ CUtensorMap rmap,
@@ -218,8 +222,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, c
     __shared__ __align__(8) unsigned long long bars[6];   // two contractions, two Q slots, R/P landed, R/P taken
     __shared__ unsigned s_tmem;
 
-    const int col0 = blockIdx.x * SCAN_NS;
-    const int s = blockIdx.y;
+    // grid.x = stream * (DP / NS) + column slice (the x dimension has no 65535 limit)
+    const int col0 = (blockIdx.x % (DP / SCAN_NS)) * SCAN_NS;
+    const int s = blockIdx.x / (DP / SCAN_NS);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int quarter = warp & 3, part = warp >> 2;
     // This thread's tensor-memory lane: state row p for the state accumulator and for the R column

@@ -19,6 +19,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from . import _lib
 from .config import SolveDeltaConfig
 from .ops import SolveDeltaState
 from .model import SolveDelta, SolveDeltaLayerState
@@ -344,6 +345,7 @@ class SolveDeltaForCausalLM(nn.Module):
                 logits = decoder.step(nxt)
             else:
                 logits = self(input_ids=nxt, past_key_values=cache, use_cache=True, logits_to_keep=1).logits
+        _lib.check_device_fault()   # one synchronisation at the end of the loop: every bounded wait completed
         return torch.cat(tokens, dim=1)
 
 

@@ -20,6 +20,8 @@ import torch
 import torch.distributed as dist
 from torch import nn
 
+from . import _lib
+
 
 class _FixedDenseLinearCrossEntropy(torch.autograd.Function):
     """loss = sum over valid tokens of CE(x W^T + b, target) / total, evaluated in token
@@ -215,6 +217,8 @@ class SolveDeltaGraphedTrainingStep:
         self.distributed = distributed
         self.process_group = process_group
         self._sync = True
+        # opt-in: read the device fault word after every replay (costs a device synchronisation per step)
+        self.check_faults = False
         self._input_dtype, self._label_dtype = sample_input_ids.dtype, sample_labels.dtype
         self._ids = sample_input_ids.clone()
         self._labels = sample_labels.clone()
@@ -259,8 +263,9 @@ class SolveDeltaGraphedTrainingStep:
             raise ValueError("input_ids and labels must share one shape [B,T]")
         if input_ids.device.type != "cuda" or labels.device != input_ids.device:
             raise ValueError("input_ids and labels must live on one CUDA device")
-        if input_ids.dtype not in (torch.int32, torch.int64) or labels.dtype not in (torch.int32, torch.int64):
-            raise TypeError("input_ids and labels must be integer tensors")
+        # as upstream (causallsso/cuda_graph.py:279-280): the loss gathers and scatters with the labels
+        if input_ids.dtype != torch.long or labels.dtype != torch.long:
+            raise TypeError("input_ids and labels must be torch.long tensors")
 
     def __call__(self, input_ids: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
         self._validate_pair(input_ids, labels)
@@ -280,6 +285,8 @@ class SolveDeltaGraphedTrainingStep:
         self.graph.replay()
         if self.distributed and self._sync:
             allreduce_gradients(self.params, self.process_group)
+        if self.check_faults:
+            _lib.check_device_fault()   # waits for the device: a bounded wait inside a kernel that ran out raises here
         return self.loss
 
     step = __call__

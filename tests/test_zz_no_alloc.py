@@ -4,7 +4,9 @@ Some callers of this library cannot hand it workspace buffers, because they
 are not allowed to call cudaMalloc where the operator runs (all device memory
 belongs to their own arena, or a stream capture is in progress).  For them the
 library keeps a fixed 32 MiB device array of its own.  This test calls that
-entry point through the C ABI twice in a row, on different inputs and shapes,
+entry point through the C ABI several times in a row, on different inputs and
+shapes (a narrow, ragged shape comes after a wide one, so that whatever the
+wide call left in the shared array lies under the narrow call's panels),
 and checks each result against sd_forward with caller-provided buffers.  The
 two paths run the same kernels on the same data, so the results must be equal
 bit for bit, which is well inside the tolerances of the parity tests.
@@ -51,7 +53,8 @@ def _forward_static(dev):
 
 
 def test_static_workspace_forward_matches_caller_buffers_twice_in_a_row():
-    for seed, (B, T, H, r, V) in ((41, (1, 150, 2, 32, 32)), (43, (1, 300, 1, 128, 128))):
+    for seed, (B, T, H, r, V) in ((41, (1, 150, 2, 32, 32)), (43, (1, 300, 1, 128, 128)), (47, (2, 70, 1, 16, 24)),
+                                  (41, (1, 150, 2, 32, 32))):
         _, dev = make_inputs(B, T, H, r, V, seed=seed)
         status, y, C_T, S_T = _forward_static(dev)
         assert status == 0, _lib.load().sd_status_string(status)
