@@ -54,6 +54,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     """Compile csrc/*.cu into the in-tree shared libraries (sm_100a only): the product library and
     its profiling twin."""
     nvcc = _nvcc()
+    jobs = []
     for path, extra in ((LIB_PATH, []), (DIAG_LIB_PATH, ["-DSD_DIAGNOSTICS"])):
         if not force and not is_stale(path):
             continue
@@ -65,7 +66,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
-        subprocess.check_call(cmd)
+        jobs.append((cmd, subprocess.Popen(cmd)))   # the two builds run side by side
+    for cmd, proc in jobs:
+        if proc.wait() != 0:
+            raise subprocess.CalledProcessError(proc.returncode, cmd)
     return LIB_PATH
 
 

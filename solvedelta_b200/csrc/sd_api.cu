@@ -251,14 +251,22 @@ cudaError_t configure_kernels() {
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64 && done[dev]) return cudaSuccess;
-    if ((e = allow_smem(k_prep_fwd<true>, PREP_FWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_prep_fwd<false>, PREP_FWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_primal_fwd<true>, PRIMAL_FWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_primal_fwd<false>, PRIMAL_FWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_exterior_prep_fwd<true>, EXT_PREP_FWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_exterior_prep_fwd<false>, EXT_PREP_FWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_output_fwd<true>, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_output_fwd<false>, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_prep_fwd<true, false>, PREP_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_prep_fwd<false, false>, PREP_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_prep_fwd<true, true>, PREP_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_prep_fwd<false, true>, PREP_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_primal_fwd<true, false>, PRIMAL_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_primal_fwd<false, false>, PRIMAL_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_primal_fwd<true, true>, PRIMAL_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_primal_fwd<false, true>, PRIMAL_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_prep_fwd<true, false>, EXT_PREP_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_prep_fwd<false, false>, EXT_PREP_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_prep_fwd<true, true>, EXT_PREP_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_prep_fwd<false, true>, EXT_PREP_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_output_fwd<true, false>, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_output_fwd<false, false>, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_output_fwd<true, true>, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_output_fwd<false, true>, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_state_scan_tc, SCAN_TC_SMEM_BYTES)) != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) {
         void* w = nullptr;
@@ -266,14 +274,22 @@ cudaError_t configure_kernels() {
         g_scan_fault_ptr[dev] = static_cast<int*>(w);
     }
     if ((e = allow_smem(k_state_scan_b, SCAN_B_SMEM_BYTES)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_exterior_prep_bwd<true>, EXT_PREP_BWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_exterior_prep_bwd<false>, EXT_PREP_BWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_exterior_pair_bwd<true>, EXT_PAIR_BWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_exterior_pair_bwd<false>, EXT_PAIR_BWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_primal_bwd<true>, PRIMAL_BWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_primal_bwd<false>, PRIMAL_BWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_predictor_close_bwd<true>, PRED_CLOSE_BWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_predictor_close_bwd<false>, PRED_CLOSE_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_prep_bwd<true, false>, EXT_PREP_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_prep_bwd<false, false>, EXT_PREP_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_prep_bwd<true, true>, EXT_PREP_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_prep_bwd<false, true>, EXT_PREP_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_pair_bwd<true, false>, EXT_PAIR_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_pair_bwd<false, false>, EXT_PAIR_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_pair_bwd<true, true>, EXT_PAIR_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_exterior_pair_bwd<false, true>, EXT_PAIR_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_primal_bwd<true, false>, PRIMAL_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_primal_bwd<false, false>, PRIMAL_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_primal_bwd<true, true>, PRIMAL_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_primal_bwd<false, true>, PRIMAL_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_predictor_close_bwd<true, false>, PRED_CLOSE_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_predictor_close_bwd<false, false>, PRED_CLOSE_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_predictor_close_bwd<true, true>, PRED_CLOSE_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_predictor_close_bwd<false, true>, PRED_CLOSE_BWD_SMEM)) != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) done[dev] = true;
     return cudaSuccess;
 }
@@ -300,6 +316,15 @@ const char* const kLaunchNames[] = {
 #endif
 
 int launch_status() { return cudaGetLastError() == cudaSuccess ? SD_OK : SD_ERR_LAUNCH_FAILED; }
+
+// One chunk kernel, instantiated for (vector-aligned operands?, token masks present?).
+#define SD_LAUNCH_CHUNK(kernel, smem)                                                          \
+    do {                                                                                       \
+        if (fast && !masked) kernel<true, false><<<chunks, NTHREADS, smem, stream>>>(p);       \
+        else if (fast) kernel<true, true><<<chunks, NTHREADS, smem, stream>>>(p);              \
+        else if (!masked) kernel<false, false><<<chunks, NTHREADS, smem, stream>>>(p);         \
+        else kernel<false, true><<<chunks, NTHREADS, smem, stream>>>(p);                       \
+    } while (0)
 
 bool operands_ok(const sd_operand* ops, int n) {
     for (int i = 0; i < n; ++i)
@@ -415,10 +440,10 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
     const dim3 scan_grid((DP / SCAN_NS) * streams);
     const Operand fwd_ops[] = {p.u, p.h, p.q, p.k, p.v, p.er, p.wr, p.ld};
     const bool fast = all_fast(fwd_ops, 8, *s);
+    const bool masked = a->valid_mask != nullptr || a->reset_mask != nullptr;
 
     set_dbg(p.g, 0, chunks);
-    if (fast) k_prep_fwd<true><<<chunks, NTHREADS, PREP_FWD_SMEM, stream>>>(p);
-    else k_prep_fwd<false><<<chunks, NTHREADS, PREP_FWD_SMEM, stream>>>(p);
+    SD_LAUNCH_CHUNK(k_prep_fwd, PREP_FWD_SMEM);
     mark(stream);
     {
         ScanParams sp{};
@@ -431,12 +456,10 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
         mark(stream);
     }
     set_dbg(p.g, 2, chunks);
-    if (fast) k_primal_fwd<true><<<chunks, NTHREADS, PRIMAL_FWD_SMEM, stream>>>(p);
-    else k_primal_fwd<false><<<chunks, NTHREADS, PRIMAL_FWD_SMEM, stream>>>(p);
+    SD_LAUNCH_CHUNK(k_primal_fwd, PRIMAL_FWD_SMEM);
     mark(stream);
     set_dbg(p.g, 3, chunks);
-    if (fast) k_exterior_prep_fwd<true><<<chunks, NTHREADS, EXT_PREP_FWD_SMEM, stream>>>(p);
-    else k_exterior_prep_fwd<false><<<chunks, NTHREADS, EXT_PREP_FWD_SMEM, stream>>>(p);
+    SD_LAUNCH_CHUNK(k_exterior_prep_fwd, EXT_PREP_FWD_SMEM);
     mark(stream);
     {
         ScanParams sp{};
@@ -448,8 +471,7 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
         mark(stream);
     }
     set_dbg(p.g, 5, chunks);
-    if (fast) k_output_fwd<true><<<chunks, NTHREADS, OUTPUT_FWD_SMEM, stream>>>(p);
-    else k_output_fwd<false><<<chunks, NTHREADS, OUTPUT_FWD_SMEM, stream>>>(p);
+    SD_LAUNCH_CHUNK(k_output_fwd, OUTPUT_FWD_SMEM);
     mark(stream);
     return launch_status();
 }
@@ -514,10 +536,10 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
     const dim3 scan_grid((DP / SCAN_NS) * streams);
     const Operand bwd_ops[] = {p.u, p.h, p.q, p.k, p.v, p.er, p.wr, p.ld, p.dy};
     const bool fast = all_fast(bwd_ops, 9, *s);
+    const bool masked = a->valid_mask != nullptr || a->reset_mask != nullptr;
 
     set_dbg(p.g, 6, chunks);
-    if (fast) k_exterior_prep_bwd<true><<<chunks, NTHREADS, EXT_PREP_BWD_SMEM, stream>>>(p);
-    else k_exterior_prep_bwd<false><<<chunks, NTHREADS, EXT_PREP_BWD_SMEM, stream>>>(p);
+    SD_LAUNCH_CHUNK(k_exterior_prep_bwd, EXT_PREP_BWD_SMEM);
     mark(stream);
     {
         ScanParamsB sp{};
@@ -529,12 +551,10 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
     mark(stream);
     }
     set_dbg(p.g, 8, chunks);
-    if (fast) k_exterior_pair_bwd<true><<<chunks, NTHREADS, EXT_PAIR_BWD_SMEM, stream>>>(p);
-    else k_exterior_pair_bwd<false><<<chunks, NTHREADS, EXT_PAIR_BWD_SMEM, stream>>>(p);
+    SD_LAUNCH_CHUNK(k_exterior_pair_bwd, EXT_PAIR_BWD_SMEM);
     mark(stream);
     set_dbg(p.g, 9, chunks);
-    if (fast) k_primal_bwd<true><<<chunks, NTHREADS, PRIMAL_BWD_SMEM, stream>>>(p);
-    else k_primal_bwd<false><<<chunks, NTHREADS, PRIMAL_BWD_SMEM, stream>>>(p);
+    SD_LAUNCH_CHUNK(k_primal_bwd, PRIMAL_BWD_SMEM);
     mark(stream);
     {
         ScanParamsB sp{};
@@ -546,8 +566,7 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
     mark(stream);
     }
     set_dbg(p.g, 11, chunks);
-    if (fast) k_predictor_close_bwd<true><<<chunks, NTHREADS, PRED_CLOSE_BWD_SMEM, stream>>>(p);
-    else k_predictor_close_bwd<false><<<chunks, NTHREADS, PRED_CLOSE_BWD_SMEM, stream>>>(p);
+    SD_LAUNCH_CHUNK(k_predictor_close_bwd, PRED_CLOSE_BWD_SMEM);
     mark(stream);
     return launch_status();
 }

@@ -94,7 +94,7 @@ __device__ __forceinline__ void epi_store_bsm(float (&acc)[NTW][4], int r0, int 
 // next kernel contracts with, and chi / -e themselves for its diagonal blocks.
 constexpr size_t EXT_PREP_BWD_SMEM = 2 * BSLOT_BYTES + BMAT_BYTES + MAT_BYTES;
 
-template <bool FAST>
+template <bool FAST, bool MASKED>
 __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
@@ -103,7 +103,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) 
     bf16* b_dt = b_dy + BSLOT_ELEMS;
     bf16* b_aqd = b_dt + BSLOT_ELEMS;
     float* f_aedT = reinterpret_cast<float*>(b_aqd + BMAT_ELEMS);
-    const Chunk ch = chunk_of(p.g, blockIdx.x);
+    const ChunkT<MASKED> ch = chunk_of<MASKED>(p.g, blockIdx.x);
     const int r = p.g.r, V = p.g.V;
     const float* gG = panel_ptr(p.Gp, ch.gi);
     const float* gd = panel_ptr(p.Dprim, ch.gi);
@@ -198,8 +198,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) 
 // partial cotangents the predictor reverse still has to complete.
 // d chi, -d e, the decay part of d d (all final), dDt and dR are read from the
 // shared BF16 panels the contractions of the same CTA just produced.
-template <bool FAST>
-__device__ __forceinline__ void sources_bwd_rows(const BwdParams& p, const Chunk& ch, const bf16* sA1,
+template <bool FAST, class CH>
+__device__ __forceinline__ void sources_bwd_rows(const BwdParams& p, const CH& ch, const bf16* sA1,
                                                  const bf16* sA2, const bf16* sPY, const bf16* sdDt,
                                                  const bf16* sdR) {
     const int r = p.g.r, V = p.g.V;
@@ -321,7 +321,7 @@ __device__ __forceinline__ void epi_scale_store_bsm(float (&acc)[NTW][4], int r0
     });
 }
 
-template <bool FAST>
+template <bool FAST, bool MASKED>
 __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
@@ -338,7 +338,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
     bf16* b_daed = b_daqd + BMAT_ELEMS;
     float* s_beta = reinterpret_cast<float*>(b_daed + BMAT_ELEMS);
     int* s_fastw = reinterpret_cast<int*>(s_beta + NBLK * DP);
-    const Chunk ch = chunk_of(p.g, blockIdx.x);
+    const ChunkT<MASKED> ch = chunk_of<MASKED>(p.g, blockIdx.x);
     const float* gG = panel_ptr(p.Gp, ch.gi);
     auto fG = [&](int i, int c) { return gG[i * DP + c]; };
 
@@ -507,7 +507,7 @@ constexpr size_t PRIMAL_BWD_SMEM = 7 * BSLOT_BYTES + BSTATE_BYTES + 2 * BMAT_BYT
                                    (3 * CL + 4 * CL + NBLK * DP + 16) * sizeof(float) +
                                    (3 + NBLK) * DP * sizeof(bf16);
 
-template <bool FAST>
+template <bool FAST, bool MASKED>
 __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
@@ -533,7 +533,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     int* s_fastw = reinterpret_cast<int*>(s_beta + NBLK * DP);
     bf16* s_Mb = reinterpret_cast<bf16*>(s_fastw + 16);
     bf16* s_ibeta_b = s_Mb + 3 * DP;
-    const Chunk ch = chunk_of(p.g, blockIdx.x);
+    const ChunkT<MASKED> ch = chunk_of<MASKED>(p.g, blockIdx.x);
     const int r = p.g.r;
     const float* gG = panel_ptr(p.Gp, ch.gi);
     const bf16* gDd = bpanel_ptr(p.Dd, ch.gi);
@@ -773,7 +773,7 @@ constexpr size_t PRED_CLOSE_BWD_SMEM = 5 * BSLOT_BYTES + 2 * BMAT_BYTES + 3 * si
                                        6 * DP * sizeof(bf16);
 static_assert(3 * size_t(CL) * LDP * 4 >= 2 * BSTATE_BYTES, "closure panels overlay both BF16 states");
 
-template <bool FAST>
+template <bool FAST, bool MASKED>
 __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
@@ -799,7 +799,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
     int* s_fastw = reinterpret_cast<int*>(s_beta + NBLK * DP);
     bf16* s_Mb = reinterpret_cast<bf16*>(s_fastw + 16);
     bf16* s_pref = s_Mb + 3 * DP;   // exp(Gprev_I) for I = 1..3: U~ = (u^ rowE) .* pref along channels
-    const Chunk ch = chunk_of(p.g, blockIdx.x);
+    const ChunkT<MASKED> ch = chunk_of<MASKED>(p.g, blockIdx.x);
     const int r = p.g.r;
     const float* gG = panel_ptr(p.Gp, ch.gi);
     auto fG = [&](int i, int c) { return gG[i * DP + c]; };
@@ -1041,18 +1041,34 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
-    if (threadIdx.x < DP && threadIdx.x < r) {
-        const int c = threadIdx.x;
-        float xs = 0.f;
-        for (int i = 0; i < CL; ++i) xs += s_X[i * LDP + c];
-        float run = __expf(gG[(CL - 1) * DP + c]) * (p.SdS[ch.gi * DP + c] + s_cdc[c]) + xs;
-        // a masked token has no gradient; nor does the decay of a reset token, which multiplies the zero state
-        const unsigned long long keep = ch.valid_rows() & ~ch.reset_rows();
-        for (int i = CL - 1; i >= 0; --i) {
-            run += s_dG[i * LDP + c];
-            if (i < ch.nvalid)
-                p.dld[(((long long)ch.b * p.g.T + ch.t0 + i) * p.g.H + ch.hh) * (long long)r + c] =
-                    ((keep >> i) & 1ull) ? run - s_dE[i * LDP + c] : 0.f;
+    {
+        // d log_decay[i] = (suffix sum of dG from row i) + end-of-chunk terms - dE[i], per channel.  Four
+        // threads per channel, 16 rows each: segment totals first, then the short suffix walk.
+        float* s_tot = reinterpret_cast<float*>(b_N);          // [4][DP] totals of dG, then [4][DP] totals of X
+        static_assert(2 * BMAT_BYTES >= 8 * DP * sizeof(float), "segment totals overlay the two pair matrices");
+        const int c = threadIdx.x & (DP - 1), seg = threadIdx.x >> 7, i0 = seg * 16;
+        float tg = 0.f, tx = 0.f;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            tg += s_dG[(i0 + k) * LDP + c];
+            tx += s_X[(i0 + k) * LDP + c];
+        }
+        s_tot[seg * DP + c] = tg;
+        s_tot[(4 + seg) * DP + c] = tx;
+        __syncthreads();
+        if (c < r) {
+            float run = __expf(gG[(CL - 1) * DP + c]) * (p.SdS[ch.gi * DP + c] + s_cdc[c]) +
+                        ((s_tot[4 * DP + c] + s_tot[5 * DP + c]) + (s_tot[6 * DP + c] + s_tot[7 * DP + c]));
+            for (int s2 = seg + 1; s2 < 4; ++s2) run += s_tot[s2 * DP + c];
+            // a masked token has no gradient; nor does the decay of a reset token, which multiplies the zero state
+            const unsigned keep = (unsigned)((ch.valid_rows() & ~ch.reset_rows()) >> i0) & 0xffffu;
+            float* out = p.dld + (((long long)ch.b * p.g.T + ch.t0 + i0) * p.g.H + ch.hh) * (long long)r + c;
+            const long long row_stride = (long long)p.g.H * r;
+#pragma unroll
+            for (int k = 15; k >= 0; --k) {
+                run += s_dG[(i0 + k) * LDP + c];
+                if (i0 + k < ch.nvalid) out[k * row_stride] = ((keep >> k) & 1u) ? run - s_dE[(i0 + k) * LDP + c] : 0.f;
+            }
         }
     }
     SD_PHASE(p.g, ph);

@@ -185,7 +185,6 @@ constexpr size_t BSTATE_BYTES = size_t(DP) * LDB * 2;  // a whole state in BF16
 // inverse is added from the FP32 registers, so only the correction (T_II^-1 - I) r
 // sees TF32 operand rounding.
 struct PanelF32 {
-    static constexpr bool kFullPrecision = true;   // FP32 right-hand sides: the diagonal blocks are applied in split TF32
     float* p0;
     float* p1;
     __device__ __forceinline__ float get(int k, int n) const {
@@ -199,7 +198,6 @@ struct PanelF32 {
     }
 };
 struct PanelBF16 {
-    static constexpr bool kFullPrecision = false;
     bf16* p0;
     bf16* p1;
     __device__ __forceinline__ float get(int k, int n) const {
@@ -314,30 +312,20 @@ __device__ __forceinline__ void trisolve_blocked(float* Mr, float sgn, Panel P) 
             __syncwarp();
         }
         {
-            // X[I] = r + (D_I) r : the block's own rows, K = 16.  FP32 panels take the product in split TF32
-            // (hi*hi + hi*lo + lo*hi), which keeps the diagonal blocks at FP32 grade like a substitution would.
+            // X[I] = r + D_I r : the block's own rows, K = 16 (the identity part stays in FP32 registers)
             float acc[2][4];
             acc_zero<2>(acc);
 #pragma unroll
             for (int kk = 0; kk < 16; kk += 8) {
-                const float af[4] = {Mr[(r0 + g) * LDA + r0 + kk + t], Mr[(r0 + g + 8) * LDA + r0 + kk + t],
-                                     Mr[(r0 + g) * LDA + r0 + kk + t + 4], Mr[(r0 + g + 8) * LDA + r0 + kk + t + 4]};
-                uint32_t ah[4], al[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    ah[e] = f2tf32(af[e]);
-                    if (Panel::kFullPrecision) al[e] = f2tf32(af[e] - __uint_as_float(ah[e]));
-                }
+                const uint32_t a0 = f2tf32(Mr[(r0 + g) * LDA + r0 + kk + t]);
+                const uint32_t a1 = f2tf32(Mr[(r0 + g + 8) * LDA + r0 + kk + t]);
+                const uint32_t a2 = f2tf32(Mr[(r0 + g) * LDA + r0 + kk + t + 4]);
+                const uint32_t a3 = f2tf32(Mr[(r0 + g + 8) * LDA + r0 + kk + t + 4]);
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) {
-                    const float b0 = P.get(r0 + kk + t, n0 + nt * 8 + g), b1 = P.get(r0 + kk + t + 4, n0 + nt * 8 + g);
-                    const uint32_t bh0 = f2tf32(b0), bh1 = f2tf32(b1);
-                    if (Panel::kFullPrecision) {
-                        const uint32_t bl0 = f2tf32(b0 - __uint_as_float(bh0)), bl1 = f2tf32(b1 - __uint_as_float(bh1));
-                        mma_tf32(acc[nt], al[0], al[1], al[2], al[3], bh0, bh1);
-                        mma_tf32(acc[nt], ah[0], ah[1], ah[2], ah[3], bl0, bl1);
-                    }
-                    mma_tf32(acc[nt], ah[0], ah[1], ah[2], ah[3], bh0, bh1);
+                    const uint32_t b0 = f2tf32(P.get(r0 + kk + t, n0 + nt * 8 + g));
+                    const uint32_t b1 = f2tf32(P.get(r0 + kk + t + 4, n0 + nt * 8 + g));
+                    mma_tf32(acc[nt], a0, a1, a2, a3, b0, b1);
                 }
             }
 #pragma unroll

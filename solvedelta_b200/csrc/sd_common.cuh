@@ -66,21 +66,28 @@ struct Geometry {
 #define SD_PHASE(g, ph) do { (void)(ph); } while (0)
 #endif
 
-struct Chunk {
+// The chunk a CTA works on.  MASKED selects, at compile time, whether token masks exist at all: the
+// unmasked instantiation of every kernel tests `i < nvalid` and carries no mask words.
+template <bool MASKED>
+struct ChunkT {
     int s, c, b, hh, t0, nvalid;
     long long gi;  // global chunk index s * NC + c
-    unsigned long long vm;  // bit i: token row i exists and is valid
-    unsigned long long rm;  // bit i: token row i is a (valid) reset token
-    __device__ __forceinline__ unsigned long long valid_rows() const { return vm; }
-    __device__ __forceinline__ unsigned long long reset_rows() const { return rm; }
-    __device__ __forceinline__ bool ok(int i) const { return (vm >> i) & 1ull; }
-    __device__ __forceinline__ bool rst(int i) const { return (rm >> i) & 1ull; }
+    unsigned long long vm;  // MASKED: bit i = token row i exists and is valid
+    unsigned long long rm;  // MASKED: bit i = token row i is a (valid) reset token
+    __device__ __forceinline__ unsigned long long valid_rows() const {
+        return MASKED ? vm : (nvalid >= CL ? ~0ull : ((1ull << nvalid) - 1ull));
+    }
+    __device__ __forceinline__ unsigned long long reset_rows() const { return MASKED ? rm : 0ull; }
+    __device__ __forceinline__ bool ok(int i) const { return MASKED ? ((vm >> i) & 1ull) != 0ull : i < nvalid; }
+    __device__ __forceinline__ bool rst(int i) const { return MASKED ? ((rm >> i) & 1ull) != 0ull : false; }
     // what the exclusive prefix E_i = G_{i-1} of a reset row still lacks: the reset belongs to row i itself
     __device__ __forceinline__ float eoff(int i) const { return rst(i) ? RESET_NATS : 0.f; }
 };
+typedef ChunkT<false> Chunk;
 
-__device__ __forceinline__ Chunk chunk_of(const Geometry& g, int idx) {
-    Chunk ch;
+template <bool MASKED>
+__device__ __forceinline__ ChunkT<MASKED> chunk_of(const Geometry& g, int idx) {
+    ChunkT<MASKED> ch;
     ch.gi = idx;
     ch.s = idx / g.NC;
     ch.c = idx - ch.s * g.NC;
@@ -89,10 +96,9 @@ __device__ __forceinline__ Chunk chunk_of(const Geometry& g, int idx) {
     ch.t0 = ch.c * CL;
     int left = g.T - ch.t0;
     ch.nvalid = left < CL ? left : CL;
-    if (g.valid == nullptr && g.reset == nullptr) {
-        ch.vm = ch.nvalid >= CL ? ~0ull : ((1ull << ch.nvalid) - 1ull);
-        ch.rm = 0ull;
-    } else {
+    ch.vm = 0ull;
+    ch.rm = 0ull;
+    if (MASKED) {
         // every warp reads the chunk's 64 mask bytes (all threads call chunk_of together); the ballots are
         // warp-uniform values
         const int lane = threadIdx.x & 31;
@@ -142,11 +148,13 @@ __device__ __forceinline__ float row_sum16(float v) {
 }
 
 // ---- strided BF16 / FP32 row access --------------------------------------
-__device__ __forceinline__ const __nv_bfloat16* row_bf16(const Operand& op, const Chunk& ch, int i) {
+template <class CH>
+__device__ __forceinline__ const __nv_bfloat16* row_bf16(const Operand& op, const CH& ch, int i) {
     return reinterpret_cast<const __nv_bfloat16*>(op.ptr) + ch.b * op.sb + (long long)(ch.t0 + i) * op.st +
            ch.hh * op.sh;
 }
-__device__ __forceinline__ const float* row_f32(const Operand& op, const Chunk& ch, int i) {
+template <class CH>
+__device__ __forceinline__ const float* row_f32(const Operand& op, const CH& ch, int i) {
     return reinterpret_cast<const float*>(op.ptr) + ch.b * op.sb + (long long)(ch.t0 + i) * op.st + ch.hh * op.sh;
 }
 
@@ -218,8 +226,8 @@ __device__ __forceinline__ void load8_f32(const float* row, int c0, int width, i
 }
 
 // Contiguous outputs [B,T,H,width]: eight channels of one row.
-template <bool FAST>
-__device__ __forceinline__ void store8_bf16(void* base, const Geometry& g, const Chunk& ch, int i, int c0,
+template <bool FAST, class CH>
+__device__ __forceinline__ void store8_bf16(void* base, const Geometry& g, const CH& ch, int i, int c0,
                                             int width, const float (&x)[8]) {
     if (FAST) {
         __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(base) +
@@ -266,7 +274,8 @@ __device__ __forceinline__ void prefetch_region(const void* base, int bytes) {
     for (int off = threadIdx.x * 128; off < bytes; off += NTHREADS * 128) prefetch_l2(b + off);
 }
 // the CL token rows of a strided operand chunk (row_bytes per row)
-__device__ __forceinline__ void prefetch_rows(const Operand& op, const Chunk& ch, int elem_bytes, int row_bytes) {
+template <class CH>
+__device__ __forceinline__ void prefetch_rows(const Operand& op, const CH& ch, int elem_bytes, int row_bytes) {
     const int lines = (row_bytes + 127) / 128;
     for (int idx = threadIdx.x; idx < CL * lines; idx += NTHREADS) {
         const int i = idx / lines, l = idx - i * lines;
@@ -376,8 +385,8 @@ __device__ __forceinline__ void chunk_cumsum(float* sG) {
 
 // Loads a BF16 operand chunk, L2-normalises every row and stores it as FP32.
 // rstd (may be null) receives 1/|x| per row.
-template <bool FAST>
-__device__ __forceinline__ void load_norm_panel(const Operand& op, const Chunk& ch, int width, float* sm,
+template <bool FAST, class CH>
+__device__ __forceinline__ void load_norm_panel(const Operand& op, const CH& ch, int width, float* sm,
                                                 float* rstd) {
     const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
 #pragma unroll
@@ -396,8 +405,8 @@ __device__ __forceinline__ void load_norm_panel(const Operand& op, const Chunk& 
     }
 }
 
-template <bool FAST>
-__device__ __forceinline__ void load_raw_panel(const Operand& op, const Chunk& ch, int width, float* sm) {
+template <bool FAST, class CH>
+__device__ __forceinline__ void load_raw_panel(const Operand& op, const CH& ch, int width, float* sm) {
     const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
 #pragma unroll
     for (int p = 0; p < ROW_PASSES; ++p) {
@@ -409,8 +418,8 @@ __device__ __forceinline__ void load_raw_panel(const Operand& op, const Chunk& c
     }
 }
 
-template <bool FAST>
-__device__ __forceinline__ void load_f32_panel(const Operand& op, const Chunk& ch, int width, float* sm) {
+template <bool FAST, class CH>
+__device__ __forceinline__ void load_f32_panel(const Operand& op, const CH& ch, int width, float* sm) {
     const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
 #pragma unroll
     for (int p = 0; p < ROW_PASSES; ++p) {
@@ -422,7 +431,8 @@ __device__ __forceinline__ void load_f32_panel(const Operand& op, const Chunk& c
     }
 }
 
-__device__ __forceinline__ void load_gamma(const Operand& op, const Chunk& ch, float* sg) {
+template <class CH>
+__device__ __forceinline__ void load_gamma(const Operand& op, const CH& ch, float* sg) {
     if (threadIdx.x < CL) {
         int i = threadIdx.x;
         sg[i] = ch.ok(i) ? *row_f32(op, ch, i) : 0.f;

@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(DEC_THREADS) k_decode_step(DecodeParams p) {
     const int r = p.g.r, V = p.g.V, tid = threadIdx.x;
     Chunk ch;
     ch.s = s; ch.c = 0; ch.b = b; ch.hh = hh; ch.t0 = 0; ch.nvalid = 1; ch.gi = s;
-    ch.vm = 1ull; ch.rm = 0ull;
+    ch.vm = 0ull; ch.rm = 0ull;
     const bool in_r = tid < r;
     float u = in_r ? __bfloat162float(row_bf16(p.u, ch, 0)[tid]) : 0.f;
     float k = in_r ? __bfloat162float(row_bf16(p.k, ch, 0)[tid]) : 0.f;

@@ -61,8 +61,8 @@ __device__ __forceinline__ void sources_fwd(const float (&uh)[8], const float (&
 }
 
 // Eight channels of one normalised BF16 row, in registers.
-template <bool FAST>
-__device__ __forceinline__ float load8_norm(const Operand& op, const Chunk& ch, int i, int c0, int width,
+template <bool FAST, class CH>
+__device__ __forceinline__ float load8_norm(const Operand& op, const CH& ch, int i, int c0, int width,
                                             float (&x)[8]) {
     load8_bf16<FAST>(row_bf16(op, ch, i), c0, width, op.vec, ch.ok(i), x);
     float ss = 0.f;
@@ -102,7 +102,7 @@ __device__ __forceinline__ void store8_smem(float* sm, int i, int c0, const floa
 // so that the C scan is  Delta = Upd + Qc Ct.
 constexpr size_t PREP_FWD_SMEM = 5 * SLOT_BYTES + MAT_BYTES + (CL + 3 * DP + NBLK * DP + 16) * sizeof(float);
 
-template <bool FAST>
+template <bool FAST, bool MASKED>
 __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
@@ -117,14 +117,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
     float* s_M = s_gam + CL;
     float* s_ibeta = s_M + 3 * DP;
     int* s_fastw = reinterpret_cast<int*>(s_ibeta + NBLK * DP);
-    const Chunk ch = chunk_of(p.g, blockIdx.x);
+    const ChunkT<MASKED> ch = chunk_of<MASKED>(p.g, blockIdx.x);
     const int r = p.g.r;
 
     load_norm_panel<FAST>(p.u, ch, r, s_uh, nullptr);
     load_f32_panel<FAST>(p.ld, ch, r, s_G);
     load_raw_panel<FAST>(p.h, ch, r, s_h);
     load_gamma(p.gam, ch, s_gam);
-    if (ch.reset_rows() != 0ull) {   // block-uniform: a reset token forgets RESET_NATS more (each thread patches what it loaded)
+    const bool any_reset = ch.reset_rows() != 0ull;
+    if (any_reset) {   // block-uniform: a reset token forgets RESET_NATS more (each thread patches what it loaded)
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
 #pragma unroll
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
@@ -147,7 +148,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
         int i = idx >> 7, c = idx & (DP - 1);
         const int i0 = i & ~(BT - 1);
         float G = s_G[i * LDP + c];
-        float E = (i ? s_G[(i - 1) * LDP + c] : 0.f) - ch.eoff(i);
+        float E = i ? s_G[(i - 1) * LDP + c] : 0.f;
+        if (any_reset) E -= ch.eoff(i);   // block-uniform branch
         float Gprev = i0 ? s_G[(i0 - 1) * LDP + c] : 0.f;
         float Gend = s_G[(i0 + BT - 1) * LDP + c];
         float uh = s_uh[i * LDP + c];
@@ -193,7 +195,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
     for (int idx = threadIdx.x; idx < CL * DP; idx += NTHREADS) {
         int i = idx >> 7, c = idx & (DP - 1);
         float gm = s_gam[i];
-        float E = (i ? s_G[(i - 1) * LDP + c] : 0.f) - ch.eoff(i);
+        float E = i ? s_G[(i - 1) * LDP + c] : 0.f;
+        if (any_reset) E -= ch.eoff(i);
         s_h[i * LDP + c] *= gm;
         s_ut[i * LDP + c] = gm * s_uh[i * LDP + c] * __expf(E);
     }
@@ -244,7 +247,7 @@ __device__ __forceinline__ void async_state_cols_f32(float* sm, const float* st,
     }
 }
 
-template <bool FAST>
+template <bool FAST, bool MASKED>
 __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
@@ -258,7 +261,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
     float* s_aqk = s_st1 + SLOT_FLOATS;
     float* s_beta = s_aqk + MAT_FLOATS;
     int* s_fastw = reinterpret_cast<int*>(s_beta + NBLK * DP);
-    const Chunk ch = chunk_of(p.g, blockIdx.x);
+    const ChunkT<MASKED> ch = chunk_of<MASKED>(p.g, blockIdx.x);
     const int r = p.g.r;
     const float* ct = state_ptr(p.CtCk, ch.gi);
 
@@ -347,7 +350,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
 // for the S scan (ag = -e exp(G), referenced to the chunk start like the scan itself).
 constexpr size_t EXT_PREP_FWD_SMEM = 6 * SLOT_BYTES + MAT_BYTES + (3 * DP + NBLK * DP + 16) * sizeof(float);
 
-template <bool FAST>
+template <bool FAST, bool MASKED>
 __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
@@ -362,7 +365,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
     float* s_M = s_aed + MAT_FLOATS;
     float* s_ibeta = s_M + 3 * DP;
     int* s_fastw = reinterpret_cast<int*>(s_ibeta + NBLK * DP);
-    const Chunk ch = chunk_of(p.g, blockIdx.x);
+    const ChunkT<MASKED> ch = chunk_of<MASKED>(p.g, blockIdx.x);
     const int r = p.g.r, V = p.g.V;
     bf16* gAqd = bmat_ptr(p.Aqd, ch.gi);
     float* gAed = mat_ptr(p.Aed, ch.gi);
@@ -485,7 +488,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
 // Output rows: y = Xg S_c + tril(Aqd) Z~, BF16 operands (the result is BF16).
 constexpr size_t OUTPUT_FWD_SMEM = 2 * BSLOT_BYTES + BSTATE_BYTES + BMAT_BYTES;
 
-template <bool FAST>
+template <bool FAST, bool MASKED>
 __global__ void __launch_bounds__(NTHREADS, 1) k_output_fwd(FwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
@@ -494,7 +497,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_output_fwd(FwdParams p) {
     bf16* b_zt = b_xg + BSLOT_ELEMS;
     bf16* b_S = b_zt + BSLOT_ELEMS;
     bf16* b_aqd = b_S + DP * LDB;
-    const Chunk ch = chunk_of(p.g, blockIdx.x);
+    const ChunkT<MASKED> ch = chunk_of<MASKED>(p.g, blockIdx.x);
     const int V = p.g.V;
 
     async_bpanel(b_xg, bpanel_ptr(p.Xg, ch.gi));
