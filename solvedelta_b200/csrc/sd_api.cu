@@ -268,6 +268,7 @@ cudaError_t configure_kernels() {
     if ((e = allow_smem(k_output_fwd<true, true>, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_output_fwd<false, true>, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_state_scan_tc, SCAN_TC_SMEM_BYTES)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_decode_step, DECODE_SMEM)) != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) {
         void* w = nullptr;
         if ((e = cudaGetSymbolAddress(&w, g_scan_fault_word)) != cudaSuccess) return e;
@@ -846,7 +847,8 @@ int sd_decode_step(const sd_decode_args* a, void* stream_) {
     p.C = a->C;
     p.S = a->S;
     p.y = a->y;
-    k_decode_step<<<a->shape.B * a->shape.H, DEC_THREADS, 0, stream>>>(p);
+    if (configure_kernels() != cudaSuccess) return SD_ERR_NO_DEVICE;
+    k_decode_step<<<a->shape.B * a->shape.H, DEC_THREADS, DECODE_SMEM, stream>>>(p);
     mark(stream);
     return launch_status();
 }

@@ -146,6 +146,11 @@ __device__ __forceinline__ void cp16(void* smem, const void* gmem) {
     unsigned s = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem));
 }
+// 16 bytes, or 16 zero bytes when !valid (nothing is read then; gmem must still be a mapped address)
+__device__ __forceinline__ void cp16_zfill(void* smem, const void* gmem, bool valid) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(valid ? 16 : 0));
+}
 __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::); }
 template <int N>
 __device__ __forceinline__ void cp_wait() {

@@ -1,7 +1,15 @@
-// Single-token recurrent step (T = 1, no gradient): one CTA per (batch, head)
-// stream updates the FP32 cache (C, S) in place and emits one output row.
-// The arithmetic is the token recurrence itself, in FP32.
+// Single-token recurrent step (T = 1, no gradient): one CTA per (batch, head) stream updates the FP32 cache
+// (C, S) in place and emits one output row.  The arithmetic is the token recurrence itself, in FP32.
+//
+// The step is pure state traffic (2 x 64 KiB read and written per stream at r = V = 128), so the kernel is
+// built around moving each state exactly once: both states stream into shared memory with 16-byte cp.async
+// copies issued up front (S lands behind the predictor phase), every phase works on the shared copies with
+// all 512 threads (four threads per row for the row dots, four row quarters per column for the column
+// sums), and each state goes back with 16-byte stores as soon as its phase is done.
+// Upstream counterparts: _predictor_recurrent_kernel, _relative_recurrent_sources_kernel and the fused
+// recurrent DPLR step (causallsso/ops/residual_frame/recurrent.py:33-98,188-327).
 #pragma once
+#include "sd_bf16.cuh"
 #include "sd_common.cuh"
 
 namespace sd {
@@ -13,26 +21,81 @@ struct DecodeParams {
     void* y;
 };
 
-constexpr int DEC_THREADS = 128;
+constexpr int DEC_THREADS = 512;
+constexpr int DEC_LD = DP + 4;   // row pitch of a shared state (floats)
+constexpr size_t DECODE_SMEM = (size_t(2) * DP * DEC_LD + 12 * DP + 32) * sizeof(float);
 
-__device__ __forceinline__ float block_sum128(float v, float* red) {
+// sum over the first DP threads' values (the others pass 0), returned to every thread
+__device__ __forceinline__ float block_sum(float v, float* red) {
 #pragma unroll
     for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
     __syncthreads();
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
     __syncthreads();
-    return red[0] + red[1] + red[2] + red[3];
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_THREADS / 32; ++w) t += red[w];
+    return t;
 }
 
-__global__ void __launch_bounds__(DEC_THREADS) k_decode_step(DecodeParams p) {
-    __shared__ float s_uh[DP], s_kh[DP], s_alpha[DP], s_delta[DP], s_e[DP], s_chi[DP], s_d[DP];
-    __shared__ float red[4];
+// [rows][cols] FP32 state in global memory (row pitch `cols`) -> shared [DP][DEC_LD], zero padded
+__device__ __forceinline__ void decode_state_in(float* sm, const float* g, int rows, int cols, bool vec) {
+    for (int idx = threadIdx.x; idx < DP * (DP / 4); idx += DEC_THREADS) {
+        const int a = idx >> 5, c4 = (idx & 31) << 2;
+        float* dst = sm + a * DEC_LD + c4;
+        if (vec) {
+            cp16_zfill(dst, g + (long long)(a < rows ? a : 0) * cols + (c4 < cols ? c4 : 0), a < rows && c4 < cols);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) dst[e] = (a < rows && c4 + e < cols) ? g[(long long)a * cols + c4 + e] : 0.f;
+        }
+    }
+}
+__device__ __forceinline__ void decode_state_out(float* g, const float* sm, int rows, int cols, bool vec) {
+    for (int idx = threadIdx.x; idx < DP * (DP / 4); idx += DEC_THREADS) {
+        const int a = idx >> 5, c4 = (idx & 31) << 2;
+        if (a >= rows || c4 >= cols) continue;
+        const float* src = sm + a * DEC_LD + c4;
+        if (vec) {
+            *reinterpret_cast<float4*>(g + (long long)a * cols + c4) = *reinterpret_cast<const float4*>(src);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (c4 + e < cols) g[(long long)a * cols + c4 + e] = src[e];
+        }
+    }
+}
+
+__global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(DecodeParams p) {
+    extern __shared__ __align__(16) float dsm[];
+    float* sC = dsm;                       // [DP][DEC_LD]
+    float* sS = sC + DP * DEC_LD;          // [DP][DEC_LD]
+    float* s_uh = sS + DP * DEC_LD;
+    float* s_kh = s_uh + DP;
+    float* s_alpha = s_kh + DP;
+    float* s_delta = s_alpha + DP;
+    float* s_e = s_delta + DP;
+    float* s_chi = s_e + DP;
+    float* s_d = s_chi + DP;
+    float* s_w = s_d + DP;
+    float* s_part = s_w + DP;              // [4][DP] partial column sums
+    float* red = s_part + 4 * DP;          // [16]
     const int s = blockIdx.x, b = s / p.g.H, hh = s - b * p.g.H;
     const int r = p.g.r, V = p.g.V, tid = threadIdx.x;
     Chunk ch;
     ch.s = s; ch.c = 0; ch.b = b; ch.hh = hh; ch.t0 = 0; ch.nvalid = 1; ch.gi = s;
     ch.vm = 0ull; ch.rm = 0ull;
-    const bool in_r = tid < r;
+    float* C = p.C + (long long)s * r * r;
+    float* S = p.S + (long long)s * r * V;
+    // 16-byte moves need rows that start on 16-byte boundaries
+    const bool vecC = (r & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0;
+    const bool vecS = (V & 3) == 0 && (reinterpret_cast<uintptr_t>(p.S) & 15) == 0;
+    decode_state_in(sC, C, r, r, vecC);
+    cp_commit();
+    decode_state_in(sS, S, r, V, vecS);
+    cp_commit();
+
+    const bool in_r = tid < r;     // threads 0..r-1 carry the token's channel values
     float u = in_r ? __bfloat162float(row_bf16(p.u, ch, 0)[tid]) : 0.f;
     float k = in_r ? __bfloat162float(row_bf16(p.k, ch, 0)[tid]) : 0.f;
     float q = in_r ? __bfloat162float(row_bf16(p.q, ch, 0)[tid]) : 0.f;
@@ -40,66 +103,99 @@ __global__ void __launch_bounds__(DEC_THREADS) k_decode_step(DecodeParams p) {
     float er = in_r ? __bfloat162float(row_bf16(p.er, ch, 0)[tid]) : 0.f;
     float ld = in_r ? row_f32(p.ld, ch, 0)[tid] : 0.f;
     const float gamma = *row_f32(p.gam, ch, 0);
-    float uh = u * rsqrtf(block_sum128(u * u, red) + 1e-24f);
-    float kh = k * rsqrtf(block_sum128(k * k, red) + 1e-24f);
-    float qh = q * rsqrtf(block_sum128(q * q, red) + 1e-24f);
-    s_uh[tid] = uh;
-    s_kh[tid] = kh;
-    s_alpha[tid] = __expf(ld);
+    const float uh = u * rsqrtf(block_sum(u * u, red) + 1e-24f);
+    const float kh = k * rsqrtf(block_sum(k * k, red) + 1e-24f);
+    const float qh = q * rsqrtf(block_sum(q * q, red) + 1e-24f);
+    if (tid < DP) {
+        s_uh[tid] = uh;
+        s_kh[tid] = kh;
+        s_alpha[tid] = __expf(ld);
+    }
+    cp_wait<1>();      // C has landed
     __syncthreads();
-    float* C = p.C + (long long)s * r * r;
-    float* S = p.S + (long long)s * r * V;
-    // residual against the old predictor: one warp per row of C
+    // residual against the old predictor: four threads per row of C, 32 columns each
     {
-        const int warp = tid >> 5, lane = tid & 31;
-        for (int a = warp; a < r; a += DEC_THREADS / 32) {
-            float acc = 0.f;
-            for (int c = lane; c < r; c += 32) acc = fmaf(C[(long long)a * r + c], s_uh[c], acc);
+        const int a = tid >> 2, q4 = (tid & 3) * 32;
+        float acc = 0.f;
 #pragma unroll
-            for (int m = 16; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
-            if (lane == 0) s_delta[a] = acc;
+        for (int c = 0; c < 32; c += 4) {
+            const float4 cv = *reinterpret_cast<const float4*>(sC + a * DEC_LD + q4 + c);
+            const float4 uv = *reinterpret_cast<const float4*>(s_uh + q4 + c);
+            acc = fmaf(cv.x, uv.x, fmaf(cv.y, uv.y, fmaf(cv.z, uv.z, fmaf(cv.w, uv.w, acc))));
         }
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        if ((tid & 3) == 0) s_delta[a] = acc;
     }
     __syncthreads();
     const float delta = in_r ? gamma * (hv - s_delta[tid]) : 0.f;
     __syncthreads();
-    s_delta[tid] = delta;
-    const float n2 = block_sum128(delta * delta, red);
+    if (tid < DP) s_delta[tid] = delta;
+    const float n2 = block_sum(delta * delta, red);
     const float fs = RHO * rsqrtf(RHO * RHO + n2);
     const float phi = fs * delta;
-    const float den = 1.f + block_sum128(phi * uh, red);
+    const float den = 1.f + block_sum(phi * uh, red);
     const float bb = sigmoidf_(er) * kh;
-    const float sb = block_sum128(uh * bb, red) / den;
-    const float sq = block_sum128(uh * qh, red) / den;
-    s_e[tid] = bb - phi * sb;
-    s_chi[tid] = qh - phi * sq;
-    // right-decay + rank-one write of C, and d = k^ + C_new^T k^ (thread = column)
-    float dcol = kh;
-    if (in_r) {
-        const float al = s_alpha[tid];
-        for (int a = 0; a < r; ++a) {
-            float cn = fmaf(C[(long long)a * r + tid], al, s_delta[a] * uh);
-            C[(long long)a * r + tid] = cn;
-            dcol = fmaf(cn, s_kh[a], dcol);
-        }
+    const float sb = block_sum(uh * bb, red) / den;
+    const float sq = block_sum(uh * qh, red) / den;
+    if (tid < DP) {
+        s_e[tid] = bb - phi * sb;
+        s_chi[tid] = qh - phi * sq;
     }
-    s_d[tid] = in_r ? dcol : 0.f;
     __syncthreads();
-    // memory: decay rows, read along e, write along d, read along chi (thread = value column)
-    if (tid < V) {
-        float pred = 0.f;
-        for (int c = 0; c < r; ++c) pred = fmaf(s_alpha[c] * S[(long long)c * V + tid], s_e[c], pred);
-        const float wr = __bfloat162float(row_bf16(p.wr, ch, 0)[tid]);
-        const float vv = __bfloat162float(row_bf16(p.v, ch, 0)[tid]);
-        const float w = sigmoidf_(wr) * vv - pred;
-        float out = 0.f;
-        for (int c = 0; c < r; ++c) {
-            float sn = fmaf(s_alpha[c], S[(long long)c * V + tid], s_d[c] * w);
-            S[(long long)c * V + tid] = sn;
-            out = fmaf(sn, s_chi[c], out);
+    // right-decay + rank-one write of C, and d = k^ + C_new^T k^ : thread = (column, quarter of the rows)
+    const int col = tid & (DP - 1), a0 = (tid >> 7) * 32;
+    {
+        const float al = s_alpha[col], uc = s_uh[col];
+        float part = 0.f;
+#pragma unroll 8
+        for (int a = a0; a < a0 + 32; ++a) {
+            const float cn = fmaf(sC[a * DEC_LD + col], al, s_delta[a] * uc);
+            sC[a * DEC_LD + col] = cn;
+            part = fmaf(cn, s_kh[a], part);
         }
-        reinterpret_cast<__nv_bfloat16*>(p.y)[(long long)s * V + tid] = __float2bfloat16_rn(out);
+        s_part[(tid >> 7) * DP + col] = part;
     }
+    cp_wait<0>();      // S has landed
+    __syncthreads();
+    decode_state_out(C, sC, r, r, vecC);
+    if (tid < DP) s_d[tid] = (tid < r) ? kh + (s_part[tid] + s_part[DP + tid]) + (s_part[2 * DP + tid] + s_part[3 * DP + tid]) : 0.f;
+    // memory: prediction along e on the decayed rows (thread = (value column, quarter of the rows))
+    {
+        float part = 0.f;
+#pragma unroll 8
+        for (int c = a0; c < a0 + 32; ++c) part = fmaf(s_alpha[c] * sS[c * DEC_LD + col], s_e[c], part);
+        __syncthreads();   // the partial sums of d have been read
+        s_part[(tid >> 7) * DP + col] = part;
+    }
+    __syncthreads();
+    if (tid < DP) {
+        float w = 0.f;
+        if (tid < V) {
+            const float wr = __bfloat162float(row_bf16(p.wr, ch, 0)[tid]);
+            const float vv = __bfloat162float(row_bf16(p.v, ch, 0)[tid]);
+            w = sigmoidf_(wr) * vv - ((s_part[tid] + s_part[DP + tid]) + (s_part[2 * DP + tid] + s_part[3 * DP + tid]));
+        }
+        s_w[tid] = w;
+    }
+    __syncthreads();
+    // decay rows, write along d, read along chi
+    {
+        const float w = s_w[col];
+        float part = 0.f;
+#pragma unroll 8
+        for (int c = a0; c < a0 + 32; ++c) {
+            const float sn = fmaf(s_alpha[c], sS[c * DEC_LD + col], s_d[c] * w);
+            sS[c * DEC_LD + col] = sn;
+            part = fmaf(sn, s_chi[c], part);
+        }
+        s_part[(tid >> 7) * DP + col] = part;
+    }
+    __syncthreads();
+    decode_state_out(S, sS, r, V, vecS);
+    if (tid < V)
+        reinterpret_cast<__nv_bfloat16*>(p.y)[(long long)s * V + tid] =
+            __float2bfloat16_rn((s_part[tid] + s_part[DP + tid]) + (s_part[2 * DP + tid] + s_part[3 * DP + tid]));
 }
 
 }  // namespace sd

@@ -64,9 +64,21 @@ def test_streams_are_independent(workload):
     assert torch.equal(finp.S, fin.S[perm]) and torch.equal(finp.predictor, fin.predictor[perm])
 
 
-@pytest.mark.parametrize("b,h", [(0, 0), (7, 7)])
-def test_single_streams_of_the_full_run_match_the_checker(workload, b, h):
+def _zero_geometry(workload):
+    """The benchmark workload with the geometry rate at zero and no initial predictor state: the operator
+    is then exactly the GDN2 edit / read (upstream tests/core/test_rebuild_semantics.py:296-316)."""
     cpu, dev = workload
+    cpu0, dev0 = dict(cpu), dict(dev)
+    for d in (cpu0, dev0):
+        d["geometry_write"] = torch.zeros_like(d["geometry_write"])
+        d["C0"] = torch.zeros_like(d["C0"])
+    return cpu0, dev0
+
+
+@pytest.mark.parametrize("gamma_zero", [False, True])
+@pytest.mark.parametrize("b,h", [(0, 0), (7, 7)])
+def test_single_streams_of_the_full_run_match_the_checker(workload, b, h, gamma_zero):
+    cpu, dev = _zero_geometry(workload) if gamma_zero else workload
     leaves = [dev[n].detach().clone().requires_grad_() for n in NAMES]
     state = SolveDeltaState(dev["C0"].clone().requires_grad_(), dev["S0"].clone().requires_grad_())
     y, fin = solvedelta_native(*leaves, initial_state=state, return_final_state=True)
@@ -82,7 +94,12 @@ def test_single_streams_of_the_full_run_match_the_checker(workload, b, h):
                        dS_T=cpu["dS_T"][b:b + 1, h:h + 1].double().numpy(), initial_state=st)
     sl = lambda x: x[b:b + 1, :, h:h + 1].detach().float().cpu().numpy()
     assert max_rel(sl(y), yo) <= 2e-2
-    assert max_rel(fin.predictor[b:b + 1, h:h + 1].detach().cpu().numpy(), so.predictor) <= 1e-3
+    if gamma_zero:
+        # nothing writes the predictor: it stays at its (zero) initial value, and the exterior is the GDN2 loop
+        assert float(np.abs(so.predictor).max()) == 0.0 and float(fin.predictor[b, h].abs().max()) == 0.0
+        assert max_rel(sl(y), _gdn2_outputs(cpu, b, h)) <= 2e-2
+    else:
+        assert max_rel(fin.predictor[b:b + 1, h:h + 1].detach().cpu().numpy(), so.predictor) <= 1e-3
     assert max_rel(fin.S[b:b + 1, h:h + 1].detach().cpu().numpy(), so.S) <= 1e-3
     se = torch.sigmoid(cpu["erase_raw"].double()).numpy()[b:b + 1, :, h:h + 1, 0]
     sw = torch.sigmoid(cpu["write_raw"].double()).numpy()[b:b + 1, :, h:h + 1, 0]
@@ -96,6 +113,51 @@ def test_single_streams_of_the_full_run_match_the_checker(workload, b, h):
     gC = grads[9][b:b + 1, h:h + 1].cpu().numpy()
     gS = grads[10][b:b + 1, h:h + 1].cpu().numpy()
     assert rel_l2(gC, ref["C0"]) <= 3e-2 and rel_l2(gS, ref["S0"]) <= 3e-2
+
+
+def _gdn2_outputs(cpu, b, h):
+    """The explicit GDN2 recurrence in FP64 for one stream: S <- diag(alpha) S; S += k (w*v - S^T (e*k))^T;
+    y = S^T q, with normalised q, k (upstream tests/core/test_rebuild_semantics.py:296-316)."""
+    f = lambda x: x[b, :, h].double().numpy()
+    q, k = f(cpu["q"]), f(cpu["keys"][:, :, :, 0])
+    q = q / np.linalg.norm(q, axis=-1, keepdims=True)
+    k = k / np.linalg.norm(k, axis=-1, keepdims=True)
+    v = f(cpu["values"][:, :, :, 0])
+    alpha = np.exp(f(cpu["log_decay"]))
+    e = 1.0 / (1.0 + np.exp(-f(cpu["erase_raw"][:, :, :, 0])))
+    w = 1.0 / (1.0 + np.exp(-f(cpu["write_raw"][:, :, :, 0])))
+    S = cpu["S0"][b, h].double().numpy().copy()
+    out = np.empty((1, q.shape[0], 1, v.shape[-1]))
+    for t in range(q.shape[0]):
+        S = alpha[t][:, None] * S
+        S = S + np.outer(k[t], w[t] * v[t] - S.T @ (e[t] * k[t]))
+        out[0, t, 0] = S.T @ q[t]
+    return out
+
+
+def test_long_prefill_then_decode_steps_equal_one_pass():
+    """Long-context continuation at the operator (upstream tests/model/test_modeling_solvedelta.py:264-301):
+    a 32 768-token prefill at B=1, H=8 followed by 256 single-token recurrent steps ends in the same (C, S)
+    as one pass over all 33 024 tokens, and produces the same outputs for the 256 tokens."""
+    from bench import make_cpu_inputs
+
+    prefill, steps = 32768, 256
+    cpu = make_cpu_inputs(1, prefill + steps, H, R, V, seed=4)
+    dev = {k: v.cuda() for k, v in cpu.items()}
+    args = lambda lo, hi: [dev[n][:, lo:hi] for n in NAMES]
+    start = SolveDeltaState(dev["C0"], dev["S0"])
+    with torch.no_grad():
+        y_all, fin_all = solvedelta_native(*args(0, prefill + steps), initial_state=start, return_final_state=True)
+        _, state = solvedelta_native(*args(0, prefill), initial_state=start, return_final_state=True)
+        pieces = []
+        for t in range(prefill, prefill + steps):
+            y_t, state = solvedelta_native(*args(t, t + 1), initial_state=state, return_final_state=True)
+            pieces.append(y_t)
+    y_dec = torch.cat(pieces, dim=1).float().cpu().numpy()
+    assert max_rel(y_dec, y_all[:, prefill:].float().cpu().numpy()) <= 2e-2
+    assert max_rel(state.predictor.cpu().numpy(), fin_all.predictor.cpu().numpy()) <= 1e-3
+    assert max_rel(state.S.cpu().numpy(), fin_all.S.cpu().numpy()) <= 1e-3
+    assert torch.isfinite(y_all).all()
 
 
 @pytest.mark.gpu

@@ -292,3 +292,36 @@ def test_graphed_steps_with_master_weights_train():
         shadows.assert_current()
     assert all(np.isfinite(losses)) and losses[-1] < losses[0] - 0.3, losses
     assert shadows.nbytes == 4 * sum(p.numel() for p in model.parameters())
+
+
+def test_long_prefill_then_decode_steps_equal_one_pass_through_the_model():
+    """The long-context configuration on a two-layer model (upstream tests/model/test_modeling_solvedelta.py:264-301):
+    a 32 768-token prefill at B=1 with use_cache, then 256 cached one-token steps, against one pass over all
+    33 024 tokens: the per-layer (C, S) cache and the logits of the 256 tokens."""
+    torch.manual_seed(11)
+    # initializer_range 0.02: with the 0.05 of the short tests this random model's memory grows without bound
+    # over tens of thousands of tokens (|S| passes 1e19 by token 8192), which is the model, not the kernels
+    config = SolveDeltaConfig(hidden_size=256, num_heads=2, head_k_dim=64, head_v_dim=128, num_hidden_layers=2,
+                              vocab_size=512, initializer_range=0.02)
+    model = SolveDeltaForCausalLM(config).prepare("cuda").eval()
+    prefill, steps = 32768, 256
+    ids = torch.randint(0, config.vocab_size, (1, prefill + steps), device="cuda")
+    with torch.no_grad():
+        full = model(input_ids=ids, use_cache=True)
+        step = model(input_ids=ids[:, :prefill], use_cache=True, logits_to_keep=1)
+        pieces = []
+        for t in range(prefill, prefill + steps):
+            step = model(input_ids=ids[:, t:t + 1], past_key_values=step.past_key_values, use_cache=True)
+            pieces.append(step.logits)
+    got = torch.cat(pieces, dim=1).float().cpu().numpy()
+    want = full.logits[:, prefill:].float().cpu().numpy()
+    assert np.isfinite(want).all()
+    assert rel_l2(got, want) < 1.5 * LOGIT_TOL
+    assert step.past_key_values.get_seq_length() == prefill + steps
+    for layer in range(config.num_hidden_layers):
+        C, S = step.past_key_values[layer]["recurrent_state"]
+        Cf, Sf = full.past_key_values[layer]["recurrent_state"]
+        # FP32 states fed by BF16 activations that the two runs round differently (other GEMM shapes, the
+        # recurrent step instead of the chunk kernels for the last 256 tokens): BF16-grade agreement
+        assert rel_l2(C.cpu().numpy(), Cf.cpu().numpy()) < 2e-2
+        assert rel_l2(S.cpu().numpy(), Sf.cpu().numpy()) < 2e-2
