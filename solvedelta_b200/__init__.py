@@ -11,7 +11,7 @@ from .config import SolveDeltaConfig
 from .mixer_ops import conv4_silu, conv4_silu_segmented, kda_decay_gate, rms_norm_gated
 from .model import RMSNormGated, SolveDelta, SolveDeltaLayerState
 from .modeling import (GraphedDecoder, SolveDeltaBlock, SolveDeltaCache, SolveDeltaCacheAdapter, SolveDeltaForCausalLM,
-                       SolveDeltaMLP, SolveDeltaModel)
+                       SolveDeltaMLP, SolveDeltaModel, SolveDeltaPreTrainedModel)
 from .training import (BF16ShadowWeights, SolveDeltaGraphedTrainingStep, allreduce_gradients, causal_lm_loss,
                        fixed_dense_linear_cross_entropy)
 from .packing import PackedSegments, build_packed_segments, pack_tokens, unpack_tokens
@@ -23,7 +23,15 @@ from .ops import (
     solvedelta_zero_state,
 )
 
+# Hugging Face registration, as upstream's package import does (causallsso/__init__.py:23-50)
+from transformers import AutoConfig, AutoModel, AutoModelForCausalLM
+
+AutoConfig.register(SolveDeltaConfig.model_type, SolveDeltaConfig, exist_ok=True)
+AutoModel.register(SolveDeltaConfig, SolveDeltaModel, exist_ok=True)
+AutoModelForCausalLM.register(SolveDeltaConfig, SolveDeltaForCausalLM, exist_ok=True)
+
 __all__ = [
+    "SolveDeltaPreTrainedModel",
     "BF16ShadowWeights",
     "SolveDeltaGraphedTrainingStep",
     "allreduce_gradients",

@@ -1,110 +1,123 @@
-"""Configuration of the mixer and of the causal LM around it: the fields of
-upstream's ``SolveDeltaConfig`` (causallsso/config.py:8-199) that this package
-reads, with the same names, defaults, validation messages and head-width
-resolution.  It is a plain object (no Hugging Face base class).  Switches that
-only select between implementations of the same arithmetic upstream
-(``fuse_norm``, ``fuse_swiglu``, ``fuse_cross_entropy``) are accepted and kept;
-hybrid attention layers (``attn``) are not built and are refused."""
+"""Configuration of the mixer and of the causal LM around it, as a Hugging Face config.
+
+Field names and defaults are those of upstream's ``SolveDeltaConfig``
+(causallsso/config.py:8-80), so an upstream ``config.json`` loads unchanged and
+``AutoConfig.for_model("solvedelta", ...)`` resolves to this class.  Fields that only
+choose between implementations of the same arithmetic upstream (``fuse_norm``,
+``fuse_swiglu``, ``fuse_cross_entropy``, ...) are accepted and kept as plain attributes;
+hybrid attention layers (``attn``) are not built and are refused.
+"""
 from __future__ import annotations
 
 import math
-from typing import Optional
+from typing import Any, Callable, Dict, Optional
+
+from transformers import PreTrainedConfig
 
 
-class SolveDeltaConfig:
+def _whole(optional: bool = False) -> Callable[[str, Any], None]:
+    """A strictly positive int (bools are not ints here); None allowed when optional."""
+    def check(name: str, value: Any) -> None:
+        if value is None and optional:
+            return
+        if type(value) is not int:
+            raise TypeError(f"{name}: expected an int{' or None' if optional else ''}, got {type(value).__name__}")
+        if value < 1:
+            raise ValueError(f"{name}: expected a value >= 1, got {value}")
+    return check
+
+
+def _positive_real(name: str, value: Any) -> None:
+    if type(value) not in (int, float):
+        raise TypeError(f"{name}: expected a real number, got {type(value).__name__}")
+    if not (math.isfinite(value) and value > 0):
+        raise ValueError(f"{name}: expected a finite value > 0, got {value}")
+
+
+def _flag(name: str, value: Any) -> None:
+    if type(value) is not bool:
+        raise TypeError(f"{name}: expected True or False, got {type(value).__name__}")
+
+
+def _activation(name: str, value: Any) -> None:
+    if value not in ("swish", "powlu"):
+        raise ValueError(f"{name}: {value!r} is not one of 'swish', 'powlu'")
+
+
+def _no_hybrid_layers(name: str, value: Any) -> None:
+    if value is not None:
+        raise NotImplementedError("hybrid attention layers (attn) are not part of this package")
+
+
+_RULES: Dict[str, Callable[[str, Any], None]] = {
+    "hidden_size": _whole(), "num_heads": _whole(), "num_edits": _whole(), "num_hidden_layers": _whole(),
+    "vocab_size": _whole(), "max_position_embeddings": _whole(),
+    "head_k_dim": _whole(optional=True), "head_v_dim": _whole(optional=True),
+    "intermediate_size": _whole(optional=True), "hidden_ratio": _whole(optional=True),
+    "expand_k": _positive_real, "expand_v": _positive_real, "norm_eps": _positive_real,
+    "initializer_range": _positive_real,
+    "use_short_conv": _flag, "bias": _flag, "use_cache": _flag, "tie_word_embeddings": _flag,
+    "hidden_act": _activation, "attn": _no_hybrid_layers,
+}
+
+
+class SolveDeltaConfig(PreTrainedConfig):
     model_type = "solvedelta"
+    keys_to_ignore_at_inference = ["past_key_values"]
 
-    def __init__(self, hidden_size: int = 2048, num_heads: int = 16, head_k_dim: Optional[int] = None,
-                 head_v_dim: Optional[int] = None, expand_k: float = 1.0, expand_v: float = 1.0,
-                 num_edits: int = 1, use_short_conv: bool = True, bias: bool = False, *,
-                 num_hidden_layers: int = 24, hidden_ratio: Optional[int] = 4,
-                 intermediate_size: Optional[int] = None, hidden_act: str = "swish",
-                 norm_eps: float = 1e-6, max_position_embeddings: int = 2048, attn=None, use_cache: bool = True,
-                 vocab_size: int = 32000, initializer_range: float = 0.02, pad_token_id: Optional[int] = None,
-                 bos_token_id: int = 1, eos_token_id: int = 2, tie_word_embeddings: bool = False,
-                 **unused) -> None:
-        self.hidden_size = hidden_size
-        self.num_heads = num_heads
-        self.head_k_dim = head_k_dim
-        self.head_v_dim = head_v_dim
-        self.expand_k = expand_k
-        self.expand_v = expand_v
-        self.num_edits = num_edits
-        self.use_short_conv = use_short_conv
-        self.bias = bias
-        self.norm_eps = norm_eps
-        self.num_hidden_layers = num_hidden_layers
-        self.hidden_ratio = hidden_ratio
-        self.intermediate_size = intermediate_size
-        self.hidden_act = hidden_act
-        self.max_position_embeddings = max_position_embeddings
-        self.attn = attn
-        self.use_cache = use_cache
-        self.vocab_size = vocab_size
-        self.initializer_range = initializer_range
-        self.pad_token_id = pad_token_id
-        self.bos_token_id = bos_token_id
-        self.eos_token_id = eos_token_id
-        self.tie_word_embeddings = tie_word_embeddings
-        self.extra = dict(unused)  # implementation switches of upstream's shell: accepted and kept, not used
-        self._validate()
+    hidden_size: int = 2048
+    num_heads: int = 16
+    head_k_dim: Optional[int] = None
+    head_v_dim: Optional[int] = None
+    expand_k: float = 1.0
+    expand_v: float = 1.0
+    num_edits: int = 1
+    use_short_conv: bool = True
+    bias: bool = False
+    num_hidden_layers: int = 24
+    hidden_ratio: Optional[int] = 4
+    intermediate_size: Optional[int] = None
+    hidden_act: str = "swish"
+    norm_eps: float = 1e-6
+    max_position_embeddings: int = 2048
+    attn: Optional[Any] = None
+    use_cache: bool = True
+    vocab_size: int = 32000
+    initializer_range: float = 0.02
+    pad_token_id: Optional[int] = None
+    bos_token_id: Optional[int] = 1
+    eos_token_id: Optional[int] = 2
+    tie_word_embeddings: bool = False
 
-    def _validate(self) -> None:
-        for name in ("hidden_size", "num_heads", "num_edits", "num_hidden_layers", "vocab_size",
-                     "max_position_embeddings"):
-            value = getattr(self, name)
-            if isinstance(value, bool) or not isinstance(value, int):
-                raise TypeError(f"{name} must be an int, got {type(value).__name__}")
-            if value <= 0:
-                raise ValueError(f"{name} must be positive, got {value}")
+    def __post_init__(self, **kwargs):
+        for name, rule in _RULES.items():
+            rule(name, getattr(self, name))
         if self.num_edits != 1:
-            raise ValueError("the current SolveDelta production contract requires num_edits=1")
-        for name in ("head_k_dim", "head_v_dim", "intermediate_size"):
-            value = getattr(self, name)
-            if value is not None:
-                if isinstance(value, bool) or not isinstance(value, int):
-                    raise TypeError(f"{name} must be an int or None")
-                if value <= 0:
-                    raise ValueError(f"{name} must be positive, got {value}")
-        if self.hidden_ratio is not None:
-            if isinstance(self.hidden_ratio, bool) or not isinstance(self.hidden_ratio, int):
-                raise TypeError("hidden_ratio must be an int or None")
-            if self.hidden_ratio <= 0:
-                raise ValueError("hidden_ratio must be positive")
-        if self.hidden_act not in ("swish", "powlu"):
-            raise ValueError(f"Unsupported hidden_act: {self.hidden_act}")
-        if self.attn is not None:
-            raise NotImplementedError("hybrid attention layers are not part of this package")
-        for name in ("expand_k", "expand_v", "norm_eps", "initializer_range"):
-            value = getattr(self, name)
-            if isinstance(value, bool) or not isinstance(value, (int, float)):
-                raise TypeError(f"{name} must be a real number")
-            if not math.isfinite(float(value)) or value <= 0:
-                raise ValueError(f"{name} must be finite and positive")
-        for name in ("use_short_conv", "bias", "use_cache", "tie_word_embeddings"):
-            if not isinstance(getattr(self, name), bool):
-                raise TypeError(f"{name} must be a bool, got {type(getattr(self, name)).__name__}")
-        _ = self.resolved_head_k_dim
-        _ = self.resolved_head_v_dim
+            raise ValueError("num_edits: the production path carries exactly one edit per token (num_edits=1)")
+        self.head_width(self.head_k_dim, self.expand_k, "expand_k")
+        self.head_width(self.head_v_dim, self.expand_v, "expand_v")
+        super().__post_init__(**kwargs)
 
-    def _resolve_head_dim(self, explicit, expand, name) -> int:
+    def head_width(self, explicit: Optional[int], expand: float, name: str) -> int:
+        """Width of one head: the explicit value, else hidden_size * expand split evenly over the heads."""
         if explicit is not None:
             return explicit
-        total_float = self.hidden_size * float(expand)
-        total = round(total_float)
-        if not math.isclose(total_float, total, rel_tol=0.0, abs_tol=1e-9):
-            raise ValueError(f"hidden_size * {name} must be an integer, got {total_float}")
-        if total % self.num_heads:
-            raise ValueError(f"resolved total width {total} must be divisible by num_heads={self.num_heads}")
-        return total // self.num_heads
+        total = self.hidden_size * expand
+        whole = int(total + 0.5)
+        if abs(total - whole) > 1e-9:
+            raise ValueError(f"{name}: hidden_size * {name} = {total} is not a whole number of channels")
+        per_head, rest = divmod(whole, self.num_heads)
+        if rest:
+            raise ValueError(f"{name}: {whole} channels do not split evenly over {self.num_heads} heads")
+        return per_head
 
     @property
     def resolved_head_k_dim(self) -> int:
-        return self._resolve_head_dim(self.head_k_dim, self.expand_k, "expand_k")
+        return self.head_width(self.head_k_dim, self.expand_k, "expand_k")
 
     @property
     def resolved_head_v_dim(self) -> int:
-        return self._resolve_head_dim(self.head_v_dim, self.expand_v, "expand_v")
+        return self.head_width(self.head_v_dim, self.expand_v, "expand_v")
 
     @property
     def key_dim(self) -> int:

@@ -12,12 +12,13 @@ device, and there is no CPU path.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
 
 import torch
 import torch.nn.functional as F
 from torch import nn
+from transformers import PreTrainedModel
+from transformers.modeling_outputs import BaseModelOutputWithPast, CausalLMOutputWithPast
 
 from . import _lib
 from .config import SolveDeltaConfig
@@ -60,6 +61,20 @@ class SolveDeltaCache:
     def get_seq_length(self, layer_idx: int = 0) -> int:
         return self._seen_tokens if len(self.states) > layer_idx else 0
 
+    def layer_state(self, layer_idx: int) -> Optional[SolveDeltaLayerState]:
+        """What layer ``layer_idx`` continues from: None while the cache has nothing for it."""
+        if layer_idx >= len(self.states):
+            return None
+        entry = self.states[layer_idx]
+        pair = entry.get("recurrent_state")
+        if pair is None:
+            return None
+        try:
+            predictor, memory = pair
+        except (TypeError, ValueError):
+            raise ValueError("SolveDelta cache recurrent_state must contain (predictor,S)") from None
+        return SolveDeltaLayerState(operator=SolveDeltaState(predictor, memory), conv=entry.get("conv_state"))
+
     def update(self, layer_idx: int, recurrent_state, conv_state, offset: int = 1) -> Dict[str, Any]:
         if layer_idx == 0:
             self._seen_tokens += offset
@@ -74,28 +89,19 @@ class SolveDeltaCache:
         return state
 
 
-def _state_from_cache(last_state: Optional[Dict[str, Any]]) -> Optional[SolveDeltaLayerState]:
-    if last_state is None:
-        return None
-    recurrent_state = last_state.get("recurrent_state")
-    if recurrent_state is None:
-        return None
-    if not isinstance(recurrent_state, (tuple, list)) or len(recurrent_state) != 2:
-        raise ValueError("SolveDelta cache recurrent_state must contain (predictor,S)")
-    return SolveDeltaLayerState(operator=SolveDeltaState(*recurrent_state), conv=last_state.get("conv_state"))
-
-
 def segment_reset_mask(hidden_states: torch.Tensor, cu_seqlens: torch.Tensor) -> torch.Tensor:
-    """Reset mask of a packed batch [1,T,D]: True at every sequence start (modeling_solvedelta.py:118-134)."""
-    if hidden_states.shape[0] != 1:
-        raise ValueError("explicit cu_seqlens require packed hidden states [1,T,D]")
-    if cu_seqlens.ndim != 1 or cu_seqlens.numel() < 2:
-        raise ValueError("cu_seqlens must be one-dimensional with at least two entries")
+    """Packed batch [1,T,D] with sequence boundaries ``cu_seqlens`` -> bool [1,T], True on the first token
+    of every sequence (what upstream's ``_segment_reset_mask`` returns, modeling_solvedelta.py:118-134)."""
     if cu_seqlens.dtype not in (torch.int32, torch.int64):
         raise TypeError("cu_seqlens must have int32 or int64 dtype")
-    starts = cu_seqlens[:-1].to(device=hidden_states.device, dtype=torch.long)
-    reset_mask = torch.zeros((1, hidden_states.shape[1]), dtype=torch.bool, device=hidden_states.device)
-    return reset_mask.scatter(1, starts.unsqueeze(0), True)
+    if cu_seqlens.ndim != 1 or cu_seqlens.numel() < 2:
+        raise ValueError("cu_seqlens must be one-dimensional with at least two entries")
+    rows, tokens = hidden_states.shape[:2]
+    if rows != 1:
+        raise ValueError("explicit cu_seqlens require packed hidden states [1,T,D]")
+    mask = hidden_states.new_zeros(tokens, dtype=torch.bool)
+    mask[cu_seqlens[:-1].to(hidden_states.device, torch.long)] = True
+    return mask.unsqueeze(0)
 
 
 class SolveDeltaMLP(nn.Module):
@@ -142,43 +148,49 @@ class SolveDeltaCacheAdapter(nn.Module):
         self.layer_idx = layer_idx
         self.mixer = SolveDelta(config)
 
+    @staticmethod
+    def _valid_tokens(attention_mask: Optional[torch.Tensor], batch: int, length: int) -> Optional[torch.Tensor]:
+        """The attention mask covers the whole history; the mixer wants the columns of the current tokens."""
+        if attention_mask is None:
+            return None
+        if attention_mask.ndim != 2 or attention_mask.shape[0] != batch:
+            raise ValueError("attention_mask must have shape [B,T]")
+        if attention_mask.shape[1] < length:
+            raise ValueError("attention_mask is shorter than the current input")
+        return attention_mask[:, attention_mask.shape[1] - length:].bool()
+
+    @staticmethod
+    def _reset_tokens(hidden_states: torch.Tensor, continuing: bool, options: Dict[str, Any]) -> Optional[torch.Tensor]:
+        """An explicit ``solvedelta_reset_mask`` wins; otherwise ``cu_seqlens`` marks the sequence starts.  When
+        the call continues a cached state, the boundary at token 0 that ``cu_seqlens`` always lists is not a reset."""
+        resets = options.get("solvedelta_reset_mask")
+        boundaries = options.get("cu_seqlens")
+        if resets is None:
+            if boundaries is None:
+                return None
+            resets = segment_reset_mask(hidden_states, boundaries)
+        if resets.dtype != torch.bool or tuple(resets.shape) != tuple(hidden_states.shape[:2]):
+            raise ValueError("solvedelta_reset_mask must be bool [B,T]")
+        if continuing and boundaries is not None:
+            resets = resets.clone()
+            resets[0, 0] = False
+        return resets
+
     def forward(self, hidden_states: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
                 past_key_values: Optional[SolveDeltaCache] = None, use_cache: Optional[bool] = False,
                 **kwargs) -> Tuple[torch.Tensor, Optional[SolveDeltaCache]]:
-        batch, length, _ = hidden_states.shape
-        last_state = None
-        if past_key_values is not None and len(past_key_values) > self.layer_idx:
-            last_state = past_key_values[self.layer_idx]
-        initial_state = _state_from_cache(last_state)
-
-        valid_mask = None
-        if attention_mask is not None:
-            if attention_mask.ndim != 2 or attention_mask.shape[0] != batch:
-                raise ValueError("attention_mask must have shape [B,T]")
-            if attention_mask.shape[1] < length:
-                raise ValueError("attention_mask is shorter than the current input")
-            valid_mask = attention_mask[:, -length:].to(torch.bool)
-
-        reset_mask = kwargs.get("solvedelta_reset_mask")
-        cu_seqlens = kwargs.get("cu_seqlens")
-        if reset_mask is None and cu_seqlens is not None:
-            reset_mask = segment_reset_mask(hidden_states, cu_seqlens)
-        if reset_mask is not None:
-            if reset_mask.shape != (batch, length) or reset_mask.dtype != torch.bool:
-                raise ValueError("solvedelta_reset_mask must be bool [B,T]")
-            if initial_state is not None and cu_seqlens is not None:
-                reset_mask = reset_mask.clone()
-                reset_mask[0, 0] = False
-
-        cache_requested = bool(use_cache and past_key_values is not None)
-        result = self.mixer(hidden_states, initial_state=initial_state, valid_mask=valid_mask,
-                            reset_mask=reset_mask, return_final_state=cache_requested)
-        if cache_requested:
-            output, final_state = result
-            past_key_values.update(self.layer_idx, recurrent_state=tuple(final_state.operator),
-                                   conv_state=final_state.conv, offset=length)
-        else:
-            output = result
+        batch, length = hidden_states.shape[:2]
+        carried = None if past_key_values is None else past_key_values.layer_state(self.layer_idx)
+        keep_state = past_key_values is not None and bool(use_cache)
+        mixed = self.mixer(hidden_states, initial_state=carried,
+                           valid_mask=self._valid_tokens(attention_mask, batch, length),
+                           reset_mask=self._reset_tokens(hidden_states, carried is not None, kwargs),
+                           return_final_state=keep_state)
+        if not keep_state:
+            return mixed, past_key_values
+        output, after = mixed
+        past_key_values.update(self.layer_idx, recurrent_state=tuple(after.operator), conv_state=after.conv,
+                               offset=length)
         return output, past_key_values
 
 
@@ -209,38 +221,52 @@ class SolveDeltaBlock(nn.Module):
         return residual + hidden_states, past_key_values
 
 
-@dataclass
-class SolveDeltaModelOutput:
-    last_hidden_state: torch.Tensor
-    past_key_values: Optional[SolveDeltaCache] = None
-    hidden_states: Optional[Tuple[torch.Tensor, ...]] = None
+class SolveDeltaPreTrainedModel(PreTrainedModel):
+    """Hugging Face base of the two model classes (upstream: modeling_solvedelta.py:259-281): checkpoint
+    save / load, ``Auto*`` construction, dtype handling.  The three scalar parameter families of the mixer
+    stay FP32 whatever dtype a checkpoint is loaded in."""
+
+    config_class = SolveDeltaConfig
+    base_model_prefix = "model"
+    supports_gradient_checkpointing = False
+    _no_split_modules = ["SolveDeltaBlock"]
+    _keep_in_fp32_modules_strict = list(FP32_PARAMETERS)
+
+    def _init_weights(self, module: nn.Module) -> None:
+        # projections and embeddings: N(0, initializer_range); the mixer sets its own gate parameters when built
+        std = self.config.initializer_range
+        if isinstance(module, (nn.Linear, nn.Embedding)):
+            nn.init.normal_(module.weight, mean=0.0, std=std)
+        if isinstance(module, nn.Linear) and module.bias is not None:
+            nn.init.zeros_(module.bias)
+        if isinstance(module, nn.Embedding) and module.padding_idx is not None:
+            with torch.no_grad():
+                module.weight[module.padding_idx].zero_()
 
 
-@dataclass
-class SolveDeltaCausalLMOutput:
-    loss: Optional[torch.Tensor] = None
-    logits: Optional[torch.Tensor] = None
-    past_key_values: Optional[SolveDeltaCache] = None
-    hidden_states: Optional[Tuple[torch.Tensor, ...]] = None
-
-
-class SolveDeltaModel(nn.Module):
+class SolveDeltaModel(SolveDeltaPreTrainedModel):
     """Embedding, the stack of blocks, final norm (modeling_solvedelta.py:283-397)."""
 
     def __init__(self, config: SolveDeltaConfig) -> None:
-        super().__init__()
-        self.config = config
+        super().__init__(config)
         self.padding_idx = config.pad_token_id
         self.vocab_size = config.vocab_size
         self.embeddings = nn.Embedding(config.vocab_size, config.hidden_size, self.padding_idx)
         self.layers = nn.ModuleList(SolveDeltaBlock(config, i) for i in range(config.num_hidden_layers))
         self.norm = nn.RMSNorm(config.hidden_size, eps=config.norm_eps)
+        self.post_init()
+
+    def get_input_embeddings(self):
+        return self.embeddings
+
+    def set_input_embeddings(self, value):
+        self.embeddings = value
 
     def forward(self, input_ids: Optional[torch.Tensor] = None, attention_mask: Optional[torch.Tensor] = None,
                 inputs_embeds: Optional[torch.Tensor] = None,
                 past_key_values: Union[SolveDeltaCache, Sequence[Dict[str, Any]], None] = None,
                 use_cache: Optional[bool] = None, output_hidden_states: bool = False,
-                **kwargs) -> SolveDeltaModelOutput:
+                **kwargs) -> BaseModelOutputWithPast:
         if input_ids is not None and inputs_embeds is not None:
             raise ValueError("specify either input_ids or inputs_embeds, not both")
         if input_ids is None and inputs_embeds is None:
@@ -265,37 +291,25 @@ class SolveDeltaModel(nn.Module):
         hidden_states = self.norm(hidden_states)
         if output_hidden_states:
             collected += (hidden_states,)
-        return SolveDeltaModelOutput(hidden_states, past_key_values, collected)
+        return BaseModelOutputWithPast(last_hidden_state=hidden_states, past_key_values=past_key_values,
+                                       hidden_states=collected)
 
 
-class SolveDeltaForCausalLM(nn.Module):
+class SolveDeltaForCausalLM(SolveDeltaPreTrainedModel):
     """Language-model head, label shift and loss over ``SolveDeltaModel``
     (modeling_solvedelta.py:400-501).  ``prepare()`` puts a freshly built or loaded
     model into the layout the CUDA mixer wants: BF16 weights on the device, the three
     scalar parameter families of every mixer kept in FP32."""
 
     ignore_index = -100
+    _tied_weights_keys = {"lm_head.weight": "model.embeddings.weight"}
 
     def __init__(self, config: SolveDeltaConfig) -> None:
-        super().__init__()
-        self.config = config
+        super().__init__(config)
         self.model = SolveDeltaModel(config)
         self.vocab_size = config.vocab_size
         self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
-        self.apply(self._init_weights)
-        if config.tie_word_embeddings:
-            self.lm_head.weight = self.model.embeddings.weight
-
-    def _init_weights(self, module: nn.Module) -> None:
-        if isinstance(module, nn.Linear):
-            nn.init.normal_(module.weight, mean=0.0, std=self.config.initializer_range)
-            if module.bias is not None:
-                nn.init.zeros_(module.bias)
-        elif isinstance(module, nn.Embedding):
-            nn.init.normal_(module.weight, mean=0.0, std=self.config.initializer_range)
-            if module.padding_idx is not None:
-                with torch.no_grad():
-                    module.weight[module.padding_idx].zero_()
+        self.post_init()
 
     def prepare(self, device: Union[str, torch.device] = "cuda") -> "SolveDeltaForCausalLM":
         self.to(device)
@@ -310,12 +324,15 @@ class SolveDeltaForCausalLM(nn.Module):
     def get_output_embeddings(self):
         return self.lm_head
 
+    def set_output_embeddings(self, value):
+        self.lm_head = value
+
     def forward(self, input_ids: Optional[torch.Tensor] = None, attention_mask: Optional[torch.Tensor] = None,
                 inputs_embeds: Optional[torch.Tensor] = None,
                 past_key_values: Union[SolveDeltaCache, Sequence[Dict[str, Any]], None] = None,
                 labels: Optional[torch.Tensor] = None, use_cache: Optional[bool] = None,
                 output_hidden_states: bool = False, logits_to_keep: Optional[int] = 0,
-                **kwargs) -> SolveDeltaCausalLMOutput:
+                **kwargs) -> CausalLMOutputWithPast:
         outputs = self.model(input_ids=input_ids, attention_mask=attention_mask, inputs_embeds=inputs_embeds,
                              past_key_values=past_key_values, use_cache=use_cache,
                              output_hidden_states=output_hidden_states, **kwargs)
@@ -328,7 +345,8 @@ class SolveDeltaForCausalLM(nn.Module):
             shifted = torch.cat((labels[..., 1:], torch.full_like(labels[:, :1], self.ignore_index)), dim=1)
             loss = F.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), shifted.reshape(-1),
                                    ignore_index=self.ignore_index)
-        return SolveDeltaCausalLMOutput(loss, logits, outputs.past_key_values, outputs.hidden_states)
+        return CausalLMOutputWithPast(loss=loss, logits=logits, past_key_values=outputs.past_key_values,
+                                      hidden_states=outputs.hidden_states)
 
     @torch.no_grad()
     def generate(self, input_ids: torch.Tensor, max_new_tokens: int, graphed: bool = False) -> torch.Tensor:
@@ -411,6 +429,5 @@ class GraphedDecoder:
         return self.logits
 
 
-__all__ = ["GraphedDecoder", "SolveDeltaBlock", "SolveDeltaCache", "SolveDeltaCacheAdapter", "SolveDeltaCausalLMOutput",
-           "SolveDeltaForCausalLM", "SolveDeltaMLP", "SolveDeltaModel", "SolveDeltaModelOutput",
-           "segment_reset_mask"]
+__all__ = ["GraphedDecoder", "SolveDeltaBlock", "SolveDeltaCache", "SolveDeltaCacheAdapter", "SolveDeltaForCausalLM",
+           "SolveDeltaMLP", "SolveDeltaModel", "SolveDeltaPreTrainedModel", "segment_reset_mask"]
