@@ -129,8 +129,8 @@ int sd_decode_step(const sd_decode_args *args, void *stream);
  * fields `saved`, `saved_bytes`, `scratch`, `scratch_bytes` are ignored.
  *
  * Limit: sd_saved_bytes(shape) + sd_forward_scratch_bytes(shape) must not
- * exceed SD_STATIC_WORKSPACE_BYTES, i.e. about B*H*ceil(T/64) <= 70 chunk
- * tasks (for example B=1, H=8, T<=512).  Larger shapes are refused with
+ * exceed SD_STATIC_WORKSPACE_BYTES, i.e. B*H*ceil(T/64) <= 54 chunk tasks of
+ * about 600 KiB each (for example B=1, H=8, T<=384).  Larger shapes are refused with
  * SD_ERR_STATIC_WORKSPACE_EXCEEDED before anything is launched.
  *
  * The call itself never calls cudaMalloc, cudaFree or any allocating routine.

@@ -26,10 +26,11 @@ struct PanelDesc {
 };
 
 const PanelDesc kSaved[] = {{"Lam", 3}, {"G", 0}, {"Delta", 0}, {"Dprim", 0}, {"Zt", 4}, {"CtCk", 2}, {"CtCkB", 6}, {"SCk", 6},
-                            {"N", 1}, {"Aed", 1}, {"Aqd", 5}};
-const PanelDesc kFwd[] = {{"Upd", 0}, {"Qc", 0}, {"Ubar", 0}, {"Wd", 0}, {"Ud", 0}, {"Dt", 0}, {"Xg", 4}};
-const PanelDesc kBwd[] = {{"Pp", 4},     {"Qp", 4},     {"Ag", 4},     {"Xg", 4},     {"Dyf", 4},    {"Dcol", 4},
-                          {"Xr", 4},     {"Er", 4},     {"Chi", 4},    {"Ee", 4},     {"dR", 4},     {"dSeCk", 6},
+                            {"N", 1}, {"Aed", 1}, {"Aqd", 5},
+                            // BF16 source panels of the exterior, written once by the forward pass
+                            {"Xg", 4}, {"Ag", 4}, {"Xr", 4}, {"Er", 4}, {"Dcol", 4}, {"DtB", 4}, {"Chi", 4}, {"Ee", 4}};
+const PanelDesc kFwd[] = {{"Upd", 0}, {"Qc", 0}, {"Ubar", 0}, {"Wd", 0}, {"Ud", 0}, {"Dt", 0}};
+const PanelDesc kBwd[] = {{"Pp", 4},     {"Qp", 4},     {"Dyf", 4},    {"dR", 4},     {"dSeCk", 6},
                           {"SdS", 3},    {"duPart", 4}, {"dkPart", 4}, {"dGPart", 4}, {"dDelta", 4}, {"DG", 4},
                           {"Xext", 4},   {"Dd", 4},     {"Tu", 4},   {"Khat", 4},   {"Ppp", 4},    {"Qpp", 4},    {"Rneg", 4},
                           {"dRr", 4},    {"dCeCk", 6}};
@@ -423,7 +424,14 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
     p.Wd = panel_at(kFwd, s, a->scratch, "Wd");
     p.Ud = panel_at(kFwd, s, a->scratch, "Ud");
     p.Dt = panel_at(kFwd, s, a->scratch, "Dt");
-    p.Xg = bpanel_at(kFwd, s, a->scratch, "Xg");
+    p.Xg = bpanel_at(kSaved, s, a->saved, "Xg");
+    p.Ag = bpanel_at(kSaved, s, a->saved, "Ag");
+    p.Xr = bpanel_at(kSaved, s, a->saved, "Xr");
+    p.Er = bpanel_at(kSaved, s, a->saved, "Er");
+    p.Dcol = bpanel_at(kSaved, s, a->saved, "Dcol");
+    p.DtB = bpanel_at(kSaved, s, a->saved, "DtB");
+    p.Chi = bpanel_at(kSaved, s, a->saved, "Chi");
+    p.Ee = bpanel_at(kSaved, s, a->saved, "Ee");
     p.Aqd = bpanel_at(kSaved, s, a->saved, "Aqd");
     p.Npair = panel_at(kSaved, s, a->saved, "N");
     p.Aed = panel_at(kSaved, s, a->saved, "Aed");
@@ -522,8 +530,15 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
     p.Aqd = bpanel_at(kSaved, s, sv, "Aqd");
 #define SD_BP(field) p.field = panel_at(kBwd, s, a->scratch, #field)
 #define SD_BB(field) p.field = bpanel_at(kBwd, s, a->scratch, #field)
-    SD_BB(Pp); SD_BB(Qp); SD_BB(Ag); SD_BB(Xg); SD_BB(Dyf); SD_BB(Dcol); SD_BB(dR); SD_BB(dSeCk);
-    SD_BB(Xr); SD_BB(Er); SD_BB(Chi); SD_BB(Ee);
+    SD_BB(Pp); SD_BB(Qp); SD_BB(Dyf); SD_BB(dR); SD_BB(dSeCk);
+    p.Xg = bpanel_at(kSaved, s, sv, "Xg");
+    p.Ag = bpanel_at(kSaved, s, sv, "Ag");
+    p.Xr = bpanel_at(kSaved, s, sv, "Xr");
+    p.Er = bpanel_at(kSaved, s, sv, "Er");
+    p.Dcol = bpanel_at(kSaved, s, sv, "Dcol");
+    p.DtB = bpanel_at(kSaved, s, sv, "DtB");
+    p.Chi = bpanel_at(kSaved, s, sv, "Chi");
+    p.Ee = bpanel_at(kSaved, s, sv, "Ee");
     SD_BB(DG); SD_BB(Dd); SD_BB(Tu); SD_BB(Khat);
     SD_BB(Ppp); SD_BB(Qpp); SD_BB(Rneg); SD_BB(dRr); SD_BB(dCeCk);
     SD_BB(duPart); SD_BB(dkPart); SD_BB(dGPart); SD_BB(dDelta); SD_BB(Xext); SD_BP(SdS);

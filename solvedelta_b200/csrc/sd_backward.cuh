@@ -22,10 +22,12 @@ struct BwdParams {
     const float *Lam, *Gp, *Delta, *Dprim, *CtCk;
     const float *Npair, *Aed;   // pair matrices N and Aed of the forward pass, [CL][CL]
     const bf16 *Zt, *SCk, *CtCkB, *Aqd;
+    const bf16 *Ag, *Xg;           // -e exp(G), chi exp(G): R and R2 of the dS scan
+    const bf16 *Xr, *Er, *Dcol;    // block-centred chi rowG, -e rowG, d col (operands of the centred contractions)
+    const bf16 *DtB;               // d exp(GL - G)
+    const bf16 *Chi, *Ee;          // chi, -e themselves (diagonal blocks on the direct path; only written for those chunks)
     // backward scratch: BF16 contraction operands / scanned panels
-    bf16 *Pp, *Qp, *Ag, *Xg, *Dyf, *dR, *dSeCk;
-    bf16 *Xr, *Er, *Dcol;   // block-centred chi rowG, -e rowG, d col (operands of the centred contractions)
-    bf16 *Chi, *Ee;         // chi, -e themselves (diagonal blocks)
+    bf16 *Pp, *Qp, *Dyf, *dR, *dSeCk;
     bf16 *DG, *Dd, *Tu, *Khat;
     bf16 *Ppp, *Qpp, *Rneg, *dRr, *dCeCk;
     // partial cotangents (BF16: they are final up to gradient tolerance) and FP32 reductions
@@ -88,14 +90,15 @@ __device__ __forceinline__ void epi_store_bsm(float (&acc)[NTW][4], int r0, int 
 }
 
 // ---------------------------------------------------------------------------
-// Recompute chi and e; with Aqd and Aed of the forward pass solve the transposed system for
+// With Aqd, Aed and Dt = d exp(GL - G) of the forward pass solve the transposed system for
 //   P' = (I-Aed)^-T (Aqd^T dy),  Q' = (I-Aed)^-T Dt
-// so that the reverse S scan is dR = P' + Q' dS.  Leaves the block-centred panels the
-// next kernel contracts with, and chi / -e themselves for its diagonal blocks.
+// so that the reverse S scan is dR = P' + Q' dS.  Also leaves dy as a dense panel for the scan and the
+// next kernel.  (The source panels chi, e and their centred forms come from the forward pass.)
 constexpr size_t EXT_PREP_BWD_SMEM = 2 * BSLOT_BYTES + BMAT_BYTES + MAT_BYTES;
 
+// 61 KB of shared memory and few registers: two CTAs share an SM
 template <bool FAST, bool MASKED>
-__global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) {
+__global__ void __launch_bounds__(NTHREADS, 2) k_exterior_prep_bwd(BwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -104,71 +107,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) 
     bf16* b_aqd = b_dt + BSLOT_ELEMS;
     float* f_aedT = reinterpret_cast<float*>(b_aqd + BMAT_ELEMS);
     const ChunkT<MASKED> ch = chunk_of<MASKED>(p.g, blockIdx.x);
-    const int r = p.g.r, V = p.g.V;
-    const float* gG = panel_ptr(p.Gp, ch.gi);
-    const float* gd = panel_ptr(p.Dprim, ch.gi);
+    const int V = p.g.V;
     async_bmat(b_aqd, bmat_ptr(p.Aqd, ch.gi));
+    async_bpanel(b_dt, bpanel_ptr(p.DtB, ch.gi));
     cp_commit();
-    g2s_mat_transposed(f_aedT, mat_ptr(p.Aed, ch.gi), [](int) { return 1.f; });
     {
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
-        const float* gDelta = panel_ptr(p.Delta, ch.gi);
-        bf16* gAg = bpanel_ptr(p.Ag, ch.gi);
-        bf16* gXg = bpanel_ptr(p.Xg, ch.gi);
         bf16* gDyf = bpanel_ptr(p.Dyf, ch.gi);
-        bf16* gXr = bpanel_ptr(p.Xr, ch.gi);
-        bf16* gEr = bpanel_ptr(p.Er, ch.gi);
-        bf16* gDc = bpanel_ptr(p.Dcol, ch.gi);
-        bf16* gChi = bpanel_ptr(p.Chi, ch.gi);
-        bf16* gEe = bpanel_ptr(p.Ee, ch.gi);
-        float GL[8];
-        load8_panel(gG, CL - 1, c0, GL);
-#pragma unroll 1
+#pragma unroll
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
-            const int i = lr + ROWS_PER_PASS * pp, i0 = i & ~(BT - 1);
-            float uh[8], kh[8], qh[8], dl[8], d[8], er[8], dy[8], G[8], Gp[8], Ge[8], se[8];
-            load8_norm<FAST>(p.u, ch, i, c0, r, uh);
-            load8_norm<FAST>(p.k, ch, i, c0, r, kh);
-            load8_norm<FAST>(p.q, ch, i, c0, r, qh);
-            load8_panel(gDelta, i, c0, dl);
-            load8_panel(gd, i, c0, d);
-            load8_panel(gG, i, c0, G);
-            load8_panel(gG, i0 + BT - 1, c0, Ge);
-            load8_panel(gG, i0 ? i0 - 1 : 0, c0, Gp);
-            load8_bf16<FAST>(row_bf16(p.er, ch, i), c0, r, p.er.vec, ch.ok(i), er);
+            const int i = lr + ROWS_PER_PASS * pp;
+            float dy[8];
             load8_bf16<FAST>(row_bf16(p.dy, ch, i), c0, V, p.dy.vec, ch.ok(i), dy);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                se[e] = sigmoidf_(er[e]);
-                if (i0 == 0) Gp[e] = 0.f;
-            }
-            Sources src;
-            sources_fwd(uh, kh, qh, dl, se, src);
-            float xg[8], ag[8], xr[8], ern[8], dc[8], dt[8], chi[8], ee[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const float ep = __expf(G[e]), rw = __expf(G[e] - Gp[e]);
-                chi[e] = src.chi[e];
-                ee[e] = -src.e[e];
-                xg[e] = src.chi[e] * ep;
-                ag[e] = -src.e[e] * ep;
-                xr[e] = src.chi[e] * rw;
-                ern[e] = -src.e[e] * rw;
-                dc[e] = d[e] * __expf(Ge[e] - G[e]);
-                dt[e] = d[e] * __expf(GL[e] - G[e]);
-            }
             store8_bsm(b_dy, i, c0, dy);
-            store8_bsm(b_dt, i, c0, dt);
-            store8_bpanel(gAg, i, c0, ag);
-            store8_bpanel(gXg, i, c0, xg);
             store8_bpanel(gDyf, i, c0, dy);
-            store8_bpanel(gXr, i, c0, xr);
-            store8_bpanel(gEr, i, c0, ern);
-            store8_bpanel(gDc, i, c0, dc);
-            store8_bpanel(gChi, i, c0, chi);
-            store8_bpanel(gEe, i, c0, ee);
         }
     }
+    g2s_mat_transposed(f_aedT, mat_ptr(p.Aed, ch.gi), [](int) { return 1.f; });
     cp_wait<0>();
     __syncthreads();
     SD_PHASE(p.g, ph);
@@ -178,7 +133,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_bwd(BwdParams p) 
         const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
         warp_mma_bf16<NT128, true, false>(acc, b_aqd, LDM, b_dy, LDB, r0, n0, r0, CL);
         __syncthreads();
-    SD_PHASE(p.g, ph);
+        SD_PHASE(p.g, ph);
         warp_epi<NT128>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
             *reinterpret_cast<__nv_bfloat162*>(b_dy + i * LDB + j) = __floats2bfloat162_rn(v0, v1);
         });

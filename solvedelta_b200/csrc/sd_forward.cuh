@@ -14,8 +14,12 @@ struct FwdParams {
     Operand u, h, q, k, v, er, wr, ld, gam;
     // forward scratch
     float *Upd, *Qc, *Ubar, *Wd, *Ud, *Dt;
-    bf16 *Xg;        // operand of the output contraction only
+    bf16 *Xg;        // chi exp(G): operand of the output contraction, kept for backward (R2 of the dS scan)
     bf16 *Aqd;       // pair matrix of the output contraction, kept for backward
+    // BF16 panels of the per-token pass of k_exterior_prep_fwd that the reverse pass contracts with; kept so
+    // that it does not evaluate the sources a second time: -e exp(G), chi rowG, -e rowG, d col, d exp(GL-G),
+    // and (only for chunks with a block on the direct path) chi and -e themselves
+    bf16 *Ag, *Xr, *Er, *Dcol, *DtB, *Chi, *Ee;
     // kept for backward
     float *Lam, *Gp, *Delta, *Dprim, *CtCk;
     float *Npair, *Aed;  // pair matrices N = Lm / gamma and Aed, [CL][CL]
@@ -429,12 +433,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
             store8_smem(s_z, i, c0, z);
             store8_panel(gDt, i, c0, dt);
             store8_bpanel(gXg, i, c0, xg);
+            store8_bpanel(bpanel_ptr(p.Ag, ch.gi), i, c0, ag);
+            store8_bpanel(bpanel_ptr(p.Xr, ch.gi), i, c0, xr);
+            store8_bpanel(bpanel_ptr(p.Er, ch.gi), i, c0, ern);
+            store8_bpanel(bpanel_ptr(p.DtB, ch.gi), i, c0, dt);
             if (all_fast) {
                 float Ge[8], dc[8];
                 load8_smem(s_G, i0 + BT - 1, c0, Ge);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) dc[e] = d[e] * __expf(Ge[e] - G[e]);
                 store8_smem(s_d, i, c0, dc);
+                store8_bpanel(bpanel_ptr(p.Dcol, ch.gi), i, c0, dc);
+            } else {
+                store8_bpanel(bpanel_ptr(p.Chi, ch.gi), i, c0, a[0]);
+                store8_bpanel(bpanel_ptr(p.Ee, ch.gi), i, c0, a[1]);
             }
             // diagonal blocks that are not fast: exp(G_i - G_j) directly; both pairs share the exponentials
             if (!block_is_fast(s_fastw, i / BT)) {
@@ -459,6 +471,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
             d.x *= __expf(Ge.x - G.x); d.y *= __expf(Ge.y - G.y);
             d.z *= __expf(Ge.z - G.z); d.w *= __expf(Ge.w - G.w);
             *reinterpret_cast<float4*>(s_d + j * LDP + c4) = d;
+            bf16* gDc = bpanel_ptr(p.Dcol, ch.gi) + j * DP + c4;
+            *reinterpret_cast<__nv_bfloat162*>(gDc) = __floats2bfloat162_rn(d.x, d.y);
+            *reinterpret_cast<__nv_bfloat162*>(gDc + 2) = __floats2bfloat162_rn(d.z, d.w);
         }
         __syncthreads();
     }
