@@ -503,8 +503,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
 // Output rows: y = Xg S_c + tril(Aqd) Z~, BF16 operands (the result is BF16).
 constexpr size_t OUTPUT_FWD_SMEM = 2 * BSLOT_BYTES + BSTATE_BYTES + BMAT_BYTES;
 
+// 79 KB of shared memory: two CTAs share an SM (one loads while the other contracts)
 template <bool FAST, bool MASKED>
-__global__ void __launch_bounds__(NTHREADS, 1) k_output_fwd(FwdParams p) {
+__global__ void __launch_bounds__(NTHREADS, 2) k_output_fwd(FwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) unsigned char smem_raw[];
