@@ -288,13 +288,12 @@ _F, _B, _S, _T, _M, _P = 32 * KIB, 16 * KIB, 64 * KIB, 32 * KIB, 8 * KIB, 16 * K
 KERNEL_BYTES_PER_CHUNK = {
     "k_prep_fwd": 2 * _B + _F + 4 * _F + _P,                    # u,h,g -> Upd,Qc,Ubar,G,N
     "k_state_scan[C]": 4 * _F + _S + _T,                        # P,Q,R -> X, FP32 + BF16 ckpt
-    "k_primal_fwd": 2 * _B + 2 * _F + _S + _F,                  # u,k,G,Delta,Ct -> d
-    # 6 operands,G,Delta,d -> Wd,Ud,Dt,Xg,Aqd,Aed
-    "k_exterior_prep_fwd": 6 * _B + 3 * _F + 3 * _F + _B + _M + _P,
+    # u,k,q,er,wr,v,G,Delta,Ct -> d, Wd,Ud,Dt, Aqd,Aed, 7 BF16 source panels
+    "k_primal_exterior_fwd": 6 * _B + 2 * _F + _S + _F + 3 * _F + _M + _P + 7 * _B,
     "k_state_scan[S]": 3 * _F + _B + _T,                        # P,Q,R -> Z~ (BF16), BF16 ckpt
     "k_output_fwd": _B + _M + _B + _T + _B,                     # Xg,Aqd,Zt,S -> y
-    # u,k,q,er,dy,G,Delta,d,Aqd,Aed -> Ag,Xg,Dyf,Dcol,Xr,Er,Chi,Ee,Pp,Qp
-    "k_exterior_prep_bwd": 5 * _B + 3 * _F + _M + _P + 10 * _B,
+    # dy,DtB,Aqd,Aed -> Dyf,Pp,Qp
+    "k_exterior_prep_bwd": 2 * _B + _M + _P + 3 * _B,
     "k_state_scan_b[dS]": 6 * _B + _T,
     # Dyf,dR,Zt,Dcol,Xr,Er,Chi,Ee,S,dSe + u,k,q,er,wr,v,G,Delta,d -> 5 partial panels, DG,Dd, dq,der,dv,dwr
     "k_exterior_pair_bwd": 8 * _B + 2 * _T + 6 * _B + 3 * _F + 7 * _B + 4 * _B,

@@ -256,14 +256,10 @@ cudaError_t configure_kernels() {
     if ((e = allow_smem(k_prep_fwd<false, false>, PREP_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_prep_fwd<true, true>, PREP_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_prep_fwd<false, true>, PREP_FWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_primal_fwd<true, false>, PRIMAL_FWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_primal_fwd<false, false>, PRIMAL_FWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_primal_fwd<true, true>, PRIMAL_FWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_primal_fwd<false, true>, PRIMAL_FWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_exterior_prep_fwd<true, false>, EXT_PREP_FWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_exterior_prep_fwd<false, false>, EXT_PREP_FWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_exterior_prep_fwd<true, true>, EXT_PREP_FWD_SMEM)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_exterior_prep_fwd<false, true>, EXT_PREP_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_primal_exterior_fwd<true, false>, PRIMAL_EXT_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_primal_exterior_fwd<false, false>, PRIMAL_EXT_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_primal_exterior_fwd<true, true>, PRIMAL_EXT_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_primal_exterior_fwd<false, true>, PRIMAL_EXT_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_output_fwd<true, false>, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_output_fwd<false, false>, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_output_fwd<true, true>, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
@@ -312,7 +308,7 @@ inline void mark(cudaStream_t) {}
 
 #ifdef SD_DIAGNOSTICS
 const char* const kLaunchNames[] = {
-    "k_prep_fwd",          "k_state_scan[C]",     "k_primal_fwd",         "k_exterior_prep_fwd", "k_state_scan[S]",
+    "k_prep_fwd",          "k_state_scan[C]",     "k_primal_exterior_fwd", "k_state_scan[S]",
     "k_output_fwd",        "k_exterior_prep_bwd", "k_state_scan_b[dS]",   "k_exterior_pair_bwd",
     "k_primal_bwd",        "k_state_scan_b[dC]",  "k_predictor_close_bwd"};
 #endif
@@ -372,7 +368,7 @@ int sd_panel_kind(const sd_shape* shape, int which, const char* name) {
     return found ? kind : SD_ERR_INVALID_ARGUMENT;
 }
 
-int sd_forward_launches(const sd_shape* shape) { return shape_ok(shape) ? 6 : 0; }
+int sd_forward_launches(const sd_shape* shape) { return shape_ok(shape) ? 5 : 0; }
 int sd_backward_launches(const sd_shape* shape) { return shape_ok(shape) ? 6 : 0; }
 int sd_chunk_tokens(void) { return CL; }
 int sd_version(void) { return 1; }
@@ -465,10 +461,7 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
         mark(stream);
     }
     set_dbg(p.g, 2, chunks);
-    SD_LAUNCH_CHUNK(k_primal_fwd, PRIMAL_FWD_SMEM);
-    mark(stream);
-    set_dbg(p.g, 3, chunks);
-    SD_LAUNCH_CHUNK(k_exterior_prep_fwd, EXT_PREP_FWD_SMEM);
+    SD_LAUNCH_CHUNK(k_primal_exterior_fwd, PRIMAL_EXT_FWD_SMEM);
     mark(stream);
     {
         ScanParams sp{};
@@ -476,10 +469,10 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
         sp.lam = p.Lam; sp.X = nullptr; sp.ck = nullptr; sp.Xb = p.Zt; sp.ckb = p.SCk;
         sp.init = a->S0; sp.fin = a->S_T;
         sp.NC = p.g.NC; sp.reverse = 0; sp.transposed_io = 0; sp.nrows = s->r; sp.ncols = s->V;
-        if (!launch_scan_tc(sp, total_chunks(s), scan_grid, stream, scan_dbg(4))) return SD_ERR_LAUNCH_FAILED;
+        if (!launch_scan_tc(sp, total_chunks(s), scan_grid, stream, scan_dbg(3))) return SD_ERR_LAUNCH_FAILED;
         mark(stream);
     }
-    set_dbg(p.g, 5, chunks);
+    set_dbg(p.g, 4, chunks);
     SD_LAUNCH_CHUNK(k_output_fwd, OUTPUT_FWD_SMEM);
     mark(stream);
     return launch_status();
@@ -554,7 +547,7 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
     const bool fast = all_fast(bwd_ops, 9, *s);
     const bool masked = a->valid_mask != nullptr || a->reset_mask != nullptr;
 
-    set_dbg(p.g, 6, chunks);
+    set_dbg(p.g, 5, chunks);
     SD_LAUNCH_CHUNK(k_exterior_prep_bwd, EXT_PREP_BWD_SMEM);
     mark(stream);
     {
@@ -566,10 +559,10 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
         k_state_scan_b<<<scan_grid, SCAN_THREADS, SCAN_B_SMEM_BYTES, stream>>>(sp);
     mark(stream);
     }
-    set_dbg(p.g, 8, chunks);
+    set_dbg(p.g, 7, chunks);
     SD_LAUNCH_CHUNK(k_exterior_pair_bwd, EXT_PAIR_BWD_SMEM);
     mark(stream);
-    set_dbg(p.g, 9, chunks);
+    set_dbg(p.g, 8, chunks);
     SD_LAUNCH_CHUNK(k_primal_bwd, PRIMAL_BWD_SMEM);
     mark(stream);
     {
@@ -581,7 +574,7 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
         k_state_scan_b<<<scan_grid, SCAN_THREADS, SCAN_B_SMEM_BYTES, stream>>>(sp);
     mark(stream);
     }
-    set_dbg(p.g, 11, chunks);
+    set_dbg(p.g, 10, chunks);
     SD_LAUNCH_CHUNK(k_predictor_close_bwd, PRED_CLOSE_BWD_SMEM);
     mark(stream);
     return launch_status();
@@ -613,7 +606,7 @@ const char* sd_launch_name(int index) {
 
 int sd_profile_step(const sd_forward_args* fwd, const sd_backward_args* bwd, void* stream_, float* ms,
                     int capacity, int* count) {
-    if (!fwd || !ms || !count || capacity < 12) return SD_ERR_INVALID_ARGUMENT;
+    if (!fwd || !ms || !count || capacity < 11) return SD_ERR_INVALID_ARGUMENT;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     LaunchRecorder rec;
     rec.n = 0;

@@ -1,7 +1,6 @@
 // Chunk-parallel forward kernels: one CTA per (stream, chunk).
 //
-// Pipeline: k_prep_fwd -> scan(C) -> k_primal_fwd -> k_exterior_prep_fwd
-//           -> scan(S) -> k_output_fwd.
+// Pipeline: k_prep_fwd -> scan(C) -> k_primal_exterior_fwd -> scan(S) -> k_output_fwd.
 #pragma once
 #include "sd_bf16.cuh"
 #include "sd_common.cuh"
@@ -16,7 +15,7 @@ struct FwdParams {
     float *Upd, *Qc, *Ubar, *Wd, *Ud, *Dt;
     bf16 *Xg;        // chi exp(G): operand of the output contraction, kept for backward (R2 of the dS scan)
     bf16 *Aqd;       // pair matrix of the output contraction, kept for backward
-    // BF16 panels of the per-token pass of k_exterior_prep_fwd that the reverse pass contracts with; kept so
+    // BF16 panels of the per-token pass of k_primal_exterior_fwd that the reverse pass contracts with; kept so
     // that it does not evaluate the sources a second time: -e exp(G), chi rowG, -e rowG, d col, d exp(GL-G),
     // and (only for chunks with a block on the direct path) chi and -e themselves
     bf16 *Ag, *Xr, *Er, *Dcol, *DtB, *Chi, *Ee;
@@ -233,10 +232,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
 }
 
 // ---------------------------------------------------------------------------
-// Primal address d = k^ + C_t^T k^ for every token of the chunk:
+// Primal address and exterior preparation in one CTA per chunk task.
+// First half: d = k^ + C_t^T k^ for every token of the chunk,
 //   d_i = k^_i + exp(G_i) (K^ Ct^T)_i + sum_{j<=i} (k^_i . Delta_j) u^_j exp(G_i - G_j),
 // the decay-weighted sum in block-centred form (Horner over blocks, direct diagonal).
-constexpr size_t PRIMAL_FWD_SMEM = 6 * SLOT_BYTES + MAT_BYTES + (NBLK * DP + 16) * sizeof(float);
+// Second half, on d and the prefix panel still in shared memory: sources (e, chi, z), the pair matrices
+//   Aqd[i][j] = sum_c chi_ic d_jc exp(G_ic - G_jc) (j <= i),  Aed likewise with -e (j < i)
+// in block-centred form, and the solved panels Wd = (I-Aed)^-1 ag, Ud = (I-Aed)^-1 Z
+// for the S scan (ag = -e exp(G), referenced to the chunk start like the scan itself).
+constexpr size_t PRIMAL_EXT_FWD_SMEM = 6 * SLOT_BYTES + MAT_BYTES + (NBLK * DP + 3 * DP + NBLK * DP + 16) * sizeof(float);
+static_assert(PRIMAL_EXT_FWD_SMEM <= 227 * 1024, "fits the shared memory of one CTA");
+
 
 __device__ __forceinline__ void async_panel_f32(float* sm, const float* g) {
     for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += NTHREADS) {
@@ -252,7 +258,7 @@ __device__ __forceinline__ void async_state_cols_f32(float* sm, const float* st,
 }
 
 template <bool FAST, bool MASKED>
-__global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
+__global__ void __launch_bounds__(NTHREADS, 1) k_primal_exterior_fwd(FwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) float smem[];
@@ -262,9 +268,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
     float* s_dl = s_G + SLOT_FLOATS;
     float* s_st0 = s_dl + SLOT_FLOATS;
     float* s_st1 = s_st0 + SLOT_FLOATS;
-    float* s_aqk = s_st1 + SLOT_FLOATS;
+    float* s_aqk = s_st1 + SLOT_FLOATS;   // Aqk, later Aed
     float* s_beta = s_aqk + MAT_FLOATS;
-    int* s_fastw = reinterpret_cast<int*>(s_beta + NBLK * DP);
+    float* s_M = s_beta + NBLK * DP;
+    float* s_ibeta = s_M + 3 * DP;
+    int* s_fastw = reinterpret_cast<int*>(s_ibeta + NBLK * DP);
+    const int V = p.g.V;
     const ChunkT<MASKED> ch = chunk_of<MASKED>(p.g, blockIdx.x);
     const int r = p.g.r;
     const float* ct = state_ptr(p.CtCk, ch.gi);
@@ -283,7 +292,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
     __syncthreads();
     SD_PHASE(p.g, ph);
     auto fG = [&](int i, int c) { return s_G[i * LDP + c]; };
-    block_decay_tables(s_beta, nullptr, s_fastw, fG);
+    block_decay_tables(s_beta, s_ibeta, s_fastw, fG);
+    pair_block_scales(s_M, fG);
     {
         float acc[NT64][4];
         acc_zero<NT64>(acc);
@@ -333,6 +343,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
                     [&](int k, int n) { return s_un[k * LDP + n]; });
     }
     SD_PHASE(p.g, ph);
+    __syncthreads();   // every warp has read k^ as an operand: d takes its place for the exterior half below
     float* gd = panel_ptr(p.Dprim, ch.gi);
     const int ref = fast ? r0 + BT - 1 : r0 - 1;   // row whose prefix the accumulated sum is referenced to
     warp_epi<NT128>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
@@ -341,47 +352,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_fwd(FwdParams p) {
         float2 Gp = make_float2(0.f, 0.f), dg = make_float2(0.f, 0.f);
         if (ref >= 0) Gp = *reinterpret_cast<const float2*>(s_G + ref * LDP + j);
         if (!fast) dg = *reinterpret_cast<const float2*>(s_dl + i * LDP + j);
-        *reinterpret_cast<float2*>(gd + i * DP + j) =
-            make_float2(kh.x + __expf(G.x - Gp.x) * v0 + dg.x, kh.y + __expf(G.y - Gp.y) * v1 + dg.y);
+        const float2 d = make_float2(kh.x + __expf(G.x - Gp.x) * v0 + dg.x, kh.y + __expf(G.y - Gp.y) * v1 + dg.y);
+        *reinterpret_cast<float2*>(gd + i * DP + j) = d;
+        *reinterpret_cast<float2*>(s_kh + i * LDP + j) = d;
     });
+    __syncthreads();
     SD_PHASE(p.g, ph);
-}
-
-// ---------------------------------------------------------------------------
-// Exterior preparation: sources (e, chi, z), the pair matrices
-//   Aqd[i][j] = sum_c chi_ic d_jc exp(G_ic - G_jc) (j <= i),  Aed likewise with -e (j < i)
-// in block-centred form, and the solved panels Wd = (I-Aed)^-1 ag, Ud = (I-Aed)^-1 Z
-// for the S scan (ag = -e exp(G), referenced to the chunk start like the scan itself).
-constexpr size_t EXT_PREP_FWD_SMEM = 6 * SLOT_BYTES + MAT_BYTES + (3 * DP + NBLK * DP + 16) * sizeof(float);
-
-template <bool FAST, bool MASKED>
-__global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) {
-    int ph = 0;
-    SD_PHASE(p.g, ph);
-    extern __shared__ __align__(16) float smem[];
-    float* s_xr = smem;                  // chi rowG   (block-centred row operand)
-    float* s_er = s_xr + SLOT_FLOATS;    // -e rowG
-    float* s_d = s_er + SLOT_FLOATS;     // d itself for the diagonal rows, then the column operand d col
-    float* s_G = s_d + SLOT_FLOATS;      // chunk prefix of the log decay
-    float* s_ag = s_G + SLOT_FLOATS;     // -e exp(G)  -> Wd
-    float* s_z = s_ag + SLOT_FLOATS;     // z          -> Ud
-    float* s_aed = s_z + SLOT_FLOATS;
-    float* s_M = s_aed + MAT_FLOATS;
-    float* s_ibeta = s_M + 3 * DP;
-    int* s_fastw = reinterpret_cast<int*>(s_ibeta + NBLK * DP);
-    const ChunkT<MASKED> ch = chunk_of<MASKED>(p.g, blockIdx.x);
-    const int r = p.g.r, V = p.g.V;
+    // ---- exterior half: the slots of the primal half take the panels of the exterior preparation ----
+    float* s_xr = s_un;     // chi rowG   (block-centred row operand)
+    float* s_er = s_dl;     // -e rowG
+    float* s_d = s_kh;      // d itself for the diagonal rows, then the column operand d col
+    float* s_ag = s_st0;    // -e exp(G)  -> Wd
+    float* s_z = s_st1;     // z          -> Ud
+    float* s_aed = s_aqk;
     bf16* gAqd = bmat_ptr(p.Aqd, ch.gi);
     float* gAed = mat_ptr(p.Aed, ch.gi);
-    async_panel_f32(s_G, panel_ptr(p.Gp, ch.gi));
-    async_panel_f32(s_d, panel_ptr(p.Dprim, ch.gi));
-    cp_commit();
-    cp_wait<0>();
-    __syncthreads();
-    SD_PHASE(p.g, ph);
-    pair_block_scales(s_M, [&](int i, int c) { return s_G[i * LDP + c]; });
-    block_decay_tables(nullptr, s_ibeta, s_fastw, [&](int i, int c) { return s_G[i * LDP + c]; });
-    __syncthreads();
     // with no block left to the direct evaluation nobody needs d itself: each row is centred as it is read
     const bool all_fast = block_is_fast(s_fastw, 0) && block_is_fast(s_fastw, 1) && block_is_fast(s_fastw, 2) &&
                           block_is_fast(s_fastw, 3);
@@ -498,6 +483,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_prep_fwd(FwdParams p) 
     s2g_panel(panel_ptr(p.Ud, ch.gi), s_z);
     SD_PHASE(p.g, ph);
 }
+
 
 // ---------------------------------------------------------------------------
 // Output rows: y = Xg S_c + tril(Aqd) Z~, BF16 operands (the result is BF16).
