@@ -268,7 +268,9 @@ __device__ __forceinline__ void trisolve_blocked(float* Mr, float sgn, Panel P) 
     __syncthreads();
     // ---- warp-local sweep over this warp's 16 columns ---------------------------------
     const int n0 = 16 * warp;
-#pragma unroll 1
+    // fully unrolled: every bound below is a compile-time constant, so the operand loads of a block run ahead
+    // of the contractions that use them
+#pragma unroll
     for (int step = 0; step < NB; ++step) {
         const int I = UPPER ? (NB - 1 - step) : step;
         const int r0 = 16 * I;
@@ -285,6 +287,7 @@ __device__ __forceinline__ void trisolve_blocked(float* Mr, float sgn, Panel P) 
             const int kend = UPPER ? CL : 16 * I;
             float acc[2][4];
             acc_zero<2>(acc);
+#pragma unroll
             for (int kk = kbeg; kk < kend; kk += 8) {
                 float af[4] = {Mr[(r0 + g) * LDA + kk + t], Mr[(r0 + g + 8) * LDA + kk + t],
                                Mr[(r0 + g) * LDA + kk + t + 4], Mr[(r0 + g + 8) * LDA + kk + t + 4]};
