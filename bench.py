@@ -344,12 +344,22 @@ def summarize_ncu(csv_path, tasks):
         unit = row.get("Metric Unit", "")
         scale = {"Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9, "byte": 1.0}.get(unit, 1.0)
         per_launch[key][row["Metric Name"]] = val * scale
+    def short(full):
+        return full.split("(")[0].replace("void ", "").split("<")[0].replace("sd::", "")
+
+    # the last complete step of the capture: k_prep_fwd ... k_predictor_close_bwd, 11 launches
+    names = [short(per_launch[k]["name"]) for k in order]
+    starts = [i for i, n in enumerate(names) if n == "k_prep_fwd" and i + 11 <= len(names)
+              and names[i + 10] == "k_predictor_close_bwd"]
+    if not starts:
+        raise SystemExit("no complete fwd+bwd step (11 launches) in the capture")
+    order = order[starts[-1]:starts[-1] + 11]
     scans = iter(("k_state_scan[C]", "k_state_scan[S]"))
     scans_b = iter(("k_state_scan_b[dS]", "k_state_scan_b[dC]"))
     print("# kernel  KiB-per-chunk-task (DRAM read + write, ncu)  time-us")
     for key in order:
         m = per_launch[key]
-        name = m["name"].split("(")[0].replace("void ", "").split("<")[0].replace("sd::", "")
+        name = short(m["name"])
         if name == "k_state_scan_tc":
             name = next(scans)
         elif name == "k_state_scan_b":
