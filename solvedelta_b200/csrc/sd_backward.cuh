@@ -167,38 +167,48 @@ __device__ __forceinline__ void sources_bwd_rows(const BwdParams& p, const CH& c
 #pragma unroll 1
     for (int pp = 0; pp < ROW_PASSES; ++pp) {
         const int i = lr + ROWS_PER_PASS * pp;
-        float uh[8], kh[8], qh[8], dl[8], d[8], er[8], G[8], se[8];
+        // the part that does not involve the sources first, stored at once (keeps the live set small)
+        float dd[8], xext[8];
+        {
+            float G[8], d[8], py[8], ddt[8], dg_[8];
+            load8_panel(gG, i, c0, G);
+            load8_panel(gd, i, c0, d);
+            load8_bsm(sPY, i, c0, py);
+            load8_bsm(sdDt, i, c0, ddt);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float ep = __expf(G[e]), et = __expf(GL[e] - G[e]);
+                dd[e] = py[e] + et * ddt[e];
+                xext[e] = ddt[e] * d[e] * et;
+                dg_[e] = dd[e] * ep;
+            }
+            store8_bpanel(bpanel_ptr(p.DG, ch.gi), i, c0, dg_);
+            store8_bpanel(bpanel_ptr(p.Dd, ch.gi), i, c0, dd);
+            store8_bpanel(bpanel_ptr(p.Xext, ch.gi), i, c0, xext);
+        }
+        float uh[8], kh[8], qh[8], dl[8], se[8];
         load8_norm<FAST>(p.u, ch, i, c0, r, uh);
         load8_norm<FAST>(p.k, ch, i, c0, r, kh);
         const float rstd_q = load8_norm<FAST>(p.q, ch, i, c0, r, qh);
         load8_panel(gDelta, i, c0, dl);
-        load8_panel(gd, i, c0, d);
-        load8_panel(gG, i, c0, G);
-        load8_bf16<FAST>(row_bf16(p.er, ch, i), c0, r, p.er.vec, ch.ok(i), er);
+        load8_bf16<FAST>(row_bf16(p.er, ch, i), c0, r, p.er.vec, ch.ok(i), se);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) se[e] = sigmoidf_(er[e]);
+        for (int e = 0; e < 8; ++e) se[e] = sigmoidf_(se[e]);
         Sources src;
         sources_fwd(uh, kh, qh, dl, se, src);
-        float a1[8], a2[8], py[8], ddt[8];
-        load8_bsm(sA1, i, c0, a1);
-        load8_bsm(sA2, i, c0, a2);
-        load8_bsm(sPY, i, c0, py);
-        load8_bsm(sdDt, i, c0, ddt);
-        float dchi[8], de[8], dd[8], dG[8], xext[8], dg_[8];
+        float dchi[8], de[8], dG[8];
+        load8_bsm(sA1, i, c0, dchi);
+        load8_bsm(sA2, i, c0, de);
         float dsb = 0.f, dsq = 0.f;
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-            float ep = __expf(G[e]), et = __expf(GL[e] - G[e]);
-            dchi[e] = a1[e];
-            de[e] = -a2[e];
-            dd[e] = py[e] + et * ddt[e];
-            float dt = d[e] * et;
-            dG[e] = src.chi[e] * dchi[e] + src.e[e] * de[e] - d[e] * py[e] + dd[e] * (d[e] - kh[e]);
-            xext[e] = ddt[e] * dt;
-            dg_[e] = dd[e] * ep;
+            de[e] = -de[e];
+            // d(-d py + dd (d - k^)) with dd - py = exp(GL - G) dDt: the d terms collapse into xext
+            dG[e] = src.chi[e] * dchi[e] + src.e[e] * de[e] + xext[e] - dd[e] * kh[e];
             dsb = fmaf(-de[e], src.phi[e], dsb);
             dsq = fmaf(-dchi[e], src.phi[e], dsq);
         }
+        store8_bpanel(bpanel_ptr(p.dGPart, ch.gi), i, c0, dG);
         dsb = row_sum16(dsb);
         dsq = row_sum16(dsq);
         const float inv_den = 1.f / src.den;
@@ -228,11 +238,7 @@ __device__ __forceinline__ void sources_bwd_rows(const BwdParams& p, const CH& c
         store8_bf16<FAST>(p.der, p.g, ch, i, c0, r, der);
         store8_bpanel(bpanel_ptr(p.duPart, ch.gi), i, c0, duh);
         store8_bpanel(bpanel_ptr(p.dkPart, ch.gi), i, c0, dkp);
-        store8_bpanel(bpanel_ptr(p.dGPart, ch.gi), i, c0, dG);
         store8_bpanel(bpanel_ptr(p.dDelta, ch.gi), i, c0, ddl);
-        store8_bpanel(bpanel_ptr(p.DG, ch.gi), i, c0, dg_);
-        store8_bpanel(bpanel_ptr(p.Dd, ch.gi), i, c0, dd);
-        store8_bpanel(bpanel_ptr(p.Xext, ch.gi), i, c0, xext);
     }
     // value side: dv = sigmoid(write) dR, d write_raw = dR v sigmoid'(write)
 #pragma unroll
