@@ -197,6 +197,12 @@ typedef struct {
     const void *initial_state;     /* BF16 [B][D][3] or NULL (= zeros) */
     void *y;                       /* out BF16 [B,T,D] contiguous */
     void *final_state;             /* out BF16 [B][D][3] or NULL */
+    /* one byte per (batch, token), either may be NULL: an invalid token gives zero output and
+     * leaves the window untouched, a reset on a valid token empties the window first
+     * (the masked loop of causallsso/model.py:146-164; upstream's CUDA branch repacks the
+     * batch into segments instead, model.py:166-273) */
+    const unsigned char *valid_mask;
+    const unsigned char *reset_mask;
 } sd_conv4_forward_args;
 
 typedef struct {
@@ -211,6 +217,8 @@ typedef struct {
     void *dinitial_state;          /* out BF16 [B][D][3] or NULL */
     void *scratch;                 /* sd_conv4_backward_scratch_bytes */
     size_t scratch_bytes;
+    const unsigned char *valid_mask;   /* as in the forward call */
+    const unsigned char *reset_mask;
 } sd_conv4_backward_args;
 
 size_t sd_conv4_backward_scratch_bytes(int32_t B, int32_t T, int32_t D);

@@ -18,6 +18,7 @@ from .packing import PackedSegments, build_packed_segments, pack_tokens, unpack_
 from .ops import (
     SolveDeltaState,
     solvedelta_native,
+    solvedelta_masked_native,
     solvedelta_segmented_native,
     solvedelta_residual_frame_native,
     solvedelta_zero_state,
@@ -56,6 +57,7 @@ __all__ = [
     "build",
     "load",
     "solvedelta_native",
+    "solvedelta_masked_native",
     "solvedelta_segmented_native",
     "solvedelta_residual_frame_native",
     "PackedSegments",

@@ -117,7 +117,7 @@ class Conv4ForwardArgs(ctypes.Structure):
     _fields_ = [("B", ctypes.c_int32), ("T", ctypes.c_int32), ("D", ctypes.c_int32),
                 ("x", ctypes.c_void_p), ("x_stride_b", ctypes.c_int64), ("x_stride_t", ctypes.c_int64),
                 ("weight", ctypes.c_void_p), ("initial_state", ctypes.c_void_p), ("y", ctypes.c_void_p),
-                ("final_state", ctypes.c_void_p)]
+                ("final_state", ctypes.c_void_p), ("valid_mask", ctypes.c_void_p), ("reset_mask", ctypes.c_void_p)]
 
 
 class Conv4BackwardArgs(ctypes.Structure):
@@ -125,7 +125,8 @@ class Conv4BackwardArgs(ctypes.Structure):
                 ("x", ctypes.c_void_p), ("x_stride_b", ctypes.c_int64), ("x_stride_t", ctypes.c_int64),
                 ("weight", ctypes.c_void_p), ("initial_state", ctypes.c_void_p), ("dy", ctypes.c_void_p),
                 ("dx", ctypes.c_void_p), ("dweight", ctypes.c_void_p), ("dinitial_state", ctypes.c_void_p),
-                ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t)]
+                ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t),
+                ("valid_mask", ctypes.c_void_p), ("reset_mask", ctypes.c_void_p)]
 
 
 class KdaGateArgs(ctypes.Structure):

@@ -697,11 +697,17 @@ int sd_conv4_silu_forward(const sd_conv4_forward_args* a, void* stream_) {
     p.init = reinterpret_cast<const __nv_bfloat16*>(a->initial_state);
     p.y = reinterpret_cast<__nv_bfloat16*>(a->y);
     p.fin = reinterpret_cast<__nv_bfloat16*>(a->final_state);
+    p.valid = a->valid_mask; p.reset = a->reset_mask;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     dim3 grid((a->D + 2 * CONV_THREADS - 1) / (2 * CONV_THREADS), conv_tiles(a->T), a->B);
-    if (conv_pairs_ok(p))
-        k_conv4_silu_fwd<true><<<grid, CONV_THREADS, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
-    else
-        k_conv4_silu_fwd<false><<<grid, CONV_THREADS, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
+    const bool masked = p.valid != nullptr || p.reset != nullptr;
+    if (conv_pairs_ok(p)) {
+        if (masked) k_conv4_silu_fwd_masked<true><<<grid, CONV_THREADS, 0, stream>>>(p);
+        else k_conv4_silu_fwd<true><<<grid, CONV_THREADS, 0, stream>>>(p);
+    } else {
+        if (masked) k_conv4_silu_fwd_masked<false><<<grid, CONV_THREADS, 0, stream>>>(p);
+        else k_conv4_silu_fwd<false><<<grid, CONV_THREADS, 0, stream>>>(p);
+    }
     return launch_status();
 }
 
@@ -721,12 +727,17 @@ int sd_conv4_silu_backward(const sd_conv4_backward_args* a, void* stream_) {
     p.dx = reinterpret_cast<__nv_bfloat16*>(a->dx);
     p.dinit = reinterpret_cast<__nv_bfloat16*>(a->dinitial_state);
     p.dw_part = reinterpret_cast<float*>(a->scratch);
+    p.valid = a->valid_mask; p.reset = a->reset_mask;
     const int tiles = conv_tiles(a->T);
     dim3 grid((a->D + 2 * CONV_THREADS - 1) / (2 * CONV_THREADS), tiles, a->B);
-    if (conv_pairs_ok(p))
-        k_conv4_silu_bwd<true><<<grid, CONV_THREADS, 0, stream>>>(p);
-    else
-        k_conv4_silu_bwd<false><<<grid, CONV_THREADS, 0, stream>>>(p);
+    const bool masked = p.valid != nullptr || p.reset != nullptr;
+    if (conv_pairs_ok(p)) {
+        if (masked) k_conv4_silu_bwd_masked<true><<<grid, CONV_THREADS, 0, stream>>>(p);
+        else k_conv4_silu_bwd<true><<<grid, CONV_THREADS, 0, stream>>>(p);
+    } else {
+        if (masked) k_conv4_silu_bwd_masked<false><<<grid, CONV_THREADS, 0, stream>>>(p);
+        else k_conv4_silu_bwd<false><<<grid, CONV_THREADS, 0, stream>>>(p);
+    }
     const long long n = (long long)a->D * 4;
     k_column_sum<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p.dw_part, a->B * tiles, n, a->dweight);
     return launch_status();

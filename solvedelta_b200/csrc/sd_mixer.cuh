@@ -27,6 +27,9 @@ struct ConvParams {
     __nv_bfloat16* dx;           // [B,T,D] contiguous
     __nv_bfloat16* dinit;        // [B][D][3] or null
     float* dw_part;              // [B * tiles][D][4]
+    // masks, one byte per (batch, token), either may be null (all valid / no reset)
+    const unsigned char* valid;
+    const unsigned char* reset;
 };
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + __expf(-z)); }
@@ -183,6 +186,159 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv4_silu_bwd(ConvParams p) {
             }
         }
     }
+    float* part = p.dw_part + ((long long)(b * gridDim.y + blockIdx.y) * p.D + d) * 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        part[j] = dwa[j];
+        if (two) part[4 + j] = dwb[j];
+    }
+}
+
+// ---- masked variants --------------------------------------------------------
+// The masked token loop of causallsso/model.py:146-164 without repacking: an invalid token
+// gives zero output and leaves the window untouched, a reset (on a valid token) empties the
+// window first, so the three taps before a token are the last three valid inputs since the
+// last reset (the carried state, oldest slots first, where the row has fewer).  The mask
+// bytes of a tile are the same for every thread of a CTA, so all walks are uniform.
+__device__ __forceinline__ bool conv_valid(const ConvParams& p, int b, int t) {
+    return p.valid == nullptr || p.valid[(long long)b * p.T + t] != 0;
+}
+__device__ __forceinline__ bool conv_reset(const ConvParams& p, int b, int t) {
+    return p.reset != nullptr && p.reset[(long long)b * p.T + t] != 0;
+}
+constexpr int CONV_NONE = -100;  // "no token" in a window slot
+
+// Times (>= 0: tokens, -3..-1: slots of the carried state) of the three inputs before t0,
+// newest first; CONV_NONE where a reset cut the window.
+__device__ __forceinline__ void conv_window_before(const ConvParams& p, int b, int t0, int (&q)[3]) {
+    int cnt = 0;
+    bool cut = false;
+    q[0] = q[1] = q[2] = CONV_NONE;
+    for (int t = t0 - 1; t >= 0 && cnt < 3; --t) {
+        if (!conv_valid(p, b, t)) continue;
+        q[cnt++] = t;
+        if (conv_reset(p, b, t)) {
+            cut = true;
+            break;
+        }
+    }
+    if (!cut)
+        for (int v = -1; cnt < 3; --v) q[cnt++] = v;
+}
+__device__ __forceinline__ float2 conv_input_at(const ConvParams& p, int b, int t, int d, bool two) {
+    return t == CONV_NONE ? make_float2(0.f, 0.f) : conv_input(p, b, t, d, two);
+}
+
+template <bool PAIR>
+__global__ void __launch_bounds__(CONV_THREADS) k_conv4_silu_fwd_masked(ConvParams p) {
+    const int d = (blockIdx.x * CONV_THREADS + threadIdx.x) * 2;
+    const int t0 = blockIdx.y * CONV_TT, b = blockIdx.z;
+    if (d >= p.D) return;
+    const bool two = d + 1 < p.D;
+    float wa[4], wb[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        wa[j] = p.w[d * 4 + j];
+        wb[j] = two ? p.w[(d + 1) * 4 + j] : 0.f;
+    }
+    int q[3];
+    conv_window_before(p, b, t0, q);
+    float2 x0 = conv_input_at(p, b, q[2], d, two), x1 = conv_input_at(p, b, q[1], d, two),
+           x2 = conv_input_at(p, b, q[0], d, two);
+    const int t1 = min(t0 + CONV_TT, p.T);
+    const __nv_bfloat16* xin = p.x + b * p.sb + d;
+    __nv_bfloat16* yout = p.y + (long long)b * p.T * p.D + d;
+    for (int t = t0; t < t1; ++t) {
+        if (!conv_valid(p, b, t)) {
+            store_pair<PAIR>(yout + (long long)t * p.D, two, 0.f, 0.f);
+            continue;
+        }
+        if (conv_reset(p, b, t)) x0 = x1 = x2 = make_float2(0.f, 0.f);
+        const float2 x3 = load_pair<PAIR>(xin + (long long)t * p.st, two);
+        const float za = wa[0] * x0.x + wa[1] * x1.x + wa[2] * x2.x + wa[3] * x3.x;
+        const float zb = wb[0] * x0.y + wb[1] * x1.y + wb[2] * x2.y + wb[3] * x3.y;
+        store_pair<PAIR>(yout + (long long)t * p.D, two, silu_f(za), silu_f(zb));
+        x0 = x1; x1 = x2; x2 = x3;
+    }
+    if (p.fin != nullptr && t1 == p.T) {
+        __nv_bfloat16* s = p.fin + ((long long)b * p.D + d) * 3;
+        s[0] = __float2bfloat16_rn(x0.x); s[1] = __float2bfloat16_rn(x1.x); s[2] = __float2bfloat16_rn(x2.x);
+        if (two) {
+            s[3] = __float2bfloat16_rn(x0.y); s[4] = __float2bfloat16_rn(x1.y); s[5] = __float2bfloat16_rn(x2.y);
+        }
+    }
+}
+
+// Reverse of the masked loop.  Walking forward in time, the last three valid inputs are "pending":
+// their gradients still collect terms from later tokens.  An input is complete when three valid
+// tokens followed it, when a reset arrives, or at the end of the sequence.  A tile emits the
+// gradients of its own tokens (and tile 0 those of the carried state), so it walks past its end
+// until none of its own inputs is pending; weight gradients come from its own tokens only.
+template <bool PAIR>
+__global__ void __launch_bounds__(CONV_THREADS) k_conv4_silu_bwd_masked(ConvParams p) {
+    const int d = (blockIdx.x * CONV_THREADS + threadIdx.x) * 2;
+    const int t0 = blockIdx.y * CONV_TT, b = blockIdx.z;
+    if (d >= p.D) return;
+    const bool two = d + 1 < p.D;
+    float wa[4], wb[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        wa[j] = p.w[d * 4 + j];
+        wb[j] = two ? p.w[(d + 1) * 4 + j] : 0.f;
+    }
+    const int t_end = min(t0 + CONV_TT, p.T);
+    const __nv_bfloat16* xin = p.x + b * p.sb + d;
+    const __nv_bfloat16* gin = p.dy + (long long)b * p.T * p.D + d;
+    __nv_bfloat16* dxout = p.dx + (long long)b * p.T * p.D + d;
+    auto own = [&](int t) { return (t >= t0 && t < t_end) || (t < 0 && t >= -3 && t0 == 0 && p.dinit != nullptr); };
+    auto emit = [&](int t, float2 a) {
+        if (!own(t)) return;
+        if (t >= 0) {
+            store_pair<PAIR>(dxout + (long long)t * p.D, two, a.x, a.y);
+        } else {
+            __nv_bfloat16* s = p.dinit + ((long long)b * p.D + d) * 3 + (t + 3);
+            s[0] = __float2bfloat16_rn(a.x);
+            if (two) s[3] = __float2bfloat16_rn(a.y);
+        }
+    };
+    int q[3];
+    conv_window_before(p, b, t0, q);
+    float2 x0 = conv_input_at(p, b, q[2], d, two), x1 = conv_input_at(p, b, q[1], d, two),
+           x2 = conv_input_at(p, b, q[0], d, two);
+    int i0 = q[2], i1 = q[1], i2 = q[0];  // pending inputs, oldest first (only own ones are ever emitted)
+    float2 a0 = make_float2(0.f, 0.f), a1 = a0, a2 = a0;
+    float dwa[4] = {0.f, 0.f, 0.f, 0.f}, dwb[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int t = t0; t < p.T; ++t) {
+        if (t >= t_end && !own(i0) && !own(i1) && !own(i2)) break;
+        if (!conv_valid(p, b, t)) {
+            if (t < t_end) store_pair<PAIR>(dxout + (long long)t * p.D, two, 0.f, 0.f);
+            continue;
+        }
+        if (conv_reset(p, b, t)) {
+            emit(i0, a0); emit(i1, a1); emit(i2, a2);
+            i0 = i1 = i2 = CONV_NONE;
+            x0 = x1 = x2 = make_float2(0.f, 0.f);
+        }
+        const float2 x3 = load_pair<PAIR>(xin + (long long)t * p.st, two);
+        const float2 gy = load_pair<PAIR>(gin + (long long)t * p.D, two);
+        const float za = wa[0] * x0.x + wa[1] * x1.x + wa[2] * x2.x + wa[3] * x3.x;
+        const float zb = wb[0] * x0.y + wb[1] * x1.y + wb[2] * x2.y + wb[3] * x3.y;
+        const float2 g = make_float2(gy.x * silu_grad_f(za), gy.y * silu_grad_f(zb));
+        if (t < t_end) {
+            dwa[0] += g.x * x0.x; dwa[1] += g.x * x1.x; dwa[2] += g.x * x2.x; dwa[3] += g.x * x3.x;
+            dwb[0] += g.y * x0.y; dwb[1] += g.y * x1.y; dwb[2] += g.y * x2.y; dwb[3] += g.y * x3.y;
+        }
+        a0.x += wa[0] * g.x; a0.y += wb[0] * g.y;
+        a1.x += wa[1] * g.x; a1.y += wb[1] * g.y;
+        a2.x += wa[2] * g.x; a2.y += wb[2] * g.y;
+        emit(i0, a0);
+        a0 = a1; i0 = i1;
+        a1 = a2; i1 = i2;
+        a2 = make_float2(wa[3] * g.x, wb[3] * g.y); i2 = t;
+        x0 = x1; x1 = x2; x2 = x3;
+    }
+    // whatever is still pending saw the end of the sequence (entries that are not this tile's are skipped)
+    emit(i0, a0); emit(i1, a1); emit(i2, a2);
     float* part = p.dw_part + ((long long)(b * gridDim.y + blockIdx.y) * p.D + d) * 4;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {

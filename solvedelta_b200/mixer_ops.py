@@ -30,7 +30,7 @@ def _require_bf16_cuda(name, t):
 
 class _Conv4Silu(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, initial_state, want_state):
+    def forward(ctx, x, weight, initial_state, want_state, valid=None, reset=None):
         lib = _lib.load()
         B, T, D = x.shape
         w32 = weight.detach().float().contiguous()
@@ -40,9 +40,12 @@ class _Conv4Silu(torch.autograd.Function):
             fin = torch.empty(B, D, 3, dtype=torch.bfloat16, device=x.device) if want_state else None
             a = _lib.Conv4ForwardArgs(B, T, D, x.data_ptr(), x.stride(0), x.stride(1), w32.data_ptr(),
                                       None if init is None else init.data_ptr(), y.data_ptr(),
-                                      None if fin is None else fin.data_ptr())
+                                      None if fin is None else fin.data_ptr(),
+                                      None if valid is None else valid.data_ptr(),
+                                      None if reset is None else reset.data_ptr())
             _lib.check(lib.sd_conv4_silu_forward(ctypes.byref(a), _stream(x.device)))
         ctx.save_for_backward(x, w32, init if init is not None else x.new_empty(0))
+        ctx.masks = (valid, reset)
         ctx.has_init = init is not None
         ctx.weight_dtype = weight.dtype
         ctx.set_materialize_grads(False)
@@ -56,8 +59,10 @@ class _Conv4Silu(torch.autograd.Function):
         x, w32, init = ctx.saved_tensors
         B, T, D = x.shape
         if dy is None:
-            return torch.zeros_like(x), torch.zeros(D, 4, dtype=ctx.weight_dtype, device=x.device), None, None
+            return (torch.zeros_like(x), torch.zeros(D, 4, dtype=ctx.weight_dtype, device=x.device), None, None,
+                    None, None)
         dy = dy.to(torch.bfloat16).contiguous()
+        valid, reset = ctx.masks
         with torch.cuda.device(x.device):
             dx = torch.empty(B, T, D, dtype=torch.bfloat16, device=x.device)
             dw = torch.empty(D, 4, dtype=torch.float32, device=x.device)
@@ -66,15 +71,36 @@ class _Conv4Silu(torch.autograd.Function):
             a = _lib.Conv4BackwardArgs(B, T, D, x.data_ptr(), x.stride(0), x.stride(1), w32.data_ptr(),
                                        init.data_ptr() if ctx.has_init else None, dy.data_ptr(), dx.data_ptr(),
                                        dw.data_ptr(), None if dinit is None else dinit.data_ptr(),
-                                       scratch.data_ptr(), scratch.numel())
+                                       scratch.data_ptr(), scratch.numel(),
+                                       None if valid is None else valid.data_ptr(),
+                                       None if reset is None else reset.data_ptr())
             _lib.check(lib.sd_conv4_silu_backward(ctypes.byref(a), _stream(x.device)))
-        return dx, dw.to(ctx.weight_dtype), dinit, None
+        return dx, dw.to(ctx.weight_dtype), dinit, None, None, None
+
+
+def _conv_mask(name: str, mask: Optional[torch.Tensor], x: torch.Tensor) -> Optional[torch.Tensor]:
+    """bool [B,T] on the activation device -> its bytes as uint8 (no copy when contiguous)."""
+    if mask is None:
+        return None
+    if mask.dtype != torch.bool or mask.shape != x.shape[:2]:
+        raise ValueError(f"{name} must be bool [B,T]")
+    if mask.device != x.device:
+        raise ValueError("masks must share the activation device")
+    return mask.contiguous().view(torch.uint8)
 
 
 def conv4_silu(x: torch.Tensor, weight: torch.Tensor, initial_state: Optional[torch.Tensor] = None,
-               return_final_state: bool = False) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+               return_final_state: bool = False, valid_mask: Optional[torch.Tensor] = None,
+               reset_mask: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """Depthwise causal conv (4 taps, tap 3 = current token) + SiLU over [B,T,D] BF16 rows
-    (any batch/token strides, unit channel stride) with a carried [B,D,3] state."""
+    (any batch/token strides, unit channel stride) with a carried [B,D,3] state.
+
+    With masks (bool [B,T]) it is the masked token loop of causallsso/model.py:146-164, run inside
+    the kernel on the padded batch: an invalid token gives zero output and leaves the state
+    untouched, a reset on a valid token starts from the zero state, and the returned state of a
+    row holds its last three valid inputs since the last reset (older slots show the carried state
+    or zeros through).  No repacking and no host synchronisation (upstream's CUDA branch gathers
+    segments around causal_conv1d instead, model.py:166-273)."""
     _require_bf16_cuda("x", x)
     if x.ndim != 3 or x.stride(-1) != 1:
         raise ValueError("x must be [B,T,D] with unit channel stride")
@@ -82,56 +108,23 @@ def conv4_silu(x: torch.Tensor, weight: torch.Tensor, initial_state: Optional[to
         raise ValueError("conv weight must have shape [D,4]")
     if initial_state is not None and initial_state.shape != (x.shape[0], x.shape[2], 3):
         raise ValueError("conv initial state must have shape [B,D,3]")
-    return _Conv4Silu.apply(x, weight, initial_state, return_final_state)
+    valid, reset = _conv_mask("valid_mask", valid_mask, x), _conv_mask("reset_mask", reset_mask, x)
+    if x.shape[1] == 0:
+        fin = None
+        if return_final_state:
+            fin = (initial_state.to(torch.bfloat16) if initial_state is not None
+                   else x.new_zeros(x.shape[0], x.shape[2], 3))
+        return x.new_zeros(x.shape), fin
+    return _Conv4Silu.apply(x, weight, initial_state, return_final_state, valid, reset)
 
 
 def conv4_silu_segmented(x: torch.Tensor, weight: torch.Tensor, plan, initial_state: Optional[torch.Tensor] = None,
                          return_final_state: bool = False) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
-    """Masked / reset batches: the conv of causallsso/model.py:146-164 with masks, run as one batch
-    of reset-free segments (plan from ``build_packed_segments``).  Invalid tokens give zero output and
-    leave the state untouched, a reset token starts from the zero state, the first segment of a batch
-    row continues ``initial_state`` unless it opens with a reset; the returned state of a row holds its
-    last three valid inputs since the last reset (older slots show the carried state or zeros through).
-    Host-side index plumbing around ``conv4_silu`` (upstream does the same around causal_conv1d,
-    model.py:166-273)."""
-    from .packing import pack_tokens, unpack_tokens
-
-    _require_bf16_cuda("x", x)
-    batch, length, channels = x.shape
-    if (plan.batch, plan.length) != (batch, length):
+    """``conv4_silu`` with the masks of a segment plan from ``build_packed_segments`` (the plan is only
+    checked against the input; the kernel works on the padded batch in place)."""
+    if (plan.batch, plan.length) != tuple(x.shape[:2]):
         raise ValueError("packed segment plan does not match the conv input")
-    if initial_state is not None and initial_state.shape != (batch, channels, 3):
-        raise ValueError("conv initial state must have shape [B,D,3]")
-    if plan.num_tokens == 0:
-        output = x.new_zeros(batch, length, channels)
-        if not return_final_state:
-            return output, None
-        return output, (initial_state if initial_state is not None else x.new_zeros(batch, channels, 3))
-    padded = plan.max_seqlen
-    position = torch.arange(plan.num_tokens, dtype=torch.long, device=x.device) - plan.cu_seqlens[plan.segment_ids]
-    destination = plan.segment_ids * padded + position
-    tokens = pack_tokens(x, plan).squeeze(0)
-    rows = tokens.new_zeros(plan.num_segments * padded, channels).index_copy(0, destination, tokens)
-    rows = rows.view(plan.num_segments, padded, channels)
-    segment_initial = None
-    if initial_state is not None:
-        carried = initial_state.to(torch.bfloat16).index_select(0, plan.segment_batch)
-        segment_initial = torch.where(plan.use_initial[:, None, None], carried, torch.zeros_like(carried))
-    segment_out, _ = conv4_silu(rows, weight, segment_initial, False)
-    flat = segment_out.reshape(plan.num_segments * padded, channels)
-    output = unpack_tokens(flat.index_select(0, destination).unsqueeze(0), plan)
-    if not return_final_state:
-        return output, None
-    with torch.no_grad():
-        # state of a segment = the three inputs before position len in [carried state | segment tokens]
-        start = segment_initial if segment_initial is not None else rows.new_zeros(plan.num_segments, channels, 3)
-        extended = torch.cat((start.transpose(1, 2), rows.detach()), dim=1)            # [S, 3 + padded, D]
-        take = plan.segment_lengths.long()[:, None] + torch.arange(3, device=x.device)[None, :]
-        final = extended.gather(1, take[:, :, None].expand(-1, -1, channels)).transpose(1, 2)  # [S, D, 3]
-        chosen = final.index_select(0, plan.last_segment.clamp_min(0))
-        base = initial_state.to(torch.bfloat16) if initial_state is not None else torch.zeros_like(chosen)
-        state = torch.where((plan.last_segment >= 0)[:, None, None], chosen, base).contiguous()
-    return output, state
+    return conv4_silu(x, weight, initial_state, return_final_state, plan.valid_mask, plan.reset_mask)
 
 
 class _KdaGate(torch.autograd.Function):

@@ -24,9 +24,8 @@ import torch.nn.functional as F
 from torch import nn
 
 from .config import SolveDeltaConfig
-from .mixer_ops import conv4_silu, conv4_silu_segmented, kda_decay_gate, rms_norm_gated
-from .ops import SolveDeltaState, solvedelta_native, solvedelta_segmented_native
-from .packing import build_packed_segments
+from .mixer_ops import conv4_silu, kda_decay_gate, rms_norm_gated
+from .ops import SolveDeltaState, solvedelta_masked_native, solvedelta_native
 
 
 class SolveDeltaLayerState(NamedTuple):
@@ -130,16 +129,17 @@ class SolveDelta(nn.Module):
             raise ValueError("hidden state width does not match the configuration")
         if hidden_states.device.type != "cuda" or hidden_states.dtype != torch.bfloat16:
             raise TypeError("the B200 mixer requires BF16 CUDA hidden states (no CPU path)")
-        packed_segments = None
-        if valid_mask is not None or reset_mask is not None:
-            # masked / reset batches run as reset-free segments (causallsso/model.py:302-316)
-            if valid_mask is None:
-                valid_mask = torch.ones(batch, length, dtype=torch.bool, device=hidden_states.device)
-            if reset_mask is None:
-                reset_mask = torch.zeros(batch, length, dtype=torch.bool, device=hidden_states.device)
-            if valid_mask.device != hidden_states.device or reset_mask.device != hidden_states.device:
-                raise ValueError("masks must share the activation device")
-            packed_segments = build_packed_segments(valid_mask, reset_mask)
+        masked = valid_mask is not None or reset_mask is not None
+        if masked:
+            # masks and resets are applied inside the conv and operator kernels on the padded batch: no segment
+            # plan, no host synchronisation (upstream repacks into reset-free segments, causallsso/model.py:302-316)
+            for name, mask in (("valid_mask", valid_mask), ("reset_mask", reset_mask)):
+                if mask is None:
+                    continue
+                if mask.dtype != torch.bool or mask.shape != (batch, length):
+                    raise ValueError(f"{name} must be bool [B,T]")
+                if mask.device != hidden_states.device:
+                    raise ValueError("masks must share the activation device")
         heads = self.config.num_heads
         width = self.config.resolved_head_k_dim
         value_width = self.config.resolved_head_v_dim
@@ -155,11 +155,8 @@ class SolveDelta(nn.Module):
             pieces = _SplitRow.apply(row, tuple(sizes))
         piece = lambda i: pieces[i]
         if self.config.use_short_conv:
-            if packed_segments is None:
-                qkv, final_conv = conv4_silu(qkv_in, self.conv_weight, conv_state, return_final_state)
-            else:
-                qkv, final_conv = conv4_silu_segmented(qkv_in, self.conv_weight, packed_segments,
-                                                       conv_state, return_final_state)
+            qkv, final_conv = conv4_silu(qkv_in, self.conv_weight, conv_state, return_final_state,
+                                         valid_mask, reset_mask)
             q_raw, key_raw, value_raw = qkv.split(sizes[:3], dim=-1)
         else:
             q_raw, key_raw, value_raw = (F.silu(piece(i)) for i in range(3))
@@ -180,13 +177,14 @@ class SolveDelta(nn.Module):
         if not associative_decay_enabled:
             log_decay = torch.zeros_like(log_decay)
         operator_initial = initial_state.operator if initial_state is not None else None
-        if packed_segments is None:
+        if not masked:
             output, operator_state = solvedelta_native(
                 u, h, q, keys, values, log_decay, erase_raw, write_raw, geometry_write,
                 initial_state=operator_initial, return_final_state=return_final_state)
         else:
-            output, operator_state = solvedelta_segmented_native(
-                u, h, q, keys, values, log_decay, erase_raw, write_raw, geometry_write, packed_segments,
+            output, operator_state = solvedelta_masked_native(
+                u, h, q, keys, values, log_decay, erase_raw, write_raw, geometry_write,
+                valid_mask=valid_mask, reset_mask=reset_mask,
                 initial_state=operator_initial, return_final_state=return_final_state)
         normed = self.output_norm(output, output_gate)
         result = self._linear(self.output_proj, normed.reshape(batch, length, heads * value_width))

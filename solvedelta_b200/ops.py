@@ -347,9 +347,44 @@ def solvedelta_segmented_native(
         _valid_mask=plan.valid_mask, _reset_mask=plan.reset_mask)
 
 
+def solvedelta_masked_native(
+    u: torch.Tensor,
+    h: torch.Tensor,
+    q: torch.Tensor,
+    keys: torch.Tensor,
+    values: torch.Tensor,
+    associative_log_decay: torch.Tensor,
+    erase_raw: torch.Tensor,
+    write_raw: torch.Tensor,
+    geometry_write: torch.Tensor,
+    *,
+    valid_mask: Optional[torch.Tensor] = None,
+    reset_mask: Optional[torch.Tensor] = None,
+    initial_state: Optional[SolveDeltaState] = None,
+    return_final_state: bool = False,
+) -> Tuple[torch.Tensor, Optional[SolveDeltaState]]:
+    """``solvedelta_segmented_native`` without the plan: the two bool ``[B,T]`` token masks of the
+    token loop (causallsso/reference.py:157-164,216-226) go straight to the kernels.  No upstream
+    counterpart (upstream needs the plan to gather segments); it exists so that a caller with
+    device-side masks never synchronises with the host."""
+    batch, length = u.shape[:2]
+    for name, mask in (("valid_mask", valid_mask), ("reset_mask", reset_mask)):
+        if mask is None:
+            continue
+        if mask.dtype != torch.bool or mask.shape != (batch, length):
+            raise ValueError(f"{name} must be bool [B,T]")
+        if mask.device != u.device:
+            raise ValueError("masks must share the operand device")
+    return solvedelta_residual_frame_native(
+        u, h, q, keys, values, associative_log_decay, erase_raw, write_raw, geometry_write,
+        initial_state=initial_state, return_final_state=return_final_state,
+        _valid_mask=valid_mask, _reset_mask=reset_mask)
+
+
 __all__ = [
     "SolveDeltaState",
     "solvedelta_native",
+    "solvedelta_masked_native",
     "solvedelta_segmented_native",
     "solvedelta_residual_frame_native",
     "solvedelta_zero_state",

@@ -38,8 +38,8 @@ def test_struct_sizes_match_header():
     assert ctypes.sizeof(_lib.BackwardArgs) == 24 + 10 * 32 + 2 * 8 + 4 * 8 + 11 * 8 + 2 * 8
     assert ctypes.sizeof(_lib.DecodeArgs) == 24 + 9 * 32 + 3 * 8
     # mixer glue: three int32 (padded to 16) + pointers / strides / sizes of 8 bytes each
-    assert ctypes.sizeof(_lib.Conv4ForwardArgs) == 16 + 7 * 8
-    assert ctypes.sizeof(_lib.Conv4BackwardArgs) == 16 + 11 * 8
+    assert ctypes.sizeof(_lib.Conv4ForwardArgs) == 16 + 9 * 8
+    assert ctypes.sizeof(_lib.Conv4BackwardArgs) == 16 + 13 * 8
     assert ctypes.sizeof(_lib.KdaGateArgs) == 16 + 10 * 8
     assert ctypes.sizeof(_lib.NormGateArgs) == 16 + 10 * 8
 

@@ -61,6 +61,65 @@ def test_conv4_silu_matches_checker(B, T, D, stateful):
         assert max_rel(_np(sg.grad), dso) <= TOL
 
 
+def _conv_masks(B, T, kind, gen):
+    valid = torch.ones(B, T, dtype=torch.bool)
+    reset = torch.zeros(B, T, dtype=torch.bool)
+    if kind == "left_padding":           # rows open with runs of padding longer than a tile
+        for b in range(B):
+            valid[b, :min(T - 1, 70 + 9 * b)] = False
+        reset[:, 1] = True               # a reset on a padded token is ignored
+    elif kind == "sparse":               # few valid tokens, far apart: windows reach across tiles
+        valid[:] = torch.rand(B, T, generator=gen) < 0.04
+        reset[:] = torch.rand(B, T, generator=gen) < 0.01
+    elif kind == "mixed":
+        valid[:] = torch.rand(B, T, generator=gen) < 0.8
+        reset[:] = torch.rand(B, T, generator=gen) < 0.05
+        valid[0, :] = False              # a row without valid tokens keeps its state
+        reset[1, 0] = True
+        valid[1, 0] = True
+        if B > 2:
+            valid[2, -5:] = False
+    return valid, reset
+
+
+@pytest.mark.parametrize("B,T,D,stateful,kind", [(3, 200, 96, True, "left_padding"), (2, 300, 70, True, "sparse"),
+                                                 (3, 150, 328, True, "mixed"), (3, 131, 64, False, "mixed"),
+                                                 (2, 5, 32, True, "mixed")])
+def test_masked_conv4_silu_matches_checker(B, T, D, stateful, kind):
+    """Masks and resets inside the conv kernels (no repacking, no host synchronisation): output, final
+    state and all gradients against the masked token loop of the checker."""
+    gen = torch.Generator().manual_seed(B * 1000 + T)
+    valid, reset = _conv_masks(B, T, kind, gen)
+    wide = torch.randn(B, T, D + 24, generator=gen).to(torch.bfloat16)
+    w = (0.5 * torch.randn(D, 4, generator=gen)).float()
+    s0 = torch.randn(B, D, 3, generator=gen).to(torch.bfloat16) if stateful else None
+    dy = torch.randn(B, T, D, generator=gen).to(torch.bfloat16)
+    wide_g = wide.cuda().requires_grad_()
+    wg = w.cuda().requires_grad_()
+    sg = None if s0 is None else s0.cuda().requires_grad_()
+    valid_g, reset_g, dy_g = valid.cuda(), reset.cuda(), dy.cuda()
+    torch.cuda.synchronize()
+    torch.cuda.set_sync_debug_mode("error")
+    try:
+        y, fin = conv4_silu(wide_g[..., 8:8 + D], wg, sg, return_final_state=True, valid_mask=valid_g,
+                            reset_mask=reset_g)
+        (y.float() * dy_g.float()).sum().backward()
+    finally:
+        torch.cuda.set_sync_debug_mode("default")
+    yo, fo, saved = mo.conv4_silu_masked_forward(_np(wide[..., 8:8 + D]), _np(w), None if s0 is None else _np(s0),
+                                                 valid.numpy(), reset.numpy())
+    dxo, dwo, dso = mo.conv4_silu_masked_backward(np.where(valid.numpy()[..., None], _np(dy), 0.0), _np(w), saved)
+    assert max_rel(_np(y), yo) <= TOL
+    assert np.all(_np(y)[~valid.numpy()] == 0)
+    assert np.array_equal(_np(fin), fo)
+    dx = _np(wide_g.grad)[..., 8:8 + D]
+    assert max_rel(dx, dxo) <= TOL
+    assert np.all(dx[~valid.numpy()] == 0)
+    assert max_rel(_np(wg.grad), dwo) <= TOL
+    if stateful:
+        assert max_rel(_np(sg.grad), dso) <= TOL
+
+
 @pytest.mark.parametrize("shape", [(2, 19, 2, 16), (1, 130, 4, 64), (3, 64, 8, 128), (1, 70, 16, 128)])
 def test_kda_decay_gate_matches_checker(shape):
     gen = torch.Generator().manual_seed(sum(shape))
@@ -269,11 +328,17 @@ def test_mixer_module_masks_and_resets(monkeypatch):
     valid, reset = torch.as_tensor(g["valid_mask"]), torch.as_tensor(g["reset_mask"])
     xg = x.cuda().requires_grad_()
     c0g, s0g, cvg = C0.cuda().requires_grad_(), S0.cuda().requires_grad_(), conv0.cuda().requires_grad_()
-    out, fin = module(xg, initial_state=SolveDeltaLayerState(SolveDeltaState(c0g, s0g), cvg),
-                      valid_mask=valid.cuda(), reset_mask=reset.cuda(), return_final_state=True)
-    loss = ((out.float() * dout.cuda().float()).sum() + (fin.operator.predictor * dC.cuda()).sum()
-            + (fin.operator.S * dS.cuda()).sum())
-    loss.backward()
+    valid_g, reset_g, dout_g, dC_g, dS_g = valid.cuda(), reset.cuda(), dout.cuda(), dC.cuda(), dS.cuda()
+    torch.cuda.synchronize()
+    torch.cuda.set_sync_debug_mode("error")   # masks never leave the device: the masked mixer does not synchronise
+    try:
+        out, fin = module(xg, initial_state=SolveDeltaLayerState(SolveDeltaState(c0g, s0g), cvg),
+                          valid_mask=valid_g, reset_mask=reset_g, return_final_state=True)
+        loss = ((out.float() * dout_g.float()).sum() + (fin.operator.predictor * dC_g).sum()
+                + (fin.operator.S * dS_g).sum())
+        loss.backward()
+    finally:
+        torch.cuda.set_sync_debug_mode("default")
     oo, fo, conv_T = checker.forward(_np(x), conv_state=_np(conv0), operator_state=(_np(C0), _np(S0)),
                                      valid_mask=g["valid_mask"], reset_mask=g["reset_mask"])
     assert max_rel(_np(out), oo) <= TOL
