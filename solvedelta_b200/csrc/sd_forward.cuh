@@ -103,30 +103,35 @@ __device__ __forceinline__ void store8_smem(float* sm, int i, int c0, const floa
 // Predictor preparation: pair matrix Lm, and the two solved panels
 //   Upd = (I+Lm)^-1 (gamma h),  W = (I+Lm)^-1 (gamma U~)   (stored negated as Qc)
 // so that the C scan is  Delta = Upd + Qc Ct.
-constexpr size_t PREP_FWD_SMEM = 5 * SLOT_BYTES + MAT_BYTES + (CL + 3 * DP + NBLK * DP + 16) * sizeof(float);
+// Two FP32 panel slots only, so that two CTAs share an SM: slot A holds the prefix G, then the
+// row-centred u^ exp(E - Gprev), then gamma U~ / W; slot B holds u^, then the column-centred
+// u^ exp(Gend - G), then gamma h / Upd.  What later phases still need of G lives in two small
+// tables (the prefix just before and at the end of every block).
+constexpr size_t PREP_FWD_SMEM =
+    2 * SLOT_BYTES + MAT_BYTES + (CL + 3 * DP + NBLK * DP + 16 + 2 * NBLK * DP) * sizeof(float);
+static_assert(2 * (PREP_FWD_SMEM + 1024) <= 228 * 1024, "two CTAs of the predictor preparation per SM");
 
 template <bool FAST, bool MASKED>
-__global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
+__global__ void __launch_bounds__(NTHREADS, 2) k_prep_fwd(FwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
     extern __shared__ __align__(16) float smem[];
-    float* s_uh = smem;
-    float* s_G = s_uh + SLOT_FLOATS;
-    float* s_ut = s_G + SLOT_FLOATS;   // u^ rowE (block-centred), then gamma U~ / W
-    float* s_un = s_ut + SLOT_FLOATS;  // u^ col  (block-centred)
-    float* s_h = s_un + SLOT_FLOATS;
-    float* s_lm = s_h + SLOT_FLOATS;
+    float* s_A = smem;
+    float* s_B = s_A + SLOT_FLOATS;
+    float* s_lm = s_B + SLOT_FLOATS;
     float* s_gam = s_lm + MAT_FLOATS;
     float* s_M = s_gam + CL;
     float* s_ibeta = s_M + 3 * DP;
     int* s_fastw = reinterpret_cast<int*>(s_ibeta + NBLK * DP);
+    float* s_gp = reinterpret_cast<float*>(s_fastw + 16);   // [NBLK][DP] prefix just before the block
+    float* s_ge = s_gp + NBLK * DP;                         // [NBLK][DP] prefix at the end of the block
     const ChunkT<MASKED> ch = chunk_of<MASKED>(p.g, blockIdx.x);
     const int r = p.g.r;
 
-    load_norm_panel<FAST>(p.u, ch, r, s_uh, nullptr);
-    load_f32_panel<FAST>(p.ld, ch, r, s_G);
-    load_raw_panel<FAST>(p.h, ch, r, s_h);
+    load_norm_panel<FAST>(p.u, ch, r, s_B, nullptr);
+    load_f32_panel<FAST>(p.ld, ch, r, s_A);
     load_gamma(p.gam, ch, s_gam);
+    prefetch_rows(p.h, ch, 2, r * 2);   // read after the pair phase
     const bool any_reset = ch.reset_rows() != 0ull;
     if (any_reset) {   // block-uniform: a reset token forgets RESET_NATS more (each thread patches what it loaded)
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
@@ -135,99 +140,136 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prep_fwd(FwdParams p) {
             const int i = lr + ROWS_PER_PASS * pp;
             if (ch.rst(i)) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) s_G[i * LDP + c0 + e] -= RESET_NATS;
+                for (int e = 0; e < 8; ++e) s_A[i * LDP + c0 + e] -= RESET_NATS;
             }
         }
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
-    chunk_cumsum(s_G);
+    chunk_cumsum(s_A);
     __syncthreads();
     SD_PHASE(p.g, ph);
-    auto fG = [&](int i, int c) { return s_G[i * LDP + c]; };
+    auto fG = [&](int i, int c) { return s_A[i * LDP + c]; };
     pair_block_scales(s_M, fG);
     block_decay_tables(nullptr, s_ibeta, s_fastw, fG);
-    for (int idx = threadIdx.x; idx < CL * DP; idx += NTHREADS) {
-        int i = idx >> 7, c = idx & (DP - 1);
-        const int i0 = i & ~(BT - 1);
-        float G = s_G[i * LDP + c];
-        float E = i ? s_G[(i - 1) * LDP + c] : 0.f;
-        if (any_reset) E -= ch.eoff(i);   // block-uniform branch
-        float Gprev = i0 ? s_G[(i0 - 1) * LDP + c] : 0.f;
-        float Gend = s_G[(i0 + BT - 1) * LDP + c];
-        float uh = s_uh[i * LDP + c];
-        s_ut[i * LDP + c] = uh * __expf(E - Gprev);
-        s_un[i * LDP + c] = uh * __expf(Gend - G);
+    {
+        const int J = threadIdx.x >> 7, c = threadIdx.x & (DP - 1);
+        s_gp[threadIdx.x] = J ? fG(BT * J - 1, c) : 0.f;
+        s_ge[threadIdx.x] = fG(BT * J + BT - 1, c);
+    }
+    float* gG = panel_ptr(p.Gp, ch.gi);
+    for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += NTHREADS) {
+        const int i = idx >> 5, c4 = (idx & 31) << 2;
+        *reinterpret_cast<float4*>(gG + i * DP + c4) = *reinterpret_cast<const float4*>(s_A + i * LDP + c4);
     }
     __syncthreads();
-    SD_PHASE(p.g, ph);
-    // Lm = gamma stril(N), N[i][j] = sum_c u^_ic u^_jc exp(E_ic - G_jc); N itself is kept for backward
+    // Lm = gamma stril(N), N[i][j] = sum_c u^_ic u^_jc exp(E_ic - G_jc); N itself is kept for backward.
+    // Diagonal blocks that are not fast: direct evaluation, while u^ and G are still in the slots.
     float* gN = mat_ptr(p.Npair, ch.gi);
-    pair_blocks_tf32<true>(s_M, s_ibeta, s_fastw, [&](int i, int k) { return s_ut[i * LDP + k]; },
-                           [&](int j, int k) { return s_un[j * LDP + k]; },
-                           [&](int i, int j, float v0, float v1) {
-                               float gm = s_gam[i];
-                               *reinterpret_cast<float2*>(s_lm + i * LDA + j) = make_float2(gm * v0, gm * v1);
-                               *reinterpret_cast<float2*>(gN + i * CL + j) = make_float2(v0, v1);
-                           });
     {
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
 #pragma unroll 1
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
             const int i = balanced_row(lr, pp);
-            if (block_is_fast(s_fastw, i / BT)) continue;   // that diagonal block ran on the tensor cores
+            if (block_is_fast(s_fastw, i / BT)) continue;   // that diagonal block runs on the tensor cores
             float a[1][8], x[8], out[1];
-            load8_smem(s_uh, i, c0, a[0]);
+            load8_smem(s_B, i, c0, a[0]);
             if (i > 0) {
-                load8_smem(s_G, i - 1, c0, x);
+                load8_smem(s_A, i - 1, c0, x);
             } else {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) x[e] = 0.f;
             }
 #pragma unroll
             for (int e = 0; e < 8; ++e) x[e] -= ch.eoff(i);
-            pair_diag_row<1, true>(i, a, x, [&](int j, float (&b)[8]) { load8_smem(s_uh, j, c0, b); },
-                                   [&](int j, float (&G)[8]) { load8_smem(s_G, j, c0, G); }, out);
+            pair_diag_row<1, true>(i, a, x, [&](int j, float (&b)[8]) { load8_smem(s_B, j, c0, b); },
+                                   [&](int j, float (&G)[8]) { load8_smem(s_A, j, c0, G); }, out);
             const int j = (i & ~(BT - 1)) + (threadIdx.x & 15);
             s_lm[i * LDA + j] = s_gam[i] * out[0];
             gN[i * CL + j] = out[0];
         }
     }
-    __syncthreads();
-    SD_PHASE(p.g, ph);
-    for (int idx = threadIdx.x; idx < CL * DP; idx += NTHREADS) {
-        int i = idx >> 7, c = idx & (DP - 1);
-        float gm = s_gam[i];
-        float E = i ? s_G[(i - 1) * LDP + c] : 0.f;
-        if (any_reset) E -= ch.eoff(i);
-        s_h[i * LDP + c] *= gm;
-        s_ut[i * LDP + c] = gm * s_uh[i * LDP + c] * __expf(E);
+    {   // centred operands in place: every thread first reads what it needs of both slots, then all write
+        constexpr int PER = CL * DP / NTHREADS;
+        float ut[PER], un[PER];
+        const int c = threadIdx.x & (DP - 1), ib = threadIdx.x >> 7;
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const int i = ib + (NTHREADS / DP) * k, I = i / BT;
+            const float G = s_A[i * LDP + c];
+            float E = i ? s_A[(i - 1) * LDP + c] : 0.f;
+            if (any_reset) E -= ch.eoff(i);   // block-uniform branch
+            const float uh = s_B[i * LDP + c];
+            ut[k] = uh * __expf(E - s_gp[I * DP + c]);
+            un[k] = uh * __expf(s_ge[I * DP + c] - G);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const int i = ib + (NTHREADS / DP) * k;
+            s_A[i * LDP + c] = ut[k];
+            s_B[i * LDP + c] = un[k];
+        }
     }
     __syncthreads();
     SD_PHASE(p.g, ph);
-    trisolve_blocked<false, false>(s_lm, 1.f, PanelF32{s_h, s_ut});
+    pair_blocks_tf32<true>(s_M, s_ibeta, s_fastw, [&](int i, int k) { return s_A[i * LDP + k]; },
+                           [&](int j, int k) { return s_B[j * LDP + k]; },
+                           [&](int i, int j, float v0, float v1) {
+                               float gm = s_gam[i];
+                               *reinterpret_cast<float2*>(s_lm + i * LDA + j) = make_float2(gm * v0, gm * v1);
+                               *reinterpret_cast<float2*>(gN + i * CL + j) = make_float2(v0, v1);
+                           });
+    {   // Ubar = u^ exp(GL - G) = (column-centred u^) exp(GL - Gend), before slot B is reused
+        float* gUbar = panel_ptr(p.Ubar, ch.gi);
+        const float* GL = s_ge + (NBLK - 1) * DP;
+        for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += NTHREADS) {
+            const int i = idx >> 5, c4 = (idx & 31) << 2, I = i / BT;
+            const float4 un = *reinterpret_cast<const float4*>(s_B + i * LDP + c4);
+            const float4 ge = *reinterpret_cast<const float4*>(s_ge + I * DP + c4);
+            const float4 gl = *reinterpret_cast<const float4*>(GL + c4);
+            *reinterpret_cast<float4*>(gUbar + i * DP + c4) =
+                make_float4(un.x * __expf(gl.x - ge.x), un.y * __expf(gl.y - ge.y), un.z * __expf(gl.z - ge.z),
+                            un.w * __expf(gl.w - ge.w));
+        }
+    }
+    __syncthreads();
+    SD_PHASE(p.g, ph);
+    {   // right-hand sides: A = gamma u^ exp(E) (from the row-centred panel), B = gamma h
+        const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
+#pragma unroll
+        for (int pp = 0; pp < ROW_PASSES; ++pp) {
+            const int i = lr + ROWS_PER_PASS * pp, I = i / BT;
+            const float gm = s_gam[i];
+            float h[8], ut[8], gp[8];
+            load8_bf16<FAST>(row_bf16(p.h, ch, i), c0, r, p.h.vec, ch.ok(i), h);
+            load8_smem(s_A, i, c0, ut);
+            load8_panel(s_gp, I, c0, gp);   // the tables have pitch DP
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                h[e] *= gm;
+                ut[e] *= gm * __expf(gp[e]);
+            }
+            store8_smem(s_B, i, c0, h);
+            store8_smem(s_A, i, c0, ut);
+        }
+    }
+    __syncthreads();
+    SD_PHASE(p.g, ph);
+    trisolve_blocked<false, false>(s_lm, 1.f, PanelF32{s_B, s_A});
     SD_PHASE(p.g, ph);
     float* gUpd = panel_ptr(p.Upd, ch.gi);
     float* gQc = panel_ptr(p.Qc, ch.gi);
-    float* gUbar = panel_ptr(p.Ubar, ch.gi);
-    float* gG = panel_ptr(p.Gp, ch.gi);
     for (int idx = threadIdx.x; idx < CL * (DP / 4); idx += NTHREADS) {
         int i = idx >> 5, c4 = (idx & 31) << 2;
-        float4 up = *reinterpret_cast<const float4*>(s_h + i * LDP + c4);
-        float4 w = *reinterpret_cast<const float4*>(s_ut + i * LDP + c4);
-        float4 uh = *reinterpret_cast<const float4*>(s_uh + i * LDP + c4);
-        float4 G = *reinterpret_cast<const float4*>(s_G + i * LDP + c4);
-        float4 GL = *reinterpret_cast<const float4*>(s_G + (CL - 1) * LDP + c4);
+        float4 up = *reinterpret_cast<const float4*>(s_B + i * LDP + c4);
+        float4 w = *reinterpret_cast<const float4*>(s_A + i * LDP + c4);
         *reinterpret_cast<float4*>(gUpd + i * DP + c4) = up;
-        *reinterpret_cast<float4*>(gG + i * DP + c4) = G;
         // contraction operands of the state scan leave here already rounded to TF32
         *reinterpret_cast<float4*>(gQc + i * DP + c4) =
             make_float4(round_tf32(-w.x), round_tf32(-w.y), round_tf32(-w.z), round_tf32(-w.w));
-        *reinterpret_cast<float4*>(gUbar + i * DP + c4) =
-            make_float4(uh.x * __expf(GL.x - G.x), uh.y * __expf(GL.y - G.y), uh.z * __expf(GL.z - G.z),
-                        uh.w * __expf(GL.w - G.w));
     }
-    if (threadIdx.x < DP) p.Lam[ch.gi * DP + threadIdx.x] = __expf(s_G[(CL - 1) * LDP + threadIdx.x]);
+    if (threadIdx.x < DP) p.Lam[ch.gi * DP + threadIdx.x] = __expf(s_ge[(NBLK - 1) * DP + threadIdx.x]);
     SD_PHASE(p.g, ph);
 }
 
