@@ -8,7 +8,7 @@ sm_100a CUDA kernels behind a C ABI (include/solvedelta_b200.h).
 """
 from ._lib import build, load
 from .config import SolveDeltaConfig
-from .mixer_ops import conv4_silu, conv4_silu_segmented, kda_decay_gate, rms_norm_gated
+from .mixer_ops import conv4_silu, conv4_silu_segmented, kda_decay_gate, rms_norm_gated, rms_norm_gated_linear
 from .model import RMSNormGated, SolveDelta, SolveDeltaLayerState
 from .modeling import (GraphedDecoder, SolveDeltaBlock, SolveDeltaCache, SolveDeltaCacheAdapter, SolveDeltaForCausalLM,
                        SolveDeltaMLP, SolveDeltaModel, SolveDeltaPreTrainedModel)
@@ -53,6 +53,7 @@ __all__ = [
     "conv4_silu_segmented",
     "kda_decay_gate",
     "rms_norm_gated",
+    "rms_norm_gated_linear",
     "SolveDeltaState",
     "build",
     "load",

@@ -11,6 +11,7 @@ import ctypes
 from typing import Optional, Tuple
 
 import torch
+import torch.nn.functional as F
 
 from . import _lib
 
@@ -206,6 +207,75 @@ class _NormGate(torch.autograd.Function):
         return dx, dg, dw.to(ctx.weight_dtype), None
 
 
+def _norm_gate_forward(xc, gc, w, eps):
+    lib = _lib.load()
+    V = xc.shape[-1]
+    with torch.cuda.device(xc.device):
+        y = torch.empty(xc.shape, dtype=torch.bfloat16, device=xc.device)
+        a = _lib.NormGateArgs(xc.numel() // V, V, float(eps), xc.data_ptr(), gc.data_ptr(), w.data_ptr(), y.data_ptr())
+        _lib.check(lib.sd_norm_gate_forward(ctypes.byref(a), _stream(xc.device)))
+    return y
+
+
+class _NormGateLinear(torch.autograd.Function):
+    """Gated RMSNorm followed by a Linear over the flattened [H*D] rows, without keeping the normalised
+    panel for the reverse pass: it is produced again from x and gate there (one more pass of the norm
+    kernel instead of a saved [..., H*D] BF16 tensor per layer).  causallsso/ops/norm_gate.py:46-159."""
+
+    @staticmethod
+    def forward(ctx, x, gate, norm_weight, linear_weight, linear_bias, eps):
+        xc, gc = x.contiguous(), gate.contiguous()
+        w = norm_weight.detach().float().contiguous()
+        y = _norm_gate_forward(xc, gc, w, eps)
+        packed_weight = linear_weight.detach().to(torch.bfloat16)
+        packed_bias = None if linear_bias is None else linear_bias.detach().to(torch.bfloat16)
+        out = F.linear(y.reshape(*x.shape[:-2], -1), packed_weight, packed_bias)
+        ctx.save_for_backward(xc, gc, w, packed_weight)
+        ctx.eps = float(eps)
+        ctx.dtypes = (norm_weight.dtype, linear_weight.dtype, None if linear_bias is None else linear_bias.dtype)
+        ctx.set_materialize_grads(False)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        if dout is None:
+            return (None,) * 6
+        lib = _lib.load()
+        xc, gc, w, packed_weight = ctx.saved_tensors
+        V = xc.shape[-1]
+        rows = xc.numel() // V
+        dout2 = dout.to(torch.bfloat16).reshape(-1, dout.shape[-1])
+        y = _norm_gate_forward(xc, gc, w, ctx.eps)           # regenerated, not saved
+        dlinear = torch.mm(dout2.t(), y.reshape(dout2.shape[0], -1))
+        dy = torch.mm(dout2, packed_weight).reshape(xc.shape).contiguous()
+        del y
+        with torch.cuda.device(xc.device):
+            dx, dg = torch.empty_like(xc), torch.empty_like(gc)
+            dw = torch.empty(V, dtype=torch.float32, device=xc.device)
+            scratch = _scratch(lib.sd_norm_gate_backward_scratch_bytes(rows, V), xc.device)
+            a = _lib.NormGateArgs(rows, V, ctx.eps, xc.data_ptr(), gc.data_ptr(), w.data_ptr(), None, dy.data_ptr(),
+                                  dx.data_ptr(), dg.data_ptr(), dw.data_ptr(), scratch.data_ptr(), scratch.numel())
+            _lib.check(lib.sd_norm_gate_backward(ctypes.byref(a), _stream(xc.device)))
+        norm_dtype, weight_dtype, bias_dtype = ctx.dtypes
+        dbias = None if bias_dtype is None else dout2.float().sum(dim=0).to(bias_dtype)
+        return dx, dg, dw.to(norm_dtype), dlinear.to(weight_dtype), dbias, None
+
+
+def rms_norm_gated_linear(x: torch.Tensor, gate: torch.Tensor, norm_weight: torch.Tensor, linear_weight: torch.Tensor,
+                          linear_bias: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    """``F.linear(rms_norm_gated(x, gate, norm_weight, eps).flatten(-2), linear_weight, linear_bias)`` in BF16,
+    with the normalised panel recomputed in the reverse pass (upstream ``RMSNormGated.forward_linear``)."""
+    _require_bf16_cuda("x", x)
+    _require_bf16_cuda("gate", gate)
+    if x.shape != gate.shape or x.ndim < 2:
+        raise ValueError("x and gate must have the same [...,H,D] shape")
+    if norm_weight.shape != (x.shape[-1],):
+        raise ValueError("weight must have shape [D]")
+    if linear_weight.ndim != 2 or linear_weight.shape[1] != x.shape[-2] * x.shape[-1]:
+        raise ValueError("the linear layer must take the flattened [H*D] rows")
+    return _NormGateLinear.apply(x, gate, norm_weight, linear_weight, linear_bias, eps)
+
+
 def rms_norm_gated(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     """y = x * rsqrt(mean(x^2) + eps) * weight * sigmoid(gate) over the last axis (<= 128)."""
     _require_bf16_cuda("x", x)
@@ -217,4 +287,4 @@ def rms_norm_gated(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, ep
     return _NormGate.apply(x, gate, weight, eps)
 
 
-__all__ = ["conv4_silu", "conv4_silu_segmented", "kda_decay_gate", "rms_norm_gated"]
+__all__ = ["conv4_silu", "conv4_silu_segmented", "kda_decay_gate", "rms_norm_gated", "rms_norm_gated_linear"]

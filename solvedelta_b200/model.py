@@ -24,7 +24,7 @@ import torch.nn.functional as F
 from torch import nn
 
 from .config import SolveDeltaConfig
-from .mixer_ops import conv4_silu, kda_decay_gate, rms_norm_gated
+from .mixer_ops import conv4_silu, kda_decay_gate, rms_norm_gated, rms_norm_gated_linear
 from .ops import SolveDeltaState, solvedelta_masked_native, solvedelta_native
 
 
@@ -78,6 +78,10 @@ class RMSNormGated(nn.Module):
 
     def forward(self, x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
         return rms_norm_gated(x, gate, self.weight, self.eps)
+
+    def forward_linear(self, x: torch.Tensor, gate: torch.Tensor, linear: nn.Linear) -> torch.Tensor:
+        """The following projection without saving the normalised panel (norm_gate.py:195-217)."""
+        return rms_norm_gated_linear(x, gate, self.weight, linear.weight, linear.bias, self.eps)
 
 
 class SolveDelta(nn.Module):
@@ -186,8 +190,7 @@ class SolveDelta(nn.Module):
                 u, h, q, keys, values, log_decay, erase_raw, write_raw, geometry_write,
                 valid_mask=valid_mask, reset_mask=reset_mask,
                 initial_state=operator_initial, return_final_state=return_final_state)
-        normed = self.output_norm(output, output_gate)
-        result = self._linear(self.output_proj, normed.reshape(batch, length, heads * value_width))
+        result = self.output_norm.forward_linear(output, output_gate, self.output_proj)
         if not return_final_state:
             return result
         if operator_state is None:

@@ -160,6 +160,41 @@ def test_rms_norm_gated_matches_checker(shape):
     assert max_rel(_np(wg.grad), dwo) <= 1e-3
 
 
+@pytest.mark.parametrize("shape,out_features,bias", [((2, 19, 2, 16), 24, True), ((1, 130, 8, 128), 256, False)])
+def test_norm_followed_by_linear_recomputes_the_normalised_panel(shape, out_features, bias):
+    """The fused owner (causallsso/ops/norm_gate.py:46-159) against the checker's norm chained with an FP64
+    linear, and nothing of the size of the normalised panel is kept for the reverse pass."""
+    from solvedelta_b200 import rms_norm_gated_linear
+
+    gen = torch.Generator().manual_seed(sum(shape) + out_features)
+    H, V = shape[-2:]
+    x = torch.randn(*shape, generator=gen).to(torch.bfloat16)
+    gate = (2.0 * torch.randn(*shape, generator=gen)).to(torch.bfloat16)
+    w = 1.0 + 0.3 * torch.randn(V, generator=gen)
+    W = (torch.randn(out_features, H * V, generator=gen) / (H * V) ** 0.5).to(torch.bfloat16)
+    b = torch.randn(out_features, generator=gen).to(torch.bfloat16) if bias else None
+    dout = torch.randn(*shape[:-2], out_features, generator=gen).to(torch.bfloat16)
+    xg, gg, wg = x.cuda().requires_grad_(), gate.cuda().requires_grad_(), w.cuda().requires_grad_()
+    Wg = W.cuda().requires_grad_()
+    bg = None if b is None else b.cuda().requires_grad_()
+    out = rms_norm_gated_linear(xg, gg, wg, Wg, bg, 1e-6)
+    saved = [t for t in out.grad_fn.saved_tensors]
+    assert all(t.shape != torch.Size(shape) or t.data_ptr() in (xg.data_ptr(), gg.data_ptr()) for t in saved)
+    (out.float() * dout.cuda().float()).sum().backward()
+    yo, norm_saved = mo.norm_gate_forward(_np(x), _np(gate), _np(w), 1e-6)
+    y2 = yo.reshape(-1, H * V)
+    oo = y2 @ _np(W).T + (0.0 if b is None else _np(b))
+    d2 = _np(dout).reshape(-1, out_features)
+    dxo, dgo, dwo = mo.norm_gate_backward((d2 @ _np(W)).reshape(shape), _np(w), norm_saved)
+    assert max_rel(_np(out).reshape(-1, out_features), oo) <= TOL
+    assert max_rel(_np(xg.grad), dxo) <= TOL
+    assert max_rel(_np(gg.grad), dgo) <= TOL
+    assert max_rel(_np(wg.grad), dwo) <= 5e-3
+    assert max_rel(_np(Wg.grad), d2.T @ y2) <= TOL
+    if b is not None:
+        assert max_rel(_np(bg.grad), d2.sum(0)) <= TOL
+
+
 # ------------------------------------------------------------------ module
 
 LINEAR_WEIGHTS = ("in_proj.weight", "in_proj.bias", "output_proj.weight", "output_proj.bias", "decay_proj.weight",
