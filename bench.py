@@ -863,9 +863,23 @@ def run_model_ddp(opts, rank, world, local_rank):
     gen = torch.Generator(device="cpu").manual_seed(100 + rank)
     ids = torch.randint(0, config.vocab_size, (B, T), generator=gen).to(device)
     shadows = BF16ShadowWeights(model, lambda masters: torch.optim.AdamW(masters, lr=1e-4, fused=True))
-    step = SolveDeltaGraphedTrainingStep(model, ids, ids, num_warmup_iters=2, distributed=world > 1)
+    if opts.ddp_mode == "graphed":
+        graphed = SolveDeltaGraphedTrainingStep(model, ids, ids, num_warmup_iters=2, distributed=world > 1)
+        step = lambda: graphed(ids, ids)
+    else:
+        # eager forward / backward; gradients live in flat buckets whose all-reduces start from autograd
+        # hooks while backward is still running
+        from solvedelta_b200 import BucketedGradientAverager, causal_lm_loss
+
+        averager = BucketedGradientAverager(model.parameters())
+
+        def step():
+            loss = causal_lm_loss(model, ids, ids, total=B * (T - 1))
+            loss.backward()
+            averager.finish()
+            return loss.detach()
     for _ in range(max(opts.warmup, 3)):
-        step(ids, ids)
+        step()
         shadows.optimizer.step()
     torch.cuda.synchronize()
     if world > 1:
@@ -873,7 +887,7 @@ def run_model_ddp(opts, rank, world, local_rank):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(opts.steps):
-        loss = step(ids, ids)
+        loss = step()
         shadows.optimizer.step()
     e1.record()
     torch.cuda.synchronize()
@@ -891,8 +905,11 @@ def run_model_ddp(opts, rank, world, local_rank):
                           "value": world * B * T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
                           "steps": opts.steps, "ms_per_step": ms, "scaling": "weak", "dtype": "bf16",
                           "data": "synthetic", "loss": float(loss), "weights_equal_across_ranks": same,
-                          "config": {"workload": f"B={B}, T={T} per GPU; graphed fwd + chunked loss + bwd, one flat "
-                                                 "NCCL gradient all-reduce, fused AdamW on FP32 masters"}}), flush=True)
+                          "config": {"workload": f"B={B}, T={T} per GPU; " + (
+                              "graphed fwd + chunked loss + bwd, one flat NCCL gradient all-reduce after the replay"
+                              if opts.ddp_mode == "graphed" else
+                              "eager fwd + chunked loss + bwd, bucketed NCCL gradient all-reduces launched from "
+                              "autograd hooks during backward") + ", fused AdamW on FP32 masters"}}), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -913,6 +930,9 @@ def main():
     ap.add_argument("--summarize-ncu", metavar="CSV", default=None,
                     help="no GPU work: turn an ncu --csv log of one step's launches (medium case, 1024 chunk tasks) "
                          "into the DRAM table of profiles/ on stdout")
+    ap.add_argument("--ddp-mode", default="bucketed", choices=["bucketed", "graphed"],
+                    help="--model-ddp only: bucketed all-reduces overlapped with an eager backward, or one flat "
+                         "all-reduce after a graph-replayed step")
     ap.add_argument("--model-ddp", action="store_true",
                     help="side measurement: only the data-parallel 24-layer training step at the launched world size")
     opts = ap.parse_args()

@@ -12,7 +12,8 @@ from .mixer_ops import conv4_silu, conv4_silu_segmented, kda_decay_gate, rms_nor
 from .model import RMSNormGated, SolveDelta, SolveDeltaLayerState
 from .modeling import (GraphedDecoder, SolveDeltaBlock, SolveDeltaCache, SolveDeltaCacheAdapter, SolveDeltaForCausalLM,
                        SolveDeltaMLP, SolveDeltaModel, SolveDeltaPreTrainedModel)
-from .training import (BF16ShadowWeights, SolveDeltaGraphedTrainingStep, allreduce_gradients, causal_lm_loss,
+from .training import (BF16ShadowWeights, BucketedGradientAverager, SolveDeltaGraphedTrainingStep,
+                       allreduce_gradients, causal_lm_loss,
                        fixed_dense_linear_cross_entropy)
 from .packing import PackedSegments, build_packed_segments, pack_tokens, unpack_tokens
 from .ops import (
@@ -34,6 +35,7 @@ AutoModelForCausalLM.register(SolveDeltaConfig, SolveDeltaForCausalLM, exist_ok=
 __all__ = [
     "SolveDeltaPreTrainedModel",
     "BF16ShadowWeights",
+    "BucketedGradientAverager",
     "SolveDeltaGraphedTrainingStep",
     "allreduce_gradients",
     "causal_lm_loss",

@@ -171,6 +171,101 @@ def allreduce_gradients(params: Iterable[torch.Tensor], group: Any = None) -> in
     return issued
 
 
+class BucketedGradientAverager:
+    """Gradient averaging overlapped with the backward pass (the role torch DDP plays upstream with
+    ``gradient_as_bucket_view=True``, causallsso/cuda_graph.py:250-262).
+
+    Parameters are grouped, last registered first (roughly the order backward produces gradients),
+    into flat buckets of about ``bucket_bytes`` per gradient dtype.  Every parameter's ``.grad`` is a view
+    of its bucket, so backward accumulates straight into the bucket and nothing is copied.  A
+    post-accumulate hook counts the gradients of a bucket; when the last one arrives the bucket's
+    all-reduce is launched asynchronously, on the communication stream of the process group, while
+    backward carries on with earlier layers.  ``finish()`` waits for the collectives and divides by the
+    world size; ``zero_grad()`` clears the buckets and keeps the views.  Parameters that receive no
+    gradient in a step would stall their bucket, so ``finish()`` launches whatever is still pending
+    (with whatever those buckets hold); every rank must skip the same parameters.
+
+    The graph-replayed step cannot use it (hooks do not run during a replay): it keeps the single flat
+    all-reduce after the replay.
+    """
+
+    def __init__(self, params: Iterable[torch.Tensor], group: Any = None, bucket_bytes: int = 64 << 20) -> None:
+        self.group = group
+        self.enabled = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+        self.world = dist.get_world_size(group) if self.enabled else 1
+        self.params = [p for p in params if p.requires_grad]
+        self.buckets: List[dict] = []
+        self._hooks = []
+        self._sync = True
+        open_bucket: dict = {}
+        for p in reversed(self.params):
+            key = (p.dtype, p.device)
+            b = open_bucket.get(key)
+            if b is None or b["bytes"] >= bucket_bytes:
+                b = {"params": [], "bytes": 0, "dtype": p.dtype, "device": p.device}
+                open_bucket[key] = b
+                self.buckets.append(b)
+            b["params"].append(p)
+            b["bytes"] += p.numel() * p.element_size()
+        for index, b in enumerate(self.buckets):
+            b["flat"] = torch.zeros(sum(p.numel() for p in b["params"]), dtype=b["dtype"], device=b["device"])
+            offset = 0
+            for p in b["params"]:
+                p.grad = b["flat"][offset:offset + p.numel()].view_as(p)
+                offset += p.numel()
+                self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(index)))
+            b["arrived"], b["handle"] = 0, None
+
+    def _make_hook(self, index: int):
+        def hook(param):
+            b = self.buckets[index]
+            b["arrived"] += 1
+            if b["arrived"] == len(b["params"]):
+                self._launch(b)
+        return hook
+
+    def _launch(self, b: dict) -> None:
+        if self.enabled and self._sync and b["handle"] is None:
+            b["handle"] = dist.all_reduce(b["flat"], op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+
+    @torch.no_grad()
+    def finish(self) -> int:
+        """Call after backward: returns the number of collectives of this step."""
+        issued = 0
+        for b in self.buckets:
+            if self.enabled and self._sync:
+                self._launch(b)
+                b["handle"].wait()
+                b["flat"].div_(self.world)
+                issued += 1
+            b["arrived"], b["handle"] = 0, None
+        return issued
+
+    @torch.no_grad()
+    def zero_grad(self) -> None:
+        for b in self.buckets:
+            b["flat"].zero_()
+            offset = 0
+            for p in b["params"]:
+                if p.grad is None or p.grad.data_ptr() != b["flat"].data_ptr() + offset * b["flat"].element_size():
+                    p.grad = b["flat"][offset:offset + p.numel()].view_as(p)
+                offset += p.numel()
+
+    @contextmanager
+    def no_sync(self):
+        """Gradient accumulation: backward passes inside add to the buckets without any collective."""
+        previous, self._sync = self._sync, False
+        try:
+            yield
+        finally:
+            self._sync = previous
+
+    def remove(self) -> None:
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []
+
+
 def causal_lm_loss(model, input_ids: torch.Tensor, labels: torch.Tensor, *, total: int,
                    num_chunks: int = 8) -> torch.Tensor:
     """The model's shifted-label loss through the chunked fixed-denominator head (same value as
@@ -301,5 +396,6 @@ class SolveDeltaGraphedTrainingStep:
             self._sync = previous
 
 
-__all__ = ["BF16ShadowWeights", "SolveDeltaGraphedTrainingStep", "allreduce_gradients", "causal_lm_loss",
+__all__ = ["BF16ShadowWeights", "BucketedGradientAverager", "SolveDeltaGraphedTrainingStep", "allreduce_gradients",
+           "causal_lm_loss",
            "fixed_dense_linear_cross_entropy"]

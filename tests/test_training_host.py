@@ -107,6 +107,73 @@ def test_gradients_are_averaged_over_two_ranks(tmp_path):
         assert torch.equal(g3, torch.tensor([1.5, -3.0], dtype=torch.float64))
 
 
+def _bucketed_worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from solvedelta_b200 import BucketedGradientAverager
+
+    torch.manual_seed(0)   # the same weights on every rank
+    model = nn.Sequential(nn.Linear(6, 16), nn.Tanh(), nn.Linear(16, 16), nn.Tanh(), nn.Linear(16, 3))
+    model[2].weight.data = model[2].weight.data.double()   # a second gradient dtype -> its own buckets
+    model[2].bias.data = model[2].bias.data.double()
+    averager = BucketedGradientAverager(model.parameters(), bucket_bytes=256)   # several buckets
+    gen = torch.Generator().manual_seed(10 + rank)
+    x = torch.randn(4, 6, generator=gen)
+
+    def loss_of(inp):
+        h = torch.tanh(model[0](inp)).double()
+        h = torch.tanh(model[2](h)).float()
+        return model[4](h).pow(2).sum()
+
+    loss_of(x).backward()
+    issued = averager.finish()
+    first = [p.grad.clone() for p in model.parameters()]
+    views = all(p.grad.data_ptr() >= b["flat"].data_ptr() for b in averager.buckets for p in b["params"])
+    # accumulation: one local micro-batch without a collective, then a synchronised one
+    averager.zero_grad()
+    with averager.no_sync():
+        loss_of(x).backward()
+        assert averager.finish() == 0
+    loss_of(2 * x).backward()
+    averager.finish()
+    second = [p.grad.clone() for p in model.parameters()]
+    torch.save({"issued": issued, "buckets": len(averager.buckets), "views": views, "first": first, "second": second,
+                "x": x}, os.path.join(out_dir, f"rank{rank}.pt"))
+    dist.destroy_process_group()
+
+
+def test_bucketed_averager_overlaps_nothing_it_should_not(tmp_path):
+    """Two gloo ranks: gradients that live in the buckets equal the plain average of the per-rank
+    gradients, for one step and for an accumulated pair of micro-batches."""
+    world = 2
+    mp.spawn(_bucketed_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    got = [torch.load(os.path.join(tmp_path, f"rank{r}.pt")) for r in range(world)]
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(6, 16), nn.Tanh(), nn.Linear(16, 16), nn.Tanh(), nn.Linear(16, 3))
+    model[2].weight.data = model[2].weight.data.double()
+    model[2].bias.data = model[2].bias.data.double()
+
+    def grads_of(inputs):
+        for p in model.parameters():
+            p.grad = None
+        for inp in inputs:
+            h = torch.tanh(model[0](inp)).double()
+            h = torch.tanh(model[2](h)).float()
+            model[4](h).pow(2).sum().backward()
+        return [p.grad.clone() for p in model.parameters()]
+
+    per_rank_first = [grads_of([g["x"]]) for g in got]
+    # second step: every rank accumulated its local x micro-batch, then the all-reduce summed (local x + 2x) over ranks
+    per_rank_second = [grads_of([g["x"], 2 * g["x"]]) for g in got]
+    for g in got:
+        assert g["issued"] == g["buckets"] and g["buckets"] >= 3 and g["views"]
+        for i, (a, b) in enumerate(zip(per_rank_first[0], per_rank_first[1])):
+            assert torch.allclose(g["first"][i], (a + b) / 2, rtol=1e-5, atol=1e-6)
+        for i, (a, b) in enumerate(zip(per_rank_second[0], per_rank_second[1])):
+            assert torch.allclose(g["second"][i], (a + b) / 2, rtol=1e-5, atol=1e-6)
+
+
 def test_allreduce_is_a_no_op_without_a_group():
     p = nn.Parameter(torch.zeros(2))
     p.grad = torch.ones(2)
