@@ -930,7 +930,7 @@ def main():
     ap.add_argument("--summarize-ncu", metavar="CSV", default=None,
                     help="no GPU work: turn an ncu --csv log of one step's launches (medium case, 1024 chunk tasks) "
                          "into the DRAM table of profiles/ on stdout")
-    ap.add_argument("--ddp-mode", default="bucketed", choices=["bucketed", "graphed"],
+    ap.add_argument("--ddp-mode", default="graphed", choices=["bucketed", "graphed"],
                     help="--model-ddp only: bucketed all-reduces overlapped with an eager backward, or one flat "
                          "all-reduce after a graph-replayed step")
     ap.add_argument("--model-ddp", action="store_true",

@@ -116,6 +116,49 @@ int sd_backward(const sd_backward_args *args, void *stream);
 int sd_decode_step(const sd_decode_args *args, void *stream);
 
 /*
+ * Predictor only: the sub-owner entry oja_residual(target, source, beta, log_decay, query,
+ * initial_state) of causallsso/ops/residual_frame/predictor.py:285-305 (forward :32-87,
+ * reverse :129-282).  `source` and `query` are taken as they are (the reference passes the
+ * L2-normalised panels; nothing is normalised here and their gradients are the gradients of
+ * the rows themselves).  Outputs: frame_action = C_t^T query accumulated through the chunk
+ * (what the operator adds to k^ to form the primal address) and update = Delta, both BF16
+ * contiguous [B,T,H,r], and the final predictor state.  Workspace sizes are those of the
+ * full operator for the same shape with V = r (sd_saved_bytes, sd_forward_scratch_bytes,
+ * sd_backward_scratch_bytes); shape.V is ignored.
+ */
+typedef struct {
+    sd_shape shape;
+    sd_operand target, source, query;   /* BF16, width r */
+    sd_operand beta;                    /* FP32, width 1 (geometry rate per token) */
+    sd_operand log_decay;               /* FP32, width r */
+    const float *C0;                    /* [B,H,r,r] or NULL */
+    void *frame_action, *update;        /* out BF16 [B,T,H,r] contiguous */
+    float *C_T;                         /* out or NULL */
+    void *saved;  size_t saved_bytes;
+    void *scratch; size_t scratch_bytes;
+    const unsigned char *valid_mask, *reset_mask;
+} sd_predictor_forward_args;
+
+typedef struct {
+    sd_shape shape;
+    sd_operand target, source, query, beta, log_decay;
+    const void *frame_action;           /* what the forward call returned */
+    const void *d_frame_action;         /* BF16 [B,T,H,r] contiguous or NULL */
+    const void *d_update;               /* BF16 [B,T,H,r] contiguous or NULL */
+    const float *dC_T;                  /* or NULL */
+    const void *saved; size_t saved_bytes;
+    void *scratch; size_t scratch_bytes;
+    void *dtarget, *dsource, *dquery;   /* out BF16 [B,T,H,r] contiguous */
+    float *dbeta;                       /* out FP32 [B,T,H] */
+    float *dlog_decay;                  /* out FP32 [B,T,H,r] */
+    float *dC0;                         /* out or NULL */
+    const unsigned char *valid_mask, *reset_mask;
+} sd_predictor_backward_args;
+
+int sd_predictor_forward(const sd_predictor_forward_args *args, void *stream);
+int sd_predictor_backward(const sd_predictor_backward_args *args, void *stream);
+
+/*
  * sd_forward_static -- forward pass for callers that are not allowed to
  * allocate device memory.  It has no counterpart in the upstream project.
  *

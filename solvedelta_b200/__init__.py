@@ -19,6 +19,7 @@ from .packing import PackedSegments, build_packed_segments, pack_tokens, unpack_
 from .ops import (
     SolveDeltaState,
     solvedelta_native,
+    oja_residual,
     solvedelta_masked_native,
     solvedelta_segmented_native,
     solvedelta_residual_frame_native,
@@ -60,6 +61,7 @@ __all__ = [
     "build",
     "load",
     "solvedelta_native",
+    "oja_residual",
     "solvedelta_masked_native",
     "solvedelta_segmented_native",
     "solvedelta_residual_frame_native",

@@ -108,6 +108,26 @@ class BackwardArgs(ctypes.Structure):
         ("valid_mask", ctypes.c_void_p), ("reset_mask", ctypes.c_void_p)])
 
 
+class PredictorForwardArgs(ctypes.Structure):
+    _fields_ = ([("shape", Shape)] + [(n, Operand) for n in ("target", "source", "query", "beta", "log_decay")] + [
+        ("C0", ctypes.c_void_p), ("frame_action", ctypes.c_void_p), ("update", ctypes.c_void_p),
+        ("C_T", ctypes.c_void_p),
+        ("saved", ctypes.c_void_p), ("saved_bytes", ctypes.c_size_t),
+        ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t),
+        ("valid_mask", ctypes.c_void_p), ("reset_mask", ctypes.c_void_p)])
+
+
+class PredictorBackwardArgs(ctypes.Structure):
+    _fields_ = ([("shape", Shape)] + [(n, Operand) for n in ("target", "source", "query", "beta", "log_decay")] + [
+        ("frame_action", ctypes.c_void_p), ("d_frame_action", ctypes.c_void_p), ("d_update", ctypes.c_void_p),
+        ("dC_T", ctypes.c_void_p),
+        ("saved", ctypes.c_void_p), ("saved_bytes", ctypes.c_size_t),
+        ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t),
+        ("dtarget", ctypes.c_void_p), ("dsource", ctypes.c_void_p), ("dquery", ctypes.c_void_p),
+        ("dbeta", ctypes.c_void_p), ("dlog_decay", ctypes.c_void_p), ("dC0", ctypes.c_void_p),
+        ("valid_mask", ctypes.c_void_p), ("reset_mask", ctypes.c_void_p)])
+
+
 class DecodeArgs(ctypes.Structure):
     _fields_ = ([("shape", Shape)] + [(n, Operand) for n in _OPERANDS] + [
         ("C", ctypes.c_void_p), ("S", ctypes.c_void_p), ("y", ctypes.c_void_p)])
@@ -150,6 +170,7 @@ EXPORTS = (
     "sd_forward", "sd_backward", "sd_decode_step", "sd_forward_launches",
     "sd_backward_launches", "sd_panel_info", "sd_status_string", "sd_version",
     "sd_chunk_tokens", "sd_forward_static", "sd_panel_kind", "sd_device_fault", "sd_device_fault_clear",
+    "sd_predictor_forward", "sd_predictor_backward",
     "sd_conv4_backward_scratch_bytes", "sd_conv4_silu_forward", "sd_conv4_silu_backward",
     "sd_kda_gate_backward_scratch_bytes", "sd_kda_gate_forward", "sd_kda_gate_backward",
     "sd_norm_gate_backward_scratch_bytes", "sd_norm_gate_forward", "sd_norm_gate_backward",
@@ -217,7 +238,8 @@ def _declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.sd_kda_gate_backward_scratch_bytes.argtypes = [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32]
     lib.sd_norm_gate_backward_scratch_bytes.restype = ctypes.c_size_t
     lib.sd_norm_gate_backward_scratch_bytes.argtypes = [ctypes.c_int64, ctypes.c_int32]
-    for name, struct in (("sd_conv4_silu_forward", Conv4ForwardArgs), ("sd_conv4_silu_backward", Conv4BackwardArgs),
+    for name, struct in (("sd_predictor_forward", PredictorForwardArgs), ("sd_predictor_backward", PredictorBackwardArgs),
+                         ("sd_conv4_silu_forward", Conv4ForwardArgs), ("sd_conv4_silu_backward", Conv4BackwardArgs),
                          ("sd_kda_gate_forward", KdaGateArgs), ("sd_kda_gate_backward", KdaGateArgs),
                          ("sd_norm_gate_forward", NormGateArgs), ("sd_norm_gate_backward", NormGateArgs)):
         getattr(lib, name).restype = ctypes.c_int

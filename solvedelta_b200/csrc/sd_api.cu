@@ -388,7 +388,22 @@ const char* sd_status_string(int status) {
     }
 }
 
-int sd_forward(const sd_forward_args* a, void* stream_) {
+namespace {
+// Non-null for the predictor-only entry points: the launch sequences stop after (forward) or start at
+// (reverse) the predictor kernels, and the source / query rows are taken as unit vectors.
+struct PredictorOnly {
+    void *action, *update;                        // forward outputs, BF16 [B,T,H,r] contiguous
+    const void *d_action, *d_update, *action_in;  // reverse inputs, same layout (the cotangents may be null)
+};
+int forward_impl(const sd_forward_args* a, void* stream_, const PredictorOnly* po);
+int backward_impl(const sd_backward_args* a, void* stream_, const PredictorOnly* po);
+}  // namespace
+
+int sd_forward(const sd_forward_args* a, void* stream_) { return forward_impl(a, stream_, nullptr); }
+int sd_backward(const sd_backward_args* a, void* stream_) { return backward_impl(a, stream_, nullptr); }
+
+namespace {
+int forward_impl(const sd_forward_args* a, void* stream_, const PredictorOnly* po) {
     if (!a || !shape_ok(&a->shape)) return SD_ERR_INVALID_ARGUMENT;
     if (!shape_supported(&a->shape)) return SD_ERR_UNSUPPORTED_SHAPE;
     const sd_operand ops[] = {a->u, a->h, a->q, a->keys, a->values, a->erase_raw, a->write_raw, a->log_decay, a->gamma};
@@ -439,6 +454,9 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
     p.CtCk = panel_at(kSaved, s, a->saved, "CtCk");
     p.SCk = bpanel_at(kSaved, s, a->saved, "SCk");
     p.y = a->y;
+    p.action = po ? po->action : nullptr;
+    p.update = po ? po->update : nullptr;
+    p.u.unit = p.k.unit = po ? 1 : 0;
 
     const int chunks = (int)total_chunks(s);
     const int streams = s->B * s->H;
@@ -463,6 +481,7 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
     set_dbg(p.g, 2, chunks);
     SD_LAUNCH_CHUNK(k_primal_exterior_fwd, PRIMAL_EXT_FWD_SMEM);
     mark(stream);
+    if (po) return launch_status();   // the kernel stopped after its primal half
     {
         ScanParams sp{};
         sp.P = p.Ud; sp.Q = p.Wd; sp.R = p.Dt;
@@ -478,7 +497,7 @@ int sd_forward(const sd_forward_args* a, void* stream_) {
     return launch_status();
 }
 
-int sd_backward(const sd_backward_args* a, void* stream_) {
+int backward_impl(const sd_backward_args* a, void* stream_, const PredictorOnly* po) {
     if (!a || !shape_ok(&a->shape)) return SD_ERR_INVALID_ARGUMENT;
     if (!shape_supported(&a->shape)) return SD_ERR_UNSUPPORTED_SHAPE;
     const sd_operand ops[] = {a->u,         a->h,         a->q,         a->keys,  a->values,
@@ -539,6 +558,7 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
 #undef SD_BP
     p.du = a->du; p.dh = a->dh; p.dq = a->dq; p.dk = a->dkeys; p.dv = a->dvalues;
     p.der = a->derase_raw; p.dwr = a->dwrite_raw; p.dld = a->dlog_decay; p.dgam = a->dgamma;
+    p.u.unit = p.k.unit = po ? 1 : 0;
 
     const int chunks = (int)total_chunks(s);
     const int streams = s->B * s->H;
@@ -547,6 +567,24 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
     const bool fast = all_fast(bwd_ops, 9, *s);
     const bool masked = a->valid_mask != nullptr || a->reset_mask != nullptr;
 
+    if (po) {
+        // cotangents of the frame action and of the update from the caller: contiguous [B,T,H,r] BF16
+        auto dense = [&](const void* ptr) {
+            sd_operand o;
+            o.ptr = ptr;
+            o.stride_h = s->r;
+            o.stride_t = (int64_t)s->H * s->r;
+            o.stride_b = (int64_t)s->T * s->H * s->r;
+            Operand op = make_operand(o, 2);
+            if (ptr == nullptr) op.vec = 0;
+            return op;
+        };
+        const Operand dact = dense(po->d_action), dupd = dense(po->d_update), act = dense(po->action_in);
+        if (masked)
+            k_predictor_seed_bwd<true><<<chunks, NTHREADS, 0, stream>>>(p, dact, dupd, act);
+        else
+            k_predictor_seed_bwd<false><<<chunks, NTHREADS, 0, stream>>>(p, dact, dupd, act);
+    } else {
     set_dbg(p.g, 5, chunks);
     SD_LAUNCH_CHUNK(k_exterior_prep_bwd, EXT_PREP_BWD_SMEM);
     mark(stream);
@@ -562,6 +600,7 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
     set_dbg(p.g, 7, chunks);
     SD_LAUNCH_CHUNK(k_exterior_pair_bwd, EXT_PAIR_BWD_SMEM);
     mark(stream);
+    }
     set_dbg(p.g, 8, chunks);
     SD_LAUNCH_CHUNK(k_primal_bwd, PRIMAL_BWD_SMEM);
     mark(stream);
@@ -578,6 +617,48 @@ int sd_backward(const sd_backward_args* a, void* stream_) {
     SD_LAUNCH_CHUNK(k_predictor_close_bwd, PRED_CLOSE_BWD_SMEM);
     mark(stream);
     return launch_status();
+}
+}  // namespace
+
+// ---- predictor-only entry points ------------------------------------------------------------------
+// The argument blocks of the full operator are reused: operands the predictor kernels never read
+// (q, values, gate logits, y and their gradients) point at the query / at scratch outputs.
+int sd_predictor_forward(const sd_predictor_forward_args* a, void* stream_) {
+    if (!a || !a->frame_action || !a->update) return SD_ERR_INVALID_ARGUMENT;
+    sd_forward_args f{};
+    f.shape = a->shape;
+    f.shape.V = a->shape.r;
+    f.u = a->source; f.h = a->target; f.keys = a->query;
+    f.q = f.values = f.erase_raw = f.write_raw = a->query;   // never read by the predictor kernels
+    f.log_decay = a->log_decay; f.gamma = a->beta;
+    f.C0 = a->C0; f.S0 = nullptr;
+    f.y = a->frame_action; f.C_T = a->C_T; f.S_T = nullptr;
+    f.saved = a->saved; f.saved_bytes = a->saved_bytes;
+    f.scratch = a->scratch; f.scratch_bytes = a->scratch_bytes;
+    f.valid_mask = a->valid_mask; f.reset_mask = a->reset_mask;
+    PredictorOnly po{a->frame_action, a->update, nullptr, nullptr, nullptr};
+    return forward_impl(&f, stream_, &po);
+}
+
+int sd_predictor_backward(const sd_predictor_backward_args* a, void* stream_) {
+    if (!a || !a->frame_action || !a->dtarget || !a->dsource || !a->dquery || !a->dbeta || !a->dlog_decay)
+        return SD_ERR_INVALID_ARGUMENT;
+    sd_backward_args b{};
+    b.shape = a->shape;
+    b.shape.V = a->shape.r;
+    b.u = a->source; b.h = a->target; b.keys = a->query;
+    b.q = b.values = b.erase_raw = b.write_raw = b.dy = a->query;   // never read by the predictor kernels
+    b.log_decay = a->log_decay; b.gamma = a->beta;
+    b.dC_T = a->dC_T; b.dS_T = nullptr;
+    b.saved = a->saved; b.saved_bytes = a->saved_bytes;
+    b.scratch = a->scratch; b.scratch_bytes = a->scratch_bytes;
+    b.du = a->dsource; b.dh = a->dtarget; b.dkeys = a->dquery;
+    b.dq = b.dvalues = b.derase_raw = b.dwrite_raw = a->dquery;     // never written by the predictor kernels
+    b.dlog_decay = a->dlog_decay; b.dgamma = a->dbeta;
+    b.dC0 = a->dC0; b.dS0 = nullptr;
+    b.valid_mask = a->valid_mask; b.reset_mask = a->reset_mask;
+    PredictorOnly po{nullptr, nullptr, a->d_frame_action, a->d_update, a->frame_action};
+    return backward_impl(&b, stream_, &po);
 }
 
 #ifdef SD_DIAGNOSTICS

@@ -455,6 +455,44 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_exterior_pair_bwd(BwdParams p) 
 }
 
 // ---------------------------------------------------------------------------
+// Predictor-only reverse pass (the sub-owner entry, causallsso/ops/residual_frame/predictor.py:129-282):
+// the cotangents of the frame action d - k^ and of the update Delta come from the caller instead of
+// from the exterior kernels.  This kernel writes the panels that k_primal_bwd and
+// k_predictor_close_bwd otherwise receive from k_exterior_pair_bwd:
+//   Dd = d_action, DG = d_action exp(G), dDelta = d_update, dGPart = d_action (d - k^)  (d(d_i)/dG_i),
+// and zeros for what only the exterior contributes (dkPart: d - k^ has no direct k^ term; duPart, Xext, SdS).
+template <bool MASKED>
+__global__ void __launch_bounds__(NTHREADS) k_predictor_seed_bwd(BwdParams p, Operand dact, Operand dupd, Operand act) {
+    const ChunkT<MASKED> ch = chunk_of<MASKED>(p.g, blockIdx.x);
+    const int r = p.g.r;
+    const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
+    const float* gG = panel_ptr(p.Gp, ch.gi);
+    const float zero[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int pp = 0; pp < ROW_PASSES; ++pp) {
+        const int i = lr + ROWS_PER_PASS * pp;
+        float dd[8], a[8], dup[8], G[8], dg[8], dgp[8];
+        load8_bf16<false>(row_bf16(dact, ch, i), c0, r, dact.vec, ch.ok(i) && dact.ptr != nullptr, dd);
+        load8_bf16<false>(row_bf16(dupd, ch, i), c0, r, dupd.vec, ch.ok(i) && dupd.ptr != nullptr, dup);
+        load8_bf16<false>(row_bf16(act, ch, i), c0, r, act.vec, ch.ok(i), a);
+        load8_panel(gG, i, c0, G);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            dg[e] = dd[e] * __expf(G[e]);
+            dgp[e] = dd[e] * a[e];
+        }
+        store8_bpanel(bpanel_ptr(p.DG, ch.gi), i, c0, dg);
+        store8_bpanel(bpanel_ptr(p.Dd, ch.gi), i, c0, dd);
+        store8_bpanel(bpanel_ptr(p.dDelta, ch.gi), i, c0, dup);
+        store8_bpanel(bpanel_ptr(p.dGPart, ch.gi), i, c0, dgp);
+        store8_bpanel(bpanel_ptr(p.dkPart, ch.gi), i, c0, zero);
+        store8_bpanel(bpanel_ptr(p.duPart, ch.gi), i, c0, zero);
+        store8_bpanel(bpanel_ptr(p.Xext, ch.gi), i, c0, zero);
+    }
+    if (threadIdx.x < DP) p.SdS[ch.gi * DP + threadIdx.x] = 0.f;
+}
+
+// ---------------------------------------------------------------------------
 // Reverse of the primal address d = k^ + C_t^T k^, and preparation of the dC
 // scan.  With dd the cotangent of d, DG = dd exp(G), Aqk = tril(K^ Delta^T):
 //   dAqk_ij = sum_c dd_ic u^_jc exp(G_ic - G_jc)   (j <= i)
@@ -670,10 +708,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 if (j + e < r) {
-                    if (ia < ch.nvalid)
-                        rowa[j + e] = __float2bfloat16_rn(ch.ok(ia) ? (acc[nt][e] - dota * kha[nt][e]) * rka : 0.f);
-                    if (ib < ch.nvalid)
-                        rowb[j + e] = __float2bfloat16_rn(ch.ok(ib) ? (acc[nt][2 + e] - dotb * khb[nt][e]) * rkb : 0.f);
+                    // rows that came in as unit vectors get the gradient of the row itself (no projection)
+                    const float va = p.k.unit ? acc[nt][e] : (acc[nt][e] - dota * kha[nt][e]) * rka;
+                    const float vb = p.k.unit ? acc[nt][2 + e] : (acc[nt][2 + e] - dotb * khb[nt][e]) * rkb;
+                    if (ia < ch.nvalid) rowa[j + e] = __float2bfloat16_rn(ch.ok(ia) ? va : 0.f);
+                    if (ib < ch.nvalid) rowb[j + e] = __float2bfloat16_rn(ch.ok(ib) ? vb : 0.f);
                 }
             }
         }
@@ -992,7 +1031,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
             store8_smem(s_dE, i, c0, dE);
             store8_smem(s_X, i, c0, X);
             float du[8], dh[8];
-            norm_vjp8(duh, uh, rstd_u, du);
+            if (p.u.unit) {   // kernel-uniform: the source rows came in as unit vectors
+#pragma unroll
+                for (int e = 0; e < 8; ++e) du[e] = duh[e];
+            } else {
+                norm_vjp8(duh, uh, rstd_u, du);
+            }
             const float gm = s_gam[i];
 #pragma unroll
             for (int e = 0; e < 8; ++e) dh[e] = gm * drr[e];

@@ -33,6 +33,8 @@ struct Operand {
     const void* ptr;
     long long sb, st, sh;  // element strides
     int vec;               // 1 when 16-byte vector access is legal
+    int unit;              // 1 when the rows already are unit vectors: loaders do not normalise them and the
+                           // reverse kernels return the gradient of the row as it is (predictor-only entry)
 };
 
 // A reset token starts from the zero state.  It is carried as RESET_NATS of extra forgetting in
@@ -398,7 +400,7 @@ __device__ __forceinline__ void load_norm_panel(const Operand& op, const CH& ch,
 #pragma unroll
         for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
         ss = row_sum16(ss);
-        float rs = rsqrtf(ss + 1e-24f);
+        float rs = op.unit ? 1.f : rsqrtf(ss + 1e-24f);
 #pragma unroll
         for (int e = 0; e < 8; ++e) sm[i * LDP + c0 + e] = x[e] * rs;
         if (rstd != nullptr && (threadIdx.x & 15) == 0) rstd[i] = rs;

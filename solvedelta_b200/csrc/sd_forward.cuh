@@ -24,6 +24,9 @@ struct FwdParams {
     float *Npair, *Aed;  // pair matrices N = Lm / gamma and Aed, [CL][CL]
     bf16 *Zt, *SCk;  // only BF16 contractions read these
     void* y;
+    // predictor-only entry (null otherwise): BF16 [B,T,H,r] outputs frame action d - k^ and update Delta;
+    // k_primal_exterior_fwd then stops after its primal half
+    void *action, *update;
 };
 
 // Per-token frame covector phi, dual address e and query chi for the eight
@@ -72,7 +75,7 @@ __device__ __forceinline__ float load8_norm(const Operand& op, const CH& ch, int
 #pragma unroll
     for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
     ss = row_sum16(ss);
-    const float rs = rsqrtf(ss + 1e-24f);
+    const float rs = op.unit ? 1.f : rsqrtf(ss + 1e-24f);
 #pragma unroll
     for (int e = 0; e < 8; ++e) x[e] *= rs;
     return rs;
@@ -387,6 +390,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_exterior_fwd(FwdParams p
     SD_PHASE(p.g, ph);
     __syncthreads();   // every warp has read k^ as an operand: d takes its place for the exterior half below
     float* gd = panel_ptr(p.Dprim, ch.gi);
+    const bool primal_only = p.action != nullptr;
     const int ref = fast ? r0 + BT - 1 : r0 - 1;   // row whose prefix the accumulated sum is referenced to
     warp_epi<NT128>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
         float2 kh = *reinterpret_cast<const float2*>(s_kh + i * LDP + j);
@@ -394,12 +398,27 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_exterior_fwd(FwdParams p
         float2 Gp = make_float2(0.f, 0.f), dg = make_float2(0.f, 0.f);
         if (ref >= 0) Gp = *reinterpret_cast<const float2*>(s_G + ref * LDP + j);
         if (!fast) dg = *reinterpret_cast<const float2*>(s_dl + i * LDP + j);
-        const float2 d = make_float2(kh.x + __expf(G.x - Gp.x) * v0 + dg.x, kh.y + __expf(G.y - Gp.y) * v1 + dg.y);
+        const float2 act = make_float2(__expf(G.x - Gp.x) * v0 + dg.x, __expf(G.y - Gp.y) * v1 + dg.y);
+        const float2 d = make_float2(kh.x + act.x, kh.y + act.y);
         *reinterpret_cast<float2*>(gd + i * DP + j) = d;
-        *reinterpret_cast<float2*>(s_kh + i * LDP + j) = d;
+        *reinterpret_cast<float2*>(s_kh + i * LDP + j) = primal_only ? act : d;
     });
     __syncthreads();
     SD_PHASE(p.g, ph);
+    if (primal_only) {   // kernel-uniform: the predictor-only entry returns the frame action and the update
+        const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
+        const float* gDelta = panel_ptr(p.Delta, ch.gi);
+#pragma unroll
+        for (int pp = 0; pp < ROW_PASSES; ++pp) {
+            const int i = lr + ROWS_PER_PASS * pp;
+            float a[8], dl[8];
+            load8_smem(s_kh, i, c0, a);
+            load8_panel(gDelta, i, c0, dl);
+            store8_bf16<FAST>(p.action, p.g, ch, i, c0, r, a);
+            store8_bf16<FAST>(p.update, p.g, ch, i, c0, r, dl);
+        }
+        return;
+    }
     // ---- exterior half: the slots of the primal half take the panels of the exterior preparation ----
     float* s_xr = s_un;     // chi rowG   (block-centred row operand)
     float* s_er = s_dl;     // -e rowG

@@ -165,6 +165,107 @@ class _SolveDeltaFunction(torch.autograd.Function):
                 dC0 if has_C0 else None, dS0 if has_S0 else None, None, None)
 
 
+class _OjaResidual(torch.autograd.Function):
+    """forward(target, source, beta[B,T,H], log_decay, query, C0|None) -> (frame_action, update, C_T)."""
+
+    @staticmethod
+    def forward(ctx, target, source, beta, log_decay, query, C0):
+        lib = _lib.load()
+        device = target.device
+        B, T, H, r = target.shape
+        shape = _shape(target, r)
+        with torch.cuda.device(device):
+            action = torch.empty(B, T, H, r, dtype=torch.bfloat16, device=device)
+            update = torch.empty(B, T, H, r, dtype=torch.bfloat16, device=device)
+            C_T = torch.empty(B, H, r, r, dtype=torch.float32, device=device)
+            saved = _buffer(lib.sd_saved_bytes(ctypes.byref(shape)), device)
+            scratch = _buffer(lib.sd_forward_scratch_bytes(ctypes.byref(shape)), device)
+            C0c = None if C0 is None else C0.contiguous()
+            args = _lib.PredictorForwardArgs()
+            args.shape = shape
+            args.target, args.source, args.query = _operand(target), _operand(source), _operand(query)
+            args.beta, args.log_decay = _gamma_operand(beta), _operand(log_decay)
+            args.C0 = _ptr(C0c)
+            args.frame_action, args.update, args.C_T = action.data_ptr(), update.data_ptr(), C_T.data_ptr()
+            args.saved, args.saved_bytes = saved.data_ptr(), saved.numel()
+            args.scratch, args.scratch_bytes = scratch.data_ptr(), scratch.numel()
+            _lib.check(lib.sd_predictor_forward(ctypes.byref(args), _stream_ptr(device)))
+        ctx.set_materialize_grads(False)
+        ctx.has_state = C0 is not None
+        ctx.save_for_backward(target, source, beta, log_decay, query, saved, action)
+        return action, update, C_T
+
+    @staticmethod
+    def backward(ctx, d_action, d_update, dC_T):
+        lib = _lib.load()
+        target, source, beta, log_decay, query, saved, action = ctx.saved_tensors
+        device = target.device
+        B, T, H, r = target.shape
+        shape = _shape(target, r)
+        with torch.cuda.device(device):
+            d_action = None if d_action is None else d_action.to(torch.bfloat16).contiguous()
+            d_update = None if d_update is None else d_update.to(torch.bfloat16).contiguous()
+            dC_T = None if dC_T is None else dC_T.float().contiguous()
+            bf = dict(dtype=torch.bfloat16, device=device)
+            dtarget, dsource, dquery = (torch.empty(B, T, H, r, **bf) for _ in range(3))
+            dld = torch.empty(B, T, H, r, dtype=torch.float32, device=device)
+            dbeta = torch.empty(B, T, H, dtype=torch.float32, device=device)
+            dC0 = torch.empty(B, H, r, r, dtype=torch.float32, device=device)
+            scratch = _buffer(lib.sd_backward_scratch_bytes(ctypes.byref(shape)), device)
+            args = _lib.PredictorBackwardArgs()
+            args.shape = shape
+            args.target, args.source, args.query = _operand(target), _operand(source), _operand(query)
+            args.beta, args.log_decay = _gamma_operand(beta), _operand(log_decay)
+            args.frame_action = action.data_ptr()
+            args.d_frame_action, args.d_update, args.dC_T = _ptr(d_action), _ptr(d_update), _ptr(dC_T)
+            args.saved, args.saved_bytes = saved.data_ptr(), saved.numel()
+            args.scratch, args.scratch_bytes = scratch.data_ptr(), scratch.numel()
+            args.dtarget, args.dsource, args.dquery = dtarget.data_ptr(), dsource.data_ptr(), dquery.data_ptr()
+            args.dbeta, args.dlog_decay, args.dC0 = dbeta.data_ptr(), dld.data_ptr(), dC0.data_ptr()
+            _lib.check(lib.sd_predictor_backward(ctypes.byref(args), _stream_ptr(device)))
+        return dtarget, dsource, dbeta, dld, dquery, dC0 if ctx.has_state else None
+
+
+def oja_residual(target: torch.Tensor, source: torch.Tensor, beta: torch.Tensor, log_decay: torch.Tensor,
+                 query: torch.Tensor, initial_state: Optional[torch.Tensor], *, chunk_size: int = 32,
+                 output_final_state: bool = True):
+    """The predictor sub-owner of causallsso/ops/residual_frame/predictor.py:285-305, same arguments and
+    returns: ``(frame_action, update, final_state)`` with ``frame_action = C_t^T query`` accumulated through
+    the sequence (what the operator adds to the normalised key to form the primal address), ``update``
+    the residual step Delta of the NLMS solve, and ``final_state`` the predictor state ``C`` ``[B,H,r,r]`` (None
+    unless requested).  ``source`` and ``query`` are used as given (upstream passes the L2-normalised panels)
+    and receive the gradients of the rows themselves.  ``chunk_size`` is accepted for signature compatibility;
+    the kernels work on 64-token chunks and the result does not depend on it."""
+    for name, t in (("target", target), ("source", source), ("query", query)):
+        if t.device.type != "cuda" or t.dtype != torch.bfloat16:
+            raise TypeError(f"{name} must be a BF16 CUDA tensor")
+        if t.ndim != 4 or t.shape != target.shape:
+            raise ValueError(f"{name} must have shape [B,T,H,r]")
+        if t.stride(-1) != 1:
+            raise ValueError("native vector operands require unit innermost stride")
+    batch, length, heads, rank = target.shape
+    if rank > 128:
+        raise ValueError("head width above 128 is not supported")
+    if log_decay.dtype != torch.float32 or log_decay.shape != target.shape:
+        raise TypeError("log_decay must be FP32 [B,T,H,r]")
+    if beta.dtype != torch.float32 or beta.shape != (batch, length, heads):
+        raise TypeError("beta must be FP32 [B,T,H]")
+    if initial_state is not None and (initial_state.dtype != torch.float32
+                                      or initial_state.shape != (batch, heads, rank, rank)):
+        raise ValueError("initial_state must be FP32 [B,H,r,r]")
+    if log_decay.stride(-1) != 1:
+        log_decay = log_decay.contiguous()
+    if length == 0:
+        empty = target.new_zeros(target.shape)
+        final = None
+        if output_final_state:
+            final = (initial_state.clone() if initial_state is not None
+                     else torch.zeros(batch, heads, rank, rank, dtype=torch.float32, device=target.device))
+        return empty, empty.clone(), final
+    action, update, final = _OjaResidual.apply(target, source, beta, log_decay, query, initial_state)
+    return action, update, (final if output_final_state else None)
+
+
 def _decode_step(u, h, q, k, v, log_decay, erase_raw, write_raw, gamma, C0, S0):
     lib = _lib.load()
     device = u.device
@@ -383,6 +484,7 @@ def solvedelta_masked_native(
 
 __all__ = [
     "SolveDeltaState",
+    "oja_residual",
     "solvedelta_native",
     "solvedelta_masked_native",
     "solvedelta_segmented_native",
