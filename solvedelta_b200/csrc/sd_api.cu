@@ -256,10 +256,12 @@ cudaError_t configure_kernels() {
     if ((e = allow_smem(k_prep_fwd<false, false>, PREP_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_prep_fwd<true, true>, PREP_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_prep_fwd<false, true>, PREP_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_prep_fwd<false, true, true>, PREP_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_primal_exterior_fwd<true, false>, PRIMAL_EXT_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_primal_exterior_fwd<false, false>, PRIMAL_EXT_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_primal_exterior_fwd<true, true>, PRIMAL_EXT_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_primal_exterior_fwd<false, true>, PRIMAL_EXT_FWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_primal_exterior_fwd<false, true, true>, PRIMAL_EXT_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_output_fwd<true, false>, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_output_fwd<false, false>, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_output_fwd<true, true>, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
@@ -284,10 +286,12 @@ cudaError_t configure_kernels() {
     if ((e = allow_smem(k_primal_bwd<false, false>, PRIMAL_BWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_primal_bwd<true, true>, PRIMAL_BWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_primal_bwd<false, true>, PRIMAL_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_primal_bwd<false, true, true>, PRIMAL_BWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_predictor_close_bwd<true, false>, PRED_CLOSE_BWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_predictor_close_bwd<false, false>, PRED_CLOSE_BWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_predictor_close_bwd<true, true>, PRED_CLOSE_BWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_predictor_close_bwd<false, true>, PRED_CLOSE_BWD_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_predictor_close_bwd<false, true, true>, PRED_CLOSE_BWD_SMEM)) != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) done[dev] = true;
     return cudaSuccess;
 }
@@ -456,7 +460,6 @@ int forward_impl(const sd_forward_args* a, void* stream_, const PredictorOnly* p
     p.y = a->y;
     p.action = po ? po->action : nullptr;
     p.update = po ? po->update : nullptr;
-    p.u.unit = p.k.unit = po ? 1 : 0;
 
     const int chunks = (int)total_chunks(s);
     const int streams = s->B * s->H;
@@ -466,7 +469,10 @@ int forward_impl(const sd_forward_args* a, void* stream_, const PredictorOnly* p
     const bool masked = a->valid_mask != nullptr || a->reset_mask != nullptr;
 
     set_dbg(p.g, 0, chunks);
-    SD_LAUNCH_CHUNK(k_prep_fwd, PREP_FWD_SMEM);
+    if (po)   // the predictor-only instantiations: general operand layout, mask-aware (null masks are legal)
+        k_prep_fwd<false, true, true><<<chunks, NTHREADS, PREP_FWD_SMEM, stream>>>(p);
+    else
+        SD_LAUNCH_CHUNK(k_prep_fwd, PREP_FWD_SMEM);
     mark(stream);
     {
         ScanParams sp{};
@@ -479,9 +485,12 @@ int forward_impl(const sd_forward_args* a, void* stream_, const PredictorOnly* p
         mark(stream);
     }
     set_dbg(p.g, 2, chunks);
+    if (po) {
+        k_primal_exterior_fwd<false, true, true><<<chunks, NTHREADS, PRIMAL_EXT_FWD_SMEM, stream>>>(p);
+        return launch_status();   // the kernel stops after its primal half
+    }
     SD_LAUNCH_CHUNK(k_primal_exterior_fwd, PRIMAL_EXT_FWD_SMEM);
     mark(stream);
-    if (po) return launch_status();   // the kernel stopped after its primal half
     {
         ScanParams sp{};
         sp.P = p.Ud; sp.Q = p.Wd; sp.R = p.Dt;
@@ -558,7 +567,6 @@ int backward_impl(const sd_backward_args* a, void* stream_, const PredictorOnly*
 #undef SD_BP
     p.du = a->du; p.dh = a->dh; p.dq = a->dq; p.dk = a->dkeys; p.dv = a->dvalues;
     p.der = a->derase_raw; p.dwr = a->dwrite_raw; p.dld = a->dlog_decay; p.dgam = a->dgamma;
-    p.u.unit = p.k.unit = po ? 1 : 0;
 
     const int chunks = (int)total_chunks(s);
     const int streams = s->B * s->H;
@@ -602,7 +610,10 @@ int backward_impl(const sd_backward_args* a, void* stream_, const PredictorOnly*
     mark(stream);
     }
     set_dbg(p.g, 8, chunks);
-    SD_LAUNCH_CHUNK(k_primal_bwd, PRIMAL_BWD_SMEM);
+    if (po)
+        k_primal_bwd<false, true, true><<<chunks, NTHREADS, PRIMAL_BWD_SMEM, stream>>>(p);
+    else
+        SD_LAUNCH_CHUNK(k_primal_bwd, PRIMAL_BWD_SMEM);
     mark(stream);
     {
         ScanParamsB sp{};
@@ -614,7 +625,10 @@ int backward_impl(const sd_backward_args* a, void* stream_, const PredictorOnly*
     mark(stream);
     }
     set_dbg(p.g, 10, chunks);
-    SD_LAUNCH_CHUNK(k_predictor_close_bwd, PRED_CLOSE_BWD_SMEM);
+    if (po)
+        k_predictor_close_bwd<false, true, true><<<chunks, NTHREADS, PRED_CLOSE_BWD_SMEM, stream>>>(p);
+    else
+        SD_LAUNCH_CHUNK(k_predictor_close_bwd, PRED_CLOSE_BWD_SMEM);
     mark(stream);
     return launch_status();
 }

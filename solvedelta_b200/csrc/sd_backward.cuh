@@ -506,7 +506,7 @@ constexpr size_t PRIMAL_BWD_SMEM = 7 * BSLOT_BYTES + BSTATE_BYTES + 2 * BMAT_BYT
                                    (3 * CL + 4 * CL + NBLK * DP + 16) * sizeof(float) +
                                    (3 + NBLK) * DP * sizeof(bf16);
 
-template <bool FAST, bool MASKED>
+template <bool FAST, bool MASKED, bool PRED = false>
 __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
@@ -560,8 +560,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
             const int i = lr + ROWS_PER_PASS * pp, i0 = i & ~(BT - 1);
             float uh[8], kh[8], G[8], E[8], Gp[8], Ge[8], dl[8], dd[8];
-            const float ru = load8_norm<FAST>(p.u, ch, i, c0, r, uh);
-            const float rk = load8_norm<FAST>(p.k, ch, i, c0, r, kh);
+            const float ru = load8_norm<FAST, PRED>(p.u, ch, i, c0, r, uh);
+            const float rk = load8_norm<FAST, PRED>(p.k, ch, i, c0, r, kh);
             load8_panel(gG, i, c0, G);
             load8_panel(gG, i > 0 ? i - 1 : 0, c0, E);  // E = G of the previous row (0 for the first)
             load8_panel(gG, i0 ? i0 - 1 : 0, c0, Gp);
@@ -709,8 +709,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
             for (int e = 0; e < 2; ++e) {
                 if (j + e < r) {
                     // rows that came in as unit vectors get the gradient of the row itself (no projection)
-                    const float va = p.k.unit ? acc[nt][e] : (acc[nt][e] - dota * kha[nt][e]) * rka;
-                    const float vb = p.k.unit ? acc[nt][2 + e] : (acc[nt][2 + e] - dotb * khb[nt][e]) * rkb;
+                    const float va = PRED ? acc[nt][e] : (acc[nt][e] - dota * kha[nt][e]) * rka;
+                    const float vb = PRED ? acc[nt][2 + e] : (acc[nt][2 + e] - dotb * khb[nt][e]) * rkb;
                     if (ia < ch.nvalid) rowa[j + e] = __float2bfloat16_rn(ch.ok(ia) ? va : 0.f);
                     if (ib < ch.nvalid) rowb[j + e] = __float2bfloat16_rn(ch.ok(ib) ? vb : 0.f);
                 }
@@ -773,7 +773,7 @@ constexpr size_t PRED_CLOSE_BWD_SMEM = 5 * BSLOT_BYTES + 2 * BMAT_BYTES + 3 * si
                                        6 * DP * sizeof(bf16);
 static_assert(3 * size_t(CL) * LDP * 4 >= 2 * BSTATE_BYTES, "closure panels overlay both BF16 states");
 
-template <bool FAST, bool MASKED>
+template <bool FAST, bool MASKED, bool PRED = false>
 __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
@@ -821,7 +821,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
             const int i = lr + ROWS_PER_PASS * pp, i0 = i & ~(BT - 1);
             float uh[8], G[8], E[8], Gp[8], Ge[8], dl[8];
-            const float ru = load8_norm<FAST>(p.u, ch, i, c0, r, uh);
+            const float ru = load8_norm<FAST, PRED>(p.u, ch, i, c0, r, uh);
             load8_panel(gG, i, c0, G);
             load8_panel(gG, i > 0 ? i - 1 : 0, c0, E);  // E = G of the previous row (0 for the first)
             load8_panel(gG, i0 ? i0 - 1 : 0, c0, Gp);
@@ -1002,7 +1002,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
             const int i = lr + ROWS_PER_PASS * pp;
             float uh[8], G[8], E[8];
-            const float rstd_u = load8_norm<FAST>(p.u, ch, i, c0, r, uh);
+            const float rstd_u = load8_norm<FAST, PRED>(p.u, ch, i, c0, r, uh);
             load8_panel(gG, i, c0, G);
             load8_panel(gG, i > 0 ? i - 1 : 0, c0, E);  // E = G of the previous row (0 for the first)
 #pragma unroll
@@ -1031,7 +1031,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_predictor_close_bwd(BwdParams p
             store8_smem(s_dE, i, c0, dE);
             store8_smem(s_X, i, c0, X);
             float du[8], dh[8];
-            if (p.u.unit) {   // kernel-uniform: the source rows came in as unit vectors
+            if (PRED) {   // the source rows came in as unit vectors
 #pragma unroll
                 for (int e = 0; e < 8; ++e) du[e] = duh[e];
             } else {

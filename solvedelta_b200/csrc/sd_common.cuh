@@ -33,8 +33,6 @@ struct Operand {
     const void* ptr;
     long long sb, st, sh;  // element strides
     int vec;               // 1 when 16-byte vector access is legal
-    int unit;              // 1 when the rows already are unit vectors: loaders do not normalise them and the
-                           // reverse kernels return the gradient of the row as it is (predictor-only entry)
 };
 
 // A reset token starts from the zero state.  It is carried as RESET_NATS of extra forgetting in
@@ -386,8 +384,9 @@ __device__ __forceinline__ void chunk_cumsum(float* sG) {
 }
 
 // Loads a BF16 operand chunk, L2-normalises every row and stores it as FP32.
-// rstd (may be null) receives 1/|x| per row.
-template <bool FAST, class CH>
+// rstd (may be null) receives 1/|x| per row.  UNIT: the rows already are unit vectors and are taken as they
+// are (the predictor-only entry, whose caller normalises).
+template <bool FAST, bool UNIT = false, class CH>
 __device__ __forceinline__ void load_norm_panel(const Operand& op, const CH& ch, int width, float* sm,
                                                 float* rstd) {
     const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
@@ -400,7 +399,7 @@ __device__ __forceinline__ void load_norm_panel(const Operand& op, const CH& ch,
 #pragma unroll
         for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
         ss = row_sum16(ss);
-        float rs = op.unit ? 1.f : rsqrtf(ss + 1e-24f);
+        float rs = UNIT ? 1.f : rsqrtf(ss + 1e-24f);
 #pragma unroll
         for (int e = 0; e < 8; ++e) sm[i * LDP + c0 + e] = x[e] * rs;
         if (rstd != nullptr && (threadIdx.x & 15) == 0) rstd[i] = rs;

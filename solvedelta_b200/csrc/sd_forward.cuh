@@ -66,8 +66,8 @@ __device__ __forceinline__ void sources_fwd(const float (&uh)[8], const float (&
     o.sq = sq;
 }
 
-// Eight channels of one normalised BF16 row, in registers.
-template <bool FAST, class CH>
+// Eight channels of one normalised BF16 row, in registers (UNIT: taken as they are).
+template <bool FAST, bool UNIT = false, class CH>
 __device__ __forceinline__ float load8_norm(const Operand& op, const CH& ch, int i, int c0, int width,
                                             float (&x)[8]) {
     load8_bf16<FAST>(row_bf16(op, ch, i), c0, width, op.vec, ch.ok(i), x);
@@ -75,7 +75,7 @@ __device__ __forceinline__ float load8_norm(const Operand& op, const CH& ch, int
 #pragma unroll
     for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
     ss = row_sum16(ss);
-    const float rs = op.unit ? 1.f : rsqrtf(ss + 1e-24f);
+    const float rs = UNIT ? 1.f : rsqrtf(ss + 1e-24f);
 #pragma unroll
     for (int e = 0; e < 8; ++e) x[e] *= rs;
     return rs;
@@ -114,7 +114,7 @@ constexpr size_t PREP_FWD_SMEM =
     2 * SLOT_BYTES + MAT_BYTES + (CL + 3 * DP + NBLK * DP + 16 + 2 * NBLK * DP) * sizeof(float);
 static_assert(2 * (PREP_FWD_SMEM + 1024) <= 228 * 1024, "two CTAs of the predictor preparation per SM");
 
-template <bool FAST, bool MASKED>
+template <bool FAST, bool MASKED, bool PRED = false>
 __global__ void __launch_bounds__(NTHREADS, 2) k_prep_fwd(FwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_prep_fwd(FwdParams p) {
     const ChunkT<MASKED> ch = chunk_of<MASKED>(p.g, blockIdx.x);
     const int r = p.g.r;
 
-    load_norm_panel<FAST>(p.u, ch, r, s_B, nullptr);
+    load_norm_panel<FAST, PRED>(p.u, ch, r, s_B, nullptr);
     load_f32_panel<FAST>(p.ld, ch, r, s_A);
     load_gamma(p.gam, ch, s_gam);
     prefetch_rows(p.h, ch, 2, r * 2);   // read after the pair phase
@@ -302,7 +302,7 @@ __device__ __forceinline__ void async_state_cols_f32(float* sm, const float* st,
     }
 }
 
-template <bool FAST, bool MASKED>
+template <bool FAST, bool MASKED, bool PRED = false>
 __global__ void __launch_bounds__(NTHREADS, 1) k_primal_exterior_fwd(FwdParams p) {
     int ph = 0;
     SD_PHASE(p.g, ph);
@@ -331,8 +331,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_exterior_fwd(FwdParams p
     cp_commit();
     async_state_cols_f32(s_st1, ct, 1);
     cp_commit();
-    load_norm_panel<FAST>(p.k, ch, r, s_kh, nullptr);
-    load_norm_panel<FAST>(p.u, ch, r, s_un, nullptr);
+    load_norm_panel<FAST, PRED>(p.k, ch, r, s_kh, nullptr);
+    load_norm_panel<FAST, PRED>(p.u, ch, r, s_un, nullptr);
     cp_wait<2>();
     __syncthreads();
     SD_PHASE(p.g, ph);
@@ -390,7 +390,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_exterior_fwd(FwdParams p
     SD_PHASE(p.g, ph);
     __syncthreads();   // every warp has read k^ as an operand: d takes its place for the exterior half below
     float* gd = panel_ptr(p.Dprim, ch.gi);
-    const bool primal_only = p.action != nullptr;
     const int ref = fast ? r0 + BT - 1 : r0 - 1;   // row whose prefix the accumulated sum is referenced to
     warp_epi<NT128>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
         float2 kh = *reinterpret_cast<const float2*>(s_kh + i * LDP + j);
@@ -401,11 +400,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_exterior_fwd(FwdParams p
         const float2 act = make_float2(__expf(G.x - Gp.x) * v0 + dg.x, __expf(G.y - Gp.y) * v1 + dg.y);
         const float2 d = make_float2(kh.x + act.x, kh.y + act.y);
         *reinterpret_cast<float2*>(gd + i * DP + j) = d;
-        *reinterpret_cast<float2*>(s_kh + i * LDP + j) = primal_only ? act : d;
+        *reinterpret_cast<float2*>(s_kh + i * LDP + j) = PRED ? act : d;
     });
     __syncthreads();
     SD_PHASE(p.g, ph);
-    if (primal_only) {   // kernel-uniform: the predictor-only entry returns the frame action and the update
+    if (PRED) {   // the predictor-only entry returns the frame action and the update, and stops here
         const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
         const float* gDelta = panel_ptr(p.Delta, ch.gi);
 #pragma unroll
