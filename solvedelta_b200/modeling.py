@@ -18,6 +18,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 from transformers import PreTrainedModel
+from transformers.generation import GenerationMixin
 from transformers.modeling_outputs import BaseModelOutputWithPast, CausalLMOutputWithPast
 
 from . import _lib
@@ -295,11 +296,16 @@ class SolveDeltaModel(SolveDeltaPreTrainedModel):
                                        hidden_states=collected)
 
 
-class SolveDeltaForCausalLM(SolveDeltaPreTrainedModel):
+class SolveDeltaForCausalLM(SolveDeltaPreTrainedModel, GenerationMixin):
     """Language-model head, label shift and loss over ``SolveDeltaModel``
-    (modeling_solvedelta.py:400-501).  ``prepare()`` puts a freshly built or loaded
+    (modeling_solvedelta.py:393-501).  ``prepare()`` puts a freshly built or loaded
     model into the layout the CUDA mixer wants: BF16 weights on the device, the three
-    scalar parameter families of every mixer kept in FP32."""
+    scalar parameter families of every mixer kept in FP32.
+
+    ``generate`` is Hugging Face's (``GenerationMixin``): the prefill returns a ``SolveDeltaCache``, which the
+    generation loop hands back with one new token at a time; no key/value cache is ever built
+    (upstream mixes in FLA's generation adapter for the same purpose, modeling_solvedelta.py:393-395).
+    ``greedy_generate`` is this package's own loop, with the option of replaying the cached step from a CUDA graph."""
 
     ignore_index = -100
     _tied_weights_keys = {"lm_head.weight": "model.embeddings.weight"}
@@ -317,6 +323,10 @@ class SolveDeltaForCausalLM(SolveDeltaPreTrainedModel):
             keep = name.rsplit(".", 1)[-1] in FP32_PARAMETERS
             parameter.data = parameter.data.to(torch.float32 if keep else torch.bfloat16)
         return self
+
+    @classmethod
+    def _supports_default_dynamic_cache(cls) -> bool:
+        return False   # the recurrent cache comes out of the prefill; generate() must not build a key/value cache
 
     def get_input_embeddings(self):
         return self.model.embeddings
@@ -349,7 +359,7 @@ class SolveDeltaForCausalLM(SolveDeltaPreTrainedModel):
                                       hidden_states=outputs.hidden_states)
 
     @torch.no_grad()
-    def generate(self, input_ids: torch.Tensor, max_new_tokens: int, graphed: bool = False) -> torch.Tensor:
+    def greedy_generate(self, input_ids: torch.Tensor, max_new_tokens: int, graphed: bool = False) -> torch.Tensor:
         """Greedy decoding through the cache: one prefill, then one-token steps (replayed from a
         CUDA graph when ``graphed``)."""
         step = self(input_ids=input_ids, use_cache=True, logits_to_keep=1)

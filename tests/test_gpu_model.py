@@ -169,7 +169,7 @@ def test_padding_mask_leaves_valid_tokens_unchanged(medium):
 def test_greedy_generation_follows_the_single_pass(medium):
     config, model = medium
     prompt = torch.randint(0, config.vocab_size, (2, 50), device="cuda")
-    out = model.generate(prompt, max_new_tokens=6)
+    out = model.greedy_generate(prompt, max_new_tokens=6)
     assert out.shape == (2, 56) and torch.equal(out[:, :50], prompt)
     with torch.no_grad():
         logits = model(input_ids=out[:, :-1]).logits.float()
@@ -178,13 +178,30 @@ def test_greedy_generation_follows_the_single_pass(medium):
     assert agree >= 5 / 6
 
 
+def test_hugging_face_generate_runs_on_the_recurrent_cache(medium):
+    """``GenerationMixin.generate`` (greedy) drives prefill + cached one-token steps and returns what the
+    package's own loop returns; with left padding it is given the attention mask and still continues each row."""
+    config, model = medium
+    prompt = torch.randint(3, config.vocab_size, (2, 40), device="cuda")
+    own = model.greedy_generate(prompt, max_new_tokens=8)
+    hf = model.generate(prompt, max_new_tokens=8, min_new_tokens=8, do_sample=False)
+    assert hf.shape == (2, 48) and torch.equal(hf[:, :40], prompt)
+    # the two loops run the same kernels on the same tokens (BF16 ties can flip an argmax, then the rows diverge)
+    assert (hf[:, :42] == own[:, :42]).all()
+    mask = torch.ones_like(prompt)
+    mask[1, :9] = 0
+    padded = model.generate(prompt, attention_mask=mask, max_new_tokens=4, min_new_tokens=4, do_sample=False,
+                            pad_token_id=0)
+    assert padded.shape == (2, 44) and torch.equal(padded[0, :42], hf[0, :42])
+
+
 def test_graphed_decode_equals_eager_decode(medium):
     """The captured one-token step, replayed, gives what the eager cached steps give, and leaves
     the cache where they leave it."""
     config, model = medium
     prompt = torch.randint(0, config.vocab_size, (2, 77), device="cuda")
-    eager = model.generate(prompt, max_new_tokens=12)
-    graphed = model.generate(prompt, max_new_tokens=12, graphed=True)
+    eager = model.greedy_generate(prompt, max_new_tokens=12)
+    graphed = model.greedy_generate(prompt, max_new_tokens=12, graphed=True)
     assert torch.equal(eager, graphed)
     from solvedelta_b200 import GraphedDecoder
 
