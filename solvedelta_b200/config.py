@@ -58,6 +58,7 @@ _RULES: Dict[str, Callable[[str, Any], None]] = {
     "initializer_range": _positive_real,
     "use_short_conv": _flag, "bias": _flag, "use_cache": _flag, "tie_word_embeddings": _flag,
     "hidden_act": _activation, "attn": _no_hybrid_layers,
+    "fuse_norm": _flag, "fuse_swiglu": _flag, "fuse_cross_entropy": _flag, "fuse_linear_cross_entropy": _flag,
 }
 
 
@@ -88,10 +89,19 @@ class SolveDeltaConfig(PreTrainedConfig):
     bos_token_id: Optional[int] = 1
     eos_token_id: Optional[int] = 2
     tie_word_embeddings: bool = False
+    # implementation switches of upstream (config.py:34-37): the first three choose between owners of the same
+    # arithmetic there and change nothing here; fuse_linear_cross_entropy makes the causal LM compute its loss
+    # through the chunked linear + cross-entropy head and return no logits, as upstream does
+    fuse_norm: bool = True
+    fuse_swiglu: bool = True
+    fuse_cross_entropy: bool = True
+    fuse_linear_cross_entropy: bool = False
 
     def __post_init__(self, **kwargs):
         for name, rule in _RULES.items():
             rule(name, getattr(self, name))
+        if self.fuse_cross_entropy and self.fuse_linear_cross_entropy:
+            raise ValueError("fuse_cross_entropy and fuse_linear_cross_entropy are mutually exclusive")
         if self.num_edits != 1:
             raise ValueError("num_edits: the production path carries exactly one edit per token (num_edits=1)")
         self.head_width(self.head_k_dim, self.expand_k, "expand_k")

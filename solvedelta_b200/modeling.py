@@ -348,13 +348,26 @@ class SolveDeltaForCausalLM(SolveDeltaPreTrainedModel, GenerationMixin):
                              output_hidden_states=output_hidden_states, **kwargs)
         hidden_states = outputs.last_hidden_state
         keep_all = labels is not None or logits_to_keep in (None, 0)
-        logits = self.lm_head(hidden_states if keep_all else hidden_states[:, -logits_to_keep:])
+        fused_head = labels is not None and self.config.fuse_linear_cross_entropy
+        logits = None
+        if not fused_head:
+            logits = self.lm_head(hidden_states if keep_all else hidden_states[:, -logits_to_keep:])
         loss = None
         if labels is not None:
             labels = labels.to(hidden_states.device)
             shifted = torch.cat((labels[..., 1:], torch.full_like(labels[:, :1], self.ignore_index)), dim=1)
-            loss = F.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), shifted.reshape(-1),
-                                   ignore_index=self.ignore_index)
+            if fused_head:
+                # head and loss in token chunks, the [tokens, vocab] logits never exist at once and none are
+                # returned (modeling_solvedelta.py:460-483); the mean's denominator is counted on the device
+                from .training import fixed_dense_linear_cross_entropy
+
+                count = (shifted != self.ignore_index).sum().clamp_min(1)
+                loss = fixed_dense_linear_cross_entropy(hidden_states, shifted, self.lm_head.weight,
+                                                        self.lm_head.bias, ignore_index=self.ignore_index,
+                                                        total=count)
+            else:
+                loss = F.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), shifted.reshape(-1),
+                                       ignore_index=self.ignore_index)
         return CausalLMOutputWithPast(loss=loss, logits=logits, past_key_values=outputs.past_key_values,
                                       hidden_states=outputs.hidden_states)
 

@@ -41,7 +41,8 @@ class _FixedDenseLinearCrossEntropy(torch.autograd.Function):
         db = torch.zeros_like(bias, dtype=torch.float32) if need[2] else None
         loss = torch.zeros((), dtype=torch.float32, device=x.device)
         step = -(-tokens // max(1, num_chunks))
-        scale = 1.0 / float(total)
+        # a tensor denominator (the count of valid labels, taken on the device) stays on the device: no host sync
+        scale = (1.0 / total.to(torch.float32)) if torch.is_tensor(total) else 1.0 / float(total)
         for lo in range(0, tokens, step):
             xs, ts = x2[lo:lo + step], t[lo:lo + step]
             logits = torch.nn.functional.linear(xs, weight, bias).float()
@@ -83,12 +84,16 @@ class _FixedDenseLinearCrossEntropy(torch.autograd.Function):
 
 def fixed_dense_linear_cross_entropy(x: torch.Tensor, target: torch.Tensor, weight: torch.Tensor,
                                      bias: Optional[torch.Tensor] = None, *, ignore_index: int = -100,
-                                     total: int, num_chunks: int = 8) -> torch.Tensor:
+                                     total, num_chunks: int = 8) -> torch.Tensor:
     """Linear layer and cross entropy in one pass over token chunks, divided by the CONSTANT
     ``total`` (the number of valid labels of the fixed batch shape) instead of a count taken
     from the data, so a captured graph holds no data-dependent scalar (upstream
-    graph_linear_cross_entropy.py:186-209)."""
-    if not isinstance(total, int) or isinstance(total, bool) or total <= 0:
+    graph_linear_cross_entropy.py:186-209).  ``total`` may also be a 0-dim tensor on the device of
+    ``x`` (e.g. the count of valid labels): the mean then matches ``F.cross_entropy`` without a host read."""
+    if torch.is_tensor(total):
+        if total.ndim != 0 or total.device != x.device:
+            raise ValueError("a tensor total must be a scalar on the device of x")
+    elif not isinstance(total, int) or isinstance(total, bool) or total <= 0:
         raise ValueError("total must be a positive int")
     if x.shape[:-1] != target.shape:
         raise ValueError("target must have the leading shape of x")

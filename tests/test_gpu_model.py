@@ -342,3 +342,28 @@ def test_long_prefill_then_decode_steps_equal_one_pass_through_the_model():
         # recurrent step instead of the chunk kernels for the last 256 tokens): BF16-grade agreement
         assert rel_l2(C.cpu().numpy(), Cf.cpu().numpy()) < 2e-2
         assert rel_l2(S.cpu().numpy(), Sf.cpu().numpy()) < 2e-2
+
+
+def test_fused_linear_cross_entropy_head_gives_the_same_loss_and_gradients():
+    """``fuse_linear_cross_entropy`` (modeling_solvedelta.py:460-483): the loss comes from the chunked
+    linear + cross-entropy head, no logits are returned, and loss and gradients equal the plain head's."""
+    def build(fused):
+        torch.manual_seed(9)
+        config = SolveDeltaConfig(hidden_size=128, num_heads=2, head_k_dim=32, head_v_dim=64, num_hidden_layers=2,
+                                  vocab_size=300, initializer_range=0.05, fuse_cross_entropy=not fused,
+                                  fuse_linear_cross_entropy=fused)
+        return SolveDeltaForCausalLM(config).prepare("cuda").train()
+
+    ids = torch.randint(0, 300, (2, 90), generator=torch.Generator().manual_seed(1)).cuda()
+    labels = ids.clone()
+    labels[1, 60:] = -100
+    plain, fused = build(False), build(True)
+    out_p = plain(input_ids=ids, labels=labels)
+    out_f = fused(input_ids=ids, labels=labels)
+    assert out_f.logits is None and out_p.logits is not None
+    assert abs(float(out_p.loss.detach()) - float(out_f.loss.detach())) < 2e-3 * float(out_p.loss.detach())
+    out_p.loss.backward()
+    out_f.loss.backward()
+    for (name, a), (_, b) in zip(plain.named_parameters(), fused.named_parameters()):
+        scale = float(a.grad.float().abs().max().clamp_min(1e-12))
+        assert float((a.grad.float() - b.grad.float()).abs().max()) <= 3e-2 * scale, name

@@ -35,6 +35,30 @@ def test_fixed_denominator_loss_equals_cross_entropy(chunks, with_bias):
         assert (got - want).abs().max().item() < 1e-6 * max(1.0, want.abs().max().item())
 
 
+def test_a_device_side_count_gives_the_mean_of_cross_entropy():
+    """``total`` as a 0-dim tensor (the count of valid labels) reproduces ``F.cross_entropy``'s mean, and the
+    configuration refuses both fused losses at once (causallsso/config.py:133-136)."""
+    from solvedelta_b200 import SolveDeltaConfig
+
+    gen = torch.Generator().manual_seed(5)
+    x = torch.randn(2, 9, 6, dtype=torch.float64, generator=gen, requires_grad=True)
+    w = torch.randn(11, 6, dtype=torch.float64, generator=gen, requires_grad=True)
+    target = torch.randint(0, 11, (2, 9), generator=gen)
+    target[1, 3:] = -100
+    count = (target != -100).sum()
+    loss = fixed_dense_linear_cross_entropy(x, target, w, None, total=count, num_chunks=4)
+    ref = F.cross_entropy(F.linear(x, w).reshape(-1, 11), target.reshape(-1), ignore_index=-100)
+    assert abs(loss.item() - ref.item()) < 1e-6
+    gx, = torch.autograd.grad(loss, [x])
+    rx, = torch.autograd.grad(ref, [x])
+    assert (gx - rx).abs().max().item() < 1e-6
+    with pytest.raises(ValueError):
+        fixed_dense_linear_cross_entropy(x, target, w, None, total=torch.ones(2))
+    assert SolveDeltaConfig(fuse_cross_entropy=False, fuse_linear_cross_entropy=True).fuse_linear_cross_entropy
+    with pytest.raises(ValueError):
+        SolveDeltaConfig(fuse_cross_entropy=True, fuse_linear_cross_entropy=True)
+
+
 def test_fixed_denominator_loss_checks_its_arguments():
     x, w = torch.randn(2, 3, 4), torch.randn(5, 4)
     t = torch.zeros(2, 3, dtype=torch.long)
