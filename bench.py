@@ -633,7 +633,20 @@ def run_ours(opts, rank, world, local_rank):
     elif opts.case == "medium":
         w.update(B=8, T=1024)
     B, T, H, r, V = w["B"], w["T"], w["H"], w["r"], w["V"]
-    cpu = make_cpu_inputs(B, T, H, r, V, seed=rank_seed(0, rank))
+    if opts.strong:
+        # strong scaling: ONE workload of B x H streams dealt out over the ranks (batch rows first, then heads);
+        # every rank draws the same inputs and keeps its shard, no data-path collective
+        from solvedelta_b200.sharding import stream_shard
+
+        bs, hs = stream_shard(B, H, rank, world)
+        full = make_cpu_inputs(B, T, H, r, V, seed=0)
+        cpu = {k: (v[bs][:, hs] if k in ("C0", "S0", "dC_T", "dS_T") else v[bs][:, :, hs]).contiguous()
+               for k, v in full.items()}
+        job_tokens = B * T
+        B, H = cpu["u"].shape[0], cpu["u"].shape[2]
+    else:
+        cpu = make_cpu_inputs(B, T, H, r, V, seed=rank_seed(0, rank))
+        job_tokens = world * B * T
     runner = DeviceStep(cpu, device)
 
     def barrier():
@@ -662,7 +675,7 @@ def run_ours(opts, rank, world, local_rank):
         block_ms.append(max_over_ranks(e0.elapsed_time(e1), device) / opts.steps)
     clocks = sampler.stop() if rank == 0 else None
     ms_step = sorted(block_ms)[len(block_ms) // 2]
-    value = job_throughput(runner.tokens, ms_step * 1e-3, world)
+    value = job_tokens / (ms_step * 1e-3)
 
     # ---- forward only (the kernel-level forward configuration), same inputs ----
     for _ in range(3):
@@ -818,9 +831,10 @@ def run_ours(opts, rank, world, local_rank):
                             "sample": f"B={rows} of {B}, first {tokens} of {T} tokens, H={H}, fwd+bwd once ({secs:.1f} s)"}
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": opts.steps,
-            "warmup": max(opts.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": max(opts.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong" if opts.strong else "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"operator fwd+bwd, B={B} per GPU, H={H}, T={T}, r=V={r}, chunk=64, "
+            "config": {"workload": f"operator fwd+bwd, B={B}{' x H=' + str(H) + ' streams on this rank of one B=8, H=8 job' if opts.strong else ' per GPU'}, H={H}, T={T}, r=V={r}, chunk=64, "
                                    "non-zero C0/S0 and state cotangents",
                        "l2": "inputs of one step (0.7 GB) exceed the 126 MB L2; no flush needed",
                        "arithmetic": "bf16 operands, tf32 tensor-core contractions, fp32 states",
@@ -930,6 +944,9 @@ def main():
     ap.add_argument("--summarize-ncu", metavar="CSV", default=None,
                     help="no GPU work: turn an ncu --csv log of one step's launches (medium case, 1024 chunk tasks) "
                          "into the DRAM table of profiles/ on stdout")
+    ap.add_argument("--strong", action="store_true",
+                    help="strong scaling: the B x H streams of ONE workload are dealt out over the ranks "
+                         "(default: weak scaling, every rank its own B=8 batch)")
     ap.add_argument("--ddp-mode", default="graphed", choices=["bucketed", "graphed"],
                     help="--model-ddp only: bucketed all-reduces overlapped with an eager backward, or one flat "
                          "all-reduce after a graph-replayed step")
