@@ -333,6 +333,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_exterior_fwd(FwdParams p
     cp_commit();
     load_norm_panel<FAST, PRED>(p.k, ch, r, s_kh, nullptr);
     load_norm_panel<FAST, PRED>(p.u, ch, r, s_un, nullptr);
+    if (!PRED) {   // rows the per-token pass of the exterior half reads from HBM much later: pull them into L2 now
+        prefetch_rows(p.q, ch, 2, r * 2);
+        prefetch_rows(p.er, ch, 2, r * 2);
+        prefetch_rows(p.wr, ch, 2, V * 2);
+        prefetch_rows(p.v, ch, 2, V * 2);
+    }
     cp_wait<2>();
     __syncthreads();
     SD_PHASE(p.g, ph);
