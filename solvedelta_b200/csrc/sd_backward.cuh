@@ -541,6 +541,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_bwd(BwdParams p) {
     async_bpanel(b_dg, bpanel_ptr(p.DG, ch.gi));
     async_panel_f32(s_G, gG);
     cp_commit();
+    // read much later: the partial cotangents of the exterior and the pair matrix of the forward pass
+    prefetch_region(bpanel_ptr(p.dkPart, ch.gi), CL * DP * 2);
+    prefetch_region(bpanel_ptr(p.dDelta, ch.gi), CL * DP * 2);
+    prefetch_region(mat_ptr(p.Npair, ch.gi), CL * CL * 4);
     load_gamma(p.gam, ch, s_gam);
     block_decay_tables(s_beta, nullptr, s_fastw, fG);
     {   // BF16 copy of 1 / beta for the fast diagonal pair blocks (0 where the block is not fast)
