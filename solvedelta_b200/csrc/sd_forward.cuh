@@ -447,10 +447,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_exterior_fwd(FwdParams p
         for (int pp = 0; pp < ROW_PASSES; ++pp) {
             const int i = balanced_row(lr, pp), i0 = i & ~(BT - 1);
             float uh[8], kh[8], qh[8], dl[8], d[8], er[8], wr[8], v[8], G[8], Gp[8], se[8];
-            load8_norm<FAST>(p.u, ch, i, c0, r, uh);
             load8_norm<FAST>(p.k, ch, i, c0, r, kh);
             load8_norm<FAST>(p.q, ch, i, c0, r, qh);
-            load8_panel(gDelta, i, c0, dl);
+            if (all_fast) {
+                // u^ and Delta of this row are still in shared memory (u^ centred on its block end, undone here;
+                // the factor is at most exp(60) on a fast block); this thread overwrites exactly these elements below
+                float Gi[8], Ge[8];
+                load8_smem(s_un, i, c0, uh);
+                load8_smem(s_G, i, c0, Gi);
+                load8_smem(s_G, i0 + BT - 1, c0, Ge);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) uh[e] *= __expf(Gi[e] - Ge[e]);
+                load8_smem(s_dl, i, c0, dl);
+            } else {
+                load8_norm<FAST>(p.u, ch, i, c0, r, uh);
+                load8_panel(gDelta, i, c0, dl);
+            }
             load8_bf16<FAST>(row_bf16(p.er, ch, i), c0, r, p.er.vec, ch.ok(i), er);
             load8_bf16<FAST>(row_bf16(p.wr, ch, i), c0, V, p.wr.vec, ch.ok(i), wr);
             load8_bf16<FAST>(row_bf16(p.v, ch, i), c0, V, p.v.vec, ch.ok(i), v);
