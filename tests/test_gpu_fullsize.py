@@ -64,6 +64,36 @@ def test_streams_are_independent(workload):
     assert torch.equal(finp.S, fin.S[perm]) and torch.equal(finp.predictor, fin.predictor[perm])
 
 
+@pytest.mark.parametrize("world", [2, 8, 16])
+def test_stream_shards_of_the_product_reassemble_the_full_run(workload, world):
+    """The strong-scaling layout of bench.py --strong on one GPU: every rank's shard (batch rows first, then
+    heads) run through the operator, forward and VJP, and put back together, is bit-equal to the full run."""
+    from solvedelta_b200.sharding import stream_shard
+
+    _, dev = workload
+    names = NAMES
+
+    def fwd_bwd(d):
+        leaves = [d[n].detach().requires_grad_() for n in names]
+        state = SolveDeltaState(d["C0"].detach().requires_grad_(), d["S0"].detach().requires_grad_())
+        y, fin = solvedelta_native(*leaves, initial_state=state, return_final_state=True)
+        grads = torch.autograd.grad((y, fin.predictor, fin.S), leaves + list(state), (d["dy"], d["dC_T"], d["dS_T"]))
+        return y.detach(), fin.predictor.detach(), fin.S.detach(), grads
+
+    y, C, S, grads = fwd_bwd(dev)
+    B, H = y.shape[0], y.shape[2]
+    for rank in range(world):
+        bs, hs = stream_shard(B, H, rank, world)
+        part = {k: (v[bs][:, hs] if k in ("C0", "S0", "dC_T", "dS_T") else v[bs][:, :, hs]).contiguous()
+                for k, v in dev.items()}
+        yp, Cp, Sp, gp = fwd_bwd(part)
+        assert torch.equal(yp, y[bs][:, :, hs])
+        assert torch.equal(Cp, C[bs][:, hs]) and torch.equal(Sp, S[bs][:, hs])
+        for full, got, name in zip(grads, gp, list(names) + ["C0", "S0"]):
+            want = full[bs][:, hs] if name in ("C0", "S0") else full[bs][:, :, hs]
+            assert torch.equal(got, want), name
+
+
 def _zero_geometry(workload):
     """The benchmark workload with the geometry rate at zero and no initial predictor state: the operator
     is then exactly the GDN2 edit / read (upstream tests/core/test_rebuild_semantics.py:296-316)."""
