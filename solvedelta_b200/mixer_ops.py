@@ -31,14 +31,15 @@ def _require_bf16_cuda(name, t):
 
 class _Conv4Silu(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, initial_state, want_state, valid=None, reset=None):
+    def forward(ctx, x, weight, initial_state, want_state, valid=None, reset=None, inplace=False):
         lib = _lib.load()
         B, T, D = x.shape
         w32 = weight.detach().float().contiguous()
         init = None if initial_state is None else initial_state.detach().to(torch.bfloat16).contiguous()
         with torch.cuda.device(x.device):
             y = torch.empty(B, T, D, dtype=torch.bfloat16, device=x.device)
-            fin = torch.empty(B, D, 3, dtype=torch.bfloat16, device=x.device) if want_state else None
+            # in place: a thread reads the three state entries of its channels before it writes them (one tile)
+            fin = (init if inplace else torch.empty(B, D, 3, dtype=torch.bfloat16, device=x.device)) if want_state else None
             a = _lib.Conv4ForwardArgs(B, T, D, x.data_ptr(), x.stride(0), x.stride(1), w32.data_ptr(),
                                       None if init is None else init.data_ptr(), y.data_ptr(),
                                       None if fin is None else fin.data_ptr(),
@@ -61,7 +62,7 @@ class _Conv4Silu(torch.autograd.Function):
         B, T, D = x.shape
         if dy is None:
             return (torch.zeros_like(x), torch.zeros(D, 4, dtype=ctx.weight_dtype, device=x.device), None, None,
-                    None, None)
+                    None, None, None)
         dy = dy.to(torch.bfloat16).contiguous()
         valid, reset = ctx.masks
         with torch.cuda.device(x.device):
@@ -76,7 +77,7 @@ class _Conv4Silu(torch.autograd.Function):
                                        None if valid is None else valid.data_ptr(),
                                        None if reset is None else reset.data_ptr())
             _lib.check(lib.sd_conv4_silu_backward(ctypes.byref(a), _stream(x.device)))
-        return dx, dw.to(ctx.weight_dtype), dinit, None, None, None
+        return dx, dw.to(ctx.weight_dtype), dinit, None, None, None, None
 
 
 def _conv_mask(name: str, mask: Optional[torch.Tensor], x: torch.Tensor) -> Optional[torch.Tensor]:
@@ -92,7 +93,8 @@ def _conv_mask(name: str, mask: Optional[torch.Tensor], x: torch.Tensor) -> Opti
 
 def conv4_silu(x: torch.Tensor, weight: torch.Tensor, initial_state: Optional[torch.Tensor] = None,
                return_final_state: bool = False, valid_mask: Optional[torch.Tensor] = None,
-               reset_mask: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+               reset_mask: Optional[torch.Tensor] = None, _inplace_state: bool = False
+               ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """Depthwise causal conv (4 taps, tap 3 = current token) + SiLU over [B,T,D] BF16 rows
     (any batch/token strides, unit channel stride) with a carried [B,D,3] state.
 
@@ -116,7 +118,11 @@ def conv4_silu(x: torch.Tensor, weight: torch.Tensor, initial_state: Optional[to
             fin = (initial_state.to(torch.bfloat16) if initial_state is not None
                    else x.new_zeros(x.shape[0], x.shape[2], 3))
         return x.new_zeros(x.shape), fin
-    return _Conv4Silu.apply(x, weight, initial_state, return_final_state, valid, reset)
+    # a cache that owns its state may have a single-token no-grad step update it in place
+    inplace = (_inplace_state and return_final_state and initial_state is not None and x.shape[1] == 1
+               and not torch.is_grad_enabled() and valid is None and reset is None
+               and initial_state.dtype == torch.bfloat16 and initial_state.is_contiguous())
+    return _Conv4Silu.apply(x, weight, initial_state, return_final_state, valid, reset, inplace)
 
 
 def conv4_silu_segmented(x: torch.Tensor, weight: torch.Tensor, plan, initial_state: Optional[torch.Tensor] = None,

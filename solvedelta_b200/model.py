@@ -125,7 +125,7 @@ class SolveDelta(nn.Module):
     def forward(self, hidden_states: torch.Tensor, *, initial_state: Optional[SolveDeltaLayerState] = None,
                 valid_mask: Optional[torch.Tensor] = None, reset_mask: Optional[torch.Tensor] = None,
                 geometry_enabled: bool = True, associative_decay_enabled: bool = True,
-                return_final_state: bool = False):
+                return_final_state: bool = False, inplace_state: bool = False):
         if hidden_states.ndim != 3:
             raise ValueError("hidden_states must have shape [B,T,hidden_size]")
         batch, length, hidden_width = hidden_states.shape
@@ -160,7 +160,7 @@ class SolveDelta(nn.Module):
         piece = lambda i: pieces[i]
         if self.config.use_short_conv:
             qkv, final_conv = conv4_silu(qkv_in, self.conv_weight, conv_state, return_final_state,
-                                         valid_mask, reset_mask)
+                                         valid_mask, reset_mask, _inplace_state=inplace_state)
             q_raw, key_raw, value_raw = qkv.split(sizes[:3], dim=-1)
         else:
             q_raw, key_raw, value_raw = (F.silu(piece(i)) for i in range(3))
@@ -182,9 +182,10 @@ class SolveDelta(nn.Module):
             log_decay = torch.zeros_like(log_decay)
         operator_initial = initial_state.operator if initial_state is not None else None
         if not masked:
+            extra = {"_inplace_state": True} if inplace_state else {}   # the public signature is upstream's
             output, operator_state = solvedelta_native(
                 u, h, q, keys, values, log_decay, erase_raw, write_raw, geometry_write,
-                initial_state=operator_initial, return_final_state=return_final_state)
+                initial_state=operator_initial, return_final_state=return_final_state, **extra)
         else:
             output, operator_state = solvedelta_masked_native(
                 u, h, q, keys, values, log_decay, erase_raw, write_raw, geometry_write,

@@ -183,10 +183,12 @@ class SolveDeltaCacheAdapter(nn.Module):
         batch, length = hidden_states.shape[:2]
         carried = None if past_key_values is None else past_key_values.layer_state(self.layer_idx)
         keep_state = past_key_values is not None and bool(use_cache)
+        # a cached single-token step without gradients updates the cache's own tensors in place
+        inplace = keep_state and carried is not None and length == 1 and not torch.is_grad_enabled()
         mixed = self.mixer(hidden_states, initial_state=carried,
                            valid_mask=self._valid_tokens(attention_mask, batch, length),
                            reset_mask=self._reset_tokens(hidden_states, carried is not None, kwargs),
-                           return_final_state=keep_state)
+                           return_final_state=keep_state, inplace_state=inplace)
         if not keep_state:
             return mixed, past_key_values
         output, after = mixed
@@ -437,9 +439,11 @@ class GraphedDecoder:
         out = self.model(input_ids=self.token, past_key_values=self.cache, use_cache=True, logits_to_keep=1)
         for state, (C, S, conv) in zip(self.cache.states, self.static):
             new_C, new_S = state["recurrent_state"]
-            C.copy_(new_C)
-            S.copy_(new_S)
-            if conv is not None:
+            if new_C.data_ptr() != C.data_ptr():   # the step updates the static tensors in place when it can
+                C.copy_(new_C)
+            if new_S.data_ptr() != S.data_ptr():
+                S.copy_(new_S)
+            if conv is not None and state["conv_state"].data_ptr() != conv.data_ptr():
                 conv.copy_(state["conv_state"])
         self._point_cache_at_static()
         return out.logits

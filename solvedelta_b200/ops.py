@@ -266,16 +266,18 @@ def oja_residual(target: torch.Tensor, source: torch.Tensor, beta: torch.Tensor,
     return action, update, (final if output_final_state else None)
 
 
-def _decode_step(u, h, q, k, v, log_decay, erase_raw, write_raw, gamma, C0, S0):
+def _decode_step(u, h, q, k, v, log_decay, erase_raw, write_raw, gamma, C0, S0, inplace=False):
     lib = _lib.load()
     device = u.device
     B, T, H, r = u.shape
     V = v.shape[-1]
     with torch.cuda.device(device):
+        # the kernel updates the cache in place; by default it works on copies, as upstream returns new tensors
+        keep = inplace and C0 is not None and S0 is not None and C0.is_contiguous() and S0.is_contiguous()
         C = (torch.zeros(B, H, r, r, dtype=torch.float32, device=device) if C0 is None
-             else C0.detach().clone(memory_format=torch.contiguous_format))
+             else (C0.detach() if keep else C0.detach().clone(memory_format=torch.contiguous_format)))
         S = (torch.zeros(B, H, r, V, dtype=torch.float32, device=device) if S0 is None
-             else S0.detach().clone(memory_format=torch.contiguous_format))
+             else (S0.detach() if keep else S0.detach().clone(memory_format=torch.contiguous_format)))
         y = torch.empty(B, 1, H, V, dtype=torch.bfloat16, device=device)
         args = _lib.DecodeArgs()
         args.shape = _shape(u, V)
@@ -300,6 +302,7 @@ def solvedelta_residual_frame_native(
     return_final_state: bool = True,
     _valid_mask: Optional[torch.Tensor] = None,
     _reset_mask: Optional[torch.Tensor] = None,
+    _inplace_state: bool = False,
 ) -> Tuple[torch.Tensor, Optional[SolveDeltaState]]:
     """Dense BF16 path from raw gate logits.
 
@@ -368,7 +371,7 @@ def solvedelta_residual_frame_native(
     if length == 1 and not torch.is_grad_enabled() and not masked:
         # single-token recurrent inference (causallsso/ops/residual_frame/operator.py:198-216)
         y, C, S = _decode_step(u, h, q, k4, v4, associative_log_decay, er4, wr4, geometry_write,
-                               predictor_initial, memory_initial)
+                               predictor_initial, memory_initial, inplace=_inplace_state)
         return y, (SolveDeltaState(C, S) if return_final_state else None)
 
     y, C_T, S_T = _SolveDeltaFunction.apply(
@@ -392,10 +395,13 @@ def solvedelta_native(
     *,
     initial_state: Optional[SolveDeltaState] = None,
     return_final_state: bool = False,
+    _inplace_state: bool = False,
 ) -> Tuple[torch.Tensor, Optional[SolveDeltaState]]:
     """Execute dense K=1 SolveDelta from raw fused-projection views.
 
-    Same contract as causallsso/ops/operator.py:13-55.
+    Same contract as causallsso/ops/operator.py:13-55.  ``_inplace_state`` (no upstream counterpart) lets a
+    single-token no-grad step update the tensors of ``initial_state`` in place and return them, for a cache
+    that owns its state; by default the step works on copies, as upstream returns new tensors.
     """
     if u.device.type != "cuda" or u.dtype != torch.bfloat16:
         raise TypeError("solvedelta_native requires BF16 CUDA activations")
@@ -409,7 +415,7 @@ def solvedelta_native(
         raise ValueError("native vector operands require unit innermost stride")
     return solvedelta_residual_frame_native(
         u, h, q, keys, values, associative_log_decay, erase_raw, write_raw, geometry_write,
-        initial_state=initial_state, return_final_state=return_final_state)
+        initial_state=initial_state, return_final_state=return_final_state, _inplace_state=_inplace_state)
 
 
 def solvedelta_segmented_native(
