@@ -105,6 +105,35 @@ typedef struct {
     void *y;                            /* out: BF16 [B,1,H,V] */
 } sd_decode_args;
 
+/*
+ * The whole mixer glue of a cached single-token step in the decode kernel: q, k, v come from
+ * the conv4 + SiLU of the projection row against the carried window (advanced in place,
+ * causallsso/model.py:146-164 at T = 1), the log decay from the decay gate
+ * (-exp(A[h]) softplus(raw + bias), model.py:375-390), the geometry rate from
+ * sigmoid(raw + bias) (model.py:391-394); then the recurrent step of sd_decode_step
+ * (recurrent.py:188-327).  One launch instead of conv, gate, three element-wise kernels and
+ * the step.  No upstream counterpart as a single call.
+ */
+typedef struct {
+    sd_shape shape;                     /* T must be 1 */
+    sd_operand u, h, erase_raw, write_raw;   /* BF16 views of the projection row, widths r,r,r,V */
+    const void *qkv;                    /* BF16 conv input of the token: per batch row 2*H*r + H*V channels (q|k|v) */
+    int64_t qkv_stride_b;               /* elements between batch rows */
+    const float *conv_weight;           /* [D][4] */
+    void *conv_state;                   /* BF16 [B][D][3], in/out */
+    const void *decay_raw;              /* BF16 [B][H*r] */
+    int64_t decay_stride_b;
+    const float *log_rate;              /* [H] */
+    const float *decay_bias;            /* [H*r] */
+    const void *geometry_raw;           /* BF16 [B][H] */
+    int64_t geometry_stride_b;
+    const float *geometry_bias;         /* [H] */
+    float *C, *S;                       /* in/out recurrent cache */
+    void *y;                            /* out: BF16 [B,1,H,V] */
+} sd_mixer_decode_args;
+
+int sd_mixer_decode_step(const sd_mixer_decode_args *args, void *stream);
+
 /* Bytes of the buffer sd_forward fills for sd_backward. */
 size_t sd_saved_bytes(const sd_shape *shape);
 size_t sd_forward_scratch_bytes(const sd_shape *shape);

@@ -108,6 +108,15 @@ class BackwardArgs(ctypes.Structure):
         ("valid_mask", ctypes.c_void_p), ("reset_mask", ctypes.c_void_p)])
 
 
+class MixerDecodeArgs(ctypes.Structure):
+    _fields_ = ([("shape", Shape)] + [(n, Operand) for n in ("u", "h", "erase_raw", "write_raw")] + [
+        ("qkv", ctypes.c_void_p), ("qkv_stride_b", ctypes.c_int64), ("conv_weight", ctypes.c_void_p),
+        ("conv_state", ctypes.c_void_p), ("decay_raw", ctypes.c_void_p), ("decay_stride_b", ctypes.c_int64),
+        ("log_rate", ctypes.c_void_p), ("decay_bias", ctypes.c_void_p), ("geometry_raw", ctypes.c_void_p),
+        ("geometry_stride_b", ctypes.c_int64), ("geometry_bias", ctypes.c_void_p),
+        ("C", ctypes.c_void_p), ("S", ctypes.c_void_p), ("y", ctypes.c_void_p)])
+
+
 class PredictorForwardArgs(ctypes.Structure):
     _fields_ = ([("shape", Shape)] + [(n, Operand) for n in ("target", "source", "query", "beta", "log_decay")] + [
         ("C0", ctypes.c_void_p), ("frame_action", ctypes.c_void_p), ("update", ctypes.c_void_p),
@@ -170,7 +179,7 @@ EXPORTS = (
     "sd_forward", "sd_backward", "sd_decode_step", "sd_forward_launches",
     "sd_backward_launches", "sd_panel_info", "sd_status_string", "sd_version",
     "sd_chunk_tokens", "sd_forward_static", "sd_panel_kind", "sd_device_fault", "sd_device_fault_clear",
-    "sd_predictor_forward", "sd_predictor_backward",
+    "sd_predictor_forward", "sd_predictor_backward", "sd_mixer_decode_step",
     "sd_conv4_backward_scratch_bytes", "sd_conv4_silu_forward", "sd_conv4_silu_backward",
     "sd_kda_gate_backward_scratch_bytes", "sd_kda_gate_forward", "sd_kda_gate_backward",
     "sd_norm_gate_backward_scratch_bytes", "sd_norm_gate_forward", "sd_norm_gate_backward",
@@ -239,6 +248,7 @@ def _declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.sd_norm_gate_backward_scratch_bytes.restype = ctypes.c_size_t
     lib.sd_norm_gate_backward_scratch_bytes.argtypes = [ctypes.c_int64, ctypes.c_int32]
     for name, struct in (("sd_predictor_forward", PredictorForwardArgs), ("sd_predictor_backward", PredictorBackwardArgs),
+                         ("sd_mixer_decode_step", MixerDecodeArgs),
                          ("sd_conv4_silu_forward", Conv4ForwardArgs), ("sd_conv4_silu_backward", Conv4BackwardArgs),
                          ("sd_kda_gate_forward", KdaGateArgs), ("sd_kda_gate_backward", KdaGateArgs),
                          ("sd_norm_gate_forward", NormGateArgs), ("sd_norm_gate_backward", NormGateArgs)):

@@ -267,7 +267,8 @@ cudaError_t configure_kernels() {
     if ((e = allow_smem(k_output_fwd<true, true>, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_output_fwd<false, true>, OUTPUT_FWD_SMEM)) != cudaSuccess) return e;
     if ((e = allow_smem(k_state_scan_tc, SCAN_TC_SMEM_BYTES)) != cudaSuccess) return e;
-    if ((e = allow_smem(k_decode_step, DECODE_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_decode_step<false>, DECODE_SMEM)) != cudaSuccess) return e;
+    if ((e = allow_smem(k_decode_step<true>, DECODE_SMEM)) != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) {
         void* w = nullptr;
         if ((e = cudaGetSymbolAddress(&w, g_scan_fault_word)) != cudaSuccess) return e;
@@ -962,8 +963,44 @@ int sd_decode_step(const sd_decode_args* a, void* stream_) {
     p.S = a->S;
     p.y = a->y;
     if (configure_kernels() != cudaSuccess) return SD_ERR_NO_DEVICE;
-    k_decode_step<<<a->shape.B * a->shape.H, DEC_THREADS, DECODE_SMEM, stream>>>(p);
+    k_decode_step<false><<<a->shape.B * a->shape.H, DEC_THREADS, DECODE_SMEM, stream>>>(p, MixerDecode{});
     mark(stream);
+    return launch_status();
+}
+
+int sd_mixer_decode_step(const sd_mixer_decode_args* a, void* stream_) {
+    if (!a || !shape_ok(&a->shape) || a->shape.T != 1) return SD_ERR_INVALID_ARGUMENT;
+    if (!shape_supported(&a->shape)) return SD_ERR_UNSUPPORTED_SHAPE;
+    const sd_operand ops[] = {a->u, a->h, a->erase_raw, a->write_raw};
+    if (!operands_ok(ops, 4) || !a->C || !a->S || !a->y || !a->qkv || !a->conv_weight || !a->conv_state ||
+        !a->decay_raw || !a->log_rate || !a->decay_bias || !a->geometry_raw || !a->geometry_bias)
+        return SD_ERR_INVALID_ARGUMENT;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    DecodeParams p{};
+    p.g = make_geometry(a->shape);
+    p.u = make_operand(a->u, 2);
+    p.h = make_operand(a->h, 2);
+    p.er = make_operand(a->erase_raw, 2);
+    p.wr = make_operand(a->write_raw, 2);
+    p.q = p.k = p.v = p.u;       // unused by the fused instantiation
+    p.ld = p.gam = p.u;
+    p.C = a->C;
+    p.S = a->S;
+    p.y = a->y;
+    MixerDecode m;
+    m.qkv = reinterpret_cast<const __nv_bfloat16*>(a->qkv);
+    m.qkv_sb = a->qkv_stride_b;
+    m.conv_w = a->conv_weight;
+    m.conv_state = reinterpret_cast<__nv_bfloat16*>(a->conv_state);
+    m.decay_raw = reinterpret_cast<const __nv_bfloat16*>(a->decay_raw);
+    m.decay_sb = a->decay_stride_b;
+    m.log_rate = a->log_rate;
+    m.decay_bias = a->decay_bias;
+    m.geom_raw = reinterpret_cast<const __nv_bfloat16*>(a->geometry_raw);
+    m.geom_sb = a->geometry_stride_b;
+    m.geom_bias = a->geometry_bias;
+    if (configure_kernels() != cudaSuccess) return SD_ERR_NO_DEVICE;
+    k_decode_step<true><<<a->shape.B * a->shape.H, DEC_THREADS, DECODE_SMEM, stream>>>(p, m);
     return launch_status();
 }
 

@@ -11,6 +11,7 @@
 #pragma once
 #include "sd_bf16.cuh"
 #include "sd_common.cuh"
+#include "sd_mixer.cuh"
 
 namespace sd {
 
@@ -20,6 +21,36 @@ struct DecodeParams {
     float *C, *S;
     void* y;
 };
+
+// The mixer glue of a cached single-token step, computed inside the decode kernel (k_decode_step<true>):
+// q, k, v = SiLU(conv4) of the projection row against the carried three-token window, which is advanced in
+// place (causallsso/model.py:146-164 at T = 1); log decay = -exp(A[h]) softplus(raw + bias) (model.py:383-390);
+// geometry rate = sigmoid(raw + bias) (model.py:391-394).  The operands q, k, v, ld, gam of DecodeParams are
+// then unused.
+struct MixerDecode {
+    const __nv_bfloat16* qkv;       // conv input of the token: [B] rows of D = 2 H r + H V channels (q | k | v)
+    long long qkv_sb;               // elements between batch rows
+    const float* conv_w;            // [D][4], tap 3 multiplies the current token
+    __nv_bfloat16* conv_state;      // [B][D][3], oldest first; in/out
+    const __nv_bfloat16* decay_raw; // [B][H*r]
+    long long decay_sb;
+    const float* log_rate;          // [H]
+    const float* decay_bias;        // [H*r]
+    const __nv_bfloat16* geom_raw;  // [B][H]
+    long long geom_sb;
+    const float* geom_bias;         // [H]
+};
+
+// one conv channel of the token: output (rounded to BF16 as the separate conv kernel stores it), window advanced
+__device__ __forceinline__ float decode_conv_channel(const MixerDecode& m, int b, int D, int chn) {
+    __nv_bfloat16* st = m.conv_state + ((long long)b * D + chn) * 3;
+    const __nv_bfloat16 b0 = st[0], b1 = st[1], b2 = st[2], b3 = m.qkv[(long long)b * m.qkv_sb + chn];
+    const float* w = m.conv_w + chn * 4;
+    const float z = w[0] * __bfloat162float(b0) + w[1] * __bfloat162float(b1) + w[2] * __bfloat162float(b2) +
+                    w[3] * __bfloat162float(b3);
+    st[0] = b1; st[1] = b2; st[2] = b3;
+    return __bfloat162float(__float2bfloat16_rn(silu_f(z)));
+}
 
 constexpr int DEC_THREADS = 512;
 constexpr int DEC_LD = DP + 4;   // row pitch of a shared state (floats)
@@ -66,7 +97,8 @@ __device__ __forceinline__ void decode_state_out(float* g, const float* sm, int 
     }
 }
 
-__global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(DecodeParams p) {
+template <bool MIXER>
+__global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(DecodeParams p, MixerDecode mix) {
     extern __shared__ __align__(16) float dsm[];
     float* sC = dsm;                       // [DP][DEC_LD]
     float* sS = sC + DP * DEC_LD;          // [DP][DEC_LD]
@@ -97,12 +129,27 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(DecodeParams p) 
 
     const bool in_r = tid < r;     // threads 0..r-1 carry the token's channel values
     float u = in_r ? __bfloat162float(row_bf16(p.u, ch, 0)[tid]) : 0.f;
-    float k = in_r ? __bfloat162float(row_bf16(p.k, ch, 0)[tid]) : 0.f;
-    float q = in_r ? __bfloat162float(row_bf16(p.q, ch, 0)[tid]) : 0.f;
     float hv = in_r ? __bfloat162float(row_bf16(p.h, ch, 0)[tid]) : 0.f;
     float er = in_r ? __bfloat162float(row_bf16(p.er, ch, 0)[tid]) : 0.f;
-    float ld = in_r ? row_f32(p.ld, ch, 0)[tid] : 0.f;
-    const float gamma = *row_f32(p.gam, ch, 0);
+    float k = 0.f, q = 0.f, ld = 0.f, gamma, v_mix = 0.f;
+    if (MIXER) {
+        const int H = p.g.H, D = 2 * H * r + H * V;
+        if (in_r) {
+            q = decode_conv_channel(mix, b, D, hh * r + tid);
+            k = decode_conv_channel(mix, b, D, H * r + hh * r + tid);
+            const int hc = hh * r + tid;
+            const float z = __bfloat162float(mix.decay_raw[(long long)b * mix.decay_sb + hc]) + mix.decay_bias[hc];
+            ld = -__expf(mix.log_rate[hh]) * softplus_f(z);
+        }
+        if (tid < V) v_mix = decode_conv_channel(mix, b, D, 2 * H * r + hh * V + tid);
+        const float graw = __bfloat162float(mix.geom_raw[(long long)b * mix.geom_sb + hh]) + mix.geom_bias[hh];
+        gamma = 1.f / (1.f + __expf(-graw));
+    } else {
+        k = in_r ? __bfloat162float(row_bf16(p.k, ch, 0)[tid]) : 0.f;
+        q = in_r ? __bfloat162float(row_bf16(p.q, ch, 0)[tid]) : 0.f;
+        ld = in_r ? row_f32(p.ld, ch, 0)[tid] : 0.f;
+        gamma = *row_f32(p.gam, ch, 0);
+    }
     const float uh = u * rsqrtf(block_sum(u * u, red) + 1e-24f);
     const float kh = k * rsqrtf(block_sum(k * k, red) + 1e-24f);
     const float qh = q * rsqrtf(block_sum(q * q, red) + 1e-24f);
@@ -173,7 +220,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(DecodeParams p) 
         float w = 0.f;
         if (tid < V) {
             const float wr = __bfloat162float(row_bf16(p.wr, ch, 0)[tid]);
-            const float vv = __bfloat162float(row_bf16(p.v, ch, 0)[tid]);
+            const float vv = MIXER ? v_mix : __bfloat162float(row_bf16(p.v, ch, 0)[tid]);
             w = sigmoidf_(wr) * vv - ((s_part[tid] + s_part[DP + tid]) + (s_part[2 * DP + tid] + s_part[3 * DP + tid]));
         }
         s_w[tid] = w;

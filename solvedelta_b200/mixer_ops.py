@@ -134,6 +134,58 @@ def conv4_silu_segmented(x: torch.Tensor, weight: torch.Tensor, plan, initial_st
     return conv4_silu(x, weight, initial_state, return_final_state, plan.valid_mask, plan.reset_mask)
 
 
+@torch.no_grad()
+def mixer_decode_step(u: torch.Tensor, h: torch.Tensor, erase_raw: torch.Tensor, write_raw: torch.Tensor,
+                      qkv: torch.Tensor, conv_weight: torch.Tensor, conv_state: torch.Tensor,
+                      decay_raw: torch.Tensor, log_rate: torch.Tensor, decay_bias: torch.Tensor,
+                      geometry_raw: torch.Tensor, geometry_bias: torch.Tensor,
+                      predictor: torch.Tensor, memory: torch.Tensor) -> torch.Tensor:
+    """One cached token of the mixer between its projections, in ONE launch: conv4 + SiLU of the q | k | v slice
+    against ``conv_state`` (advanced in place), the decay gate, the geometry rate and the recurrent step on
+    ``predictor`` / ``memory`` (updated in place).  ``u, h`` are ``[B,1,H,r]`` and ``erase_raw, write_raw``
+    ``[B,1,H,r|V]`` views of the projection row, ``qkv`` ``[B,1,D]``, ``decay_raw`` ``[B,1,H,r]``, ``geometry_raw``
+    ``[B,1,H]``; FP32 ``conv_weight [D,4]``, ``log_rate [H]``, ``decay_bias [H*r]``, ``geometry_bias [H]``.
+    Returns the output row ``[B,1,H,V]`` (BF16).  Same arithmetic as ``conv4_silu`` + ``kda_decay_gate`` +
+    ``sigmoid`` + the T = 1 branch of ``solvedelta_native``."""
+    lib = _lib.load()
+    B, T, H, r = u.shape
+    V = write_raw.shape[-1]
+    if T != 1:
+        raise ValueError("mixer_decode_step takes exactly one token")
+    for name, t in (("u", u), ("h", h), ("erase_raw", erase_raw), ("write_raw", write_raw), ("qkv", qkv),
+                    ("decay_raw", decay_raw), ("geometry_raw", geometry_raw), ("conv_state", conv_state)):
+        _require_bf16_cuda(name, t)
+    for name, t in (("conv_weight", conv_weight), ("log_rate", log_rate), ("decay_bias", decay_bias),
+                    ("geometry_bias", geometry_bias), ("predictor", predictor), ("memory", memory)):
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            raise TypeError(f"{name} must be contiguous FP32")
+    D = 2 * H * r + H * V
+    if qkv.shape != (B, 1, D) or conv_state.shape != (B, D, 3) or not conv_state.is_contiguous():
+        raise ValueError("qkv must be [B,1,D] and conv_state contiguous [B,D,3] with D = 2*H*r + H*V")
+    if qkv.stride(-1) != 1 or decay_raw.stride(-1) != 1 or geometry_raw.stride(-1) != 1:
+        raise ValueError("row operands require unit innermost stride")
+
+    def operand(t):
+        return _lib.Operand(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
+
+    with torch.cuda.device(u.device):
+        y = torch.empty(B, 1, H, V, dtype=torch.bfloat16, device=u.device)
+        a = _lib.MixerDecodeArgs()
+        a.shape = _lib.Shape(B, 1, H, r, V)
+        a.u, a.h = operand(u), operand(h)
+        a.erase_raw, a.write_raw = operand(erase_raw), operand(write_raw)
+        a.qkv, a.qkv_stride_b = qkv.data_ptr(), qkv.stride(0)
+        a.conv_weight, a.conv_state = conv_weight.data_ptr(), conv_state.data_ptr()
+        decay2 = decay_raw.reshape(B, H * r) if decay_raw.is_contiguous() else decay_raw.contiguous().view(B, H * r)
+        a.decay_raw, a.decay_stride_b = decay2.data_ptr(), decay2.stride(0)
+        a.log_rate, a.decay_bias = log_rate.data_ptr(), decay_bias.data_ptr()
+        a.geometry_raw, a.geometry_stride_b = geometry_raw.data_ptr(), geometry_raw.stride(0)
+        a.geometry_bias = geometry_bias.data_ptr()
+        a.C, a.S, a.y = predictor.data_ptr(), memory.data_ptr(), y.data_ptr()
+        _lib.check(lib.sd_mixer_decode_step(ctypes.byref(a), _stream(u.device)))
+    return y
+
+
 class _KdaGate(torch.autograd.Function):
     @staticmethod
     def forward(ctx, raw, log_rate, bias):
@@ -293,4 +345,5 @@ def rms_norm_gated(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, ep
     return _NormGate.apply(x, gate, weight, eps)
 
 
-__all__ = ["conv4_silu", "conv4_silu_segmented", "kda_decay_gate", "rms_norm_gated", "rms_norm_gated_linear"]
+__all__ = ["conv4_silu", "conv4_silu_segmented", "kda_decay_gate", "mixer_decode_step", "rms_norm_gated",
+           "rms_norm_gated_linear"]

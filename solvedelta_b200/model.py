@@ -24,7 +24,7 @@ import torch.nn.functional as F
 from torch import nn
 
 from .config import SolveDeltaConfig
-from .mixer_ops import conv4_silu, kda_decay_gate, rms_norm_gated, rms_norm_gated_linear
+from .mixer_ops import conv4_silu, kda_decay_gate, mixer_decode_step, rms_norm_gated, rms_norm_gated_linear
 from .ops import SolveDeltaState, solvedelta_masked_native, solvedelta_native
 
 
@@ -122,6 +122,30 @@ class SolveDelta(nn.Module):
         bias = None if layer.bias is None else layer.bias.to(x.dtype)
         return F.linear(x, layer.weight.to(x.dtype), bias)
 
+    def _fp32_copy(self, name: str) -> torch.Tensor:
+        """Contiguous FP32 copy of a parameter for the fused decode kernel, refreshed when the parameter changes."""
+        parameter = getattr(self, name)
+        if parameter.dtype == torch.float32 and parameter.is_contiguous():
+            return parameter.detach()
+        cache = self.__dict__.setdefault("_fp32_copies", {})
+        key = (parameter.data_ptr(), parameter._version)
+        hit = cache.get(name)
+        if hit is None or hit[0] != key:
+            hit = (key, parameter.detach().float().contiguous())
+            cache[name] = hit
+        return hit[1]
+
+    def _fused_decode_applies(self, inplace_state, masked, length, initial_state, geometry_enabled,
+                              associative_decay_enabled, return_final_state) -> bool:
+        if not (inplace_state and return_final_state and not masked and length == 1 and self.config.use_short_conv
+                and geometry_enabled and associative_decay_enabled and not torch.is_grad_enabled()):
+            return False
+        if initial_state is None or initial_state.conv is None or initial_state.operator is None:
+            return False
+        conv, (C, S) = initial_state.conv, initial_state.operator
+        return (conv.dtype == torch.bfloat16 and conv.is_contiguous() and C.dtype == torch.float32
+                and S.dtype == torch.float32 and C.is_contiguous() and S.is_contiguous())
+
     def forward(self, hidden_states: torch.Tensor, *, initial_state: Optional[SolveDeltaLayerState] = None,
                 valid_mask: Optional[torch.Tensor] = None, reset_mask: Optional[torch.Tensor] = None,
                 geometry_enabled: bool = True, associative_decay_enabled: bool = True,
@@ -158,6 +182,21 @@ class SolveDelta(nn.Module):
         else:
             pieces = _SplitRow.apply(row, tuple(sizes))
         piece = lambda i: pieces[i]
+        view = lambda x, size: x.unflatten(-1, (heads, size))  # stays a view of the projection row
+        if self._fused_decode_applies(inplace_state, masked, length, initial_state, geometry_enabled,
+                                      associative_decay_enabled, return_final_state):
+            # cached single-token step: conv, decay gate, geometry rate and the recurrent step in one launch, the
+            # cache's conv window and operator states updated in place
+            associative_raw = self._linear(self.decay_proj, piece(8)).view(batch, length, heads, width)
+            output_gate = self._linear(self.output_gate_proj, piece(9)).view(batch, length, heads, value_width)
+            operator = initial_state.operator
+            output = mixer_decode_step(
+                view(piece(3), width), view(piece(4), width), view(piece(5), width), view(piece(6), value_width),
+                qkv_in, self._fp32_copy("conv_weight"), initial_state.conv, associative_raw,
+                self._fp32_copy("associative_log_rate"), self._fp32_copy("associative_decay_bias").reshape(-1),
+                piece(7), self._fp32_copy("geometry_write_bias"), operator.predictor, operator.S)
+            result = self.output_norm.forward_linear(output, output_gate, self.output_proj)
+            return result, SolveDeltaLayerState(SolveDeltaState(operator.predictor, operator.S), initial_state.conv)
         if self.config.use_short_conv:
             qkv, final_conv = conv4_silu(qkv_in, self.conv_weight, conv_state, return_final_state,
                                          valid_mask, reset_mask, _inplace_state=inplace_state)
@@ -165,7 +204,6 @@ class SolveDelta(nn.Module):
         else:
             q_raw, key_raw, value_raw = (F.silu(piece(i)) for i in range(3))
             final_conv = None
-        view = lambda x, size: x.unflatten(-1, (heads, size))  # stays a view of the projection row
         u, h = view(piece(3), width), view(piece(4), width)
         q = view(q_raw, width)
         keys = view(key_raw, width).unsqueeze(-2)

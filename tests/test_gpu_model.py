@@ -367,3 +367,33 @@ def test_fused_linear_cross_entropy_head_gives_the_same_loss_and_gradients():
     for (name, a), (_, b) in zip(plain.named_parameters(), fused.named_parameters()):
         scale = float(a.grad.float().abs().max().clamp_min(1e-12))
         assert float((a.grad.float() - b.grad.float()).abs().max()) <= 3e-2 * scale, name
+
+
+def test_fused_single_token_step_equals_the_separate_kernels(medium, monkeypatch):
+    """A cached one-token step runs conv, decay gate, geometry rate and the recurrent step as ONE launch
+    that updates the cache in place; with that path switched off the separate kernels give the same logits
+    and leave the same cache."""
+    from solvedelta_b200.model import SolveDelta
+
+    config, model = medium
+    ids = torch.randint(0, config.vocab_size, (2, 70), device="cuda")
+
+    def run(fused):
+        if not fused:
+            monkeypatch.setattr(SolveDelta, "_fused_decode_applies", lambda self, *a, **k: False)
+        with torch.no_grad():
+            step = model(input_ids=ids[:, :60], use_cache=True)
+            cache, logits = step.past_key_values, []
+            for t in range(60, 70):
+                step = model(input_ids=ids[:, t:t + 1], past_key_values=cache, use_cache=True)
+                logits.append(step.logits.float())
+        monkeypatch.undo()
+        return torch.cat(logits, 1), cache
+
+    fused_logits, fused_cache = run(True)
+    plain_logits, plain_cache = run(False)
+    assert rel_l2(fused_logits.cpu().numpy(), plain_logits.cpu().numpy()) < 2e-3
+    for a, b in zip(fused_cache.states, plain_cache.states):
+        for x, y in zip(a["recurrent_state"], b["recurrent_state"]):
+            assert float((x - y).abs().max()) <= 1e-4 * float(y.abs().max())
+        assert torch.equal(a["conv_state"], b["conv_state"])   # the window is a copy of BF16 inputs
