@@ -111,8 +111,8 @@ typedef struct {
  * causallsso/model.py:146-164 at T = 1), the log decay from the decay gate
  * (-exp(A[h]) softplus(raw + bias), model.py:375-390), the geometry rate from
  * sigmoid(raw + bias) (model.py:391-394); then the recurrent step of sd_decode_step
- * (recurrent.py:188-327).  One launch instead of conv, gate, three element-wise kernels and
- * the step.  No upstream counterpart as a single call.
+ * (recurrent.py:188-327), optionally followed by the gated RMSNorm of the output row.  One
+ * launch instead of conv, gate, three element-wise kernels, the step and the norm.  No upstream counterpart as a single call.
  */
 typedef struct {
     sd_shape shape;                     /* T must be 1 */
@@ -130,6 +130,12 @@ typedef struct {
     const float *geometry_bias;         /* [H] */
     float *C, *S;                       /* in/out recurrent cache */
     void *y;                            /* out: BF16 [B,1,H,V] */
+    /* optional: the sigmoid-gated RMSNorm of the output row (causallsso/ops/norm_gate.py:19-43),
+     * y <- y rsqrt(mean(y^2) + eps) w sigmoid(gate); norm_weight NULL = off */
+    const float *norm_weight;           /* [V] or NULL */
+    float norm_eps;
+    const void *output_gate;            /* BF16 [B][H*V] */
+    int64_t output_gate_stride_b;
 } sd_mixer_decode_args;
 
 int sd_mixer_decode_step(const sd_mixer_decode_args *args, void *stream);

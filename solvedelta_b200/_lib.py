@@ -114,7 +114,9 @@ class MixerDecodeArgs(ctypes.Structure):
         ("conv_state", ctypes.c_void_p), ("decay_raw", ctypes.c_void_p), ("decay_stride_b", ctypes.c_int64),
         ("log_rate", ctypes.c_void_p), ("decay_bias", ctypes.c_void_p), ("geometry_raw", ctypes.c_void_p),
         ("geometry_stride_b", ctypes.c_int64), ("geometry_bias", ctypes.c_void_p),
-        ("C", ctypes.c_void_p), ("S", ctypes.c_void_p), ("y", ctypes.c_void_p)])
+        ("C", ctypes.c_void_p), ("S", ctypes.c_void_p), ("y", ctypes.c_void_p),
+        ("norm_weight", ctypes.c_void_p), ("norm_eps", ctypes.c_float), ("output_gate", ctypes.c_void_p),
+        ("output_gate_stride_b", ctypes.c_int64)])
 
 
 class PredictorForwardArgs(ctypes.Structure):

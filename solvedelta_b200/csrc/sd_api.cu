@@ -999,6 +999,11 @@ int sd_mixer_decode_step(const sd_mixer_decode_args* a, void* stream_) {
     m.geom_raw = reinterpret_cast<const __nv_bfloat16*>(a->geometry_raw);
     m.geom_sb = a->geometry_stride_b;
     m.geom_bias = a->geometry_bias;
+    m.norm_w = a->norm_weight;
+    m.norm_eps = a->norm_eps;
+    m.gate = reinterpret_cast<const __nv_bfloat16*>(a->output_gate);
+    m.gate_sb = a->output_gate_stride_b;
+    if (m.norm_w != nullptr && m.gate == nullptr) return SD_ERR_INVALID_ARGUMENT;
     if (configure_kernels() != cudaSuccess) return SD_ERR_NO_DEVICE;
     k_decode_step<true><<<a->shape.B * a->shape.H, DEC_THREADS, DECODE_SMEM, stream>>>(p, m);
     return launch_status();

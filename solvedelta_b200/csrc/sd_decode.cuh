@@ -39,6 +39,11 @@ struct MixerDecode {
     const __nv_bfloat16* geom_raw;  // [B][H]
     long long geom_sb;
     const float* geom_bias;         // [H]
+    // optional (norm_w != null): the sigmoid-gated RMSNorm of the output row (causallsso/ops/norm_gate.py:19-43)
+    const float* norm_w;            // [V]
+    float norm_eps;
+    const __nv_bfloat16* gate;      // [B][H*V]
+    long long gate_sb;
 };
 
 // one conv channel of the token: output (rounded to BF16 as the separate conv kernel stores it), window advanced
@@ -240,9 +245,18 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(DecodeParams p, 
     }
     __syncthreads();
     decode_state_out(S, sS, r, V, vecS);
+    float yv = 0.f;   // the output element of this thread, rounded to BF16 as the operator returns it
     if (tid < V)
-        reinterpret_cast<__nv_bfloat16*>(p.y)[(long long)s * V + tid] =
-            __float2bfloat16_rn((s_part[tid] + s_part[DP + tid]) + (s_part[2 * DP + tid] + s_part[3 * DP + tid]));
+        yv = __bfloat162float(__float2bfloat16_rn((s_part[tid] + s_part[DP + tid]) +
+                                                  (s_part[2 * DP + tid] + s_part[3 * DP + tid])));
+    if (MIXER && mix.norm_w != nullptr) {   // kernel-uniform
+        const float rstd = rsqrtf(block_sum(yv * yv, red) / V + mix.norm_eps);
+        if (tid < V) {
+            const float g = __bfloat162float(mix.gate[(long long)b * mix.gate_sb + hh * V + tid]);
+            yv = yv * rstd * mix.norm_w[tid] * sigmoidf_(g);
+        }
+    }
+    if (tid < V) reinterpret_cast<__nv_bfloat16*>(p.y)[(long long)s * V + tid] = __float2bfloat16_rn(yv);
 }
 
 }  // namespace sd

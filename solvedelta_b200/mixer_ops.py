@@ -139,14 +139,16 @@ def mixer_decode_step(u: torch.Tensor, h: torch.Tensor, erase_raw: torch.Tensor,
                       qkv: torch.Tensor, conv_weight: torch.Tensor, conv_state: torch.Tensor,
                       decay_raw: torch.Tensor, log_rate: torch.Tensor, decay_bias: torch.Tensor,
                       geometry_raw: torch.Tensor, geometry_bias: torch.Tensor,
-                      predictor: torch.Tensor, memory: torch.Tensor) -> torch.Tensor:
+                      predictor: torch.Tensor, memory: torch.Tensor, *, output_gate: Optional[torch.Tensor] = None,
+                      norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 1e-6) -> torch.Tensor:
     """One cached token of the mixer between its projections, in ONE launch: conv4 + SiLU of the q | k | v slice
     against ``conv_state`` (advanced in place), the decay gate, the geometry rate and the recurrent step on
     ``predictor`` / ``memory`` (updated in place).  ``u, h`` are ``[B,1,H,r]`` and ``erase_raw, write_raw``
     ``[B,1,H,r|V]`` views of the projection row, ``qkv`` ``[B,1,D]``, ``decay_raw`` ``[B,1,H,r]``, ``geometry_raw``
     ``[B,1,H]``; FP32 ``conv_weight [D,4]``, ``log_rate [H]``, ``decay_bias [H*r]``, ``geometry_bias [H]``.
     Returns the output row ``[B,1,H,V]`` (BF16).  Same arithmetic as ``conv4_silu`` + ``kda_decay_gate`` +
-    ``sigmoid`` + the T = 1 branch of ``solvedelta_native``."""
+    ``sigmoid`` + the T = 1 branch of ``solvedelta_native``; with ``output_gate`` ``[B,1,H,V]`` and FP32
+    ``norm_weight [V]`` the row also passes through ``rms_norm_gated``."""
     lib = _lib.load()
     B, T, H, r = u.shape
     V = write_raw.shape[-1]
@@ -182,6 +184,13 @@ def mixer_decode_step(u: torch.Tensor, h: torch.Tensor, erase_raw: torch.Tensor,
         a.geometry_raw, a.geometry_stride_b = geometry_raw.data_ptr(), geometry_raw.stride(0)
         a.geometry_bias = geometry_bias.data_ptr()
         a.C, a.S, a.y = predictor.data_ptr(), memory.data_ptr(), y.data_ptr()
+        if norm_weight is not None:
+            if output_gate is None or output_gate.dtype != torch.bfloat16 or not output_gate.is_contiguous():
+                raise ValueError("the fused norm needs a contiguous BF16 output_gate [B,1,H,V]")
+            if norm_weight.dtype != torch.float32 or norm_weight.shape != (V,):
+                raise TypeError("norm_weight must be FP32 [V]")
+            a.norm_weight, a.norm_eps = norm_weight.data_ptr(), float(norm_eps)
+            a.output_gate, a.output_gate_stride_b = output_gate.data_ptr(), H * V
         _lib.check(lib.sd_mixer_decode_step(ctypes.byref(a), _stream(u.device)))
     return y
 

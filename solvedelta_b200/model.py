@@ -135,6 +135,18 @@ class SolveDelta(nn.Module):
             cache[name] = hit
         return hit[1]
 
+    def _fp32_norm_weight(self) -> torch.Tensor:
+        weight = self.output_norm.weight
+        if weight.dtype == torch.float32 and weight.is_contiguous():
+            return weight.detach()
+        cache = self.__dict__.setdefault("_fp32_copies", {})
+        key = (weight.data_ptr(), weight._version)
+        hit = cache.get("output_norm.weight")
+        if hit is None or hit[0] != key:
+            hit = (key, weight.detach().float().contiguous())
+            cache["output_norm.weight"] = hit
+        return hit[1]
+
     def _fused_decode_applies(self, inplace_state, masked, length, initial_state, geometry_enabled,
                               associative_decay_enabled, return_final_state) -> bool:
         if not (inplace_state and return_final_state and not masked and length == 1 and self.config.use_short_conv
@@ -194,8 +206,9 @@ class SolveDelta(nn.Module):
                 view(piece(3), width), view(piece(4), width), view(piece(5), width), view(piece(6), value_width),
                 qkv_in, self._fp32_copy("conv_weight"), initial_state.conv, associative_raw,
                 self._fp32_copy("associative_log_rate"), self._fp32_copy("associative_decay_bias").reshape(-1),
-                piece(7), self._fp32_copy("geometry_write_bias"), operator.predictor, operator.S)
-            result = self.output_norm.forward_linear(output, output_gate, self.output_proj)
+                piece(7), self._fp32_copy("geometry_write_bias"), operator.predictor, operator.S,
+                output_gate=output_gate, norm_weight=self._fp32_norm_weight(), norm_eps=self.output_norm.eps)
+            result = self._linear(self.output_proj, output.reshape(batch, length, heads * value_width))
             return result, SolveDeltaLayerState(SolveDeltaState(operator.predictor, operator.S), initial_state.conv)
         if self.config.use_short_conv:
             qkv, final_conv = conv4_silu(qkv_in, self.conv_weight, conv_state, return_final_state,
