@@ -136,6 +136,17 @@ typedef struct {
     float norm_eps;
     const void *output_gate;            /* BF16 [B][H*V] */
     int64_t output_gate_stride_b;
+    /* optional, both or neither (then decay_raw / output_gate above may be NULL): the two small
+     * projections in front of the gates, raw = BF16(W hidden (+ bias)) (causallsso/model.py:369-374);
+     * gate_rank a multiple of 8, at most 128; weights 16-byte aligned; needs the fused norm */
+    int32_t gate_rank;
+    const void *decay_hidden;           /* BF16 [B][gate_rank] */
+    int64_t decay_hidden_stride_b;
+    const void *decay_proj_weight;      /* BF16 [H*r][gate_rank] */
+    const void *gate_hidden;            /* BF16 [B][gate_rank] */
+    int64_t gate_hidden_stride_b;
+    const void *gate_proj_weight;       /* BF16 [H*V][gate_rank] */
+    const void *gate_proj_bias;         /* BF16 [H*V] or NULL */
 } sd_mixer_decode_args;
 
 int sd_mixer_decode_step(const sd_mixer_decode_args *args, void *stream);

@@ -116,7 +116,11 @@ class MixerDecodeArgs(ctypes.Structure):
         ("geometry_stride_b", ctypes.c_int64), ("geometry_bias", ctypes.c_void_p),
         ("C", ctypes.c_void_p), ("S", ctypes.c_void_p), ("y", ctypes.c_void_p),
         ("norm_weight", ctypes.c_void_p), ("norm_eps", ctypes.c_float), ("output_gate", ctypes.c_void_p),
-        ("output_gate_stride_b", ctypes.c_int64)])
+        ("output_gate_stride_b", ctypes.c_int64),
+        ("gate_rank", ctypes.c_int32), ("decay_hidden", ctypes.c_void_p), ("decay_hidden_stride_b", ctypes.c_int64),
+        ("decay_proj_weight", ctypes.c_void_p), ("gate_hidden", ctypes.c_void_p),
+        ("gate_hidden_stride_b", ctypes.c_int64), ("gate_proj_weight", ctypes.c_void_p),
+        ("gate_proj_bias", ctypes.c_void_p)])
 
 
 class PredictorForwardArgs(ctypes.Structure):

@@ -973,7 +973,7 @@ int sd_mixer_decode_step(const sd_mixer_decode_args* a, void* stream_) {
     if (!shape_supported(&a->shape)) return SD_ERR_UNSUPPORTED_SHAPE;
     const sd_operand ops[] = {a->u, a->h, a->erase_raw, a->write_raw};
     if (!operands_ok(ops, 4) || !a->C || !a->S || !a->y || !a->qkv || !a->conv_weight || !a->conv_state ||
-        !a->decay_raw || !a->log_rate || !a->decay_bias || !a->geometry_raw || !a->geometry_bias)
+        !a->log_rate || !a->decay_bias || !a->geometry_raw || !a->geometry_bias)
         return SD_ERR_INVALID_ARGUMENT;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     DecodeParams p{};
@@ -1003,7 +1003,24 @@ int sd_mixer_decode_step(const sd_mixer_decode_args* a, void* stream_) {
     m.norm_eps = a->norm_eps;
     m.gate = reinterpret_cast<const __nv_bfloat16*>(a->output_gate);
     m.gate_sb = a->output_gate_stride_b;
-    if (m.norm_w != nullptr && m.gate == nullptr) return SD_ERR_INVALID_ARGUMENT;
+    m.G = a->gate_rank;
+    m.decay_hidden = reinterpret_cast<const __nv_bfloat16*>(a->decay_hidden);
+    m.decay_w = reinterpret_cast<const __nv_bfloat16*>(a->decay_proj_weight);
+    m.dh_sb = a->decay_hidden_stride_b;
+    m.gate_hidden = reinterpret_cast<const __nv_bfloat16*>(a->gate_hidden);
+    m.gate_w = reinterpret_cast<const __nv_bfloat16*>(a->gate_proj_weight);
+    m.gate_b = reinterpret_cast<const __nv_bfloat16*>(a->gate_proj_bias);
+    m.gh_sb = a->gate_hidden_stride_b;
+    if ((m.decay_w != nullptr) != (m.gate_w != nullptr)) return SD_ERR_INVALID_ARGUMENT;   // both or neither
+    if (m.decay_w != nullptr) {
+        auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+        if (m.G <= 0 || m.G > DP || (m.G & 7) || !m.decay_hidden || !m.gate_hidden || !al(m.decay_w) || !al(m.gate_w))
+            return SD_ERR_INVALID_ARGUMENT;
+        if (m.norm_w == nullptr) return SD_ERR_INVALID_ARGUMENT;   // the fused gate projection feeds the fused norm
+    } else if (m.decay_raw == nullptr) {
+        return SD_ERR_INVALID_ARGUMENT;
+    }
+    if (m.norm_w != nullptr && m.gate == nullptr && m.gate_w == nullptr) return SD_ERR_INVALID_ARGUMENT;
     if (configure_kernels() != cudaSuccess) return SD_ERR_NO_DEVICE;
     k_decode_step<true><<<a->shape.B * a->shape.H, DEC_THREADS, DECODE_SMEM, stream>>>(p, m);
     return launch_status();

@@ -44,7 +44,30 @@ struct MixerDecode {
     float norm_eps;
     const __nv_bfloat16* gate;      // [B][H*V]
     long long gate_sb;
+    // optional (decay_w / gate_w != null): the two small projections in front of the gates are taken here too,
+    // raw = BF16(W hidden (+ bias)) with W [H*r][G] / [H*V][G] (causallsso/model.py:369-374); decay_raw / gate
+    // above are then unused
+    int G;
+    const __nv_bfloat16 *decay_hidden, *decay_w;   // [B][G] (row stride dh_sb), [H*r][G]
+    long long dh_sb;
+    const __nv_bfloat16 *gate_hidden, *gate_w, *gate_b;   // [B][G], [H*V][G], [H*V] or null
+    long long gh_sb;
 };
+
+// BF16(w_row . hidden (+ bias)) with FP32 accumulation; hidden [G] FP32 in shared memory, G a multiple of 8
+__device__ __forceinline__ float decode_row_dot(const __nv_bfloat16* w_row, const float* hidden, int G, float bias) {
+    float acc = 0.f;
+    for (int j = 0; j < G; j += 8) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(w_row + j);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h2[e]);
+            acc = fmaf(f.x, hidden[j + 2 * e], fmaf(f.y, hidden[j + 2 * e + 1], acc));
+        }
+    }
+    return __bfloat162float(__float2bfloat16_rn(acc + bias));
+}
 
 // one conv channel of the token: output (rounded to BF16 as the separate conv kernel stores it), window advanced
 __device__ __forceinline__ float decode_conv_channel(const MixerDecode& m, int b, int D, int chn) {
@@ -137,13 +160,32 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(DecodeParams p, 
     float hv = in_r ? __bfloat162float(row_bf16(p.h, ch, 0)[tid]) : 0.f;
     float er = in_r ? __bfloat162float(row_bf16(p.er, ch, 0)[tid]) : 0.f;
     float k = 0.f, q = 0.f, ld = 0.f, gamma, v_mix = 0.f;
+    float gate_mix = 0.f;   // raw output gate of this thread's value channel (fused projection)
     if (MIXER) {
         const int H = p.g.H, D = 2 * H * r + H * V;
+        float decay_raw_mix = 0.f;
+        if (mix.decay_w != nullptr) {   // kernel-uniform: the two small projections
+            float* s_hid = s_part;      // [2][G]: free until the predictor phase
+            for (int j = tid; j < 2 * mix.G; j += DEC_THREADS) {
+                const bool second = j >= mix.G;
+                const int jj = second ? j - mix.G : j;
+                s_hid[j] = __bfloat162float(second ? mix.gate_hidden[(long long)b * mix.gh_sb + jj]
+                                                   : mix.decay_hidden[(long long)b * mix.dh_sb + jj]);
+            }
+            __syncthreads();
+            if (in_r) decay_raw_mix = decode_row_dot(mix.decay_w + (long long)(hh * r + tid) * mix.G, s_hid, mix.G, 0.f);
+            if (tid < V)
+                gate_mix = decode_row_dot(mix.gate_w + (long long)(hh * V + tid) * mix.G, s_hid + mix.G, mix.G,
+                                          mix.gate_b ? __bfloat162float(mix.gate_b[hh * V + tid]) : 0.f);
+            __syncthreads();   // s_part is reused below
+        }
         if (in_r) {
             q = decode_conv_channel(mix, b, D, hh * r + tid);
             k = decode_conv_channel(mix, b, D, H * r + hh * r + tid);
             const int hc = hh * r + tid;
-            const float z = __bfloat162float(mix.decay_raw[(long long)b * mix.decay_sb + hc]) + mix.decay_bias[hc];
+            const float raw = mix.decay_w != nullptr ? decay_raw_mix
+                                                     : __bfloat162float(mix.decay_raw[(long long)b * mix.decay_sb + hc]);
+            const float z = raw + mix.decay_bias[hc];
             ld = -__expf(mix.log_rate[hh]) * softplus_f(z);
         }
         if (tid < V) v_mix = decode_conv_channel(mix, b, D, 2 * H * r + hh * V + tid);
@@ -252,7 +294,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(DecodeParams p, 
     if (MIXER && mix.norm_w != nullptr) {   // kernel-uniform
         const float rstd = rsqrtf(block_sum(yv * yv, red) / V + mix.norm_eps);
         if (tid < V) {
-            const float g = __bfloat162float(mix.gate[(long long)b * mix.gate_sb + hh * V + tid]);
+            const float g = mix.gate_w != nullptr ? gate_mix
+                                                  : __bfloat162float(mix.gate[(long long)b * mix.gate_sb + hh * V + tid]);
             yv = yv * rstd * mix.norm_w[tid] * sigmoidf_(g);
         }
     }

@@ -140,7 +140,8 @@ def mixer_decode_step(u: torch.Tensor, h: torch.Tensor, erase_raw: torch.Tensor,
                       decay_raw: torch.Tensor, log_rate: torch.Tensor, decay_bias: torch.Tensor,
                       geometry_raw: torch.Tensor, geometry_bias: torch.Tensor,
                       predictor: torch.Tensor, memory: torch.Tensor, *, output_gate: Optional[torch.Tensor] = None,
-                      norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 1e-6) -> torch.Tensor:
+                      norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 1e-6,
+                      gate_projections: Optional[tuple] = None) -> torch.Tensor:
     """One cached token of the mixer between its projections, in ONE launch: conv4 + SiLU of the q | k | v slice
     against ``conv_state`` (advanced in place), the decay gate, the geometry rate and the recurrent step on
     ``predictor`` / ``memory`` (updated in place).  ``u, h`` are ``[B,1,H,r]`` and ``erase_raw, write_raw``
@@ -148,15 +149,20 @@ def mixer_decode_step(u: torch.Tensor, h: torch.Tensor, erase_raw: torch.Tensor,
     ``[B,1,H]``; FP32 ``conv_weight [D,4]``, ``log_rate [H]``, ``decay_bias [H*r]``, ``geometry_bias [H]``.
     Returns the output row ``[B,1,H,V]`` (BF16).  Same arithmetic as ``conv4_silu`` + ``kda_decay_gate`` +
     ``sigmoid`` + the T = 1 branch of ``solvedelta_native``; with ``output_gate`` ``[B,1,H,V]`` and FP32
-    ``norm_weight [V]`` the row also passes through ``rms_norm_gated``."""
+    ``norm_weight [V]`` the row also passes through ``rms_norm_gated``.  ``gate_projections`` =
+    ``(decay_hidden [B,1,G], decay_proj.weight [H*r,G], gate_hidden [B,1,G], output_gate_proj.weight [H*V,G],
+    output_gate_proj.bias [H*V] | None)``, all BF16, moves the two small projections in front of the gates into the
+    kernel as well (``decay_raw`` and ``output_gate`` may then be None; needs ``norm_weight``)."""
     lib = _lib.load()
     B, T, H, r = u.shape
     V = write_raw.shape[-1]
     if T != 1:
         raise ValueError("mixer_decode_step takes exactly one token")
     for name, t in (("u", u), ("h", h), ("erase_raw", erase_raw), ("write_raw", write_raw), ("qkv", qkv),
-                    ("decay_raw", decay_raw), ("geometry_raw", geometry_raw), ("conv_state", conv_state)):
+                    ("geometry_raw", geometry_raw), ("conv_state", conv_state)):
         _require_bf16_cuda(name, t)
+    if gate_projections is None:
+        _require_bf16_cuda("decay_raw", decay_raw)
     for name, t in (("conv_weight", conv_weight), ("log_rate", log_rate), ("decay_bias", decay_bias),
                     ("geometry_bias", geometry_bias), ("predictor", predictor), ("memory", memory)):
         if t.dtype != torch.float32 or not t.is_contiguous():
@@ -164,7 +170,7 @@ def mixer_decode_step(u: torch.Tensor, h: torch.Tensor, erase_raw: torch.Tensor,
     D = 2 * H * r + H * V
     if qkv.shape != (B, 1, D) or conv_state.shape != (B, D, 3) or not conv_state.is_contiguous():
         raise ValueError("qkv must be [B,1,D] and conv_state contiguous [B,D,3] with D = 2*H*r + H*V")
-    if qkv.stride(-1) != 1 or decay_raw.stride(-1) != 1 or geometry_raw.stride(-1) != 1:
+    if qkv.stride(-1) != 1 or geometry_raw.stride(-1) != 1 or (decay_raw is not None and decay_raw.stride(-1) != 1):
         raise ValueError("row operands require unit innermost stride")
 
     def operand(t):
@@ -178,19 +184,37 @@ def mixer_decode_step(u: torch.Tensor, h: torch.Tensor, erase_raw: torch.Tensor,
         a.erase_raw, a.write_raw = operand(erase_raw), operand(write_raw)
         a.qkv, a.qkv_stride_b = qkv.data_ptr(), qkv.stride(0)
         a.conv_weight, a.conv_state = conv_weight.data_ptr(), conv_state.data_ptr()
-        decay2 = decay_raw.reshape(B, H * r) if decay_raw.is_contiguous() else decay_raw.contiguous().view(B, H * r)
-        a.decay_raw, a.decay_stride_b = decay2.data_ptr(), decay2.stride(0)
+        if decay_raw is not None:
+            decay2 = decay_raw.reshape(B, H * r) if decay_raw.is_contiguous() else decay_raw.contiguous().view(B, H * r)
+            a.decay_raw, a.decay_stride_b = decay2.data_ptr(), decay2.stride(0)
         a.log_rate, a.decay_bias = log_rate.data_ptr(), decay_bias.data_ptr()
         a.geometry_raw, a.geometry_stride_b = geometry_raw.data_ptr(), geometry_raw.stride(0)
         a.geometry_bias = geometry_bias.data_ptr()
         a.C, a.S, a.y = predictor.data_ptr(), memory.data_ptr(), y.data_ptr()
+        if gate_projections is not None:
+            decay_hidden, decay_w, gate_hidden, gate_w, gate_b = gate_projections
+            G = decay_hidden.shape[-1]
+            for name, t in (("decay_hidden", decay_hidden), ("decay_proj.weight", decay_w),
+                            ("gate_hidden", gate_hidden), ("output_gate_proj.weight", gate_w)):
+                _require_bf16_cuda(name, t)
+            if (decay_w.shape != (H * r, G) or gate_w.shape != (H * V, G) or not decay_w.is_contiguous()
+                    or not gate_w.is_contiguous() or G % 8 or G > 128 or norm_weight is None):
+                raise ValueError("fused gate projections: weights [H*r,G] / [H*V,G] contiguous, G a multiple of 8, "
+                                 "at most 128, and the fused norm")
+            a.gate_rank = G
+            a.decay_hidden, a.decay_hidden_stride_b = decay_hidden.data_ptr(), decay_hidden.stride(0)
+            a.gate_hidden, a.gate_hidden_stride_b = gate_hidden.data_ptr(), gate_hidden.stride(0)
+            a.decay_proj_weight, a.gate_proj_weight = decay_w.data_ptr(), gate_w.data_ptr()
+            a.gate_proj_bias = None if gate_b is None else gate_b.data_ptr()
         if norm_weight is not None:
-            if output_gate is None or output_gate.dtype != torch.bfloat16 or not output_gate.is_contiguous():
+            if gate_projections is None and (output_gate is None or output_gate.dtype != torch.bfloat16
+                                             or not output_gate.is_contiguous()):
                 raise ValueError("the fused norm needs a contiguous BF16 output_gate [B,1,H,V]")
             if norm_weight.dtype != torch.float32 or norm_weight.shape != (V,):
                 raise TypeError("norm_weight must be FP32 [V]")
             a.norm_weight, a.norm_eps = norm_weight.data_ptr(), float(norm_eps)
-            a.output_gate, a.output_gate_stride_b = output_gate.data_ptr(), H * V
+            if output_gate is not None:
+                a.output_gate, a.output_gate_stride_b = output_gate.data_ptr(), H * V
         _lib.check(lib.sd_mixer_decode_step(ctypes.byref(a), _stream(u.device)))
     return y
 

@@ -199,15 +199,24 @@ class SolveDelta(nn.Module):
                                       associative_decay_enabled, return_final_state):
             # cached single-token step: conv, decay gate, geometry rate and the recurrent step in one launch, the
             # cache's conv window and operator states updated in place
-            associative_raw = self._linear(self.decay_proj, piece(8)).view(batch, length, heads, width)
-            output_gate = self._linear(self.output_gate_proj, piece(9)).view(batch, length, heads, value_width)
+            dw, gw, gb = self.decay_proj.weight, self.output_gate_proj.weight, self.output_gate_proj.bias
+            in_kernel = (dw.dtype == gw.dtype == torch.bfloat16 and dw.is_contiguous() and gw.is_contiguous()
+                         and gb.dtype == torch.bfloat16 and dw.shape[1] % 8 == 0 and dw.shape[1] <= 128)
+            if in_kernel:   # the two small projections in front of the gates run inside the kernel too
+                associative_raw = output_gate = None
+                projections = (piece(8), dw.detach(), piece(9), gw.detach(), gb.detach())
+            else:
+                associative_raw = self._linear(self.decay_proj, piece(8)).view(batch, length, heads, width)
+                output_gate = self._linear(self.output_gate_proj, piece(9)).view(batch, length, heads, value_width)
+                projections = None
             operator = initial_state.operator
             output = mixer_decode_step(
                 view(piece(3), width), view(piece(4), width), view(piece(5), width), view(piece(6), value_width),
                 qkv_in, self._fp32_copy("conv_weight"), initial_state.conv, associative_raw,
                 self._fp32_copy("associative_log_rate"), self._fp32_copy("associative_decay_bias").reshape(-1),
                 piece(7), self._fp32_copy("geometry_write_bias"), operator.predictor, operator.S,
-                output_gate=output_gate, norm_weight=self._fp32_norm_weight(), norm_eps=self.output_norm.eps)
+                output_gate=output_gate, norm_weight=self._fp32_norm_weight(), norm_eps=self.output_norm.eps,
+                gate_projections=projections)
             result = self._linear(self.output_proj, output.reshape(batch, length, heads * value_width))
             return result, SolveDeltaLayerState(SolveDeltaState(operator.predictor, operator.S), initial_state.conv)
         if self.config.use_short_conv:
