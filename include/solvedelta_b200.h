@@ -106,6 +106,31 @@ typedef struct {
 } sd_decode_args;
 
 /*
+ * Inference glue of the block around the mixer (no reverse pass; BF16 rows, contiguous):
+ * sd_add_rmsnorm  sum = x + delta and normed = RMSNorm(sum) * weight in one pass: a residual add and
+ *                 the norm that follows it (causallsso/modeling_solvedelta.py:230-255)
+ * sd_swiglu       out = silu(gate) * value for rows [gate | value] (modeling_solvedelta.py:68-101)
+ */
+typedef struct {
+    int64_t rows;
+    int32_t D;
+    float eps;
+    const void *x, *delta;             /* BF16 [rows][D] */
+    const float *weight;               /* [D] */
+    void *sum, *normed;                /* out BF16 [rows][D] */
+} sd_add_rmsnorm_args;
+
+typedef struct {
+    int64_t rows;
+    int32_t I;
+    const void *gate_value;            /* BF16 [rows][2 I] */
+    void *out;                         /* BF16 [rows][I] */
+} sd_swiglu_args;
+
+int sd_add_rmsnorm(const sd_add_rmsnorm_args *args, void *stream);
+int sd_swiglu(const sd_swiglu_args *args, void *stream);
+
+/*
  * The whole mixer glue of a cached single-token step in the decode kernel: q, k, v come from
  * the conv4 + SiLU of the projection row against the carried window (advanced in place,
  * causallsso/model.py:146-164 at T = 1), the log decay from the decay gate

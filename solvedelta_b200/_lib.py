@@ -108,6 +108,17 @@ class BackwardArgs(ctypes.Structure):
         ("valid_mask", ctypes.c_void_p), ("reset_mask", ctypes.c_void_p)])
 
 
+class AddRmsnormArgs(ctypes.Structure):
+    _fields_ = [("rows", ctypes.c_int64), ("D", ctypes.c_int32), ("eps", ctypes.c_float),
+                ("x", ctypes.c_void_p), ("delta", ctypes.c_void_p), ("weight", ctypes.c_void_p),
+                ("sum", ctypes.c_void_p), ("normed", ctypes.c_void_p)]
+
+
+class SwigluArgs(ctypes.Structure):
+    _fields_ = [("rows", ctypes.c_int64), ("I", ctypes.c_int32), ("gate_value", ctypes.c_void_p),
+                ("out", ctypes.c_void_p)]
+
+
 class MixerDecodeArgs(ctypes.Structure):
     _fields_ = ([("shape", Shape)] + [(n, Operand) for n in ("u", "h", "erase_raw", "write_raw")] + [
         ("qkv", ctypes.c_void_p), ("qkv_stride_b", ctypes.c_int64), ("conv_weight", ctypes.c_void_p),
@@ -185,7 +196,7 @@ EXPORTS = (
     "sd_forward", "sd_backward", "sd_decode_step", "sd_forward_launches",
     "sd_backward_launches", "sd_panel_info", "sd_status_string", "sd_version",
     "sd_chunk_tokens", "sd_forward_static", "sd_panel_kind", "sd_device_fault", "sd_device_fault_clear",
-    "sd_predictor_forward", "sd_predictor_backward", "sd_mixer_decode_step",
+    "sd_predictor_forward", "sd_predictor_backward", "sd_mixer_decode_step", "sd_add_rmsnorm", "sd_swiglu",
     "sd_conv4_backward_scratch_bytes", "sd_conv4_silu_forward", "sd_conv4_silu_backward",
     "sd_kda_gate_backward_scratch_bytes", "sd_kda_gate_forward", "sd_kda_gate_backward",
     "sd_norm_gate_backward_scratch_bytes", "sd_norm_gate_forward", "sd_norm_gate_backward",
@@ -254,7 +265,8 @@ def _declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.sd_norm_gate_backward_scratch_bytes.restype = ctypes.c_size_t
     lib.sd_norm_gate_backward_scratch_bytes.argtypes = [ctypes.c_int64, ctypes.c_int32]
     for name, struct in (("sd_predictor_forward", PredictorForwardArgs), ("sd_predictor_backward", PredictorBackwardArgs),
-                         ("sd_mixer_decode_step", MixerDecodeArgs),
+                         ("sd_mixer_decode_step", MixerDecodeArgs), ("sd_add_rmsnorm", AddRmsnormArgs),
+                         ("sd_swiglu", SwigluArgs),
                          ("sd_conv4_silu_forward", Conv4ForwardArgs), ("sd_conv4_silu_backward", Conv4BackwardArgs),
                          ("sd_kda_gate_forward", KdaGateArgs), ("sd_kda_gate_backward", KdaGateArgs),
                          ("sd_norm_gate_forward", NormGateArgs), ("sd_norm_gate_backward", NormGateArgs)):

@@ -942,6 +942,33 @@ int sd_norm_gate_backward(const sd_norm_gate_args* a, void* stream_) {
     return launch_status();
 }
 
+int sd_add_rmsnorm(const sd_add_rmsnorm_args* a, void* stream_) {
+    if (!a || a->rows <= 0 || a->D <= 0 || !a->x || !a->delta || !a->weight || !a->sum || !a->normed)
+        return SD_ERR_INVALID_ARGUMENT;
+    if (a->rows > 0x7fffffffLL) return SD_ERR_UNSUPPORTED_SHAPE;
+    AddNormParams p{};
+    p.N = a->rows; p.D = a->D; p.eps = a->eps;
+    p.x = reinterpret_cast<const __nv_bfloat16*>(a->x);
+    p.delta = reinterpret_cast<const __nv_bfloat16*>(a->delta);
+    p.w = a->weight;
+    p.sum = reinterpret_cast<__nv_bfloat16*>(a->sum);
+    p.normed = reinterpret_cast<__nv_bfloat16*>(a->normed);
+    k_add_rmsnorm<<<(unsigned)a->rows, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
+    return launch_status();
+}
+
+int sd_swiglu(const sd_swiglu_args* a, void* stream_) {
+    if (!a || a->rows <= 0 || a->I <= 0 || !a->gate_value || !a->out) return SD_ERR_INVALID_ARGUMENT;
+    SwigluParams p{};
+    p.N = a->rows; p.I = a->I;
+    p.in = reinterpret_cast<const __nv_bfloat16*>(a->gate_value);
+    p.out = reinterpret_cast<__nv_bfloat16*>(a->out);
+    long long blocks = (a->rows * ((a->I + 7) / 8) + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    k_swiglu<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
+    return launch_status();
+}
+
 int sd_decode_step(const sd_decode_args* a, void* stream_) {
     if (!a || !shape_ok(&a->shape) || a->shape.T != 1) return SD_ERR_INVALID_ARGUMENT;
     if (!shape_supported(&a->shape)) return SD_ERR_UNSUPPORTED_SHAPE;

@@ -621,4 +621,77 @@ __global__ void __launch_bounds__(256) k_norm_gate_bwd(NormParams p) {
     }
 }
 
+// ---- inference glue of the block around the mixer (no reverse pass) ------------------------
+// sum = x + delta (the residual stream, rounded to BF16 as the separate add stores it) and
+// normed = sum rsqrt(mean(sum^2) + eps) w: the residual add and the RMSNorm that follows it
+// (causallsso/modeling_solvedelta.py:230-255) in one pass.  One CTA per row.
+struct AddNormParams {
+    long long N;
+    int D;
+    float eps;
+    const __nv_bfloat16 *x, *delta;
+    const float* w;
+    __nv_bfloat16 *sum, *normed;
+};
+
+__global__ void __launch_bounds__(256) k_add_rmsnorm(AddNormParams p) {
+    __shared__ float red[8];
+    const long long row = blockIdx.x;
+    const __nv_bfloat16* x = p.x + row * p.D;
+    const __nv_bfloat16* d = p.delta + row * p.D;
+    __nv_bfloat16* so = p.sum + row * p.D;
+    float ss = 0.f;
+    for (int c0 = threadIdx.x * 8; c0 < p.D; c0 += 256 * 8) {
+        float a[8], b[8], s8[8];
+        norm_load8(x, c0, p.D, true, a);
+        norm_load8(d, c0, p.D, true, b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            s8[e] = __bfloat162float(__float2bfloat16_rn(a[e] + b[e]));
+            ss = fmaf(s8[e], s8[e], ss);
+        }
+        norm_store8(so, c0, p.D, true, s8);
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();   // also orders this thread's stores to `sum` before its reads below (same thread, same addresses)
+    float tot = 0.f;
+#pragma unroll
+    for (int w8 = 0; w8 < 8; ++w8) tot += red[w8];
+    const float rstd = rsqrtf(tot / p.D + p.eps);
+    __nv_bfloat16* no = p.normed + row * p.D;
+    for (int c0 = threadIdx.x * 8; c0 < p.D; c0 += 256 * 8) {
+        float s8[8], y[8];
+        norm_load8(so, c0, p.D, true, s8);   // what this thread just wrote
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] = (c0 + e < p.D) ? s8[e] * rstd * p.w[c0 + e] : 0.f;
+        norm_store8(no, c0, p.D, true, y);
+    }
+}
+
+// out = silu(gate) * value for rows [gate | value] of width 2 I (the gated MLP between its two
+// projections, causallsso/modeling_solvedelta.py:68-101).
+struct SwigluParams {
+    long long N;
+    int I;
+    const __nv_bfloat16* in;   // [N][2 I]
+    __nv_bfloat16* out;        // [N][I]
+};
+
+__global__ void __launch_bounds__(256) k_swiglu(SwigluParams p) {
+    const long long per_row = (p.I + 7) / 8, total = p.N * per_row;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long row = idx / per_row;
+        const int c0 = (int)(idx - row * per_row) * 8;
+        float g[8], v[8], y[8];
+        norm_load8(p.in + row * 2 * p.I, c0, p.I, true, g);
+        norm_load8(p.in + row * 2 * p.I + p.I, c0, p.I, true, v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] = silu_f(g[e]) * v[e];
+        norm_store8(p.out + row * p.I, c0, p.I, true, y);
+    }
+}
+
 }  // namespace sd

@@ -219,6 +219,41 @@ def mixer_decode_step(u: torch.Tensor, h: torch.Tensor, erase_raw: torch.Tensor,
     return y
 
 
+@torch.no_grad()
+def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, eps: float):
+    """``s = x + delta`` and ``RMSNorm(s) * weight`` in one pass (inference only): returns ``(s, normed)``, both
+    BF16 with the shape of ``x``.  ``weight`` FP32 ``[D]``."""
+    _require_bf16_cuda("x", x)
+    _require_bf16_cuda("delta", delta)
+    if x.shape != delta.shape or weight.shape != (x.shape[-1],) or weight.dtype != torch.float32:
+        raise ValueError("x and delta must share a shape [...,D]; weight FP32 [D]")
+    lib = _lib.load()
+    xc, dc = x.contiguous(), delta.contiguous()
+    D = x.shape[-1]
+    with torch.cuda.device(x.device):
+        total, normed = torch.empty_like(xc), torch.empty_like(xc)
+        a = _lib.AddRmsnormArgs(xc.numel() // D, D, float(eps), xc.data_ptr(), dc.data_ptr(), weight.data_ptr(),
+                                total.data_ptr(), normed.data_ptr())
+        _lib.check(lib.sd_add_rmsnorm(ctypes.byref(a), _stream(x.device)))
+    return total, normed
+
+
+@torch.no_grad()
+def swiglu(gate_value: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * value`` for rows ``[gate | value]`` (inference only): ``[..., 2 I]`` -> ``[..., I]`` BF16."""
+    _require_bf16_cuda("gate_value", gate_value)
+    if gate_value.shape[-1] % 2:
+        raise ValueError("the last axis must hold gate and value halves")
+    lib = _lib.load()
+    gv = gate_value.contiguous()
+    width = gv.shape[-1] // 2
+    with torch.cuda.device(gv.device):
+        out = torch.empty(*gv.shape[:-1], width, dtype=torch.bfloat16, device=gv.device)
+        a = _lib.SwigluArgs(gv.numel() // (2 * width), width, gv.data_ptr(), out.data_ptr())
+        _lib.check(lib.sd_swiglu(ctypes.byref(a), _stream(gv.device)))
+    return out
+
+
 class _KdaGate(torch.autograd.Function):
     @staticmethod
     def forward(ctx, raw, log_rate, bias):
@@ -378,5 +413,6 @@ def rms_norm_gated(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, ep
     return _NormGate.apply(x, gate, weight, eps)
 
 
-__all__ = ["conv4_silu", "conv4_silu_segmented", "kda_decay_gate", "mixer_decode_step", "rms_norm_gated",
+__all__ = ["add_rmsnorm", "conv4_silu", "conv4_silu_segmented", "kda_decay_gate", "mixer_decode_step", "rms_norm_gated",
+           "swiglu",
            "rms_norm_gated_linear"]

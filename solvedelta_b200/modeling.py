@@ -24,6 +24,7 @@ from transformers.modeling_outputs import BaseModelOutputWithPast, CausalLMOutpu
 from . import _lib
 from .config import SolveDeltaConfig
 from .ops import SolveDeltaState
+from .mixer_ops import add_rmsnorm, swiglu
 from .model import SolveDelta, SolveDeltaLayerState
 
 FP32_PARAMETERS = ("geometry_write_bias", "associative_log_rate", "associative_decay_bias")
@@ -128,6 +129,9 @@ class SolveDeltaMLP(nn.Module):
         self.down_proj = nn.Linear(intermediate_size, hidden_size, bias=False)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if (self.hidden_act == "swish" and not torch.is_grad_enabled() and x.is_cuda
+                and x.dtype == torch.bfloat16):
+            return self.down_proj(swiglu(self.gate_up_proj(x)))   # inference: activation and product in one kernel
         gate, value = self.gate_up_proj(x).chunk(2, dim=-1)
         if self.hidden_act == "swish":
             activated = F.silu(gate)
@@ -197,6 +201,19 @@ class SolveDeltaCacheAdapter(nn.Module):
         return output, past_key_values
 
 
+def _fp32_weight(norm: nn.Module) -> torch.Tensor:
+    """Contiguous FP32 copy of a norm's weight for the fused inference kernels, refreshed when the weight changes."""
+    weight = norm.weight
+    if weight.dtype == torch.float32 and weight.is_contiguous():
+        return weight.detach()
+    key = (weight.data_ptr(), weight._version)
+    hit = norm.__dict__.get("_fp32_weight_copy")
+    if hit is None or hit[0] != key:
+        hit = (key, weight.detach().float().contiguous())
+        norm.__dict__["_fp32_weight_copy"] = hit
+    return hit[1]
+
+
 class SolveDeltaBlock(nn.Module):
     """Pre-norm residual block: mixer, then MLP (modeling_solvedelta.py:197-255)."""
 
@@ -218,9 +235,16 @@ class SolveDeltaBlock(nn.Module):
         hidden_states, past_key_values = self.mixer(hidden_states, attention_mask=attention_mask,
                                                     past_key_values=past_key_values, use_cache=use_cache,
                                                     **kwargs)
-        hidden_states = residual + hidden_states
-        residual = hidden_states
-        hidden_states = self.mlp(self.mlp_norm(hidden_states))
+        if (not torch.is_grad_enabled() and hidden_states.is_cuda and hidden_states.dtype == torch.bfloat16
+                and self.mlp_norm.weight is not None):
+            # inference: the residual add and the norm that follows it in one kernel
+            residual, hidden_states = add_rmsnorm(residual, hidden_states, _fp32_weight(self.mlp_norm),
+                                                  self.mlp_norm.eps if self.mlp_norm.eps is not None else 1e-6)
+        else:
+            hidden_states = residual + hidden_states
+            residual = hidden_states
+            hidden_states = self.mlp_norm(hidden_states)
+        hidden_states = self.mlp(hidden_states)
         return residual + hidden_states, past_key_values
 
 

@@ -423,3 +423,26 @@ def test_mixer_module_rejects_cpu_inputs():
         module(torch.zeros(1, 4, 64))
     with pytest.raises(ValueError):
         module(torch.zeros(1, 4, 32, dtype=torch.bfloat16, device="cuda"))
+
+
+def test_inference_glue_kernels_match_pytorch():
+    """The two inference-only kernels of the block: residual add + RMSNorm, and SiLU(gate) * value."""
+    from solvedelta_b200.mixer_ops import add_rmsnorm, swiglu
+
+    gen = torch.Generator().manual_seed(3)
+    for rows, D in ((5, 1024), (3, 200), (2, 4100)):
+        x = torch.randn(rows, D, generator=gen).to(torch.bfloat16).cuda()
+        d = torch.randn(rows, D, generator=gen).to(torch.bfloat16).cuda()
+        w = (1.0 + 0.2 * torch.randn(D, generator=gen)).cuda()
+        total, normed = add_rmsnorm(x, d, w, 1e-6)
+        want_sum = x + d
+        assert torch.equal(total, want_sum)
+        s = want_sum.float()
+        want = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+        assert float((normed.float() - want).abs().max()) <= 1e-2 * float(want.abs().max())
+        gv = torch.randn(rows, 2 * D, generator=gen).to(torch.bfloat16).cuda()
+        out = swiglu(gv)
+        g, v = gv.float().chunk(2, dim=-1)
+        want = torch.nn.functional.silu(g) * v
+        assert out.shape == (rows, D)
+        assert float((out.float() - want).abs().max()) <= 1e-2 * float(want.abs().max())
