@@ -227,11 +227,25 @@ class SolveDeltaBlock(nn.Module):
         self.mlp = SolveDeltaMLP(hidden_size=config.hidden_size, hidden_ratio=config.hidden_ratio,
                                  intermediate_size=config.intermediate_size, hidden_act=config.hidden_act)
 
+    @staticmethod
+    def fuses(hidden_states: torch.Tensor) -> bool:
+        """Inference on BF16 CUDA activations: residual adds are folded into the norms that follow them."""
+        return not torch.is_grad_enabled() and hidden_states.is_cuda and hidden_states.dtype == torch.bfloat16
+
     def forward(self, hidden_states: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
                 past_key_values: Optional[SolveDeltaCache] = None, use_cache: Optional[bool] = False,
-                **kwargs) -> Tuple[torch.Tensor, Optional[SolveDeltaCache]]:
-        residual = hidden_states
-        hidden_states = self.mixer_norm(hidden_states)
+                pending: Optional[torch.Tensor] = None, defer_add: bool = False,
+                **kwargs):
+        """``pending``: the previous block's MLP output, not yet added to ``hidden_states`` (it is added inside this
+        block's first norm kernel).  ``defer_add``: return ``(residual, mlp_output, cache)`` and leave the last add
+        to the next norm.  Both are only used on the inference path (``fuses``)."""
+        if pending is not None:
+            hidden_states, normed = add_rmsnorm(hidden_states, pending, _fp32_weight(self.mixer_norm),
+                                                self.mixer_norm.eps if self.mixer_norm.eps is not None else 1e-6)
+            residual, hidden_states = hidden_states, normed
+        else:
+            residual = hidden_states
+            hidden_states = self.mixer_norm(hidden_states)
         hidden_states, past_key_values = self.mixer(hidden_states, attention_mask=attention_mask,
                                                     past_key_values=past_key_values, use_cache=use_cache,
                                                     **kwargs)
@@ -245,6 +259,8 @@ class SolveDeltaBlock(nn.Module):
             residual = hidden_states
             hidden_states = self.mlp_norm(hidden_states)
         hidden_states = self.mlp(hidden_states)
+        if defer_add:
+            return residual, hidden_states, past_key_values
         return residual + hidden_states, past_key_values
 
 
@@ -309,13 +325,25 @@ class SolveDeltaModel(SolveDeltaPreTrainedModel):
         if cu_seqlens is not None and "solvedelta_reset_mask" not in kwargs:
             kwargs["solvedelta_reset_mask"] = segment_reset_mask(hidden_states, cu_seqlens)
         collected = () if output_hidden_states else None
+        # inference: every block leaves its last residual add to the norm kernel that follows it
+        defer = SolveDeltaBlock.fuses(hidden_states) and not output_hidden_states and self.norm.weight is not None
+        pending = None
         for layer in self.layers:
             if output_hidden_states:
                 collected += (hidden_states,)
-            hidden_states, past_key_values = layer(hidden_states, attention_mask=attention_mask,
-                                                   past_key_values=past_key_values, use_cache=use_cache,
-                                                   **kwargs)
-        hidden_states = self.norm(hidden_states)
+            if defer:
+                hidden_states, pending, past_key_values = layer(
+                    hidden_states, attention_mask=attention_mask, past_key_values=past_key_values,
+                    use_cache=use_cache, pending=pending, defer_add=True, **kwargs)
+            else:
+                hidden_states, past_key_values = layer(hidden_states, attention_mask=attention_mask,
+                                                       past_key_values=past_key_values, use_cache=use_cache,
+                                                       **kwargs)
+        if pending is not None:
+            _, hidden_states = add_rmsnorm(hidden_states, pending, _fp32_weight(self.norm),
+                                           self.norm.eps if self.norm.eps is not None else 1e-6)
+        else:
+            hidden_states = self.norm(hidden_states)
         if output_hidden_states:
             collected += (hidden_states,)
         return BaseModelOutputWithPast(last_hidden_state=hidden_states, past_key_values=past_key_values,
