@@ -291,7 +291,7 @@ KERNEL_BYTES_PER_CHUNK = {
     # u,k,q,er,wr,v,G,Delta,Ct -> d, Wd,Ud,Dt, Aqd,Aed, 7 BF16 source panels
     "k_primal_exterior_fwd": 6 * _B + 2 * _F + _S + _F + 3 * _F + _M + _P + 7 * _B,
     "k_state_scan[S]": 3 * _F + _B + _T,                        # P,Q,R -> Z~ (BF16), BF16 ckpt
-    "k_output_fwd": _B + _M + _B + _T + _B,                     # Xg,Aqd,Zt,S -> y
+    "k_output_fwd_tc": _B + _M + _B + _T + _B,                  # Xg,Aqd,Zt,S -> y
     # dy,DtB,Aqd,Aed -> Dyf,Pp,Qp
     "k_exterior_prep_bwd": 2 * _B + _M + _P + 3 * _B,
     "k_state_scan_b[dS]": 6 * _B + _T,

@@ -266,10 +266,11 @@ int sd_backward_launches(const sd_shape *shape);
 /*
  * Device fault word.  Every wait inside the kernels is bounded; a wait that runs out does
  * not hang the GPU: it stores a code here, the kernel walks to its end, and the results of
- * that launch are undefined.  Codes (all from the tensor-memory state scan): 1 = the first
+ * that launch are undefined.  Codes 1-5 come from the tensor-memory state scan: 1 = the first
  * contraction of a step (X = P + Q St) never completed, 2 = the second (state update),
  * 3 = a step's Q panel never landed, 4 = its R / P panels never landed, 5 = the slot of
- * the R / P panels was never released.  No upstream counterpart.
+ * the R / P panels was never released; codes 6-7 from the tensor-memory output contraction:
+ * 6 = its panels never landed, 7 = the contraction never completed.  No upstream counterpart.
  *
  * sd_device_fault waits for the device and returns the word (0 = no fault, -1 = the device
  * could not be read); the word stays set until sd_device_fault_clear() (which also waits

@@ -1,6 +1,6 @@
 // Chunk-parallel forward kernels: one CTA per (stream, chunk).
 //
-// Pipeline: k_prep_fwd -> scan(C) -> k_primal_exterior_fwd -> scan(S) -> k_output_fwd.
+// Pipeline: k_prep_fwd -> scan(C) -> k_primal_exterior_fwd -> scan(S) -> k_output_fwd_tc.
 #pragma once
 #include "sd_bf16.cuh"
 #include "sd_common.cuh"
@@ -562,56 +562,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_primal_exterior_fwd(FwdParams p
     SD_PHASE(p.g, ph);
 }
 
-
-// ---------------------------------------------------------------------------
-// Output rows: y = Xg S_c + tril(Aqd) Z~, BF16 operands (the result is BF16).
-constexpr size_t OUTPUT_FWD_SMEM = 2 * BSLOT_BYTES + BSTATE_BYTES + BMAT_BYTES;
-
-// 79 KB of shared memory: two CTAs share an SM (one loads while the other contracts)
-template <bool FAST, bool MASKED>
-__global__ void __launch_bounds__(NTHREADS, 2) k_output_fwd(FwdParams p) {
-    int ph = 0;
-    SD_PHASE(p.g, ph);
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* b_xg = reinterpret_cast<bf16*>(smem_raw);
-    bf16* b_zt = b_xg + BSLOT_ELEMS;
-    bf16* b_S = b_zt + BSLOT_ELEMS;
-    bf16* b_aqd = b_S + DP * LDB;
-    const ChunkT<MASKED> ch = chunk_of<MASKED>(p.g, blockIdx.x);
-    const int V = p.g.V;
-
-    async_bpanel(b_xg, bpanel_ptr(p.Xg, ch.gi));
-    async_bmat(b_aqd, bmat_ptr(p.Aqd, ch.gi));
-    async_bpanel(b_zt, bpanel_ptr(p.Zt, ch.gi));
-    {
-        const bf16* gS = p.SCk + ch.gi * (long long)(DP * DP);
-        for (int idx = threadIdx.x; idx < DP * (DP / 8); idx += NTHREADS) {
-            int i = idx >> 4, c8 = (idx & 15) << 3;
-            cp16(b_S + i * LDB + c8, gS + i * DP + c8);
-        }
-    }
-    cp_commit();
-    cp_wait<0>();
-    __syncthreads();
-    SD_PHASE(p.g, ph);
-    float acc[NT128][4];
-    acc_zero<NT128>(acc);
-    const int r0 = Tile64<DP>::r0(), n0 = Tile64<DP>::n0();
-    warp_mma_bf16<NT128, false, false>(acc, b_xg, LDB, b_S, LDB, r0, n0, 0, DP);
-    warp_mma_bf16<NT128, false, false>(acc, b_aqd, LDM, b_zt, LDB, r0, n0, 0, r0 + 16);
-    __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y);
-    warp_epi<NT128>(acc, r0, n0, [&](int i, int j, float v0, float v1) {
-        if (i >= ch.nvalid || j >= V) return;
-        if (!ch.ok(i)) v0 = v1 = 0.f;   // a masked token: exact zeros
-        __nv_bfloat16* row = y + (((long long)ch.b * p.g.T + ch.t0 + i) * p.g.H + ch.hh) * (long long)V;
-        if (j + 1 < V && (V & 1) == 0) {
-            *reinterpret_cast<__nv_bfloat162*>(row + j) = __floats2bfloat162_rn(v0, v1);
-        } else {
-            row[j] = __float2bfloat16_rn(v0);
-            if (j + 1 < V) row[j + 1] = __float2bfloat16_rn(v1);
-        }
-    });
-    SD_PHASE(p.g, ph);
-}
+// The output rows y = Xg S_c + tril(Aqd) Z~ are k_output_fwd_tc (sd_output_tc.cuh).
 
 }  // namespace sd
