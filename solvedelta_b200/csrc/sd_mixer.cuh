@@ -72,6 +72,18 @@ __device__ __forceinline__ void store_pair(__nv_bfloat16* row, bool two, float a
     }
 }
 
+// Ring of tokens in flight per thread (PAIR instantiations): every thread streams its own channel pair through
+// shared memory with 4-byte cp.async copies, CONV_RING tokens ahead of the one it works on, so the walk along the
+// sequence is not bound by one load latency per token.  A thread only ever touches its own ring column: no barrier.
+constexpr int CONV_RING = 8;
+__device__ __forceinline__ void conv_cp4(unsigned* smem, const __nv_bfloat16* gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ float2 conv_ring_pair(unsigned raw) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw));
+}
+
 constexpr int CONV_BATCH = 4;      // forward: tokens whose loads are issued together
 constexpr int CONV_BATCH_BWD = 1;  // reverse: more registers per token; batching cost occupancy and time
 
@@ -92,6 +104,24 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv4_silu_fwd(ConvParams p) {
     const int t1 = min(t0 + CONV_TT, p.T);
     const __nv_bfloat16* xin = p.x + b * p.sb + d;
     __nv_bfloat16* yout = p.y + (long long)b * p.T * p.D + d;
+    if (PAIR) {
+        __shared__ unsigned ring[CONV_RING][CONV_THREADS];
+        auto issue = [&](int t) {
+            if (t < t1) conv_cp4(&ring[(t - t0) % CONV_RING][threadIdx.x], xin + (long long)t * p.st);
+            asm volatile("cp.async.commit_group;" ::);
+        };
+#pragma unroll
+        for (int k = 0; k < CONV_RING; ++k) issue(t0 + k);
+        for (int t = t0; t < t1; ++t) {
+            asm volatile("cp.async.wait_group %0;" ::"n"(CONV_RING - 1));
+            const float2 x3 = conv_ring_pair(ring[(t - t0) % CONV_RING][threadIdx.x]);
+            issue(t + CONV_RING);
+            const float za = wa[0] * x0.x + wa[1] * x1.x + wa[2] * x2.x + wa[3] * x3.x;
+            const float zb = wb[0] * x0.y + wb[1] * x1.y + wb[2] * x2.y + wb[3] * x3.y;
+            store_pair<PAIR>(yout + (long long)t * p.D, two, silu_f(za), silu_f(zb));
+            x0 = x1; x1 = x2; x2 = x3;
+        }
+    } else
     for (int ts = t0; ts < t1; ts += CONV_BATCH) {
         float2 xs[CONV_BATCH];
 #pragma unroll
@@ -144,6 +174,50 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv4_silu_bwd(ConvParams p) {
     const __nv_bfloat16* xin = p.x + b * p.sb + d;
     const __nv_bfloat16* gin = p.dy + (long long)b * p.T * p.D + d;
     __nv_bfloat16* dxout = p.dx + (long long)b * p.T * p.D + d;
+    if (PAIR) {
+        __shared__ unsigned ring_x[CONV_RING][CONV_THREADS], ring_g[CONV_RING][CONV_THREADS];
+        auto issue = [&](int t) {
+            if (t < t_last) {
+                conv_cp4(&ring_x[(t - t0) % CONV_RING][threadIdx.x], xin + (long long)t * p.st);
+                conv_cp4(&ring_g[(t - t0) % CONV_RING][threadIdx.x], gin + (long long)t * p.D);
+            }
+            asm volatile("cp.async.commit_group;" ::);
+        };
+#pragma unroll
+        for (int k = 0; k < CONV_RING; ++k) issue(t0 + k);
+        for (int t = t0; t < t_end + 3; ++t) {
+            asm volatile("cp.async.wait_group %0;" ::"n"(CONV_RING - 1));
+            float2 x3 = make_float2(0.f, 0.f), gy = x3;
+            if (t < t_last) {
+                x3 = conv_ring_pair(ring_x[(t - t0) % CONV_RING][threadIdx.x]);
+                gy = conv_ring_pair(ring_g[(t - t0) % CONV_RING][threadIdx.x]);
+            }
+            issue(t + CONV_RING);
+            float2 g3 = make_float2(0.f, 0.f);
+            if (t < p.T) {
+                const float za = wa[0] * x0.x + wa[1] * x1.x + wa[2] * x2.x + wa[3] * x3.x;
+                const float zb = wb[0] * x0.y + wb[1] * x1.y + wb[2] * x2.y + wb[3] * x3.y;
+                g3.x = gy.x * silu_grad_f(za);
+                g3.y = gy.y * silu_grad_f(zb);
+                if (t < t_end) {  // weight gradient: own tile only
+                    dwa[0] += g3.x * x0.x; dwa[1] += g3.x * x1.x; dwa[2] += g3.x * x2.x; dwa[3] += g3.x * x3.x;
+                    dwb[0] += g3.y * x0.y; dwb[1] += g3.y * x1.y; dwb[2] += g3.y * x2.y; dwb[3] += g3.y * x3.y;
+                }
+            }
+            const int tq = t - 3;  // the input whose gradient is now complete
+            const float da = wa[0] * g3.x + wa[1] * g2.x + wa[2] * g1.x + wa[3] * g0.x;
+            const float db = wb[0] * g3.y + wb[1] * g2.y + wb[2] * g1.y + wb[3] * g0.y;
+            if (tq >= t0 && tq < t_end) {
+                store_pair<PAIR>(dxout + (long long)tq * p.D, two, da, db);
+            } else if (tq < 0 && t0 == 0 && p.dinit != nullptr) {
+                __nv_bfloat16* sd = p.dinit + ((long long)b * p.D + d) * 3 + (tq + 3);
+                sd[0] = __float2bfloat16_rn(da);
+                if (two) sd[3] = __float2bfloat16_rn(db);
+            }
+            x0 = x1; x1 = x2; x2 = x3;
+            g0 = g1; g1 = g2; g2 = g3;
+        }
+    } else
     for (int ts = t0; ts < t_end + 3; ts += CONV_BATCH_BWD) {
         float2 xs[CONV_BATCH_BWD], gs[CONV_BATCH_BWD];
 #pragma unroll
