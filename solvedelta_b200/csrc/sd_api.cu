@@ -887,7 +887,7 @@ int sd_conv4_silu_backward(const sd_conv4_backward_args* a, void* stream_) {
         else k_conv4_silu_bwd<false><<<grid, CONV_THREADS, 0, stream>>>(p);
     }
     const long long n = (long long)a->D * 4;
-    k_column_sum<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p.dw_part, a->B * tiles, n, a->dweight);
+    launch_column_sum(p.dw_part, a->B * tiles, n, a->dweight, stream);
     return launch_status();
 }
 
@@ -944,9 +944,9 @@ int sd_kda_gate_backward(const sd_kda_gate_args* a, void* stream_) {
     } else {
         k_kda_gate_bwd<<<dim3(blocks, (HR + 255) / 256), 256, 0, stream>>>(p);
     }
-    k_column_sum<<<(HR + 255) / 256, 256, 0, stream>>>(p.dbias_part, blocks, HR, a->dbias);
-    k_column_sum<<<(HR + 255) / 256, 256, 0, stream>>>(p.dA_part, blocks, HR, dA_cols);
-    k_group_sum<<<(a->H + 63) / 64, 64, 0, stream>>>(dA_cols, a->H, a->r, a->dlog_rate);
+    launch_column_sum(p.dbias_part, blocks, HR, a->dbias, stream);
+    launch_column_sum(p.dA_part, blocks, HR, dA_cols, stream);
+    k_group_sum<<<a->H, 32, 0, stream>>>(dA_cols, a->H, a->r, a->dlog_rate);
     return launch_status();
 }
 
@@ -990,7 +990,7 @@ int sd_norm_gate_backward(const sd_norm_gate_args* a, void* stream_) {
     p.dw_part = reinterpret_cast<float*>(a->scratch);
     p.rows_per_block = NORM_ROWS_PER_BLOCK;
     k_norm_gate_bwd<<<blocks, 256, 0, stream>>>(p);
-    k_column_sum<<<(a->V + 255) / 256, 256, 0, stream>>>(p.dw_part, blocks, a->V, a->dweight);
+    launch_column_sum(p.dw_part, blocks, a->V, a->dweight, stream);
     return launch_status();
 }
 

@@ -421,22 +421,40 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv4_silu_bwd_masked(ConvPara
     }
 }
 
-// out[n] = sum_p partial[p][n]: deterministic column sum of per-CTA partials.
-__global__ void k_column_sum(const float* part, int P, long long N, float* out) {
-    const long long n = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (n >= N) return;
+// out[n] = sum_p partial[p][n]: deterministic column sum of per-CTA partials.  A CTA takes 32 columns with 32
+// row lanes each (a lane adds every 32nd partial, eight loads in flight), then one thread per column adds the
+// lanes in a fixed order.
+constexpr int CSUM_COLS = 32, CSUM_LANES = 32;
+__global__ void __launch_bounds__(CSUM_COLS * CSUM_LANES) k_column_sum(const float* part, int P, long long N, float* out) {
+    __shared__ float s_lane[CSUM_LANES][CSUM_COLS + 1];
+    const int cx = threadIdx.x % CSUM_COLS, ry = threadIdx.x / CSUM_COLS;
+    const long long n = (long long)blockIdx.x * CSUM_COLS + cx;
     float acc = 0.f;
-    for (int q = 0; q < P; ++q) acc += part[(long long)q * N + n];
-    out[n] = acc;
+    if (n < N) {
+#pragma unroll 8
+        for (int q = ry; q < P; q += CSUM_LANES) acc += part[(long long)q * N + n];
+    }
+    s_lane[ry][cx] = acc;
+    __syncthreads();
+    if (ry == 0 && n < N) {
+        float total = 0.f;
+#pragma unroll
+        for (int l = 0; l < CSUM_LANES; ++l) total += s_lane[l][cx];
+        out[n] = total;
+    }
+}
+inline void launch_column_sum(const float* part, int P, long long N, float* out, cudaStream_t stream) {
+    k_column_sum<<<(unsigned)((N + CSUM_COLS - 1) / CSUM_COLS), CSUM_COLS * CSUM_LANES, 0, stream>>>(part, P, N, out);
 }
 
-// out[g] = sum_c in[g*width + c]
-__global__ void k_group_sum(const float* in, int groups, int width, float* out) {
-    const int g = blockIdx.x * blockDim.x + threadIdx.x;
-    if (g >= groups) return;
+// out[g] = sum_c in[g*width + c]: one warp per group, lanes stride the row, fixed shuffle tree.
+__global__ void __launch_bounds__(32) k_group_sum(const float* in, int groups, int width, float* out) {
+    const int g = blockIdx.x, lane = threadIdx.x;
     float acc = 0.f;
-    for (int c = 0; c < width; ++c) acc += in[(long long)g * width + c];
-    out[g] = acc;
+    for (int c = lane; c < width; c += 32) acc += in[(long long)g * width + c];
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+    if (lane == 0) out[g] = acc;
 }
 
 // ---- decay gate: log_decay = -exp(A[h]) * softplus(raw + bias[h][c]) ---------

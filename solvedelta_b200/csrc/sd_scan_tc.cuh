@@ -289,6 +289,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, c
         const long long gi = chunk_at(step);
         const int b = step & 1;
         TC_STAMP(0);
+        // next step's Q: its ring slot was last read by the first contraction of the previous step, which every
+        // thread has seen complete, so the load gets a whole step to land
+        issue(step + 1);
         const float lam = p.lam[gi * DP + row];
         // the slice, transposed and rounded, as this step's A operand
 #pragma unroll
@@ -314,8 +317,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_state_scan_tc(ScanParams p, c
         }
         __syncwarp();
         TC_STAMP(1);
-        // behind the first contraction: prefetch, this thread's R (and P) values, checkpoints, decay
-        issue(step + 1);
+        // behind the first contraction: this thread's R (and P) values, checkpoints, decay
         // The warps that own X^T rows (lane quarters 0 and 1) take their P values and later run the X
         // epilogue; the other two quarters turn R, for two state rows each (their own and the one 64
         // below).  Both read the panels as TMA landed them: rows of consecutive columns, one lane each.
