@@ -473,6 +473,15 @@ struct GateParams {
 };
 
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(__expf(z)); }
+// sigmoid(z) and softplus(z) from one exponential, en = exp(-|z|) in (0, 1]:
+// softplus = max(z, 0) + log1p(en) (two series terms below 1e-3, where log(1 + en) would lose its digits).
+// The reverse kernels use it: softplus only enters the sum for the rate gradient there.
+__device__ __forceinline__ void sigmoid_softplus(float z, float& sig, float& sp) {
+    const float en = __expf(-fabsf(z));
+    const float inv = __fdividef(1.f, 1.f + en);
+    sig = z >= 0.f ? inv : en * inv;
+    sp = fmaxf(z, 0.f) + (en < 1e-3f ? en * (1.f - 0.5f * en) : __logf(1.f + en));
+}
 
 __global__ void k_kda_gate_fwd(GateParams p) {
     const long long total = p.N * p.H * p.r;
@@ -522,11 +531,12 @@ __global__ void __launch_bounds__(256) k_kda_gate_bwd(GateParams p) {
         const long long i = n * HR + hc;
         const float z = __bfloat162float(p.raw[i]) + bias;
         const float g = p.dout[i];
-        const float sig = 1.f / (1.f + __expf(-z));
+        float sig, sp;
+        sigmoid_softplus(z, sig, sp);
         const float dz = g * rate * sig;
         p.draw[i] = __float2bfloat16_rn(dz);
         sum_b += dz;
-        sum_a += g * rate * softplus_f(z);  // d/dA of -exp(A) softplus = out
+        sum_a += g * rate * sp;  // d/dA of -exp(A) softplus = out
     }
     p.dbias_part[(long long)blockIdx.x * HR + hc] = sum_b;
     p.dA_part[(long long)blockIdx.x * HR + hc] = sum_a;  // summed over c on the host side of the ABI
@@ -551,23 +561,36 @@ __global__ void __launch_bounds__(256) k_kda_gate_bwd_v8(GateParams p, int cgb) 
         const float bias[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
         const long long n0 = (long long)blockIdx.x * p.rows_per_block;
         const long long n1 = (n0 + p.rows_per_block < p.N) ? n0 + p.rows_per_block : p.N;
-#pragma unroll 2
-        for (long long n = n0 + lane; n < n1; n += lanes) {
+        // the next row's 48 bytes are requested before this row is worked on
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        float4 g0 = make_float4(0.f, 0.f, 0.f, 0.f), g1 = g0;
+        long long n = n0 + lane;
+        if (n < n1) {
+            raw = *reinterpret_cast<const uint4*>(p.raw + n * HR + hc);
+            g0 = *reinterpret_cast<const float4*>(p.dout + n * HR + hc);
+            g1 = *reinterpret_cast<const float4*>(p.dout + n * HR + hc + 4);
+        }
+        for (; n < n1; n += lanes) {
             const long long i = n * HR + hc;
-            const uint4 raw = *reinterpret_cast<const uint4*>(p.raw + i);
-            const float4 g0 = *reinterpret_cast<const float4*>(p.dout + i);
-            const float4 g1 = *reinterpret_cast<const float4*>(p.dout + i + 4);
+            const uint4 raw_c = raw;
             const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            if (n + lanes < n1) {
+                const long long in = i + (long long)lanes * HR;
+                raw = *reinterpret_cast<const uint4*>(p.raw + in);
+                g0 = *reinterpret_cast<const float4*>(p.dout + in);
+                g1 = *reinterpret_cast<const float4*>(p.dout + in + 4);
+            }
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw_c);
             float dz[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const float2 f = __bfloat1622float2(h[e >> 1]);
                 const float z = ((e & 1) ? f.y : f.x) + bias[e];
-                const float sig = 1.f / (1.f + __expf(-z));
+                float sig, sp;
+                sigmoid_softplus(z, sig, sp);
                 dz[e] = g[e] * rate * sig;
                 sb[e] += dz[e];
-                sa[e] += g[e] * rate * softplus_f(z);
+                sa[e] += g[e] * rate * sp;
             }
             uint4 outv;
             __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&outv);
@@ -612,23 +635,31 @@ struct NormParams {
     int rows_per_block;
 };
 
-// Eight channels of a BF16 row starting at c0; channels >= V read as zero.  One 16-byte
-// access when V is a multiple of eight (rows then start on 16-byte boundaries).
-__device__ __forceinline__ void norm_load8(const __nv_bfloat16* row, int c0, int V, bool live, float (&x)[8]) {
+// Eight channels of a BF16 row starting at c0, as they lie (channels >= V and dead rows read as zero).  One
+// 16-byte access when V is a multiple of eight (rows then start on 16-byte boundaries).
+__device__ __forceinline__ uint4 norm_raw8(const __nv_bfloat16* row, int c0, int V, bool live) {
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
     if ((V & 7) == 0) {
-        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
         if (live && c0 < V) raw = *reinterpret_cast<const uint4*>(row + c0);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(h[e]);
-            x[2 * e] = f.x;
-            x[2 * e + 1] = f.y;
-        }
     } else {
+        __nv_bfloat16* h = reinterpret_cast<__nv_bfloat16*>(&raw);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) x[e] = (live && c0 + e < V) ? __bfloat162float(row[c0 + e]) : 0.f;
+        for (int e = 0; e < 8; ++e)
+            if (live && c0 + e < V) h[e] = row[c0 + e];
     }
+    return raw;
+}
+__device__ __forceinline__ void norm_unpack8(const uint4& raw, float (&x)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        x[2 * e] = f.x;
+        x[2 * e + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void norm_load8(const __nv_bfloat16* row, int c0, int V, bool live, float (&x)[8]) {
+    norm_unpack8(norm_raw8(row, c0, V, live), x);
 }
 __device__ __forceinline__ void norm_store8(__nv_bfloat16* row, int c0, int V, bool live, const float (&x)[8]) {
     if (!live || c0 >= V) return;
@@ -665,20 +696,31 @@ __global__ void __launch_bounds__(256) k_norm_gate_fwd(NormParams p) {
     }
 }
 
-__global__ void __launch_bounds__(256) k_norm_gate_bwd(NormParams p) {
+__global__ void __launch_bounds__(256, 3) k_norm_gate_bwd(NormParams p) {
     __shared__ float s_dw[16][DP];
     const int lr = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
     float dw[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     const long long n0 = (long long)blockIdx.x * p.rows_per_block;
     const long long n1 = (n0 + p.rows_per_block < p.N) ? n0 + p.rows_per_block : p.N;
+    // the next row's three 16-byte pieces are requested before this row is worked on
+    uint4 rx = norm_raw8(p.x + (n0 + lr) * p.V, c0, p.V, n0 + lr < n1);
+    uint4 rg = norm_raw8(p.gate + (n0 + lr) * p.V, c0, p.V, n0 + lr < n1);
+    uint4 rd = norm_raw8(p.dout + (n0 + lr) * p.V, c0, p.V, n0 + lr < n1);
     for (long long base = n0; base < n1; base += 16) {
         const long long row = base + lr;
         const bool live = row < n1;
         float x[8], g[8], dy[8];
         float ss = 0.f;
-        norm_load8(p.x + row * p.V, c0, p.V, live, x);
-        norm_load8(p.gate + row * p.V, c0, p.V, live, g);
-        norm_load8(p.dout + row * p.V, c0, p.V, live, dy);
+        norm_unpack8(rx, x);
+        norm_unpack8(rg, g);
+        norm_unpack8(rd, dy);
+        {
+            const long long nrow = row + 16;
+            const bool nlive = nrow < n1;
+            rx = norm_raw8(p.x + nrow * p.V, c0, p.V, nlive);
+            rg = norm_raw8(p.gate + nrow * p.V, c0, p.V, nlive);
+            rd = norm_raw8(p.dout + nrow * p.V, c0, p.V, nlive);
+        }
 #pragma unroll
         for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
         ss = row_sum16(ss);
