@@ -106,29 +106,52 @@ typedef struct {
 } sd_decode_args;
 
 /*
- * Inference glue of the block around the mixer (no reverse pass; BF16 rows, contiguous):
+ * Glue of the block around the mixer (BF16 rows, contiguous), forward and reverse:
  * sd_add_rmsnorm  sum = x + delta and normed = RMSNorm(sum) * weight in one pass: a residual add and
- *                 the norm that follows it (causallsso/modeling_solvedelta.py:230-255)
+ *                 the norm that follows it (causallsso/modeling_solvedelta.py:230-255).  delta may be
+ *                 NULL (the norm alone: sum is not written) when D is a multiple of 256 up to 2048.
+ * sd_add_rmsnorm_backward  the one gradient x and delta share, dsum + d normed / d sum, and the weight
+ *                 gradient; D a multiple of 256 up to 2048 (else SD_ERR_UNSUPPORTED_SHAPE)
  * sd_swiglu       out = silu(gate) * value for rows [gate | value] (modeling_solvedelta.py:68-101)
+ * sd_swiglu_backward  the gradient row [d gate | d value] from dout
  */
 typedef struct {
     int64_t rows;
     int32_t D;
     float eps;
-    const void *x, *delta;             /* BF16 [rows][D] */
+    const void *x, *delta;             /* BF16 [rows][D]; delta may be NULL */
     const float *weight;               /* [D] */
-    void *sum, *normed;                /* out BF16 [rows][D] */
+    void *sum, *normed;                /* out BF16 [rows][D]; sum unused when delta is NULL */
 } sd_add_rmsnorm_args;
+
+typedef struct {
+    int64_t rows;
+    int32_t D;
+    float eps;
+    const void *sum;                   /* BF16 [rows][D]: the forward's sum (x itself when delta was NULL) */
+    const float *weight;               /* [D] */
+    const void *dsum;                  /* BF16 cotangent of sum, or NULL */
+    const void *dnormed;               /* BF16 cotangent of normed */
+    void *dx;                          /* out BF16 [rows][D]: gradient of x, and of delta */
+    float *dweight;                    /* out [D] */
+    void *scratch;                     /* sd_add_rmsnorm_backward_scratch_bytes */
+    size_t scratch_bytes;
+} sd_add_rmsnorm_backward_args;
 
 typedef struct {
     int64_t rows;
     int32_t I;
     const void *gate_value;            /* BF16 [rows][2 I] */
-    void *out;                         /* BF16 [rows][I] */
+    void *out;                         /* forward: BF16 [rows][I] */
+    const void *dout;                  /* backward: BF16 [rows][I] */
+    void *dgate_value;                 /* backward: out BF16 [rows][2 I] */
 } sd_swiglu_args;
 
 int sd_add_rmsnorm(const sd_add_rmsnorm_args *args, void *stream);
+size_t sd_add_rmsnorm_backward_scratch_bytes(int64_t rows, int32_t D);
+int sd_add_rmsnorm_backward(const sd_add_rmsnorm_backward_args *args, void *stream);
 int sd_swiglu(const sd_swiglu_args *args, void *stream);
+int sd_swiglu_backward(const sd_swiglu_args *args, void *stream);
 
 /*
  * The whole mixer glue of a cached single-token step in the decode kernel: q, k, v come from

@@ -114,9 +114,16 @@ class AddRmsnormArgs(ctypes.Structure):
                 ("sum", ctypes.c_void_p), ("normed", ctypes.c_void_p)]
 
 
+class AddRmsnormBackwardArgs(ctypes.Structure):
+    _fields_ = [("rows", ctypes.c_int64), ("D", ctypes.c_int32), ("eps", ctypes.c_float),
+                ("sum", ctypes.c_void_p), ("weight", ctypes.c_void_p), ("dsum", ctypes.c_void_p),
+                ("dnormed", ctypes.c_void_p), ("dx", ctypes.c_void_p), ("dweight", ctypes.c_void_p),
+                ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t)]
+
+
 class SwigluArgs(ctypes.Structure):
     _fields_ = [("rows", ctypes.c_int64), ("I", ctypes.c_int32), ("gate_value", ctypes.c_void_p),
-                ("out", ctypes.c_void_p)]
+                ("out", ctypes.c_void_p), ("dout", ctypes.c_void_p), ("dgate_value", ctypes.c_void_p)]
 
 
 class MixerDecodeArgs(ctypes.Structure):
@@ -197,6 +204,7 @@ EXPORTS = (
     "sd_backward_launches", "sd_panel_info", "sd_status_string", "sd_version",
     "sd_chunk_tokens", "sd_forward_static", "sd_panel_kind", "sd_device_fault", "sd_device_fault_clear",
     "sd_predictor_forward", "sd_predictor_backward", "sd_mixer_decode_step", "sd_add_rmsnorm", "sd_swiglu",
+    "sd_add_rmsnorm_backward_scratch_bytes", "sd_add_rmsnorm_backward", "sd_swiglu_backward",
     "sd_conv4_backward_scratch_bytes", "sd_conv4_silu_forward", "sd_conv4_silu_backward",
     "sd_kda_gate_backward_scratch_bytes", "sd_kda_gate_forward", "sd_kda_gate_backward",
     "sd_norm_gate_backward_scratch_bytes", "sd_norm_gate_forward", "sd_norm_gate_backward",
@@ -264,9 +272,12 @@ def _declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.sd_kda_gate_backward_scratch_bytes.argtypes = [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32]
     lib.sd_norm_gate_backward_scratch_bytes.restype = ctypes.c_size_t
     lib.sd_norm_gate_backward_scratch_bytes.argtypes = [ctypes.c_int64, ctypes.c_int32]
+    lib.sd_add_rmsnorm_backward_scratch_bytes.restype = ctypes.c_size_t
+    lib.sd_add_rmsnorm_backward_scratch_bytes.argtypes = [ctypes.c_int64, ctypes.c_int32]
     for name, struct in (("sd_predictor_forward", PredictorForwardArgs), ("sd_predictor_backward", PredictorBackwardArgs),
                          ("sd_mixer_decode_step", MixerDecodeArgs), ("sd_add_rmsnorm", AddRmsnormArgs),
-                         ("sd_swiglu", SwigluArgs),
+                         ("sd_swiglu", SwigluArgs), ("sd_swiglu_backward", SwigluArgs),
+                         ("sd_add_rmsnorm_backward", AddRmsnormBackwardArgs),
                          ("sd_conv4_silu_forward", Conv4ForwardArgs), ("sd_conv4_silu_backward", Conv4BackwardArgs),
                          ("sd_kda_gate_forward", KdaGateArgs), ("sd_kda_gate_backward", KdaGateArgs),
                          ("sd_norm_gate_forward", NormGateArgs), ("sd_norm_gate_backward", NormGateArgs)):

@@ -978,7 +978,16 @@ int sd_norm_gate_backward(const sd_norm_gate_args* a, void* stream_) {
     if (a->V > DP) return SD_ERR_UNSUPPORTED_SHAPE;
     if (a->scratch_bytes < sd_norm_gate_backward_scratch_bytes(a->rows, a->V)) return SD_ERR_BUFFER_TOO_SMALL;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-    const int blocks = (int)((a->rows + NORM_ROWS_PER_BLOCK - 1) / NORM_ROWS_PER_BLOCK);
+    // rows per CTA: at least NORM_ROWS_PER_BLOCK (the scratch is sized for that), stretched so that the grid is a
+    // whole number of waves of resident CTAs
+    long long rpb = NORM_ROWS_PER_BLOCK;
+    {
+        const long long wave = resident_ctas(k_norm_gate_bwd, 256, 0);
+        const long long waves = a->rows / (wave * NORM_ROWS_PER_BLOCK);
+        if (waves >= 1) rpb = ((a->rows + wave * waves - 1) / (wave * waves) + 15) / 16 * 16;
+        if (rpb < NORM_ROWS_PER_BLOCK) rpb = NORM_ROWS_PER_BLOCK;
+    }
+    const int blocks = (int)((a->rows + rpb - 1) / rpb);
     NormParams p{};
     p.N = a->rows; p.V = a->V; p.eps = a->eps;
     p.x = reinterpret_cast<const __nv_bfloat16*>(a->x);
@@ -988,16 +997,17 @@ int sd_norm_gate_backward(const sd_norm_gate_args* a, void* stream_) {
     p.dx = reinterpret_cast<__nv_bfloat16*>(a->dx);
     p.dgate = reinterpret_cast<__nv_bfloat16*>(a->dgate);
     p.dw_part = reinterpret_cast<float*>(a->scratch);
-    p.rows_per_block = NORM_ROWS_PER_BLOCK;
+    p.rows_per_block = (int)rpb;
     k_norm_gate_bwd<<<blocks, 256, 0, stream>>>(p);
     launch_column_sum(p.dw_part, blocks, a->V, a->dweight, stream);
     return launch_status();
 }
 
 int sd_add_rmsnorm(const sd_add_rmsnorm_args* a, void* stream_) {
-    if (!a || a->rows <= 0 || a->D <= 0 || !a->x || !a->delta || !a->weight || !a->sum || !a->normed)
+    if (!a || a->rows <= 0 || a->D <= 0 || !a->x || !a->weight || !a->normed || (a->delta && !a->sum))
         return SD_ERR_INVALID_ARGUMENT;
     if (a->rows > 0x7fffffffLL) return SD_ERR_UNSUPPORTED_SHAPE;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     AddNormParams p{};
     p.N = a->rows; p.D = a->D; p.eps = a->eps;
     p.x = reinterpret_cast<const __nv_bfloat16*>(a->x);
@@ -1005,8 +1015,42 @@ int sd_add_rmsnorm(const sd_add_rmsnorm_args* a, void* stream_) {
     p.w = a->weight;
     p.sum = reinterpret_cast<__nv_bfloat16*>(a->sum);
     p.normed = reinterpret_cast<__nv_bfloat16*>(a->normed);
-    k_add_rmsnorm<<<(unsigned)a->rows, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
+    if (addnorm_rows_ok(a->D)) {
+        dispatch_addnorm_rows(p, false, stream);
+    } else {
+        if (!a->delta) return SD_ERR_UNSUPPORTED_SHAPE;   // the norm alone is only built for the row kernels
+        k_add_rmsnorm<<<(unsigned)a->rows, 256, 0, stream>>>(p);
+    }
     return launch_status();
+}
+
+size_t sd_add_rmsnorm_backward_scratch_bytes(int64_t rows, int32_t D) {
+    if (rows <= 0 || D <= 0) return 0;
+    return align256(size_t(addnorm_blocks(rows)) * size_t(D) * sizeof(float));
+}
+
+int sd_add_rmsnorm_backward(const sd_add_rmsnorm_backward_args* a, void* stream_) {
+    if (!a || a->rows <= 0 || a->D <= 0 || !a->sum || !a->weight || !a->dnormed || !a->dx || !a->dweight || !a->scratch)
+        return SD_ERR_INVALID_ARGUMENT;
+    if (!addnorm_rows_ok(a->D)) return SD_ERR_UNSUPPORTED_SHAPE;
+    if (a->scratch_bytes < sd_add_rmsnorm_backward_scratch_bytes(a->rows, a->D)) return SD_ERR_BUFFER_TOO_SMALL;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    AddNormParams p{};
+    p.N = a->rows; p.D = a->D; p.eps = a->eps;
+    p.sum = const_cast<__nv_bfloat16*>(reinterpret_cast<const __nv_bfloat16*>(a->sum));
+    p.w = a->weight;
+    p.dsum = reinterpret_cast<const __nv_bfloat16*>(a->dsum);
+    p.dnormed = reinterpret_cast<const __nv_bfloat16*>(a->dnormed);
+    p.dx = reinterpret_cast<__nv_bfloat16*>(a->dx);
+    p.dw_part = reinterpret_cast<float*>(a->scratch);
+    const unsigned blocks = dispatch_addnorm_rows(p, true, stream);
+    launch_column_sum(p.dw_part, (int)blocks, a->D, a->dweight, stream);
+    return launch_status();
+}
+
+static unsigned swiglu_blocks(const sd_swiglu_args* a) {
+    long long blocks = (a->rows * ((a->I + 7) / 8) + 255) / 256;
+    return (unsigned)(blocks > 148 * 32 ? 148 * 32 : blocks);
 }
 
 int sd_swiglu(const sd_swiglu_args* a, void* stream_) {
@@ -1015,9 +1059,18 @@ int sd_swiglu(const sd_swiglu_args* a, void* stream_) {
     p.N = a->rows; p.I = a->I;
     p.in = reinterpret_cast<const __nv_bfloat16*>(a->gate_value);
     p.out = reinterpret_cast<__nv_bfloat16*>(a->out);
-    long long blocks = (a->rows * ((a->I + 7) / 8) + 255) / 256;
-    if (blocks > 148 * 32) blocks = 148 * 32;
-    k_swiglu<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
+    k_swiglu<<<swiglu_blocks(a), 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
+    return launch_status();
+}
+
+int sd_swiglu_backward(const sd_swiglu_args* a, void* stream_) {
+    if (!a || a->rows <= 0 || a->I <= 0 || !a->gate_value || !a->dout || !a->dgate_value) return SD_ERR_INVALID_ARGUMENT;
+    SwigluParams p{};
+    p.N = a->rows; p.I = a->I;
+    p.in = reinterpret_cast<const __nv_bfloat16*>(a->gate_value);
+    p.dout = reinterpret_cast<const __nv_bfloat16*>(a->dout);
+    p.din = reinterpret_cast<__nv_bfloat16*>(a->dgate_value);
+    k_swiglu_bwd<<<swiglu_blocks(a), 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
     return launch_status();
 }
 

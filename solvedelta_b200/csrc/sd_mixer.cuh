@@ -763,9 +763,14 @@ struct AddNormParams {
     long long N;
     int D;
     float eps;
-    const __nv_bfloat16 *x, *delta;
+    const __nv_bfloat16 *x, *delta;   // delta may be null: sum = x, nothing is stored for it
     const float* w;
     __nv_bfloat16 *sum, *normed;
+    // reverse pass: cotangents of the two outputs (dsum may be null), the one gradient x and delta share, partial
+    // weight gradients [CTAs][D]
+    const __nv_bfloat16 *dsum, *dnormed;
+    __nv_bfloat16* dx;
+    float* dw_part;
 };
 
 __global__ void __launch_bounds__(256) k_add_rmsnorm(AddNormParams p) {
@@ -804,6 +809,178 @@ __global__ void __launch_bounds__(256) k_add_rmsnorm(AddNormParams p) {
     }
 }
 
+// The same pair for rows of width D = 256 IT, one warp per row (a lane holds eight channels of every 256), used
+// when D allows it; this is also the forward pass of training.  delta == nullptr: the norm alone.
+constexpr int ADDNORM_WARPS = 4;
+template <int IT>
+__global__ void __launch_bounds__(32 * ADDNORM_WARPS) k_add_rmsnorm_rows(AddNormParams p) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long stride = (long long)gridDim.x * ADDNORM_WARPS;
+    for (long long row = (long long)blockIdx.x * ADDNORM_WARPS + warp; row < p.N; row += stride) {
+        float s8[IT][8];
+        float ss = 0.f;
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+            const int c0 = it * 256 + lane * 8;
+            norm_load8(p.x + row * p.D, c0, p.D, true, s8[it]);
+            if (p.delta != nullptr) {
+                float b[8];
+                norm_load8(p.delta + row * p.D, c0, p.D, true, b);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) s8[it][e] = __bfloat162float(__float2bfloat16_rn(s8[it][e] + b[e]));
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss = fmaf(s8[it][e], s8[it][e], ss);
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+        const float rstd = rsqrtf(ss / p.D + p.eps);
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+            const int c0 = it * 256 + lane * 8;
+            if (p.delta != nullptr) norm_store8(p.sum + row * p.D, c0, p.D, true, s8[it]);
+            const float4 w0 = *reinterpret_cast<const float4*>(p.w + c0), w1 = *reinterpret_cast<const float4*>(p.w + c0 + 4);
+            const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+            float y[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) y[e] = s8[it][e] * rstd * w[e];
+            norm_store8(p.normed + row * p.D, c0, p.D, true, y);
+        }
+    }
+}
+
+// A 16-byte load that stays where it is written: the compiler otherwise sinks the loads of a row to their first
+// use, which turns one memory phase per row into three.
+__device__ __forceinline__ uint4 load16_pinned(const __nv_bfloat16* p) {
+    uint4 r;
+    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
+}
+
+// Reverse of the pair: with y = s rstd w and rstd = (mean(s^2) + eps)^-1/2,
+//   ds = dsum + rstd (dn w - s rstd^2 mean(dn w s)),   dw = sum over rows of dn s rstd;
+// ds is the gradient of x and of delta alike.  One warp per row; a CTA adds its warps' weight gradients in shared
+// memory and leaves one partial row, which a column sum finishes.
+template <int IT>
+__global__ void __launch_bounds__(32 * ADDNORM_WARPS, 3) k_add_rmsnorm_bwd(AddNormParams p) {
+    extern __shared__ float s_dw[];   // [ADDNORM_WARPS][D]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long stride = (long long)gridDim.x * ADDNORM_WARPS;
+    // a warp's weight gradients live in its own row of shared memory (nobody else touches it before the barrier)
+    float* my_dw = s_dw + warp * p.D;
+#pragma unroll
+    for (int it = 0; it < IT; ++it) {
+        *reinterpret_cast<float4*>(my_dw + it * 256 + lane * 8) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4*>(my_dw + it * 256 + lane * 8 + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (long long row = (long long)blockIdx.x * ADDNORM_WARPS + warp; row < p.N; row += stride) {
+        // every 16-byte piece of the row is requested at once and kept as it lies (BF16); the passes below unpack
+        uint4 rs[IT], rn[IT], ru[IT];
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+            const int c0 = it * 256 + lane * 8;
+            rs[it] = load16_pinned(p.sum + row * p.D + c0);
+            rn[it] = load16_pinned(p.dnormed + row * p.D + c0);
+            ru[it] = p.dsum != nullptr ? load16_pinned(p.dsum + row * p.D + c0) : make_uint4(0u, 0u, 0u, 0u);
+        }
+        float ss = 0.f, dot = 0.f;
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+            float s8[8];
+            norm_unpack8(rs[it], s8);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss = fmaf(s8[e], s8[e], ss);
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+        const float rstd = rsqrtf(ss / p.D + p.eps);
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+            const int c0 = it * 256 + lane * 8;
+            const float4 w0 = *reinterpret_cast<const float4*>(p.w + c0), w1 = *reinterpret_cast<const float4*>(p.w + c0 + 4);
+            const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+            float s8[8], dn[8];
+            norm_unpack8(rs[it], s8);
+            norm_unpack8(rn[it], dn);
+            float4 a0 = *reinterpret_cast<const float4*>(my_dw + c0), a1 = *reinterpret_cast<const float4*>(my_dw + c0 + 4);
+            float dw[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                dw[e] = fmaf(dn[e] * rstd, s8[e], dw[e]);
+                dot = fmaf(dn[e] * w[e], s8[e], dot);
+            }
+            *reinterpret_cast<float4*>(my_dw + c0) = make_float4(dw[0], dw[1], dw[2], dw[3]);
+            *reinterpret_cast<float4*>(my_dw + c0 + 4) = make_float4(dw[4], dw[5], dw[6], dw[7]);
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, m);
+        const float coef = dot * rstd * rstd / p.D;
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+            const int c0 = it * 256 + lane * 8;
+            const float4 w0 = *reinterpret_cast<const float4*>(p.w + c0), w1 = *reinterpret_cast<const float4*>(p.w + c0 + 4);
+            const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+            float s8[8], dn[8], up[8], ds[8];
+            norm_unpack8(rs[it], s8);
+            norm_unpack8(rn[it], dn);
+            norm_unpack8(ru[it], up);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ds[e] = up[e] + rstd * (dn[e] * w[e] - s8[e] * coef);
+            norm_store8(p.dx + row * p.D, c0, p.D, true, ds);
+        }
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < p.D; c += 32 * ADDNORM_WARPS) {
+        float acc = 0.f;
+#pragma unroll
+        for (int q = 0; q < ADDNORM_WARPS; ++q) acc += s_dw[q * p.D + c];
+        p.dw_part[(long long)blockIdx.x * p.D + c] = acc;
+    }
+}
+
+// widths the one-warp-per-row kernels take: whole groups of 256 channels, at most eight of them
+inline bool addnorm_rows_ok(int D) { return D % 256 == 0 && D <= 2048; }
+// upper bound of the CTAs either kernel is launched with (sizes the partial weight gradients)
+inline unsigned addnorm_blocks(long long rows) {
+    long long blocks = (rows + ADDNORM_WARPS - 1) / ADDNORM_WARPS;
+    return (unsigned)(blocks > 148 * 8 ? 148 * 8 : blocks);
+}
+// CTAs of `kernel` the whole device holds at once: a grid-stride kernel launched with more than that runs a partly
+// filled last wave
+template <class K>
+inline unsigned resident_ctas(K kernel, int threads, size_t smem) {
+    int per_sm = 0, sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem);
+    return unsigned(per_sm < 1 ? 1 : per_sm) * unsigned(sms < 1 ? 1 : sms);
+}
+// returns the number of CTAs launched (= partial weight-gradient rows of the reverse kernel)
+template <int IT>
+inline unsigned launch_addnorm_rows(const AddNormParams& p, bool reverse, cudaStream_t stream) {
+    const int threads = 32 * ADDNORM_WARPS;
+    const size_t smem = reverse ? size_t(ADDNORM_WARPS) * p.D * sizeof(float) : 0;
+    unsigned blocks = addnorm_blocks(p.N);
+    const unsigned wave = reverse ? resident_ctas(k_add_rmsnorm_bwd<IT>, threads, smem)
+                                  : resident_ctas(k_add_rmsnorm_rows<IT>, threads, smem);
+    if (blocks > wave) blocks = wave;
+    if (reverse) k_add_rmsnorm_bwd<IT><<<blocks, threads, smem, stream>>>(p);
+    else k_add_rmsnorm_rows<IT><<<blocks, threads, smem, stream>>>(p);
+    return blocks;
+}
+inline unsigned dispatch_addnorm_rows(const AddNormParams& p, bool reverse, cudaStream_t stream) {
+    switch (p.D / 256) {
+        case 1: return launch_addnorm_rows<1>(p, reverse, stream);
+        case 2: return launch_addnorm_rows<2>(p, reverse, stream);
+        case 3: return launch_addnorm_rows<3>(p, reverse, stream);
+        case 4: return launch_addnorm_rows<4>(p, reverse, stream);
+        case 5: return launch_addnorm_rows<5>(p, reverse, stream);
+        case 6: return launch_addnorm_rows<6>(p, reverse, stream);
+        case 7: return launch_addnorm_rows<7>(p, reverse, stream);
+        default: return launch_addnorm_rows<8>(p, reverse, stream);
+    }
+}
+
 // out = silu(gate) * value for rows [gate | value] of width 2 I (the gated MLP between its two
 // projections, causallsso/modeling_solvedelta.py:68-101).
 struct SwigluParams {
@@ -811,6 +988,8 @@ struct SwigluParams {
     int I;
     const __nv_bfloat16* in;   // [N][2 I]
     __nv_bfloat16* out;        // [N][I]
+    const __nv_bfloat16* dout; // reverse pass: [N][I]
+    __nv_bfloat16* din;        // reverse pass: [N][2 I]
 };
 
 __global__ void __launch_bounds__(256) k_swiglu(SwigluParams p) {
@@ -825,6 +1004,28 @@ __global__ void __launch_bounds__(256) k_swiglu(SwigluParams p) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) y[e] = silu_f(g[e]) * v[e];
         norm_store8(p.out + row * p.I, c0, p.I, true, y);
+    }
+}
+
+// Reverse of k_swiglu: d gate = dout value silu'(gate), d value = dout silu(gate), written as one [gate | value] row.
+__global__ void __launch_bounds__(256) k_swiglu_bwd(SwigluParams p) {
+    const long long per_row = (p.I + 7) / 8, total = p.N * per_row;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long row = idx / per_row;
+        const int c0 = (int)(idx - row * per_row) * 8;
+        float g[8], v[8], d[8], dg[8], dv[8];
+        norm_load8(p.in + row * 2 * p.I, c0, p.I, true, g);
+        norm_load8(p.in + row * 2 * p.I + p.I, c0, p.I, true, v);
+        norm_load8(p.dout + row * p.I, c0, p.I, true, d);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float sg = sigmoidf_(g[e]), act = g[e] * sg;
+            dg[e] = d[e] * v[e] * (sg + act * (1.f - sg));
+            dv[e] = d[e] * act;
+        }
+        norm_store8(p.din + row * 2 * p.I, c0, p.I, true, dg);
+        norm_store8(p.din + row * 2 * p.I + p.I, c0, p.I, true, dv);
     }
 }
 

@@ -220,38 +220,127 @@ def mixer_decode_step(u: torch.Tensor, h: torch.Tensor, erase_raw: torch.Tensor,
 
 
 @torch.no_grad()
-def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, eps: float):
-    """``s = x + delta`` and ``RMSNorm(s) * weight`` in one pass (inference only): returns ``(s, normed)``, both
-    BF16 with the shape of ``x``.  ``weight`` FP32 ``[D]``."""
-    _require_bf16_cuda("x", x)
-    _require_bf16_cuda("delta", delta)
-    if x.shape != delta.shape or weight.shape != (x.shape[-1],) or weight.dtype != torch.float32:
-        raise ValueError("x and delta must share a shape [...,D]; weight FP32 [D]")
+def add_rmsnorm_reverse_supported(width: int) -> bool:
+    """Row widths the reverse pass of :func:`add_rmsnorm` is built for (whole groups of 256 channels, up to 2048)."""
+    return width % 256 == 0 and 0 < width <= 2048
+
+
+def _add_rmsnorm_forward(xc, dc, w, eps):
     lib = _lib.load()
-    xc, dc = x.contiguous(), delta.contiguous()
-    D = x.shape[-1]
-    with torch.cuda.device(x.device):
-        total, normed = torch.empty_like(xc), torch.empty_like(xc)
-        a = _lib.AddRmsnormArgs(xc.numel() // D, D, float(eps), xc.data_ptr(), dc.data_ptr(), weight.data_ptr(),
-                                total.data_ptr(), normed.data_ptr())
-        _lib.check(lib.sd_add_rmsnorm(ctypes.byref(a), _stream(x.device)))
+    D = xc.shape[-1]
+    with torch.cuda.device(xc.device):
+        normed = torch.empty_like(xc)
+        total = torch.empty_like(xc) if dc is not None else xc
+        a = _lib.AddRmsnormArgs(xc.numel() // D, D, float(eps), xc.data_ptr(), dc.data_ptr() if dc is not None else None,
+                                w.data_ptr(), total.data_ptr() if dc is not None else None, normed.data_ptr())
+        _lib.check(lib.sd_add_rmsnorm(ctypes.byref(a), _stream(xc.device)))
     return total, normed
 
 
-@torch.no_grad()
-def swiglu(gate_value: torch.Tensor) -> torch.Tensor:
-    """``silu(gate) * value`` for rows ``[gate | value]`` (inference only): ``[..., 2 I]`` -> ``[..., I]`` BF16."""
-    _require_bf16_cuda("gate_value", gate_value)
-    if gate_value.shape[-1] % 2:
-        raise ValueError("the last axis must hold gate and value halves")
+class _AddRmsNorm(torch.autograd.Function):
+    """``(x + delta, RMSNorm(x + delta) * weight)`` with one reverse kernel: the cotangents of both outputs become
+    the single gradient that ``x`` and ``delta`` share, plus the weight gradient.  Only the sum is saved."""
+
+    @staticmethod
+    def forward(ctx, x, delta, weight, eps):
+        xc = x.contiguous()
+        dc = delta.contiguous() if delta is not None else None
+        w = weight.detach().float().contiguous()
+        total, normed = _add_rmsnorm_forward(xc, dc, w, eps)
+        ctx.save_for_backward(total, w)
+        ctx.eps, ctx.has_delta, ctx.weight_dtype = float(eps), delta is not None, weight.dtype
+        ctx.set_materialize_grads(False)
+        if delta is None:   # the sum is x itself: the caller keeps using x, this output is a placeholder
+            total = xc.new_empty(0)
+            ctx.mark_non_differentiable(total)
+        return total, normed
+
+    @staticmethod
+    def backward(ctx, dtotal, dnormed):
+        lib = _lib.load()
+        total, w = ctx.saved_tensors
+        if dnormed is None:
+            return dtotal, (dtotal if ctx.has_delta else None), None, None
+        D = total.shape[-1]
+        rows = total.numel() // D
+        dn = dnormed.to(torch.bfloat16).contiguous()
+        dt = dtotal.to(torch.bfloat16).contiguous() if dtotal is not None else None
+        with torch.cuda.device(total.device):
+            dx = torch.empty_like(total)
+            dw = torch.empty(D, dtype=torch.float32, device=total.device)
+            scratch = _scratch(lib.sd_add_rmsnorm_backward_scratch_bytes(rows, D), total.device)
+            a = _lib.AddRmsnormBackwardArgs(rows, D, ctx.eps, total.data_ptr(), w.data_ptr(),
+                                            dt.data_ptr() if dt is not None else None, dn.data_ptr(), dx.data_ptr(),
+                                            dw.data_ptr(), scratch.data_ptr(), scratch.numel())
+            _lib.check(lib.sd_add_rmsnorm_backward(ctypes.byref(a), _stream(total.device)))
+        return dx, (dx if ctx.has_delta else None), dw.to(ctx.weight_dtype), None
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float):
+    """``s = x + delta`` and ``RMSNorm(s) * weight`` in one pass: returns ``(s, normed)``, both BF16 with the shape
+    of ``x`` (``delta=None``: the norm alone, ``s`` is ``x``).  ``weight`` ``[D]``, FP32 without autograd; with
+    autograd any floating dtype, and ``D`` must satisfy :func:`add_rmsnorm_reverse_supported`."""
+    _require_bf16_cuda("x", x)
+    if delta is not None:
+        _require_bf16_cuda("delta", delta)
+        if x.shape != delta.shape:
+            raise ValueError("x and delta must share a shape [...,D]")
+    if weight.shape != (x.shape[-1],):
+        raise ValueError("weight must be [D]")
+    needs_grad = torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad
+                                              or (delta is not None and delta.requires_grad))
+    if needs_grad:
+        if not add_rmsnorm_reverse_supported(x.shape[-1]):
+            raise ValueError("the reverse pass takes rows of 256, 512, ..., 2048 channels")
+        total, normed = _AddRmsNorm.apply(x, delta, weight, eps)
+        return (x if delta is None else total), normed
+    if weight.dtype != torch.float32:
+        raise ValueError("weight must be FP32 [D]")
+    if delta is None and not add_rmsnorm_reverse_supported(x.shape[-1]):
+        raise ValueError("the norm alone takes rows of 256, 512, ..., 2048 channels")
+    return _add_rmsnorm_forward(x.contiguous(), delta.contiguous() if delta is not None else None,
+                                weight.detach().contiguous(), eps)
+
+
+class _Swiglu(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate_value):
+        gv = gate_value.contiguous()
+        ctx.save_for_backward(gv)
+        return _swiglu_forward(gv)
+
+    @staticmethod
+    def backward(ctx, dout):
+        lib = _lib.load()
+        (gv,) = ctx.saved_tensors
+        width = gv.shape[-1] // 2
+        do = dout.to(torch.bfloat16).contiguous()
+        with torch.cuda.device(gv.device):
+            dgv = torch.empty_like(gv)
+            a = _lib.SwigluArgs(gv.numel() // (2 * width), width, gv.data_ptr(), None, do.data_ptr(), dgv.data_ptr())
+            _lib.check(lib.sd_swiglu_backward(ctypes.byref(a), _stream(gv.device)))
+        return dgv
+
+
+def _swiglu_forward(gv):
     lib = _lib.load()
-    gv = gate_value.contiguous()
     width = gv.shape[-1] // 2
     with torch.cuda.device(gv.device):
         out = torch.empty(*gv.shape[:-1], width, dtype=torch.bfloat16, device=gv.device)
-        a = _lib.SwigluArgs(gv.numel() // (2 * width), width, gv.data_ptr(), out.data_ptr())
+        a = _lib.SwigluArgs(gv.numel() // (2 * width), width, gv.data_ptr(), out.data_ptr(), None, None)
         _lib.check(lib.sd_swiglu(ctypes.byref(a), _stream(gv.device)))
     return out
+
+
+def swiglu(gate_value: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * value`` for rows ``[gate | value]``: ``[..., 2 I]`` -> ``[..., I]`` BF16, with a reverse pass
+    that writes the gradient row ``[d gate | d value]`` in one kernel."""
+    _require_bf16_cuda("gate_value", gate_value)
+    if gate_value.shape[-1] % 2:
+        raise ValueError("the last axis must hold gate and value halves")
+    if torch.is_grad_enabled() and gate_value.requires_grad:
+        return _Swiglu.apply(gate_value)
+    return _swiglu_forward(gate_value.contiguous())
 
 
 class _KdaGate(torch.autograd.Function):

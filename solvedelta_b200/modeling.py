@@ -24,7 +24,7 @@ from transformers.modeling_outputs import BaseModelOutputWithPast, CausalLMOutpu
 from . import _lib
 from .config import SolveDeltaConfig
 from .ops import SolveDeltaState
-from .mixer_ops import add_rmsnorm, swiglu
+from .mixer_ops import add_rmsnorm, add_rmsnorm_reverse_supported, swiglu
 from .model import SolveDelta, SolveDeltaLayerState
 
 FP32_PARAMETERS = ("geometry_write_bias", "associative_log_rate", "associative_decay_bias")
@@ -129,9 +129,8 @@ class SolveDeltaMLP(nn.Module):
         self.down_proj = nn.Linear(intermediate_size, hidden_size, bias=False)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if (self.hidden_act == "swish" and not torch.is_grad_enabled() and x.is_cuda
-                and x.dtype == torch.bfloat16):
-            return self.down_proj(swiglu(self.gate_up_proj(x)))   # inference: activation and product in one kernel
+        if self.hidden_act == "swish" and x.is_cuda and x.dtype == torch.bfloat16:
+            return self.down_proj(swiglu(self.gate_up_proj(x)))   # activation and product in one kernel
         gate, value = self.gate_up_proj(x).chunk(2, dim=-1)
         if self.hidden_act == "swish":
             activated = F.silu(gate)
@@ -202,8 +201,11 @@ class SolveDeltaCacheAdapter(nn.Module):
 
 
 def _fp32_weight(norm: nn.Module) -> torch.Tensor:
-    """Contiguous FP32 copy of a norm's weight for the fused inference kernels, refreshed when the weight changes."""
+    """The weight the fused add + norm kernel takes: the parameter itself while gradients are recorded (so that it
+    receives one), else a contiguous FP32 copy, refreshed when the weight changes."""
     weight = norm.weight
+    if torch.is_grad_enabled() and weight.requires_grad:
+        return weight
     if weight.dtype == torch.float32 and weight.is_contiguous():
         return weight.detach()
     key = (weight.data_ptr(), weight._version)
@@ -229,8 +231,11 @@ class SolveDeltaBlock(nn.Module):
 
     @staticmethod
     def fuses(hidden_states: torch.Tensor) -> bool:
-        """Inference on BF16 CUDA activations: residual adds are folded into the norms that follow them."""
-        return not torch.is_grad_enabled() and hidden_states.is_cuda and hidden_states.dtype == torch.bfloat16
+        """BF16 CUDA activations: residual adds are folded into the norms that follow them (with gradients recorded,
+        for the row widths the reverse kernel takes)."""
+        if not (hidden_states.is_cuda and hidden_states.dtype == torch.bfloat16):
+            return False
+        return not torch.is_grad_enabled() or add_rmsnorm_reverse_supported(hidden_states.shape[-1])
 
     def forward(self, hidden_states: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
                 past_key_values: Optional[SolveDeltaCache] = None, use_cache: Optional[bool] = False,
@@ -238,8 +243,9 @@ class SolveDeltaBlock(nn.Module):
                 **kwargs):
         """``pending``: the previous block's MLP output, not yet added to ``hidden_states`` (it is added inside this
         block's first norm kernel).  ``defer_add``: return ``(residual, mlp_output, cache)`` and leave the last add
-        to the next norm.  Both are only used on the inference path (``fuses``)."""
-        if pending is not None:
+        to the next norm.  Both are only used on the fused path (``fuses``)."""
+        fused = self.fuses(hidden_states) and self.mixer_norm.weight is not None and self.mlp_norm.weight is not None
+        if pending is not None or (fused and add_rmsnorm_reverse_supported(hidden_states.shape[-1])):
             hidden_states, normed = add_rmsnorm(hidden_states, pending, _fp32_weight(self.mixer_norm),
                                                 self.mixer_norm.eps if self.mixer_norm.eps is not None else 1e-6)
             residual, hidden_states = hidden_states, normed
@@ -249,9 +255,8 @@ class SolveDeltaBlock(nn.Module):
         hidden_states, past_key_values = self.mixer(hidden_states, attention_mask=attention_mask,
                                                     past_key_values=past_key_values, use_cache=use_cache,
                                                     **kwargs)
-        if (not torch.is_grad_enabled() and hidden_states.is_cuda and hidden_states.dtype == torch.bfloat16
-                and self.mlp_norm.weight is not None):
-            # inference: the residual add and the norm that follows it in one kernel
+        if fused and hidden_states.dtype == torch.bfloat16:
+            # the residual add and the norm that follows it in one kernel
             residual, hidden_states = add_rmsnorm(residual, hidden_states, _fp32_weight(self.mlp_norm),
                                                   self.mlp_norm.eps if self.mlp_norm.eps is not None else 1e-6)
         else:
@@ -325,7 +330,7 @@ class SolveDeltaModel(SolveDeltaPreTrainedModel):
         if cu_seqlens is not None and "solvedelta_reset_mask" not in kwargs:
             kwargs["solvedelta_reset_mask"] = segment_reset_mask(hidden_states, cu_seqlens)
         collected = () if output_hidden_states else None
-        # inference: every block leaves its last residual add to the norm kernel that follows it
+        # every block leaves its last residual add to the norm kernel that follows it
         defer = SolveDeltaBlock.fuses(hidden_states) and not output_hidden_states and self.norm.weight is not None
         pending = None
         for layer in self.layers:

@@ -42,6 +42,9 @@ def test_struct_sizes_match_header():
     assert ctypes.sizeof(_lib.Conv4BackwardArgs) == 16 + 13 * 8
     assert ctypes.sizeof(_lib.KdaGateArgs) == 16 + 10 * 8
     assert ctypes.sizeof(_lib.NormGateArgs) == 16 + 10 * 8
+    assert ctypes.sizeof(_lib.AddRmsnormArgs) == 16 + 5 * 8
+    assert ctypes.sizeof(_lib.AddRmsnormBackwardArgs) == 16 + 8 * 8
+    assert ctypes.sizeof(_lib.SwigluArgs) == 16 + 4 * 8
 
 
 def test_workspace_queries_scale_with_chunks(lib):

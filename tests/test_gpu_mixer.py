@@ -446,3 +446,61 @@ def test_inference_glue_kernels_match_pytorch():
         want = torch.nn.functional.silu(g) * v
         assert out.shape == (rows, D)
         assert float((out.float() - want).abs().max()) <= 1e-2 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("rows,D,with_delta", [(37, 256, True), (64, 1024, True), (19, 768, False), (5, 2048, True)])
+def test_add_rmsnorm_reverse_matches_float64_autograd(rows, D, with_delta):
+    """Residual add + RMSNorm with its one reverse kernel: both outputs, the gradient x and delta share, and the
+    weight gradient against FP64 autograd of the same formula (the sum rounded to BF16 as the kernel stores it)."""
+    from solvedelta_b200.mixer_ops import add_rmsnorm
+
+    gen = torch.Generator().manual_seed(rows + D)
+    x = torch.randn(rows, D, generator=gen).to(torch.bfloat16)
+    d = torch.randn(rows, D, generator=gen).to(torch.bfloat16) if with_delta else None
+    w = (1.0 + 0.3 * torch.randn(D, generator=gen))
+    ds = torch.randn(rows, D, generator=gen).to(torch.bfloat16)
+    dn = torch.randn(rows, D, generator=gen).to(torch.bfloat16)
+    xg, wg = x.cuda().requires_grad_(), w.cuda().requires_grad_()
+    dg = d.cuda().requires_grad_() if with_delta else None
+    total, normed = add_rmsnorm(xg, dg, wg, 1e-6)
+    (total.float() * ds.cuda().float()).sum().backward(retain_graph=True)
+    (normed.float() * dn.cuda().float()).sum().backward()
+    # FP64 reference
+    xr, wr = x.double().requires_grad_(), w.double().requires_grad_()
+    dr = d.double().requires_grad_() if with_delta else None
+    s = xr + dr if with_delta else xr
+    s = s + (s.detach().to(torch.bfloat16).double() - s.detach())   # the stored sum, identity derivative
+    n = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-6) * wr
+    ((s * ds.double()).sum() + (n * dn.double()).sum()).backward()
+    assert torch.equal(total.detach().cpu().double(), s.detach())
+    assert max_rel(_np(normed), n.detach().numpy()) <= TOL
+    assert max_rel(_np(xg.grad), xr.grad.numpy()) <= TOL
+    if with_delta:
+        assert torch.equal(dg.grad, xg.grad)
+    assert max_rel(_np(wg.grad), wr.grad.numpy()) <= 1e-3
+
+
+def test_add_rmsnorm_reverse_refuses_other_widths():
+    from solvedelta_b200.mixer_ops import add_rmsnorm
+
+    x = torch.randn(4, 200).to(torch.bfloat16).cuda().requires_grad_()
+    with pytest.raises(ValueError):
+        add_rmsnorm(x, x.detach(), torch.ones(200, device="cuda"), 1e-6)
+
+
+@pytest.mark.parametrize("rows,I", [(33, 64), (7, 2816), (5, 100)])
+def test_swiglu_reverse_matches_float64_autograd(rows, I):
+    from solvedelta_b200.mixer_ops import swiglu
+
+    gen = torch.Generator().manual_seed(rows + I)
+    gv = (1.5 * torch.randn(rows, 2 * I, generator=gen)).to(torch.bfloat16)
+    do = torch.randn(rows, I, generator=gen).to(torch.bfloat16)
+    gg = gv.cuda().requires_grad_()
+    out = swiglu(gg)
+    (out.float() * do.cuda().float()).sum().backward()
+    gr = gv.double().requires_grad_()
+    g, v = gr.chunk(2, dim=-1)
+    want = torch.nn.functional.silu(g) * v
+    (want * do.double()).sum().backward()
+    assert max_rel(_np(out), want.detach().numpy()) <= TOL
+    assert max_rel(_np(gg.grad), gr.grad.numpy()) <= TOL
