@@ -154,6 +154,26 @@ int sd_swiglu(const sd_swiglu_args *args, void *stream);
 int sd_swiglu_backward(const sd_swiglu_args *args, void *stream);
 
 /*
+ * The gradient of the fused projection row (causallsso/model.py:321-332 slices it; autograd upstream
+ * adds one zero-filled full row per slice) written in one pass: dst[row] = [piece 0 | piece 1 | ... | zeros].
+ * Every piece is a contiguous BF16 matrix [rows][width] (NULL: zeros); widths and row_width are whole groups
+ * of eight channels and all pointers 16-byte aligned, else SD_ERR_UNSUPPORTED_SHAPE.
+ */
+#define SD_PACK_MAX_PIECES 12
+typedef struct {
+    const void *src;
+    int32_t width;
+} sd_row_piece;
+typedef struct {
+    int64_t rows;
+    int32_t pieces;
+    int32_t row_width;                 /* >= the sum of the widths; the rest of a row is zero-filled */
+    sd_row_piece piece[SD_PACK_MAX_PIECES];
+    void *dst;                         /* out BF16 [rows][row_width] */
+} sd_pack_rows_args;
+int sd_pack_rows(const sd_pack_rows_args *args, void *stream);
+
+/*
  * The whole mixer glue of a cached single-token step in the decode kernel: q, k, v come from
  * the conv4 + SiLU of the projection row against the carried window (advanced in place,
  * causallsso/model.py:146-164 at T = 1), the log decay from the decay gate

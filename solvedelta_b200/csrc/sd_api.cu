@@ -1074,6 +1074,31 @@ int sd_swiglu_backward(const sd_swiglu_args* a, void* stream_) {
     return launch_status();
 }
 
+int sd_pack_rows(const sd_pack_rows_args* a, void* stream_) {
+    if (!a || a->rows <= 0 || a->pieces <= 0 || a->pieces > SD_PACK_MAX_PIECES || a->row_width <= 0 || !a->dst)
+        return SD_ERR_INVALID_ARGUMENT;
+    PackRowsParams p{};
+    p.N = a->rows; p.pieces = a->pieces; p.row_width = a->row_width;
+    p.dst = reinterpret_cast<__nv_bfloat16*>(a->dst);
+    long long total = 0;
+    for (int k = 0; k < a->pieces; ++k) {
+        if (a->piece[k].width <= 0) return SD_ERR_INVALID_ARGUMENT;
+        // 16-byte groups: widths in whole groups of eight channels, sources on 16-byte boundaries
+        if (a->piece[k].width % 8 != 0 || (reinterpret_cast<uintptr_t>(a->piece[k].src) & 15) != 0)
+            return SD_ERR_UNSUPPORTED_SHAPE;
+        p.src[k] = reinterpret_cast<const __nv_bfloat16*>(a->piece[k].src);
+        p.width[k] = a->piece[k].width;
+        total += a->piece[k].width;
+    }
+    if (total > a->row_width) return SD_ERR_INVALID_ARGUMENT;
+    if (a->row_width % 8 != 0 || (reinterpret_cast<uintptr_t>(a->dst) & 15) != 0) return SD_ERR_UNSUPPORTED_SHAPE;
+    const unsigned gx = (unsigned)((a->row_width / 8 + 255) / 256);
+    long long gy = (148 * 8 + gx - 1) / gx;
+    if (gy > a->rows) gy = a->rows;
+    k_pack_rows<<<dim3(gx, (unsigned)gy), 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
+    return launch_status();
+}
+
 int sd_decode_step(const sd_decode_args* a, void* stream_) {
     if (!a || !shape_ok(&a->shape) || a->shape.T != 1) return SD_ERR_INVALID_ARGUMENT;
     if (!shape_supported(&a->shape)) return SD_ERR_UNSUPPORTED_SHAPE;

@@ -1029,4 +1029,50 @@ __global__ void __launch_bounds__(256) k_swiglu_bwd(SwigluParams p) {
     }
 }
 
+// ---- gradient of the fused projection row, assembled from its slices ---------------------------------
+// dst[row] = [piece 0 | piece 1 | ... | zeros]: every slice of the row (the conv's input gradient, the operator's
+// four, the small projections') is a contiguous BF16 matrix of its own; one pass writes them side by side.  A
+// thread owns one 16-byte group of the destination row and walks down the rows, four loads in flight.
+constexpr int PACK_MAX_PIECES = 12;
+struct PackRowsParams {
+    long long N;
+    int pieces, row_width;
+    const __nv_bfloat16* src[PACK_MAX_PIECES];   // null: zeros
+    int width[PACK_MAX_PIECES];
+    __nv_bfloat16* dst;
+};
+
+__global__ void __launch_bounds__(256) k_pack_rows(PackRowsParams p) {
+    const int c0 = (blockIdx.x * 256 + threadIdx.x) * 8;
+    if (c0 >= p.row_width) return;
+    const __nv_bfloat16* src = nullptr;
+    int width = 0;
+    {
+        int off = 0;
+        for (int k = 0; k < p.pieces; ++k) {
+            if (c0 >= off && c0 < off + p.width[k]) {
+                width = p.width[k];
+                src = p.src[k] != nullptr ? p.src[k] + (c0 - off) : nullptr;
+            }
+            off += p.width[k];
+        }
+    }
+    __nv_bfloat16* dst = p.dst + c0;
+    const long long step = gridDim.y;
+    long long row = blockIdx.y;
+    if (src == nullptr) {
+        for (; row < p.N; row += step) *reinterpret_cast<uint4*>(dst + row * p.row_width) = make_uint4(0u, 0u, 0u, 0u);
+        return;
+    }
+    for (; row + 3 * step < p.N; row += 4 * step) {
+        uint4 v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = *reinterpret_cast<const uint4*>(src + (row + k * step) * width);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) *reinterpret_cast<uint4*>(dst + (row + k * step) * p.row_width) = v[k];
+    }
+    for (; row < p.N; row += step)
+        *reinterpret_cast<uint4*>(dst + row * p.row_width) = *reinterpret_cast<const uint4*>(src + row * width);
+}
+
 }  // namespace sd

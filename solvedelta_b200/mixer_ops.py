@@ -343,6 +343,27 @@ def swiglu(gate_value: torch.Tensor) -> torch.Tensor:
     return _swiglu_forward(gate_value.contiguous())
 
 
+def pack_rows(pieces, widths, row_shape, device) -> Optional[torch.Tensor]:
+    """One BF16 row-shaped tensor ``[..., P]`` holding ``pieces`` side by side (``None``: zeros; columns past the
+    last piece: zeros), written by one kernel; ``None`` when the layout is not one the kernel takes (widths in whole
+    groups of eight channels, at most twelve pieces, BF16 CUDA) and the caller has to assemble the row itself."""
+    P = row_shape[-1]
+    if (device.type != "cuda" or len(widths) > _lib.PACK_MAX_PIECES or P % 8 or any(w % 8 for w in widths)
+            or any(g is not None and g.dtype != torch.bfloat16 for g in pieces)):
+        return None
+    lib = _lib.load()
+    held = [g.contiguous() if g is not None else None for g in pieces]
+    with torch.cuda.device(device):
+        out = torch.empty(row_shape, dtype=torch.bfloat16, device=device)
+        a = _lib.PackRowsArgs()
+        a.rows, a.pieces, a.row_width, a.dst = out.numel() // P, len(widths), P, out.data_ptr()
+        for k, (g, w) in enumerate(zip(held, widths)):
+            a.piece[k].src = g.data_ptr() if g is not None else None
+            a.piece[k].width = w
+        _lib.check(lib.sd_pack_rows(ctypes.byref(a), _stream(device)))
+    return out
+
+
 class _KdaGate(torch.autograd.Function):
     @staticmethod
     def forward(ctx, raw, log_rate, bias):

@@ -24,7 +24,8 @@ import torch.nn.functional as F
 from torch import nn
 
 from .config import SolveDeltaConfig
-from .mixer_ops import conv4_silu, kda_decay_gate, mixer_decode_step, rms_norm_gated, rms_norm_gated_linear
+from .mixer_ops import (conv4_silu, kda_decay_gate, mixer_decode_step, pack_rows, rms_norm_gated,
+                        rms_norm_gated_linear)
 from .ops import SolveDeltaState, solvedelta_masked_native, solvedelta_native
 
 
@@ -53,6 +54,10 @@ class _SplitRow(torch.autograd.Function):
     def backward(ctx, *grads):
         if all(g is None for g in grads):
             return None, None
+        if ctx.row_dtype == torch.bfloat16:
+            packed = pack_rows(grads, ctx.sizes, ctx.row_shape, ctx.row_device)   # one kernel for the whole row
+            if packed is not None:
+                return packed, None
         drow = torch.empty(ctx.row_shape, dtype=ctx.row_dtype, device=ctx.row_device)
         start = 0
         for size, grad in zip(ctx.sizes, grads):

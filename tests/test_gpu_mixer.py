@@ -504,3 +504,22 @@ def test_swiglu_reverse_matches_float64_autograd(rows, I):
     (want * do.double()).sum().backward()
     assert max_rel(_np(out), want.detach().numpy()) <= TOL
     assert max_rel(_np(gg.grad), gr.grad.numpy()) <= TOL
+
+
+def test_pack_rows_writes_the_slices_side_by_side():
+    from solvedelta_b200.mixer_ops import pack_rows
+
+    gen = torch.Generator().manual_seed(11)
+    widths = (48, 16, 8, 24)
+    pieces = [torch.randn(3, 37, w, generator=gen).to(torch.bfloat16).cuda() for w in widths]
+    pieces[2] = None
+    row = pack_rows(pieces, widths, (3, 37, 128), torch.device("cuda", 0))
+    want = torch.zeros(3, 37, 128, dtype=torch.bfloat16, device="cuda")
+    start = 0
+    for g, w in zip(pieces, widths):
+        if g is not None:
+            want[..., start:start + w] = g
+        start += w
+    assert torch.equal(row, want)
+    # layouts the kernel does not take are left to the caller
+    assert pack_rows([pieces[0][..., :5]], (5,), (3, 37, 8), torch.device("cuda", 0)) is None
