@@ -1015,7 +1015,8 @@ int sd_add_rmsnorm(const sd_add_rmsnorm_args* a, void* stream_) {
     p.w = a->weight;
     p.sum = reinterpret_cast<__nv_bfloat16*>(a->sum);
     p.normed = reinterpret_cast<__nv_bfloat16*>(a->normed);
-    if (addnorm_rows_ok(a->D)) {
+    // few rows (single-token steps): a whole CTA per row finishes sooner than one warp per row
+    if (addnorm_rows_ok(a->D) && (a->rows >= 1024 || !a->delta)) {
         dispatch_addnorm_rows(p, false, stream);
     } else {
         if (!a->delta) return SD_ERR_UNSUPPORTED_SHAPE;   // the norm alone is only built for the row kernels

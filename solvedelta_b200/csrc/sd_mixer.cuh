@@ -32,9 +32,10 @@ struct ConvParams {
     const unsigned char* reset;
 };
 
-__device__ __forceinline__ float silu_f(float z) { return z / (1.f + __expf(-z)); }
+// the fast reciprocal (2 ulp) instead of an IEEE division: these kernels are bound by instruction issue
+__device__ __forceinline__ float silu_f(float z) { return __fdividef(z, 1.f + __expf(-z)); }
 __device__ __forceinline__ float silu_grad_f(float z) {
-    const float s = 1.f / (1.f + __expf(-z));
+    const float s = __fdividef(1.f, 1.f + __expf(-z));
     return s * (1.f + z * (1.f - s));
 }
 
@@ -112,6 +113,7 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv4_silu_fwd(ConvParams p) {
         };
 #pragma unroll
         for (int k = 0; k < CONV_RING; ++k) issue(t0 + k);
+#pragma unroll 8
         for (int t = t0; t < t1; ++t) {
             asm volatile("cp.async.wait_group %0;" ::"n"(CONV_RING - 1));
             const float2 x3 = conv_ring_pair(ring[(t - t0) % CONV_RING][threadIdx.x]);
@@ -185,6 +187,7 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv4_silu_bwd(ConvParams p) {
         };
 #pragma unroll
         for (int k = 0; k < CONV_RING; ++k) issue(t0 + k);
+#pragma unroll 4
         for (int t = t0; t < t_end + 3; ++t) {
             asm volatile("cp.async.wait_group %0;" ::"n"(CONV_RING - 1));
             float2 x3 = make_float2(0.f, 0.f), gy = x3;
