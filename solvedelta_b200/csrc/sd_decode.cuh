@@ -186,7 +186,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(DecodeParams p, 
             const float raw = mix.decay_w != nullptr ? decay_raw_mix
                                                      : __bfloat162float(mix.decay_raw[(long long)b * mix.decay_sb + hc]);
             const float z = raw + mix.decay_bias[hc];
-            ld = -__expf(mix.log_rate[hh]) * softplus_f(z);
+            ld = -__expf(mix.log_rate[hh]) * softplus_fast(z);
         }
         if (tid < V) v_mix = decode_conv_channel(mix, b, D, 2 * H * r + hh * V + tid);
         const float graw = __bfloat162float(mix.geom_raw[(long long)b * mix.geom_sb + hh]) + mix.geom_bias[hh];
