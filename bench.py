@@ -368,59 +368,107 @@ def summarize_ncu(csv_path, tasks):
         print(f"{name} {total / tasks / KIB:.1f} {m.get('gpu__time_duration.sum', 0.0) / 1e3:.1f}")
 
 
-def time_mixer_glue(B, T, H, r, V, device, reps=10):
-    """Device time of the mixer glue kernels around the operator at the workload's shape
-    (conv over the q|k|v slice of a projection row, decay gate, gated RMSNorm), forward and
-    reverse, with the HBM bandwidth their one-pass algorithmic bytes amount to.  Every
-    operand is larger than the 126 MB L2."""
+def time_mixer_glue(B, T, H, r, V, device, reps=20):
+    """Device time of the glue kernels around the operator at the workload's shape (conv over the q|k|v slice of
+    a projection row, decay gate, gated RMSNorm; residual add + RMSNorm and SwiGLU of the block at hidden 1024 /
+    intermediate 2816), forward and reverse, called through the C ABI on preallocated buffers like the main leg,
+    with the HBM bandwidth their one-pass algorithmic bytes amount to.  Every operand set is larger than the
+    126 MB L2 except the block glue's (B*T rows of 1024), which is stated in `shape`."""
     import torch
 
-    from solvedelta_b200 import conv4_silu, kda_decay_gate, rms_norm_gated
+    from solvedelta_b200 import _lib
 
+    lib = _lib.load()
     peak, _ = _peaks()
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
     gen = torch.Generator(device="cpu").manual_seed(3)
-    D = 2 * H * r + H * V
-    row = torch.randn(B, T, D + 64, generator=gen).to(torch.bfloat16).to(device)
-    x = row[..., :D].requires_grad_()
-    w = (0.5 * torch.randn(D, 4, generator=gen)).to(device).requires_grad_()
-    raw = torch.randn(B, T, H, r, generator=gen).to(torch.bfloat16).to(device).requires_grad_()
-    A = torch.zeros(H, device=device).requires_grad_()
-    bias = torch.zeros(H, r, device=device).requires_grad_()
-    o = torch.randn(B, T, H, V, generator=gen).to(torch.bfloat16).to(device).requires_grad_()
-    gate = torch.randn(B, T, H, V, generator=gen).to(torch.bfloat16).to(device).requires_grad_()
-    nw = torch.ones(V, device=device).requires_grad_()
-    n_conv, n_gate, n_norm = B * T * D, B * T * H * r, B * T * H * V
-    cases = {
-        "conv4_silu": (lambda: conv4_silu(x, w)[0], (x, w), 2 * n_conv * 2, 3 * n_conv * 2),
-        "kda_decay_gate": (lambda: kda_decay_gate(raw, A, bias), (raw, A, bias), n_gate * (2 + 4), n_gate * (2 + 4 + 2)),
-        "rms_norm_gated": (lambda: rms_norm_gated(o, gate, nw, 1e-6), (o, gate, nw), 3 * n_norm * 2, 5 * n_norm * 2),
-    }
-    out = {}
+
+    def bf16(*shape):
+        return torch.randn(*shape, generator=gen).to(torch.bfloat16).to(device)
+
+    def scratch(nbytes):
+        return torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=device)
+
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    for name, (fn, leaves, fwd_bytes, bwd_bytes) in cases.items():
-        y = fn()
-        dy = torch.randn_like(y)
+
+    def timed(fn, args):
         for _ in range(3):
-            torch.autograd.grad(fn(), leaves, dy)
+            _lib.check(fn(ctypes.byref(args), stream))
         torch.cuda.synchronize()
         e0.record()
         for _ in range(reps):
-            y = fn()
+            _lib.check(fn(ctypes.byref(args), stream))
         e1.record()
         torch.cuda.synchronize()
-        fwd_ms = e0.elapsed_time(e1) / reps
-        e0.record()
-        for _ in range(reps):
-            torch.autograd.grad(fn(), leaves, dy)
-        e1.record()
-        torch.cuda.synchronize()
-        both_ms = e0.elapsed_time(e1) / reps
-        bwd_ms = max(both_ms - fwd_ms, 1e-6)
-        out[name] = {"fwd_ms": round(fwd_ms, 4), "bwd_ms": round(bwd_ms, 4),
-                     "fwd_gbs": round(fwd_bytes / fwd_ms / 1e6, 1), "bwd_gbs": round(bwd_bytes / bwd_ms / 1e6, 1),
-                     "fwd_frac": round(fwd_bytes / fwd_ms / 1e6 / peak, 3),
-                     "bwd_frac": round(bwd_bytes / bwd_ms / 1e6 / peak, 3)}
-    out["shape"] = f"B={B}, T={T}, conv channels {D}, gate/norm rows {B * T * H} x {r}; timed through the autograd wrappers"
+        return e0.elapsed_time(e1) / reps
+
+    def entry(fwd_ms, bwd_ms, fwd_bytes, bwd_bytes):
+        return {"fwd_ms": round(fwd_ms, 4), "bwd_ms": round(bwd_ms, 4),
+                "fwd_gbs": round(fwd_bytes / fwd_ms / 1e6, 1), "bwd_gbs": round(bwd_bytes / bwd_ms / 1e6, 1),
+                "fwd_frac": round(fwd_bytes / fwd_ms / 1e6 / peak, 3),
+                "bwd_frac": round(bwd_bytes / bwd_ms / 1e6 / peak, 3)}
+
+    out = {}
+    rows = B * T * H
+    # conv4 + SiLU on the first D columns of a wider row (the projection row's layout)
+    D = 2 * H * r + H * V
+    row = bf16(B, T, D + 64)
+    x = row[..., :D]
+    w = (0.5 * torch.randn(D, 4, generator=gen)).to(device)
+    y, dy, dx = torch.empty(B, T, D, dtype=torch.bfloat16, device=device), bf16(B, T, D), torch.empty(
+        B, T, D, dtype=torch.bfloat16, device=device)
+    dw = torch.empty(D, 4, device=device)
+    sc = scratch(lib.sd_conv4_backward_scratch_bytes(B, T, D))
+    f = _lib.Conv4ForwardArgs(B, T, D, x.data_ptr(), x.stride(0), x.stride(1), w.data_ptr(), None, y.data_ptr(), None,
+                              None, None)
+    g = _lib.Conv4BackwardArgs(B, T, D, x.data_ptr(), x.stride(0), x.stride(1), w.data_ptr(), None, dy.data_ptr(),
+                               dx.data_ptr(), dw.data_ptr(), None, sc.data_ptr(), sc.numel(), None, None)
+    n = B * T * D
+    out["conv4_silu"] = entry(timed(lib.sd_conv4_silu_forward, f), timed(lib.sd_conv4_silu_backward, g), 4 * n, 6 * n)
+    del row, x, y, dy, dx
+    # decay gate
+    raw, A, bias = bf16(rows, r), torch.zeros(H, device=device), torch.zeros(H, r, device=device)
+    ld, dld, draw = torch.empty(rows, r, device=device), torch.randn(rows, r, generator=gen).to(device), torch.empty(
+        rows, r, dtype=torch.bfloat16, device=device)
+    dA, db = torch.empty(H, device=device), torch.empty(H, r, device=device)
+    sc = scratch(lib.sd_kda_gate_backward_scratch_bytes(B * T, H, r))
+    f = _lib.KdaGateArgs(B * T, H, r, raw.data_ptr(), A.data_ptr(), bias.data_ptr(), ld.data_ptr())
+    g = _lib.KdaGateArgs(B * T, H, r, raw.data_ptr(), A.data_ptr(), bias.data_ptr(), None, dld.data_ptr(),
+                         draw.data_ptr(), dA.data_ptr(), db.data_ptr(), sc.data_ptr(), sc.numel())
+    n = rows * r
+    out["kda_decay_gate"] = entry(timed(lib.sd_kda_gate_forward, f), timed(lib.sd_kda_gate_backward, g), 6 * n, 8 * n)
+    del raw, ld, dld, draw
+    # gated RMSNorm
+    o, gate, dyn = bf16(rows, V), bf16(rows, V), bf16(rows, V)
+    nw, yn = torch.ones(V, device=device), torch.empty(rows, V, dtype=torch.bfloat16, device=device)
+    dxn, dgn, dwn = torch.empty_like(yn), torch.empty_like(yn), torch.empty(V, device=device)
+    sc = scratch(lib.sd_norm_gate_backward_scratch_bytes(rows, V))
+    f = _lib.NormGateArgs(rows, V, 1e-6, o.data_ptr(), gate.data_ptr(), nw.data_ptr(), yn.data_ptr())
+    g = _lib.NormGateArgs(rows, V, 1e-6, o.data_ptr(), gate.data_ptr(), nw.data_ptr(), None, dyn.data_ptr(),
+                          dxn.data_ptr(), dgn.data_ptr(), dwn.data_ptr(), sc.data_ptr(), sc.numel())
+    n = rows * V
+    out["rms_norm_gated"] = entry(timed(lib.sd_norm_gate_forward, f), timed(lib.sd_norm_gate_backward, g), 6 * n, 10 * n)
+    del o, gate, dyn, yn, dxn, dgn
+    # the block's residual add + RMSNorm and SwiGLU (hidden 1024, intermediate 2816 of the 24-layer model)
+    hidden, inter, tokens = 1024, 2816, B * T
+    xh, dh, hw = bf16(tokens, hidden), bf16(tokens, hidden), torch.ones(hidden, device=device)
+    sh, nh = torch.empty_like(xh), torch.empty_like(xh)
+    dsh, dnh, dxh, dwh = bf16(tokens, hidden), bf16(tokens, hidden), torch.empty_like(xh), torch.empty(hidden, device=device)
+    sc = scratch(lib.sd_add_rmsnorm_backward_scratch_bytes(tokens, hidden))
+    f = _lib.AddRmsnormArgs(tokens, hidden, 1e-6, xh.data_ptr(), dh.data_ptr(), hw.data_ptr(), sh.data_ptr(), nh.data_ptr())
+    g = _lib.AddRmsnormBackwardArgs(tokens, hidden, 1e-6, sh.data_ptr(), hw.data_ptr(), dsh.data_ptr(), dnh.data_ptr(),
+                                    dxh.data_ptr(), dwh.data_ptr(), sc.data_ptr(), sc.numel())
+    n = tokens * hidden
+    out["add_rmsnorm"] = entry(timed(lib.sd_add_rmsnorm, f), timed(lib.sd_add_rmsnorm_backward, g), 8 * n, 8 * n)
+    del xh, dh, sh, nh, dsh, dnh, dxh
+    gv, so, dso = bf16(tokens, 2 * inter), torch.empty(tokens, inter, dtype=torch.bfloat16, device=device), bf16(tokens, inter)
+    dgv = torch.empty_like(gv)
+    f = _lib.SwigluArgs(tokens, inter, gv.data_ptr(), so.data_ptr(), None, None)
+    g = _lib.SwigluArgs(tokens, inter, gv.data_ptr(), None, dso.data_ptr(), dgv.data_ptr())
+    n = tokens * inter
+    out["swiglu"] = entry(timed(lib.sd_swiglu, f), timed(lib.sd_swiglu_backward, g), 6 * n, 10 * n)
+    out["shape"] = (f"B={B}, T={T}: conv channels {D}; gate/norm rows {rows} x {r}; add+norm {tokens} x {hidden} "
+                    f"(0.27 GB per pass, above L2); SwiGLU {tokens} x {inter}; through the C ABI on preallocated buffers")
     return out
 
 
