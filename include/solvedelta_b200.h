@@ -174,6 +174,27 @@ typedef struct {
 int sd_pack_rows(const sd_pack_rows_args *args, void *stream);
 
 /*
+ * Cross entropy over BF16 logits, the owner behind fuse_cross_entropy upstream
+ * (FusedCrossEntropyLoss, causallsso/modeling_solvedelta.py:469-470).  Forward: per row the log-sum-exp
+ * and -log softmax(label), 0 for rows whose label is ignore_index.  Backward: d logits =
+ * (softmax - onehot(label)) * coef, coef a device scalar (upstream gradient / token count); zeros for
+ * ignored rows.  The mean over the counted rows is the caller's (a sum of `rows` floats).
+ */
+typedef struct {
+    int64_t rows;
+    int32_t V;
+    const void *logits;                /* BF16 [rows][V] */
+    const int64_t *labels;             /* [rows] */
+    int64_t ignore_index;
+    float *lse;                        /* [rows]: out of forward, in of backward */
+    float *row_loss;                   /* forward: out [rows] */
+    const float *coef;                 /* backward: device scalar */
+    void *dlogits;                     /* backward: out BF16 [rows][V] */
+} sd_cross_entropy_args;
+int sd_cross_entropy_forward(const sd_cross_entropy_args *args, void *stream);
+int sd_cross_entropy_backward(const sd_cross_entropy_args *args, void *stream);
+
+/*
  * The whole mixer glue of a cached single-token step in the decode kernel: q, k, v come from
  * the conv4 + SiLU of the projection row against the carried window (advanced in place,
  * causallsso/model.py:146-164 at T = 1), the log decay from the decay gate

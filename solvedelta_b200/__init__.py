@@ -14,7 +14,7 @@ from .modeling import (GraphedDecoder, SolveDeltaBlock, SolveDeltaCache, SolveDe
                        SolveDeltaMLP, SolveDeltaModel, SolveDeltaPreTrainedModel)
 from .training import (BF16ShadowWeights, BucketedGradientAverager, SolveDeltaGraphedTrainingStep,
                        allreduce_gradients, causal_lm_loss,
-                       fixed_dense_linear_cross_entropy)
+                       fixed_dense_linear_cross_entropy, fused_cross_entropy)
 from .packing import PackedSegments, build_packed_segments, pack_tokens, unpack_tokens
 from .ops import (
     SolveDeltaState,
@@ -41,6 +41,7 @@ __all__ = [
     "allreduce_gradients",
     "causal_lm_loss",
     "fixed_dense_linear_cross_entropy",
+    "fused_cross_entropy",
     "GraphedDecoder",
     "SolveDeltaBlock",
     "SolveDeltaCache",

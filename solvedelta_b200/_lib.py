@@ -138,6 +138,12 @@ class PackRowsArgs(ctypes.Structure):
                 ("piece", RowPiece * PACK_MAX_PIECES), ("dst", ctypes.c_void_p)]
 
 
+class CrossEntropyArgs(ctypes.Structure):
+    _fields_ = [("rows", ctypes.c_int64), ("V", ctypes.c_int32), ("logits", ctypes.c_void_p),
+                ("labels", ctypes.c_void_p), ("ignore_index", ctypes.c_int64), ("lse", ctypes.c_void_p),
+                ("row_loss", ctypes.c_void_p), ("coef", ctypes.c_void_p), ("dlogits", ctypes.c_void_p)]
+
+
 class MixerDecodeArgs(ctypes.Structure):
     _fields_ = ([("shape", Shape)] + [(n, Operand) for n in ("u", "h", "erase_raw", "write_raw")] + [
         ("qkv", ctypes.c_void_p), ("qkv_stride_b", ctypes.c_int64), ("conv_weight", ctypes.c_void_p),
@@ -217,6 +223,7 @@ EXPORTS = (
     "sd_chunk_tokens", "sd_forward_static", "sd_panel_kind", "sd_device_fault", "sd_device_fault_clear",
     "sd_predictor_forward", "sd_predictor_backward", "sd_mixer_decode_step", "sd_add_rmsnorm", "sd_swiglu",
     "sd_add_rmsnorm_backward_scratch_bytes", "sd_add_rmsnorm_backward", "sd_swiglu_backward", "sd_pack_rows",
+    "sd_cross_entropy_forward", "sd_cross_entropy_backward",
     "sd_conv4_backward_scratch_bytes", "sd_conv4_silu_forward", "sd_conv4_silu_backward",
     "sd_kda_gate_backward_scratch_bytes", "sd_kda_gate_forward", "sd_kda_gate_backward",
     "sd_norm_gate_backward_scratch_bytes", "sd_norm_gate_forward", "sd_norm_gate_backward",
@@ -290,6 +297,7 @@ def _declare(lib: ctypes.CDLL) -> ctypes.CDLL:
                          ("sd_mixer_decode_step", MixerDecodeArgs), ("sd_add_rmsnorm", AddRmsnormArgs),
                          ("sd_swiglu", SwigluArgs), ("sd_swiglu_backward", SwigluArgs),
                          ("sd_add_rmsnorm_backward", AddRmsnormBackwardArgs), ("sd_pack_rows", PackRowsArgs),
+                         ("sd_cross_entropy_forward", CrossEntropyArgs), ("sd_cross_entropy_backward", CrossEntropyArgs),
                          ("sd_conv4_silu_forward", Conv4ForwardArgs), ("sd_conv4_silu_backward", Conv4BackwardArgs),
                          ("sd_kda_gate_forward", KdaGateArgs), ("sd_kda_gate_backward", KdaGateArgs),
                          ("sd_norm_gate_forward", NormGateArgs), ("sd_norm_gate_backward", NormGateArgs)):

@@ -89,9 +89,11 @@ class SolveDeltaConfig(PreTrainedConfig):
     bos_token_id: Optional[int] = 1
     eos_token_id: Optional[int] = 2
     tie_word_embeddings: bool = False
-    # implementation switches of upstream (config.py:34-37): the first three choose between owners of the same
-    # arithmetic there and change nothing here; fuse_linear_cross_entropy makes the causal LM compute its loss
-    # through the chunked linear + cross-entropy head and return no logits, as upstream does
+    # implementation switches of upstream (config.py:34-37): the first two choose between owners of the same
+    # arithmetic there and change nothing here (the fused kernels are used whenever the layout allows);
+    # fuse_cross_entropy takes the loss from the two cross-entropy kernels on the BF16 logits instead of
+    # F.cross_entropy on an FP32 copy; fuse_linear_cross_entropy makes the causal LM compute its loss through the
+    # chunked linear + cross-entropy head and return no logits, as upstream does
     fuse_norm: bool = True
     fuse_swiglu: bool = True
     fuse_cross_entropy: bool = True

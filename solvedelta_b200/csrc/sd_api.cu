@@ -1075,6 +1075,32 @@ int sd_swiglu_backward(const sd_swiglu_args* a, void* stream_) {
     return launch_status();
 }
 
+int sd_cross_entropy_forward(const sd_cross_entropy_args* a, void* stream_) {
+    if (!a || a->rows <= 0 || a->V <= 0 || !a->logits || !a->labels || !a->lse || !a->row_loss) return SD_ERR_INVALID_ARGUMENT;
+    if (a->rows > 0x7fffffffLL) return SD_ERR_UNSUPPORTED_SHAPE;
+    CrossEntropyParams p{};
+    p.N = a->rows; p.V = a->V; p.ignore_index = a->ignore_index;
+    p.logits = reinterpret_cast<const __nv_bfloat16*>(a->logits);
+    p.labels = reinterpret_cast<const long long*>(a->labels);
+    p.lse = a->lse; p.row_loss = a->row_loss;
+    k_cross_entropy_fwd<<<(unsigned)a->rows, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
+    return launch_status();
+}
+
+int sd_cross_entropy_backward(const sd_cross_entropy_args* a, void* stream_) {
+    if (!a || a->rows <= 0 || a->V <= 0 || !a->logits || !a->labels || !a->lse || !a->coef || !a->dlogits)
+        return SD_ERR_INVALID_ARGUMENT;
+    if (a->rows > 0x7fffffffLL) return SD_ERR_UNSUPPORTED_SHAPE;
+    CrossEntropyParams p{};
+    p.N = a->rows; p.V = a->V; p.ignore_index = a->ignore_index;
+    p.logits = reinterpret_cast<const __nv_bfloat16*>(a->logits);
+    p.labels = reinterpret_cast<const long long*>(a->labels);
+    p.lse = a->lse; p.coef = a->coef;
+    p.dlogits = reinterpret_cast<__nv_bfloat16*>(a->dlogits);
+    k_cross_entropy_bwd<<<(unsigned)a->rows, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
+    return launch_status();
+}
+
 int sd_pack_rows(const sd_pack_rows_args* a, void* stream_) {
     if (!a || a->rows <= 0 || a->pieces <= 0 || a->pieces > SD_PACK_MAX_PIECES || a->row_width <= 0 || !a->dst)
         return SD_ERR_INVALID_ARGUMENT;

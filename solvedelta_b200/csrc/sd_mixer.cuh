@@ -1084,4 +1084,83 @@ __global__ void __launch_bounds__(256) k_pack_rows(PackRowsParams p) {
         *reinterpret_cast<uint4*>(dst + row * p.row_width) = *reinterpret_cast<const uint4*>(src + row * width);
 }
 
+// ---- cross entropy over BF16 logits (the FusedCrossEntropyLoss owner upstream calls, -------------------
+// causallsso/modeling_solvedelta.py:469-470) ------------------------------------------------------------
+// Forward: per row the log-sum-exp (kept for the reverse pass) and -log softmax(label) (0 for an ignored row), one
+// read of the row.  Reverse: d logits = (softmax - onehot(label)) * coef with coef a device scalar (upstream
+// gradient / token count), zeros for ignored rows.  One CTA per row; a thread takes 16-byte groups of the row.
+struct CrossEntropyParams {
+    long long N;
+    int V;
+    const __nv_bfloat16* logits;
+    const long long* labels;
+    long long ignore_index;
+    float* lse;        // [N]
+    float* row_loss;   // [N]
+    const float* coef; // reverse: device scalar
+    __nv_bfloat16* dlogits;
+};
+
+__device__ __forceinline__ float ce_block_reduce(float v, bool take_max, float* red) {
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+        const float o = __shfl_xor_sync(0xffffffffu, v, m);
+        v = take_max ? fmaxf(v, o) : v + o;
+    }
+    __syncthreads();   // red is reused between calls
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) t = take_max ? fmaxf(t, red[w]) : t + red[w];
+    return t;
+}
+
+__global__ void __launch_bounds__(256) k_cross_entropy_fwd(CrossEntropyParams p) {
+    __shared__ float red[8];
+    const long long row = blockIdx.x;
+    const __nv_bfloat16* x = p.logits + row * p.V;
+    const long long label = p.labels[row];
+    // running maximum and sum of exp(x - maximum) per thread, merged at the end
+    float mx = -INFINITY, sum = 0.f;
+    for (int c0 = threadIdx.x * 8; c0 < p.V; c0 += 256 * 8) {
+        float v[8];
+        norm_load8(x, c0, p.V, true, v);
+        float gm = mx;
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            if (c0 + e < p.V) gm = fmaxf(gm, v[e]);
+        float add = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            if (c0 + e < p.V) add += __expf(v[e] - gm);
+        sum = sum * __expf(mx - gm) + add;   // exp(-inf - finite) = 0 on the first group
+        mx = gm;
+    }
+    const float top = ce_block_reduce(mx, true, red);
+    const float total = ce_block_reduce(mx == -INFINITY ? 0.f : sum * __expf(mx - top), false, red);
+    if (threadIdx.x == 0) {
+        const float lse = top + __logf(total);
+        p.lse[row] = lse;
+        const bool live = label != p.ignore_index && label >= 0 && label < p.V;
+        p.row_loss[row] = live ? lse - __bfloat162float(x[label]) : 0.f;
+    }
+}
+
+__global__ void __launch_bounds__(256) k_cross_entropy_bwd(CrossEntropyParams p) {
+    const long long row = blockIdx.x;
+    const __nv_bfloat16* x = p.logits + row * p.V;
+    __nv_bfloat16* d = p.dlogits + row * p.V;
+    const long long label = p.labels[row];
+    const bool live = label != p.ignore_index && label >= 0 && label < p.V;
+    const float coef = live ? *p.coef : 0.f, lse = p.lse[row];
+    for (int c0 = threadIdx.x * 8; c0 < p.V; c0 += 256 * 8) {
+        float v[8], g[8];
+        norm_load8(x, c0, p.V, true, v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) g[e] = live ? (__expf(v[e] - lse) - (c0 + e == label ? 1.f : 0.f)) * coef : 0.f;
+        norm_store8(d, c0, p.V, true, g);
+    }
+}
+
 }  // namespace sd

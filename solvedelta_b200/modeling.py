@@ -424,6 +424,10 @@ class SolveDeltaForCausalLM(SolveDeltaPreTrainedModel, GenerationMixin):
                 loss = fixed_dense_linear_cross_entropy(hidden_states, shifted, self.lm_head.weight,
                                                         self.lm_head.bias, ignore_index=self.ignore_index,
                                                         total=count)
+            elif self.config.fuse_cross_entropy and logits.is_cuda and logits.dtype == torch.bfloat16:
+                from .training import fused_cross_entropy   # two kernels on the BF16 logits, no FP32 copy
+
+                loss = fused_cross_entropy(logits, shifted, ignore_index=self.ignore_index)
             else:
                 loss = F.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), shifted.reshape(-1),
                                        ignore_index=self.ignore_index)

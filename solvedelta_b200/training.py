@@ -13,6 +13,7 @@ masters live beside them, and forward and backward are captured as one graph.
 """
 from __future__ import annotations
 
+import ctypes
 from contextlib import contextmanager
 from typing import Any, Iterable, List, Optional
 
@@ -100,6 +101,58 @@ def fixed_dense_linear_cross_entropy(x: torch.Tensor, target: torch.Tensor, weig
     if weight.ndim != 2 or weight.shape[1] != x.shape[-1]:
         raise ValueError("weight must have shape [vocab, hidden]")
     return _FixedDenseLinearCrossEntropy.apply(x, target, weight, bias, ignore_index, total, num_chunks)
+
+
+class _FusedCrossEntropy(torch.autograd.Function):
+    """Mean cross entropy over BF16 logits in two kernels: the forward reads every row once (log-sum-exp and the
+    label's term), the reverse writes d logits = (softmax - onehot) * cotangent / count in BF16.  The FP32 copy of the
+    [tokens, vocab] logits that ``F.cross_entropy(logits.float(), ...)`` makes never exists."""
+
+    @staticmethod
+    def forward(ctx, logits, labels, ignore_index, count):
+        lib = _lib.load()
+        rows, vocab = logits.shape
+        with torch.cuda.device(logits.device):
+            lse = torch.empty(rows, dtype=torch.float32, device=logits.device)
+            row_loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+            a = _lib.CrossEntropyArgs(rows, vocab, logits.data_ptr(), labels.data_ptr(), int(ignore_index),
+                                      lse.data_ptr(), row_loss.data_ptr(), None, None)
+            stream = ctypes.c_void_p(torch.cuda.current_stream(logits.device).cuda_stream)
+            _lib.check(lib.sd_cross_entropy_forward(ctypes.byref(a), stream))
+        ctx.save_for_backward(logits, labels, lse, count)
+        ctx.ignore_index = int(ignore_index)
+        return row_loss.sum() / count
+
+    @staticmethod
+    def backward(ctx, gout):
+        lib = _lib.load()
+        logits, labels, lse, count = ctx.saved_tensors
+        rows, vocab = logits.shape
+        with torch.cuda.device(logits.device):
+            coef = (gout.float() / count).reshape(1).contiguous()
+            dlogits = torch.empty_like(logits)
+            a = _lib.CrossEntropyArgs(rows, vocab, logits.data_ptr(), labels.data_ptr(), ctx.ignore_index,
+                                      lse.data_ptr(), None, coef.data_ptr(), dlogits.data_ptr())
+            stream = ctypes.c_void_p(torch.cuda.current_stream(logits.device).cuda_stream)
+            _lib.check(lib.sd_cross_entropy_backward(ctypes.byref(a), stream))
+        return dlogits, None, None, None
+
+
+def fused_cross_entropy(logits: torch.Tensor, labels: torch.Tensor, *, ignore_index: int = -100) -> torch.Tensor:
+    """``F.cross_entropy(logits.float(), labels, ignore_index=...)`` (mean over the counted tokens) for BF16 CUDA
+    logits ``[..., V]`` and ``torch.long`` labels ``[...]``, the role of upstream's ``FusedCrossEntropyLoss``
+    (``modeling_solvedelta.py:469-470``).  The token count is taken on the device (no host synchronisation); with no
+    counted token the loss is 0 where PyTorch returns NaN."""
+    if logits.device.type != "cuda" or logits.dtype != torch.bfloat16:
+        raise TypeError("logits must be a BF16 CUDA tensor")
+    if labels.dtype != torch.long:
+        raise TypeError("labels must be torch.long")
+    if labels.shape != logits.shape[:-1]:
+        raise ValueError("labels must have the shape of logits without its last axis")
+    flat = logits.reshape(-1, logits.shape[-1]).contiguous()
+    target = labels.reshape(-1).to(logits.device).contiguous()
+    count = (target != ignore_index).sum().clamp_min(1).to(torch.float32)
+    return _FusedCrossEntropy.apply(flat, target, ignore_index, count)
 
 
 class BF16ShadowWeights:
@@ -403,4 +456,4 @@ class SolveDeltaGraphedTrainingStep:
 
 __all__ = ["BF16ShadowWeights", "BucketedGradientAverager", "SolveDeltaGraphedTrainingStep", "allreduce_gradients",
            "causal_lm_loss",
-           "fixed_dense_linear_cross_entropy"]
+           "fixed_dense_linear_cross_entropy", "fused_cross_entropy"]

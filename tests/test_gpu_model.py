@@ -401,3 +401,29 @@ def test_fused_single_token_step_equals_the_separate_kernels(medium, monkeypatch
             assert float((x - y).abs().max()) <= 2e-2 * float(y.abs().max())
         assert float((a["conv_state"].float() - b["conv_state"].float()).abs().max()) <= \
             3e-2 * float(b["conv_state"].float().abs().max())
+
+
+@pytest.mark.parametrize("rows,vocab", [(37, 1003), (64, 32000), (5, 8)])
+def test_fused_cross_entropy_matches_pytorch_on_float32_logits(rows, vocab):
+    from solvedelta_b200 import fused_cross_entropy
+
+    gen = torch.Generator().manual_seed(rows + vocab)
+    logits = (3.0 * torch.randn(rows, vocab, generator=gen)).to(torch.bfloat16).cuda()
+    labels = torch.randint(0, vocab, (rows,), generator=gen).cuda()
+    labels[::5] = -100
+    got_in = logits.clone().requires_grad_()
+    got = fused_cross_entropy(got_in, labels, ignore_index=-100)
+    (2.0 * got).backward()
+    want_in = logits.float().requires_grad_()
+    want = torch.nn.functional.cross_entropy(want_in, labels, ignore_index=-100)
+    (2.0 * want).backward()
+    assert abs(got.item() - want.item()) <= 2e-4 * max(1.0, abs(want.item()))
+    assert got_in.grad.dtype == torch.bfloat16
+    err = (got_in.grad.float() - want_in.grad).abs().max().item()
+    assert err <= 1e-2 * want_in.grad.abs().max().item()
+    assert not got_in.grad[::5].any()
+    # no counted token: zero loss and zero gradient
+    none = fused_cross_entropy(logits.clone().requires_grad_(), torch.full_like(labels, -100))
+    assert none.item() == 0.0
+    with pytest.raises(TypeError):
+        fused_cross_entropy(logits, labels.int())
