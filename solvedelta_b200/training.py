@@ -24,6 +24,33 @@ from torch import nn
 from . import _lib
 
 
+def _ce_rows(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int):
+    """Per row of BF16 CUDA logits ``[N, V]``: log-sum-exp and -log softmax(label) (0 where ignored), one kernel."""
+    lib = _lib.load()
+    rows, vocab = logits.shape
+    with torch.cuda.device(logits.device):
+        lse = torch.empty(rows, dtype=torch.float32, device=logits.device)
+        row_loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+        a = _lib.CrossEntropyArgs(rows, vocab, logits.data_ptr(), labels.data_ptr(), int(ignore_index),
+                                  lse.data_ptr(), row_loss.data_ptr(), None, None)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(logits.device).cuda_stream)
+        _lib.check(lib.sd_cross_entropy_forward(ctypes.byref(a), stream))
+    return lse, row_loss
+
+
+def _ce_grad(logits: torch.Tensor, labels: torch.Tensor, lse: torch.Tensor, coef: torch.Tensor, ignore_index: int):
+    """d logits = (softmax - onehot(label)) * coef in BF16 (zeros where ignored); ``coef`` an FP32 device scalar."""
+    lib = _lib.load()
+    rows, vocab = logits.shape
+    with torch.cuda.device(logits.device):
+        dlogits = torch.empty_like(logits)
+        a = _lib.CrossEntropyArgs(rows, vocab, logits.data_ptr(), labels.data_ptr(), int(ignore_index),
+                                  lse.data_ptr(), None, coef.data_ptr(), dlogits.data_ptr())
+        stream = ctypes.c_void_p(torch.cuda.current_stream(logits.device).cuda_stream)
+        _lib.check(lib.sd_cross_entropy_backward(ctypes.byref(a), stream))
+    return dlogits
+
+
 class _FixedDenseLinearCrossEntropy(torch.autograd.Function):
     """loss = sum over valid tokens of CE(x W^T + b, target) / total, evaluated in token
     chunks so that the [tokens, vocab] logits never exist at once.  The gradients with
@@ -44,8 +71,25 @@ class _FixedDenseLinearCrossEntropy(torch.autograd.Function):
         step = -(-tokens // max(1, num_chunks))
         # a tensor denominator (the count of valid labels, taken on the device) stays on the device: no host sync
         scale = (1.0 / total.to(torch.float32)) if torch.is_tensor(total) else 1.0 / float(total)
+        on_kernels = x2.is_cuda and x2.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and t.dtype == torch.long
+        if on_kernels:   # the loss kernels work on the BF16 logits of a chunk as the projection leaves them
+            coef = (scale if torch.is_tensor(scale) else torch.full((), scale, device=x.device)).reshape(1).float()
         for lo in range(0, tokens, step):
             xs, ts = x2[lo:lo + step], t[lo:lo + step]
+            if on_kernels:
+                logits = torch.nn.functional.linear(xs, weight, bias)
+                ts = ts.contiguous()
+                lse, row_loss = _ce_rows(logits, ts, ignore_index)
+                loss = loss + row_loss.sum() * scale
+                if need[0] or need[1] or need[2]:
+                    g = _ce_grad(logits, ts, lse, coef, ignore_index)
+                    if need[0]:
+                        dx[lo:lo + step] = g @ weight
+                    if need[1]:
+                        dw.add_((g.t() @ xs).float())
+                    if need[2]:
+                        db.add_(g.float().sum(0))
+                continue
             logits = torch.nn.functional.linear(xs, weight, bias).float()
             valid = ts != ignore_index
             safe = torch.where(valid, ts, torch.zeros_like(ts))
@@ -110,32 +154,16 @@ class _FusedCrossEntropy(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, logits, labels, ignore_index, count):
-        lib = _lib.load()
-        rows, vocab = logits.shape
-        with torch.cuda.device(logits.device):
-            lse = torch.empty(rows, dtype=torch.float32, device=logits.device)
-            row_loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
-            a = _lib.CrossEntropyArgs(rows, vocab, logits.data_ptr(), labels.data_ptr(), int(ignore_index),
-                                      lse.data_ptr(), row_loss.data_ptr(), None, None)
-            stream = ctypes.c_void_p(torch.cuda.current_stream(logits.device).cuda_stream)
-            _lib.check(lib.sd_cross_entropy_forward(ctypes.byref(a), stream))
+        lse, row_loss = _ce_rows(logits, labels, ignore_index)
         ctx.save_for_backward(logits, labels, lse, count)
         ctx.ignore_index = int(ignore_index)
         return row_loss.sum() / count
 
     @staticmethod
     def backward(ctx, gout):
-        lib = _lib.load()
         logits, labels, lse, count = ctx.saved_tensors
-        rows, vocab = logits.shape
-        with torch.cuda.device(logits.device):
-            coef = (gout.float() / count).reshape(1).contiguous()
-            dlogits = torch.empty_like(logits)
-            a = _lib.CrossEntropyArgs(rows, vocab, logits.data_ptr(), labels.data_ptr(), ctx.ignore_index,
-                                      lse.data_ptr(), None, coef.data_ptr(), dlogits.data_ptr())
-            stream = ctypes.c_void_p(torch.cuda.current_stream(logits.device).cuda_stream)
-            _lib.check(lib.sd_cross_entropy_backward(ctypes.byref(a), stream))
-        return dlogits, None, None, None
+        coef = (gout.float() / count).reshape(1).contiguous()
+        return _ce_grad(logits, labels, lse, coef, ctx.ignore_index), None, None, None
 
 
 def fused_cross_entropy(logits: torch.Tensor, labels: torch.Tensor, *, ignore_index: int = -100) -> torch.Tensor:
