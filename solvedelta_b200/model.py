@@ -124,8 +124,13 @@ class SolveDelta(nn.Module):
 
     @staticmethod
     def _linear(layer: nn.Linear, x: torch.Tensor) -> torch.Tensor:
-        bias = None if layer.bias is None else layer.bias.to(x.dtype)
-        return F.linear(x, layer.weight.to(x.dtype), bias)
+        weight = layer.weight.to(x.dtype)
+        if layer.bias is None:
+            return F.linear(x, weight)
+        # one GEMM with the bias in its epilogue: on a strided slice of the projection row F.linear would run the
+        # product and a separate element-wise add
+        rows = x.reshape(-1, x.shape[-1])
+        return torch.addmm(layer.bias.to(x.dtype), rows, weight.t()).view(*x.shape[:-1], weight.shape[0])
 
     def _fp32_copy(self, name: str) -> torch.Tensor:
         """Contiguous FP32 copy of a parameter for the fused decode kernel, refreshed when the parameter changes."""
