@@ -174,6 +174,25 @@ typedef struct {
 int sd_pack_rows(const sd_pack_rows_args *args, void *stream);
 
 /*
+ * A projection of a cached single-token step: y [M][N] = x [M][K] weight^T (+ bias) for M <= 4 rows
+ * (nn.Linear layout, BF16, FP32 accumulation), one warp per output column.  With swiglu != 0 the output is
+ * [M][N/2] = silu(y[:, :N/2]) * y[:, N/2:] (the gated MLP's first projection and activation,
+ * causallsso/modeling_solvedelta.py:68-101).  K and x_stride multiples of 8, x and weight 16-byte aligned,
+ * else SD_ERR_UNSUPPORTED_SHAPE (the caller then runs its library GEMM).
+ */
+typedef struct {
+    int32_t M, N, K;
+    int32_t swiglu;
+    const void *x;                     /* BF16 [M][K], rows x_stride elements apart */
+    int64_t x_stride;
+    const void *weight;                /* BF16 [N][K] contiguous */
+    const void *bias;                  /* BF16 [N] or NULL */
+    void *y;                           /* out BF16, rows y_stride elements apart */
+    int64_t y_stride;
+} sd_gemv_args;
+int sd_gemv(const sd_gemv_args *args, void *stream);
+
+/*
  * Cross entropy over BF16 logits, the owner behind fuse_cross_entropy upstream
  * (FusedCrossEntropyLoss, causallsso/modeling_solvedelta.py:469-470).  Forward: per row the log-sum-exp
  * and -log softmax(label), 0 for rows whose label is ignore_index.  Backward: d logits =

@@ -138,6 +138,15 @@ class PackRowsArgs(ctypes.Structure):
                 ("piece", RowPiece * PACK_MAX_PIECES), ("dst", ctypes.c_void_p)]
 
 
+GEMV_MAX_ROWS = 4
+
+
+class GemvArgs(ctypes.Structure):
+    _fields_ = [("M", ctypes.c_int32), ("N", ctypes.c_int32), ("K", ctypes.c_int32), ("swiglu", ctypes.c_int32),
+                ("x", ctypes.c_void_p), ("x_stride", ctypes.c_int64), ("weight", ctypes.c_void_p),
+                ("bias", ctypes.c_void_p), ("y", ctypes.c_void_p), ("y_stride", ctypes.c_int64)]
+
+
 class CrossEntropyArgs(ctypes.Structure):
     _fields_ = [("rows", ctypes.c_int64), ("V", ctypes.c_int32), ("logits", ctypes.c_void_p),
                 ("labels", ctypes.c_void_p), ("ignore_index", ctypes.c_int64), ("lse", ctypes.c_void_p),
@@ -223,7 +232,7 @@ EXPORTS = (
     "sd_chunk_tokens", "sd_forward_static", "sd_panel_kind", "sd_device_fault", "sd_device_fault_clear",
     "sd_predictor_forward", "sd_predictor_backward", "sd_mixer_decode_step", "sd_add_rmsnorm", "sd_swiglu",
     "sd_add_rmsnorm_backward_scratch_bytes", "sd_add_rmsnorm_backward", "sd_swiglu_backward", "sd_pack_rows",
-    "sd_cross_entropy_forward", "sd_cross_entropy_backward",
+    "sd_cross_entropy_forward", "sd_cross_entropy_backward", "sd_gemv",
     "sd_conv4_backward_scratch_bytes", "sd_conv4_silu_forward", "sd_conv4_silu_backward",
     "sd_kda_gate_backward_scratch_bytes", "sd_kda_gate_forward", "sd_kda_gate_backward",
     "sd_norm_gate_backward_scratch_bytes", "sd_norm_gate_forward", "sd_norm_gate_backward",
@@ -298,6 +307,7 @@ def _declare(lib: ctypes.CDLL) -> ctypes.CDLL:
                          ("sd_swiglu", SwigluArgs), ("sd_swiglu_backward", SwigluArgs),
                          ("sd_add_rmsnorm_backward", AddRmsnormBackwardArgs), ("sd_pack_rows", PackRowsArgs),
                          ("sd_cross_entropy_forward", CrossEntropyArgs), ("sd_cross_entropy_backward", CrossEntropyArgs),
+                         ("sd_gemv", GemvArgs),
                          ("sd_conv4_silu_forward", Conv4ForwardArgs), ("sd_conv4_silu_backward", Conv4BackwardArgs),
                          ("sd_kda_gate_forward", KdaGateArgs), ("sd_kda_gate_backward", KdaGateArgs),
                          ("sd_norm_gate_forward", NormGateArgs), ("sd_norm_gate_backward", NormGateArgs)):

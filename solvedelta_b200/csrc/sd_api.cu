@@ -1101,6 +1101,22 @@ int sd_cross_entropy_backward(const sd_cross_entropy_args* a, void* stream_) {
     return launch_status();
 }
 
+int sd_gemv(const sd_gemv_args* a, void* stream_) {
+    if (!a || a->M <= 0 || a->N <= 0 || a->K <= 0 || !a->x || !a->weight || !a->y) return SD_ERR_INVALID_ARGUMENT;
+    if (a->M > GEMV_MAX_ROWS || a->K % 8 != 0 || a->x_stride % 8 != 0 || (a->swiglu && a->N % 2 != 0) ||
+        ((reinterpret_cast<uintptr_t>(a->x) | reinterpret_cast<uintptr_t>(a->weight)) & 15) != 0)
+        return SD_ERR_UNSUPPORTED_SHAPE;
+    GemvParams p{};
+    p.M = a->M; p.N = a->N; p.K = a->K; p.swiglu = a->swiglu ? 1 : 0;
+    p.x = reinterpret_cast<const __nv_bfloat16*>(a->x); p.x_stride = a->x_stride;
+    p.W = reinterpret_cast<const __nv_bfloat16*>(a->weight);
+    p.bias = reinterpret_cast<const __nv_bfloat16*>(a->bias);
+    p.y = reinterpret_cast<__nv_bfloat16*>(a->y); p.y_stride = a->y_stride;
+    const int outs = p.swiglu ? p.N / 2 : p.N;
+    k_gemv<<<(unsigned)((outs + 7) / 8), 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
+    return launch_status();
+}
+
 int sd_pack_rows(const sd_pack_rows_args* a, void* stream_) {
     if (!a || a->rows <= 0 || a->pieces <= 0 || a->pieces > SD_PACK_MAX_PIECES || a->row_width <= 0 || !a->dst)
         return SD_ERR_INVALID_ARGUMENT;

@@ -1163,4 +1163,79 @@ __global__ void __launch_bounds__(256) k_cross_entropy_bwd(CrossEntropyParams p)
     }
 }
 
+// ---- projections of a cached single-token step: y [M][N] = x [M][K] W^T (+ bias), M <= 4 ---------------
+// At one to four rows a projection is a read of its weights: one warp per output column walks its weight row in
+// 16-byte pieces (all loads of a row in flight at once) against the few input rows, FP32 accumulation, one
+// shuffle reduction.  With `swiglu` a warp takes the gate row n and the value row n + N/2 and writes
+// silu(gate) * value (the gated MLP's first projection and its activation in one launch).
+constexpr int GEMV_MAX_ROWS = 4;
+struct GemvParams {
+    int M, N, K, swiglu;
+    const __nv_bfloat16* x;
+    long long x_stride;
+    const __nv_bfloat16* W;
+    const __nv_bfloat16* bias;
+    __nv_bfloat16* y;
+    long long y_stride;
+};
+
+__device__ __forceinline__ void gemv_row(const GemvParams& p, const __nv_bfloat16* w, int lane, float (&acc)[GEMV_MAX_ROWS]) {
+#pragma unroll
+    for (int m = 0; m < GEMV_MAX_ROWS; ++m) acc[m] = 0.f;
+    // four 16-byte pieces of the weight row are requested together (pinned: the compiler would sink each load to its
+    // use and leave one in flight per lane), then worked on
+    for (int kb = lane * 8; kb < p.K; kb += 4 * 256) {
+        uint4 raw[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            raw[q] = kb + q * 256 < p.K ? load16_pinned(w + kb + q * 256) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int k0 = kb + q * 256;
+            if (k0 >= p.K) break;
+            float wv[8];
+            norm_unpack8(raw[q], wv);
+#pragma unroll
+            for (int m = 0; m < GEMV_MAX_ROWS; ++m) {
+                if (m < p.M) {
+                    float xv[8];
+                    norm_unpack8(*reinterpret_cast<const uint4*>(p.x + m * p.x_stride + k0), xv);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[m] = fmaf(wv[e], xv[e], acc[m]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < GEMV_MAX_ROWS; ++m)
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], s);
+}
+
+__global__ void __launch_bounds__(256) k_gemv(GemvParams p) {
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int outs = p.swiglu ? p.N / 2 : p.N;
+    if (n >= outs) return;
+    float a[GEMV_MAX_ROWS], b[GEMV_MAX_ROWS];
+    gemv_row(p, p.W + (long long)n * p.K, lane, a);
+    if (p.swiglu) gemv_row(p, p.W + (long long)(n + outs) * p.K, lane, b);
+    if (lane == 0) {
+#pragma unroll
+        for (int m = 0; m < GEMV_MAX_ROWS; ++m) {
+            if (m < p.M) {
+                float v = a[m] + (p.bias != nullptr ? __bfloat162float(p.bias[n]) : 0.f);
+                if (p.swiglu) {
+                    // both halves rounded to BF16 first, as the separate projection stores them
+                    const float g = __bfloat162float(__float2bfloat16_rn(v));
+                    const float u = __bfloat162float(__float2bfloat16_rn(
+                        b[m] + (p.bias != nullptr ? __bfloat162float(p.bias[n + outs]) : 0.f)));
+                    v = silu_f(g) * u;
+                }
+                p.y[m * p.y_stride + n] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+}
+
 }  // namespace sd

@@ -343,6 +343,37 @@ def swiglu(gate_value: torch.Tensor) -> torch.Tensor:
     return _swiglu_forward(gate_value.contiguous())
 
 
+def small_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, *,
+                 swiglu: bool = False) -> Optional[torch.Tensor]:
+    """``F.linear(x, weight, bias)`` for the one to four rows of a cached single-token step (inference only), one warp
+    per output column; with ``swiglu`` the result is ``silu(y[..., :N/2]) * y[..., N/2:]``.  Returns ``None`` when the
+    call is not one the kernel takes (gradients recorded, more rows, not BF16 CUDA, unaligned), and the caller runs
+    its library projection."""
+    if torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad):
+        return None
+    K = x.shape[-1]
+    if (x.device.type != "cuda" or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or weight.ndim != 2
+            or weight.shape[1] != K or not weight.is_contiguous() or weight.device != x.device or K % 8
+            or (bias is not None and (bias.dtype != torch.bfloat16 or not bias.is_contiguous()))):
+        return None
+    rows = x.numel() // K
+    if rows < 1 or rows > _lib.GEMV_MAX_ROWS or x.stride(-1) != 1:
+        return None
+    x2 = x.reshape(rows, K)   # a view for the layouts a decode step produces; a copy of a few KB otherwise
+    stride = x2.stride(0) if rows > 1 else K
+    N = weight.shape[0]
+    if stride % 8 or x2.data_ptr() % 16 or weight.data_ptr() % 16 or (swiglu and N % 2):
+        return None
+    lib = _lib.load()
+    width = N // 2 if swiglu else N
+    with torch.cuda.device(x.device):
+        out = torch.empty(*x.shape[:-1], width, dtype=torch.bfloat16, device=x.device)
+        a = _lib.GemvArgs(rows, N, K, 1 if swiglu else 0, x2.data_ptr(), stride, weight.data_ptr(),
+                          bias.data_ptr() if bias is not None else None, out.data_ptr(), width)
+        _lib.check(lib.sd_gemv(ctypes.byref(a), _stream(x.device)))
+    return out
+
+
 def pack_rows(pieces, widths, row_shape, device) -> Optional[torch.Tensor]:
     """One BF16 row-shaped tensor ``[..., P]`` holding ``pieces`` side by side (``None``: zeros; columns past the
     last piece: zeros), written by one kernel; ``None`` when the layout is not one the kernel takes (widths in whole

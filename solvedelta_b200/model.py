@@ -25,7 +25,7 @@ from torch import nn
 
 from .config import SolveDeltaConfig
 from .mixer_ops import (conv4_silu, kda_decay_gate, mixer_decode_step, pack_rows, rms_norm_gated,
-                        rms_norm_gated_linear)
+                        rms_norm_gated_linear, small_linear)
 from .ops import SolveDeltaState, solvedelta_masked_native, solvedelta_native
 
 
@@ -125,6 +125,9 @@ class SolveDelta(nn.Module):
     @staticmethod
     def _linear(layer: nn.Linear, x: torch.Tensor) -> torch.Tensor:
         weight = layer.weight.to(x.dtype)
+        small = small_linear(x, weight, None if layer.bias is None else layer.bias.to(x.dtype))
+        if small is not None:   # the few rows of a cached single-token step
+            return small
         if layer.bias is None:
             return F.linear(x, weight)
         # one GEMM with the bias in its epilogue: on a strided slice of the projection row F.linear would run the

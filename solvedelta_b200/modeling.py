@@ -24,7 +24,7 @@ from transformers.modeling_outputs import BaseModelOutputWithPast, CausalLMOutpu
 from . import _lib
 from .config import SolveDeltaConfig
 from .ops import SolveDeltaState
-from .mixer_ops import add_rmsnorm, add_rmsnorm_reverse_supported, swiglu
+from .mixer_ops import add_rmsnorm, add_rmsnorm_reverse_supported, small_linear, swiglu
 from .model import SolveDelta, SolveDeltaLayerState
 
 FP32_PARAMETERS = ("geometry_write_bias", "associative_log_rate", "associative_decay_bias")
@@ -130,7 +130,12 @@ class SolveDeltaMLP(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.hidden_act == "swish" and x.is_cuda and x.dtype == torch.bfloat16:
-            return self.down_proj(swiglu(self.gate_up_proj(x)))   # activation and product in one kernel
+            # a cached single-token step: projection + activation in one launch, then the second projection
+            act = small_linear(x, self.gate_up_proj.weight, self.gate_up_proj.bias, swiglu=True)
+            if act is None:
+                act = swiglu(self.gate_up_proj(x))   # activation and product in one kernel
+            out = small_linear(act, self.down_proj.weight, self.down_proj.bias)
+            return out if out is not None else self.down_proj(act)
         gate, value = self.gate_up_proj(x).chunk(2, dim=-1)
         if self.hidden_act == "swish":
             activated = F.silu(gate)

@@ -47,6 +47,7 @@ def test_struct_sizes_match_header():
     assert ctypes.sizeof(_lib.SwigluArgs) == 16 + 4 * 8
     assert ctypes.sizeof(_lib.RowPiece) == 16
     assert ctypes.sizeof(_lib.CrossEntropyArgs) == 16 + 7 * 8
+    assert ctypes.sizeof(_lib.GemvArgs) == 16 + 6 * 8
     assert ctypes.sizeof(_lib.PackRowsArgs) == 16 + 12 * 16 + 8
 
 

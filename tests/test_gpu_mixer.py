@@ -523,3 +523,27 @@ def test_pack_rows_writes_the_slices_side_by_side():
     assert torch.equal(row, want)
     # layouts the kernel does not take are left to the caller
     assert pack_rows([pieces[0][..., :5]], (5,), (3, 37, 8), torch.device("cuda", 0)) is None
+
+
+@pytest.mark.parametrize("rows,K,N,swiglu_on,with_bias", [(1, 1024, 7488, False, False), (4, 2816, 1024, False, True),
+                                                          (2, 1024, 5632, True, False), (3, 64, 24, True, True)])
+def test_small_linear_matches_the_library_projection(rows, K, N, swiglu_on, with_bias):
+    from solvedelta_b200.mixer_ops import small_linear
+
+    gen = torch.Generator().manual_seed(rows + K + N)
+    wide = torch.randn(rows, 1, K + 64, generator=gen).to(torch.bfloat16).cuda()
+    x = wide[..., 8:8 + K]                      # a strided view, as a slice of the projection row is
+    w = (torch.randn(N, K, generator=gen) / K ** 0.5).to(torch.bfloat16).cuda()
+    b = torch.randn(N, generator=gen).to(torch.bfloat16).cuda() if with_bias else None
+    with torch.no_grad():
+        got = small_linear(x, w, b, swiglu=swiglu_on)
+        want = torch.nn.functional.linear(x.float(), w.float(), b.float() if with_bias else None)
+        if swiglu_on:
+            g, v = want.to(torch.bfloat16).float().chunk(2, dim=-1)
+            want = torch.nn.functional.silu(g) * v
+    assert got is not None and got.shape == want.shape and got.dtype == torch.bfloat16
+    assert float((got.float() - want).abs().max()) <= 1e-2 * float(want.abs().max()) + 1e-3
+    with torch.no_grad():   # layouts the kernel does not take are left to the caller
+        assert small_linear(torch.zeros(5, K, dtype=torch.bfloat16, device="cuda"), w) is None
+        assert small_linear(x.float(), w) is None
+    assert small_linear(x.clone().requires_grad_(), w) is None
