@@ -82,7 +82,7 @@ __device__ __forceinline__ float decode_conv_channel(const MixerDecode& m, int b
 
 constexpr int DEC_THREADS = 512;
 constexpr int DEC_LD = DP + 4;   // row pitch of a shared state (floats)
-constexpr size_t DECODE_SMEM = (size_t(2) * DP * DEC_LD + 12 * DP + 32) * sizeof(float);
+constexpr size_t DECODE_SMEM = (size_t(2) * DP * DEC_LD + 12 * DP + 96) * sizeof(float);
 
 // sum over the first DP threads' values (the others pass 0), returned to every thread
 __device__ __forceinline__ float block_sum(float v, float* red) {
@@ -95,6 +95,28 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 #pragma unroll
     for (int w = 0; w < DEC_THREADS / 32; ++w) t += red[w];
     return t;
+}
+
+// N sums at once (one pair of barriers for all of them); red holds [N][16] floats
+template <int N>
+__device__ __forceinline__ void block_sum_n(float (&v)[N], float* red) {
+#pragma unroll
+    for (int n = 0; n < N; ++n)
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) v[n] += __shfl_xor_sync(0xffffffffu, v[n], m);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) {
+#pragma unroll
+        for (int n = 0; n < N; ++n) red[n * (DEC_THREADS / 32) + (threadIdx.x >> 5)] = v[n];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int n = 0; n < N; ++n) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < DEC_THREADS / 32; ++w) t += red[n * (DEC_THREADS / 32) + w];
+        v[n] = t;
+    }
 }
 
 // [rows][cols] FP32 state in global memory (row pitch `cols`) -> shared [DP][DEC_LD], zero padded
@@ -139,7 +161,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(DecodeParams p, 
     float* s_d = s_chi + DP;
     float* s_w = s_d + DP;
     float* s_part = s_w + DP;              // [4][DP] partial column sums
-    float* red = s_part + 4 * DP;          // [16]
+    float* red = s_part + 4 * DP;          // [5][16] (block_sum_n)
     const int s = blockIdx.x, b = s / p.g.H, hh = s - b * p.g.H;
     const int r = p.g.r, V = p.g.V, tid = threadIdx.x;
     Chunk ch;
@@ -197,9 +219,13 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(DecodeParams p, 
         ld = in_r ? row_f32(p.ld, ch, 0)[tid] : 0.f;
         gamma = *row_f32(p.gam, ch, 0);
     }
-    const float uh = u * rsqrtf(block_sum(u * u, red) + 1e-24f);
-    const float kh = k * rsqrtf(block_sum(k * k, red) + 1e-24f);
-    const float qh = q * rsqrtf(block_sum(q * q, red) + 1e-24f);
+    // the three norms and the two dot products that only need them, in one reduction
+    const float se = sigmoidf_(er);
+    float sums[5] = {u * u, k * k, q * q, u * se * k, u * q};
+    block_sum_n<5>(sums, red);
+    const float rs_u = rsqrtf(sums[0] + 1e-24f), rs_k = rsqrtf(sums[1] + 1e-24f), rs_q = rsqrtf(sums[2] + 1e-24f);
+    const float uh = u * rs_u, kh = k * rs_k, qh = q * rs_q;
+    const float dot_ub = sums[3] * rs_u * rs_k, dot_uq = sums[4] * rs_u * rs_q;   // u^ . (sigma(e) k^),  u^ . q^
     if (tid < DP) {
         s_uh[tid] = uh;
         s_kh[tid] = kh;
@@ -225,13 +251,15 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(DecodeParams p, 
     const float delta = in_r ? gamma * (hv - s_delta[tid]) : 0.f;
     __syncthreads();
     if (tid < DP) s_delta[tid] = delta;
-    const float n2 = block_sum(delta * delta, red);
+    float two[2] = {delta * delta, delta * uh};
+    block_sum_n<2>(two, red);
+    const float n2 = two[0];
     const float fs = RHO * rsqrtf(RHO * RHO + n2);
     const float phi = fs * delta;
-    const float den = 1.f + block_sum(phi * uh, red);
-    const float bb = sigmoidf_(er) * kh;
-    const float sb = block_sum(uh * bb, red) / den;
-    const float sq = block_sum(uh * qh, red) / den;
+    const float den = 1.f + fs * two[1];
+    const float bb = se * kh;
+    const float sb = dot_ub / den;
+    const float sq = dot_uq / den;
     if (tid < DP) {
         s_e[tid] = bb - phi * sb;
         s_chi[tid] = qh - phi * sq;
