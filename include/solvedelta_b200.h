@@ -246,7 +246,7 @@ typedef struct {
     int64_t output_gate_stride_b;
     /* optional, both or neither (then decay_raw / output_gate above may be NULL): the two small
      * projections in front of the gates, raw = BF16(W hidden (+ bias)) (causallsso/model.py:369-374);
-     * gate_rank a multiple of 8, at most 128; weights 16-byte aligned; needs the fused norm */
+     * gate_rank a multiple of 16, at most 128; weights 16-byte aligned; needs the fused norm */
     int32_t gate_rank;
     const void *decay_hidden;           /* BF16 [B][gate_rank] */
     int64_t decay_hidden_stride_b;

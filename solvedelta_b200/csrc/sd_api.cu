@@ -1214,7 +1214,7 @@ int sd_mixer_decode_step(const sd_mixer_decode_args* a, void* stream_) {
     if ((m.decay_w != nullptr) != (m.gate_w != nullptr)) return SD_ERR_INVALID_ARGUMENT;   // both or neither
     if (m.decay_w != nullptr) {
         auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-        if (m.G <= 0 || m.G > DP || (m.G & 7) || !m.decay_hidden || !m.gate_hidden || !al(m.decay_w) || !al(m.gate_w))
+        if (m.G <= 0 || m.G > DP || (m.G & 15) || !m.decay_hidden || !m.gate_hidden || !al(m.decay_w) || !al(m.gate_w))
             return SD_ERR_INVALID_ARGUMENT;
         if (m.norm_w == nullptr) return SD_ERR_INVALID_ARGUMENT;   // the fused gate projection feeds the fused norm
     } else if (m.decay_raw == nullptr) {

@@ -54,19 +54,25 @@ struct MixerDecode {
     long long gh_sb;
 };
 
-// BF16(w_row . hidden (+ bias)) with FP32 accumulation; hidden [G] FP32 in shared memory, G a multiple of 8
-__device__ __forceinline__ float decode_row_dot(const __nv_bfloat16* w_row, const float* hidden, int G, float bias) {
-    float acc = 0.f;
-    for (int j = 0; j < G; j += 8) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(w_row + j);
-        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+// Partial dot of up to 64 weights (BF16, 16-byte aligned) with `hidden`: every piece of the weight row is requested
+// before any is used (pinned loads: a loop of load-then-multiply waits for memory once per piece).
+__device__ __forceinline__ float decode_row_dot_pinned(const __nv_bfloat16* w, const float* hidden, int span) {
+    uint4 raw[8];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(h2[e]);
-            acc = fmaf(f.x, hidden[j + 2 * e], fmaf(f.y, hidden[j + 2 * e + 1], acc));
+    for (int q = 0; q < 8; ++q) raw[q] = q * 8 < span ? load16_pinned(w + q * 8) : make_uint4(0u, 0u, 0u, 0u);
+    float acc = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        if (q * 8 < span) {
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[q]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(h2[e]);
+                acc = fmaf(f.x, hidden[q * 8 + 2 * e], fmaf(f.y, hidden[q * 8 + 2 * e + 1], acc));
+            }
         }
     }
-    return __bfloat162float(__float2bfloat16_rn(acc + bias));
+    return acc;
 }
 
 // one conv channel of the token: output (rounded to BF16 as the separate conv kernel stores it), window advanced
@@ -195,10 +201,30 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k_decode_step(DecodeParams p, 
                                                    : mix.decay_hidden[(long long)b * mix.dh_sb + jj]);
             }
             __syncthreads();
-            if (in_r) decay_raw_mix = decode_row_dot(mix.decay_w + (long long)(hh * r + tid) * mix.G, s_hid, mix.G, 0.f);
-            if (tid < V)
-                gate_mix = decode_row_dot(mix.gate_w + (long long)(hh * V + tid) * mix.G, s_hid + mix.G, mix.G,
-                                          mix.gate_b ? __bfloat162float(mix.gate_b[hh * V + tid]) : 0.f);
+            {
+                // two threads per output (r decay rows, then V gate rows: all 512 threads at r = V = 128), each half
+                // of the row's G weights; the pair adds up through a shuffle and leaves the BF16-rounded value in
+                // shared memory for the thread that owns the channel
+                float* s_proj = s_part + 2 * mix.G;   // [r + V], behind the hidden rows (G <= 128)
+                const int row2 = tid >> 1, half = tid & 1, span = mix.G / 2;
+                const bool is_gate = row2 >= r;
+                const int rr = is_gate ? row2 - r : row2;
+                const bool live = rr < (is_gate ? V : r);
+                float part = 0.f;
+                if (live) {
+                    const __nv_bfloat16* w = is_gate ? mix.gate_w + (long long)(hh * V + rr) * mix.G
+                                                     : mix.decay_w + (long long)(hh * r + rr) * mix.G;
+                    part = decode_row_dot_pinned(w + half * span, s_hid + (is_gate ? mix.G : 0) + half * span, span);
+                }
+                part += __shfl_xor_sync(0xffffffffu, part, 1);
+                if (live && half == 0) {
+                    const float bias = is_gate && mix.gate_b ? __bfloat162float(mix.gate_b[hh * V + rr]) : 0.f;
+                    s_proj[row2] = __bfloat162float(__float2bfloat16_rn(part + bias));
+                }
+                __syncthreads();
+                if (in_r) decay_raw_mix = s_proj[tid];
+                if (tid < V) gate_mix = s_proj[r + tid];
+            }
             __syncthreads();   // s_part is reused below
         }
         if (in_r) {

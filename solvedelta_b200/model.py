@@ -214,7 +214,7 @@ class SolveDelta(nn.Module):
             # cache's conv window and operator states updated in place
             dw, gw, gb = self.decay_proj.weight, self.output_gate_proj.weight, self.output_gate_proj.bias
             in_kernel = (dw.dtype == gw.dtype == torch.bfloat16 and dw.is_contiguous() and gw.is_contiguous()
-                         and gb.dtype == torch.bfloat16 and dw.shape[1] % 8 == 0 and dw.shape[1] <= 128)
+                         and gb.dtype == torch.bfloat16 and dw.shape[1] % 16 == 0 and dw.shape[1] <= 128)
             if in_kernel:   # the two small projections in front of the gates run inside the kernel too
                 associative_raw = output_gate = None
                 projections = (piece(8), dw.detach(), piece(9), gw.detach(), gb.detach())
