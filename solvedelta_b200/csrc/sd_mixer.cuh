@@ -764,10 +764,11 @@ __global__ void __launch_bounds__(256, 3) k_norm_gate_bwd(NormParams p) {
     }
 }
 
-// ---- inference glue of the block around the mixer (no reverse pass) ------------------------
+// ---- glue of the block around the mixer -----------------------------------------------------
 // sum = x + delta (the residual stream, rounded to BF16 as the separate add stores it) and
 // normed = sum rsqrt(mean(sum^2) + eps) w: the residual add and the RMSNorm that follows it
-// (causallsso/modeling_solvedelta.py:230-255) in one pass.  One CTA per row.
+// (causallsso/modeling_solvedelta.py:230-255) in one pass.  k_add_rmsnorm: one CTA per row, any width (the few rows
+// of a single-token step); k_add_rmsnorm_rows / k_add_rmsnorm_bwd below: one warp per row, forward and reverse.
 struct AddNormParams {
     long long N;
     int D;
