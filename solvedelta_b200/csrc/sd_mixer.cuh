@@ -7,6 +7,7 @@
 // [B,D,3] state), model.py:375-390 (decay gate -exp(A) softplus(raw + bias)),
 // causallsso/ops/norm_gate.py:19-43 (y = x rstd w sigmoid(gate)).
 #pragma once
+#include <type_traits>
 #include "sd_common.cuh"
 
 namespace sd {
@@ -187,22 +188,24 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv4_silu_bwd(ConvParams p) {
         };
 #pragma unroll
         for (int k = 0; k < CONV_RING; ++k) issue(t0 + k);
-#pragma unroll 4
-        for (int t = t0; t < t_end + 3; ++t) {
+        // one token: INNER = a token of the tile with the whole tile's length behind it and three tokens of the tile
+        // before it (every bound below holds, so none is tested)
+        auto token = [&](int t, auto inner_tag) {
+            constexpr bool INNER = decltype(inner_tag)::value;
             asm volatile("cp.async.wait_group %0;" ::"n"(CONV_RING - 1));
             float2 x3 = make_float2(0.f, 0.f), gy = x3;
-            if (t < t_last) {
+            if (INNER || t < t_last) {
                 x3 = conv_ring_pair(ring_x[(t - t0) % CONV_RING][threadIdx.x]);
                 gy = conv_ring_pair(ring_g[(t - t0) % CONV_RING][threadIdx.x]);
             }
             issue(t + CONV_RING);
             float2 g3 = make_float2(0.f, 0.f);
-            if (t < p.T) {
+            if (INNER || t < p.T) {
                 const float za = wa[0] * x0.x + wa[1] * x1.x + wa[2] * x2.x + wa[3] * x3.x;
                 const float zb = wb[0] * x0.y + wb[1] * x1.y + wb[2] * x2.y + wb[3] * x3.y;
                 g3.x = gy.x * silu_grad_f(za);
                 g3.y = gy.y * silu_grad_f(zb);
-                if (t < t_end) {  // weight gradient: own tile only
+                if (INNER || t < t_end) {  // weight gradient: own tile only
                     dwa[0] += g3.x * x0.x; dwa[1] += g3.x * x1.x; dwa[2] += g3.x * x2.x; dwa[3] += g3.x * x3.x;
                     dwb[0] += g3.y * x0.y; dwb[1] += g3.y * x1.y; dwb[2] += g3.y * x2.y; dwb[3] += g3.y * x3.y;
                 }
@@ -210,7 +213,7 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv4_silu_bwd(ConvParams p) {
             const int tq = t - 3;  // the input whose gradient is now complete
             const float da = wa[0] * g3.x + wa[1] * g2.x + wa[2] * g1.x + wa[3] * g0.x;
             const float db = wb[0] * g3.y + wb[1] * g2.y + wb[2] * g1.y + wb[3] * g0.y;
-            if (tq >= t0 && tq < t_end) {
+            if (INNER || (tq >= t0 && tq < t_end)) {
                 store_pair<PAIR>(dxout + (long long)tq * p.D, two, da, db);
             } else if (tq < 0 && t0 == 0 && p.dinit != nullptr) {
                 __nv_bfloat16* sd = p.dinit + ((long long)b * p.D + d) * 3 + (tq + 3);
@@ -219,7 +222,12 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv4_silu_bwd(ConvParams p) {
             }
             x0 = x1; x1 = x2; x2 = x3;
             g0 = g1; g1 = g2; g2 = g3;
-        }
+        };
+        const int head_end = min(t0 + 3, t_end + 3);
+        for (int t = t0; t < head_end; ++t) token(t, std::false_type{});
+#pragma unroll 4
+        for (int t = t0 + 3; t < t_end; ++t) token(t, std::true_type{});
+        for (int t = max(t0 + 3, t_end); t < t_end + 3; ++t) token(t, std::false_type{});
     } else
     for (int ts = t0; ts < t_end + 3; ts += CONV_BATCH_BWD) {
         float2 xs[CONV_BATCH_BWD], gs[CONV_BATCH_BWD];
